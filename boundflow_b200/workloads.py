@@ -1,0 +1,202 @@
+"""Seeded synthetic verification workloads (networks, input boxes, margin specs, ReLU splits).
+
+Five configurations, all fp32 and generated on the CPU so that every consumer
+(the CUDA backend, the CPU oracle, the reference itself) sees identical bits:
+
+  c1  MLP 784-100-100-10,            64 inputs,  eps 0.02,  IBP + CROWN
+  c2  CNN 1x28x28 [16k4s2p1, 32k4s2p1, fc100, fc10], 256 inputs, eps 0.1, CROWN with CROWN intermediates
+  c3  MLP 784-256x5-10,              128 inputs, eps 0.015, alpha-CROWN 20 steps lr 0.1
+  c4  MLP 784-512x4-10,              1 input, eps 0.02, batches of 8192 ReLU-split subdomains, 10 alpha steps
+  c5  CNN 3x32x32 [32k3s1p1, 32k4s2p1, 64k3s1p1, 64k4s2p1, fc512, fc10], 64 inputs, eps 2/255
+
+Inputs are uniform [0,1] tensors shaped like MNIST / CIFAR images (no dataset
+items are used); weights are He-normal, biases N(0, 0.1^2); the input set is the
+L-inf ball clipped to [0,1], i.e. a per-element box; the 9 spec rows per input
+are logit[y] - logit[j], j != y, with y the clean arg-max.
+
+The module layout mirrors the reference's hand-built test fixtures
+(tests/test_phase6b_crown_ibp_mlp.py:10-27 in the reference): a single
+INTERVAL_IBP task whose ops are linear/conv2d/relu/flatten with parameters in
+`module.bindings["params"]`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .ir import BFTaskModule, BoundTask, TaskKind, TaskOp
+
+
+@dataclass
+class NetSpec:
+    input_shape: Tuple[int, ...]
+    # ("conv", out_ch, k, stride, pad) | ("fc", out)
+    body: Sequence[tuple]
+
+
+NETS: Dict[str, NetSpec] = {
+    "c1": NetSpec((784,), [("fc", 100), ("fc", 100), ("fc", 10)]),
+    "c2": NetSpec((1, 28, 28), [("conv", 16, 4, 2, 1), ("conv", 32, 4, 2, 1), ("fc", 100), ("fc", 10)]),
+    "c3": NetSpec((784,), [("fc", 256)] * 5 + [("fc", 10)]),
+    "c4": NetSpec((784,), [("fc", 512)] * 4 + [("fc", 10)]),
+    "c5": NetSpec(
+        (3, 32, 32),
+        [("conv", 32, 3, 1, 1), ("conv", 32, 4, 2, 1), ("conv", 64, 3, 1, 1), ("conv", 64, 4, 2, 1), ("fc", 512), ("fc", 10)],
+    ),
+}
+DEFAULTS = {
+    "c1": dict(batch=64, eps=0.02),
+    "c2": dict(batch=256, eps=0.1),
+    "c3": dict(batch=128, eps=0.015),
+    "c4": dict(batch=1, eps=0.02),
+    "c5": dict(batch=64, eps=2.0 / 255.0),
+}
+SEEDS = {"c1": 1001, "c2": 1002, "c3": 1003, "c4": 1004, "c5": 1005}
+
+
+@dataclass
+class Workload:
+    name: str
+    module: BFTaskModule
+    layers: List[dict]            # chain description (op dicts holding CPU tensors)
+    x: torch.Tensor               # [B, *input_shape]
+    lo: torch.Tensor              # clipped box lower
+    up: torch.Tensor              # clipped box upper
+    C: torch.Tensor               # [B, 9, 10]
+    labels: torch.Tensor          # [B]
+    eps: float
+    relu_names: List[str] = field(default_factory=list)
+    generator: Optional[torch.Generator] = None
+
+
+def build_chain(spec: NetSpec, g: torch.Generator, *, scale: Optional[Sequence[int]] = None):
+    """Draw the parameters in layer order and return (layers, module)."""
+    layers: List[dict] = []
+    ops: List[TaskOp] = []
+    params: Dict[str, torch.Tensor] = {}
+    shape = tuple(spec.input_shape)
+    cur = "input"
+    relu_names: List[str] = []
+    body = list(spec.body)
+    for k, item in enumerate(body, start=1):
+        last = k == len(body)
+        if item[0] == "conv":
+            _, oc, ks, st, pd = item
+            ic, h, w = shape
+            fan_in = ic * ks * ks
+            W = torch.randn((oc, ic, ks, ks), generator=g) * math.sqrt(2.0 / fan_in)
+            b = torch.randn((oc,), generator=g) * 0.1
+            ho = (h + 2 * pd - ks) // st + 1
+            wo = (w + 2 * pd - ks) // st + 1
+            layers.append({"op": "conv2d", "W": W, "b": b, "stride": (st, st), "padding": (pd, pd)})
+            out = f"h{k}"
+            ops.append(TaskOp("conv2d", f"conv{k}", [cur, f"W{k}", f"b{k}"], [out], {"stride": (st, st), "padding": (pd, pd)}))
+            shape = (oc, ho, wo)
+        else:
+            if len(shape) == 3:
+                layers.append({"op": "flatten"})
+                flat = f"f{k}"
+                ops.append(TaskOp("flatten", f"flatten{k}", [cur], [flat], {"start_dim": 1, "end_dim": -1}))
+                cur = flat
+                shape = (shape[0] * shape[1] * shape[2],)
+            n_out = int(item[1])
+            fan_in = shape[0]
+            W = torch.randn((n_out, fan_in), generator=g) * math.sqrt(2.0 / fan_in)
+            b = torch.randn((n_out,), generator=g) * 0.1
+            layers.append({"op": "linear", "W": W, "b": b})
+            out = "out" if last else f"h{k}"
+            ops.append(TaskOp("linear", f"linear{k}", [cur, f"W{k}", f"b{k}"], [out]))
+            shape = (n_out,)
+        params[f"W{k}"] = W
+        params[f"b{k}"] = b
+        cur = out
+        if not last:
+            layers.append({"op": "relu"})
+            relu_names.append(cur)
+            ops.append(TaskOp("relu", f"relu{k}", [cur], [f"r{k}"]))
+            cur = f"r{k}"
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    module = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": params})
+    return layers, module, relu_names
+
+
+def clean_forward(layers: List[dict], x: torch.Tensor) -> torch.Tensor:
+    import torch.nn.functional as F
+
+    for layer in layers:
+        op = layer["op"]
+        if op == "linear":
+            x = x.matmul(layer["W"].t()) + layer["b"]
+        elif op == "conv2d":
+            x = F.conv2d(x, layer["W"], layer["b"], layer["stride"], layer["padding"])
+        elif op == "relu":
+            x = torch.relu(x)
+        elif op == "flatten":
+            x = x.flatten(1)
+    return x
+
+
+def margin_specs(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """C[b,k,:] = e_y - e_j for the k-th j != y in ascending j."""
+    B, O = logits.shape
+    y = logits.argmax(dim=1)
+    C = torch.zeros(B, O - 1, O, dtype=logits.dtype)
+    for b in range(B):
+        k = 0
+        for j in range(O):
+            if j == int(y[b]):
+                continue
+            C[b, k, int(y[b])] = 1.0
+            C[b, k, j] = -1.0
+            k += 1
+    return C, y
+
+
+def make_workload(name: str, *, batch: Optional[int] = None, eps: Optional[float] = None, net: Optional[NetSpec] = None, seed: Optional[int] = None) -> Workload:
+    """Build configuration `name` (c1..c5); `batch` draws only the first inputs
+    of the same stream so a reduced batch is a prefix of the full one."""
+    spec = net or NETS[name]
+    d = DEFAULTS[name]
+    full_batch = int(d["batch"])
+    B = int(batch) if batch is not None else full_batch
+    e = float(eps) if eps is not None else float(d["eps"])
+    g = torch.Generator("cpu").manual_seed(int(seed) if seed is not None else SEEDS[name])
+    layers, module, relu_names = build_chain(spec, g)
+    x_full = torch.rand((max(B, full_batch),) + tuple(spec.input_shape), generator=g)
+    x = x_full[:B].contiguous()
+    logits = clean_forward(layers, x)
+    C, y = margin_specs(logits)
+    lo = torch.clamp(x - e, min=0.0)
+    up = torch.clamp(x + e, max=1.0)
+    return Workload(name=name, module=module, layers=layers, x=x, lo=lo, up=up, C=C, labels=y, eps=e, relu_names=relu_names, generator=g)
+
+
+def make_split_domains(wl: Workload, root_pre: Sequence[Tuple[torch.Tensor, torch.Tensor]], *, n_domains: int, n_split: int = 10) -> List[torch.Tensor]:
+    """ReLU-split subdomains of the single-input configuration (c4).
+
+    `root_pre` are the root's pre-activation bounds per ReLU ([1,n_k] each).
+    For every domain, `n_split` neurons are drawn without replacement from the
+    root's unstable set (l<0<u) and assigned active(+1)/inactive(-1) with equal
+    probability.  Returns one int8 [n_domains, n_k] tensor per ReLU.  Draws
+    continue the workload's generator stream, so they are reproducible.
+    """
+    g = wl.generator
+    unstable: List[Tuple[int, int]] = []
+    for r, (l, u) in enumerate(root_pre):
+        lf, uf = l.reshape(-1), u.reshape(-1)
+        idx = torch.nonzero((lf < 0) & (uf > 0)).flatten().tolist()
+        unstable.extend((r, j) for j in idx)
+    if len(unstable) < n_split:
+        raise ValueError(f"only {len(unstable)} unstable neurons at the root, need {n_split}")
+    splits = [torch.zeros(n_domains, l.reshape(-1).shape[0], dtype=torch.int8) for l, _ in root_pre]
+    U = len(unstable)
+    for d in range(n_domains):
+        pick = torch.randperm(U, generator=g)[:n_split].tolist()
+        sign = torch.rand(n_split, generator=g) < 0.5
+        for t, p in enumerate(pick):
+            r, j = unstable[p]
+            splits[r][d, j] = 1 if bool(sign[t]) else -1
+    return splits

@@ -1,0 +1,564 @@
+"""CPU restatement of BoundFlow's IBP -> CROWN -> concretise -> alpha-CROWN path.
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA kernels: the
+test-suite, the smoke check and the benchmark's CPU-baseline leg may import it;
+nothing in the shipped package does.  It uses plain torch CPU tensor ops (the
+reference's own arithmetic library), is dtype generic (float32 / float64) and
+follows the reference function by function; every function cites the reference
+file:line it restates (paths are relative to the reference project root).
+
+Parity status: PINNED.  `tests/golden/make_golden.py` runs the reference's own
+functions (imported from the reference checkout) on seeded inputs and stores
+their outputs under `tests/golden/*.npz`; `tests/test_oracle_golden.py` checks
+this restatement against those vectors and against the literal known-answer
+cases the reference's tests hold.
+
+Network description used throughout: a chain `layers`, a list of dicts
+  {"op": "linear", "W": [out,in], "b": [out] or None}
+  {"op": "conv2d", "W": [O,I,kh,kw], "b": [O] or None, "stride": (sh,sw), "padding": (ph,pw)}
+  {"op": "relu"}
+  {"op": "flatten"}
+The input set is a per-element box [lo, up] (an L-inf ball is the box
+[x0-eps, x0+eps] with midpoint x0 and radius eps, see `linf_box`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+Layers = List[dict]
+
+
+# ----------------------------------------------------------------------------
+# input sets
+# ----------------------------------------------------------------------------
+@dataclass
+class InputSet:
+    """Midpoint/radius view of the input perturbation set.
+
+    Box: perturbation.py:297-298 and 345-346 (`midpoint=(lower+upper)/2`,
+    `radius=(upper-lower)/2`).  L-inf ball: perturbation.py:201-215 uses the
+    centre itself and the scalar eps.
+    """
+
+    mid: torch.Tensor
+    rad: torch.Tensor
+    lo: torch.Tensor
+    up: torch.Tensor
+
+
+def box_input(lo: torch.Tensor, up: torch.Tensor) -> InputSet:
+    return InputSet(mid=(lo + up) / 2.0, rad=(up - lo) / 2.0, lo=lo, up=up)
+
+
+def linf_box(x0: torch.Tensor, eps: float) -> InputSet:
+    rad = torch.full_like(x0, float(eps))
+    return InputSet(mid=x0, rad=rad, lo=x0 - float(eps), up=x0 + float(eps))
+
+
+# ----------------------------------------------------------------------------
+# IBP transformers
+# ----------------------------------------------------------------------------
+def ibp_first_linear(inp: InputSet, W: torch.Tensor, b: Optional[torch.Tensor]):
+    """First affine layer straight from the input set.
+
+    Box: `BoxPerturbation.concretize_matmul` perturbation.py:282-325
+    (`midpoint @ W^T`, `radius @ |W|^T`).  L-inf: perturbation.py:102-134 gives
+    the same numbers with radius == eps (`eps * |W|.sum(1)`).
+    """
+    mid = inp.mid.reshape(inp.mid.shape[0], -1)
+    rad = inp.rad.reshape(inp.rad.shape[0], -1)
+    center = mid.matmul(W.t())
+    dev = rad.matmul(W.abs().t())
+    lower, upper = center - dev, center + dev
+    if b is not None:
+        lower, upper = lower + b, upper + b
+    return lower, upper
+
+
+def ibp_linear(l: torch.Tensor, u: torch.Tensor, W: torch.Tensor, b: Optional[torch.Tensor]):
+    """`IntervalDomain.affine_transformer` linear branch, domains/interval.py:79-86."""
+    w_pos = torch.clamp(W, min=0.0)
+    w_neg = torch.clamp(W, max=0.0)
+    y_l = l.matmul(w_pos.t()) + u.matmul(w_neg.t())
+    y_u = u.matmul(w_pos.t()) + l.matmul(w_neg.t())
+    if b is not None:
+        y_l, y_u = y_l + b, y_u + b
+    return y_l, y_u
+
+
+def ibp_conv2d(l, u, W, b, stride, padding):
+    """`IntervalDomain.affine_transformer` conv2d branch, domains/interval.py:57-74."""
+    w_pos = torch.clamp(W, min=0.0)
+    w_neg = torch.clamp(W, max=0.0)
+    y_l = F.conv2d(l, w_pos, None, stride, padding) + F.conv2d(u, w_neg, None, stride, padding)
+    y_u = F.conv2d(u, w_pos, None, stride, padding) + F.conv2d(l, w_neg, None, stride, padding)
+    if b is not None:
+        y_l = y_l + b.view(1, -1, 1, 1)
+        y_u = y_u + b.view(1, -1, 1, 1)
+    return y_l, y_u
+
+
+def apply_relu_split(l: torch.Tensor, u: torch.Tensor, split: torch.Tensor):
+    """`_apply_relu_split`, runtime/crown_ibp.py:70-98.
+
+    split in {-1,0,+1} with the pre-activation's shape (a leading batch axis of
+    1 or a missing batch axis broadcasts, runtime/relu_shape_utils.py:82-115).
+    Returns the clamped bounds and a per-domain `infeasible` mask; the reference
+    raises ValueError for the whole batch when any entry has lower > upper
+    (crown_ibp.py:92-95) -- callers that mirror that behaviour test `.any()`.
+    """
+    shape = l.shape
+    B = shape[0]
+    lf, uf = l.reshape(B, -1), u.reshape(B, -1)
+    s = split.reshape(-1, lf.shape[1]) if split.dim() >= 1 and split.numel() != 1 else split.reshape(1, 1)
+    s = s.expand(B, lf.shape[1])
+    lf = torch.where(s > 0, torch.maximum(lf, torch.zeros_like(lf)), lf)
+    uf = torch.where(s < 0, torch.minimum(uf, torch.zeros_like(uf)), uf)
+    infeasible = (lf > uf).any(dim=1)
+    return lf.reshape(shape), uf.reshape(shape), infeasible
+
+
+@dataclass
+class ForwardTrace:
+    """What `_forward_ibp_trace_mlp` (crown_ibp.py:101-342) returns, positionally.
+
+    pre[i]  : (l, u) bounds of the i-th ReLU's input after constraint/split clamps
+    shapes  : per-layer output shapes without batch (input shape first)
+    out     : IBP bounds of the chain output
+    infeasible : [B] bool, any split/constraint made lower > upper
+    """
+
+    pre: List[Tuple[torch.Tensor, torch.Tensor]]
+    shapes: List[Tuple[int, ...]]
+    out: Tuple[torch.Tensor, torch.Tensor]
+    infeasible: torch.Tensor
+
+
+def forward_ibp_trace(
+    layers: Layers,
+    inp: InputSet,
+    *,
+    splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
+    constraints: Optional[Sequence[Tuple[torch.Tensor, torch.Tensor]]] = None,
+) -> ForwardTrace:
+    """One IBP sweep recording every ReLU pre-activation, crown_ibp.py:101-342.
+
+    The first linear layer consumes the input set exactly
+    (crown_ibp.py:151-159); a first conv2d uses the bounding box
+    (crown_ibp.py:173-178).  `constraints[i]` is intersected with the i-th
+    pre-activation (crown_ibp.py:186-209) before `splits[i]` is applied
+    (crown_ibp.py:210-213).
+    """
+    B = inp.mid.shape[0]
+    at_input = True
+    cur_l, cur_u = inp.lo, inp.up
+    cur_inp = inp
+    pre: List[Tuple[torch.Tensor, torch.Tensor]] = []
+    shapes: List[Tuple[int, ...]] = [tuple(inp.mid.shape[1:])]
+    infeasible = torch.zeros(B, dtype=torch.bool)
+    relu_idx = 0
+    for layer in layers:
+        op = layer["op"]
+        if op == "linear":
+            if at_input:
+                cur_l, cur_u = ibp_first_linear(cur_inp, layer["W"], layer.get("b"))
+            else:
+                cur_l, cur_u = ibp_linear(cur_l, cur_u, layer["W"], layer.get("b"))
+            at_input = False
+        elif op == "conv2d":
+            cur_l, cur_u = ibp_conv2d(cur_l, cur_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"])
+            at_input = False
+        elif op == "relu":
+            if constraints is not None:
+                c_l, c_u = constraints[relu_idx]
+                cur_l = torch.maximum(cur_l, c_l)
+                cur_u = torch.minimum(cur_u, c_u)
+                infeasible |= (cur_l > cur_u).reshape(B, -1).any(dim=1)
+            if splits is not None and splits[relu_idx] is not None:
+                cur_l, cur_u, bad = apply_relu_split(cur_l, cur_u, splits[relu_idx])
+                infeasible |= bad
+            pre.append((cur_l, cur_u))
+            relu_idx += 1
+            cur_l, cur_u = torch.relu(cur_l), torch.relu(cur_u)  # interval.py:88-91
+        elif op == "flatten":
+            if at_input:
+                cur_inp = InputSet(
+                    mid=cur_inp.mid.flatten(1), rad=cur_inp.rad.flatten(1), lo=cur_inp.lo.flatten(1), up=cur_inp.up.flatten(1)
+                )
+            cur_l, cur_u = cur_l.flatten(1), cur_u.flatten(1)
+        else:
+            raise NotImplementedError(op)
+        shapes.append(tuple(cur_l.shape[1:]))
+    return ForwardTrace(pre=pre, shapes=shapes, out=(cur_l, cur_u), infeasible=infeasible)
+
+
+# ----------------------------------------------------------------------------
+# ReLU relaxation and backward transformers
+# ----------------------------------------------------------------------------
+def relu_relax(l: torch.Tensor, u: torch.Tensor):
+    """`_relu_relax`, crown_ibp.py:722-758.
+
+    pos = l>=0 -> slope 1; neg = u<=0 -> slope 0 (the later masked write wins
+    when l == u == 0); otherwise upper line u/(u-l) with intercept -l*u/(u-l),
+    lower slope 0.  The denominator is clamped at the dtype's machine epsilon.
+    """
+    pos = l >= 0
+    neg = u <= 0
+    amb = (~pos) & (~neg)
+    denom = (u - l).clamp_min(torch.finfo(l.dtype).eps)
+    a = u / denom
+    one, zero = torch.ones_like(l), torch.zeros_like(l)
+    alpha_u = torch.where(amb, a, torch.where(neg, zero, one))
+    beta_u = torch.where(amb, -l * a, zero)
+    alpha_l = torch.where(amb, zero, torch.where(neg, zero, one))
+    beta_l = zero
+    return alpha_u, beta_u, alpha_l, beta_l
+
+
+def relu_slopes(l, u, alpha: Optional[torch.Tensor]):
+    """`_relu_backward_relaxation`, crown_ibp.py:1176-1208: flattened slopes with
+    the alpha override `clamp(alpha,0,1)` (crown_ibp.py:1001) applied only where
+    l < 0 < u (crown_ibp.py:1199-1201)."""
+    B = l.shape[0]
+    lf, uf = l.reshape(B, -1), u.reshape(B, -1)
+    alpha_u, beta_u, alpha_l, beta_l = relu_relax(lf, uf)
+    if alpha is not None:
+        a = alpha.reshape(-1, lf.shape[1]).expand(B, lf.shape[1]).clamp(0.0, 1.0)
+        amb = (lf < 0) & (uf > 0)
+        alpha_l = torch.where(amb, a, alpha_l)
+    return alpha_u, beta_u, alpha_l, beta_l
+
+
+def relu_backward(A_u, A_l, b_u, b_l, alpha_u, beta_u, alpha_l, beta_l, add_u=None, add_l=None):
+    """`_backprop_relu_step_dense_reference`, crown_ibp.py:1262-1298.
+
+    A_* are [B,S,n]; slopes [B,n]; add_* (the beta term, [B,n]) is broadcast
+    over S and added after scaling.
+    """
+    sel_a = torch.where(A_u >= 0, alpha_u.unsqueeze(1), alpha_l.unsqueeze(1))
+    sel_b = torch.where(A_u >= 0, beta_u.unsqueeze(1), beta_l.unsqueeze(1))
+    out_b_u = b_u + (A_u * sel_b).sum(dim=2)
+    out_A_u = A_u * sel_a
+    if add_u is not None:
+        out_A_u = out_A_u + add_u.unsqueeze(1)
+    sel_a = torch.where(A_l >= 0, alpha_l.unsqueeze(1), alpha_u.unsqueeze(1))
+    sel_b = torch.where(A_l >= 0, beta_l.unsqueeze(1), beta_u.unsqueeze(1))
+    out_b_l = b_l + (A_l * sel_b).sum(dim=2)
+    out_A_l = A_l * sel_a
+    if add_l is not None:
+        out_A_l = out_A_l + add_l.unsqueeze(1)
+    return out_A_u, out_A_l, out_b_u, out_b_l
+
+
+def linear_backward(A, b, W, bias):
+    """`_backprop_linear_step`, crown_ibp.py:1073-1090: A' = A @ W
+    (linear_operator.py:585-586 `einsum bko,oi->bki`), b' = b + A @ bias
+    (linear_operator.py:374-383)."""
+    b_out = b + torch.einsum("bko,o->bk", A, bias) if bias is not None else b
+    return torch.einsum("bko,oi->bki", A, W), b_out
+
+
+def conv2d_output_padding(in_hw, out_hw, k, stride, padding):
+    """linear_operator.py:140-163: output_padding = H_in - ((H_out-1)*s - 2p + (k-1) + 1)."""
+    return tuple(
+        int(in_hw[i]) - ((int(out_hw[i]) - 1) * stride[i] - 2 * padding[i] + (k[i] - 1) + 1) for i in range(2)
+    )
+
+
+def conv2d_backward(A, b, W, bias, stride, padding, in_shape, out_shape):
+    """`_backprop_conv2d_step`, crown_ibp.py:1106-1173, with
+    `Conv2dLinearOperator.to_dense` (linear_operator.py:1067-1092): the
+    coefficient rows [B,S,C_o*H_o*W_o] go through conv_transpose2d with batch =
+    B*S; the bias term is sum over (c,h,w) of A*bias[c] (crown_ibp.py:1149-1152).
+    """
+    B, S = A.shape[0], A.shape[1]
+    A4 = A.reshape(B * S, *out_shape)
+    b_out = b
+    if bias is not None:
+        b_out = b + (A4.sum(dim=(2, 3)) * bias.view(1, -1)).sum(dim=1).reshape(B, S)
+    opad = conv2d_output_padding(in_shape[1:], out_shape[1:], W.shape[2:], stride, padding)
+    prev = F.conv_transpose2d(A4, W, None, stride, padding, opad)
+    return prev.reshape(B, S, -1), b_out
+
+
+def concretize(inp: InputSet, A, b, side: str):
+    """`BoxPerturbation.concretize_affine`, perturbation.py:327-359:
+    lower = A.mid - |A|.rad + b, upper = A.mid + |A|.rad + b.  (L-inf ball:
+    perturbation.py:201-215, identical with rad == eps.)"""
+    B = A.shape[0]
+    mid = inp.mid.reshape(B, 1, -1)
+    rad = inp.rad.reshape(B, 1, -1)
+    center = (A * mid).sum(dim=2)
+    dev = (A.abs() * rad).sum(dim=2)
+    return (center - dev + b) if side == "lower" else (center + dev + b)
+
+
+# ----------------------------------------------------------------------------
+# CROWN backward sweep
+# ----------------------------------------------------------------------------
+def relu_layer_indices(layers: Layers) -> List[int]:
+    return [i for i, layer in enumerate(layers) if layer["op"] == "relu"]
+
+
+def crown_backward(
+    layers: Layers,
+    inp: InputSet,
+    trace: ForwardTrace,
+    C: Optional[torch.Tensor],
+    *,
+    alpha: Optional[Sequence[Optional[torch.Tensor]]] = None,
+    add_l: Optional[Sequence[Optional[torch.Tensor]]] = None,
+    upto: Optional[int] = None,
+):
+    """`_run_crown_backward_from_trace`, crown_ibp.py:1669-2051, for chains.
+
+    Bounds `C @ value` where value is the output of `layers[:upto]` (default:
+    the whole chain; crown_ibp.py:1722 `output_value=`).  C is [B,S,O] (or
+    [S,O], broadcast; or None = identity, crown_ibp.py:672-719).  `alpha[i]`
+    overrides the i-th ReLU's lower slope, `add_l[i]` is the beta term added to
+    the lower coefficients (alpha_beta_crown.py:615-640).  Returns (lower, upper)
+    both [B,S].
+    """
+    n_layers = len(layers) if upto is None else int(upto)
+    B = inp.mid.shape[0]
+    out_shape = trace.shapes[n_layers]
+    out_dim = 1
+    for d in out_shape:
+        out_dim *= int(d)
+    dtype = inp.mid.dtype
+    if C is None:
+        C = torch.eye(out_dim, dtype=dtype).unsqueeze(0).expand(B, out_dim, out_dim)
+    elif C.dim() == 2:
+        C = C.unsqueeze(0).expand(B, C.shape[0], C.shape[1])
+    A_u, A_l = C.clone(), C.clone()
+    S = A_u.shape[1]
+    b_u = torch.zeros(B, S, dtype=dtype)
+    b_l = torch.zeros(B, S, dtype=dtype)
+    relu_ids = relu_layer_indices(layers)
+    for idx in range(n_layers - 1, -1, -1):
+        layer = layers[idx]
+        op = layer["op"]
+        if op == "linear":
+            A_u, b_u = linear_backward(A_u, b_u, layer["W"], layer.get("b"))
+            A_l, b_l = linear_backward(A_l, b_l, layer["W"], layer.get("b"))
+        elif op == "conv2d":
+            in_shape, o_shape = trace.shapes[idx], trace.shapes[idx + 1]
+            A_u, b_u = conv2d_backward(A_u, b_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape)
+            A_l, b_l = conv2d_backward(A_l, b_l, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape)
+        elif op == "relu":
+            r = relu_ids.index(idx)
+            l, u = trace.pre[r]
+            a = alpha[r] if alpha is not None else None
+            alpha_u, beta_u, alpha_l, beta_l = relu_slopes(l, u, a)
+            add = add_l[r] if add_l is not None else None
+            A_u, A_l, b_u, b_l = relu_backward(A_u, A_l, b_u, b_l, alpha_u, beta_u, alpha_l, beta_l, None, add)
+        elif op == "flatten":
+            pass  # coefficients are kept flattened; reshape is a view (crown_ibp.py:1093-1103)
+        else:
+            raise NotImplementedError(op)
+    lower = concretize(inp, A_l, b_l, "lower")
+    upper = concretize(inp, A_u, b_u, "upper")
+    return lower, upper
+
+
+def crown_ibp(layers: Layers, inp: InputSet, C, *, splits=None, alpha=None):
+    """`run_crown_ibp_mlp`, crown_ibp.py:2054-2133: IBP trace then one backward sweep."""
+    trace = forward_ibp_trace(layers, inp, splits=splits)
+    lower, upper = crown_backward(layers, inp, trace, C, alpha=alpha)
+    return lower, upper, trace
+
+
+def crown_with_intermediate_crown(layers: Layers, inp: InputSet, C, *, chunk: int = 512):
+    """CROWN whose intermediate (ReLU-input) bounds are themselves CROWN bounds.
+
+    Composition of reference primitives as in
+    runtime/native_intermediate_refinement.py:923-988: for every ReLU input in
+    graph order bound it with an identity spec
+    (`run_crown_ibp_mlp_from_forward_trace(output_value=name)`), intersect with
+    the current bounds (maximum/minimum), re-propagate IBP under the constraints
+    (`_forward_ibp_trace_mlp(relu_pre_constraints=...)`), and finally bound the
+    spec rows.  Identity rows are processed in chunks to bound memory.
+    """
+    trace = forward_ibp_trace(layers, inp)
+    relu_ids = relu_layer_indices(layers)
+    B = inp.mid.shape[0]
+    cons = [(l.clone(), u.clone()) for l, u in trace.pre]
+    for r, idx in enumerate(relu_ids):
+        if r == 0:
+            continue  # the first pre-activation's CROWN bound equals its IBP bound
+        shape = trace.shapes[idx]
+        n = 1
+        for d in shape:
+            n *= int(d)
+        lo_rows, up_rows = [], []
+        eye = torch.eye(n, dtype=inp.mid.dtype)
+        for s in range(0, n, chunk):
+            Cc = eye[s : s + chunk]
+            lo_c, up_c = crown_backward(layers, inp, trace, Cc, upto=idx)
+            lo_rows.append(lo_c)
+            up_rows.append(up_c)
+        new_l = torch.cat(lo_rows, dim=1).reshape(B, *shape)
+        new_u = torch.cat(up_rows, dim=1).reshape(B, *shape)
+        cons[r] = (torch.maximum(cons[r][0], new_l), torch.minimum(cons[r][1], new_u))
+        trace = forward_ibp_trace(layers, inp, constraints=cons)
+        cons = [(l.clone(), u.clone()) for l, u in trace.pre]
+    lower, upper = crown_backward(layers, inp, trace, C)
+    return lower, upper, trace
+
+
+# ----------------------------------------------------------------------------
+# alpha-CROWN
+# ----------------------------------------------------------------------------
+def adaptive_alpha_init(trace: ForwardTrace) -> List[torch.Tensor]:
+    """Adaptive lower-slope start, native_alpha_beta_optimizer_schedule.py:635-656:
+    1 where l >= 0 or (l < 0 < u and u > -l), else 0."""
+    out = []
+    for l, u in trace.pre:
+        lf, uf = l.reshape(l.shape[0], -1), u.reshape(u.shape[0], -1)
+        out.append(((lf >= 0) | ((lf < 0) & (uf > 0) & (uf > -lf))).to(l.dtype))
+    return out
+
+
+def alpha_crown(
+    layers: Layers,
+    inp: InputSet,
+    C,
+    *,
+    steps: int,
+    lr: float,
+    alpha0: Optional[Sequence[torch.Tensor]] = None,
+    alpha_init: float = 0.5,
+    splits=None,
+    spec_reduce: str = "mean",
+    trace: Optional[ForwardTrace] = None,
+):
+    """Per-domain alpha optimisation, `run_alpha_beta_crown_mlp` with
+    `per_batch_params=True, objective="lower"` and beta fixed at its zero
+    initial value restated (alpha_beta_crown.py:716-923).
+
+    steps+1 bound evaluations (756); metric_b = mean (or sum) over specs of the
+    lower bound (787-805); per-domain best with strict improvement, step 0
+    initialises (821-866); loss = -sum_b metric_b (913); torch Adam with default
+    betas/eps (747); projection alpha in [0,1] (919-921).  Returns the best
+    (lower, upper) per domain, the best alpha per ReLU, and the trace.
+    """
+    if trace is None:
+        trace = forward_ibp_trace(layers, inp, splits=splits)
+    B = inp.mid.shape[0]
+    dtype = inp.mid.dtype
+    alphas = []
+    for r, (l, _u) in enumerate(trace.pre):
+        n = l.reshape(B, -1).shape[1]
+        if alpha0 is not None:
+            a = alpha0[r].reshape(-1, n).expand(B, n).to(dtype).clone()
+        else:
+            a = torch.full((B, n), float(alpha_init), dtype=dtype)
+        alphas.append(a.requires_grad_(True))
+    opt = torch.optim.Adam(alphas, lr=float(lr))
+    best_metric = None
+    best_lower = best_upper = None
+    best_alpha: List[torch.Tensor] = []
+    for step in range(int(steps) + 1):
+        lower, upper = crown_backward(layers, inp, trace, C, alpha=alphas)
+        metric_b = lower.mean(dim=1) if spec_reduce == "mean" else lower.sum(dim=1)
+        if best_metric is None:
+            best_metric = metric_b.detach().clone()
+            best_lower, best_upper = lower.detach().clone(), upper.detach().clone()
+            best_alpha = [a.detach().clone() for a in alphas]
+        else:
+            improve = metric_b.detach() > best_metric
+            best_metric = torch.where(improve, metric_b.detach(), best_metric)
+            best_lower = torch.where(improve.unsqueeze(1), lower.detach(), best_lower)
+            best_upper = torch.where(improve.unsqueeze(1), upper.detach(), best_upper)
+            best_alpha = [torch.where(improve.unsqueeze(1), a.detach(), p) for a, p in zip(alphas, best_alpha)]
+        if step == int(steps):
+            break
+        loss = -metric_b.sum()
+        if not loss.requires_grad:
+            break
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        with torch.no_grad():
+            for a in alphas:
+                a.clamp_(0.0, 1.0)
+    return best_lower, best_upper, best_alpha, trace
+
+
+def alpha_gradient(layers: Layers, inp: InputSet, trace: ForwardTrace, C, alphas: Sequence[torch.Tensor], spec_reduce="mean"):
+    """Gradient of `-sum_b reduce_s lower[b,s]` w.r.t. each per-domain alpha via
+    autograd through `crown_backward` -- the quantity the reference's
+    `loss.backward()` (alpha_beta_crown.py:913-917) hands to Adam."""
+    leaves = [a.detach().clone().requires_grad_(True) for a in alphas]
+    lower, _ = crown_backward(layers, inp, trace, C, alpha=leaves)
+    metric_b = lower.mean(dim=1) if spec_reduce == "mean" else lower.sum(dim=1)
+    (-metric_b.sum()).backward()
+    return [a.grad if a.grad is not None else torch.zeros_like(a) for a in leaves], lower.detach()
+
+
+# ----------------------------------------------------------------------------
+# verdicts and soundness
+# ----------------------------------------------------------------------------
+def verdict(lower: torch.Tensor, threshold: float = 0.0, tol: float = 1e-6) -> torch.Tensor:
+    """bab.py:881-895: a domain is proven iff min over specs of the lower bound
+    is >= threshold - tol."""
+    return lower.min(dim=1).values >= (threshold - tol)
+
+
+def concrete_forward(layers: Layers, x: torch.Tensor) -> torch.Tensor:
+    """Plain forward evaluation of the chain (task_executor.py:574-784 restated
+    for chains) used by the sampling soundness check."""
+    for layer in layers:
+        op = layer["op"]
+        if op == "linear":
+            x = x.matmul(layer["W"].t())
+            if layer.get("b") is not None:
+                x = x + layer["b"]
+        elif op == "conv2d":
+            x = F.conv2d(x, layer["W"], layer.get("b"), layer["stride"], layer["padding"])
+        elif op == "relu":
+            x = torch.relu(x)
+        elif op == "flatten":
+            x = x.flatten(1)
+        else:
+            raise NotImplementedError(op)
+    return x
+
+
+def sample_soundness(layers: Layers, inp: InputSet, C, lower, upper, *, n: int, seed: int, splits=None, chunk: int = 1000):
+    """Worst violation of `lower <= C f(x) <= upper` over n uniform samples per
+    box (tests/test_phase6b_crown_ibp_mlp.py:68-110 style).  With `splits`, only
+    samples that satisfy every split constraint count.  Returns
+    (max(lower - y), max(y - upper)) over valid samples (<= 0 means sound)."""
+    g = torch.Generator("cpu").manual_seed(int(seed))
+    B = inp.lo.shape[0]
+    worst_lo = torch.tensor(-float("inf"), dtype=torch.float64)
+    worst_up = torch.tensor(-float("inf"), dtype=torch.float64)
+    Cb = C if C.dim() == 3 else C.unsqueeze(0).expand(B, *C.shape)
+    relu_ids = relu_layer_indices(layers)
+    for s in range(0, n, chunk):
+        m = min(chunk, n - s)
+        r = torch.rand((m,) + tuple(inp.lo.shape), generator=g, dtype=inp.lo.dtype)
+        xs = inp.lo.unsqueeze(0) + r * (inp.up - inp.lo).unsqueeze(0)
+        x = xs.reshape(m * B, *inp.lo.shape[1:]).to(torch.float64)
+        valid = torch.ones(m * B, dtype=torch.bool)
+        ri = 0
+        for i, layer in enumerate(layers):
+            if layer["op"] == "relu" and splits is not None and splits[ri] is not None:
+                sp = splits[ri].reshape(-1, x[0].numel()).expand(B, -1).repeat(m, 1)
+                xf = x.reshape(m * B, -1)
+                valid &= ~(((sp > 0) & (xf < 0)) | ((sp < 0) & (xf > 0))).any(dim=1)
+            if layer["op"] == "relu":
+                ri += 1
+            lay = {k: (v.to(torch.float64) if torch.is_tensor(v) else v) for k, v in layer.items()}
+            x = concrete_forward([lay], x)
+        y = torch.einsum("bso,mbo->mbs", Cb.to(torch.float64), x.reshape(m, B, -1))
+        v = valid.reshape(m, B, 1).expand_as(y)
+        if v.any():
+            worst_lo = torch.maximum(worst_lo, (lower.unsqueeze(0).to(torch.float64) - y)[v].max())
+            worst_up = torch.maximum(worst_up, (y - upper.unsqueeze(0).to(torch.float64))[v].max())
+    return float(worst_lo), float(worst_up)

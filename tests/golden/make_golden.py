@@ -1,0 +1,288 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE.
+
+Run once where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/boundflow-checkout
+
+It imports the reference's own PyTorch path (boundflow.runtime.*), feeds it the
+seeded synthetic workloads of `boundflow_b200.workloads`, and stores the
+reference's outputs as small .npz files.  The tests never import the reference;
+they regenerate the same inputs from the same seeds (an input checksum in every
+file guards against generator drift) and compare against the stored outputs.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+sys.path.insert(0, REF)
+
+from boundflow.domains.interval import IntervalState  # noqa: E402
+from boundflow.ir.task import BFTaskModule, BoundTask, TaskKind, TaskOp  # noqa: E402
+from boundflow.runtime.alpha_beta_crown import run_alpha_beta_crown_mlp  # noqa: E402
+from boundflow.runtime.alpha_crown import AlphaState  # noqa: E402
+from boundflow.runtime.crown_ibp import (  # noqa: E402
+    _forward_ibp_trace_mlp,
+    run_crown_ibp_mlp,
+    run_crown_ibp_mlp_from_forward_trace,
+)
+from boundflow.runtime.fused_crown import FusedReluAffineRequest, TorchDenseFusedCrownReference  # noqa: E402
+from boundflow.runtime.task_executor import InputSpec, PythonTaskExecutor  # noqa: E402
+
+from boundflow_b200 import workloads as W  # noqa: E402
+
+
+def ref_module(wl) -> BFTaskModule:
+    """Rebuild the workload's module with the reference's own IR classes."""
+    src = wl.module.get_entry_task()
+    ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    return BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(wl.module.bindings["params"])})
+
+
+def checksum(*tensors) -> np.ndarray:
+    return np.array([float(t.double().sum()) for t in tensors] + [float(t.double().abs().sum()) for t in tensors])
+
+
+def save(name, **arrays):
+    out = {k: (v.detach().cpu().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in arrays.items()}
+    path = os.path.join(HERE, name)
+    np.savez_compressed(path, **out)
+    print(f"wrote {path} ({os.path.getsize(path) / 1024:.1f} KiB)")
+
+
+def adaptive_alpha(relu_pre):
+    out = {}
+    for name, pre in relu_pre.items():
+        l = pre.lower.reshape(pre.lower.shape[0], -1)
+        u = pre.upper.reshape(pre.upper.shape[0], -1)
+        out[name] = ((l >= 0) | ((l < 0) & (u > 0) & (u > -l))).to(l.dtype)
+    return out
+
+
+def ref_alpha_only_loop(module, spec, C, relu_pre, interval_env, alpha0, *, steps, lr, reduce):
+    """alpha-only per-domain loop built on the reference's backward primitive
+    (`run_crown_ibp_mlp_from_forward_trace(relu_alpha=[B,n])`), with the update
+    rule of alpha_beta_crown.py:747-923 (Adam, sum-over-domains loss, clamp,
+    strict per-domain best)."""
+    alphas = {k: v.detach().clone().requires_grad_(True) for k, v in alpha0.items()}
+    opt = torch.optim.Adam(list(alphas.values()), lr=lr)
+    best_m = best_l = best_u = None
+    best_a = None
+    for step in range(steps + 1):
+        bounds = run_crown_ibp_mlp_from_forward_trace(
+            module, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=C, relu_alpha=alphas
+        )
+        m = bounds.lower.mean(dim=1) if reduce == "mean" else bounds.lower.sum(dim=1)
+        if best_m is None:
+            best_m, best_l, best_u = m.detach().clone(), bounds.lower.detach().clone(), bounds.upper.detach().clone()
+            best_a = {k: v.detach().clone() for k, v in alphas.items()}
+        else:
+            imp = m.detach() > best_m
+            best_m = torch.where(imp, m.detach(), best_m)
+            best_l = torch.where(imp[:, None], bounds.lower.detach(), best_l)
+            best_u = torch.where(imp[:, None], bounds.upper.detach(), best_u)
+            best_a = {k: torch.where(imp[:, None], alphas[k].detach(), best_a[k]) for k in alphas}
+        if step == steps:
+            break
+        loss = -m.sum()
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        with torch.no_grad():
+            for a in alphas.values():
+                a.clamp_(0.0, 1.0)
+    return best_l, best_u, best_a
+
+
+def ref_crown_intermediate(module, spec, C, relu_names, chunk=512):
+    """CROWN with CROWN intermediate bounds composed from reference primitives
+    (native_intermediate_refinement.py:923-988 recipe)."""
+    interval_env, relu_pre = _forward_ibp_trace_mlp(module, spec)
+    current = dict(relu_pre)
+    for i, name in enumerate(relu_names):
+        if i == 0:
+            continue
+        pre = current[name]
+        B = pre.lower.shape[0]
+        n = int(pre.lower[0].numel())
+        eye = torch.eye(n)
+        los, ups = [], []
+        for s in range(0, n, chunk):
+            out = run_crown_ibp_mlp_from_forward_trace(
+                module, spec, interval_env=interval_env, relu_pre=current, linear_spec_C=eye[s : s + chunk], output_value=name
+            )
+            los.append(out.lower)
+            ups.append(out.upper)
+        new_l = torch.cat(los, dim=1).reshape(pre.lower.shape)
+        new_u = torch.cat(ups, dim=1).reshape(pre.upper.shape)
+        current[name] = IntervalState(lower=torch.maximum(pre.lower, new_l), upper=torch.minimum(pre.upper, new_u))
+        interval_env, current = _forward_ibp_trace_mlp(module, spec, relu_pre_constraints=current)
+    final = run_crown_ibp_mlp_from_forward_trace(module, spec, interval_env=interval_env, relu_pre=current, linear_spec_C=C)
+    return final, current
+
+
+def main() -> None:
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.manual_seed(0)
+
+    # ---- c1: IBP + CROWN, full configuration --------------------------------
+    wl = W.make_workload("c1")
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    ibp = PythonTaskExecutor().run_ibp(m, spec)
+    crown = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C)
+    _, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    spec_linf = InputSpec.linf(value_name="input", center=wl.x, eps=wl.eps)
+    crown_linf = run_crown_ibp_mlp(m, spec_linf, linear_spec_C=wl.C)
+    save(
+        "c1_ibp_crown.npz",
+        input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),
+        ibp_lower=ibp.lower, ibp_upper=ibp.upper,
+        crown_lower=crown.lower, crown_upper=crown.upper,
+        crown_linf_lower=crown_linf.lower, crown_linf_upper=crown_linf.upper,
+        pre1_lower=relu_pre["h1"].lower, pre1_upper=relu_pre["h1"].upper,
+        pre2_lower=relu_pre["h2"].lower, pre2_upper=relu_pre["h2"].upper,
+    )
+
+    # ---- c2: CNN, CROWN-IBP on 8 inputs and full-CROWN intermediates on 4 ----
+    wl = W.make_workload("c2", batch=8)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    ibp = PythonTaskExecutor().run_ibp(m, spec)
+    crown = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C)
+    wl4 = W.make_workload("c2", batch=4)
+    m4 = ref_module(wl4)
+    spec4 = InputSpec.box(value_name="input", lower=wl4.lo, upper=wl4.up)
+    t0 = time.time()
+    full, cur = ref_crown_intermediate(m4, spec4, wl4.C, wl4.relu_names)
+    print(f"c2 intermediate recipe: {time.time() - t0:.1f}s")
+    save(
+        "c2_cnn.npz",
+        input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),
+        ibp_lower=ibp.lower, ibp_upper=ibp.upper,
+        crown_lower=crown.lower, crown_upper=crown.upper,
+        full_lower=full.lower, full_upper=full.upper,
+        **{f"pre_{n}_lower": cur[n].lower.reshape(4, -1)[:, ::7] for n in wl4.relu_names},
+        **{f"pre_{n}_upper": cur[n].upper.reshape(4, -1)[:, ::7] for n in wl4.relu_names},
+    )
+
+    # ---- c3: alpha-CROWN verbatim reference function on 8 inputs -------------
+    wl = W.make_workload("c3", batch=8)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    interval_env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    a0 = adaptive_alpha(relu_pre)
+    bounds, a_best, _b, _s = run_alpha_beta_crown_mlp(
+        m, spec, linear_spec_C=wl.C, steps=20, lr=0.1, warm_start_alpha=AlphaState(alpha_by_relu_input=a0),
+        per_batch_params=True, objective="lower", spec_reduce="mean",
+    )
+    plain = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C)
+    step0 = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C, relu_alpha=a0)
+    sum_l, sum_u, sum_a = ref_alpha_only_loop(m, spec, wl.C, relu_pre, interval_env, a0, steps=20, lr=0.1, reduce="sum")
+    # gradient of the first step (what Adam sees), via the reference's autograd
+    leaves = {k: v.detach().clone().requires_grad_(True) for k, v in a0.items()}
+    b0 = run_crown_ibp_mlp_from_forward_trace(m, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=wl.C, relu_alpha=leaves)
+    (-b0.lower.mean(dim=1).sum()).backward()
+    save(
+        "c3_alpha.npz",
+        input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),
+        plain_lower=plain.lower, plain_upper=plain.upper,
+        step0_lower=step0.lower, step0_upper=step0.upper,
+        best_lower=bounds.lower, best_upper=bounds.upper,
+        sum_best_lower=sum_l, sum_best_upper=sum_u,
+        **{f"alpha_{k}": v for k, v in a_best.alpha_by_relu_input.items()},
+        **{f"grad0_{k}": v.grad for k, v in leaves.items()},
+    )
+
+    # ---- c4: split subdomains, alpha-only loop on 24 domains -----------------
+    wl = W.make_workload("c4")
+    m = ref_module(wl)
+    root_spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _, root_pre = _forward_ibp_trace_mlp(m, root_spec)
+    D = 24
+    splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
+    lo = wl.lo.expand(D, -1).contiguous()
+    up = wl.up.expand(D, -1).contiguous()
+    spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+    split_state = {n: s for n, s in zip(wl.relu_names, splits)}
+    interval_env, relu_pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=split_state)
+    C = wl.C.expand(D, -1, -1).contiguous()
+    a0 = adaptive_alpha(relu_pre)
+    best_l, best_u, best_a = ref_alpha_only_loop(m, spec, C, relu_pre, interval_env, a0, steps=10, lr=0.1, reduce="mean")
+    step0 = run_crown_ibp_mlp_from_forward_trace(m, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=C, relu_alpha=a0)
+    save(
+        "c4_split_alpha.npz",
+        input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),
+        split_checksum=np.array([int(s.to(torch.int64).sum()) for s in splits] + [int(s.to(torch.int64).abs().sum()) for s in splits]),
+        step0_lower=step0.lower, step0_upper=step0.upper,
+        best_lower=best_l, best_upper=best_u,
+        **{f"pre_{n}_lower": relu_pre[n].lower for n in wl.relu_names},
+        **{f"pre_{n}_upper": relu_pre[n].upper for n in wl.relu_names},
+        **{f"alpha_{k}": v for k, v in best_a.items()},
+    )
+
+    # ---- c5: CIFAR-shaped CNN, CROWN-IBP on 2 inputs, full-CROWN on 1 --------
+    wl = W.make_workload("c5", batch=2)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    ibp = PythonTaskExecutor().run_ibp(m, spec)
+    crown = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C)
+    wl1 = W.make_workload("c5", batch=1)
+    m1 = ref_module(wl1)
+    spec1 = InputSpec.box(value_name="input", lower=wl1.lo, upper=wl1.up)
+    t0 = time.time()
+    full, cur = ref_crown_intermediate(m1, spec1, wl1.C, wl1.relu_names, chunk=256)
+    print(f"c5 intermediate recipe: {time.time() - t0:.1f}s")
+    save(
+        "c5_cnn.npz",
+        input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),
+        ibp_lower=ibp.lower, ibp_upper=ibp.upper,
+        crown_lower=crown.lower, crown_upper=crown.upper,
+        full_lower=full.lower, full_upper=full.upper,
+        **{f"pre_{n}_lower": cur[n].lower.reshape(1, -1)[:, ::31] for n in wl1.relu_names},
+        **{f"pre_{n}_upper": cur[n].upper.reshape(1, -1)[:, ::31] for n in wl1.relu_names},
+    )
+
+    # ---- fused ReLU+affine region requests (boundary B3) ---------------------
+    g = torch.Generator("cpu").manual_seed(77)
+    D, S, n_cur, n_prev = 5, 9, 37, 53
+    A_u = torch.randn(D, S, n_cur, generator=g)
+    A_l = torch.randn(D, S, n_cur, generator=g)
+    l = torch.randn(D, n_cur, generator=g) - 0.2
+    u = l + torch.rand(D, n_cur, generator=g) * 2.0
+    from boundflow.runtime.crown_ibp import _relu_relax
+
+    au, bu, al, bl = _relu_relax(l, u)
+    Wt = torch.randn(n_cur, n_prev, generator=g)
+    bias = torch.randn(n_cur, generator=g)
+    req = FusedReluAffineRequest("linear", A_u, A_l, au, al, bu, bl, Wt, bias, (n_prev,), (n_cur,), {})
+    res = TorchDenseFusedCrownReference().run(req)
+    Co, Ho, Wo, Ci, k, st, pd = 6, 5, 5, 3, 4, 2, 1
+    Hi = (Ho - 1) * st - 2 * pd + k
+    A_uc = torch.randn(D, S, Co, Ho, Wo, generator=g)
+    A_lc = torch.randn(D, S, Co, Ho, Wo, generator=g)
+    lc = torch.randn(D, Co * Ho * Wo, generator=g) - 0.2
+    uc = lc + torch.rand(D, Co * Ho * Wo, generator=g) * 2.0
+    auc, buc, alc, blc = _relu_relax(lc, uc)
+    Wc = torch.randn(Co, Ci, k, k, generator=g)
+    bc = torch.randn(Co, generator=g)
+    reqc = FusedReluAffineRequest("conv2d", A_uc, A_lc, auc, alc, buc, blc, Wc, bc, (Ci, Hi, Hi), (Co, Ho, Wo), {"stride": (st, st), "padding": (pd, pd)})
+    resc = TorchDenseFusedCrownReference().run(reqc)
+    save(
+        "fused_region.npz",
+        lin_A_prev_u=res.A_prev_u, lin_A_prev_l=res.A_prev_l, lin_delta_u=res.bias_delta_u, lin_delta_l=res.bias_delta_l,
+        conv_A_prev_u=resc.A_prev_u, conv_A_prev_l=resc.A_prev_l, conv_delta_u=resc.bias_delta_u, conv_delta_l=resc.bias_delta_l,
+    )
+
+
+if __name__ == "__main__":
+    main()

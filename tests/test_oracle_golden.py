@@ -1,0 +1,172 @@
+"""Pins the CPU oracle against outputs of the reference itself (tests/golden/*.npz,
+made by tests/golden/make_golden.py) and against the literal known-answer cases of
+the reference's own tests."""
+import numpy as np
+import torch
+
+from boundflow_b200 import workloads as W
+from oracle import crown_oracle as O
+from tests.helpers import assert_close, workload_checksum
+
+
+def _check_inputs(wl, g):
+    assert np.allclose(workload_checksum(wl), g["input_checksum"], rtol=1e-12, atol=0), "seeded inputs drifted from the golden run"
+
+
+def test_c1_ibp_and_crown(golden):
+    g = golden("c1_ibp_crown.npz")
+    wl = W.make_workload("c1")
+    _check_inputs(wl, g)
+    inp = O.box_input(wl.lo, wl.up)
+    lower, upper, trace = O.crown_ibp(wl.layers, inp, wl.C)
+    assert_close(trace.out[0], g["ibp_lower"], "ibp lower")
+    assert_close(trace.out[1], g["ibp_upper"], "ibp upper")
+    assert_close(trace.pre[0][0], g["pre1_lower"], "pre1 lower")
+    assert_close(trace.pre[1][1], g["pre2_upper"], "pre2 upper")
+    assert_close(lower, g["crown_lower"], "crown lower")
+    assert_close(upper, g["crown_upper"], "crown upper")
+    lo2, up2, _ = O.crown_ibp(wl.layers, O.linf_box(wl.x, wl.eps), wl.C)
+    assert_close(lo2, g["crown_linf_lower"], "crown linf lower")
+    assert_close(up2, g["crown_linf_upper"], "crown linf upper")
+
+
+def test_c2_cnn(golden):
+    g = golden("c2_cnn.npz")
+    wl = W.make_workload("c2", batch=8)
+    _check_inputs(wl, g)
+    lower, upper, trace = O.crown_ibp(wl.layers, O.box_input(wl.lo, wl.up), wl.C)
+    assert_close(trace.out[0], g["ibp_lower"], "ibp lower")
+    assert_close(trace.out[1], g["ibp_upper"], "ibp upper")
+    assert_close(lower, g["crown_lower"], "crown lower")
+    assert_close(upper, g["crown_upper"], "crown upper")
+    wl4 = W.make_workload("c2", batch=4)
+    lo4, up4, tr4 = O.crown_with_intermediate_crown(wl4.layers, O.box_input(wl4.lo, wl4.up), wl4.C)
+    assert_close(lo4, g["full_lower"], "full-crown lower")
+    assert_close(up4, g["full_upper"], "full-crown upper")
+    for r, name in enumerate(wl4.relu_names):
+        assert_close(tr4.pre[r][0].reshape(4, -1)[:, ::7], g[f"pre_{name}_lower"], f"pre {name} lower")
+        assert_close(tr4.pre[r][1].reshape(4, -1)[:, ::7], g[f"pre_{name}_upper"], f"pre {name} upper")
+
+
+def test_c3_alpha(golden):
+    g = golden("c3_alpha.npz")
+    wl = W.make_workload("c3", batch=8)
+    _check_inputs(wl, g)
+    inp = O.box_input(wl.lo, wl.up)
+    lower, upper, trace = O.crown_ibp(wl.layers, inp, wl.C)
+    assert_close(lower, g["plain_lower"], "plain lower")
+    assert_close(upper, g["plain_upper"], "plain upper")
+    a0 = O.adaptive_alpha_init(trace)
+    lo0, up0 = O.crown_backward(wl.layers, inp, trace, wl.C, alpha=a0)
+    assert_close(lo0, g["step0_lower"], "step0 lower")
+    assert_close(up0, g["step0_upper"], "step0 upper")
+    grads, _ = O.alpha_gradient(wl.layers, inp, trace, wl.C, a0)
+    for r, name in enumerate(wl.relu_names):
+        assert_close(grads[r], g[f"grad0_{name}"], f"grad0 {name}", atol=1e-5, rtol=1e-4)
+    bl, bu, ba, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=20, lr=0.1, alpha0=a0, spec_reduce="mean")
+    assert_close(bl, g["best_lower"], "alpha best lower")
+    assert_close(bu, g["best_upper"], "alpha best upper")
+    sl, su, _, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=20, lr=0.1, alpha0=a0, spec_reduce="sum")
+    # 20 Adam steps amplify rounding-level differences (Adam normalises even
+    # 1e-7-sized gradients to +-lr steps, and a moved alpha flips coefficient
+    # signs downstream), so two fp32 runs that differ only in summation order
+    # agree to ~1e-4 relative, not 1e-5; the optimised bound is compared at
+    # that looser tolerance, single evaluations at the strict one.
+    assert_close(sl, g["sum_best_lower"], "alpha(sum) best lower", rtol=3e-4)
+    assert (bl.mean(dim=1) >= lo0.mean(dim=1) - 1e-6).all()
+
+
+def test_c4_split_alpha(golden):
+    g = golden("c4_split_alpha.npz")
+    wl = W.make_workload("c4")
+    _check_inputs(wl, g)
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 24
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    chk = np.array([int(s.to(torch.int64).sum()) for s in splits] + [int(s.to(torch.int64).abs().sum()) for s in splits])
+    assert (chk == g["split_checksum"]).all()
+    inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+    C = wl.C.expand(D, -1, -1).contiguous()
+    trace = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+    assert not trace.infeasible.any()
+    for r, name in enumerate(wl.relu_names):
+        assert_close(trace.pre[r][0], g[f"pre_{name}_lower"], f"pre {name} lower")
+        assert_close(trace.pre[r][1], g[f"pre_{name}_upper"], f"pre {name} upper")
+    a0 = O.adaptive_alpha_init(trace)
+    lo0, up0 = O.crown_backward(wl.layers, inp, trace, C, alpha=a0)
+    assert_close(lo0, g["step0_lower"], "step0 lower")
+    bl, bu, _, _ = O.alpha_crown(wl.layers, inp, C, steps=10, lr=0.1, alpha0=a0, trace=trace)
+    assert_close(bl, g["best_lower"], "best lower")
+    assert_close(bu, g["best_upper"], "best upper")
+
+
+def test_c5_cnn(golden):
+    g = golden("c5_cnn.npz")
+    wl = W.make_workload("c5", batch=2)
+    _check_inputs(wl, g)
+    lower, upper, trace = O.crown_ibp(wl.layers, O.box_input(wl.lo, wl.up), wl.C)
+    assert_close(trace.out[0], g["ibp_lower"], "ibp lower")
+    assert_close(lower, g["crown_lower"], "crown lower")
+    assert_close(upper, g["crown_upper"], "crown upper")
+
+
+def test_bruteforce_grid_known_answer():
+    """Toy 2-2-2 network of the reference's grid test
+    (tests/test_phase6b_crown_ibp_mlp.py:153-175): bounds must contain every
+    point of a 41x41 grid in float64 to 1e-9."""
+    dt = torch.float64
+    x0 = torch.tensor([[0.2, -0.1]], dtype=dt)
+    layers = [
+        {"op": "linear", "W": torch.tensor([[1.3, -0.7], [-0.4, 0.9]], dtype=dt), "b": torch.tensor([0.05, -0.02], dtype=dt)},
+        {"op": "relu"},
+        {"op": "linear", "W": torch.tensor([[-1.2, 0.8], [0.6, -0.5]], dtype=dt), "b": torch.tensor([0.1, -0.3], dtype=dt)},
+    ]
+    inp = O.linf_box(x0, 0.3)
+    lower, upper, _ = O.crown_ibp(layers, inp, None)
+    grid = torch.linspace(-0.3, 0.3, steps=41, dtype=dt)
+    xs = torch.stack([x0[0] + torch.stack([dx, dy]) for dx in grid for dy in grid])
+    ys = O.concrete_forward(layers, xs)
+    assert (ys >= lower - 1e-9).all() and (ys <= upper + 1e-9).all()
+
+
+def test_alpha_gradient_sign_selection_formula():
+    """Closed form of the reference's known-answer test
+    (tests/test_phase7a_pr10_relu_dense_reference.py:132-162):
+    d/dalpha sum(outputs) = sum over rows of A_u[A_u<0 & amb] + A_l[A_l>=0 & amb]."""
+    dt = torch.float64
+    g = torch.Generator("cpu").manual_seed(5)
+    l = torch.tensor([[0.5, -2.0, -1.0, -0.3]], dtype=dt)
+    u = torch.tensor([[1.0, -0.5, 2.0, 0.9]], dtype=dt)
+    A_u = torch.randn(1, 3, 4, generator=g, dtype=dt)
+    A_l = torch.randn(1, 3, 4, generator=g, dtype=dt)
+    alpha = torch.tensor([[0.2, 0.3, 0.6, 0.8]], dtype=dt, requires_grad=True)
+    au, bu, al, bl = O.relu_slopes(l, u, alpha)
+    out = O.relu_backward(A_u, A_l, torch.zeros(1, 3, dtype=dt), torch.zeros(1, 3, dtype=dt), au, bu, al, bl)
+    sum(o.sum() for o in out).backward()
+    amb = ((l < 0) & (u > 0)).unsqueeze(1)
+    expected = (torch.where((A_u < 0) & amb, A_u, torch.zeros_like(A_u)) + torch.where((A_l >= 0) & amb, A_l, torch.zeros_like(A_l))).sum(dim=(0, 1))
+    assert torch.allclose(alpha.grad[0], expected, atol=1e-12, rtol=1e-12)
+    assert torch.equal(alpha.grad[0, :2], torch.zeros(2, dtype=dt))
+
+
+def test_fused_region_reference_vectors(golden):
+    """The oracle's ReLU-backward + affine-backward equals the reference's eager
+    fused-region executor (runtime/fused_crown.py:330-400) on seeded requests."""
+    g = golden("fused_region.npz")
+    gen = torch.Generator("cpu").manual_seed(77)
+    D, S, n_cur, n_prev = 5, 9, 37, 53
+    A_u = torch.randn(D, S, n_cur, generator=gen)
+    A_l = torch.randn(D, S, n_cur, generator=gen)
+    l = torch.randn(D, n_cur, generator=gen) - 0.2
+    u = l + torch.rand(D, n_cur, generator=gen) * 2.0
+    Wt = torch.randn(n_cur, n_prev, generator=gen)
+    bias = torch.randn(n_cur, generator=gen)
+    au, bu, al, bl = O.relu_relax(l, u)
+    z = torch.zeros(D, S)
+    sA_u, sA_l, d_u, d_l = O.relu_backward(A_u, A_l, z, z, au, bu, al, bl)
+    P_u, d_u = O.linear_backward(sA_u, d_u, Wt, bias)
+    P_l, d_l = O.linear_backward(sA_l, d_l, Wt, bias)
+    assert_close(P_u, g["lin_A_prev_u"], "A_prev_u")
+    assert_close(P_l, g["lin_A_prev_l"], "A_prev_l")
+    assert_close(d_u, g["lin_delta_u"], "delta_u")
+    assert_close(d_l, g["lin_delta_l"], "delta_l")
