@@ -1,0 +1,122 @@
+"""ctypes binding of libbf_b200.so (the C ABI declared in include/bf_b200.h).
+
+There is no fallback: if the shared library is missing the import of any
+compute entry point raises, and every non-zero return code becomes a Python
+exception carrying bf_last_error_string().
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbf_b200.so")
+
+BF_OK = 0
+BF_E_INVALID, BF_E_UNSUPPORTED, BF_E_WORKSPACE, BF_E_CUDA = -1, -2, -3, -4
+SIDE_LOWER, SIDE_UPPER = 0, 1
+IN_LOWER_UPPER, IN_MID_RAD = 0, 1
+OP_LINEAR, OP_CONV2D, OP_RELU, OP_FLATTEN = 1, 2, 3, 4
+REDUCE_MEAN, REDUCE_SUM = 0, 1
+
+_p = C.c_void_p
+_i = C.c_int
+_f = C.c_float
+_sz = C.c_size_t
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("op", _i), ("W", _p), ("bias", _p), ("n_in", _i), ("n_out", _i)] + [
+        (k, _i) for k in ("Ci", "Hi", "Wi", "Co", "Ho", "Wo", "kh", "kw", "sh", "sw", "ph", "pw")
+    ]
+
+
+# name -> (restype, argtypes); mirrors include/bf_b200.h one to one
+SIGNATURES = {
+    "bf_version": (_i, []),
+    "bf_last_error_string": (C.c_char_p, []),
+    "bf_launch_count": (C.c_ulonglong, []),
+    "bf_kernel_timing_enable": (None, [_i]),
+    "bf_kernel_timing_read": (_i, [_i, C.POINTER(_i), C.POINTER(_f)]),
+    "bf_ibp_linear": (_i, [_p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "bf_ibp_conv2d": (_i, [_p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p] + [_i] * 11 + [_p]),
+    "bf_relu_relax": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _p]),
+    "bf_alpha_adaptive_init": (_i, [_p, _p, _p, _i, _i, _p]),
+    "bf_crown_relu_linear_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "bf_crown_relu_conv2d_bwd_scratch_bytes": (_sz, [_i] * 5),
+    "bf_crown_relu_conv2d_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _sz] + [_i] * 14 + [_p]),
+    "bf_concretize": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "bf_verdict": (_i, [_p, _f, _f, _p, _p, _i, _i, _p]),
+    "bf_chain_create": (_i, [C.POINTER(LayerDesc), _i, C.POINTER(_p)]),
+    "bf_chain_destroy": (None, [_p]),
+    "bf_chain_num_relu": (_i, [_p]),
+    "bf_chain_ibp": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _p]),
+    "bf_chain_crown_workspace_bytes": (_sz, [_p, _i, _i, _i]),
+    "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_workspace_bytes": (_sz, [_p, _i, _i]),
+    "bf_chain_alpha_crown": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _sz, _i, _i, _p]),
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+class BackendError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libbf_b200 error {code}: {message}")
+        self.code = code
+
+
+def load() -> C.CDLL:
+    """Load the shared library (once) and set every prototype."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m boundflow_b200.csrc.build` "
+            "(the CUDA backend has no CPU or PyTorch fallback)"
+        )
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    if code != BF_OK:
+        msg = load().bf_last_error_string().decode("utf-8", "replace")
+        if code == BF_E_UNSUPPORTED:
+            raise NotImplementedError(f"libbf_b200: {msg}")
+        if code == BF_E_INVALID:
+            raise ValueError(f"libbf_b200: {msg}")
+        raise BackendError(code, msg)
+
+
+def ptr(t) -> Optional[int]:
+    """Device pointer of a torch tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def ptr_array(ts: Optional[Sequence]) -> Optional[C.Array]:
+    """Host array of device pointers (entries may be None)."""
+    if ts is None:
+        return None
+    arr = (_p * len(ts))()
+    for k, t in enumerate(ts):
+        arr[k] = None if t is None else t.data_ptr()
+    return arr
+
+
+def int_array(vals: Optional[Sequence[int]]):
+    if vals is None:
+        return None
+    return (_i * len(vals))(*[int(v) for v in vals])
+
+
+def launch_count() -> int:
+    return int(load().bf_launch_count())

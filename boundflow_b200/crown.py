@@ -1,0 +1,606 @@
+"""Whole-query entry points of the CUDA backend (IBP trace, CROWN, alpha-CROWN).
+
+Same names, argument meaning and error behaviour as the reference's solver
+stack so that callers (the BaB driver, benchmarks, tests) switch by import:
+
+  forward_ibp_trace_mlp                 <- _forward_ibp_trace_mlp            runtime/crown_ibp.py:101-342
+  run_crown_ibp_mlp                     <- run_crown_ibp_mlp                 runtime/crown_ibp.py:2054-2133
+  run_crown_ibp_mlp_from_forward_trace  <- same name                         runtime/crown_ibp.py:2136-2230
+  run_alpha_beta_crown_mlp              <- same name (alpha part, beta = 0)  runtime/alpha_beta_crown.py:643-941
+  run_crown_intermediate_mlp            <- the layer-by-layer refinement recipe of
+                                           runtime/native_intermediate_refinement.py:923-988
+
+All arithmetic happens in libbf_b200.so; torch only owns the device buffers and
+the stream.  Tensors given on the CPU are copied to the current CUDA device and
+results are returned on the device the inputs came from.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .ir import IntervalState, input_mid_rad, normalize_input_spec
+from .network import CudaChain, compile_chain
+
+
+@dataclass
+class AlphaState:
+    alpha_by_relu_input: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+@dataclass
+class BetaState:
+    beta_by_relu_input: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+@dataclass
+class AlphaCrownStats:
+    steps: int
+    lr: float
+    objective: str
+    spec_reduce: str
+    relu_inputs: Tuple[str, ...]
+    feasibility: str = "unknown"
+    reason: str = "ok"
+    infeasible_domains: Optional[torch.Tensor] = None
+
+
+def _cuda_device(t: torch.Tensor) -> torch.device:
+    if t.device.type == "cuda":
+        return t.device
+    if not torch.cuda.is_available():
+        raise RuntimeError("boundflow_b200 needs a CUDA device (no CPU fallback exists)")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _f32(t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    return t.detach().to(device=device, dtype=torch.float32, non_blocking=True).contiguous()
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class _Workspace:
+    """One growing device buffer per (device, stream): sized by the library's
+    *_workspace_bytes queries, reused across calls."""
+
+    _pool: Dict[Tuple[int, int], torch.Tensor] = {}
+
+    @classmethod
+    def get(cls, device: torch.device, nbytes: int) -> torch.Tensor:
+        key = (device.index or 0, _stream_ptr(device))
+        buf = cls._pool.get(key)
+        if buf is None or buf.numel() < nbytes:
+            cls._pool.pop(key, None)
+            buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+            cls._pool[key] = buf
+        return buf
+
+
+@dataclass
+class ForwardTrace:
+    """Device-side result of one IBP sweep."""
+
+    chain: CudaChain
+    mid: torch.Tensor           # [B, n0]
+    rad: torch.Tensor           # [B, n0]
+    pre_l: List[torch.Tensor]   # per ReLU [B, n_r]
+    pre_u: List[torch.Tensor]
+    out_l: torch.Tensor         # [B, n_out]
+    out_u: torch.Tensor
+    infeasible: torch.Tensor    # int32 [B]
+    B: int
+
+
+def _prepare_input(module: Any, input_spec: Any):
+    spec = normalize_input_spec(input_spec)
+    center = spec.center
+    device = _cuda_device(center)
+    mid, rad, lo, up = input_mid_rad(spec)
+    chain = compile_chain(module, tuple(int(d) for d in center.shape[1:]), device)
+    B = int(center.shape[0])
+    mid = _f32(mid, device).reshape(B, -1)
+    rad = _f32(rad, device).reshape(B, -1)
+    return spec, chain, device, B, mid, rad, center.device
+
+
+def _split_tensor(raw: Any, B: int, n: int, device: torch.device, name: str):
+    """int8 [B,n] or [1,n] view of a split assignment; shapes as the reference
+    accepts them (runtime/relu_shape_utils.py:82-115)."""
+    s = raw if torch.is_tensor(raw) else torch.as_tensor(raw)
+    if s.dtype not in (torch.int8, torch.int16, torch.int32, torch.int64):
+        raise TypeError(f"relu split for {name} must be integer tensor, got dtype={s.dtype}")
+    s = s.to(device=device, dtype=torch.int8)
+    if s.numel() == 1:
+        s = s.reshape(1, 1).expand(1, n)
+    elif s.numel() == n:
+        s = s.reshape(1, n)
+    elif s.numel() == B * n and int(s.shape[0]) == B:
+        s = s.reshape(B, n)
+    else:
+        raise ValueError(f"relu_split_state[{name}] shape {tuple(s.shape)} cannot broadcast to [{B},{n}]")
+    s = s.contiguous()
+    return s, (n if int(s.shape[0]) == B else 0)
+
+
+def ibp_trace(
+    module: Any,
+    input_spec: Any,
+    *,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_constraints: Optional[Mapping[str, Any]] = None,
+) -> ForwardTrace:
+    """Run the IBP sweep on the device and keep everything there."""
+    _spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
+    lib = chain.lib
+    R = len(chain.relu_layer_ids)
+    pre_l = [torch.empty(B, n, dtype=torch.float32, device=device) for n in chain.relu_widths]
+    pre_u = [torch.empty(B, n, dtype=torch.float32, device=device) for n in chain.relu_widths]
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    out_l = torch.empty(B, n_out, dtype=torch.float32, device=device)
+    out_u = torch.empty(B, n_out, dtype=torch.float32, device=device)
+    infeasible = torch.zeros(B, dtype=torch.int32, device=device)
+    splits: List[Optional[torch.Tensor]] = [None] * R
+    strides = [0] * R
+    if relu_split_state:
+        for r, name in enumerate(chain.relu_input_names):
+            if name in relu_split_state:
+                splits[r], strides[r] = _split_tensor(relu_split_state[name], B, chain.relu_widths[r], device, name)
+    cons_l: Optional[List[Optional[torch.Tensor]]] = None
+    cons_u: Optional[List[Optional[torch.Tensor]]] = None
+    if relu_pre_constraints is not None:
+        if tuple(relu_pre_constraints) != tuple(chain.relu_input_names):
+            raise ValueError("ReLU pre-activation constraint identities differ")
+        cons_l, cons_u = [], []
+        for r, name in enumerate(chain.relu_input_names):
+            c = relu_pre_constraints[name]
+            if tuple(c.lower.shape[1:]) != tuple(chain.relu_shapes[r]) or int(c.lower.shape[0]) != B:
+                raise ValueError(f"ReLU pre-activation constraint schema differs for {name}")
+            cons_l.append(_f32(c.lower, device).reshape(B, -1))
+            cons_u.append(_f32(c.upper, device).reshape(B, -1))
+    scratch = torch.empty(4 * (B * chain.max_width + 64), dtype=torch.float32, device=device)
+    _lib.check(
+        lib.bf_chain_ibp(
+            chain.handle, _lib.ptr(mid), _lib.ptr(rad), _lib.IN_MID_RAD,
+            _lib.ptr_array(splits), _lib.int_array(strides),
+            _lib.ptr_array(cons_l), _lib.ptr_array(cons_u),
+            _lib.ptr_array(pre_l), _lib.ptr_array(pre_u),
+            _lib.ptr(out_l), _lib.ptr(out_u), _lib.ptr(infeasible),
+            _lib.ptr(scratch), scratch.numel() * 4, B, _stream_ptr(device),
+        )
+    )
+    # keep the temporaries alive until the stream has consumed them
+    trace = ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=out_l, out_u=out_u, infeasible=infeasible, B=B)
+    trace._keep = (splits, cons_l, cons_u, scratch)  # type: ignore[attr-defined]
+    return trace
+
+
+def _raise_if_infeasible(trace: ForwardTrace, what: str) -> None:
+    if bool(trace.infeasible.any().item()):
+        bad = torch.nonzero(trace.infeasible).flatten().tolist()
+        raise ValueError(f"infeasible {what}: lower>upper after applying split/constraint (domains {bad[:8]}{'...' if len(bad) > 8 else ''})")
+
+
+def forward_ibp_trace_mlp(
+    module: Any,
+    input_spec: Any,
+    *,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_constraints: Optional[Mapping[str, Any]] = None,
+) -> Tuple[Dict[str, IntervalState], Dict[str, IntervalState]]:
+    """Reference-shaped result: (interval_env, relu_pre) keyed by value name.
+
+    Raises ValueError when any domain's split or constraint is infeasible, as
+    the reference does (crown_ibp.py:92-95, 205-208)."""
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state, relu_pre_constraints=relu_pre_constraints)
+    _raise_if_infeasible(trace, "relu split")
+    return _trace_to_env(trace, normalize_input_spec(input_spec).center.device)
+
+
+def _trace_to_env(trace: ForwardTrace, out_device: torch.device):
+    chain = trace.chain
+    relu_pre: Dict[str, IntervalState] = {}
+    env: Dict[str, IntervalState] = {}
+    for r, name in enumerate(chain.relu_input_names):
+        shape = (trace.B,) + tuple(chain.relu_shapes[r])
+        st = IntervalState(lower=trace.pre_l[r].reshape(shape).to(out_device), upper=trace.pre_u[r].reshape(shape).to(out_device))
+        relu_pre[name] = st
+        env[name] = st
+    oshape = (trace.B,) + tuple(chain.output_shape)
+    env[chain.output_name] = IntervalState(lower=trace.out_l.reshape(oshape).to(out_device), upper=trace.out_u.reshape(oshape).to(out_device))
+    env["__trace__"] = trace  # type: ignore[assignment]
+    return env, relu_pre
+
+
+def _trace_from_env(module: Any, input_spec: Any, interval_env: Mapping[str, Any], relu_pre: Mapping[str, Any]) -> ForwardTrace:
+    """Recover (or rebuild from tensors) the device trace for a backward-only call."""
+    tr = interval_env.get("__trace__") if isinstance(interval_env, Mapping) else None
+    _spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
+    if isinstance(tr, ForwardTrace) and tr.chain is chain and tr.B == B:
+        same = all(
+            relu_pre[n].lower.data_ptr() == tr.pre_l[r].data_ptr() for r, n in enumerate(chain.relu_input_names) if n in relu_pre
+        )
+        if same:
+            return tr
+    pre_l, pre_u = [], []
+    for r, name in enumerate(chain.relu_input_names):
+        if name not in relu_pre:
+            raise KeyError(f"missing relu pre-activation bounds for value: {name}")
+        pre_l.append(_f32(relu_pre[name].lower, device).reshape(B, -1))
+        pre_u.append(_f32(relu_pre[name].upper, device).reshape(B, -1))
+    z = torch.zeros(B, 1, dtype=torch.float32, device=device)
+    return ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=z, out_u=z, infeasible=torch.zeros(B, dtype=torch.int32, device=device), B=B)
+
+
+def _expand_spec(C: Optional[torch.Tensor], B: int, out_dim: int, device: torch.device) -> torch.Tensor:
+    """[B,S,O] contiguous spec rows; None = identity, [S,O] is shared (crown_ibp.py:672-719)."""
+    if C is None:
+        return torch.eye(out_dim, dtype=torch.float32, device=device).unsqueeze(0).expand(B, out_dim, out_dim).contiguous()
+    C = C if torch.is_tensor(C) else torch.as_tensor(C)
+    C = C.detach().to(device=device, dtype=torch.float32)
+    if C.dim() == 2:
+        if int(C.shape[1]) != out_dim:
+            raise ValueError(f"linear_spec_C shape mismatch: C={tuple(C.shape)} out=({B}, {out_dim})")
+        C = C.unsqueeze(0).expand(B, C.shape[0], out_dim)
+    if C.dim() != 3:
+        raise ValueError(f"linear_spec_C expects rank-3 [B,S,O], got {tuple(C.shape)}")
+    if int(C.shape[0]) != B or int(C.shape[2]) != out_dim:
+        raise ValueError(f"linear_spec_C shape mismatch: C={tuple(C.shape)} out=({B}, {out_dim})")
+    return C.contiguous()
+
+
+def _alpha_rows(raw: Any, B: int, n: int, device: torch.device, name: str) -> Tuple[torch.Tensor, int]:
+    """alpha as [B,n] (stride n) or [1,n] (stride 0), shapes as crown_ibp.py:940-1001 accepts."""
+    a = raw if torch.is_tensor(raw) else torch.as_tensor(raw)
+    if not torch.is_floating_point(a):
+        raise TypeError(f"relu_alpha[{name}] must be floating, got dtype={a.dtype}")
+    a = a.detach().to(device=device, dtype=torch.float32)
+    if a.numel() == 1:
+        return a.reshape(1, 1).expand(1, n).contiguous(), 0
+    if a.numel() == n:
+        return a.reshape(1, n).contiguous(), 0
+    if a.numel() == B * n and int(a.shape[0]) == B:
+        return a.reshape(B, n).contiguous(), n
+    raise ValueError(f"relu_alpha[{name}] shape {tuple(a.shape)} cannot broadcast to [{B},{n}]")
+
+
+def _relaxations(trace: ForwardTrace, relu_alpha: Optional[Mapping[str, torch.Tensor]], n_relu: int):
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    au, bu, al = [], [], []
+    keep = []
+    for r in range(n_relu):
+        n = chain.relu_widths[r]
+        name = chain.relu_input_names[r]
+        a_u = torch.empty(B, n, dtype=torch.float32, device=device)
+        b_u = torch.empty_like(a_u)
+        a_l = torch.empty_like(a_u)
+        alpha, stride = (None, 0)
+        if relu_alpha is not None and name in relu_alpha:
+            alpha, stride = _alpha_rows(relu_alpha[name], B, n, device, name)
+            keep.append(alpha)
+        _lib.check(
+            chain.lib.bf_relu_relax(
+                _lib.ptr(trace.pre_l[r]), _lib.ptr(trace.pre_u[r]), _lib.ptr(alpha), stride,
+                _lib.ptr(a_u), _lib.ptr(b_u), _lib.ptr(a_l), B, n, _stream_ptr(device),
+            )
+        )
+        au.append(a_u)
+        bu.append(b_u)
+        al.append(a_l)
+    return au, bu, al, keep
+
+
+def crown_from_trace(
+    trace: ForwardTrace,
+    linear_spec_C: Optional[torch.Tensor],
+    *,
+    output_value: Optional[str] = None,
+    relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+    sides: Sequence[int] = (_lib.SIDE_LOWER, _lib.SIDE_UPPER),
+) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Backward sweep(s) on the device; returns (lower, upper) [B,S] CUDA tensors."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    upto = chain.layers_upto(output_value)
+    out_shape = chain.layers[upto - 1].out_shape
+    out_dim = 1
+    for d in out_shape:
+        out_dim *= int(d)
+    C = _expand_spec(linear_spec_C, B, out_dim, device)
+    S = int(C.shape[1])
+    n_relu = sum(1 for i in chain.relu_layer_ids if i < upto)
+    au, bu, al, keep = _relaxations(trace, relu_alpha, n_relu)
+    add = None
+    if relu_pre_add_coeff_l:
+        add = [None] * n_relu
+        for r in range(n_relu):
+            name = chain.relu_input_names[r]
+            if name in relu_pre_add_coeff_l:
+                t = relu_pre_add_coeff_l[name]
+                t = t.detach().to(device=device, dtype=torch.float32)
+                n = chain.relu_widths[r]
+                add[r] = (t.reshape(1, n).expand(B, n) if t.numel() == n else t.reshape(B, n)).contiguous()
+    nbytes = int(chain.lib.bf_chain_crown_workspace_bytes(chain.handle, B, S, upto))
+    ws = _Workspace.get(device, nbytes)
+    outs: List[Optional[torch.Tensor]] = [None, None]
+    for side in sides:
+        out = torch.empty(B, S, dtype=torch.float32, device=device)
+        _lib.check(
+            chain.lib.bf_chain_crown(
+                chain.handle, upto, side, _lib.ptr(C),
+                _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add),
+                _lib.ptr(trace.mid), _lib.ptr(trace.rad), _lib.ptr(out),
+                _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+            )
+        )
+        outs[side] = out
+    return outs[0], outs[1]
+
+
+def run_crown_ibp_mlp(
+    module: Any,
+    input_spec: Any,
+    *,
+    linear_spec_C: Optional[torch.Tensor] = None,
+    output_value: Optional[str] = None,
+    relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+) -> IntervalState:
+    """IBP trace + one CROWN backward sweep per side (crown_ibp.py:2054-2133)."""
+    if relu_pre_add_coeff_u:
+        raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
+    _raise_if_infeasible(trace, "relu split")
+    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+    dev = normalize_input_spec(input_spec).center.device
+    return IntervalState(lower=lo.to(dev), upper=up.to(dev))
+
+
+def run_crown_ibp_mlp_from_forward_trace(
+    module: Any,
+    input_spec: Any,
+    *,
+    interval_env: Mapping[str, Any],
+    relu_pre: Mapping[str, Any],
+    linear_spec_C: Optional[torch.Tensor] = None,
+    output_value: Optional[str] = None,
+    relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None,
+    relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+) -> IntervalState:
+    """Backward-only CROWN given a forward trace (crown_ibp.py:2136-2230)."""
+    if relu_pre_add_coeff_u:
+        raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
+    trace = _trace_from_env(module, input_spec, interval_env, relu_pre)
+    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+    dev = normalize_input_spec(input_spec).center.device
+    return IntervalState(lower=lo.to(dev), upper=up.to(dev))
+
+
+def adaptive_alpha_from_trace(trace: ForwardTrace) -> List[torch.Tensor]:
+    """alpha start = 1 where l>=0 or (l<0<u and u>-l), else 0
+    (runtime/native_alpha_beta_optimizer_schedule.py:635-656)."""
+    out = []
+    device = trace.mid.device
+    for l, u, n in zip(trace.pre_l, trace.pre_u, trace.chain.relu_widths):
+        a = torch.empty(trace.B, n, dtype=torch.float32, device=device)
+        _lib.check(trace.chain.lib.bf_alpha_adaptive_init(_lib.ptr(l), _lib.ptr(u), _lib.ptr(a), trace.B, n, _stream_ptr(device)))
+        out.append(a)
+    return out
+
+
+def alpha_crown_from_trace(
+    trace: ForwardTrace,
+    linear_spec_C: torch.Tensor,
+    alpha0: Sequence[torch.Tensor],
+    *,
+    steps: int,
+    lr: float,
+    spec_reduce: str = "mean",
+    want_upper: bool = True,
+):
+    """Device-resident alpha loop; returns (best_lower, best_upper|None, best_alpha list, last alpha list, best_metric)."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    if spec_reduce not in ("mean", "sum"):
+        raise NotImplementedError(f"spec_reduce={spec_reduce!r} is not supported by the CUDA backend (mean | sum)")
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    C = _expand_spec(linear_spec_C, B, n_out, device)
+    S = int(C.shape[1])
+    alpha = [a.detach().to(device=device, dtype=torch.float32).reshape(-1, n).expand(B, n).contiguous().clone() for a, n in zip(alpha0, chain.relu_widths)]
+    best_alpha = [torch.empty_like(a) for a in alpha]
+    best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
+    best_upper = torch.empty(B, S, dtype=torch.float32, device=device) if want_upper else None
+    best_metric = torch.empty(B, dtype=torch.float32, device=device)
+    nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, S))
+    ws = _Workspace.get(device, nbytes)
+    _lib.check(
+        chain.lib.bf_chain_alpha_crown(
+            chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
+            _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+            _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
+            int(steps), float(lr), _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM,
+            _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+        )
+    )
+    return best_lower, best_upper, best_alpha, alpha, best_metric
+
+
+def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alpha: Sequence[torch.Tensor], *, spec_reduce: str = "mean"):
+    """Gradient of -sum_b reduce_s lower wrt alpha and the lower bounds at `alpha`."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    C = _expand_spec(linear_spec_C, B, n_out, device)
+    S = int(C.shape[1])
+    alpha = [a.detach().to(device=device, dtype=torch.float32).reshape(-1, n).expand(B, n).contiguous() for a, n in zip(alpha, chain.relu_widths)]
+    grads = [torch.empty_like(a) for a in alpha]
+    lower = torch.empty(B, S, dtype=torch.float32, device=device)
+    nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, S))
+    ws = _Workspace.get(device, nbytes)
+    _lib.check(
+        chain.lib.bf_chain_alpha_grad(
+            chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.ptr_array(alpha),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad), _lib.ptr_array(grads), _lib.ptr(lower),
+            _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM,
+            _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+        )
+    )
+    return grads, lower
+
+
+def run_alpha_beta_crown_mlp(
+    module: Any,
+    input_spec: Any,
+    *,
+    linear_spec_C: Optional[torch.Tensor] = None,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+    steps: int = 20,
+    lr: float = 0.2,
+    alpha_init: float = 0.5,
+    beta_init: float = 0.0,
+    warm_start_alpha: Optional[Any] = None,
+    warm_start_beta: Optional[Any] = None,
+    objective: str = "lower",
+    spec_reduce: str = "mean",
+    per_batch_params: bool = False,
+    optimize_beta: bool = False,
+):
+    """Per-domain alpha optimisation (alpha_beta_crown.py:643-941).
+
+    Differences from the reference, all explicit: parameters are always
+    per-domain (`per_batch_params=True`; the shared-parameter mode raises
+    NotImplementedError); beta stays at its zero start (`optimize_beta=True`
+    raises NotImplementedError), which for the alpha-only configurations is
+    exactly the reference with beta's learning suppressed; the objective is the
+    lower bound.  Infeasible splits raise ValueError like the reference.
+    """
+    if not per_batch_params:
+        raise NotImplementedError("the CUDA backend optimises per-domain parameters only (per_batch_params=True)")
+    if objective != "lower":
+        raise NotImplementedError("the CUDA backend optimises the lower bound only")
+    if optimize_beta or warm_start_beta is not None or float(beta_init) != 0.0:
+        raise NotImplementedError("beta optimisation is not implemented by the CUDA backend")
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
+    _raise_if_infeasible(trace, "relu split")
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    alpha0 = []
+    for r, name in enumerate(chain.relu_input_names):
+        n = chain.relu_widths[r]
+        ws_map = getattr(warm_start_alpha, "alpha_by_relu_input", None) if warm_start_alpha is not None else None
+        if ws_map is not None and name in ws_map:
+            a, _ = _alpha_rows(ws_map[name], B, n, device, name)
+            alpha0.append(a.expand(B, n))
+        else:
+            alpha0.append(torch.full((B, n), float(alpha_init), dtype=torch.float32, device=device))
+    if linear_spec_C is None:
+        n_out = 1
+        for d in chain.output_shape:
+            n_out *= int(d)
+        linear_spec_C = torch.eye(n_out, dtype=torch.float32, device=device)
+    best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
+    dev = normalize_input_spec(input_spec).center.device
+    bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
+    a_state = AlphaState({n: a.reshape((B,) + tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
+    b_state = BetaState({n: torch.zeros((B,) + tuple(s), dtype=torch.float32, device=dev) for n, s in zip(chain.relu_input_names, chain.relu_shapes)})
+    stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(chain.relu_input_names))
+    return bounds, a_state, b_state, stats
+
+
+def run_crown_intermediate_mlp(
+    module: Any,
+    input_spec: Any,
+    *,
+    linear_spec_C: Optional[torch.Tensor] = None,
+    chunk_rows: int = 1024,
+) -> Tuple[IntervalState, Dict[str, IntervalState]]:
+    """CROWN whose ReLU-input bounds are themselves CROWN bounds.
+
+    For every ReLU input after the first, in graph order: bound it with identity
+    spec rows (in chunks of `chunk_rows` rows per domain), intersect with the
+    current bounds, and re-propagate IBP under those constraints; then bound the
+    spec rows.  Restates runtime/native_intermediate_refinement.py:923-988 on
+    the device.  Returns (final bounds, refined pre-activation bounds)."""
+    trace = ibp_trace(module, input_spec)
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    names = chain.relu_input_names
+    cons = {n: IntervalState(lower=l, upper=u) for n, l, u in zip(names, trace.pre_l, trace.pre_u)}
+    for r, name in enumerate(names):
+        if r == 0:
+            continue  # the first pre-activation's CROWN bound is its IBP bound
+        n = chain.relu_widths[r]
+        new_l = torch.empty(B, n, dtype=torch.float32, device=device)
+        new_u = torch.empty(B, n, dtype=torch.float32, device=device)
+        eye = torch.eye(n, dtype=torch.float32, device=device)
+        for s in range(0, n, int(chunk_rows)):
+            lo, up = crown_from_trace(trace, eye[s : s + int(chunk_rows)], output_value=name)
+            new_l[:, s : s + lo.shape[1]] = lo
+            new_u[:, s : s + up.shape[1]] = up
+        shape = (B,) + tuple(chain.relu_shapes[r])
+        cons[name] = IntervalState(lower=torch.maximum(trace.pre_l[r], new_l).reshape(shape), upper=torch.minimum(trace.pre_u[r], new_u).reshape(shape))
+        for k, nm in enumerate(names):
+            if k != r:
+                cons[nm] = IntervalState(lower=trace.pre_l[k].reshape((B,) + tuple(chain.relu_shapes[k])), upper=trace.pre_u[k].reshape((B,) + tuple(chain.relu_shapes[k])))
+        trace = ibp_trace(module, input_spec, relu_pre_constraints={nm: cons[nm] for nm in names})
+        _raise_if_infeasible(trace, "ReLU pre-activation intersection")
+    lo, up = crown_from_trace(trace, linear_spec_C)
+    dev = normalize_input_spec(input_spec).center.device
+    pre = {nm: IntervalState(lower=trace.pre_l[k].reshape((B,) + tuple(chain.relu_shapes[k])).to(dev), upper=trace.pre_u[k].reshape((B,) + tuple(chain.relu_shapes[k])).to(dev)) for k, nm in enumerate(names)}
+    return IntervalState(lower=lo.to(dev), upper=up.to(dev)), pre
+
+
+@dataclass
+class DomainBatchResult:
+    """Per-domain outcome of one batch of BaB subdomains."""
+
+    lower: torch.Tensor        # [B,S] best lower bounds
+    upper: Optional[torch.Tensor]
+    verdict: torch.Tensor      # int8 [B]: 1 = proven (min_s lower >= threshold - tol)
+    infeasible: torch.Tensor   # int32 [B]: 1 = the split assignment is empty (bounds meaningless)
+    alpha: List[torch.Tensor]  # best alpha per ReLU, [B,n_r] (warm start for the children)
+
+
+def bound_split_domains(
+    module: Any,
+    input_spec: Any,
+    *,
+    linear_spec_C: torch.Tensor,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]],
+    steps: int = 10,
+    lr: float = 0.1,
+    spec_reduce: str = "mean",
+    warm_start_alpha: Optional[Sequence[torch.Tensor]] = None,
+    threshold: float = 0.0,
+    tol: float = 1e-6,
+    want_upper: bool = True,
+) -> DomainBatchResult:
+    """Bound one batch of ReLU-split subdomains: IBP with the split clamps, alpha
+    start from the adaptive rule (or the parents' alpha), `steps` Adam steps, verdicts.
+
+    This is the node-batch evaluation of the BaB driver (runtime/bab.py:1250-1340 stacking
+    split rows and calling run_alpha_beta_crown_mlp(per_batch_params=True) at 1323, then
+    the proven test at 881-895) without the whole-batch ValueError: an infeasible
+    domain is flagged in `infeasible` instead (the driver's per-node fallback,
+    bab.py:1400-1460, exists only to recover from that exception).  No host
+    synchronisation happens inside; tensors follow the input's device."""
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    a0 = list(warm_start_alpha) if warm_start_alpha is not None else adaptive_alpha_from_trace(trace)
+    best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(
+        trace, linear_spec_C, a0, steps=steps, lr=lr, spec_reduce=spec_reduce, want_upper=want_upper)
+    verdict = torch.empty(B, dtype=torch.int8, device=device)
+    _lib.check(chain.lib.bf_verdict(_lib.ptr(best_l), float(threshold), float(tol), _lib.ptr(verdict), None, B, int(best_l.shape[1]), _stream_ptr(device)))
+    out_dev = normalize_input_spec(input_spec).center.device
+    if out_dev != device:
+        return DomainBatchResult(best_l.to(out_dev), None if best_u is None else best_u.to(out_dev), verdict.to(out_dev), trace.infeasible.to(out_dev), [a.to(out_dev) for a in best_a])
+    return DomainBatchResult(best_l, best_u, verdict, trace.infeasible, best_a)

@@ -1,0 +1,232 @@
+// CROWN backward sweep through Linear layers (fused with the ReLU backward
+// transformer and, on the first layer, with the concretisation) and the adjoint
+// (alpha-gradient) sweep, as FP32 FFMA tiles.
+#include "gemm_ffma.cuh"
+#include "kernels.cuh"
+
+namespace bf {
+
+// ---------------------------------------------------------------------------
+// Backward: A_prev[M,N] = relu_bwd(A)[M,K] * W[K,N]
+// ---------------------------------------------------------------------------
+struct BwdEpilogue {
+  float* out;            // [M,N] or nullptr
+  const float* mid;      // [D,N] (only with `partial`)
+  const float* rad;      // [D,N]
+  float* partial;        // [M, gridDim.y] concretisation partial sums or nullptr
+  int side;              // BF_SIDE_LOWER: a*mid - |a|*rad ; BF_SIDE_UPPER: a*mid + |a|*rad
+};
+
+template <int PRO>
+__global__ void __launch_bounds__(GEMM_THREADS, 2) crown_bwd_linear_kernel(GemmArgs g, BwdEpilogue e) {
+  __shared__ __align__(16) float smem[MAINLOOP_SMEM_FLOATS];
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  float acc[8][8];
+  gemm_mainloop<PRO, false>(g, m0, n0, acc, smem);
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const bool vN = g.vecN != 0;
+  const float sgn = (e.side == BF_SIDE_LOWER) ? -1.f : 1.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = m0 + tile_row(ty, i);
+    const bool row_ok = row < g.M;
+    float p = 0.f;
+#pragma unroll
+    for (int jb = 0; jb < 2; ++jb) {
+      const int col = n0 + tile_col(tx, jb);
+      const float4 v = make_float4(acc[i][jb * 4 + 0], acc[i][jb * 4 + 1], acc[i][jb * 4 + 2], acc[i][jb * 4 + 3]);
+      if (row_ok && col < g.N) {
+        if (e.out) store4_guard(e.out + (size_t)row * g.N, col, g.N, vN, v);
+        if (e.partial) {
+          const size_t off = (size_t)(row / g.S) * g.N;
+          const float4 md = load4_guard(e.mid + off, col, g.N, vN);
+          const float4 rd = load4_guard(e.rad + off, col, g.N, vN);
+          p += v.x * md.x + sgn * fabsf(v.x) * rd.x;
+          p += v.y * md.y + sgn * fabsf(v.y) * rd.y;
+          p += v.z * md.z + sgn * fabsf(v.z) * rd.z;
+          p += v.w * md.w + sgn * fabsf(v.w) * rd.w;
+        }
+      }
+    }
+    if (e.partial) {  // uniform across the CTA
+      p += __shfl_xor_sync(0xffffffffu, p, 1);
+      p += __shfl_xor_sync(0xffffffffu, p, 2);
+      p += __shfl_xor_sync(0xffffffffu, p, 4);
+      p += __shfl_xor_sync(0xffffffffu, p, 8);
+      if (tx == 0 && row_ok) e.partial[(size_t)row * gridDim.y + blockIdx.y] = p;
+    }
+  }
+}
+
+int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                            const float* add, const float* W, const float* kbias, float* A_prev, float* delta,
+                            int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S,
+                            int K, int N, cudaStream_t stream) {
+  GemmArgs g{};
+  g.A = A; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
+  const void* kptrs[] = {A, dpos, dneg, epos, eneg, add, kbias};
+  g.vecK = (K % 4 == 0);
+  for (const void* p : kptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecK = 0;
+  const void* nptrs[] = {W, A_prev, mid, rad};
+  g.vecN = (N % 4 == 0);
+  for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
+  g.dpos = dpos; g.dneg = dneg; g.epos = epos; g.eneg = eneg; g.add = add; g.kbias = kbias;
+  g.delta = delta; g.accumulate = accumulate;
+  BwdEpilogue e{A_prev, mid, rad, partial, side};
+  dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
+  timing_begin(0, stream);
+  crown_bwd_linear_kernel<PRO_RELU><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
+  timing_end(0, stream);
+  BF_CHECK_LAUNCH("crown_bwd_linear_kernel");
+  return BF_OK;
+}
+
+int crown_bwd_partial_tiles(int N) { return ceil_div(N, BN); }
+
+// ---------------------------------------------------------------------------
+// Adjoint (gradient) sweep: g[M,N] = h_prev[M,K] * W[N,K]^T + b[N]
+// epilogue: h = d_sel*g + e_sel ; grad[d,n] += sum_s [amb][A>=0] * A * g
+// ---------------------------------------------------------------------------
+struct AdjEpilogue {
+  const float* nbias;  // [N] bias of this layer (nullable)
+  const float* Ahat;   // [M,N] coefficients w.r.t. this layer's ReLU output, saved by the backward sweep
+  const float* dpos;   // [D,N]
+  const float* dneg;   // [D,N]
+  const float* epos;   // [D,N] nullable
+  const float* eneg;   // [D,N] nullable
+  const float* pre_l;  // [D,N]
+  const float* pre_u;  // [D,N]
+  float* hout;         // [M,N] or nullptr (last ReLU layer needs no adjoint point)
+  float* grad;         // [D,N], accumulated with atomicAdd (at most two tiles touch one entry when S <= 128)
+};
+
+constexpr int STAGE_LD = BN + 1;
+constexpr int ADJ_SMEM_BYTES = BM * STAGE_LD * (int)sizeof(float);
+static_assert(ADJ_SMEM_BYTES >= MAINLOOP_SMEM_FLOATS * (int)sizeof(float), "stage buffer must cover the main loop slabs");
+
+template <int PRO>
+__global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(GemmArgs g, AdjEpilogue e) {
+  extern __shared__ __align__(16) float dsmem[];
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  float acc[8][8];
+  gemm_mainloop<PRO, true>(g, m0, n0, acc, dsmem);
+  // the main loop ends with __syncthreads(): the slabs may now be overwritten by the stage tile
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const bool vN = g.vecN != 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = tile_row(ty, i);
+    const int row = m0 + rl;
+#pragma unroll
+    for (int jb = 0; jb < 2; ++jb) {
+      const int cl = tile_col(tx, jb);
+      const int col = n0 + cl;
+      float c4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (row < g.M && col < g.N) {
+        const size_t off = (size_t)(row / g.S) * g.N;
+        float4 nb = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e.nbias) nb = load4_guard(e.nbias, col, g.N, vN);
+        const float4 ah = load4_guard(e.Ahat + (size_t)row * g.N, col, g.N, vN);
+        const float4 dp = load4_guard(e.dpos + off, col, g.N, vN);
+        const float4 dn = load4_guard(e.dneg + off, col, g.N, vN);
+        float4 ep = make_float4(0.f, 0.f, 0.f, 0.f), en = ep;
+        if (e.epos) ep = load4_guard(e.epos + off, col, g.N, vN);
+        if (e.eneg) en = load4_guard(e.eneg + off, col, g.N, vN);
+        const float4 pl = load4_guard(e.pre_l + off, col, g.N, vN);
+        const float4 pu = load4_guard(e.pre_u + off, col, g.N, vN);
+        float4 h;
+#define BF_ADJ(c, idx)                                               \
+  {                                                                  \
+    const float gg = acc[i][jb * 4 + idx] + nb.c;                    \
+    const bool sel = ah.c >= 0.f;                                    \
+    h.c = (sel ? dp.c : dn.c) * gg + (sel ? ep.c : en.c);            \
+    c4[idx] = (sel && pl.c < 0.f && pu.c > 0.f) ? ah.c * gg : 0.f;   \
+  }
+        BF_ADJ(x, 0) BF_ADJ(y, 1) BF_ADJ(z, 2) BF_ADJ(w, 3)
+#undef BF_ADJ
+        if (e.hout) store4_guard(e.hout + (size_t)row * g.N, col, g.N, vN, h);
+        // columns beyond N inside this float4 carry zeros from the guarded loads
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dsmem[rl * STAGE_LD + cl + q] = c4[q];
+    }
+  }
+  __syncthreads();
+
+  // Deterministic per-domain reduction over the spec rows that fall inside this tile.
+  const int c = tid & (BN - 1);
+  const int half = tid >> 7;
+  const int m_end = min(m0 + BM, g.M);
+  const int d_first = m0 / g.S;
+  const int d_last = (m_end - 1) / g.S;
+  const int col = n0 + c;
+  for (int d = d_first + half; d <= d_last; d += 2) {
+    const int r_lo = max(d * g.S, m0) - m0;
+    const int r_hi = min((d + 1) * g.S, m_end) - m0;
+    float s = 0.f;
+    for (int r = r_lo; r < r_hi; ++r) s += dsmem[r * STAGE_LD + c];
+    if (col < g.N) atomicAdd(&e.grad[(size_t)d * g.N + col], s);
+  }
+}
+
+int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
+                                const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
+                                const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
+                                float* hout, float* grad, int M, int S, int K, int N, cudaStream_t stream) {
+  static bool attr_set[2] = {false, false};
+  GemmArgs g{};
+  g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
+  const void* kptrs[] = {Hprev, W, mid, rad};
+  g.vecK = (K % 4 == 0);
+  for (const void* p : kptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecK = 0;
+  const void* nptrs[] = {nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout};
+  g.vecN = (N % 4 == 0);
+  for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
+  g.mid = mid; g.rad = rad;
+  AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad};
+  dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
+  timing_begin(1, stream);
+  if (first_layer) {
+    if (!attr_set[0]) {
+      cudaFuncSetAttribute(crown_adjoint_linear_kernel<PRO_H0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADJ_SMEM_BYTES);
+      attr_set[0] = true;
+    }
+    crown_adjoint_linear_kernel<PRO_H0><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
+  } else {
+    if (!attr_set[1]) {
+      cudaFuncSetAttribute(crown_adjoint_linear_kernel<PRO_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADJ_SMEM_BYTES);
+      attr_set[1] = true;
+    }
+    crown_adjoint_linear_kernel<PRO_PLAIN><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
+  }
+  timing_end(1, stream);
+  BF_CHECK_LAUNCH("crown_adjoint_linear_kernel");
+  return BF_OK;
+}
+
+}  // namespace bf
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" int bf_crown_relu_linear_bwd(const float* A, int side, const float* alpha_u, const float* alpha_l,
+                                        const float* beta_u, const float* beta_l, const float* add, const float* W,
+                                        const float* bias, float* A_prev, float* delta, int accumulate, int B, int S,
+                                        int n_cur, int n_prev, bf_stream_t stream) {
+  BF_REQUIRE(A && W, BF_E_INVALID, "bf_crown_relu_linear_bwd: A and W must be non-null");
+  BF_REQUIRE(B > 0 && S > 0 && n_cur > 0 && n_prev > 0, BF_E_INVALID, "bf_crown_relu_linear_bwd: sizes must be positive");
+  BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_crown_relu_linear_bwd: bad side");
+  BF_REQUIRE(A_prev || delta, BF_E_INVALID, "bf_crown_relu_linear_bwd: nothing to compute");
+  const bool relu = alpha_u || alpha_l || beta_u || beta_l;
+  BF_REQUIRE(!relu || (alpha_u && alpha_l), BF_E_INVALID, "bf_crown_relu_linear_bwd: alpha_u and alpha_l must both be given");
+  BF_REQUIRE((long long)B * S < 2147483647LL, BF_E_INVALID, "bf_crown_relu_linear_bwd: B*S overflows int");
+  const float *dpos = nullptr, *dneg = nullptr, *epos = nullptr, *eneg = nullptr;
+  if (relu) {
+    if (side == BF_SIDE_LOWER) { dpos = alpha_l; dneg = alpha_u; epos = beta_l; eneg = beta_u; }
+    else { dpos = alpha_u; dneg = alpha_l; epos = beta_u; eneg = beta_l; }
+  }
+  return bf::launch_crown_bwd_linear(A, dpos, dneg, epos, eneg, relu ? add : nullptr, W, bias, A_prev, delta, accumulate,
+                                     nullptr, nullptr, nullptr, side, B * S, S, n_cur, n_prev, bf::as_stream(stream));
+}

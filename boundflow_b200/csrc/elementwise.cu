@@ -1,0 +1,246 @@
+// HBM-bound pieces: ReLU relaxation, concretisation, partial-sum finalisation,
+// per-domain best tracking, the fused Adam/projection/slope kernel and verdicts.
+#include <float.h>
+
+#include "kernels.cuh"
+
+namespace bf {
+
+// ---- ReLU relaxation ---------------------------------------------------------
+__device__ __forceinline__ void relax_one(float l, float u, float& au, float& bu, float& al_plain) {
+  // pos = l >= 0 -> slope 1; neg = u <= 0 -> slope 0 and wins when both hold.
+  if (u <= 0.f) { au = 0.f; bu = 0.f; al_plain = 0.f; }
+  else if (l >= 0.f) { au = 1.f; bu = 0.f; al_plain = 1.f; }
+  else {
+    const float denom = fmaxf(u - l, FLT_EPSILON);
+    au = u / denom;
+    bu = -l * au;
+    al_plain = 0.f;
+  }
+}
+
+__global__ void relu_relax_kernel(const float* __restrict__ l, const float* __restrict__ u, const float* __restrict__ alpha,
+                                  int alpha_stride, float* __restrict__ alpha_u, float* __restrict__ beta_u,
+                                  float* __restrict__ alpha_l, int n, long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float lo = l[i], up = u[i];
+    float au, bu, al;
+    relax_one(lo, up, au, bu, al);
+    if (alpha != nullptr && lo < 0.f && up > 0.f) {
+      const long long b = i / n;
+      const int j = (int)(i - b * n);
+      const float a = alpha[b * (long long)alpha_stride + j];
+      al = fminf(fmaxf(a, 0.f), 1.f);
+    }
+    alpha_u[i] = au;
+    beta_u[i] = bu;
+    alpha_l[i] = al;
+  }
+}
+
+static int ew_grid(long long total, int threads) {
+  long long blocks = (total + threads - 1) / threads;
+  const long long cap = 148LL * 16;
+  return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+int launch_relu_relax(const float* l, const float* u, const float* alpha, int alpha_stride, float* alpha_u,
+                      float* beta_u, float* alpha_l, int B, int n, cudaStream_t stream) {
+  const long long total = (long long)B * n;
+  relu_relax_kernel<<<ew_grid(total, 256), 256, 0, stream>>>(l, u, alpha, alpha_stride, alpha_u, beta_u, alpha_l, n, total);
+  BF_CHECK_LAUNCH("relu_relax_kernel");
+  return BF_OK;
+}
+
+// ---- concretisation: one warp per coefficient row -----------------------------
+__global__ void __launch_bounds__(256) concretize_kernel(const float* __restrict__ A, const float* __restrict__ mid,
+                                                         const float* __restrict__ rad, const float* __restrict__ bias_in,
+                                                         float* __restrict__ out, float sgn, int M, int S, int n0, int vec) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int m = warp; m < M; m += nwarps) {
+    const float* a = A + (size_t)m * n0;
+    const size_t off = (size_t)(m / S) * n0;
+    float center = 0.f, dev = 0.f;
+    for (int k = lane * 4; k < n0; k += 128) {
+      const float4 av = load4_guard(a, k, n0, vec != 0);
+      const float4 md = load4_guard(mid + off, k, n0, vec != 0);
+      const float4 rd = load4_guard(rad + off, k, n0, vec != 0);
+      center = fmaf(av.x, md.x, center); center = fmaf(av.y, md.y, center);
+      center = fmaf(av.z, md.z, center); center = fmaf(av.w, md.w, center);
+      dev = fmaf(fabsf(av.x), rd.x, dev); dev = fmaf(fabsf(av.y), rd.y, dev);
+      dev = fmaf(fabsf(av.z), rd.z, dev); dev = fmaf(fabsf(av.w), rd.w, dev);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      center += __shfl_xor_sync(0xffffffffu, center, o);
+      dev += __shfl_xor_sync(0xffffffffu, dev, o);
+    }
+    if (lane == 0) out[m] = center + sgn * dev + (bias_in ? bias_in[m] : 0.f);
+  }
+}
+
+int launch_concretize(const float* A, const float* mid, const float* rad, const float* bias_in, float* out, int side,
+                      int B, int S, int n0, cudaStream_t stream) {
+  const int M = B * S;
+  int vec = (n0 % 4 == 0);
+  const void* ptrs[] = {A, mid, rad};
+  for (const void* p : ptrs) if (reinterpret_cast<uintptr_t>(p) & 15u) vec = 0;
+  int blocks = ceil_div(M, 8);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  concretize_kernel<<<blocks, 256, 0, stream>>>(A, mid, rad, bias_in, out, side == BF_SIDE_LOWER ? -1.f : 1.f, M, S, n0, vec);
+  BF_CHECK_LAUNCH("concretize_kernel");
+  return BF_OK;
+}
+
+// ---- finalisation of the fused first-layer concretisation ---------------------
+__global__ void sum_partials_kernel(const float* __restrict__ c, const float* __restrict__ partial, int ntiles,
+                                    float* __restrict__ out, int M) {
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float s = 0.f;
+  for (int t = 0; t < ntiles; ++t) s += partial[(size_t)m * ntiles + t];
+  out[m] = s + (c ? c[m] : 0.f);
+}
+
+int launch_sum_partials(const float* c, const float* partial, int ntiles, float* out, int M, cudaStream_t stream) {
+  sum_partials_kernel<<<ceil_div(M, 256), 256, 0, stream>>>(c, partial, ntiles, out, M);
+  BF_CHECK_LAUNCH("sum_partials_kernel");
+  return BF_OK;
+}
+
+// ---- per-domain objective and strict best-of ----------------------------------
+__global__ void select_best_kernel(const float* __restrict__ cur, float* __restrict__ best_lower,
+                                   float* __restrict__ best_metric, int* __restrict__ improve, int first, int spec_reduce,
+                                   int B, int S) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  float s = 0.f;
+  for (int k = 0; k < S; ++k) s += cur[(size_t)b * S + k];
+  const float metric = (spec_reduce == BF_REDUCE_MEAN) ? (s / (float)S) : s;
+  const bool imp = first || (metric > best_metric[b]);
+  if (imp) {
+    best_metric[b] = metric;
+    for (int k = 0; k < S; ++k) best_lower[(size_t)b * S + k] = cur[(size_t)b * S + k];
+  }
+  improve[b] = imp ? 1 : 0;
+}
+
+int launch_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first,
+                       int spec_reduce, int B, int S, cudaStream_t stream) {
+  select_best_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(cur, best_lower, best_metric, improve, first, spec_reduce, B, S);
+  BF_CHECK_LAUNCH("select_best_kernel");
+  return BF_OK;
+}
+
+// ---- Adam + projection + best-alpha snapshot + next lower slope ---------------
+__global__ void adam_step_kernel(float* __restrict__ alpha, float* __restrict__ m, float* __restrict__ v,
+                                 float* __restrict__ grad, const int* __restrict__ improve, float* __restrict__ best_alpha,
+                                 const float* __restrict__ pre_l, const float* __restrict__ pre_u,
+                                 float* __restrict__ slope_l, AdamScalars sc, int do_update, int n, long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long b = i / n;
+    float a = alpha[i];
+    if (improve[b]) best_alpha[i] = a;
+    if (!do_update) continue;
+    const float g = grad[i] * sc.grad_scale;
+    grad[i] = 0.f;
+    // torch.optim.Adam (no amsgrad / weight decay): lerp for the first moment,
+    // mul+addcmul for the second, sqrt(v)/sqrt(bc2)+eps as denominator.
+    float mi = m[i], vi = v[i];
+    mi = mi + sc.one_minus_beta1 * (g - mi);
+    vi = vi * sc.beta2 + sc.one_minus_beta2 * g * g;
+    const float denom = sqrtf(vi) / sc.bc2_sqrt + sc.eps;
+    a = a - sc.lr_step * (mi / denom);
+    a = fminf(fmaxf(a, 0.f), 1.f);
+    m[i] = mi;
+    v[i] = vi;
+    alpha[i] = a;
+    const float lo = pre_l[i], up = pre_u[i];
+    slope_l[i] = (up <= 0.f) ? 0.f : ((lo >= 0.f) ? 1.f : a);
+  }
+}
+
+int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
+                     const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
+                     cudaStream_t stream) {
+  const long long total = (long long)B * n;
+  adam_step_kernel<<<ew_grid(total, 256), 256, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l,
+                                                            sc, do_update, n, total);
+  BF_CHECK_LAUNCH("adam_step_kernel");
+  return BF_OK;
+}
+
+__global__ void scale_copy_kernel(const float* __restrict__ src, float scale, float* __restrict__ dst, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = src[i] * scale;
+}
+
+int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream) {
+  scale_copy_kernel<<<ew_grid(n, 256), 256, 0, stream>>>(src, scale, dst, n);
+  BF_CHECK_LAUNCH("scale_copy_kernel");
+  return BF_OK;
+}
+
+// ---- adaptive alpha start ------------------------------------------------------
+__global__ void alpha_adaptive_init_kernel(const float* __restrict__ l, const float* __restrict__ u, float* __restrict__ alpha,
+                                           long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const float lo = l[i], up = u[i];
+    alpha[i] = (lo >= 0.f || (lo < 0.f && up > 0.f && up > -lo)) ? 1.f : 0.f;
+  }
+}
+
+// ---- verdicts ---------------------------------------------------------------
+__global__ void verdict_kernel(const float* __restrict__ lower, float threshold, float tol, int8_t* __restrict__ verdict,
+                               float* __restrict__ min_lower, int B, int S) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  float mn = lower[(size_t)b * S];
+  for (int k = 1; k < S; ++k) mn = fminf(mn, lower[(size_t)b * S + k]);
+  verdict[b] = (mn >= threshold - tol) ? 1 : 0;
+  if (min_lower) min_lower[b] = mn;
+}
+
+int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
+                   cudaStream_t stream) {
+  verdict_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(lower, threshold, tol, verdict, min_lower, B, S);
+  BF_CHECK_LAUNCH("verdict_kernel");
+  return BF_OK;
+}
+
+}  // namespace bf
+
+extern "C" int bf_relu_relax(const float* l, const float* u, const float* alpha, int alpha_stride, float* alpha_u,
+                             float* beta_u, float* alpha_l, int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(l && u && alpha_u && beta_u && alpha_l, BF_E_INVALID, "bf_relu_relax: null tensor");
+  BF_REQUIRE(B > 0 && n > 0, BF_E_INVALID, "bf_relu_relax: sizes must be positive");
+  BF_REQUIRE(!alpha || alpha_stride == 0 || alpha_stride == n, BF_E_INVALID, "bf_relu_relax: alpha_stride must be 0 or n");
+  return bf::launch_relu_relax(l, u, alpha, alpha_stride, alpha_u, beta_u, alpha_l, B, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_alpha_adaptive_init(const float* l, const float* u, float* alpha, int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(l && u && alpha, BF_E_INVALID, "bf_alpha_adaptive_init: null tensor");
+  BF_REQUIRE(B > 0 && n > 0, BF_E_INVALID, "bf_alpha_adaptive_init: sizes must be positive");
+  const long long total = (long long)B * n;
+  bf::alpha_adaptive_init_kernel<<<bf::ew_grid(total, 256), 256, 0, bf::as_stream(stream)>>>(l, u, alpha, total);
+  BF_CHECK_LAUNCH("alpha_adaptive_init_kernel");
+  return BF_OK;
+}
+
+extern "C" int bf_concretize(const float* A, const float* mid, const float* rad, const float* bias_in, float* out, int side,
+                             int B, int S, int n0, bf_stream_t stream) {
+  BF_REQUIRE(A && mid && rad && out, BF_E_INVALID, "bf_concretize: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n0 > 0, BF_E_INVALID, "bf_concretize: sizes must be positive");
+  BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_concretize: bad side");
+  BF_REQUIRE((long long)B * S < 2147483647LL, BF_E_INVALID, "bf_concretize: B*S overflows int");
+  return bf::launch_concretize(A, mid, rad, bias_in, out, side, B, S, n0, bf::as_stream(stream));
+}
+
+extern "C" int bf_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
+                          bf_stream_t stream) {
+  BF_REQUIRE(lower && verdict, BF_E_INVALID, "bf_verdict: null tensor");
+  BF_REQUIRE(B > 0 && S > 0, BF_E_INVALID, "bf_verdict: sizes must be positive");
+  return bf::launch_verdict(lower, threshold, tol, verdict, min_lower, B, S, bf::as_stream(stream));
+}

@@ -1,0 +1,49 @@
+// Internal launchers shared between the C-ABI wrappers and the chain drivers.
+#pragma once
+#include "common.cuh"
+
+namespace bf {
+
+// crown_linear.cu
+int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                            const float* add, const float* W, const float* kbias, float* A_prev, float* delta,
+                            int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S,
+                            int K, int N, cudaStream_t stream);
+int crown_bwd_partial_tiles(int N);
+int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
+                                const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
+                                const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
+                                float* hout, float* grad, int M, int S, int K, int N, cudaStream_t stream);
+
+// ibp.cu
+int launch_ibp_linear(const float* in_a, const float* in_b, int in_mode, int relu_in, const float* W, const float* bias,
+                      const int8_t* split, int split_stride, const float* cons_l, const float* cons_u, float* out_l,
+                      float* out_u, int* infeasible, int B, int K, int N, cudaStream_t stream);
+
+// elementwise.cu
+int launch_relu_relax(const float* l, const float* u, const float* alpha, int alpha_stride, float* alpha_u,
+                      float* beta_u, float* alpha_l, int B, int n, cudaStream_t stream);
+int launch_concretize(const float* A, const float* mid, const float* rad, const float* bias_in, float* out, int side,
+                      int B, int S, int n0, cudaStream_t stream);
+// lower[m] = c[m] + sum_t partial[m,t]; out may alias nothing else
+int launch_sum_partials(const float* c, const float* partial, int ntiles, float* out, int M, cudaStream_t stream);
+// per-domain objective + strict best-of tracking (first != 0 initialises)
+int launch_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first,
+                       int spec_reduce, int B, int S, cudaStream_t stream);
+struct AdamScalars {
+  float lr_step;      // lr / (1 - beta1^t)
+  float bc2_sqrt;     // sqrt(1 - beta2^t)
+  float beta1, beta2, eps;
+  float one_minus_beta1, one_minus_beta2;
+  float grad_scale;   // -1/S (mean) or -1 (sum): d loss / d lower
+};
+// Snapshot of the best alpha (where improve[b]), Adam update + projection to [0,1], and the
+// lower slope for the next evaluation.  grad is scaled by grad_scale before use and zeroed.
+int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
+                     const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
+                     cudaStream_t stream);
+int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream);
+int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
+                   cudaStream_t stream);
+
+}  // namespace bf

@@ -1,0 +1,193 @@
+"""Executor-step boundary: `CudaTaskExecutor` and `CudaIntervalDomain`.
+
+`CudaTaskExecutor` offers the two methods the reference's schedulers call on an
+executor -- `run_ibp(module, input_spec, output_value=None)`
+(runtime/task_executor.py:108-115, implemented by PythonTaskExecutor at 127-358
+and TVMTaskExecutor runtime/tvm_executor.py:730-1034) and
+`run_ibp_task(task, env=, params=, storage_plan=)` (runtime/scheduler.py:21-30,
+PythonTaskExecutor 360-563) -- and `CudaIntervalDomain` the transformer methods
+of `AbstractDomain` (domains/base.py:5-36, IntervalDomain domains/interval.py:27-114).
+Affine and ReLU work runs in libbf_b200.so; pure data-movement ops (flatten,
+reshape, permute, concat) stay views.  Unsupported ops raise NotImplementedError
+exactly like the reference executors.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+
+from . import _lib
+from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace
+from .ir import IntervalState, normalize_input_spec
+from .network import _pair
+
+
+def _is_interval_kind(kind: Any) -> bool:
+    return getattr(kind, "value", kind) == "interval_ibp"
+
+
+class CudaIntervalDomain:
+    """Interval transformers on the device (centre/radius arithmetic)."""
+
+    @property
+    def domain_id(self) -> str:
+        return "interval"
+
+    def affine_transformer(self, state_in: Any, weight: Any, bias: Any, **attrs: Any) -> IntervalState:
+        if not (hasattr(state_in, "lower") and hasattr(state_in, "upper")):
+            raise TypeError(f"IntervalDomain expects IntervalState, got {type(state_in)}")
+        lib = _lib.load()
+        x_l, x_u = state_in.lower, state_in.upper
+        device = _cuda_device(x_l)
+        w = weight if torch.is_tensor(weight) else torch.as_tensor(weight)
+        w = _f32(w, device)
+        b = None
+        if bias is not None:
+            b = bias if torch.is_tensor(bias) else torch.as_tensor(bias)
+            b = _f32(b, device)
+        op = attrs.get("op")
+        relu_in = 1 if attrs.get("relu_in", False) else 0
+        xl, xu = _f32(x_l, device), _f32(x_u, device)
+        B = int(xl.shape[0])
+        if op == "conv2d" or (op is None and xl.dim() == 4 and w.dim() == 4):
+            st, pd = _pair(attrs.get("stride", 1)), _pair(attrs.get("padding", 0))
+            if _pair(attrs.get("dilation", 1)) != (1, 1) or int(attrs.get("groups", 1)) != 1:
+                raise NotImplementedError("conv2d with dilation or groups is not supported by the CUDA backend")
+            Ci, Hi, Wi = (int(d) for d in xl.shape[1:])
+            Co, _, kh, kw = (int(d) for d in w.shape)
+            Ho = (Hi + 2 * pd[0] - kh) // st[0] + 1
+            Wo = (Wi + 2 * pd[1] - kw) // st[1] + 1
+            y_l = torch.empty(B, Co, Ho, Wo, dtype=torch.float32, device=device)
+            y_u = torch.empty_like(y_l)
+            _lib.check(lib.bf_ibp_conv2d(
+                _lib.ptr(xl), _lib.ptr(xu), _lib.IN_LOWER_UPPER, relu_in, _lib.ptr(w), _lib.ptr(b), None, 0, None, None,
+                _lib.ptr(y_l), _lib.ptr(y_u), None, B, Ci, Hi, Wi, Co, kh, kw, st[0], st[1], pd[0], pd[1], _stream_ptr(device)))
+            return IntervalState(lower=y_l.to(x_l.device), upper=y_u.to(x_l.device))
+        if op not in (None, "linear"):
+            raise NotImplementedError(f"unsupported affine op for IntervalDomain: {op}")
+        lead = tuple(xl.shape[:-1])
+        n_in, n_out = int(w.shape[1]), int(w.shape[0])
+        x2l, x2u = xl.reshape(-1, n_in), xu.reshape(-1, n_in)
+        rows = int(x2l.shape[0])
+        y_l = torch.empty(rows, n_out, dtype=torch.float32, device=device)
+        y_u = torch.empty_like(y_l)
+        _lib.check(lib.bf_ibp_linear(
+            _lib.ptr(x2l), _lib.ptr(x2u), _lib.IN_LOWER_UPPER, relu_in, _lib.ptr(w), _lib.ptr(b), None, 0, None, None,
+            _lib.ptr(y_l), _lib.ptr(y_u), None, rows, n_in, n_out, _stream_ptr(device)))
+        return IntervalState(lower=y_l.reshape(lead + (n_out,)).to(x_l.device), upper=y_u.reshape(lead + (n_out,)).to(x_l.device))
+
+    def relu_transformer(self, state_in: Any) -> IntervalState:
+        if not (hasattr(state_in, "lower") and hasattr(state_in, "upper")):
+            raise TypeError(f"IntervalDomain expects IntervalState, got {type(state_in)}")
+        # The clamp itself is fused into the consuming affine kernel (relu_in); as a
+        # stand-alone transformer it is a pure elementwise view-level op.
+        return IntervalState(lower=state_in.lower.clamp_min(0), upper=state_in.upper.clamp_min(0))
+
+    def elementwise_transformer(self, states_in, op: str) -> IntervalState:
+        if len(states_in) != 2:
+            raise ValueError(f"elementwise '{op}' expects 2 inputs, got {len(states_in)}")
+        a, b = states_in
+        if op == "add":
+            return IntervalState(lower=a.lower + b.lower, upper=a.upper + b.upper)
+        raise NotImplementedError(f"unsupported elementwise op: {op}")
+
+
+class CudaTaskExecutor:
+    """Drop-in for PythonTaskExecutor / TVMTaskExecutor on INTERVAL_IBP tasks."""
+
+    def __init__(self, domain: Optional[CudaIntervalDomain] = None):
+        self.domain = domain or CudaIntervalDomain()
+
+    # ---- whole-module IBP -------------------------------------------------
+    def run_ibp(self, module: Any, input_spec: Any, *, output_value: Optional[str] = None) -> IntervalState:
+        module.validate()
+        task = module.get_entry_task()
+        if not _is_interval_kind(task.kind):
+            raise NotImplementedError(f"CudaTaskExecutor only supports INTERVAL_IBP, got {task.kind}")
+        spec = normalize_input_spec(input_spec)
+        if spec.value_name not in task.input_values:
+            raise ValueError(f"input_spec.value_name '{spec.value_name}' not in task.input_values: {task.input_values}")
+        if output_value is None:
+            if len(task.output_values) != 1:
+                raise ValueError(f"task has {len(task.output_values)} outputs; specify output_value explicitly")
+            output_value = task.output_values[0]
+        trace = ibp_trace(module, spec)
+        chain = trace.chain
+        dev = spec.center.device
+        B = trace.B
+        if output_value == chain.output_name:
+            shape = (B,) + tuple(chain.output_shape)
+            return IntervalState(lower=trace.out_l.reshape(shape).to(dev), upper=trace.out_u.reshape(shape).to(dev))
+        for r, name in enumerate(chain.relu_input_names):
+            shape = (B,) + tuple(chain.relu_shapes[r])
+            if output_value == name:
+                return IntervalState(lower=trace.pre_l[r].reshape(shape).to(dev), upper=trace.pre_u[r].reshape(shape).to(dev))
+            if output_value == chain.layers[chain.relu_layer_ids[r]].out_name:
+                return IntervalState(lower=trace.pre_l[r].reshape(shape).clamp_min(0).to(dev), upper=trace.pre_u[r].reshape(shape).clamp_min(0).to(dev))
+        raise KeyError(f"missing value in env/params: {output_value}")
+
+    # ---- one task of a scheduled task graph -------------------------------
+    def run_ibp_task(self, task: Any, *, env: Dict[str, IntervalState], params: Dict[str, Any], storage_plan: Any) -> None:
+        if not _is_interval_kind(task.kind):
+            raise NotImplementedError(f"CudaTaskExecutor only supports INTERVAL_IBP, got {task.kind}")
+
+        def buf(value_name: str) -> str:
+            logical = storage_plan.value_to_buffer.get(value_name)
+            if logical is None:
+                raise KeyError(f"value not found in storage_plan: {value_name}")
+            return storage_plan.to_physical(logical)
+
+        def get_interval(value_name: str) -> IntervalState:
+            bid = buf(value_name)
+            if bid in env:
+                return env[bid]
+            if value_name in params:
+                t = params[value_name]
+                t = t if torch.is_tensor(t) else torch.as_tensor(t)
+                st = IntervalState(lower=t, upper=t)
+                env[bid] = st
+                return st
+            raise KeyError(f"missing value in env/params: {value_name}")
+
+        def get_tensor(value_name: str) -> Any:
+            if value_name in params:
+                return params[value_name]
+            raise KeyError(f"missing param tensor: {value_name}")
+
+        for op in task.ops:
+            t = op.op_type
+            if t in ("linear", "conv2d"):
+                x = get_interval(op.inputs[0])
+                w = get_tensor(op.inputs[1])
+                b = get_tensor(op.inputs[2]) if len(op.inputs) == 3 else None
+                if torch.is_tensor(w) and w.dim() == 3 and t == "linear":
+                    raise NotImplementedError("batched-weight linear is not supported by the CUDA executor")
+                attrs = dict(op.attrs)
+                attrs["op"] = t
+                env[buf(op.outputs[0])] = self.domain.affine_transformer(x, w, b, **attrs)
+            elif t == "relu":
+                env[buf(op.outputs[0])] = self.domain.relu_transformer(get_interval(op.inputs[0]))
+            elif t == "add":
+                a, b2 = get_interval(op.inputs[0]), get_interval(op.inputs[1])
+                if tuple(a.lower.shape) != tuple(b2.lower.shape):
+                    raise NotImplementedError("CudaTaskExecutor only supports add with exact same-shape inputs")
+                env[buf(op.outputs[0])] = self.domain.elementwise_transformer([a, b2], op="add")
+            elif t == "flatten":
+                x = get_interval(op.inputs[0])
+                sd, ed = int(op.attrs.get("start_dim", 0)), int(op.attrs.get("end_dim", -1))
+                env[buf(op.outputs[0])] = IntervalState(lower=torch.flatten(x.lower, sd, ed), upper=torch.flatten(x.upper, sd, ed))
+            elif t == "reshape":
+                x = get_interval(op.inputs[0])
+                shape = op.attrs.get("shape")
+                env[buf(op.outputs[0])] = x if shape is None else IntervalState(lower=x.lower.reshape(shape), upper=x.upper.reshape(shape))
+            elif t in ("permute", "transpose"):
+                x = get_interval(op.inputs[0])
+                dims = [int(d) for d in op.attrs.get("dims")]
+                env[buf(op.outputs[0])] = IntervalState(lower=x.lower.permute(*dims), upper=x.upper.permute(*dims))
+            elif t == "concat":
+                parts = [get_interval(n) for n in op.inputs]
+                axis = int(op.attrs.get("axis", 1))
+                env[buf(op.outputs[0])] = IntervalState(lower=torch.cat([p.lower for p in parts], dim=axis), upper=torch.cat([p.upper for p in parts], dim=axis))
+            else:
+                raise NotImplementedError(f"unsupported op_type in task executor: {t}")

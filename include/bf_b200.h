@@ -1,0 +1,253 @@
+/*
+ * bf_b200.h -- C ABI of the B200 (sm_100a) bound-propagation backend.
+ *
+ * The reference project (BoundFlow) has no FFI: its plug points are Python
+ * protocols.  Each entry point below names the reference interface whose
+ * arithmetic it replaces (path:line inside the reference project).  All
+ * pointers are DEVICE pointers owned by the caller unless stated otherwise,
+ * all tensors are contiguous row-major fp32 unless stated otherwise, every call
+ * is asynchronous on `stream` and allocates nothing.  Return value: 0 on
+ * success, a negative BF_E_* code otherwise (bf_last_error_string() explains).
+ *
+ * Shapes: B = domains (inputs or BaB subdomains), S = spec rows per domain,
+ * M = B*S coefficient rows, n = neurons of a layer.
+ */
+#ifndef BF_B200_H
+#define BF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* bf_stream_t; /* a cudaStream_t */
+
+#define BF_OK 0
+#define BF_E_INVALID (-1)     /* bad argument (null pointer, non-positive size, ...) */
+#define BF_E_UNSUPPORTED (-2) /* legal request this backend does not implement */
+#define BF_E_WORKSPACE (-3)   /* workspace too small */
+#define BF_E_CUDA (-4)        /* a CUDA runtime call failed */
+
+#define BF_SIDE_LOWER 0
+#define BF_SIDE_UPPER 1
+
+#define BF_IN_LOWER_UPPER 0 /* (in_a, in_b) = (lower, upper) */
+#define BF_IN_MID_RAD 1     /* (in_a, in_b) = (midpoint, radius) */
+
+#define BF_OP_LINEAR 1
+#define BF_OP_CONV2D 2
+#define BF_OP_RELU 3
+#define BF_OP_FLATTEN 4
+
+#define BF_REDUCE_MEAN 0 /* per-domain objective = mean over spec rows */
+#define BF_REDUCE_SUM 1  /* per-domain objective = sum over spec rows  */
+
+/* Library identity and diagnostics. */
+int bf_version(void);
+const char* bf_last_error_string(void);
+/* Number of kernels this library has launched since it was loaded. */
+unsigned long long bf_launch_count(void);
+
+/* Measurement aid (no counterpart in the reference): when enabled, every launch of the
+ * two contraction kernels is bracketed by a CUDA event pair on its own stream.
+ * bf_kernel_timing_read waits for the recorded events and returns the number of launches and
+ * their summed device time since the last enable.  slot 0: CROWN backward contraction,
+ * slot 1: adjoint (gradient) contraction.  Not thread-safe; meant for benchmarks. */
+void bf_kernel_timing_enable(int on);
+int bf_kernel_timing_read(int slot, int* launches, float* total_ms);
+
+/* ------------------------------------------------------------------------
+ * Layer-level kernels
+ * ---------------------------------------------------------------------- */
+
+/* Interval linear layer, optionally preceded by the interval ReLU and followed
+ * by the pre-activation constraint intersection and the ReLU split clamp.
+ *   replaces IntervalDomain.affine_transformer, boundflow/domains/interval.py:79-86
+ *            (W+/W- form; computed here in centre/radius form W*c+b -/+ |W|*r),
+ *            BoxPerturbation.concretize_matmul, boundflow/runtime/perturbation.py:282-325
+ *            (in_mode = BF_IN_MID_RAD or a box given as lower/upper),
+ *            relu_transformer interval.py:88-91 (relu_in != 0),
+ *            the constraint intersection boundflow/runtime/crown_ibp.py:186-209,
+ *            _apply_relu_split crown_ibp.py:70-98.
+ * in_a,in_b [B,n_in]; W [n_out,n_in]; bias [n_out] or NULL;
+ * split int8 [B,n_out] in {-1,0,+1} or NULL, split_stride = n_out or 0 (one row for all domains);
+ * cons_l,cons_u [B,n_out] or NULL; out_l,out_u [B,n_out];
+ * infeasible int32 [B] or NULL: set to 1 where a clamp produced lower > upper (never cleared). */
+int bf_ibp_linear(const float* in_a, const float* in_b, int in_mode, int relu_in,
+                  const float* W, const float* bias,
+                  const int8_t* split, int split_stride,
+                  const float* cons_l, const float* cons_u,
+                  float* out_l, float* out_u, int* infeasible,
+                  int B, int n_in, int n_out, bf_stream_t stream);
+
+/* Interval Conv2d (NCHW input, OIHW weight, groups = 1, dilation = 1), same
+ * fusion options as bf_ibp_linear.
+ *   replaces IntervalDomain.affine_transformer conv2d branch, boundflow/domains/interval.py:57-74. */
+int bf_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, int relu_in,
+                  const float* W, const float* bias,
+                  const int8_t* split, int split_stride,
+                  const float* cons_l, const float* cons_u,
+                  float* out_l, float* out_u, int* infeasible,
+                  int B, int Ci, int Hi, int Wi, int Co, int kh, int kw,
+                  int sh, int sw, int ph, int pw, bf_stream_t stream);
+
+/* ReLU relaxation from pre-activation bounds.
+ *   replaces _relu_relax crown_ibp.py:722-758 and the alpha override
+ *            _relu_backward_relaxation crown_ibp.py:1176-1208.
+ * l,u [B,n]; alpha [B,n] (alpha_stride = n) or [n] (alpha_stride = 0) or NULL;
+ * outputs [B,n]: alpha_u (upper slope), beta_u (upper intercept), alpha_l
+ * (lower slope: 1 / 0 for stable neurons, clamp(alpha,0,1) or 0 for unstable). */
+int bf_relu_relax(const float* l, const float* u, const float* alpha, int alpha_stride,
+                  float* alpha_u, float* beta_u, float* alpha_l,
+                  int B, int n, bf_stream_t stream);
+
+/* Start value of the per-domain lower slopes: 1 where l >= 0 or (l < 0 < u and u > -l), else 0.
+ *   replaces _initial_alpha_state, boundflow/runtime/native_alpha_beta_optimizer_schedule.py:635-656.
+ * l,u,alpha [B,n]. */
+int bf_alpha_adaptive_init(const float* l, const float* u, float* alpha, int B, int n, bf_stream_t stream);
+
+/* Fused ReLU backward + Linear backward region for one side (lower or upper).
+ *   replaces FusedCrownExecutor.run for kind == "linear", boundflow/runtime/fused_crown.py:97-123
+ *            (eager oracle fused_crown.py:330-363; TVM kernel backends/tvm/fused_crown_linear.py:85-156),
+ *            i.e. _backprop_relu_step_dense_reference crown_ibp.py:1262-1298 followed by
+ *            _backprop_linear_step crown_ibp.py:1073-1090.
+ * A [B,S,n_cur] coefficients w.r.t. the ReLU output;
+ * alpha_u, alpha_l, beta_u, beta_l [B,n_cur] (beta_l may be NULL = 0; passing all four
+ * NULL skips the ReLU, giving the plain Linear backward);
+ * add [B,n_cur] or NULL: term added to the scaled coefficients of every spec row (beta-CROWN);
+ * W [n_cur,n_prev], bias [n_cur] or NULL;
+ * A_prev [B,S,n_prev] (may be NULL when only delta is wanted);
+ * delta [B,S]: sum_j A*beta_sel + sum_j A_scaled*bias; if accumulate != 0 it is added to the
+ * existing contents of `delta`, otherwise it overwrites them. */
+int bf_crown_relu_linear_bwd(const float* A, int side,
+                             const float* alpha_u, const float* alpha_l,
+                             const float* beta_u, const float* beta_l,
+                             const float* add,
+                             const float* W, const float* bias,
+                             float* A_prev, float* delta, int accumulate,
+                             int B, int S, int n_cur, int n_prev, bf_stream_t stream);
+
+/* Fused ReLU backward + Conv2d backward (transposed convolution) for one side.
+ *   replaces FusedCrownExecutor.run for kind == "conv2d", fused_crown.py:365-400
+ *            (TVM kernel backends/tvm/fused_crown_conv2d.py:202-344), i.e.
+ *            _backprop_conv2d_step crown_ibp.py:1106-1173 with Conv2dLinearOperator.to_dense
+ *            boundflow/runtime/linear_operator.py:1067-1092.
+ * A [B,S,Co*Ho*Wo]; slopes [B,Co*Ho*Wo]; W OIHW [Co,Ci,kh,kw]; bias [Co] or NULL;
+ * A_prev [B,S,Ci*Hi*Wi]; delta [B,S] as above.  groups = 1, dilation = 1; any kernel size,
+ * stride and padding with 0 <= output_padding < stride.  `scratch` (device,
+ * bf_crown_relu_conv2d_bwd_scratch_bytes) holds the ReLU-scaled coefficients between the
+ * two passes; it may be NULL when no ReLU is applied. */
+size_t bf_crown_relu_conv2d_bwd_scratch_bytes(int B, int S, int Co, int Ho, int Wo);
+int bf_crown_relu_conv2d_bwd(const float* A, int side,
+                             const float* alpha_u, const float* alpha_l,
+                             const float* beta_u, const float* beta_l,
+                             const float* W, const float* bias,
+                             float* A_prev, float* delta, int accumulate,
+                             void* scratch, size_t scratch_bytes,
+                             int B, int S, int Ci, int Hi, int Wi, int Co, int Ho, int Wo,
+                             int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
+
+/* Concretisation of an affine form over a box (or L-inf ball: rad == eps).
+ *   replaces BoxPerturbation.concretize_affine perturbation.py:327-359 and
+ *            LpBallPerturbation.concretize_affine (p = inf) perturbation.py:175-222.
+ * A [B,S,n0]; mid, rad [B,n0]; bias_in [B,S] or NULL; out [B,S]:
+ *   lower: A.mid - |A|.rad + bias_in     upper: A.mid + |A|.rad + bias_in */
+int bf_concretize(const float* A, const float* mid, const float* rad, const float* bias_in,
+                  float* out, int side, int B, int S, int n0, bf_stream_t stream);
+
+/* Verdict per domain: proven iff min over spec rows of the lower bound >= threshold - tol.
+ *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895.
+ * lower [B,S]; verdict int8 [B] (1 proven, 0 not); min_lower [B] or NULL. */
+int bf_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower,
+               int B, int S, bf_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Whole-chain drivers (host loops over the kernels above; no host sync)
+ * ---------------------------------------------------------------------- */
+
+typedef struct bf_layer_desc {
+  int op;            /* BF_OP_* */
+  const float* W;    /* linear [n_out,n_in]; conv2d OIHW; NULL otherwise */
+  const float* bias; /* [n_out] / [Co] or NULL */
+  int n_in, n_out;   /* flattened feature counts in / out of this layer */
+  int Ci, Hi, Wi, Co, Ho, Wo, kh, kw, sh, sw, ph, pw; /* conv2d only */
+} bf_layer_desc;
+
+typedef struct bf_chain bf_chain; /* opaque: a validated copy of the layer list */
+
+int bf_chain_create(const bf_layer_desc* layers, int n_layers, bf_chain** out);
+void bf_chain_destroy(bf_chain* chain);
+int bf_chain_num_relu(const bf_chain* chain);
+
+/* One IBP sweep that records every ReLU pre-activation.
+ *   replaces _forward_ibp_trace_mlp crown_ibp.py:101-342 (and the op loop of
+ *            PythonTaskExecutor.run_ibp boundflow/runtime/task_executor.py:127-358,
+ *            TVMTaskExecutor.run_ibp boundflow/runtime/tvm_executor.py:730-1034).
+ * in_a,in_b [B,n0] per in_mode; `splits`, `cons_l`, `cons_u`, `pre_l`, `pre_u` are HOST arrays
+ * of device pointers, one entry per ReLU in chain order (entries or whole arrays may be NULL
+ * for splits/constraints); pre_l[r],pre_u[r] [B,n_r] receive the clamped pre-activation
+ * bounds; out_l,out_u [B,n_last] the chain output bounds; infeasible int32 [B] or NULL.
+ * scratch: 2 * B * max_width floats (device) used when a layer's output is not a ReLU input. */
+int bf_chain_ibp(const bf_chain* chain, const float* in_a, const float* in_b, int in_mode,
+                 const int8_t* const* splits, const int* split_strides,
+                 const float* const* cons_l, const float* const* cons_u,
+                 float* const* pre_l, float* const* pre_u,
+                 float* out_l, float* out_u, int* infeasible,
+                 float* scratch, size_t scratch_bytes, int B, bf_stream_t stream);
+
+size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, int S, int upto_layer);
+
+/* One CROWN backward sweep + concretisation for one side.
+ *   replaces _run_crown_backward_from_trace crown_ibp.py:1669-2051 for chain graphs
+ *            (run_crown_ibp_mlp crown_ibp.py:2054, run_crown_ibp_mlp_from_forward_trace crown_ibp.py:2136).
+ * Bounds C @ (output of layers[0:upto_layer]) (upto_layer = number of layers for the chain
+ * output).  C [B,S,O] (a spec shared by all domains is expanded by the caller).
+ * alpha_u/beta_u/alpha_l: HOST arrays of device pointers per ReLU, each [B,n_r] (from
+ * bf_relu_relax); add: per ReLU [B,n_r] or NULL entries / NULL array (lower side only).
+ * mid, rad [B,n0]; out [B,S]. */
+int bf_chain_crown(const bf_chain* chain, int upto_layer, int side,
+                   const float* C,
+                   const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                   const float* const* add,
+                   const float* mid, const float* rad, float* out,
+                   void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S);
+
+/* Per-domain alpha-CROWN: steps+1 lower-bound evaluations, analytic alpha gradient,
+ * Adam(lr, 0.9, 0.999, 1e-8), projection to [0,1], strict per-domain best tracking, and
+ * one upper-bound evaluation at the best alpha.  Linear/ReLU chains only.
+ *   replaces run_alpha_beta_crown_mlp(per_batch_params=True, objective="lower") with beta at
+ *            zero, boundflow/runtime/alpha_beta_crown.py:643-941 (loop 756-923), whose gradient
+ *            comes from torch autograd through crown_ibp.py:1211-1298.
+ * pre_l,pre_u: HOST arrays of device pointers [B,n_r] (from bf_chain_ibp);
+ * alpha: HOST array of device pointers [B,n_r], in: start values, out: values after the last step;
+ * best_alpha: same layout, out: alpha of each domain's best evaluation;
+ * best_lower,best_upper [B,S] (best_upper may be NULL to skip the upper sweep);
+ * best_metric [B] or NULL. */
+int bf_chain_alpha_crown(const bf_chain* chain,
+                         const float* C,
+                         const float* const* pre_l, const float* const* pre_u,
+                         float* const* alpha, float* const* best_alpha,
+                         const float* mid, const float* rad,
+                         float* best_lower, float* best_upper, float* best_metric,
+                         int steps, float lr, int spec_reduce,
+                         void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+/* Gradient of  -sum_b reduce_s lower[b,s]  w.r.t. every per-domain alpha at the given alpha
+ * (the tensor torch autograd hands to Adam in alpha_beta_crown.py:913-917), plus the lower
+ * bounds themselves.  grad: HOST array of device pointers [B,n_r]; lower [B,S]. */
+int bf_chain_alpha_grad(const bf_chain* chain,
+                        const float* C,
+                        const float* const* pre_l, const float* const* pre_u,
+                        const float* const* alpha,
+                        const float* mid, const float* rad,
+                        float* const* grad, float* lower, int spec_reduce,
+                        void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BF_B200_H */

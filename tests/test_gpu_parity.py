@@ -1,0 +1,523 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the golden
+vectors of the reference.  Tolerance on every bound: |got-ref| <= 1e-4 + 1e-5*|ref|
+unless a test states otherwise and why."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import assert_close, close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+def _spec(wl, dev, lo=None, up=None):
+    from boundflow_b200.ir import InputSpec
+
+    lo = wl.lo if lo is None else lo
+    up = wl.up if up is None else up
+    return InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+
+
+# ---------------------------------------------------------------------------
+# layer-level kernels, ragged sizes (tile-edge remainders)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("B,n_in,n_out", [(1, 1, 1), (5, 7, 9), (64, 100, 127), (130, 129, 128), (3, 784, 10), (67, 128, 130)])
+def test_ibp_linear_kernel(dev, B, n_in, n_out):
+    from boundflow_b200 import _lib
+    from oracle import crown_oracle as O
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(B * 1000 + n_in)
+    l = torch.randn(B, n_in, generator=g)
+    u = l + torch.rand(B, n_in, generator=g)
+    W = torch.randn(n_out, n_in, generator=g)
+    b = torch.randn(n_out, generator=g)
+    split = torch.randint(-1, 2, (B, n_out), generator=g, dtype=torch.int8)
+    ref_l, ref_u = O.ibp_linear(torch.relu(l), torch.relu(u), W, b)
+    ref_l, ref_u, ref_bad = O.apply_relu_split(ref_l, ref_u, split)
+    d = lambda t: t.to(dev).contiguous()
+    out_l = torch.full((B, n_out), float("nan"), device=dev)
+    out_u = torch.full((B, n_out), float("nan"), device=dev)
+    bad = torch.zeros(B, dtype=torch.int32, device=dev)
+    dl, du, dW, db, ds = d(l), d(u), d(W), d(b), d(split)
+    _lib.check(lib.bf_ibp_linear(dl.data_ptr(), du.data_ptr(), _lib.IN_LOWER_UPPER, 1, dW.data_ptr(), db.data_ptr(), ds.data_ptr(), n_out,
+                                 None, None, out_l.data_ptr(), out_u.data_ptr(), bad.data_ptr(), B, n_in, n_out,
+                                 torch.cuda.current_stream().cuda_stream))
+    assert_close(out_l, ref_l, "ibp lower")
+    assert_close(out_u, ref_u, "ibp upper")
+    # a flag may differ only where lower and upper are within rounding of each other
+    disagree = bad.cpu().bool() != ref_bad
+    if disagree.any():
+        gap = (ref_l - ref_u)[disagree].abs().min()
+        assert gap < 1e-4
+
+
+def test_ibp_first_layer_midrad_and_constraints(dev):
+    from boundflow_b200 import _lib
+    from oracle import crown_oracle as O
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(3)
+    B, n_in, n_out = 9, 50, 33
+    lo = torch.rand(B, n_in, generator=g)
+    up = lo + torch.rand(B, n_in, generator=g) * 0.1
+    W = torch.randn(n_out, n_in, generator=g)
+    inp = O.box_input(lo, up)
+    ref_l, ref_u = O.ibp_first_linear(inp, W, None)
+    cl = ref_l + 0.01
+    cu = ref_u - 0.02
+    d = lambda t: t.to(dev).contiguous()
+    out_l = torch.empty(B, n_out, device=dev)
+    out_u = torch.empty(B, n_out, device=dev)
+    bad = torch.zeros(B, dtype=torch.int32, device=dev)
+    dm, dr, dW, dcl, dcu = d(inp.mid), d(inp.rad), d(W), d(cl), d(cu)
+    _lib.check(lib.bf_ibp_linear(dm.data_ptr(), dr.data_ptr(), _lib.IN_MID_RAD, 0, dW.data_ptr(), None, None, 0, dcl.data_ptr(), dcu.data_ptr(),
+                                 out_l.data_ptr(), out_u.data_ptr(), bad.data_ptr(), B, n_in, n_out, torch.cuda.current_stream().cuda_stream))
+    assert_close(out_l, torch.maximum(ref_l, cl), "constrained lower")
+    assert_close(out_u, torch.minimum(ref_u, cu), "constrained upper")
+    assert torch.equal(bad.cpu().bool(), (torch.maximum(ref_l, cl) > torch.minimum(ref_u, cu)).any(dim=1))
+
+
+def test_relu_relax_kernel(dev):
+    from boundflow_b200 import _lib
+    from oracle import crown_oracle as O
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(11)
+    B, n = 13, 101
+    l = torch.randn(B, n, generator=g)
+    u = l + torch.rand(B, n, generator=g) * 2
+    l[0, :4] = torch.tensor([0.0, -1.0, 0.0, -0.0])
+    u[0, :4] = torch.tensor([0.0, 0.0, 1.0, 0.0])
+    alpha = torch.rand(B, n, generator=g) * 1.4 - 0.2  # outside [0,1] on purpose: clamp on read
+    for a in (None, alpha):
+        ref = O.relu_slopes(l, u, a)
+        outs = [torch.empty(B, n, device=dev) for _ in range(3)]
+        dl, du = l.to(dev), u.to(dev)
+        da = a.to(dev) if a is not None else None
+        _lib.check(lib.bf_relu_relax(dl.data_ptr(), du.data_ptr(), da.data_ptr() if da is not None else None, n,
+                                     outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, n, torch.cuda.current_stream().cuda_stream))
+        assert_close(outs[0], ref[0], "alpha_u", atol=1e-6)
+        assert_close(outs[1], ref[1], "beta_u", atol=1e-6)
+        assert_close(outs[2], ref[2], "alpha_l", atol=1e-6)
+
+
+@pytest.mark.parametrize("D,S,n_cur,n_prev", [(5, 9, 37, 53), (1, 1, 1, 1), (3, 9, 128, 784), (17, 5, 129, 127), (2, 200, 16, 20)])
+def test_fused_relu_linear_region(dev, golden, D, S, n_cur, n_prev):
+    from boundflow_b200.fused import CudaFusedCrownExecutor, FusedReluAffineRequest
+    from oracle import crown_oracle as O
+
+    gen = torch.Generator("cpu").manual_seed(77)
+    A_u = torch.randn(D, S, n_cur, generator=gen)
+    A_l = torch.randn(D, S, n_cur, generator=gen)
+    l = torch.randn(D, n_cur, generator=gen) - 0.2
+    u = l + torch.rand(D, n_cur, generator=gen) * 2.0
+    Wt = torch.randn(n_cur, n_prev, generator=gen)
+    bias = torch.randn(n_cur, generator=gen)
+    au, bu, al, bl = O.relu_relax(l, u)
+    z = torch.zeros(D, S)
+    sA_u, sA_l, d_u, d_l = O.relu_backward(A_u, A_l, z, z, au, bu, al, bl)
+    P_u, d_u = O.linear_backward(sA_u, d_u, Wt, bias)
+    P_l, d_l = O.linear_backward(sA_l, d_l, Wt, bias)
+    t = lambda x: x.to(dev).contiguous()
+    req = FusedReluAffineRequest("linear", t(A_u), t(A_l), t(au), t(al), t(bu), t(bl), t(Wt), t(bias), (n_prev,), (n_cur,), {})
+    ex = CudaFusedCrownExecutor()
+
+    class Ctx:
+        plain_crown = True
+        requires_grad = alpha_enabled = beta_enabled = split_state_present = False
+
+    assert ex.supports(req, Ctx())
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    res = ex.run(req, stream=side)  # custom-stream contract: no global sync inside
+    side.synchronize()
+    tol = dict(atol=1e-4 * max(1.0, n_cur / 64), rtol=1e-5)
+    assert_close(res.A_prev_u, P_u, "A_prev_u", **tol)
+    assert_close(res.A_prev_l, P_l, "A_prev_l", **tol)
+    assert_close(res.bias_delta_u, d_u, "delta_u", **tol)
+    assert_close(res.bias_delta_l, d_l, "delta_l", **tol)
+    if (D, S, n_cur, n_prev) == (5, 9, 37, 53):
+        g = golden("fused_region.npz")
+        assert_close(res.A_prev_u, g["lin_A_prev_u"], "golden A_prev_u")
+        assert_close(res.A_prev_l, g["lin_A_prev_l"], "golden A_prev_l")
+        assert_close(res.bias_delta_u, g["lin_delta_u"], "golden delta_u")
+        assert_close(res.bias_delta_l, g["lin_delta_l"], "golden delta_l")
+
+    class AlphaCtx(Ctx):
+        alpha_enabled = True
+
+    assert not ex.supports(req, AlphaCtx())
+
+
+def test_fused_relu_conv_region_golden(dev, golden):
+    from boundflow_b200.fused import CudaFusedCrownExecutor, FusedReluAffineRequest
+    from oracle import crown_oracle as O
+
+    g = golden("fused_region.npz")
+    D, S, n_cur, n_prev = 5, 9, 37, 53
+    # replay the generator stream of make_golden.py exactly
+    gen = torch.Generator("cpu").manual_seed(77)
+    torch.randn(D, S, n_cur, generator=gen); torch.randn(D, S, n_cur, generator=gen)
+    torch.randn(D, n_cur, generator=gen); torch.rand(D, n_cur, generator=gen)
+    torch.randn(n_cur, n_prev, generator=gen); torch.randn(n_cur, generator=gen)
+    Co, Ho, Wo, Ci, k, st, pd = 6, 5, 5, 3, 4, 2, 1
+    Hi = (Ho - 1) * st - 2 * pd + k
+    A_u = torch.randn(D, S, Co, Ho, Wo, generator=gen)
+    A_l = torch.randn(D, S, Co, Ho, Wo, generator=gen)
+    l = torch.randn(D, Co * Ho * Wo, generator=gen) - 0.2
+    u = l + torch.rand(D, Co * Ho * Wo, generator=gen) * 2.0
+    au, bu, al, bl = O.relu_relax(l, u)
+    Wc = torch.randn(Co, Ci, k, k, generator=gen)
+    bc = torch.randn(Co, generator=gen)
+    t = lambda x: x.to(dev).contiguous()
+    req = FusedReluAffineRequest("conv2d", t(A_u), t(A_l), t(au), t(al), t(bu), t(bl), t(Wc), t(bc), (Ci, Hi, Hi), (Co, Ho, Wo),
+                                 {"stride": (st, st), "padding": (pd, pd)})
+    res = CudaFusedCrownExecutor().run(req)
+    assert_close(res.A_prev_u, g["conv_A_prev_u"], "conv A_prev_u")
+    assert_close(res.A_prev_l, g["conv_A_prev_l"], "conv A_prev_l")
+    assert_close(res.bias_delta_u, g["conv_delta_u"], "conv delta_u")
+    assert_close(res.bias_delta_l, g["conv_delta_l"], "conv delta_l")
+
+
+@pytest.mark.parametrize("B,S,n0", [(1, 1, 1), (4, 9, 784), (3, 7, 130), (2, 5, 3072)])
+def test_concretize_kernel(dev, B, S, n0):
+    from boundflow_b200 import _lib
+    from oracle import crown_oracle as O
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(S)
+    A = torch.randn(B, S, n0, generator=g)
+    lo = torch.rand(B, n0, generator=g)
+    up = lo + torch.rand(B, n0, generator=g) * 0.1
+    bias = torch.randn(B, S, generator=g)
+    inp = O.box_input(lo, up)
+    dA, dm, dr, db = A.to(dev), inp.mid.to(dev), inp.rad.to(dev), bias.to(dev)
+    for side, name in ((_lib.SIDE_LOWER, "lower"), (_lib.SIDE_UPPER, "upper")):
+        out = torch.empty(B, S, device=dev)
+        _lib.check(lib.bf_concretize(dA.data_ptr(), dm.data_ptr(), dr.data_ptr(), db.data_ptr(), out.data_ptr(), side, B, S, n0,
+                                     torch.cuda.current_stream().cuda_stream))
+        assert_close(out, O.concretize(inp, A, bias, name), f"concretize {name}")
+
+
+def test_verdict_kernel(dev):
+    from boundflow_b200 import _lib
+    from oracle import crown_oracle as O
+
+    lib = _lib.load()
+    lower = torch.tensor([[0.5, 0.1], [0.2, -1e-7], [0.3, -1e-3], [-5.0, 4.0]])
+    dl = lower.to(dev)
+    v = torch.empty(4, dtype=torch.int8, device=dev)
+    mn = torch.empty(4, device=dev)
+    _lib.check(lib.bf_verdict(dl.data_ptr(), 0.0, 1e-6, v.data_ptr(), mn.data_ptr(), 4, 2, torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(v.cpu().bool(), O.verdict(lower))
+    assert torch.equal(mn.cpu(), lower.min(dim=1).values)
+
+
+# ---------------------------------------------------------------------------
+# whole-query parity on the five configurations
+# ---------------------------------------------------------------------------
+def test_c1_ibp_and_crown(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import forward_ibp_trace_mlp, run_crown_ibp_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("c1_ibp_crown.npz")
+    wl = W.make_workload("c1")
+    spec = _spec(wl, dev)
+    ibp = CudaTaskExecutor().run_ibp(wl.module, spec)
+    assert ibp.lower.device.type == "cuda"
+    assert_close(ibp.lower, g["ibp_lower"], "ibp lower")
+    assert_close(ibp.upper, g["ibp_upper"], "ibp upper")
+    _, pre = forward_ibp_trace_mlp(wl.module, spec)
+    assert_close(pre["h1"].lower, g["pre1_lower"], "pre1 lower")
+    assert_close(pre["h2"].upper, g["pre2_upper"], "pre2 upper")
+    crown = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev))
+    assert_close(crown.lower, g["crown_lower"], "crown lower")
+    assert_close(crown.upper, g["crown_upper"], "crown upper")
+    linf = run_crown_ibp_mlp(wl.module, InputSpec.linf(value_name="input", center=wl.x.to(dev), eps=wl.eps), linear_spec_C=wl.C.to(dev))
+    assert_close(linf.lower, g["crown_linf_lower"], "crown linf lower")
+    assert_close(linf.upper, g["crown_linf_upper"], "crown linf upper")
+    # host tensors in -> host tensors out (the end-to-end plugin path)
+    host = run_crown_ibp_mlp(wl.module, InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up), linear_spec_C=wl.C)
+    assert host.lower.device.type == "cpu"
+    assert torch.equal(host.lower, crown.lower.cpu())  # deterministic: bit-equal across runs
+
+
+def test_c1_identity_spec_and_shared_spec(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c1", batch=5)
+    spec = _spec(wl, dev)
+    inp = O.box_input(wl.lo, wl.up)
+    lo, up, _ = O.crown_ibp(wl.layers, inp, None)
+    got = run_crown_ibp_mlp(wl.module, spec)
+    assert_close(got.lower, lo, "identity lower")
+    assert_close(got.upper, up, "identity upper")
+    shared = wl.C[0]
+    lo, up, _ = O.crown_ibp(wl.layers, inp, shared)
+    got = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=shared.to(dev))
+    assert_close(got.lower, lo, "shared-spec lower")
+    # intermediate value bounds (output_value=) are CROWN bounds of that value
+    trace = O.forward_ibp_trace(wl.layers, inp)
+    lo2, up2 = O.crown_backward(wl.layers, inp, trace, None, upto=3)
+    got2 = run_crown_ibp_mlp(wl.module, spec, output_value="h2")
+    assert_close(got2.lower, lo2, "h2 lower")
+    assert_close(got2.upper, up2, "h2 upper")
+
+
+def test_c2_cnn(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp, run_crown_intermediate_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+
+    g = golden("c2_cnn.npz")
+    wl = W.make_workload("c2", batch=8)
+    spec = _spec(wl, dev)
+    ibp = CudaTaskExecutor().run_ibp(wl.module, spec)
+    assert_close(ibp.lower, g["ibp_lower"], "ibp lower")
+    assert_close(ibp.upper, g["ibp_upper"], "ibp upper")
+    crown = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev))
+    assert_close(crown.lower, g["crown_lower"], "crown lower")
+    assert_close(crown.upper, g["crown_upper"], "crown upper")
+    wl4 = W.make_workload("c2", batch=4)
+    full, pre = run_crown_intermediate_mlp(wl4.module, _spec(wl4, dev), linear_spec_C=wl4.C.to(dev), chunk_rows=512)
+    assert_close(full.lower, g["full_lower"], "full-crown lower")
+    assert_close(full.upper, g["full_upper"], "full-crown upper")
+    for name in wl4.relu_names:
+        assert_close(pre[name].lower.reshape(4, -1)[:, ::7], g[f"pre_{name}_lower"], f"pre {name} lower")
+        assert_close(pre[name].upper.reshape(4, -1)[:, ::7], g[f"pre_{name}_upper"], f"pre {name} upper")
+
+
+def test_c5_cnn(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp, run_crown_intermediate_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+
+    g = golden("c5_cnn.npz")
+    wl = W.make_workload("c5", batch=2)
+    spec = _spec(wl, dev)
+    ibp = CudaTaskExecutor().run_ibp(wl.module, spec)
+    assert_close(ibp.lower, g["ibp_lower"], "ibp lower")
+    crown = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev))
+    assert_close(crown.lower, g["crown_lower"], "crown lower")
+    assert_close(crown.upper, g["crown_upper"], "crown upper")
+    wl1 = W.make_workload("c5", batch=1)
+    full, pre = run_crown_intermediate_mlp(wl1.module, _spec(wl1, dev), linear_spec_C=wl1.C.to(dev), chunk_rows=1024)
+    assert_close(full.lower, g["full_lower"], "full-crown lower")
+    assert_close(full.upper, g["full_upper"], "full-crown upper")
+    for name in wl1.relu_names:
+        assert_close(pre[name].lower.reshape(1, -1)[:, ::31], g[f"pre_{name}_lower"], f"pre {name} lower")
+
+
+def _alpha0(trace):
+    from boundflow_b200.crown import adaptive_alpha_from_trace
+
+    return adaptive_alpha_from_trace(trace)
+
+
+def test_c3_alpha_crown(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, alpha_grad_from_trace, crown_from_trace, ibp_trace, run_alpha_beta_crown_mlp
+
+    g = golden("c3_alpha.npz")
+    wl = W.make_workload("c3", batch=8)
+    spec = _spec(wl, dev)
+    C = wl.C.to(dev)
+    trace = ibp_trace(wl.module, spec)
+    lo, up = crown_from_trace(trace, C)
+    assert_close(lo, g["plain_lower"], "plain lower")
+    assert_close(up, g["plain_upper"], "plain upper")
+    a0 = _alpha0(trace)
+    names = trace.chain.relu_input_names
+    lo0, up0 = crown_from_trace(trace, C, relu_alpha=dict(zip(names, a0)))
+    assert_close(lo0, g["step0_lower"], "step0 lower")
+    assert_close(up0, g["step0_upper"], "step0 upper")
+    # the analytic gradient equals the reference's autograd gradient (what Adam sees at step 0);
+    # entries are sums of ~1e3-sized products, hence the absolute term
+    grads, lower = alpha_grad_from_trace(trace, C, a0)
+    assert_close(lower, g["step0_lower"], "grad-pass lower")
+    for r, name in enumerate(names):
+        ref = g[f"grad0_{name}"]
+        scale = float(np.abs(ref).max())
+        assert_close(grads[r], ref, f"grad0 {name}", atol=2e-5 * scale, rtol=1e-4)
+    # whole optimisation through the reference-shaped entry point.  20 Adam steps amplify
+    # rounding-level differences (Adam turns even 1e-7-sized gradients into +-lr moves and a
+    # moved alpha flips coefficient signs), so optimised bounds agree to ~1e-4 relative
+    # between any two fp32 implementations; single evaluations above are held to 1e-5.
+    bounds, a_state, _b, stats = run_alpha_beta_crown_mlp(
+        wl.module, spec, linear_spec_C=C, steps=20, lr=0.1, warm_start_alpha=AlphaState(dict(zip(names, a0))), per_batch_params=True)
+    assert_close(bounds.lower, g["best_lower"], "alpha best lower", rtol=3e-4)
+    assert_close(bounds.upper, g["best_upper"], "alpha best upper", rtol=3e-4)
+    assert (bounds.lower.mean(dim=1) >= lo0.mean(dim=1) - 1e-3).all(), "best-of must not be worse than step 0"
+    got_m, ref_m = bounds.lower.mean(dim=1).cpu(), torch.as_tensor(g["best_lower"]).mean(dim=1)
+    assert (got_m >= ref_m - 2e-4 * ref_m.abs()).all(), "optimised objective is as good as the reference's"
+    for name in names:
+        a = a_state.alpha_by_relu_input[name]
+        assert float(a.min()) >= 0.0 and float(a.max()) <= 1.0
+    # the returned bounds are reproduced by one evaluation at the returned alpha
+    lo_chk, up_chk = crown_from_trace(trace, C, relu_alpha=a_state.alpha_by_relu_input)
+    assert_close(lo_chk, bounds.lower, "lower at best alpha")
+    assert_close(up_chk, bounds.upper, "upper at best alpha")
+    s_bounds, _, _, _ = run_alpha_beta_crown_mlp(
+        wl.module, spec, linear_spec_C=C, steps=20, lr=0.1, warm_start_alpha=AlphaState(dict(zip(names, a0))), per_batch_params=True, spec_reduce="sum")
+    assert_close(s_bounds.lower, g["sum_best_lower"], "alpha(sum) best lower", rtol=3e-4)
+
+
+def test_c4_split_domains(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import alpha_crown_from_trace, crown_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    g = golden("c4_split_alpha.npz")
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 24
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    lo = wl.lo.expand(D, -1).contiguous()
+    up = wl.up.expand(D, -1).contiguous()
+    spec = _spec(wl, dev, lo, up)
+    C = wl.C.expand(D, -1, -1).contiguous().to(dev)
+    trace = ibp_trace(wl.module, spec, relu_split_state={n: s.to(dev) for n, s in zip(wl.relu_names, splits)})
+    assert int(trace.infeasible.sum()) == 0
+    for r, name in enumerate(wl.relu_names):
+        # pre-activation bounds are differences of O(1e3) terms: the absolute term scales with them
+        scale = max(1.0, float(np.abs(g[f"pre_{name}_upper"]).max()))
+        assert_close(trace.pre_l[r], g[f"pre_{name}_lower"], f"pre {name} lower", atol=1e-6 * scale + 1e-4)
+        assert_close(trace.pre_u[r], g[f"pre_{name}_upper"], f"pre {name} upper", atol=1e-6 * scale + 1e-4)
+    a0 = _alpha0(trace)
+    lo0, _ = crown_from_trace(trace, C, relu_alpha=dict(zip(wl.relu_names, a0)), sides=(0,))
+    assert_close(lo0, g["step0_lower"], "step0 lower")
+    best_l, best_u, best_a, _, _ = alpha_crown_from_trace(trace, C, a0, steps=10, lr=0.1)
+    assert_close(best_l, g["best_lower"], "best lower", rtol=3e-4)
+    assert_close(best_u, g["best_upper"], "best upper", rtol=3e-4)
+    assert (best_l.mean(dim=1) >= lo0.mean(dim=1) - 1e-2).all()
+
+
+def test_infeasible_split_is_reported_per_domain(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import forward_ibp_trace_mlp, ibp_trace
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c1", batch=6)
+    inp = O.box_input(wl.lo, wl.up)
+    root = O.forward_ibp_trace(wl.layers, inp)
+    l1, u1 = root.pre[0]
+    split = torch.zeros(6, 100, dtype=torch.int8)
+    j_pos = int(torch.nonzero(l1[2] > 0.05)[0])   # stably active neuron forced inactive -> infeasible
+    split[2, j_pos] = -1
+    j_amb = int(torch.nonzero((l1[4] < 0) & (u1[4] > 0))[0])
+    split[4, j_amb] = 1                           # a legal split
+    ref = O.forward_ibp_trace(wl.layers, inp, splits=[split, None])
+    spec = _spec(wl, dev)
+    trace = ibp_trace(wl.module, spec, relu_split_state={"h1": split.to(dev)})
+    assert torch.equal(trace.infeasible.cpu().bool(), ref.infeasible)
+    assert ref.infeasible.tolist() == [False, False, True, False, False, False]
+    assert_close(trace.pre_l[1][4], ref.pre[1][0][4], "feasible row after split")
+    with pytest.raises(ValueError):
+        forward_ibp_trace_mlp(wl.module, spec, relu_split_state={"h1": split.to(dev)})
+
+
+def test_sampled_soundness_c1_and_c3(dev):
+    """Every bound holds on 10^4 uniform samples per input box."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c1", batch=16)
+    got = run_crown_ibp_mlp(wl.module, _spec(wl, dev), linear_spec_C=wl.C.to(dev))
+    inp = O.box_input(wl.lo, wl.up)
+    wlo, wup = O.sample_soundness(wl.layers, inp, wl.C, got.lower.cpu(), got.upper.cpu(), n=10000, seed=1)
+    assert wlo <= 1e-4 and wup <= 1e-4
+    wl = W.make_workload("c3", batch=4)
+    bounds, _, _, _ = run_alpha_beta_crown_mlp(wl.module, _spec(wl, dev), linear_spec_C=wl.C.to(dev), steps=5, lr=0.1, per_batch_params=True)
+    wlo, wup = O.sample_soundness(wl.layers, O.box_input(wl.lo, wl.up), wl.C, bounds.lower.cpu(), bounds.upper.cpu(), n=10000, seed=2)
+    assert wlo <= 1e-2 and wup <= 1e-2   # bounds here are O(1e4); 1e-2 is 1e-6 relative
+
+
+def test_executor_run_ibp_task_matches_whole_module(dev):
+    """Scheduler-style execution (one op per task over a buffer env) equals run_ibp."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import BoundTask, IntervalState, StoragePlan, TaskKind
+
+    wl = W.make_workload("c2", batch=3)
+    spec = _spec(wl, dev)
+    ex = CudaTaskExecutor()
+    whole = ex.run_ibp(wl.module, spec)
+    ops = wl.module.get_entry_task().ops
+    names = {"input"} | {o.outputs[0] for o in ops} | set(wl.module.bindings["params"])
+    plan = StoragePlan(value_to_buffer={n: f"buf_{n}" for n in names})
+    env = {"buf_input": IntervalState(lower=wl.lo.to(dev), upper=wl.up.to(dev))}
+    params = {k: v.to(dev) for k, v in wl.module.bindings["params"].items()}
+    for k, op in enumerate(ops):
+        task = BoundTask(task_id=f"t{k}", kind=TaskKind.INTERVAL_IBP, ops=[op], input_values=[op.inputs[0]], output_values=list(op.outputs))
+        ex.run_ibp_task(task, env=env, params=params, storage_plan=plan)
+    out = env["buf_out"]
+    assert_close(out.lower, whole.lower, "task-by-task lower")
+    assert_close(out.upper, whole.upper, "task-by-task upper")
+    with pytest.raises(NotImplementedError):
+        from boundflow_b200.ir import TaskOp
+
+        bad = BoundTask(task_id="x", kind=TaskKind.INTERVAL_IBP, ops=[TaskOp("softmax", "s", ["input"], ["y"])], input_values=["input"], output_values=["y"])
+        plan.value_to_buffer["y"] = "buf_y"
+        ex.run_ibp_task(bad, env=env, params=params, storage_plan=plan)
+
+
+def test_c4_full_batch_properties(dev):
+    """Full-size subdomain batch (8192 domains): size-independent properties."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import alpha_crown_from_trace, crown_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 8192
+    g = torch.Generator("cpu").manual_seed(4)
+    # cheap vectorised split draw for the full batch (10 unstable neurons per domain)
+    splits = []
+    per_layer = [torch.nonzero(((l < 0) & (u > 0)).reshape(-1)).flatten() for l, u in root.pre]
+    for r, idx in enumerate(per_layer):
+        s = torch.zeros(D, root.pre[r][0].shape[1], dtype=torch.int8)
+        k = 3 if r < 2 else 2
+        pick = idx[torch.randint(0, len(idx), (D, k), generator=g)]
+        sign = (torch.randint(0, 2, (D, k), generator=g) * 2 - 1).to(torch.int8)
+        s.scatter_(1, pick, sign)
+        splits.append(s)
+    spec = _spec(wl, dev, wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+    C = wl.C.expand(D, -1, -1).contiguous().to(dev)
+    trace = ibp_trace(wl.module, spec, relu_split_state={n: s.to(dev) for n, s in zip(wl.relu_names, splits)})
+    feasible = trace.infeasible == 0
+    assert int(feasible.sum()) > D // 2
+    a0 = _alpha0(trace)
+    lo0, _ = crown_from_trace(trace, C, relu_alpha=dict(zip(wl.relu_names, a0)), sides=(0,))
+    best_l, best_u, best_a, _, metric = alpha_crown_from_trace(trace, C, a0, steps=10, lr=0.1)
+    torch.cuda.synchronize()
+    f = feasible.cpu()
+    assert torch.isfinite(best_l[feasible]).all() and torch.isfinite(best_u[feasible]).all()
+    assert (best_l[feasible].mean(dim=1) >= lo0[feasible].mean(dim=1) - 1e-2).all(), "best-of-steps never below step 0"
+    assert (best_l[feasible] <= best_u[feasible] + 1e-2).all(), "lower <= upper"
+    # a split domain is a subset of the root box: its bound can only be tighter than the unsplit root's
+    # pre-activation boxes (IBP monotonicity)
+    for r in range(len(root.pre)):
+        assert (trace.pre_l[r][feasible].cpu() >= root.pre[r][0] - 1e-3).all()
+        assert (trace.pre_u[r][feasible].cpu() <= root.pre[r][1] + 1e-3).all()
+    # spot-check 4 domains against the oracle's evaluation at the returned alpha
+    sel = torch.nonzero(f).flatten()[:4]
+    inp = O.box_input(wl.lo.expand(4, -1).contiguous(), wl.up.expand(4, -1).contiguous())
+    tr = O.forward_ibp_trace(wl.layers, inp, splits=[s[sel] for s in splits])
+    lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, wl.C.expand(4, -1, -1), alpha=[a[sel.to(dev)].cpu() for a in best_a])
+    assert_close(best_l[sel.to(dev)], lo_ref, "oracle at returned alpha (lower)", rtol=3e-5)
+    assert_close(best_u[sel.to(dev)], up_ref, "oracle at returned alpha (upper)", rtol=3e-5)
