@@ -51,6 +51,9 @@ SIGNATURES = {
     "bf_chain_create": (_i, [C.POINTER(LayerDesc), _i, C.POINTER(_p)]),
     "bf_chain_destroy": (None, [_p]),
     "bf_chain_num_relu": (_i, [_p]),
+    "bf_chain_tc_bytes": (_sz, [_p]),
+    "bf_chain_tc_prepare": (_i, [_p, _p, _sz, _p]),
+    "bf_chain_tc_status": (_i, [_p, C.POINTER(_i)]),
     "bf_chain_ibp": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "bf_chain_crown_workspace_bytes": (_sz, [_p, _i, _i, _i]),
     "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _p]),

@@ -3,6 +3,7 @@
 // alpha-CROWN optimisation loop and its analytic gradient).
 #include <math.h>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -81,6 +82,10 @@ struct bf_chain {
   int n0 = 0;
   int max_width = 0;
   bool linear_relu_alternating = false;  // linear (relu linear)*
+  // tensor-core path: per layer, packed hi/lo weight images for the backward (W^T as B) and
+  // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
+  std::vector<const unsigned char*> pk_bwd, pk_adj;
+  int* status = nullptr;
 };
 
 extern "C" int bf_version(void) { return 100; }
@@ -177,6 +182,110 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
                             const bf_layer_desc& L, void* scratch, cudaStream_t stream);
 size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L);
 }  // namespace bf
+
+// ---------------------------------------------------------------------------
+// tensor-core path set-up and dispatch
+// ---------------------------------------------------------------------------
+namespace bf {
+
+static bool tc_allowed() {
+  const char* e = getenv("BF_B200_FORCE_FFMA");
+  return !(e && e[0] == '1');
+}
+
+static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoint, int M, int K, int N) {
+  if (c->pk_bwd.empty() || !tc_allowed()) return nullptr;
+  if (M < 256 || K < 32 || N < 32) return nullptr;  // tiny problems stay on the FFMA tiles
+  return adjoint ? c->pk_adj[layer] : c->pk_bwd[layer];
+}
+
+// Backward contraction of linear layer `layer`; *ptiles receives the number of column tiles
+// (the second dimension of the concretisation partial-sum buffer).
+static int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos, const float* dneg,
+                        const float* epos, const float* eneg, const float* add, float* A_prev, float* delta, int accumulate,
+                        const float* mid, const float* rad, float* partial, int side, int M, int S, int* ptiles,
+                        cudaStream_t stream) {
+  const bf_layer_desc& L = c->layers[layer];
+  const int K = L.n_out, N = L.n_in;
+  const unsigned char* pk = tc_weights(c, layer, false, M, K, N);
+  if (pk) {
+    if (ptiles) *ptiles = crown_tc_partial_tiles(N, K);
+    return launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, add, pk, L.bias, A_prev, delta, accumulate, mid, rad, partial,
+                                      side, M, S, K, N, c->status, stream);
+  }
+  if (ptiles) *ptiles = crown_bwd_partial_tiles(N);
+  return launch_crown_bwd_linear(A, dpos, dneg, epos, eneg, add, L.W, L.bias, A_prev, delta, accumulate, mid, rad, partial, side,
+                                 M, S, K, N, stream);
+}
+
+static int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid,
+                            const float* rad, const float* Ahat, const float* dpos, const float* dneg, const float* epos,
+                            const float* eneg, const float* pre_l, const float* pre_u, float* hout, float* grad, int M, int S,
+                            cudaStream_t stream) {
+  const bf_layer_desc& L = c->layers[layer];
+  const int K = L.n_in, N = L.n_out;
+  const unsigned char* pk = tc_weights(c, layer, true, M, K, N);
+  if (pk)
+    return launch_crown_adjoint_linear_tc(Hprev, first_layer, mid, rad, pk, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
+                                          hout, grad, M, S, K, N, c->status, stream);
+  return launch_crown_adjoint_linear(Hprev, first_layer, mid, rad, L.W, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout,
+                                     grad, M, S, K, N, stream);
+}
+
+}  // namespace bf
+
+extern "C" size_t bf_chain_tc_bytes(const bf_chain* chain) {
+  if (!chain) return 0;
+  size_t total = 256;  // status word
+  for (const bf_layer_desc& L : chain->layers)
+    if (L.op == BF_OP_LINEAR)
+      total += bf::align_up(bf::tc_packed_bytes(L.n_in, L.n_out)) + bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in));
+  return total;
+}
+
+extern "C" int bf_chain_tc_prepare(bf_chain* chain, void* buffer, size_t bytes, bf_stream_t stream_) {
+  BF_REQUIRE(chain && buffer, BF_E_INVALID, "bf_chain_tc_prepare: null argument");
+  BF_REQUIRE((reinterpret_cast<uintptr_t>(buffer) & 255u) == 0, BF_E_INVALID, "bf_chain_tc_prepare: buffer must be 256-byte aligned");
+  BF_REQUIRE(bytes >= bf_chain_tc_bytes(chain), BF_E_WORKSPACE, "bf_chain_tc_prepare: %zu bytes needed", bf_chain_tc_bytes(chain));
+  cudaStream_t stream = bf::as_stream(stream_);
+  unsigned char* base = static_cast<unsigned char*>(buffer);
+  if (cudaMemsetAsync(base, 0, 256, stream) != cudaSuccess) {
+    bf::set_error("bf_chain_tc_prepare: cudaMemsetAsync failed");
+    return BF_E_CUDA;
+  }
+  chain->status = reinterpret_cast<int*>(base);
+  size_t off = 256;
+  chain->pk_bwd.assign(chain->layers.size(), nullptr);
+  chain->pk_adj.assign(chain->layers.size(), nullptr);
+  for (size_t i = 0; i < chain->layers.size(); ++i) {
+    const bf_layer_desc& L = chain->layers[i];
+    if (L.op != BF_OP_LINEAR) continue;
+    // backward: C = Lambda[M, n_out] * W[n_out, n_in]  ->  B[n][k] = W[k][n]  (transposed read)
+    unsigned char* pb = base + off;
+    off += bf::align_up(bf::tc_packed_bytes(L.n_in, L.n_out));
+    int rc = bf::tc_pack_weights(L.W, L.n_out, L.n_in, 1, pb, stream);
+    if (rc != BF_OK) return rc;
+    // adjoint: g = h[M, n_in] * W[n_out, n_in]^T  ->  B[n][k] = W[n][k]
+    unsigned char* pa = base + off;
+    off += bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in));
+    rc = bf::tc_pack_weights(L.W, L.n_out, L.n_in, 0, pa, stream);
+    if (rc != BF_OK) return rc;
+    chain->pk_bwd[i] = pb;
+    chain->pk_adj[i] = pa;
+  }
+  return BF_OK;
+}
+
+extern "C" int bf_chain_tc_status(const bf_chain* chain, int* status_out) {
+  BF_REQUIRE(chain && status_out, BF_E_INVALID, "bf_chain_tc_status: null argument");
+  *status_out = 0;
+  if (!chain->status) return BF_OK;
+  if (cudaMemcpy(status_out, chain->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    bf::set_error("bf_chain_tc_status: cudaMemcpy failed");
+    return BF_E_CUDA;
+  }
+  return BF_OK;
+}
 
 // ---------------------------------------------------------------------------
 // IBP trace
@@ -323,6 +432,7 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
   int have_c = 0;
   int toggle = 0;
   bool fused_concretize = false;
+  int ptiles = 1;
   for (int i = upto_layer - 1; i >= 0; --i) {
     const bf_layer_desc& L = chain->layers[i];
     if (L.op == BF_OP_FLATTEN) continue;
@@ -343,9 +453,8 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
     if (L.op == BF_OP_LINEAR) {
       const bool last = (i == low);
       float* dst = last ? nullptr : ws.buf[toggle];
-      rc = bf::launch_crown_bwd_linear(curA, dpos, dneg, epos, eneg, ad, L.W, L.bias, dst, ws.cacc, have_c,
-                                       last ? mid : nullptr, last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S,
-                                       L.n_out, L.n_in, stream);
+      rc = bf::dispatch_bwd(chain, i, curA, dpos, dneg, epos, eneg, ad, dst, ws.cacc, have_c, last ? mid : nullptr,
+                            last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, &ptiles, stream);
       if (last) fused_concretize = true;
       curA = dst;
     } else {
@@ -361,7 +470,7 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
     pending = -1;
   }
   BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown: a ReLU directly on the input is not supported");
-  if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, bf::crown_bwd_partial_tiles(chain->n0), out, M, stream);
+  if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
   return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
 }
 
@@ -427,13 +536,15 @@ static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int
   const int R = (int)c->relu_layers.size();
   const bf_layer_desc& top = c->layers[2 * R];
   int rc;
+  int ptiles = 1;
+  (void)top;
   if (R == 0) {
-    rc = launch_crown_bwd_linear(C, nullptr, nullptr, nullptr, nullptr, nullptr, top.W, top.bias, keep_A0 ? ws.A0 : nullptr,
-                                 ws.cacc, 0, mid, rad, ws.partial, side, M, S, top.n_out, top.n_in, stream);
+    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, ws.cacc, 0, mid, rad,
+                      ws.partial, side, M, S, &ptiles, stream);
     if (rc != BF_OK) return rc;
   } else {
-    rc = launch_crown_bwd_linear(C, nullptr, nullptr, nullptr, nullptr, nullptr, top.W, top.bias, ws.Ahat[R - 1], ws.cacc, 0,
-                                 nullptr, nullptr, nullptr, side, M, S, top.n_out, top.n_in, stream);
+    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], ws.cacc, 0, nullptr, nullptr,
+                      nullptr, side, M, S, nullptr, stream);
     if (rc != BF_OK) return rc;
     for (int r = R - 1; r >= 0; --r) {
       const bf_layer_desc& L = c->layers[2 * r];
@@ -442,13 +553,12 @@ static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int
       else { dpos = ws.au[r]; dneg = ws.sl[r]; epos = ws.bu[r]; }
       const bool last = (r == 0);
       float* dst = last ? (keep_A0 ? ws.A0 : nullptr) : ws.Ahat[r - 1];
-      rc = launch_crown_bwd_linear(ws.Ahat[r], dpos, dneg, epos, eneg, nullptr, L.W, L.bias, dst, ws.cacc, 1,
-                                   last ? mid : nullptr, last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, L.n_out,
-                                   L.n_in, stream);
+      rc = dispatch_bwd(c, 2 * r, ws.Ahat[r], dpos, dneg, epos, eneg, nullptr, dst, ws.cacc, 1, last ? mid : nullptr,
+                        last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
       if (rc != BF_OK) return rc;
     }
   }
-  return launch_sum_partials(ws.cacc, ws.partial, crown_bwd_partial_tiles(c->n0), out, M, stream);
+  return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
 }
 
 // Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r].
@@ -460,8 +570,8 @@ static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* cons
     const bf_layer_desc& L = c->layers[2 * r];
     const float* hprev = (r == 0) ? ws.A0 : ws.H[(r - 1) & 1];
     float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
-    int rc = launch_crown_adjoint_linear(hprev, r == 0, mid, rad, L.W, L.bias, ws.Ahat[r], ws.sl[r], ws.au[r], nullptr,
-                                         ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r], M, S, L.n_in, L.n_out, stream);
+    int rc = dispatch_adjoint(c, 2 * r, hprev, r == 0, mid, rad, ws.Ahat[r], ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r],
+                              pre_u[r], hout, ws.grad[r], M, S, stream);
     if (rc != BF_OK) return rc;
   }
   return BF_OK;

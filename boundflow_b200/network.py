@@ -142,6 +142,16 @@ class CudaChain:
         handle = C.c_void_p()
         _lib.check(self.lib.bf_chain_create(descs, len(layers), C.byref(handle)))
         self.handle = handle
+        # tensor-core path: split + pack the static weights once (buffer owned here, freed with the chain)
+        nbytes = int(self.lib.bf_chain_tc_bytes(handle))
+        self._tc_buffer = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        _lib.check(self.lib.bf_chain_tc_prepare(handle, self._tc_buffer.data_ptr(), nbytes, torch.cuda.current_stream(self.device).cuda_stream))
+
+    def tc_status(self) -> int:
+        """Synchronous read of the tensor-core kernels' status word (non-zero: a bounded wait expired)."""
+        st = C.c_int(0)
+        _lib.check(self.lib.bf_chain_tc_status(self.handle, C.byref(st)))
+        return int(st.value)
 
     def __del__(self):
         h = getattr(self, "handle", None)

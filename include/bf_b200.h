@@ -181,6 +181,20 @@ int bf_chain_create(const bf_layer_desc* layers, int n_layers, bf_chain** out);
 void bf_chain_destroy(bf_chain* chain);
 int bf_chain_num_relu(const bf_chain* chain);
 
+/* Tensor-core path set-up (no counterpart in the reference, whose GEMMs are cuBLAS calls made
+ * by torch.einsum, boundflow/runtime/linear_operator.py:585-586).  The CROWN backward and
+ * adjoint contractions of Linear layers run as tcgen05 (kind::tf32) tiles with 3xTF32 split
+ * operands once the static weights have been split into hi/lo parts and packed into the
+ * shared-memory image the MMA consumes.  bf_chain_tc_prepare does that packing into a
+ * caller-owned device buffer of bf_chain_tc_bytes(chain) bytes (256-byte aligned) that must
+ * outlive the chain; without it, or with the environment variable BF_B200_FORCE_FFMA=1, or
+ * for tiny problems, the FP32 FFMA kernels are used.  Every wait inside the tensor-core
+ * kernels is bounded; bf_chain_tc_status (synchronous) returns non-zero in *status if a
+ * wait ever expired, in which case results of that call are invalid. */
+size_t bf_chain_tc_bytes(const bf_chain* chain);
+int bf_chain_tc_prepare(bf_chain* chain, void* buffer, size_t bytes, bf_stream_t stream);
+int bf_chain_tc_status(const bf_chain* chain, int* status);
+
 /* One IBP sweep that records every ReLU pre-activation.
  *   replaces _forward_ibp_trace_mlp crown_ibp.py:101-342 (and the op loop of
  *            PythonTaskExecutor.run_ibp boundflow/runtime/task_executor.py:127-358,

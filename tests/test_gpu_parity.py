@@ -505,6 +505,7 @@ def test_c4_full_batch_properties(dev):
     lo0, _ = crown_from_trace(trace, C, relu_alpha=dict(zip(wl.relu_names, a0)), sides=(0,))
     best_l, best_u, best_a, _, metric = alpha_crown_from_trace(trace, C, a0, steps=10, lr=0.1)
     torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
     f = feasible.cpu()
     assert torch.isfinite(best_l[feasible]).all() and torch.isfinite(best_u[feasible]).all()
     assert (best_l[feasible].mean(dim=1) >= lo0[feasible].mean(dim=1) - 1e-2).all(), "best-of-steps never below step 0"
@@ -512,8 +513,9 @@ def test_c4_full_batch_properties(dev):
     # a split domain is a subset of the root box: its bound can only be tighter than the unsplit root's
     # pre-activation boxes (IBP monotonicity)
     for r in range(len(root.pre)):
-        assert (trace.pre_l[r][feasible].cpu() >= root.pre[r][0] - 1e-3).all()
-        assert (trace.pre_u[r][feasible].cpu() <= root.pre[r][1] + 1e-3).all()
+        slack = 1e-5 * float(root.pre[r][1].abs().max()) + 1e-4   # fp32 rounding of O(1e3) sums
+        assert (trace.pre_l[r][feasible].cpu() >= root.pre[r][0] - slack).all()
+        assert (trace.pre_u[r][feasible].cpu() <= root.pre[r][1] + slack).all()
     # spot-check 4 domains against the oracle's evaluation at the returned alpha
     sel = torch.nonzero(f).flatten()[:4]
     inp = O.box_input(wl.lo.expand(4, -1).contiguous(), wl.up.expand(4, -1).contiguous())

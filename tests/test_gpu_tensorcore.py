@@ -1,0 +1,149 @@
+"""The tcgen05 (3xTF32) contraction path against the FP32 FFMA path and the CPU oracle.
+
+The chain drivers pick the tensor-core kernels when B*S >= 256 and the layer is at least
+32 wide; BF_B200_FORCE_FFMA=1 (read at every launch) forces the FFMA tiles, which gives
+an A/B comparison of the two implementations on identical inputs."""
+import os
+
+import pytest
+import torch
+
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+class _ffma:
+    def __enter__(self):
+        os.environ["BF_B200_FORCE_FFMA"] = "1"
+
+    def __exit__(self, *a):
+        os.environ.pop("BF_B200_FORCE_FFMA", None)
+
+
+def _spec(wl, dev):
+    from boundflow_b200.ir import InputSpec
+
+    return InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+
+
+def _launch_delta(fn):
+    from boundflow_b200 import _lib
+
+    n0 = _lib.launch_count()
+    out = fn()
+    return out, _lib.launch_count() - n0
+
+
+def test_tc_crown_matches_ffma_and_oracle_c3(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, crown_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c3", batch=64)   # M = 576 rows, layers 256 wide
+    spec = _spec(wl, dev)
+    C = wl.C.to(dev)
+    trace = ibp_trace(wl.module, spec)
+    a0 = adaptive_alpha_from_trace(trace)
+    alpha = dict(zip(trace.chain.relu_input_names, a0))
+    lo_tc, up_tc = crown_from_trace(trace, C, relu_alpha=alpha)
+    with _ffma():
+        lo_ff, up_ff = crown_from_trace(trace, C, relu_alpha=alpha)
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
+    assert not torch.equal(lo_tc, lo_ff), "the two paths should not be the same kernel"
+    assert_close(lo_tc, lo_ff, "tc vs ffma lower")
+    assert_close(up_tc, up_ff, "tc vs ffma upper")
+    inp = O.box_input(wl.lo, wl.up)
+    tr = O.forward_ibp_trace(wl.layers, inp)
+    lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, wl.C, alpha=[a.cpu() for a in a0])
+    assert_close(lo_tc, lo_ref, "tc vs oracle lower")
+    assert_close(up_tc, up_ref, "tc vs oracle upper")
+
+
+def test_tc_gradient_matches_ffma_and_oracle(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_grad_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c3", batch=40)   # M = 360: a ragged last row tile
+    spec = _spec(wl, dev)
+    C = wl.C.to(dev)
+    trace = ibp_trace(wl.module, spec)
+    a0 = adaptive_alpha_from_trace(trace)
+    a0 = [0.25 + 0.5 * a for a in a0]      # interior alpha: both sign branches carry gradient
+    g_tc, lo_tc = alpha_grad_from_trace(trace, C, a0)
+    with _ffma():
+        g_ff, lo_ff = alpha_grad_from_trace(trace, C, a0)
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
+    assert_close(lo_tc, lo_ff, "lower")
+    inp = O.box_input(wl.lo, wl.up)
+    tr = O.forward_ibp_trace(wl.layers, inp)
+    g_ref, lo_ref = O.alpha_gradient(wl.layers, inp, tr, wl.C, [a.cpu() for a in a0])
+    assert_close(lo_tc, lo_ref, "lower vs oracle")
+    for r in range(len(g_tc)):
+        scale = float(g_ref[r].abs().max())
+        assert_close(g_tc[r], g_ff[r], f"grad {r} tc vs ffma", atol=2e-5 * scale, rtol=1e-4)
+        assert_close(g_tc[r], g_ref[r], f"grad {r} tc vs oracle", atol=2e-5 * scale, rtol=1e-4)
+
+
+@pytest.mark.parametrize("widths,B,S", [((784, 200, 136, 10), 60, 5), ((100, 72, 40, 33, 7), 300, 1), ((64, 512, 300, 10), 29, 9)])
+def test_tc_ragged_shapes(dev, widths, B, S):
+    """Layer widths that are not multiples of the 32-wide k-block or the column tile,
+    row counts that are not multiples of 128, and S values that put several domains in
+    one 8-row group."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import alpha_grad_from_trace, crown_from_trace, ibp_trace
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    net = W.NetSpec((widths[0],), [("fc", w) for w in widths[1:]])
+    g = torch.Generator("cpu").manual_seed(sum(widths))
+    layers, module, names = W.build_chain(net, g)
+    x = torch.rand(B, widths[0], generator=g)
+    lo, up = x - 0.05, x + 0.05
+    C = torch.randn(B, S, widths[-1], generator=g)
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    trace = ibp_trace(module, spec)
+    alpha = [torch.rand(B, w, generator=g) for w in widths[1:-1]]
+    amap = dict(zip(names, [a.to(dev) for a in alpha]))
+    (lo_tc, up_tc), n_launch = _launch_delta(lambda: crown_from_trace(trace, C.to(dev), relu_alpha=amap))
+    inp = O.box_input(lo, up)
+    tr = O.forward_ibp_trace(layers, inp)
+    lo_ref, up_ref = O.crown_backward(layers, inp, tr, C, alpha=alpha)
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
+    scale = max(1.0, float(lo_ref.abs().max()))
+    assert_close(lo_tc, lo_ref, "lower", atol=1e-4 + 2e-6 * scale)
+    assert_close(up_tc, up_ref, "upper", atol=1e-4 + 2e-6 * scale)
+    grads, lower = alpha_grad_from_trace(trace, C.to(dev), [a.to(dev) for a in alpha])
+    g_ref, _ = O.alpha_gradient(layers, inp, tr, C, alpha)
+    for r in range(len(grads)):
+        s = max(1e-3, float(g_ref[r].abs().max()))
+        assert_close(grads[r], g_ref[r], f"grad {r}", atol=3e-5 * s, rtol=1e-4)
+
+
+def test_tc_is_deterministic(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
+
+    wl = W.make_workload("c3", batch=48)
+    trace = ibp_trace(wl.module, _spec(wl, dev))
+    a0 = adaptive_alpha_from_trace(trace)
+    r1 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
+    r2 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
+    assert torch.equal(r1[0], r2[0]) and torch.equal(r1[1], r2[1])
+    for a, b in zip(r1[2], r2[2]):
+        assert torch.equal(a, b)
