@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "kernels.cuh"
@@ -394,7 +395,7 @@ static size_t crown_ws_layout(const bf_chain* c, int B, int S, int upto, void* b
   float* b0 = cv.take<float>(M * maxw);
   float* b1 = cv.take<float>(M * maxw);
   float* cacc = cv.take<float>(M);
-  float* partial = cv.take<float>(M * (size_t)crown_bwd_partial_tiles(c->n0));
+  float* partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
   char* cs = cv.take<char>(conv_scratch);
   if (ws) {
     ws->buf[0] = b0; ws->buf[1] = b1; ws->cacc = cacc; ws->partial = partial; ws->conv_scratch = cs; ws->bytes = cv.off;
@@ -520,7 +521,7 @@ static size_t alpha_ws_layout(const bf_chain* c, int B, int S, void* base, Alpha
   w.H[0] = cv.take<float>(M * (size_t)maxw);
   w.H[1] = cv.take<float>(M * (size_t)maxw);
   w.cacc = cv.take<float>(M);
-  w.partial = cv.take<float>(M * (size_t)crown_bwd_partial_tiles(c->n0));
+  w.partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
   w.cur = cv.take<float>(M);
   w.metric = cv.take<float>((size_t)B);
   w.improve = cv.take<int>((size_t)B);

@@ -17,6 +17,8 @@
 //   tcgen05.ld, transpose through shared memory and write coalesced rows.
 // Every wait is bounded: on expiry the CTA raises a status word, stops, frees its
 // tensor memory and returns (the host reports the status; nothing traps).
+#include <stdlib.h>
+
 #include "kernels.cuh"
 
 namespace bf {
@@ -26,9 +28,14 @@ constexpr int BM = 128;
 constexpr int BK = 32;                  // fp32 per k-block row = 128 bytes
 constexpr int MAX_BN = 256;
 constexpr int A_TILE = BM * BK * 4;     // bytes of one A tile (hi or lo)
-constexpr int PRODUCERS = 128;          // warps 0-3
-constexpr int THREADS = 192;            // + warp 4 (bulk-copy issue) + warp 5 (MMA issue, TMEM alloc)
-constexpr int TMEM_COLS = 256;
+constexpr int A_STAGES = 2;
+constexpr int MAX_B_STAGES = 4;
+constexpr int PROD_WARPS = 8;
+constexpr int PRODUCERS = PROD_WARPS * 32;
+constexpr int COPY_WARP = PROD_WARPS;       // bulk-copy issue
+constexpr int MMA_WARP = PROD_WARPS + 1;    // MMA issue, TMEM alloc / free
+constexpr int THREADS = (PROD_WARPS + 2) * 32;
+constexpr int STG_LD = 36;                  // leading dimension of the per-warp epilogue transpose buffer
 constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
 enum { MODE_BWD = 0, MODE_ADJ = 1 };
@@ -38,7 +45,7 @@ struct Params {
   // operands
   const float* A;            // [M,K]
   const unsigned char* Bpk;  // packed hi/lo images, [ntiles][nkb][2][BN][128 B]
-  int M, N, K, S, BN, nkb, stages;
+  int M, N, K, S, BN, nkb, ntiles, b_stages;
   int vecK, vecN;
   // prologue (see gemm_ffma.cuh for the meaning)
   const float* dpos; const float* dneg; const float* epos; const float* eneg; const float* add; const float* kbias;
@@ -47,12 +54,13 @@ struct Params {
   // backward epilogue
   float* out;                // [M,N] or null
   const float* mid_n; const float* rad_n;   // [D,N] with `partial`
-  float* partial;            // [M, gridDim.y] or null
+  float* partial;            // [M, 2*gridDim.y] or null
   float conc_sign;           // -1 lower, +1 upper
   // adjoint epilogue
   const float* nbias; const float* Ahat; const float* e_dpos; const float* e_dneg; const float* e_epos; const float* e_eneg;
   const float* pre_l; const float* pre_u; float* hout; float* grad;
   int* status;               // device word, set non-zero when a wait expired
+  long long* trace;  // debug timeline of CTA (0,0): [role 0..3][kb 0..31][event 0..3]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -139,38 +147,58 @@ __device__ __forceinline__ float sgnf(float a) { return (a > 0.f) ? 1.f : ((a < 
 
 // Shared-memory control block placed in front of the (1024-byte aligned) tiles.
 struct Control {
-  unsigned long long full[4];
-  unsigned long long empty[4];
+  unsigned long long a_full[A_STAGES];
+  unsigned long long a_empty[A_STAGES];
+  unsigned long long b_full[MAX_B_STAGES];
+  unsigned long long b_empty[MAX_B_STAGES];
   unsigned long long accum;
   uint32_t tmem_base;
   int abort_flag;
 };
 
+// Work split of one CTA (320 threads):
+//   warps 0-7  A producers during the main loop (4 tile rows x one 16-byte chunk per thread and
+//              k-block), then the epilogue (warp w reads TMEM lane quarter w%4, column chunks of
+//              parity w/4)
+//   warp 8     lane 0 issues the bulk copies of the packed weight images
+//   warp 9     lane 0 issues the MMAs; the warp allocates / frees tensor memory
+// A CTA owns 128 rows and up to two column sub-tiles of BN columns (accumulators side by side in
+// tensor memory), so one produced A k-block feeds two sets of MMAs.
 template <int MODE, int PRO>
 __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   extern __shared__ unsigned char raw_smem[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1024 + 1023) & ~(uintptr_t)1023);
   Control* ctl = reinterpret_cast<Control*>(tiles - 1024);
+  unsigned char* b_tiles = tiles + A_STAGES * 2 * A_TILE;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * BM;
-  const int nt = blockIdx.y;
-  const int n0 = nt * p.BN;
-  const int b_bytes = 2 * p.BN * 128;              // hi + lo image of one k-block
-  const int stage_bytes = 2 * A_TILE + b_bytes;
+  const int nt0 = blockIdx.y * 2;                       // first column sub-tile of this CTA
+  const int nh = min(2, p.ntiles - nt0);                // sub-tiles handled here
+  const int ncol0 = nt0 * p.BN;                         // first global column
+  const int ncols = nh * p.BN;                          // accumulator columns in use
+  const int b_bytes = 2 * p.BN * 128;                   // hi + lo image of one k-block of one sub-tile
+  const uint32_t tmem_cols = (ncols <= 256) ? 256u : 512u;
   volatile int* abort_flag = &ctl->abort_flag;
+  const bool tr = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+#define BF_TS(role, kb, ev) \
+  if (tr && (kb) < 32) p.trace[((role) * 32 + (kb)) * 4 + (ev)] = clock64();
 
   if (tid == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), PRODUCERS + 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    for (int s = 0; s < A_STAGES; ++s) {
+      mbar_init(smem_u32(&ctl->a_full[s]), PRODUCERS);
+      mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+    }
+    for (int s = 0; s < p.b_stages; ++s) {
+      mbar_init(smem_u32(&ctl->b_full[s]), 1);
+      mbar_init(smem_u32(&ctl->b_empty[s]), 1);
     }
     mbar_init(smem_u32(&ctl->accum), 1);
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS)
+  if (warp == MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -179,37 +207,36 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
-  if (warp < 4) {
+  if (warp < PROD_WARPS) {
     // ------------------------------------------------------------------ A producers
     const int c = tid & 7;        // 16-byte chunk inside the 128-byte k-block row
-    const int rg = tid >> 3;      // 8-row group (= swizzle atom) of this thread
-    const int row0 = m0 + rg * 8;
+    const int rg = tid >> 3;      // 4-row group of this thread
+    const int row0 = m0 + rg * 4;
     const bool vK = p.vecK != 0;
+    const bool want_delta = (PRO == PRO_RELU) && p.delta != nullptr && blockIdx.y == 0;
     const int d_first = (row0 < p.M) ? (row0 / p.S) : 0;
-    const int d_last = (min(row0 + 7, p.M - 1) >= row0) ? (min(row0 + 7, p.M - 1) / p.S) : d_first;
-    float rowacc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) rowacc[i] = 0.f;
+    const int d_last = (row0 < p.M) ? (min(row0 + 3, p.M - 1) / p.S) : 0;
+    float rowacc[4] = {0.f, 0.f, 0.f, 0.f};
 
-    float4 a_next[8];
+    float4 a_next[4];
     float4 s_next[2][5];  // per domain set: dpos, dneg, epos|mid, eneg|rad, add
     float4 kb_next;
     auto load_block = [&](int kb) {
       const int k = kb * BK + c * 4;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int m = row0 + i;
-        a_next[i] = (m < p.M && k < p.K) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool ok = k < p.K;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = row0 + i;
+        a_next[i] = (m < p.M && ok) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : z;
+      }
       kb_next = z;
       if (PRO == PRO_RELU) {
-        if (p.kbias && k < p.K) kb_next = load4_guard(p.kbias, k, p.K, vK);
+        if (p.kbias && ok) kb_next = load4_guard(p.kbias, k, p.K, vK);
         if (p.dpos) {
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             const size_t off = (size_t)(q == 0 ? d_first : d_last) * p.K;
-            const bool ok = k < p.K;
             s_next[q][0] = ok ? load4_guard(p.dpos + off, k, p.K, vK) : z;
             s_next[q][1] = ok ? load4_guard(p.dneg + off, k, p.K, vK) : z;
             s_next[q][2] = (ok && p.epos) ? load4_guard(p.epos + off, k, p.K, vK) : z;
@@ -221,7 +248,6 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const size_t off = (size_t)(q == 0 ? d_first : d_last) * p.K;
-          const bool ok = k < p.K;
           s_next[q][2] = ok ? load4_guard(p.mid_k + off, k, p.K, vK) : z;
           s_next[q][3] = ok ? load4_guard(p.rad_k + off, k, p.K, vK) : z;
         }
@@ -230,25 +256,27 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
 
     load_block(0);
     bool alive = true;
-    for (int kb = 0; kb < p.nkb && alive; ++kb) {
-      float4 a_cur[8], s_cur[2][5];
+    for (int kb = 0; kb < p.nkb; ++kb) {
+      float4 a_cur[4], s_cur[2][5];
       const float4 kbv = kb_next;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) a_cur[i] = a_next[i];
+      for (int i = 0; i < 4; ++i) a_cur[i] = a_next[i];
 #pragma unroll
       for (int q = 0; q < 2; ++q)
 #pragma unroll
         for (int j = 0; j < 5; ++j) s_cur[q][j] = s_next[q][j];
       if (kb + 1 < p.nkb) load_block(kb + 1);
 
-      const int s = kb % p.stages;
-      const uint32_t phase = (uint32_t)(kb / p.stages) & 1u;
-      if (!mbar_wait(smem_u32(&ctl->empty[s]), phase ^ 1u, abort_flag)) { alive = false; break; }
-      unsigned char* a_hi = tiles + (size_t)s * stage_bytes;
+      const int s = kb % A_STAGES;
+      const uint32_t phase = (uint32_t)(kb / A_STAGES) & 1u;
+      if (tid == 0) BF_TS(0, kb, 0)
+      if (!mbar_wait(smem_u32(&ctl->a_empty[s]), phase ^ 1u, abort_flag)) { alive = false; break; }
+      if (tid == 0) BF_TS(0, kb, 1)
+      unsigned char* a_hi = tiles + (size_t)s * 2 * A_TILE;
       unsigned char* a_lo = a_hi + A_TILE;
       const int k = kb * BK + c * 4;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         float4 a = a_cur[i];
         const int m = row0 + i;
         if (PRO == PRO_RELU) {
@@ -257,7 +285,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
             float4 dp, dn, ep, en, ad;
             if (d == d_first) { dp = s_cur[0][0]; dn = s_cur[0][1]; ep = s_cur[0][2]; en = s_cur[0][3]; ad = s_cur[0][4]; }
             else if (d == d_last) { dp = s_cur[1][0]; dn = s_cur[1][1]; ep = s_cur[1][2]; en = s_cur[1][3]; ad = s_cur[1][4]; }
-            else {  // more than two domains inside 8 rows (S < 7): direct loads
+            else {  // more than two domains inside 4 rows (S < 3): direct loads
               const size_t off = (size_t)d * p.K;
               const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
               const bool ok = k < p.K;
@@ -267,19 +295,26 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
               en = (ok && p.eneg) ? load4_guard(p.eneg + off, k, p.K, vK) : z;
               ad = (ok && p.add) ? load4_guard(p.add + off, k, p.K, vK) : z;
             }
-            float r = rowacc[i];
-#define BF_TC_SEL(cc)                                      \
-  {                                                        \
-    const bool sel = a.cc >= 0.f;                          \
+            if (want_delta) {
+              float r = rowacc[i];
+#define BF_TC_SEL(cc)                                       \
+  {                                                         \
+    const bool sel = a.cc >= 0.f;                           \
     const float lam = a.cc * (sel ? dp.cc : dn.cc) + ad.cc; \
-    r += a.cc * (sel ? ep.cc : en.cc);                     \
-    r = fmaf(lam, kbv.cc, r);                              \
-    a.cc = lam;                                            \
+    r = fmaf(a.cc, sel ? ep.cc : en.cc, r);                 \
+    r = fmaf(lam, kbv.cc, r);                               \
+    a.cc = lam;                                             \
   }
-            BF_TC_SEL(x) BF_TC_SEL(y) BF_TC_SEL(z) BF_TC_SEL(w)
+              BF_TC_SEL(x) BF_TC_SEL(y) BF_TC_SEL(z) BF_TC_SEL(w)
 #undef BF_TC_SEL
-            rowacc[i] = r;
-          } else {
+              rowacc[i] = r;
+            } else {
+              a.x = a.x * (a.x >= 0.f ? dp.x : dn.x) + ad.x;
+              a.y = a.y * (a.y >= 0.f ? dp.y : dn.y) + ad.y;
+              a.z = a.z * (a.z >= 0.f ? dp.z : dn.z) + ad.z;
+              a.w = a.w * (a.w >= 0.f ? dp.w : dn.w) + ad.w;
+            }
+          } else if (want_delta) {
             rowacc[i] += a.x * kbv.x + a.y * kbv.y + a.z * kbv.z + a.w * kbv.w;
           }
         } else if (PRO == PRO_H0) {
@@ -293,51 +328,60 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
               md = load4_guard(p.mid_k + off, k, p.K, vK);
               rd = load4_guard(p.rad_k + off, k, p.K, vK);
             }
+            // lanes of this float4 beyond K stay 0: a, mid and rad were all loaded guarded
             a.x = md.x - sgnf(a.x) * rd.x; a.y = md.y - sgnf(a.y) * rd.y;
             a.z = md.z - sgnf(a.z) * rd.z; a.w = md.w - sgnf(a.w) * rd.w;
-            // lanes of this float4 beyond K stay 0 because mid/rad were loaded guarded
           }
         }
         float4 hi, lo;
         hi.x = tf32_rna(a.x); hi.y = tf32_rna(a.y); hi.z = tf32_rna(a.z); hi.w = tf32_rna(a.w);
         lo.x = tf32_rna(a.x - hi.x); lo.y = tf32_rna(a.y - hi.y); lo.z = tf32_rna(a.z - hi.z); lo.w = tf32_rna(a.w - hi.w);
-        const int off = rg * 1024 + i * 128 + ((c ^ i) << 4);
+        const int rl = rg * 4 + i;  // row inside the tile; 8-row swizzle atoms
+        const int off = (rl >> 3) * 1024 + (rl & 7) * 128 + ((c ^ (rl & 7)) << 4);
         *reinterpret_cast<float4*>(a_hi + off) = hi;
         *reinterpret_cast<float4*>(a_lo + off) = lo;
       }
+      if (tid == 0) BF_TS(0, kb, 2)
       fence_proxy_async();
-      mbar_arrive(smem_u32(&ctl->full[s]));
+      mbar_arrive(smem_u32(&ctl->a_full[s]));
+      if (tid == 0) BF_TS(0, kb, 3)
     }
 
     if (PRO == PRO_RELU) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         float v = rowacc[i];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         v += __shfl_xor_sync(0xffffffffu, v, 4);
         const int m = row0 + i;
-        if (alive && p.delta != nullptr && nt == 0 && c == 0 && m < p.M) p.delta[m] = p.accumulate ? (p.delta[m] + v) : v;
+        if (alive && want_delta && c == 0 && m < p.M) p.delta[m] = p.accumulate ? (p.delta[m] + v) : v;
       }
     }
 
-    // ------------------------------------------------------------------ epilogue (same four warps)
+    // ------------------------------------------------------------------ epilogue (same eight warps)
+    if (tid == 0) BF_TS(3, 0, 0)
     if (alive && mbar_wait(smem_u32(&ctl->accum), 0, abort_flag)) {
+      if (tid == 0) BF_TS(3, 0, 1)
       tc_fence_after();
-      float* stage = reinterpret_cast<float*>(tiles) + warp * (32 * 33);  // per-warp 32x33 transpose buffer
-      const int my_row = m0 + warp * 32 + lane;                          // TMEM lane = tile row
+      const int q = warp & 3;          // TMEM lane quarter = rows q*32 .. q*32+31 of the tile
+      const int half = warp >> 2;      // column chunks of this parity
+      float* stg = reinterpret_cast<float*>(tiles) + warp * (32 * STG_LD);  // per-warp 32 x 36 transpose buffer
+      const int row_base = m0 + q * 32;
+      const int my_row = row_base + lane;  // thread-per-row view right after tcgen05.ld
+      const int rs = lane >> 3, c4 = lane & 7;  // (row sub-index, 16-byte column chunk) view after the transpose
       const bool vN = p.vecN != 0;
       float conc = 0.f;
-      // adjoint: running per-domain column sums, flushed with atomicAdd when the domain changes
-      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+      for (int c0 = half * 32; c0 < ncols; c0 += 64) {
         float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        const int colbase = ncol0 + c0;
         if (MODE == MODE_BWD && p.partial != nullptr && my_row < p.M) {
           const size_t off = (size_t)(my_row / p.S) * p.N;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            const int col = n0 + c0 + j;
-            if (c0 + j < p.BN && col < p.N) {
+            const int col = colbase + j;
+            if (col < p.N) {
               const float4 md = load4_guard(p.mid_n + off, col, p.N, vN);
               const float4 rd = load4_guard(p.rad_n + off, col, p.N, vN);
               conc += v[j] * md.x + p.conc_sign * fabsf(v[j]) * rd.x;
@@ -348,57 +392,96 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
           }
         }
         const bool need_rows = (MODE == MODE_ADJ) || (p.out != nullptr);
-        if (need_rows) {
-          __syncwarp();
+        if (!need_rows) continue;
+        __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = v[j];
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(&stg[lane * STG_LD + 4 * j]) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+        const int col = colbase + c4 * 4;
+        if (MODE == MODE_BWD) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + rs;
+            const int row = row_base + r;
+            if (row < p.M && col < p.N) {
+              const float4 val = *reinterpret_cast<const float4*>(&stg[r * STG_LD + c4 * 4]);
+              store4_guard(p.out + (size_t)row * p.N, col, p.N, vN, val);
+            }
+          }
+        } else {
+          float4 nb = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.nbias && col < p.N) nb = load4_guard(p.nbias, col, p.N, vN);
+#pragma unroll 2
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + rs;
+            const int row = row_base + r;
+            float4 contrib = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < p.M && col < p.N) {
+              const float4 g4 = *reinterpret_cast<const float4*>(&stg[r * STG_LD + c4 * 4]);
+              const size_t off = (size_t)(row / p.S) * p.N;
+              const float4 ah = load4_guard(p.Ahat + (size_t)row * p.N, col, p.N, vN);
+              const float4 dp = load4_guard(p.e_dpos + off, col, p.N, vN);
+              const float4 dn = load4_guard(p.e_dneg + off, col, p.N, vN);
+              float4 ep = make_float4(0.f, 0.f, 0.f, 0.f), en = ep;
+              if (p.e_epos) ep = load4_guard(p.e_epos + off, col, p.N, vN);
+              if (p.e_eneg) en = load4_guard(p.e_eneg + off, col, p.N, vN);
+              const float4 pl = load4_guard(p.pre_l + off, col, p.N, vN);
+              const float4 pu = load4_guard(p.pre_u + off, col, p.N, vN);
+              float4 h;
+#define BF_TC_ADJ(cc)                                                         \
+  {                                                                           \
+    const float gg = g4.cc + nb.cc;                                           \
+    const bool sel = ah.cc >= 0.f;                                            \
+    h.cc = (sel ? dp.cc : dn.cc) * gg + (sel ? ep.cc : en.cc);                \
+    contrib.cc = (sel && pl.cc < 0.f && pu.cc > 0.f) ? ah.cc * gg : 0.f;      \
+  }
+              BF_TC_ADJ(x) BF_TC_ADJ(y) BF_TC_ADJ(z) BF_TC_ADJ(w)
+#undef BF_TC_ADJ
+              if (p.hout) store4_guard(p.hout + (size_t)row * p.N, col, p.N, vN, h);
+            }
+            *reinterpret_cast<float4*>(&stg[r * STG_LD + c4 * 4]) = contrib;  // in place: same lane read this chunk
+          }
           __syncwarp();
-          const int col = n0 + c0 + lane;
-          const bool col_ok = (c0 + lane < p.BN) && (col < p.N);
+          // per-domain column sums over this warp's 32 rows; at most two warps/tiles touch one (domain, column)
+          const int colj = colbase + lane;
           float run = 0.f;
           int run_d = -1;
           for (int r = 0; r < 32; ++r) {
-            const int row = m0 + warp * 32 + r;
+            const int row = row_base + r;
             if (row >= p.M) break;
-            const float val = stage[r * 33 + lane];
-            if (MODE == MODE_BWD) {
-              if (col_ok) p.out[(size_t)row * p.N + col] = val;
-            } else {
-              const int d = row / p.S;
-              if (d != run_d) {
-                if (run_d >= 0 && col_ok) atomicAdd(&p.grad[(size_t)run_d * p.N + col], run);
-                run = 0.f;
-                run_d = d;
-              }
-              if (col_ok) {
-                const size_t off = (size_t)d * p.N + col;
-                const float gg = val + (p.nbias ? __ldg(p.nbias + col) : 0.f);
-                const float ah = __ldg(p.Ahat + (size_t)row * p.N + col);
-                const bool sel = ah >= 0.f;
-                const float dsel = sel ? __ldg(p.e_dpos + off) : __ldg(p.e_dneg + off);
-                const float esel = sel ? (p.e_epos ? __ldg(p.e_epos + off) : 0.f) : (p.e_eneg ? __ldg(p.e_eneg + off) : 0.f);
-                if (p.hout) p.hout[(size_t)row * p.N + col] = dsel * gg + esel;
-                if (sel && __ldg(p.pre_l + off) < 0.f && __ldg(p.pre_u + off) > 0.f) run += ah * gg;
-              }
+            const int d = row / p.S;
+            if (d != run_d) {
+              if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
+              run = 0.f;
+              run_d = d;
             }
+            run += stg[r * STG_LD + lane];
           }
-          if (MODE == MODE_ADJ && run_d >= 0 && col_ok) atomicAdd(&p.grad[(size_t)run_d * p.N + col], run);
+          if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
         }
       }
-      if (MODE == MODE_BWD && p.partial != nullptr && my_row < p.M) p.partial[(size_t)my_row * gridDim.y + nt] = conc;
+      if (MODE == MODE_BWD && p.partial != nullptr && my_row < p.M)
+        p.partial[(size_t)my_row * (2 * gridDim.y) + 2 * blockIdx.y + half] = conc;
       tc_fence_before();
+      if (tid == 0) BF_TS(3, 0, 2)
     }
-  } else if (warp == 4) {
+  } else if (warp == COPY_WARP) {
     // ------------------------------------------------------------------ bulk-copy issue for B
     if (lane == 0) {
-      const unsigned char* src = p.Bpk + (size_t)nt * p.nkb * b_bytes;
+      int it = 0;
       for (int kb = 0; kb < p.nkb; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t phase = (uint32_t)(kb / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&ctl->empty[s]), phase ^ 1u, abort_flag)) break;
-        const uint32_t bar = smem_u32(&ctl->full[s]);
-        mbar_arrive_expect_tx(bar, (uint32_t)b_bytes);
-        bulk_copy_g2s(smem_u32(tiles + (size_t)s * stage_bytes + 2 * A_TILE), src + (size_t)kb * b_bytes, (uint32_t)b_bytes, bar);
+        for (int h = 0; h < nh; ++h, ++it) {
+          const int s = it % p.b_stages;
+          const uint32_t phase = (uint32_t)(it / p.b_stages) & 1u;
+          BF_TS(1, kb, 2 * h)
+          if (!mbar_wait(smem_u32(&ctl->b_empty[s]), phase ^ 1u, abort_flag)) { kb = p.nkb; break; }
+          BF_TS(1, kb, 2 * h + 1)
+          const uint32_t bar = smem_u32(&ctl->b_full[s]);
+          const unsigned char* src = p.Bpk + ((size_t)(nt0 + h) * p.nkb + kb) * b_bytes;
+          mbar_arrive_expect_tx(bar, (uint32_t)b_bytes);
+          bulk_copy_g2s(smem_u32(b_tiles + (size_t)s * b_bytes), src, (uint32_t)b_bytes, bar);
+        }
       }
     }
   } else {
@@ -406,24 +489,33 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       bool ok = true;
-      for (int kb = 0; kb < p.nkb; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t phase = (uint32_t)(kb / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&ctl->full[s]), phase, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t a_hi = smem_u32(tiles + (size_t)s * stage_bytes);
+      int it = 0;
+      for (int kb = 0; kb < p.nkb && ok; ++kb) {
+        const int sa = kb % A_STAGES;
+        BF_TS(2, kb, 0)
+        if (!mbar_wait(smem_u32(&ctl->a_full[sa]), (uint32_t)(kb / A_STAGES) & 1u, abort_flag)) { ok = false; break; }
+        BF_TS(2, kb, 1)
+        const uint32_t a_hi = smem_u32(tiles + (size_t)sa * 2 * A_TILE);
         const uint32_t a_lo = a_hi + A_TILE;
-        const uint32_t b_hi = a_hi + 2 * A_TILE;
-        const uint32_t b_lo = b_hi + p.BN * 128;
+        for (int h = 0; h < nh; ++h, ++it) {
+          const int sb = it % p.b_stages;
+          if (!mbar_wait(smem_u32(&ctl->b_full[sb]), (uint32_t)(it / p.b_stages) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t b_hi = smem_u32(b_tiles + (size_t)sb * b_bytes);
+          const uint32_t b_lo = b_hi + p.BN * 128;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(h * p.BN);
 #pragma unroll
-        for (int j = 0; j < BK / 8; ++j) {
-          const uint64_t dah = make_desc(a_hi + j * 32), dal = make_desc(a_lo + j * 32);
-          const uint64_t dbh = make_desc(b_hi + j * 32), dbl = make_desc(b_lo + j * 32);
-          mma_tf32(tmem_base, dal, dbh, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          mma_tf32(tmem_base, dah, dbl, idesc, 1u);
-          mma_tf32(tmem_base, dah, dbh, idesc, 1u);
+          for (int j = 0; j < BK / 8; ++j) {
+            const uint64_t dah = make_desc(a_hi + j * 32), dal = make_desc(a_lo + j * 32);
+            const uint64_t dbh = make_desc(b_hi + j * 32), dbl = make_desc(b_lo + j * 32);
+            mma_tf32(d_tmem, dal, dbh, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            mma_tf32(d_tmem, dah, dbl, idesc, 1u);
+            mma_tf32(d_tmem, dah, dbh, idesc, 1u);
+          }
+          mma_commit(smem_u32(&ctl->b_empty[sb]));  // frees the B stage when these MMAs have read it
         }
-        mma_commit(smem_u32(&ctl->empty[s]));  // frees the stage when these MMAs have read it
+        if (ok) mma_commit(smem_u32(&ctl->a_empty[sa]));
+        BF_TS(2, kb, 2)
       }
       if (ok) mma_commit(smem_u32(&ctl->accum));
     }
@@ -435,18 +527,19 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     if (tid == 0 && p.status) atomicExch(p.status, 1);
     // give bulk copies that were already issued time to land before the CTA's shared memory is released
     if (tid == 0) {
-      for (int s = 0; s < p.stages; ++s) {
+      for (int s = 0; s < p.b_stages; ++s) {
         const long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&ctl->full[s]), 0) && !mbar_try_wait(smem_u32(&ctl->full[s]), 1) && clock64() - t0 < 200000000LL) {
+        while (!mbar_try_wait(smem_u32(&ctl->b_full[s]), 0) && !mbar_try_wait(smem_u32(&ctl->b_full[s]), 1) && clock64() - t0 < 200000000LL) {
         }
       }
     }
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
+#undef BF_TS
 }
 
 // ---------------------------------------------------------------------------
@@ -498,7 +591,7 @@ void tc_tile_shape(int N, int K, int* BN, int* ntiles, int* nkb) {
 int crown_tc_partial_tiles(int N, int K) {
   int BN, nt, nkb;
   tc_tile_shape(N, K, &BN, &nt, &nkb);
-  return nt;
+  return 2 * ((nt + 1) / 2);  // two partial sums per CTA column (one per epilogue warp group)
 }
 
 size_t tc_packed_bytes(int N, int K) {
@@ -520,20 +613,21 @@ int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned
   return BF_OK;
 }
 
-static int tc_smem_bytes(int BN, int* stages_out) {
-  const int stage = 2 * tc::A_TILE + 2 * BN * 128;
-  int stages = (200 * 1024) / stage;
-  if (stages > 4) stages = 4;
-  if (stages < 2) stages = 2;
-  *stages_out = stages;
-  return stages * stage + 2048;  // control block + alignment slack
+static int tc_smem_bytes(int BN, int* b_stages_out) {
+  const int b_bytes = 2 * BN * 128;
+  int b_stages = (200 * 1024 - tc::A_STAGES * 2 * tc::A_TILE) / b_bytes;
+  if (b_stages > tc::MAX_B_STAGES) b_stages = tc::MAX_B_STAGES;
+  if (b_stages < 2) b_stages = 2;
+  *b_stages_out = b_stages;
+  return tc::A_STAGES * 2 * tc::A_TILE + b_stages * b_bytes + 2048;  // + control block and alignment slack
 }
 
 template <int MODE, int PRO>
 static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char* name) {
-  int stages;
-  const int smem = tc_smem_bytes(p.BN, &stages);
-  p.stages = stages;
+  int b_stages;
+  const int smem = tc_smem_bytes(p.BN, &b_stages);
+  p.b_stages = b_stages;
+  p.ntiles = ntiles;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(tc::crown_tc_kernel<MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -543,8 +637,29 @@ static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char*
     }
     attr_done = true;
   }
-  dim3 grid(ceil_div(p.M, tc::BM), ntiles);
+  dim3 grid(ceil_div(p.M, tc::BM), (ntiles + 1) / 2);
+  static int traced = 0;
+  long long* dtrace = nullptr;
+  if (getenv("BF_TC_TRACE") && p.K >= 512 && traced < 2) {
+    cudaMalloc(&dtrace, 4 * 32 * 4 * sizeof(long long));
+    cudaMemset(dtrace, 0, 4 * 32 * 4 * sizeof(long long));
+    p.trace = dtrace;
+  }
   tc::crown_tc_kernel<MODE, PRO><<<grid, tc::THREADS, smem, stream>>>(p);
+  if (dtrace) {
+    ++traced;
+    cudaDeviceSynchronize();
+    static long long h[4 * 32 * 4];
+    cudaMemcpy(h, dtrace, sizeof(h), cudaMemcpyDeviceToHost);
+    cudaFree(dtrace);
+    long long t0 = h[0];
+    fprintf(stderr, "TRACE %s N=%d K=%d BN=%d b_stages=%d\n", name, p.N, p.K, p.BN, p.b_stages);
+    const char* roles[4] = {"prod", "bcopy", "mma", "epi"};
+    for (int r = 0; r < 4; ++r)
+      for (int kb = 0; kb < (r == 3 ? 1 : p.nkb) && kb < 32; ++kb)
+        fprintf(stderr, "  %s kb=%2d  %8lld %8lld %8lld %8lld\n", roles[r], kb, h[(r * 32 + kb) * 4 + 0] - t0, h[(r * 32 + kb) * 4 + 1] - t0,
+                h[(r * 32 + kb) * 4 + 2] - t0, h[(r * 32 + kb) * 4 + 3] - t0);
+  }
   BF_CHECK_LAUNCH(name);
   return BF_OK;
 }
@@ -561,7 +676,7 @@ int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* d
   const void* kptrs[] = {A, dpos, dneg, epos, eneg, add, kbias};
   for (const void* q : kptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecK = 0;
   p.vecN = (N % 4 == 0);
-  const void* nptrs[] = {mid, rad};
+  const void* nptrs[] = {mid, rad, A_prev};
   for (const void* q : nptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecN = 0;
   p.dpos = dpos; p.dneg = dneg; p.epos = epos; p.eneg = eneg; p.add = add; p.kbias = kbias;
   p.delta = delta; p.accumulate = accumulate;
@@ -586,7 +701,9 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
   p.vecK = (K % 4 == 0);
   const void* kptrs[] = {Hprev, mid, rad};
   for (const void* q : kptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecK = 0;
-  p.vecN = 0;
+  p.vecN = (N % 4 == 0);
+  const void* nptrs[] = {nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout};
+  for (const void* q : nptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecN = 0;
   p.mid_k = mid; p.rad_k = rad;
   p.nbias = nbias; p.Ahat = Ahat; p.e_dpos = dpos; p.e_dneg = dneg; p.e_epos = epos; p.e_eneg = eneg;
   p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad;
