@@ -3,20 +3,23 @@
 // operands for fp32-faithful results:
 //     a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo,   x_hi = tf32(x), x_lo = tf32(x - x_hi)
 //
-// One CTA computes a 128 x BN tile (BN <= 256, multiple of 16) of
+// One CTA computes 128 rows x up to two column sub-tiles of BN columns (BN <= 256, multiple of
+// 16; the two accumulators sit side by side in the 512 tensor-memory columns) of
 //     C[M,N] = f(A)[M,K] * B[K,N]
-// * B (the layer weight, static) is pre-split into hi/lo and pre-packed per
-//   (n-tile, 32-wide k-block) into the exact shared-memory image the MMA reads
-//   (K-major rows of 128 bytes, 128-byte swizzle); one bulk asynchronous copy
-//   (cp.async.bulk, completion on an mbarrier) brings a k-block's hi+lo image in.
-// * A changes per call and needs the ReLU-backward prologue (sign-selected slope
-//   per domain, intercept and bias row sums), so four producer warps load it with
-//   coalesced 128-bit loads, transform, split and write the swizzled hi/lo tiles.
-// * One thread issues the MMAs; tcgen05.commit releases shared-memory stages and
-//   finally signals the epilogue warps, which read the accumulators with
-//   tcgen05.ld, transpose through shared memory and write coalesced rows.
-// Every wait is bounded: on expiry the CTA raises a status word, stops, frees its
-// tensor memory and returns (the host reports the status; nothing traps).
+// * B (the layer weight, static) is pre-split into hi/lo and pre-packed per (column sub-tile,
+//   32-wide k-block) into the exact shared-memory image the MMA reads (K-major rows of 128
+//   bytes, 128-byte swizzle); one bulk asynchronous copy (cp.async.bulk, completion on an
+//   mbarrier) brings a k-block's hi+lo image in.
+// * A changes per call and needs the ReLU-backward prologue (sign-selected slope per domain,
+//   intercept and bias row sums), so sixteen producer warps load it with coalesced 128-bit
+//   loads (one k-block ahead in registers, further ahead as L2 prefetches), transform, split
+//   and write the swizzled hi/lo tiles; one produced k-block feeds both sub-tiles' MMAs.
+// * One thread issues the MMAs; tcgen05.commit releases shared-memory stages and finally
+//   signals the same sixteen warps, which read the accumulators with tcgen05.ld, transpose
+//   32x32 blocks through shared memory and do coalesced 128-bit row accesses (store, fused
+//   concretisation partial sums, or the adjoint step with its per-domain gradient sums).
+// Every wait is bounded: on expiry the CTA raises a status word, stops, frees its tensor
+// memory and returns (the host reports the status; nothing traps).
 #include <stdlib.h>
 
 #include "kernels.cuh"
@@ -30,11 +33,15 @@ constexpr int MAX_BN = 256;
 constexpr int A_TILE = BM * BK * 4;     // bytes of one A tile (hi or lo)
 constexpr int A_STAGES = 2;
 constexpr int MAX_B_STAGES = 4;
-constexpr int PROD_WARPS = 8;
+constexpr int PROD_WARPS = 16;
+constexpr int ROWS_PER_THREAD = BM / (PROD_WARPS * 4);  // 8 threads cover one 128-byte row
+constexpr int COL_PARTS = PROD_WARPS / 4;               // epilogue warps per TMEM lane quarter
 constexpr int PRODUCERS = PROD_WARPS * 32;
 constexpr int COPY_WARP = PROD_WARPS;       // bulk-copy issue
 constexpr int MMA_WARP = PROD_WARPS + 1;    // MMA issue, TMEM alloc / free
 constexpr int THREADS = (PROD_WARPS + 2) * 32;
+constexpr int PREFETCH_KB = 4;              // k-blocks of L2 prefetch distance for the A operand
+constexpr int TBL_MAX = 5;                  // domains per 32 rows served from the epilogue's slope table (S >= 8)
 constexpr int STG_LD = 36;                  // leading dimension of the per-warp epilogue transpose buffer
 constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
@@ -54,13 +61,12 @@ struct Params {
   // backward epilogue
   float* out;                // [M,N] or null
   const float* mid_n; const float* rad_n;   // [D,N] with `partial`
-  float* partial;            // [M, 2*gridDim.y] or null
+  float* partial;            // [M, COL_PARTS*gridDim.y] or null
   float conc_sign;           // -1 lower, +1 upper
   // adjoint epilogue
   const float* nbias; const float* Ahat; const float* e_dpos; const float* e_dneg; const float* e_epos; const float* e_eneg;
   const float* pre_l; const float* pre_u; float* hout; float* grad;
   int* status;               // device word, set non-zero when a wait expired
-  long long* trace;  // debug timeline of CTA (0,0): [role 0..3][kb 0..31][event 0..3]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -180,9 +186,6 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   const int b_bytes = 2 * p.BN * 128;                   // hi + lo image of one k-block of one sub-tile
   const uint32_t tmem_cols = (ncols <= 256) ? 256u : 512u;
   volatile int* abort_flag = &ctl->abort_flag;
-  const bool tr = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-#define BF_TS(role, kb, ev) \
-  if (tr && (kb) < 32) p.trace[((role) * 32 + (kb)) * 4 + (ev)] = clock64();
 
   if (tid == 0) {
     for (int s = 0; s < A_STAGES; ++s) {
@@ -210,91 +213,80 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   if (warp < PROD_WARPS) {
     // ------------------------------------------------------------------ A producers
     const int c = tid & 7;        // 16-byte chunk inside the 128-byte k-block row
-    const int rg = tid >> 3;      // 4-row group of this thread
-    const int row0 = m0 + rg * 4;
+    const int rg = tid >> 3;      // row pair of this thread
+    const int row0 = m0 + rg * ROWS_PER_THREAD;
     const bool vK = p.vecK != 0;
     const bool want_delta = (PRO == PRO_RELU) && p.delta != nullptr && blockIdx.y == 0;
-    const int d_first = (row0 < p.M) ? (row0 / p.S) : 0;
-    const int d_last = (row0 < p.M) ? (min(row0 + 3, p.M - 1) / p.S) : 0;
-    float rowacc[4] = {0.f, 0.f, 0.f, 0.f};
+    int dom[ROWS_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) dom[i] = (row0 + i < p.M) ? ((row0 + i) / p.S) : 0;
+    float rowacc[ROWS_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) rowacc[i] = 0.f;
 
-    float4 a_next[4];
-    float4 s_next[2][5];  // per domain set: dpos, dneg, epos|mid, eneg|rad, add
-    float4 kb_next;
+    // The coefficient rows stream from HBM: they are loaded one k-block ahead into registers and
+    // their lines are pulled into L2 PREFETCH_KB k-blocks ahead.  The per-domain slope vectors are
+    // L2-resident and are loaded when a k-block is processed.
+    float4 a_next[ROWS_PER_THREAD];
     auto load_block = [&](int kb) {
       const int k = kb * BK + c * 4;
-      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
       const bool ok = k < p.K;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         const int m = row0 + i;
-        a_next[i] = (m < p.M && ok) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : z;
-      }
-      kb_next = z;
-      if (PRO == PRO_RELU) {
-        if (p.kbias && ok) kb_next = load4_guard(p.kbias, k, p.K, vK);
-        if (p.dpos) {
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const size_t off = (size_t)(q == 0 ? d_first : d_last) * p.K;
-            s_next[q][0] = ok ? load4_guard(p.dpos + off, k, p.K, vK) : z;
-            s_next[q][1] = ok ? load4_guard(p.dneg + off, k, p.K, vK) : z;
-            s_next[q][2] = (ok && p.epos) ? load4_guard(p.epos + off, k, p.K, vK) : z;
-            s_next[q][3] = (ok && p.eneg) ? load4_guard(p.eneg + off, k, p.K, vK) : z;
-            s_next[q][4] = (ok && p.add) ? load4_guard(p.add + off, k, p.K, vK) : z;
-          }
-        }
-      } else if (PRO == PRO_H0) {
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const size_t off = (size_t)(q == 0 ? d_first : d_last) * p.K;
-          s_next[q][2] = ok ? load4_guard(p.mid_k + off, k, p.K, vK) : z;
-          s_next[q][3] = ok ? load4_guard(p.rad_k + off, k, p.K, vK) : z;
-        }
+        a_next[i] = (m < p.M && ok) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c == 0 && m < p.M && (kb + PREFETCH_KB) * BK < p.K)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.A + (size_t)m * p.K + (size_t)(kb + PREFETCH_KB) * BK));
       }
     };
 
     load_block(0);
     bool alive = true;
     for (int kb = 0; kb < p.nkb; ++kb) {
-      float4 a_cur[4], s_cur[2][5];
-      const float4 kbv = kb_next;
+      float4 a_cur[ROWS_PER_THREAD];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a_cur[i] = a_next[i];
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int j = 0; j < 5; ++j) s_cur[q][j] = s_next[q][j];
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) a_cur[i] = a_next[i];
       if (kb + 1 < p.nkb) load_block(kb + 1);
+
+      const int k = kb * BK + c * 4;
+      const bool ok = k < p.K;
+      const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 kbv = z4;
+      float4 sv[ROWS_PER_THREAD][5];  // dpos, dneg, epos|mid, eneg|rad, add of each row's domain
+      if (PRO == PRO_RELU) {
+        if (want_delta && p.kbias && ok) kbv = load4_guard(p.kbias, k, p.K, vK);
+        if (p.dpos) {
+#pragma unroll
+          for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+            const size_t off = (size_t)dom[i] * p.K;
+            sv[i][0] = ok ? load4_guard(p.dpos + off, k, p.K, vK) : z4;
+            sv[i][1] = ok ? load4_guard(p.dneg + off, k, p.K, vK) : z4;
+            sv[i][2] = (ok && want_delta && p.epos) ? load4_guard(p.epos + off, k, p.K, vK) : z4;
+            sv[i][3] = (ok && want_delta && p.eneg) ? load4_guard(p.eneg + off, k, p.K, vK) : z4;
+            sv[i][4] = (ok && p.add) ? load4_guard(p.add + off, k, p.K, vK) : z4;
+          }
+        }
+      } else if (PRO == PRO_H0) {
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+          const size_t off = (size_t)dom[i] * p.K;
+          sv[i][2] = ok ? load4_guard(p.mid_k + off, k, p.K, vK) : z4;
+          sv[i][3] = ok ? load4_guard(p.rad_k + off, k, p.K, vK) : z4;
+        }
+      }
 
       const int s = kb % A_STAGES;
       const uint32_t phase = (uint32_t)(kb / A_STAGES) & 1u;
-      if (tid == 0) BF_TS(0, kb, 0)
       if (!mbar_wait(smem_u32(&ctl->a_empty[s]), phase ^ 1u, abort_flag)) { alive = false; break; }
-      if (tid == 0) BF_TS(0, kb, 1)
       unsigned char* a_hi = tiles + (size_t)s * 2 * A_TILE;
       unsigned char* a_lo = a_hi + A_TILE;
-      const int k = kb * BK + c * 4;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         float4 a = a_cur[i];
         const int m = row0 + i;
         if (PRO == PRO_RELU) {
           if (p.dpos != nullptr && m < p.M) {
-            const int d = m / p.S;
-            float4 dp, dn, ep, en, ad;
-            if (d == d_first) { dp = s_cur[0][0]; dn = s_cur[0][1]; ep = s_cur[0][2]; en = s_cur[0][3]; ad = s_cur[0][4]; }
-            else if (d == d_last) { dp = s_cur[1][0]; dn = s_cur[1][1]; ep = s_cur[1][2]; en = s_cur[1][3]; ad = s_cur[1][4]; }
-            else {  // more than two domains inside 4 rows (S < 3): direct loads
-              const size_t off = (size_t)d * p.K;
-              const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-              const bool ok = k < p.K;
-              dp = ok ? load4_guard(p.dpos + off, k, p.K, vK) : z;
-              dn = ok ? load4_guard(p.dneg + off, k, p.K, vK) : z;
-              ep = (ok && p.epos) ? load4_guard(p.epos + off, k, p.K, vK) : z;
-              en = (ok && p.eneg) ? load4_guard(p.eneg + off, k, p.K, vK) : z;
-              ad = (ok && p.add) ? load4_guard(p.add + off, k, p.K, vK) : z;
-            }
+            const float4 dp = sv[i][0], dn = sv[i][1], ep = sv[i][2], en = sv[i][3], ad = sv[i][4];
             if (want_delta) {
               float r = rowacc[i];
 #define BF_TC_SEL(cc)                                       \
@@ -318,16 +310,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
             rowacc[i] += a.x * kbv.x + a.y * kbv.y + a.z * kbv.z + a.w * kbv.w;
           }
         } else if (PRO == PRO_H0) {
-          if (m < p.M && k < p.K) {
-            const int d = m / p.S;
-            float4 md, rd;
-            if (d == d_first) { md = s_cur[0][2]; rd = s_cur[0][3]; }
-            else if (d == d_last) { md = s_cur[1][2]; rd = s_cur[1][3]; }
-            else {
-              const size_t off = (size_t)d * p.K;
-              md = load4_guard(p.mid_k + off, k, p.K, vK);
-              rd = load4_guard(p.rad_k + off, k, p.K, vK);
-            }
+          if (m < p.M && ok) {
+            const float4 md = sv[i][2], rd = sv[i][3];
             // lanes of this float4 beyond K stay 0: a, mid and rad were all loaded guarded
             a.x = md.x - sgnf(a.x) * rd.x; a.y = md.y - sgnf(a.y) * rd.y;
             a.z = md.z - sgnf(a.z) * rd.z; a.w = md.w - sgnf(a.w) * rd.w;
@@ -336,20 +320,18 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
         float4 hi, lo;
         hi.x = tf32_rna(a.x); hi.y = tf32_rna(a.y); hi.z = tf32_rna(a.z); hi.w = tf32_rna(a.w);
         lo.x = tf32_rna(a.x - hi.x); lo.y = tf32_rna(a.y - hi.y); lo.z = tf32_rna(a.z - hi.z); lo.w = tf32_rna(a.w - hi.w);
-        const int rl = rg * 4 + i;  // row inside the tile; 8-row swizzle atoms
+        const int rl = rg * ROWS_PER_THREAD + i;  // row inside the tile; 8-row swizzle atoms
         const int off = (rl >> 3) * 1024 + (rl & 7) * 128 + ((c ^ (rl & 7)) << 4);
         *reinterpret_cast<float4*>(a_hi + off) = hi;
         *reinterpret_cast<float4*>(a_lo + off) = lo;
       }
-      if (tid == 0) BF_TS(0, kb, 2)
       fence_proxy_async();
       mbar_arrive(smem_u32(&ctl->a_full[s]));
-      if (tid == 0) BF_TS(0, kb, 3)
     }
 
     if (PRO == PRO_RELU) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         float v = rowacc[i];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
@@ -360,19 +342,22 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     }
 
     // ------------------------------------------------------------------ epilogue (same eight warps)
-    if (tid == 0) BF_TS(3, 0, 0)
     if (alive && mbar_wait(smem_u32(&ctl->accum), 0, abort_flag)) {
-      if (tid == 0) BF_TS(3, 0, 1)
       tc_fence_after();
       const int q = warp & 3;          // TMEM lane quarter = rows q*32 .. q*32+31 of the tile
-      const int half = warp >> 2;      // column chunks of this parity
+      const int part = warp >> 2;      // this warp takes every COL_PARTS-th 32-column chunk
       float* stg = reinterpret_cast<float*>(tiles) + warp * (32 * STG_LD);  // per-warp 32 x 36 transpose buffer
       const int row_base = m0 + q * 32;
       const int my_row = row_base + lane;  // thread-per-row view right after tcgen05.ld
       const int rs = lane >> 3, c4 = lane & 7;  // (row sub-index, 16-byte column chunk) view after the transpose
       const bool vN = p.vecN != 0;
       float conc = 0.f;
-      for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+      // adjoint: domains covered by this warp's 32 rows and their per-chunk table
+      float* tbl = reinterpret_cast<float*>(tiles) + PROD_WARPS * (32 * STG_LD) + warp * (TBL_MAX * 5 * 32);
+      const int d0 = (row_base < p.M) ? row_base / p.S : 0;
+      const int nd = (row_base < p.M) ? (min(row_base + 31, p.M - 1) / p.S - d0 + 1) : 0;
+      const bool tbl_ok = nd <= TBL_MAX;
+      for (int c0 = part * 32; c0 < ncols; c0 += 32 * COL_PARTS) {
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
         const int colbase = ncol0 + c0;
@@ -410,31 +395,75 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
             }
           }
         } else {
+          // All loads of this chunk are issued before any is consumed: the coefficient rows
+          // (one float4 per (row, 4 columns)), and one table row per domain of this warp's 32
+          // rows with the slopes / intercepts / unstable flag of the chunk's 32 columns.
           float4 nb = make_float4(0.f, 0.f, 0.f, 0.f);
           if (p.nbias && col < p.N) nb = load4_guard(p.nbias, col, p.N, vN);
-#pragma unroll 2
+          float4 ah[8];
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = row_base + it * 4 + rs;
+            ah[it] = (row < p.M && col < p.N) ? load4_guard(p.Ahat + (size_t)row * p.N, col, p.N, vN) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          if (tbl_ok) {
+            const int colj = colbase + lane;
+            float t[TBL_MAX][5];
+#pragma unroll
+            for (int dl = 0; dl < TBL_MAX; ++dl) {
+              const bool okd = dl < nd && colj < p.N;
+              const size_t off = (size_t)(d0 + (okd ? dl : 0)) * p.N + (okd ? colj : 0);
+              t[dl][0] = okd ? __ldg(p.e_dpos + off) : 0.f;
+              t[dl][1] = okd ? __ldg(p.e_dneg + off) : 0.f;
+              t[dl][2] = (okd && p.e_epos) ? __ldg(p.e_epos + off) : 0.f;
+              t[dl][3] = (okd && p.e_eneg) ? __ldg(p.e_eneg + off) : 0.f;
+              const float pl = okd ? __ldg(p.pre_l + off) : 0.f;
+              const float pu = okd ? __ldg(p.pre_u + off) : 0.f;
+              t[dl][4] = (pl < 0.f && pu > 0.f) ? 1.f : 0.f;
+            }
+#pragma unroll
+            for (int dl = 0; dl < TBL_MAX; ++dl)
+#pragma unroll
+              for (int a5 = 0; a5 < 5; ++a5) tbl[(dl * 5 + a5) * 32 + lane] = t[dl][a5];
+          }
+          __syncwarp();
+#pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + rs;
             const int row = row_base + r;
             float4 contrib = make_float4(0.f, 0.f, 0.f, 0.f);
             if (row < p.M && col < p.N) {
               const float4 g4 = *reinterpret_cast<const float4*>(&stg[r * STG_LD + c4 * 4]);
-              const size_t off = (size_t)(row / p.S) * p.N;
-              const float4 ah = load4_guard(p.Ahat + (size_t)row * p.N, col, p.N, vN);
-              const float4 dp = load4_guard(p.e_dpos + off, col, p.N, vN);
-              const float4 dn = load4_guard(p.e_dneg + off, col, p.N, vN);
-              float4 ep = make_float4(0.f, 0.f, 0.f, 0.f), en = ep;
-              if (p.e_epos) ep = load4_guard(p.e_epos + off, col, p.N, vN);
-              if (p.e_eneg) en = load4_guard(p.e_eneg + off, col, p.N, vN);
-              const float4 pl = load4_guard(p.pre_l + off, col, p.N, vN);
-              const float4 pu = load4_guard(p.pre_u + off, col, p.N, vN);
+              const int d = row / p.S;
+              float4 dp, dn, ep, en, am;
+              if (tbl_ok) {
+                const float* tb = tbl + (size_t)(d - d0) * 5 * 32 + c4 * 4;
+                dp = *reinterpret_cast<const float4*>(tb);
+                dn = *reinterpret_cast<const float4*>(tb + 32);
+                ep = *reinterpret_cast<const float4*>(tb + 64);
+                en = *reinterpret_cast<const float4*>(tb + 96);
+                am = *reinterpret_cast<const float4*>(tb + 128);
+              } else {  // more than TBL_MAX domains inside 32 rows (small S): direct loads
+                const size_t off = (size_t)d * p.N;
+                dp = load4_guard(p.e_dpos + off, col, p.N, vN);
+                dn = load4_guard(p.e_dneg + off, col, p.N, vN);
+                ep = make_float4(0.f, 0.f, 0.f, 0.f);
+                en = ep;
+                if (p.e_epos) ep = load4_guard(p.e_epos + off, col, p.N, vN);
+                if (p.e_eneg) en = load4_guard(p.e_eneg + off, col, p.N, vN);
+                const float4 pl = load4_guard(p.pre_l + off, col, p.N, vN);
+                const float4 pu = load4_guard(p.pre_u + off, col, p.N, vN);
+                am.x = (pl.x < 0.f && pu.x > 0.f) ? 1.f : 0.f; am.y = (pl.y < 0.f && pu.y > 0.f) ? 1.f : 0.f;
+                am.z = (pl.z < 0.f && pu.z > 0.f) ? 1.f : 0.f; am.w = (pl.w < 0.f && pu.w > 0.f) ? 1.f : 0.f;
+              }
+              const float4 a4 = ah[it];
               float4 h;
-#define BF_TC_ADJ(cc)                                                         \
-  {                                                                           \
-    const float gg = g4.cc + nb.cc;                                           \
-    const bool sel = ah.cc >= 0.f;                                            \
-    h.cc = (sel ? dp.cc : dn.cc) * gg + (sel ? ep.cc : en.cc);                \
-    contrib.cc = (sel && pl.cc < 0.f && pu.cc > 0.f) ? ah.cc * gg : 0.f;      \
+#define BF_TC_ADJ(cc)                                                 \
+  {                                                                   \
+    const float gg = g4.cc + nb.cc;                                   \
+    const bool sel = a4.cc >= 0.f;                                    \
+    h.cc = (sel ? dp.cc : dn.cc) * gg + (sel ? ep.cc : en.cc);        \
+    contrib.cc = (sel && am.cc != 0.f) ? a4.cc * gg : 0.f;            \
   }
               BF_TC_ADJ(x) BF_TC_ADJ(y) BF_TC_ADJ(z) BF_TC_ADJ(w)
 #undef BF_TC_ADJ
@@ -445,26 +474,37 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
           __syncwarp();
           // per-domain column sums over this warp's 32 rows; at most two warps/tiles touch one (domain, column)
           const int colj = colbase + lane;
-          float run = 0.f;
-          int run_d = -1;
-          for (int r = 0; r < 32; ++r) {
-            const int row = row_base + r;
-            if (row >= p.M) break;
-            const int d = row / p.S;
-            if (d != run_d) {
-              if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
-              run = 0.f;
-              run_d = d;
+          const int nrows = min(32, p.M - row_base);
+          if (tbl_ok) {
+#pragma unroll
+            for (int dl = 0; dl < TBL_MAX; ++dl) {
+              if (dl < nd) {
+                const int r_lo = max((d0 + dl) * p.S - row_base, 0);
+                const int r_hi = min((d0 + dl + 1) * p.S - row_base, nrows);
+                float run = 0.f;
+                for (int r = r_lo; r < r_hi; ++r) run += stg[r * STG_LD + lane];
+                if (colj < p.N) atomicAdd(&p.grad[(size_t)(d0 + dl) * p.N + colj], run);
+              }
             }
-            run += stg[r * STG_LD + lane];
+          } else {
+            float run = 0.f;
+            int run_d = -1;
+            for (int r = 0; r < nrows; ++r) {
+              const int d = (row_base + r) / p.S;
+              if (d != run_d) {
+                if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
+                run = 0.f;
+                run_d = d;
+              }
+              run += stg[r * STG_LD + lane];
+            }
+            if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
           }
-          if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
         }
       }
       if (MODE == MODE_BWD && p.partial != nullptr && my_row < p.M)
-        p.partial[(size_t)my_row * (2 * gridDim.y) + 2 * blockIdx.y + half] = conc;
+        p.partial[(size_t)my_row * (COL_PARTS * gridDim.y) + COL_PARTS * blockIdx.y + part] = conc;
       tc_fence_before();
-      if (tid == 0) BF_TS(3, 0, 2)
     }
   } else if (warp == COPY_WARP) {
     // ------------------------------------------------------------------ bulk-copy issue for B
@@ -474,9 +514,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
         for (int h = 0; h < nh; ++h, ++it) {
           const int s = it % p.b_stages;
           const uint32_t phase = (uint32_t)(it / p.b_stages) & 1u;
-          BF_TS(1, kb, 2 * h)
           if (!mbar_wait(smem_u32(&ctl->b_empty[s]), phase ^ 1u, abort_flag)) { kb = p.nkb; break; }
-          BF_TS(1, kb, 2 * h + 1)
           const uint32_t bar = smem_u32(&ctl->b_full[s]);
           const unsigned char* src = p.Bpk + ((size_t)(nt0 + h) * p.nkb + kb) * b_bytes;
           mbar_arrive_expect_tx(bar, (uint32_t)b_bytes);
@@ -492,9 +530,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
       int it = 0;
       for (int kb = 0; kb < p.nkb && ok; ++kb) {
         const int sa = kb % A_STAGES;
-        BF_TS(2, kb, 0)
         if (!mbar_wait(smem_u32(&ctl->a_full[sa]), (uint32_t)(kb / A_STAGES) & 1u, abort_flag)) { ok = false; break; }
-        BF_TS(2, kb, 1)
         const uint32_t a_hi = smem_u32(tiles + (size_t)sa * 2 * A_TILE);
         const uint32_t a_lo = a_hi + A_TILE;
         for (int h = 0; h < nh; ++h, ++it) {
@@ -515,7 +551,6 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
           mma_commit(smem_u32(&ctl->b_empty[sb]));  // frees the B stage when these MMAs have read it
         }
         if (ok) mma_commit(smem_u32(&ctl->a_empty[sa]));
-        BF_TS(2, kb, 2)
       }
       if (ok) mma_commit(smem_u32(&ctl->accum));
     }
@@ -539,7 +574,6 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
-#undef BF_TS
 }
 
 // ---------------------------------------------------------------------------
@@ -591,7 +625,7 @@ void tc_tile_shape(int N, int K, int* BN, int* ntiles, int* nkb) {
 int crown_tc_partial_tiles(int N, int K) {
   int BN, nt, nkb;
   tc_tile_shape(N, K, &BN, &nt, &nkb);
-  return 2 * ((nt + 1) / 2);  // two partial sums per CTA column (one per epilogue warp group)
+  return tc::COL_PARTS * ((nt + 1) / 2);  // one partial sum per CTA column and epilogue warp group
 }
 
 size_t tc_packed_bytes(int N, int K) {
@@ -638,28 +672,7 @@ static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char*
     attr_done = true;
   }
   dim3 grid(ceil_div(p.M, tc::BM), (ntiles + 1) / 2);
-  static int traced = 0;
-  long long* dtrace = nullptr;
-  if (getenv("BF_TC_TRACE") && p.K >= 512 && traced < 2) {
-    cudaMalloc(&dtrace, 4 * 32 * 4 * sizeof(long long));
-    cudaMemset(dtrace, 0, 4 * 32 * 4 * sizeof(long long));
-    p.trace = dtrace;
-  }
   tc::crown_tc_kernel<MODE, PRO><<<grid, tc::THREADS, smem, stream>>>(p);
-  if (dtrace) {
-    ++traced;
-    cudaDeviceSynchronize();
-    static long long h[4 * 32 * 4];
-    cudaMemcpy(h, dtrace, sizeof(h), cudaMemcpyDeviceToHost);
-    cudaFree(dtrace);
-    long long t0 = h[0];
-    fprintf(stderr, "TRACE %s N=%d K=%d BN=%d b_stages=%d\n", name, p.N, p.K, p.BN, p.b_stages);
-    const char* roles[4] = {"prod", "bcopy", "mma", "epi"};
-    for (int r = 0; r < 4; ++r)
-      for (int kb = 0; kb < (r == 3 ? 1 : p.nkb) && kb < 32; ++kb)
-        fprintf(stderr, "  %s kb=%2d  %8lld %8lld %8lld %8lld\n", roles[r], kb, h[(r * 32 + kb) * 4 + 0] - t0, h[(r * 32 + kb) * 4 + 1] - t0,
-                h[(r * 32 + kb) * 4 + 2] - t0, h[(r * 32 + kb) * 4 + 3] - t0);
-  }
   BF_CHECK_LAUNCH(name);
   return BF_OK;
 }
