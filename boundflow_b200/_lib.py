@@ -46,6 +46,8 @@ SIGNATURES = {
     "bf_crown_relu_linear_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "bf_crown_relu_conv2d_bwd_scratch_bytes": (_sz, [_i] * 5),
     "bf_crown_relu_conv2d_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _sz] + [_i] * 14 + [_p]),
+    "bf_crown_relu_conv2d_bwd_noalloc_max_bytes": (_sz, []),
+    "bf_crown_relu_conv2d_bwd_noalloc": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i] + [_i] * 14 + [_p]),
     "bf_concretize": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "bf_verdict": (_i, [_p, _f, _f, _p, _p, _i, _i, _p]),
     "bf_chain_create": (_i, [C.POINTER(LayerDesc), _i, C.POINTER(_p)]),

@@ -300,3 +300,53 @@ extern "C" int bf_crown_relu_conv2d_bwd(const float* A, int side, const float* a
   return bf::launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, W, bias, A_prev, delta, accumulate, B * S, S, L, scratch,
                                      bf::as_stream(stream));
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the fused ReLU + Conv2d backward.
+//
+// Some callers cannot obtain device memory at the moment they need this kernel:
+// a verification service whose device pool is sized at start-up and then
+// frozen, a plugin loaded into a process that already owns all device memory,
+// or a host runtime that forbids cudaMalloc / cudaFree on its request path
+// because those calls synchronise the whole device.
+// For them the scratch that holds the ReLU-scaled coefficients lives in a
+// fixed-size array inside the library image instead of a caller buffer.
+// ---------------------------------------------------------------------------
+#define BF_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BF_NOALLOC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle; the device address is resolved
+// once per device (with that device current) and cached here.
+static void* g_noalloc_scratch_addr[64] = {nullptr};
+
+extern "C" size_t bf_crown_relu_conv2d_bwd_noalloc_max_bytes(void) { return (size_t)BF_NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int bf_crown_relu_conv2d_bwd_noalloc(const float* A, int side, const float* alpha_u, const float* alpha_l,
+                                                const float* beta_u, const float* beta_l, const float* W, const float* bias,
+                                                float* A_prev, float* delta, int accumulate, int B, int S, int Ci, int Hi,
+                                                int Wi, int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw,
+                                                bf_stream_t stream) {
+  BF_REQUIRE(B > 0 && S > 0 && Co > 0 && Ho > 0 && Wo > 0, BF_E_INVALID, "bf_crown_relu_conv2d_bwd_noalloc: bad geometry");
+  const size_t need = bf_crown_relu_conv2d_bwd_scratch_bytes(B, S, Co, Ho, Wo);
+  BF_REQUIRE(need <= (size_t)BF_NOALLOC_SCRATCH_BYTES, BF_E_WORKSPACE,
+             "bf_crown_relu_conv2d_bwd_noalloc: B*S*Co*Ho*Wo*4 = %zu bytes exceeds the built-in scratch of %u bytes; "
+             "use bf_crown_relu_conv2d_bwd with a caller buffer",
+             need, BF_NOALLOC_SCRATCH_BYTES);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    bf::set_error("bf_crown_relu_conv2d_bwd_noalloc: cannot identify the current device");
+    return BF_E_CUDA;
+  }
+  void* scratch = g_noalloc_scratch_addr[dev];
+  if (scratch == nullptr) {
+    // first call on this device: resolve the symbol's device address (do this before any stream capture)
+    cudaError_t e = cudaGetSymbolAddress(&scratch, g_noalloc_scratch);
+    if (e != cudaSuccess || scratch == nullptr) {
+      bf::set_error("bf_crown_relu_conv2d_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return BF_E_CUDA;
+    }
+    g_noalloc_scratch_addr[dev] = scratch;
+  }
+  return bf_crown_relu_conv2d_bwd(A, side, alpha_u, alpha_l, beta_u, beta_l, W, bias, A_prev, delta, accumulate, scratch,
+                                  (size_t)BF_NOALLOC_SCRATCH_BYTES, B, S, Ci, Hi, Wi, Co, Ho, Wo, kh, kw, sh, sw, ph, pw, stream);
+}

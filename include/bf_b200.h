@@ -149,6 +149,28 @@ int bf_crown_relu_conv2d_bwd(const float* A, int side,
                              int B, int S, int Ci, int Hi, int Wi, int Co, int Ho, int Wo,
                              int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
 
+/* Allocation-free variant of bf_crown_relu_conv2d_bwd.  It has no counterpart in the
+ * reference.  It exists for callers that cannot hand over (or obtain) device scratch when
+ * they call: services whose device pool is sized at start-up and then frozen, plugins loaded
+ * into a process that already owns all device memory, runtimes that ban cudaMalloc / cudaFree
+ * on the request path because those calls synchronise the device.
+ * The ReLU-scaled coefficients are staged in an array that is part of the library image
+ * (bf_crown_relu_conv2d_bwd_noalloc_max_bytes() = 16 MiB, held on every GPU that loads the
+ * library until the process exits); requests with B*S*Co*Ho*Wo*4 bytes beyond that return
+ * BF_E_WORKSPACE.  The first call on each device looks up the array's device address; make
+ * that call with the device current and before any stream capture.  No call allocates or
+ * frees memory.  The array is shared by all calls and keeps the last call's contents (every
+ * element a call reads was written by that same call, so nothing needs clearing); two calls
+ * whose kernels may overlap on the GPU (different streams) race on it. */
+size_t bf_crown_relu_conv2d_bwd_noalloc_max_bytes(void);
+int bf_crown_relu_conv2d_bwd_noalloc(const float* A, int side,
+                                     const float* alpha_u, const float* alpha_l,
+                                     const float* beta_u, const float* beta_l,
+                                     const float* W, const float* bias,
+                                     float* A_prev, float* delta, int accumulate,
+                                     int B, int S, int Ci, int Hi, int Wi, int Co, int Ho, int Wo,
+                                     int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
+
 /* Concretisation of an affine form over a box (or L-inf ball: rad == eps).
  *   replaces BoxPerturbation.concretize_affine perturbation.py:327-359 and
  *            LpBallPerturbation.concretize_affine (p = inf) perturbation.py:175-222.
