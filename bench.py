@@ -33,6 +33,9 @@ import torch  # noqa: E402
 DOMAINS_PER_GPU = 8192
 ALPHA_STEPS = 10
 LR = 0.1
+# DRAM bytes of one backward-contraction launch of a 512x512 layer at 8192 domains (M = 73728 rows):
+# ncu capture at 4096 domains (profiles/crown_tc_kernel_bwd_c4_4096domains.md) scaled x2 by the row count.
+TRAFFIC_BYTES_PER_LAUNCH = 2 * (198.6e6 + 45.6e6)
 METRIC = "bab_domains_bounded_per_s"
 UNIT = "domains/s"
 
@@ -304,15 +307,16 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {
-            "bound": "tensor", "kernel": "crown_bwd_linear_kernel (ReLU-backward + Linear-backward contraction, FP32 FFMA)",
+            "bound": "tensor", "kernel": "crown_tc_kernel<bwd> (ReLU-backward + Linear-backward contraction, tcgen05 3xTF32; the 10-wide top layer runs as FFMA tiles)",
             "achieved": achieved, "peak": fp32_equiv_peak, "unit": "TFLOP/s", "frac": (achieved / fp32_equiv_peak) if achieved else None,
-            "traffic": None,
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH * (D / 8192.0),
+            "traffic_source": "ncu dram__bytes_read+write of one 512x512-layer launch at 4096 domains, scaled by rows (profiles/)",
             "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 6 = fp32-equivalent 3xTF32 tensor peak",
             "launches": n_l.value, "avg_launch_ms": (t_l.value / n_l.value) if n_l.value else None,
             "share_of_step": t_l.value / ms_res if ms_res else None,
         },
         "roofline_adjoint": {
-            "kernel": "crown_adjoint_linear_kernel", "achieved": achieved_adj, "unit": "TFLOP/s",
+            "kernel": "crown_tc_kernel<adjoint> (gradient sweep, tcgen05 3xTF32)", "achieved": achieved_adj, "unit": "TFLOP/s",
             "frac": (achieved_adj / fp32_equiv_peak) if achieved_adj else None, "launches": n_a.value,
             "share_of_step": t_a.value / ms_res if ms_res else None,
         },

@@ -247,6 +247,14 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) a_cur[i] = a_next[i];
       if (kb + 1 < p.nkb) load_block(kb + 1);
+      if (MODE == MODE_ADJ && kb == 1) {
+        // the epilogue will read this tile's saved coefficients: start pulling their lines into L2 now
+        const int lpr = (ncols + 31) >> 5;  // 128-byte lines per row
+        for (int idx = tid; idx < BM * lpr; idx += PRODUCERS) {
+          const int r = idx / lpr, col = ncol0 + (idx - r * lpr) * 32;
+          if (m0 + r < p.M && col < p.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Ahat + (size_t)(m0 + r) * p.N + col));
+        }
+      }
 
       const int k = kb * BK + c * 4;
       const bool ok = k < p.K;

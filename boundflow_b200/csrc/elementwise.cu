@@ -27,9 +27,8 @@ __global__ void relu_relax_kernel(const float* __restrict__ l, const float* __re
     float au, bu, al;
     relax_one(lo, up, au, bu, al);
     if (alpha != nullptr && lo < 0.f && up > 0.f) {
-      const long long b = i / n;
-      const int j = (int)(i - b * n);
-      const float a = alpha[b * (long long)alpha_stride + j];
+      // alpha_stride is n (per-domain rows, same flat index) or 0 (one shared row)
+      const float a = (alpha_stride != 0) ? alpha[i] : alpha[i % n];
       al = fminf(fmaxf(a, 0.f), 1.f);
     }
     alpha_u[i] = au;
@@ -135,39 +134,74 @@ int launch_select_best(const float* cur, float* best_lower, float* best_metric, 
 }
 
 // ---- Adam + projection + best-alpha snapshot + next lower slope ---------------
-__global__ void adam_step_kernel(float* __restrict__ alpha, float* __restrict__ m, float* __restrict__ v,
-                                 float* __restrict__ grad, const int* __restrict__ improve, float* __restrict__ best_alpha,
-                                 const float* __restrict__ pre_l, const float* __restrict__ pre_u,
-                                 float* __restrict__ slope_l, AdamScalars sc, int do_update, int n, long long total) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long b = i / n;
+// One element: torch.optim.Adam (no amsgrad / weight decay): lerp for the first moment,
+// mul+addcmul for the second, sqrt(v)/sqrt(bc2)+eps as denominator, then clamp to [0,1].
+__device__ __forceinline__ void adam_one(float& a, float& mi, float& vi, float g, float lo, float up, float& sl,
+                                         const AdamScalars& sc) {
+  mi = mi + sc.one_minus_beta1 * (g - mi);
+  vi = vi * sc.beta2 + sc.one_minus_beta2 * g * g;
+  const float denom = sqrtf(vi) / sc.bc2_sqrt + sc.eps;
+  a = a - sc.lr_step * (mi / denom);
+  a = fminf(fmaxf(a, 0.f), 1.f);
+  sl = (up <= 0.f) ? 0.f : ((lo >= 0.f) ? 1.f : a);
+}
+
+// grid (B, column chunks): one domain row per blockIdx.x, VEC consecutive columns per thread.
+template <int VEC>
+__global__ void __launch_bounds__(128) adam_step_kernel(float* __restrict__ alpha, float* __restrict__ m, float* __restrict__ v,
+                                                        float* __restrict__ grad, const int* __restrict__ improve,
+                                                        float* __restrict__ best_alpha, const float* __restrict__ pre_l,
+                                                        const float* __restrict__ pre_u, float* __restrict__ slope_l,
+                                                        AdamScalars sc, int do_update, int n) {
+  const int b = blockIdx.x;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (j >= n) return;
+  const size_t i = (size_t)b * n + j;
+  const bool imp = improve[b] != 0;
+  if (VEC == 4) {
+    float4 a = *reinterpret_cast<const float4*>(alpha + i);
+    if (imp) *reinterpret_cast<float4*>(best_alpha + i) = a;
+    if (!do_update) return;
+    float4 g = *reinterpret_cast<const float4*>(grad + i);
+    float4 mi = *reinterpret_cast<const float4*>(m + i), vi = *reinterpret_cast<const float4*>(v + i);
+    const float4 lo = *reinterpret_cast<const float4*>(pre_l + i), up = *reinterpret_cast<const float4*>(pre_u + i);
+    float4 sl;
+    adam_one(a.x, mi.x, vi.x, g.x * sc.grad_scale, lo.x, up.x, sl.x, sc);
+    adam_one(a.y, mi.y, vi.y, g.y * sc.grad_scale, lo.y, up.y, sl.y, sc);
+    adam_one(a.z, mi.z, vi.z, g.z * sc.grad_scale, lo.z, up.z, sl.z, sc);
+    adam_one(a.w, mi.w, vi.w, g.w * sc.grad_scale, lo.w, up.w, sl.w, sc);
+    *reinterpret_cast<float4*>(grad + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(m + i) = mi;
+    *reinterpret_cast<float4*>(v + i) = vi;
+    *reinterpret_cast<float4*>(alpha + i) = a;
+    *reinterpret_cast<float4*>(slope_l + i) = sl;
+  } else {
     float a = alpha[i];
-    if (improve[b]) best_alpha[i] = a;
-    if (!do_update) continue;
-    const float g = grad[i] * sc.grad_scale;
+    if (imp) best_alpha[i] = a;
+    if (!do_update) return;
+    float mi = m[i], vi = v[i], sl;
+    adam_one(a, mi, vi, grad[i] * sc.grad_scale, pre_l[i], pre_u[i], sl, sc);
     grad[i] = 0.f;
-    // torch.optim.Adam (no amsgrad / weight decay): lerp for the first moment,
-    // mul+addcmul for the second, sqrt(v)/sqrt(bc2)+eps as denominator.
-    float mi = m[i], vi = v[i];
-    mi = mi + sc.one_minus_beta1 * (g - mi);
-    vi = vi * sc.beta2 + sc.one_minus_beta2 * g * g;
-    const float denom = sqrtf(vi) / sc.bc2_sqrt + sc.eps;
-    a = a - sc.lr_step * (mi / denom);
-    a = fminf(fmaxf(a, 0.f), 1.f);
     m[i] = mi;
     v[i] = vi;
     alpha[i] = a;
-    const float lo = pre_l[i], up = pre_u[i];
-    slope_l[i] = (up <= 0.f) ? 0.f : ((lo >= 0.f) ? 1.f : a);
+    slope_l[i] = sl;
   }
 }
 
 int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
                      const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
                      cudaStream_t stream) {
-  const long long total = (long long)B * n;
-  adam_step_kernel<<<ew_grid(total, 256), 256, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l,
-                                                            sc, do_update, n, total);
+  bool vec = (n % 4 == 0);
+  const void* ptrs[] = {alpha, m, v, grad, best_alpha, pre_l, pre_u, slope_l};
+  for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = false;
+  if (vec) {
+    dim3 grid(B, ceil_div(n / 4, 128));
+    adam_step_kernel<4><<<grid, 128, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l, sc, do_update, n);
+  } else {
+    dim3 grid(B, ceil_div(n, 128));
+    adam_step_kernel<1><<<grid, 128, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l, sc, do_update, n);
+  }
   BF_CHECK_LAUNCH("adam_step_kernel");
   return BF_OK;
 }
