@@ -35,7 +35,7 @@ ALPHA_STEPS = 10
 LR = 0.1
 # DRAM bytes of one backward-contraction launch of a 512x512 layer at 8192 domains (M = 73728 rows):
 # ncu capture at 4096 domains (profiles/crown_tc_kernel_bwd_c4_4096domains.md) scaled x2 by the row count.
-TRAFFIC_BYTES_PER_LAUNCH = 2 * (198.6e6 + 45.6e6)
+TRAFFIC_BYTES_PER_LAUNCH = 2 * (104.8e6 + 31.7e6)
 METRIC = "bab_domains_bounded_per_s"
 UNIT = "domains/s"
 
