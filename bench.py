@@ -169,6 +169,64 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def crown_bounds_secondary(world: int, rank: int, dev):
+    """Second half of the metric: CROWN bounds/s (one bound = one (input, spec) lower bound) on the
+    input-sharded configurations, whole job over all ranks, device-timed, max over ranks.
+      c1: IBP + CROWN (both sides), MLP 784-100-100-10, 64 inputs
+      c2: CROWN with CROWN intermediate bounds, MNIST-shaped CNN, 256 inputs
+      c3: alpha-CROWN, 20 Adam steps, MLP 784-256x5-10, 128 inputs"""
+    import torch.distributed as dist
+
+    from boundflow_b200 import _lib
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, ibp_trace, run_alpha_beta_crown_mlp, run_crown_ibp_mlp, run_crown_intermediate_mlp
+    from boundflow_b200.dist import gather_domain_results, shard_range
+    from boundflow_b200.ir import InputSpec
+
+    lib = _lib.load()
+    out = {}
+    for name, reps in (("c1", 20), ("c2", 2), ("c3", 5)):
+        wl = W.make_workload(name)
+        n = wl.x.shape[0]
+        a, b = shard_range(n, rank, world)
+        lo, up, C = wl.lo[a:b].to(dev), wl.up[a:b].to(dev), wl.C[a:b].to(dev)
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+
+        def run():
+            if name == "c1":
+                res = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=C).lower
+            elif name == "c2":
+                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=512)[0].lower
+            else:
+                tr = ibp_trace(wl.module, spec)
+                a0 = adaptive_alpha_from_trace(tr)
+                res = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=C, steps=20, lr=0.1, per_batch_params=True,
+                                               warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))))[0].lower
+            verdict = torch.empty(res.shape[0], dtype=torch.int8, device=dev)
+            _lib.check(lib.bf_verdict(res.data_ptr(), 0.0, 1e-6, verdict.data_ptr(), None, res.shape[0], res.shape[1],
+                                      torch.cuda.current_stream().cuda_stream))
+            return gather_domain_results(res, verdict, n) if world > 1 else (res, verdict)
+
+        for _ in range(2):
+            run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out[name] = {"bounds_per_s": n * 9 / (ms * 1e-3), "ms": ms, "inputs": n}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -271,6 +329,8 @@ def main():
         step_e2e()
     ms_e2e, out_e2e = timed(step_e2e, args.steps)
 
+    secondary = crown_bounds_secondary(world, rank, dev)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -320,6 +380,7 @@ def main():
             "frac": (achieved_adj / fp32_equiv_peak) if achieved_adj else None, "launches": n_a.value,
             "share_of_step": t_a.value / ms_res if ms_res else None,
         },
+        "crown_bounds_per_s": secondary,
         "result_check": {"domains": n_total, "proven": proven, "infeasible_local": infeasible,
                          "mean_lower": float(lower[torch.isfinite(lower).all(dim=1)].mean().item())},
     }
