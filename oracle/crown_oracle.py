@@ -435,10 +435,15 @@ def alpha_crown(
     splits=None,
     spec_reduce: str = "mean",
     trace: Optional[ForwardTrace] = None,
+    optimize_beta: bool = False,
+    return_beta: bool = False,
 ):
-    """Per-domain alpha optimisation, `run_alpha_beta_crown_mlp` with
-    `per_batch_params=True, objective="lower"` and beta fixed at its zero
-    initial value restated (alpha_beta_crown.py:716-923).
+    """Per-domain alpha (and optionally beta) optimisation, `run_alpha_beta_crown_mlp`
+    with `per_batch_params=True, objective="lower"` restated (alpha_beta_crown.py:716-923).
+    With `optimize_beta` every ReLU also gets a per-domain beta >= 0 (start 0) whose
+    split term -beta*s*[s != 0] is added to the lower coefficients
+    (`_beta_to_relu_pre_add_coeff`, alpha_beta_crown.py:615-640) and which the same Adam
+    instance updates; without it beta stays at zero, i.e. the alpha-only loop.
 
     steps+1 bound evaluations (756); metric_b = mean (or sum) over specs of the
     lower bound (787-805); per-domain best with strict improvement, step 0
@@ -458,23 +463,37 @@ def alpha_crown(
         else:
             a = torch.full((B, n), float(alpha_init), dtype=dtype)
         alphas.append(a.requires_grad_(True))
-    opt = torch.optim.Adam(alphas, lr=float(lr))
+    betas: List[torch.Tensor] = []
+    split_f: List[Optional[torch.Tensor]] = []
+    if optimize_beta:
+        for r, (l, _u) in enumerate(trace.pre):
+            n = l.reshape(B, -1).shape[1]
+            betas.append(torch.zeros(B, n, dtype=dtype, requires_grad=True))
+            sp = splits[r] if (splits is not None and splits[r] is not None) else None
+            split_f.append(None if sp is None else sp.reshape(-1, n).expand(B, n).to(dtype))
+    opt = torch.optim.Adam(alphas + betas, lr=float(lr))
     best_metric = None
     best_lower = best_upper = None
     best_alpha: List[torch.Tensor] = []
+    best_beta: List[torch.Tensor] = []
     for step in range(int(steps) + 1):
-        lower, upper = crown_backward(layers, inp, trace, C, alpha=alphas)
+        add_l = None
+        if optimize_beta:
+            add_l = [None if sf is None else -bt * sf * (sf != 0).to(dtype) for bt, sf in zip(betas, split_f)]
+        lower, upper = crown_backward(layers, inp, trace, C, alpha=alphas, add_l=add_l)
         metric_b = lower.mean(dim=1) if spec_reduce == "mean" else lower.sum(dim=1)
         if best_metric is None:
             best_metric = metric_b.detach().clone()
             best_lower, best_upper = lower.detach().clone(), upper.detach().clone()
             best_alpha = [a.detach().clone() for a in alphas]
+            best_beta = [b.detach().clone() for b in betas]
         else:
             improve = metric_b.detach() > best_metric
             best_metric = torch.where(improve, metric_b.detach(), best_metric)
             best_lower = torch.where(improve.unsqueeze(1), lower.detach(), best_lower)
             best_upper = torch.where(improve.unsqueeze(1), upper.detach(), best_upper)
             best_alpha = [torch.where(improve.unsqueeze(1), a.detach(), p) for a, p in zip(alphas, best_alpha)]
+            best_beta = [torch.where(improve.unsqueeze(1), b.detach(), p) for b, p in zip(betas, best_beta)]
         if step == int(steps):
             break
         loss = -metric_b.sum()
@@ -486,7 +505,32 @@ def alpha_crown(
         with torch.no_grad():
             for a in alphas:
                 a.clamp_(0.0, 1.0)
+            for b in betas:
+                b.clamp_(0.0)
+    if return_beta:
+        return best_lower, best_upper, best_alpha, best_beta, trace
     return best_lower, best_upper, best_alpha, trace
+
+
+def branch_choices(trace: ForwardTrace) -> List[Optional[Tuple[int, int]]]:
+    """Widest-unstable-gap branching hint, `_branch_choices_from_relu_pre`
+    (alpha_beta_crown.py:145-182): per domain the (ReLU index, neuron index) with the largest
+    u - l among neurons with l < 0 < u; earlier ReLUs win ties (strict improvement), the first
+    index wins inside a ReLU (argmax); None when no neuron is unstable."""
+    B = trace.pre[0][0].shape[0]
+    best_gap = torch.full((B,), float("-inf"), dtype=trace.pre[0][0].dtype)
+    best: List[Optional[Tuple[int, int]]] = [None] * B
+    for r, (l, u) in enumerate(trace.pre):
+        lf, uf = l.reshape(B, -1), u.reshape(B, -1)
+        amb = (lf < 0) & (uf > 0)
+        gap = torch.where(amb, (uf - lf).clamp_min(0.0), torch.full_like(lf, float("-inf")))
+        row_best = gap.max(dim=1).values
+        row_idx = gap.argmax(dim=1)
+        improve = row_best > best_gap
+        best_gap = torch.where(improve, row_best, best_gap)
+        for i in torch.nonzero(improve).flatten().tolist():
+            best[i] = (r, int(row_idx[i]))
+    return best
 
 
 def alpha_gradient(layers: Layers, inp: InputSet, trace: ForwardTrace, C, alphas: Sequence[torch.Tensor], spec_reduce="mean"):

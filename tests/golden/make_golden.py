@@ -219,6 +219,20 @@ def main() -> None:
     a0 = adaptive_alpha(relu_pre)
     best_l, best_u, best_a = ref_alpha_only_loop(m, spec, C, relu_pre, interval_env, a0, steps=10, lr=0.1, reduce="mean")
     step0 = run_crown_ibp_mlp_from_forward_trace(m, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=C, relu_alpha=a0)
+    from boundflow.runtime.alpha_beta_crown import _branch_choices_from_relu_pre
+
+    ab_bounds, ab_alpha, ab_beta, ab_stats = run_alpha_beta_crown_mlp(
+        m, spec, linear_spec_C=C, relu_split_state=split_state, steps=10, lr=0.1,
+        warm_start_alpha=AlphaState(alpha_by_relu_input=a0), per_batch_params=True, objective="lower", spec_reduce="mean",
+    )
+    choices = _branch_choices_from_relu_pre(relu_pre)
+    choice_arr = np.array([[-1, -1] if c is None else [wl.relu_names.index(c[0]), c[1]] for c in choices], dtype=np.int64)
+    save(
+        "c4_split_alpha_beta.npz",
+        best_lower=ab_bounds.lower, best_upper=ab_bounds.upper, branch_choices=choice_arr,
+        **{f"alpha_{k}": v for k, v in ab_alpha.alpha_by_relu_input.items()},
+        **{f"beta_{k}": v for k, v in ab_beta.beta_by_relu_input.items()},
+    )
     save(
         "c4_split_alpha.npz",
         input_checksum=checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()]),

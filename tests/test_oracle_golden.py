@@ -170,3 +170,30 @@ def test_fused_region_reference_vectors(golden):
     assert_close(P_l, g["lin_A_prev_l"], "A_prev_l")
     assert_close(d_u, g["lin_delta_u"], "delta_u")
     assert_close(d_l, g["lin_delta_l"], "delta_l")
+
+
+def test_c4_alpha_beta_and_branch_choices(golden):
+    """The verbatim reference function `run_alpha_beta_crown_mlp` (alpha and beta optimised,
+    per-domain parameters) and its widest-gap branching hint on 24 split subdomains."""
+    g = golden("c4_split_alpha_beta.npz")
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 24
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+    C = wl.C.expand(D, -1, -1).contiguous()
+    trace = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+    choices = O.branch_choices(trace)
+    got = np.array([[-1, -1] if c is None else list(c) for c in choices])
+    assert (got == g["branch_choices"]).all()
+    a0 = O.adaptive_alpha_init(trace)
+    bl, bu, ba, bb, _ = O.alpha_crown(wl.layers, inp, C, steps=10, lr=0.1, alpha0=a0, splits=splits, trace=trace,
+                                      optimize_beta=True, return_beta=True)
+    assert_close(bl, g["best_lower"], "alpha-beta best lower")
+    assert_close(bu, g["best_upper"], "alpha-beta best upper")
+    for r, name in enumerate(wl.relu_names):
+        assert_close(bb[r], g[f"beta_{name}"], f"beta {name}", atol=1e-5, rtol=1e-4)
+    # beta moves only where a split exists and stays non-negative
+    for r in range(len(splits)):
+        assert float(bb[r].min()) >= 0.0
+        assert float(bb[r][splits[r] == 0].abs().max()) == 0.0
