@@ -406,8 +406,13 @@ def alpha_crown_from_trace(
     lr: float,
     spec_reduce: str = "mean",
     want_upper: bool = True,
+    beta_splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
+    beta0: Optional[Sequence[torch.Tensor]] = None,
 ):
-    """Device-resident alpha loop; returns (best_lower, best_upper|None, best_alpha list, last alpha list, best_metric)."""
+    """Device-resident alpha (and, with `beta_splits`, beta) loop; returns (best_lower,
+    best_upper|None, best_alpha list, last alpha list, best_metric) and, with beta, a sixth
+    element best_beta list.  `beta_splits[r]` is the int8 split assignment [B,n_r] or [1,n_r]
+    of ReLU r (None = no split there)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
     if spec_reduce not in ("mean", "sum"):
         raise NotImplementedError(f"spec_reduce={spec_reduce!r} is not supported by the CUDA backend (mean | sum)")
@@ -421,18 +426,46 @@ def alpha_crown_from_trace(
     best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
     best_upper = torch.empty(B, S, dtype=torch.float32, device=device) if want_upper else None
     best_metric = torch.empty(B, dtype=torch.float32, device=device)
-    nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, S))
+    reduce_code = _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM
+    if beta_splits is None:
+        nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, S))
+        ws = _Workspace.get(device, nbytes)
+        _lib.check(
+            chain.lib.bf_chain_alpha_crown(
+                chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
+                _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+                _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
+                int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+            )
+        )
+        return best_lower, best_upper, best_alpha, alpha, best_metric
+    splits, strides = [], []
+    for r, n in enumerate(chain.relu_widths):
+        sp = beta_splits[r] if r < len(beta_splits) else None
+        if sp is None:
+            splits.append(None)
+            strides.append(0)
+        else:
+            t, st = _split_tensor(sp, B, n, device, chain.relu_input_names[r])
+            splits.append(t)
+            strides.append(st)
+    if beta0 is not None:
+        beta = [b.detach().to(device=device, dtype=torch.float32).reshape(-1, n).expand(B, n).contiguous().clone() for b, n in zip(beta0, chain.relu_widths)]
+    else:
+        beta = [torch.zeros(B, n, dtype=torch.float32, device=device) for n in chain.relu_widths]
+    best_beta = [b.clone() for b in beta]
+    nbytes = int(chain.lib.bf_chain_alpha_beta_workspace_bytes(chain.handle, B, S))
     ws = _Workspace.get(device, nbytes)
     _lib.check(
-        chain.lib.bf_chain_alpha_crown(
+        chain.lib.bf_chain_alpha_beta_crown(
             chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
-            _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+            _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr_array(beta), _lib.ptr_array(best_beta),
+            _lib.ptr_array(splits), _lib.int_array(strides), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
             _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
-            int(steps), float(lr), _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM,
-            _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+            int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
     )
-    return best_lower, best_upper, best_alpha, alpha, best_metric
+    return best_lower, best_upper, best_alpha, alpha, best_metric, best_beta
 
 
 def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alpha: Sequence[torch.Tensor], *, spec_reduce: str = "mean"):
@@ -474,23 +507,28 @@ def run_alpha_beta_crown_mlp(
     objective: str = "lower",
     spec_reduce: str = "mean",
     per_batch_params: bool = False,
-    optimize_beta: bool = False,
+    optimize_beta: Optional[bool] = None,
 ):
-    """Per-domain alpha optimisation (alpha_beta_crown.py:643-941).
+    """Per-domain alpha-beta optimisation (alpha_beta_crown.py:643-941).
 
-    Differences from the reference, all explicit: parameters are always
-    per-domain (`per_batch_params=True`; the shared-parameter mode raises
-    NotImplementedError); beta stays at its zero start (`optimize_beta=True`
-    raises NotImplementedError), which for the alpha-only configurations is
-    exactly the reference with beta's learning suppressed; the objective is the
-    lower bound.  Infeasible splits raise ValueError like the reference.
+    Like the reference, beta (one multiplier >= 0 per split neuron and domain, start
+    `beta_init` or `warm_start_beta`) is optimised together with alpha whenever a split
+    assignment is given; `optimize_beta=False` freezes it at its start (the alpha-only
+    loop), `None` means "as the reference".  Differences from the reference, all explicit:
+    parameters are always per-domain (`per_batch_params=True`; the shared-parameter mode
+    raises NotImplementedError), the objective is the lower bound, and the batch-size-1
+    first-layer infeasibility certificate (alpha_beta_crown.py:391-532) is not evaluated.
+    Infeasible splits raise ValueError like the reference.
     """
     if not per_batch_params:
         raise NotImplementedError("the CUDA backend optimises per-domain parameters only (per_batch_params=True)")
     if objective != "lower":
         raise NotImplementedError("the CUDA backend optimises the lower bound only")
-    if optimize_beta or warm_start_beta is not None or float(beta_init) != 0.0:
-        raise NotImplementedError("beta optimisation is not implemented by the CUDA backend")
+    has_split = bool(relu_split_state)
+    if optimize_beta is None:
+        optimize_beta = has_split
+    if optimize_beta and not has_split:
+        optimize_beta = False  # nothing to constrain: beta's gradient is identically zero
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, B, device = trace.chain, trace.B, trace.mid.device
@@ -508,13 +546,44 @@ def run_alpha_beta_crown_mlp(
         for d in chain.output_shape:
             n_out *= int(d)
         linear_spec_C = torch.eye(n_out, dtype=torch.float32, device=device)
-    best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
     dev = normalize_input_spec(input_spec).center.device
+    beta_start = []
+    wb_map = getattr(warm_start_beta, "beta_by_relu_input", None) if warm_start_beta is not None else None
+    for r, name in enumerate(chain.relu_input_names):
+        n = chain.relu_widths[r]
+        if wb_map is not None and name in wb_map:
+            bt, _ = _alpha_rows(wb_map[name], B, n, device, name)
+            beta_start.append(bt.expand(B, n))
+        else:
+            beta_start.append(torch.full((B, n), float(beta_init), dtype=torch.float32, device=device))
+    if optimize_beta:
+        beta_splits = [relu_split_state.get(n) for n in chain.relu_input_names]
+        best_l, best_u, best_a, _last, _metric, best_b = alpha_crown_from_trace(
+            trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce, beta_splits=beta_splits, beta0=beta_start)
+    else:
+        if has_split and any(float(b.abs().max()) != 0.0 for b in beta_start):
+            raise NotImplementedError("a frozen non-zero beta is not supported; pass optimize_beta=None/True")
+        best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
+        best_b = beta_start
     bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
     a_state = AlphaState({n: a.reshape((B,) + tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
-    b_state = BetaState({n: torch.zeros((B,) + tuple(s), dtype=torch.float32, device=dev) for n, s in zip(chain.relu_input_names, chain.relu_shapes)})
+    b_state = BetaState({n: b.reshape((B,) + tuple(s)).to(dev) for n, b, s in zip(chain.relu_input_names, best_b, chain.relu_shapes)})
     stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(chain.relu_input_names))
+    stats.branch_choices = branch_choices_from_trace(trace)  # type: ignore[attr-defined]
     return bounds, a_state, b_state, stats
+
+
+def branch_choices_from_trace(trace: ForwardTrace) -> List[Optional[Tuple[str, int]]]:
+    """Widest-unstable-gap branching hint per domain as (ReLU input name, flat neuron index) or None
+    (`_branch_choices_from_relu_pre`, alpha_beta_crown.py:145-182).  Synchronises to return Python values."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    gap = torch.empty(B, dtype=torch.float32, device=device)
+    relu = torch.empty(B, dtype=torch.int32, device=device)
+    idx = torch.empty(B, dtype=torch.int32, device=device)
+    _lib.check(chain.lib.bf_branch_scores(_lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.int_array(chain.relu_widths),
+                                          len(chain.relu_widths), _lib.ptr(gap), _lib.ptr(relu), _lib.ptr(idx), B, _stream_ptr(device)))
+    relu_h, idx_h = relu.cpu().tolist(), idx.cpu().tolist()
+    return [None if r < 0 else (chain.relu_input_names[r], int(j)) for r, j in zip(relu_h, idx_h)]
 
 
 def run_crown_intermediate_mlp(

@@ -9,7 +9,7 @@
 #include <algorithm>
 #include <vector>
 
-#include "kernels.cuh"
+#include "chain_internal.cuh"
 
 namespace bf {
 
@@ -77,17 +77,6 @@ extern "C" int bf_kernel_timing_read(int slot, int* launches, float* total_ms) {
   return BF_OK;
 }
 
-struct bf_chain {
-  std::vector<bf_layer_desc> layers;
-  std::vector<int> relu_layers;  // layer index of every ReLU, chain order
-  int n0 = 0;
-  int max_width = 0;
-  bool linear_relu_alternating = false;  // linear (relu linear)*
-  // tensor-core path: per layer, packed hi/lo weight images for the backward (W^T as B) and
-  // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
-  std::vector<const unsigned char*> pk_bwd, pk_adj;
-  int* status = nullptr;
-};
 
 extern "C" int bf_version(void) { return 100; }
 extern "C" const char* bf_last_error_string(void) { return bf::g_err; }
@@ -145,20 +134,6 @@ extern "C" int bf_chain_num_relu(const bf_chain* chain) { return chain ? (int)ch
 
 namespace bf {
 
-static inline size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
-
-struct Carver {
-  char* base;
-  size_t off = 0;
-  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
-  template <typename T>
-  T* take(size_t n) {
-    T* p = reinterpret_cast<T*>(base + off);
-    off += align_up(n * sizeof(T));
-    return p;
-  }
-};
-
 static int relu_index_of(const bf_chain* c, int layer) {
   for (size_t r = 0; r < c->relu_layers.size(); ++r)
     if (c->relu_layers[r] == layer) return (int)r;
@@ -202,7 +177,7 @@ static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoin
 
 // Backward contraction of linear layer `layer`; *ptiles receives the number of column tiles
 // (the second dimension of the concretisation partial-sum buffer).
-static int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos, const float* dneg,
+int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos, const float* dneg,
                         const float* epos, const float* eneg, const float* add, float* A_prev, float* delta, int accumulate,
                         const float* mid, const float* rad, float* partial, int side, int M, int S, int* ptiles,
                         cudaStream_t stream) {
@@ -219,18 +194,18 @@ static int dispatch_bwd(const bf_chain* c, int layer, const float* A, const floa
                                  M, S, K, N, stream);
 }
 
-static int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid,
+int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid,
                             const float* rad, const float* Ahat, const float* dpos, const float* dneg, const float* epos,
-                            const float* eneg, const float* pre_l, const float* pre_u, float* hout, float* grad, int M, int S,
-                            cudaStream_t stream) {
+                            const float* eneg, const float* pre_l, const float* pre_u, float* hout, float* grad, float* gsum,
+                            int M, int S, cudaStream_t stream) {
   const bf_layer_desc& L = c->layers[layer];
   const int K = L.n_in, N = L.n_out;
   const unsigned char* pk = tc_weights(c, layer, true, M, K, N);
   if (pk)
     return launch_crown_adjoint_linear_tc(Hprev, first_layer, mid, rad, pk, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
-                                          hout, grad, M, S, K, N, c->status, stream);
+                                          hout, grad, gsum, M, S, K, N, c->status, stream);
   return launch_crown_adjoint_linear(Hprev, first_layer, mid, rad, L.W, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout,
-                                     grad, M, S, K, N, stream);
+                                     grad, gsum, M, S, K, N, stream);
 }
 
 }  // namespace bf
@@ -475,218 +450,3 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
   return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
 }
 
-// ---------------------------------------------------------------------------
-// alpha-CROWN
-// ---------------------------------------------------------------------------
-namespace bf {
-
-struct AlphaWs {
-  std::vector<float*> au, bu, sl, grad, m, v, Ahat;
-  float* A0;
-  float* H[2];
-  float* cacc;
-  float* partial;
-  float* cur;
-  float* metric;
-  int* improve;
-  size_t state_floats_begin, state_bytes;  // grad/m/v region (zero-initialised)
-  size_t bytes;
-};
-
-static size_t alpha_ws_layout(const bf_chain* c, int B, int S, void* base, AlphaWs* ws) {
-  const size_t M = (size_t)B * S;
-  const int R = (int)c->relu_layers.size();
-  Carver cv(base);
-  AlphaWs w;
-  int maxw = 1;
-  // zero-initialised optimiser state first, as one contiguous region
-  const size_t z0 = cv.off;
-  for (int r = 0; r < R; ++r) {
-    const size_t n = (size_t)c->layers[c->relu_layers[r]].n_in;
-    w.grad.push_back(cv.take<float>((size_t)B * n));
-    w.m.push_back(cv.take<float>((size_t)B * n));
-    w.v.push_back(cv.take<float>((size_t)B * n));
-  }
-  w.state_floats_begin = z0;
-  w.state_bytes = cv.off - z0;
-  for (int r = 0; r < R; ++r) {
-    const size_t n = (size_t)c->layers[c->relu_layers[r]].n_in;
-    if ((int)n > maxw) maxw = (int)n;
-    w.au.push_back(cv.take<float>((size_t)B * n));
-    w.bu.push_back(cv.take<float>((size_t)B * n));
-    w.sl.push_back(cv.take<float>((size_t)B * n));
-    w.Ahat.push_back(cv.take<float>(M * n));
-  }
-  w.A0 = cv.take<float>(M * (size_t)c->n0);
-  w.H[0] = cv.take<float>(M * (size_t)maxw);
-  w.H[1] = cv.take<float>(M * (size_t)maxw);
-  w.cacc = cv.take<float>(M);
-  w.partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
-  w.cur = cv.take<float>(M);
-  w.metric = cv.take<float>((size_t)B);
-  w.improve = cv.take<int>((size_t)B);
-  w.bytes = cv.off;
-  if (ws) *ws = w;
-  return cv.off;
-}
-
-// One lower- or upper-side sweep of a linear/ReLU chain with the relaxations in ws.
-static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int side, bool keep_A0, const float* mid,
-                       const float* rad, float* out, int B, int S, cudaStream_t stream) {
-  const int M = B * S;
-  const int R = (int)c->relu_layers.size();
-  const bf_layer_desc& top = c->layers[2 * R];
-  int rc;
-  int ptiles = 1;
-  (void)top;
-  if (R == 0) {
-    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, ws.cacc, 0, mid, rad,
-                      ws.partial, side, M, S, &ptiles, stream);
-    if (rc != BF_OK) return rc;
-  } else {
-    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], ws.cacc, 0, nullptr, nullptr,
-                      nullptr, side, M, S, nullptr, stream);
-    if (rc != BF_OK) return rc;
-    for (int r = R - 1; r >= 0; --r) {
-      const bf_layer_desc& L = c->layers[2 * r];
-      const float *dpos, *dneg, *epos = nullptr, *eneg = nullptr;
-      if (side == BF_SIDE_LOWER) { dpos = ws.sl[r]; dneg = ws.au[r]; eneg = ws.bu[r]; }
-      else { dpos = ws.au[r]; dneg = ws.sl[r]; epos = ws.bu[r]; }
-      const bool last = (r == 0);
-      float* dst = last ? (keep_A0 ? ws.A0 : nullptr) : ws.Ahat[r - 1];
-      rc = dispatch_bwd(c, 2 * r, ws.Ahat[r], dpos, dneg, epos, eneg, nullptr, dst, ws.cacc, 1, last ? mid : nullptr,
-                        last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
-      if (rc != BF_OK) return rc;
-    }
-  }
-  return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
-}
-
-// Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r].
-static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* const* pre_l, const float* const* pre_u,
-                         const float* mid, const float* rad, int B, int S, cudaStream_t stream) {
-  const int M = B * S;
-  const int R = (int)c->relu_layers.size();
-  for (int r = 0; r < R; ++r) {
-    const bf_layer_desc& L = c->layers[2 * r];
-    const float* hprev = (r == 0) ? ws.A0 : ws.H[(r - 1) & 1];
-    float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
-    int rc = dispatch_adjoint(c, 2 * r, hprev, r == 0, mid, rad, ws.Ahat[r], ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r],
-                              pre_u[r], hout, ws.grad[r], M, S, stream);
-    if (rc != BF_OK) return rc;
-  }
-  return BF_OK;
-}
-
-}  // namespace bf
-
-extern "C" size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S) {
-  if (!chain || B <= 0 || S <= 0) return 0;
-  return bf::alpha_ws_layout(chain, B, S, nullptr, nullptr);
-}
-
-static int alpha_common_checks(const char* who, const bf_chain* chain, const void* C, const void* pre_l, const void* pre_u,
-                               const void* alpha, const void* mid, const void* rad, void* workspace, size_t workspace_bytes,
-                               int B, int S, bf::AlphaWs* ws) {
-  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && mid && rad && workspace, BF_E_INVALID, "%s: null argument", who);
-  BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "%s: bad B/S", who);
-  BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
-  const size_t need = bf::alpha_ws_layout(chain, B, S, workspace, ws);
-  BF_REQUIRE(workspace_bytes >= need, BF_E_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, workspace_bytes);
-  return BF_OK;
-}
-
-extern "C" int bf_chain_alpha_crown(const bf_chain* chain, const float* C, const float* const* pre_l,
-                                    const float* const* pre_u, float* const* alpha, float* const* best_alpha,
-                                    const float* mid, const float* rad, float* best_lower, float* best_upper,
-                                    float* best_metric, int steps, float lr, int spec_reduce, void* workspace,
-                                    size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
-  bf::AlphaWs ws;
-  int rc = alpha_common_checks("bf_chain_alpha_crown", chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S, &ws);
-  if (rc != BF_OK) return rc;
-  BF_REQUIRE(best_alpha && best_lower && steps >= 0, BF_E_INVALID, "bf_chain_alpha_crown: null output or negative steps");
-  BF_REQUIRE(spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_SUM, BF_E_INVALID, "bf_chain_alpha_crown: bad spec_reduce");
-  cudaStream_t stream = bf::as_stream(stream_);
-  const int R = (int)chain->relu_layers.size();
-  float* metric = best_metric ? best_metric : ws.metric;
-
-  if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_floats_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
-    bf::set_error("bf_chain_alpha_crown: cudaMemsetAsync failed");
-    return BF_E_CUDA;
-  }
-  for (int r = 0; r < R; ++r) {
-    const int n = chain->layers[chain->relu_layers[r]].n_in;
-    rc = bf::launch_relu_relax(pre_l[r], pre_u[r], alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
-    if (rc != BF_OK) return rc;
-  }
-  const double beta1 = 0.9, beta2 = 0.999;
-  for (int t = 0; t <= steps; ++t) {
-    const bool last = (t == steps);
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, mid, rad, ws.cur, B, S, stream);
-    if (rc != BF_OK) return rc;
-    rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, B, S, stream);
-    if (rc != BF_OK) return rc;
-    bf::AdamScalars sc{};
-    if (!last) {
-      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, mid, rad, B, S, stream);
-      if (rc != BF_OK) return rc;
-      const double bc1 = 1.0 - pow(beta1, t + 1), bc2 = 1.0 - pow(beta2, t + 1);
-      sc.lr_step = (float)((double)lr / bc1);
-      sc.bc2_sqrt = (float)sqrt(bc2);
-      sc.beta1 = (float)beta1;
-      sc.beta2 = (float)beta2;
-      sc.eps = 1e-8f;
-      sc.one_minus_beta1 = (float)(1.0 - beta1);
-      sc.one_minus_beta2 = (float)(1.0 - beta2);
-      sc.grad_scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
-    }
-    for (int r = 0; r < R; ++r) {
-      const int n = chain->layers[chain->relu_layers[r]].n_in;
-      rc = bf::launch_adam_step(alpha[r], ws.m[r], ws.v[r], ws.grad[r], ws.improve, best_alpha[r], pre_l[r], pre_u[r],
-                                ws.sl[r], sc, last ? 0 : 1, B, n, stream);
-      if (rc != BF_OK) return rc;
-    }
-  }
-  if (best_upper) {
-    for (int r = 0; r < R; ++r) {
-      const int n = chain->layers[chain->relu_layers[r]].n_in;
-      rc = bf::launch_relu_relax(pre_l[r], pre_u[r], best_alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
-      if (rc != BF_OK) return rc;
-    }
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, mid, rad, best_upper, B, S, stream);
-    if (rc != BF_OK) return rc;
-  }
-  return BF_OK;
-}
-
-extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const float* const* pre_l,
-                                   const float* const* pre_u, const float* const* alpha, const float* mid,
-                                   const float* rad, float* const* grad, float* lower, int spec_reduce, void* workspace,
-                                   size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
-  bf::AlphaWs ws;
-  int rc = alpha_common_checks("bf_chain_alpha_grad", chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S, &ws);
-  if (rc != BF_OK) return rc;
-  BF_REQUIRE(grad && lower, BF_E_INVALID, "bf_chain_alpha_grad: null output");
-  cudaStream_t stream = bf::as_stream(stream_);
-  const int R = (int)chain->relu_layers.size();
-  if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_floats_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
-    bf::set_error("bf_chain_alpha_grad: cudaMemsetAsync failed");
-    return BF_E_CUDA;
-  }
-  for (int r = 0; r < R; ++r) {
-    const int n = chain->layers[chain->relu_layers[r]].n_in;
-    rc = bf::launch_relu_relax(pre_l[r], pre_u[r], alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
-    if (rc != BF_OK) return rc;
-  }
-  rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, true, mid, rad, lower, B, S, stream);
-  if (rc != BF_OK) return rc;
-  rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, mid, rad, B, S, stream);
-  if (rc != BF_OK) return rc;
-  const float scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
-  for (int r = 0; r < R; ++r) {
-    const int n = chain->layers[chain->relu_layers[r]].n_in;
-    rc = bf::launch_scale_copy(ws.grad[r], scale, grad[r], (long long)B * n, stream);
-    if (rc != BF_OK) return rc;
-  }
-  return BF_OK;
-}

@@ -1,0 +1,264 @@
+// alpha-CROWN / alpha-beta-CROWN driver for linear (relu linear)* chains: steps+1 lower-bound
+// sweeps, analytic gradients by an adjoint sweep, Adam, projections and per-domain best-of
+// tracking, all queued on one stream without host synchronisation.
+#include <math.h>
+
+#include <algorithm>
+
+#include "chain_internal.cuh"
+
+namespace bf {
+
+struct AlphaWs {
+  std::vector<float*> au, bu, sl, grad, m, v, Ahat;
+  std::vector<float*> gsum, mb, vb, addv;  // beta: gradient sums, Adam moments, split term -beta*s
+  float* A0;
+  float* H[2];
+  float* cacc;
+  float* partial;
+  float* cur;
+  float* metric;
+  int* improve;
+  size_t state_begin, state_bytes;  // grad/m/v (+ beta state) region, zero-initialised per call
+  size_t bytes;
+};
+
+static size_t alpha_ws_layout(const bf_chain* c, int B, int S, bool with_beta, void* base, AlphaWs* ws) {
+  const size_t M = (size_t)B * S;
+  const int R = (int)c->relu_layers.size();
+  Carver cv(base);
+  AlphaWs w;
+  int maxw = 1;
+  const size_t z0 = cv.off;
+  for (int r = 0; r < R; ++r) {
+    const size_t n = (size_t)c->layers[c->relu_layers[r]].n_in;
+    w.grad.push_back(cv.take<float>((size_t)B * n));
+    w.m.push_back(cv.take<float>((size_t)B * n));
+    w.v.push_back(cv.take<float>((size_t)B * n));
+    if (with_beta) {
+      w.gsum.push_back(cv.take<float>((size_t)B * n));
+      w.mb.push_back(cv.take<float>((size_t)B * n));
+      w.vb.push_back(cv.take<float>((size_t)B * n));
+      w.addv.push_back(cv.take<float>((size_t)B * n));
+    }
+  }
+  w.state_begin = z0;
+  w.state_bytes = cv.off - z0;
+  for (int r = 0; r < R; ++r) {
+    const size_t n = (size_t)c->layers[c->relu_layers[r]].n_in;
+    if ((int)n > maxw) maxw = (int)n;
+    w.au.push_back(cv.take<float>((size_t)B * n));
+    w.bu.push_back(cv.take<float>((size_t)B * n));
+    w.sl.push_back(cv.take<float>((size_t)B * n));
+    w.Ahat.push_back(cv.take<float>(M * n));
+  }
+  w.A0 = cv.take<float>(M * (size_t)c->n0);
+  w.H[0] = cv.take<float>(M * (size_t)maxw);
+  w.H[1] = cv.take<float>(M * (size_t)maxw);
+  w.cacc = cv.take<float>(M);
+  w.partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
+  w.cur = cv.take<float>(M);
+  w.metric = cv.take<float>((size_t)B);
+  w.improve = cv.take<int>((size_t)B);
+  w.bytes = cv.off;
+  if (ws) *ws = w;
+  return cv.off;
+}
+
+// One lower- or upper-side sweep with the relaxations in ws; `use_add` adds the split term of
+// every ReLU to the lower coefficients (beta-CROWN).
+static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int side, bool keep_A0, bool use_add,
+                       const float* mid, const float* rad, float* out, int B, int S, cudaStream_t stream) {
+  const int M = B * S;
+  const int R = (int)c->relu_layers.size();
+  int rc;
+  int ptiles = 1;
+  if (R == 0) {
+    rc = dispatch_bwd(c, 0, C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, ws.cacc, 0, mid, rad,
+                      ws.partial, side, M, S, &ptiles, stream);
+    if (rc != BF_OK) return rc;
+  } else {
+    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], ws.cacc, 0, nullptr, nullptr,
+                      nullptr, side, M, S, nullptr, stream);
+    if (rc != BF_OK) return rc;
+    for (int r = R - 1; r >= 0; --r) {
+      const float *dpos, *dneg, *epos = nullptr, *eneg = nullptr;
+      if (side == BF_SIDE_LOWER) { dpos = ws.sl[r]; dneg = ws.au[r]; eneg = ws.bu[r]; }
+      else { dpos = ws.au[r]; dneg = ws.sl[r]; epos = ws.bu[r]; }
+      const float* add = (use_add && side == BF_SIDE_LOWER) ? ws.addv[r] : nullptr;
+      const bool last = (r == 0);
+      float* dst = last ? (keep_A0 ? ws.A0 : nullptr) : ws.Ahat[r - 1];
+      rc = dispatch_bwd(c, 2 * r, ws.Ahat[r], dpos, dneg, epos, eneg, add, dst, ws.cacc, 1, last ? mid : nullptr,
+                        last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
+      if (rc != BF_OK) return rc;
+    }
+  }
+  return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
+}
+
+// Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r] and, with beta,
+// sum_s g_r[b,s,j] into ws.gsum[r].
+static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* const* pre_l, const float* const* pre_u,
+                         bool with_beta, const float* mid, const float* rad, int B, int S, cudaStream_t stream) {
+  const int M = B * S;
+  const int R = (int)c->relu_layers.size();
+  for (int r = 0; r < R; ++r) {
+    const float* hprev = (r == 0) ? ws.A0 : ws.H[(r - 1) & 1];
+    float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
+    int rc = dispatch_adjoint(c, 2 * r, hprev, r == 0, mid, rad, ws.Ahat[r], ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r],
+                              pre_u[r], hout, ws.grad[r], with_beta ? ws.gsum[r] : nullptr, M, S, stream);
+    if (rc != BF_OK) return rc;
+  }
+  return BF_OK;
+}
+
+static AdamScalars adam_scalars(int t, float lr, int spec_reduce, int S) {
+  const double beta1 = 0.9, beta2 = 0.999;
+  AdamScalars sc{};
+  const double bc1 = 1.0 - pow(beta1, t + 1), bc2 = 1.0 - pow(beta2, t + 1);
+  sc.lr_step = (float)((double)lr / bc1);
+  sc.bc2_sqrt = (float)sqrt(bc2);
+  sc.beta1 = (float)beta1;
+  sc.beta2 = (float)beta2;
+  sc.eps = 1e-8f;
+  sc.one_minus_beta1 = (float)(1.0 - beta1);
+  sc.one_minus_beta2 = (float)(1.0 - beta2);
+  sc.grad_scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
+  return sc;
+}
+
+}  // namespace bf
+
+extern "C" size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S) {
+  if (!chain || B <= 0 || S <= 0) return 0;
+  return bf::alpha_ws_layout(chain, B, S, false, nullptr, nullptr);
+}
+
+extern "C" size_t bf_chain_alpha_beta_workspace_bytes(const bf_chain* chain, int B, int S) {
+  if (!chain || B <= 0 || S <= 0) return 0;
+  return bf::alpha_ws_layout(chain, B, S, true, nullptr, nullptr);
+}
+
+static int alpha_common_checks(const char* who, const bf_chain* chain, const void* C, const void* pre_l, const void* pre_u,
+                               const void* alpha, const void* mid, const void* rad, void* workspace, size_t workspace_bytes,
+                               int B, int S, bool with_beta, bf::AlphaWs* ws) {
+  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && mid && rad && workspace, BF_E_INVALID, "%s: null argument", who);
+  BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "%s: bad B/S", who);
+  BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
+  const size_t need = bf::alpha_ws_layout(chain, B, S, with_beta, workspace, ws);
+  BF_REQUIRE(workspace_bytes >= need, BF_E_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, workspace_bytes);
+  return BF_OK;
+}
+
+extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                         const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                         float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                         const int* split_strides, const float* mid, const float* rad, float* best_lower,
+                                         float* best_upper, float* best_metric, int steps, float lr, int spec_reduce,
+                                         void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+  const bool with_beta = beta != nullptr;
+  const char* who = with_beta ? "bf_chain_alpha_beta_crown" : "bf_chain_alpha_crown";
+  bf::AlphaWs ws;
+  int rc = alpha_common_checks(who, chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S, with_beta, &ws);
+  if (rc != BF_OK) return rc;
+  BF_REQUIRE(best_alpha && best_lower && steps >= 0, BF_E_INVALID, "%s: null output or negative steps", who);
+  BF_REQUIRE(spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_SUM, BF_E_INVALID, "%s: bad spec_reduce", who);
+  BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
+  cudaStream_t stream = bf::as_stream(stream_);
+  const int R = (int)chain->relu_layers.size();
+  float* metric = best_metric ? best_metric : ws.metric;
+
+  if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
+    bf::set_error("%s: cudaMemsetAsync failed", who);
+    return BF_E_CUDA;
+  }
+  for (int r = 0; r < R; ++r) {
+    const int n = chain->layers[chain->relu_layers[r]].n_in;
+    rc = bf::launch_relu_relax(pre_l[r], pre_u[r], alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
+    if (rc != BF_OK) return rc;
+    if (with_beta) {  // split term of the start beta (no update, no snapshot: improve flags are not set yet)
+      bf::AdamScalars none{};
+      rc = bf::launch_beta_step(beta[r], ws.mb[r], ws.vb[r], ws.gsum[r], splits[r], split_strides ? split_strides[r] : n, nullptr,
+                                nullptr, ws.addv[r], none, 0, B, n, stream);
+      if (rc != BF_OK) return rc;
+    }
+  }
+  for (int t = 0; t <= steps; ++t) {
+    const bool last = (t == steps);
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, mid, rad, ws.cur, B, S, stream);
+    if (rc != BF_OK) return rc;
+    rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, B, S, stream);
+    if (rc != BF_OK) return rc;
+    bf::AdamScalars sc{};
+    if (!last) {
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, mid, rad, B, S, stream);
+      if (rc != BF_OK) return rc;
+      sc = bf::adam_scalars(t, lr, spec_reduce, S);
+    }
+    for (int r = 0; r < R; ++r) {
+      const int n = chain->layers[chain->relu_layers[r]].n_in;
+      rc = bf::launch_adam_step(alpha[r], ws.m[r], ws.v[r], ws.grad[r], ws.improve, best_alpha[r], pre_l[r], pre_u[r], ws.sl[r],
+                                sc, last ? 0 : 1, B, n, stream);
+      if (rc != BF_OK) return rc;
+      if (with_beta) {
+        rc = bf::launch_beta_step(beta[r], ws.mb[r], ws.vb[r], ws.gsum[r], splits[r], split_strides ? split_strides[r] : n,
+                                  ws.improve, best_beta[r], ws.addv[r], sc, last ? 0 : 1, B, n, stream);
+        if (rc != BF_OK) return rc;
+      }
+    }
+  }
+  if (best_upper) {
+    // the upper bound of each domain's best iteration = the upper sweep at its best alpha (beta acts on the lower side only)
+    for (int r = 0; r < R; ++r) {
+      const int n = chain->layers[chain->relu_layers[r]].n_in;
+      rc = bf::launch_relu_relax(pre_l[r], pre_u[r], best_alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
+      if (rc != BF_OK) return rc;
+    }
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, mid, rad, best_upper, B, S, stream);
+    if (rc != BF_OK) return rc;
+  }
+  return BF_OK;
+}
+
+extern "C" int bf_chain_alpha_crown(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                    const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                    const float* mid, const float* rad, float* best_lower, float* best_upper,
+                                    float* best_metric, int steps, float lr, int spec_reduce, void* workspace,
+                                    size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  return bf_chain_alpha_beta_crown(chain, C, pre_l, pre_u, alpha, best_alpha, nullptr, nullptr, nullptr, nullptr, mid, rad,
+                                   best_lower, best_upper, best_metric, steps, lr, spec_reduce, workspace, workspace_bytes, B, S,
+                                   stream);
+}
+
+extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                   const float* const* pre_u, const float* const* alpha, const float* mid,
+                                   const float* rad, float* const* grad, float* lower, int spec_reduce, void* workspace,
+                                   size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+  bf::AlphaWs ws;
+  int rc = alpha_common_checks("bf_chain_alpha_grad", chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S,
+                               false, &ws);
+  if (rc != BF_OK) return rc;
+  BF_REQUIRE(grad && lower, BF_E_INVALID, "bf_chain_alpha_grad: null output");
+  cudaStream_t stream = bf::as_stream(stream_);
+  const int R = (int)chain->relu_layers.size();
+  if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
+    bf::set_error("bf_chain_alpha_grad: cudaMemsetAsync failed");
+    return BF_E_CUDA;
+  }
+  for (int r = 0; r < R; ++r) {
+    const int n = chain->layers[chain->relu_layers[r]].n_in;
+    rc = bf::launch_relu_relax(pre_l[r], pre_u[r], alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
+    if (rc != BF_OK) return rc;
+  }
+  rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, true, false, mid, rad, lower, B, S, stream);
+  if (rc != BF_OK) return rc;
+  rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, false, mid, rad, B, S, stream);
+  if (rc != BF_OK) return rc;
+  const float scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
+  for (int r = 0; r < R; ++r) {
+    const int n = chain->layers[chain->relu_layers[r]].n_in;
+    rc = bf::launch_scale_copy(ws.grad[r], scale, grad[r], (long long)B * n, stream);
+    if (rc != BF_OK) return rc;
+  }
+  return BF_OK;
+}

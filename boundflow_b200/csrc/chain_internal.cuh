@@ -1,0 +1,47 @@
+// Shared between the chain drivers (chain.cu, chain_alpha.cu).
+#pragma once
+#include <vector>
+
+#include "kernels.cuh"
+
+struct bf_chain {
+  std::vector<bf_layer_desc> layers;
+  std::vector<int> relu_layers;  // layer index of every ReLU, chain order
+  int n0 = 0;
+  int max_width = 0;
+  bool linear_relu_alternating = false;  // linear (relu linear)*
+  // tensor-core path: per layer, packed hi/lo weight images for the backward (W^T as B) and
+  // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
+  std::vector<const unsigned char*> pk_bwd, pk_adj;
+  int* status = nullptr;
+};
+
+namespace bf {
+
+static inline size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  template <typename T>
+  T* take(size_t n) {
+    T* p = reinterpret_cast<T*>(base + off);
+    off += align_up(n * sizeof(T));
+    return p;
+  }
+};
+
+
+// Backward contraction of linear layer `layer` (tensor-core path when the packed weights exist and the
+// problem is large enough, FFMA tiles otherwise); *ptiles receives the number of column tiles of the
+// concretisation partial-sum buffer.
+int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos, const float* dneg, const float* epos,
+                 const float* eneg, const float* add, float* A_prev, float* delta, int accumulate, const float* mid,
+                 const float* rad, float* partial, int side, int M, int S, int* ptiles, cudaStream_t stream);
+int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid, const float* rad,
+                     const float* Ahat, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                     const float* pre_l, const float* pre_u, float* hout, float* grad, float* gsum, int M, int S,
+                     cudaStream_t stream);
+
+}  // namespace bf

@@ -99,6 +99,7 @@ struct AdjEpilogue {
   const float* pre_u;  // [D,N]
   float* hout;         // [M,N] or nullptr (last ReLU layer needs no adjoint point)
   float* grad;         // [D,N], accumulated with atomicAdd (at most two tiles touch one entry when S <= 128)
+  float* gsum;         // [D,N] or nullptr: sum over the domain's rows of g (beta gradient), same accumulation
 };
 
 constexpr int STAGE_LD = BN + 1;
@@ -169,12 +170,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
     for (int r = r_lo; r < r_hi; ++r) s += dsmem[r * STAGE_LD + c];
     if (col < g.N) atomicAdd(&e.grad[(size_t)d * g.N + col], s);
   }
+
+  // Second reduction for the beta gradient: sum over the domain's spec rows of g itself.
+  if (e.gsum != nullptr) {
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rl = tile_row(ty, i);
+      const int row = m0 + rl;
+#pragma unroll
+      for (int jb = 0; jb < 2; ++jb) {
+        const int cl = tile_col(tx, jb);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int cc = n0 + cl + q;
+          float gg = 0.f;
+          if (row < g.M && cc < g.N) gg = acc[i][jb * 4 + q] + (e.nbias ? __ldg(e.nbias + cc) : 0.f);
+          dsmem[rl * STAGE_LD + cl + q] = gg;
+        }
+      }
+    }
+    __syncthreads();
+    for (int d = d_first + half; d <= d_last; d += 2) {
+      const int r_lo = max(d * g.S, m0) - m0;
+      const int r_hi = min((d + 1) * g.S, m_end) - m0;
+      float s = 0.f;
+      for (int r = r_lo; r < r_hi; ++r) s += dsmem[r * STAGE_LD + c];
+      if (col < g.N) atomicAdd(&e.gsum[(size_t)d * g.N + col], s);
+    }
+  }
 }
 
 int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
-                                float* hout, float* grad, int M, int S, int K, int N, cudaStream_t stream) {
+                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream) {
   static bool attr_set[2] = {false, false};
   GemmArgs g{};
   g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
@@ -185,7 +215,7 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
   g.vecN = (N % 4 == 0);
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   g.mid = mid; g.rad = rad;
-  AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad};
+  AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum};
   dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
   timing_begin(1, stream);
   if (first_layer) {

@@ -66,6 +66,7 @@ struct Params {
   // adjoint epilogue
   const float* nbias; const float* Ahat; const float* e_dpos; const float* e_dneg; const float* e_epos; const float* e_eneg;
   const float* pre_l; const float* pre_u; float* hout; float* grad;
+  float* gsum;               // [D,N] or null: per-domain sums of g (beta gradient)
   int* status;               // device word, set non-zero when a wait expired
 };
 
@@ -362,6 +363,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
       float conc = 0.f;
       // adjoint: domains covered by this warp's 32 rows and their per-chunk table
       float* tbl = reinterpret_cast<float*>(tiles) + PROD_WARPS * (32 * STG_LD) + warp * (TBL_MAX * 5 * 32);
+      float* stg2 = reinterpret_cast<float*>(tiles) + PROD_WARPS * (32 * STG_LD + TBL_MAX * 5 * 32) + warp * (32 * 33);  // g itself, for the beta gradient
       const int d0 = (row_base < p.M) ? row_base / p.S : 0;
       const int nd = (row_base < p.M) ? (min(row_base + 31, p.M - 1) / p.S - d0 + 1) : 0;
       const bool tbl_ok = nd <= TBL_MAX;
@@ -440,8 +442,10 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
             const int r = it * 4 + rs;
             const int row = row_base + r;
             float4 contrib = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 ggv = contrib;
             if (row < p.M && col < p.N) {
               const float4 g4 = *reinterpret_cast<const float4*>(&stg[r * STG_LD + c4 * 4]);
+              ggv = make_float4(g4.x + nb.x, g4.y + nb.y, g4.z + nb.z, g4.w + nb.w);
               const int d = row / p.S;
               float4 dp, dn, ep, en, am;
               if (tbl_ok) {
@@ -478,6 +482,11 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
               if (p.hout) store4_guard(p.hout + (size_t)row * p.N, col, p.N, vN, h);
             }
             *reinterpret_cast<float4*>(&stg[r * STG_LD + c4 * 4]) = contrib;  // in place: same lane read this chunk
+            if (p.gsum) {
+              float* g2 = stg2 + r * 33 + c4 * 4;
+              g2[0] = (col + 0 < p.N) ? ggv.x : 0.f; g2[1] = (col + 1 < p.N) ? ggv.y : 0.f;
+              g2[2] = (col + 2 < p.N) ? ggv.z : 0.f; g2[3] = (col + 3 < p.N) ? ggv.w : 0.f;
+            }
           }
           __syncwarp();
           // per-domain column sums over this warp's 32 rows; at most two warps/tiles touch one (domain, column)
@@ -507,6 +516,20 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
               run += stg[r * STG_LD + lane];
             }
             if (run_d >= 0 && colj < p.N) atomicAdd(&p.grad[(size_t)run_d * p.N + colj], run);
+          }
+          if (p.gsum) {
+            float run = 0.f;
+            int run_d = -1;
+            for (int r = 0; r < nrows; ++r) {
+              const int d = (row_base + r) / p.S;
+              if (d != run_d) {
+                if (run_d >= 0 && colj < p.N) atomicAdd(&p.gsum[(size_t)run_d * p.N + colj], run);
+                run = 0.f;
+                run_d = d;
+              }
+              run += stg2[r * 33 + lane];
+            }
+            if (run_d >= 0 && colj < p.N) atomicAdd(&p.gsum[(size_t)run_d * p.N + colj], run);
           }
         }
       }
@@ -661,7 +684,10 @@ static int tc_smem_bytes(int BN, int* b_stages_out) {
   if (b_stages > tc::MAX_B_STAGES) b_stages = tc::MAX_B_STAGES;
   if (b_stages < 2) b_stages = 2;
   *b_stages_out = b_stages;
-  return tc::A_STAGES * 2 * tc::A_TILE + b_stages * b_bytes + 2048;  // + control block and alignment slack
+  const int mainloop = tc::A_STAGES * 2 * tc::A_TILE + b_stages * b_bytes;
+  // the epilogue reuses the tile area for per-warp buffers: transpose block, slope table, second block (beta gradient)
+  const int epilogue = tc::PROD_WARPS * (32 * tc::STG_LD + tc::TBL_MAX * 5 * 32 + 32 * 33) * (int)sizeof(float);
+  return (mainloop > epilogue ? mainloop : epilogue) + 2048;  // + control block and alignment slack
 }
 
 template <int MODE, int PRO>
@@ -713,8 +739,8 @@ int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* d
 int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const float* mid, const float* rad,
                                    const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
                                    const float* dneg, const float* epos, const float* eneg, const float* pre_l,
-                                   const float* pre_u, float* hout, float* grad, int M, int S, int K, int N, int* status,
-                                   cudaStream_t stream) {
+                                   const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
+                                   int* status, cudaStream_t stream) {
   tc::Params p{};
   int nt;
   tc_tile_shape(N, K, &p.BN, &nt, &p.nkb);
@@ -727,7 +753,7 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
   for (const void* q : nptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecN = 0;
   p.mid_k = mid; p.rad_k = rad;
   p.nbias = nbias; p.Ahat = Ahat; p.e_dpos = dpos; p.e_dneg = dneg; p.e_epos = epos; p.e_eneg = eneg;
-  p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad;
+  p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad; p.gsum = gsum;
   p.status = status;
   timing_begin(1, stream);
   int rc = first_layer ? tc_launch<tc::MODE_ADJ, tc::PRO_H0>(p, nt, stream, "crown_tc_kernel<adjoint,h0>")

@@ -278,3 +278,103 @@ extern "C" int bf_verdict(const float* lower, float threshold, float tol, int8_t
   BF_REQUIRE(B > 0 && S > 0, BF_E_INVALID, "bf_verdict: sizes must be positive");
   return bf::launch_verdict(lower, threshold, tol, verdict, min_lower, B, S, bf::as_stream(stream));
 }
+
+// ---- beta parameters (split-constraint multipliers) and branching scores -------------
+namespace bf {
+
+// gradient of the loss w.r.t. beta_j is grad_scale * (-s_j) * sum_s g[s,j]  (add_j = -beta_j * s_j enters the lower
+// coefficients, d lower / d add_j = g_j); entries without a split never move.  Same Adam recurrences as alpha,
+// projection to beta >= 0.
+__global__ void __launch_bounds__(128) beta_step_kernel(float* __restrict__ beta, float* __restrict__ m, float* __restrict__ v,
+                                                        float* __restrict__ gsum, const int8_t* __restrict__ split,
+                                                        int split_stride, const int* __restrict__ improve,
+                                                        float* __restrict__ best_beta, float* __restrict__ add, AdamScalars sc,
+                                                        int do_update, int n) {
+  const int b = blockIdx.x;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const size_t i = (size_t)b * n + j;
+  const float s = split ? (float)split[(size_t)b * split_stride + j] : 0.f;
+  float bt = beta[i];
+  if (improve != nullptr && best_beta != nullptr && improve[b] != 0) best_beta[i] = bt;
+  if (do_update) {
+    const float g = gsum[i] * sc.grad_scale * (-s);
+    gsum[i] = 0.f;
+    float mi = m[i], vi = v[i];
+    mi = mi + sc.one_minus_beta1 * (g - mi);
+    vi = vi * sc.beta2 + sc.one_minus_beta2 * g * g;
+    const float denom = sqrtf(vi) / sc.bc2_sqrt + sc.eps;
+    bt = fmaxf(bt - sc.lr_step * (mi / denom), 0.f);
+    m[i] = mi;
+    v[i] = vi;
+    beta[i] = bt;
+  }
+  add[i] = -bt * s;
+}
+
+int launch_beta_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride, const int* improve,
+                     float* best_beta, float* add, AdamScalars sc, int do_update, int B, int n, cudaStream_t stream) {
+  dim3 grid(B, ceil_div(n, 128));
+  beta_step_kernel<<<grid, 128, 0, stream>>>(beta, m, v, gsum, split, split_stride, improve, best_beta, add, sc, do_update, n);
+  BF_CHECK_LAUNCH("beta_step_kernel");
+  return BF_OK;
+}
+
+__global__ void fill_kernel(float* __restrict__ dst, float value, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = value;
+}
+
+// Widest unstable gap of one ReLU per domain: one warp per domain, first index wins ties; the caller
+// combines ReLUs in chain order with a strict comparison (earlier ReLUs win ties).
+__global__ void __launch_bounds__(256) branch_score_kernel(const float* __restrict__ l, const float* __restrict__ u, int n, int B,
+                                                           int relu_index, float* __restrict__ best_gap,
+                                                           int* __restrict__ best_relu, int* __restrict__ best_idx) {
+  const int b = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  float gap = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int j = lane; j < n; j += 32) {
+    const float lo = l[(size_t)b * n + j], up = u[(size_t)b * n + j];
+    if (lo < 0.f && up > 0.f) {
+      const float g = fmaxf(up - lo, 0.f);
+      if (g > gap) { gap = g; idx = j; }  // j increases: the first index of a tie is kept
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float og = __shfl_xor_sync(0xffffffffu, gap, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (og > gap || (og == gap && oi < idx)) { gap = og; idx = oi; }
+  }
+  if (lane == 0 && gap > best_gap[b]) {
+    best_gap[b] = gap;
+    best_relu[b] = relu_index;
+    best_idx[b] = idx;
+  }
+}
+
+}  // namespace bf
+
+extern "C" int bf_branch_scores(const float* const* pre_l, const float* const* pre_u, const int* widths, int n_relu,
+                                float* best_gap, int* best_relu, int* best_idx, int B, bf_stream_t stream_) {
+  BF_REQUIRE(pre_l && pre_u && widths && best_gap && best_relu && best_idx, BF_E_INVALID, "bf_branch_scores: null argument");
+  BF_REQUIRE(B > 0 && n_relu >= 0, BF_E_INVALID, "bf_branch_scores: bad sizes");
+  cudaStream_t stream = bf::as_stream(stream_);
+  // best_relu / best_idx start at -1 ("no unstable neuron"), best_gap at -inf
+  if (cudaMemsetAsync(best_relu, 0xff, sizeof(int) * (size_t)B, stream) != cudaSuccess ||
+      cudaMemsetAsync(best_idx, 0xff, sizeof(int) * (size_t)B, stream) != cudaSuccess) {
+    bf::set_error("bf_branch_scores: cudaMemsetAsync failed");
+    return BF_E_CUDA;
+  }
+  bf::fill_kernel<<<bf::ceil_div(B, 256), 256, 0, stream>>>(best_gap, -INFINITY, B);
+  BF_CHECK_LAUNCH("fill_kernel");
+  for (int r = 0; r < n_relu; ++r) {
+    BF_REQUIRE(pre_l[r] && pre_u[r] && widths[r] > 0, BF_E_INVALID, "bf_branch_scores: bad ReLU %d", r);
+    bf::branch_score_kernel<<<bf::ceil_div((long long)B * 32, 256), 256, 0, stream>>>(pre_l[r], pre_u[r], widths[r], B, r, best_gap,
+                                                                                  best_relu, best_idx);
+    BF_CHECK_LAUNCH("branch_score_kernel");
+  }
+  return BF_OK;
+}

@@ -13,7 +13,7 @@ int crown_bwd_partial_tiles(int N);
 int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
-                                float* hout, float* grad, int M, int S, int K, int N, cudaStream_t stream);
+                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream);
 
 // crown_tc.cu (tcgen05 3xTF32 path; weights pre-packed by tc_pack_weights)
 size_t tc_packed_bytes(int N, int K);
@@ -25,8 +25,8 @@ int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* d
 int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const float* mid, const float* rad,
                                    const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
                                    const float* dneg, const float* epos, const float* eneg, const float* pre_l,
-                                   const float* pre_u, float* hout, float* grad, int M, int S, int K, int N, int* status,
-                                   cudaStream_t stream);
+                                   const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
+                                   int* status, cudaStream_t stream);
 int crown_tc_partial_tiles(int N, int K);
 
 // ibp.cu
@@ -57,6 +57,10 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
                      const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
                      cudaStream_t stream);
 int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream);
+// beta parameters: snapshot, Adam step with gradient -split * gsum * grad_scale, projection to >= 0,
+// and the next split term add = -beta * split (split in {-1,0,+1}; entries with split == 0 never move)
+int launch_beta_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride, const int* improve,
+                     float* best_beta, float* add, AdamScalars sc, int do_update, int B, int n, cudaStream_t stream);
 int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
                    cudaStream_t stream);
 

@@ -272,6 +272,35 @@ int bf_chain_alpha_crown(const bf_chain* chain,
                          int steps, float lr, int spec_reduce,
                          void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
+/* alpha-beta-CROWN: as bf_chain_alpha_crown, plus one multiplier beta >= 0 per (domain, split
+ * neuron) whose term -beta*s (s = split sign) is added to the lower coefficients at that ReLU and
+ * which the same Adam recurrences update (gradient -s * sum over spec rows of the adjoint value).
+ *   replaces run_alpha_beta_crown_mlp(per_batch_params=True, objective="lower"),
+ *            boundflow/runtime/alpha_beta_crown.py:643-941, with _beta_to_relu_pre_add_coeff 615-640.
+ * beta, best_beta: HOST arrays of device pointers [B,n_r] (in: start values / out: last and best);
+ * splits: HOST array of int8 device pointers [B,n_r] (or [1,n_r] with split_strides[r] == 0; NULL
+ * entries = no split at that ReLU).  beta == NULL degenerates to bf_chain_alpha_crown.
+ * Workspace: bf_chain_alpha_beta_workspace_bytes. */
+size_t bf_chain_alpha_beta_workspace_bytes(const bf_chain* chain, int B, int S);
+int bf_chain_alpha_beta_crown(const bf_chain* chain,
+                              const float* C,
+                              const float* const* pre_l, const float* const* pre_u,
+                              float* const* alpha, float* const* best_alpha,
+                              float* const* beta, float* const* best_beta,
+                              const int8_t* const* splits, const int* split_strides,
+                              const float* mid, const float* rad,
+                              float* best_lower, float* best_upper, float* best_metric,
+                              int steps, float lr, int spec_reduce,
+                              void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+/* Branching hint: per domain the ReLU (chain order) and neuron with the widest gap u - l among
+ * unstable neurons (l < 0 < u); earlier ReLUs and lower indices win ties; -1/-1 when none.
+ *   replaces _branch_choices_from_relu_pre, boundflow/runtime/alpha_beta_crown.py:145-182.
+ * pre_l, pre_u: HOST arrays of device pointers [B,widths[r]]; outputs best_gap float [B],
+ * best_relu / best_idx int32 [B]. */
+int bf_branch_scores(const float* const* pre_l, const float* const* pre_u, const int* widths, int n_relu,
+                     float* best_gap, int* best_relu, int* best_idx, int B, bf_stream_t stream);
+
 /* Gradient of  -sum_b reduce_s lower[b,s]  w.r.t. every per-domain alpha at the given alpha
  * (the tensor torch autograd hands to Adam in alpha_beta_crown.py:913-917), plus the lower
  * bounds themselves.  grad: HOST array of device pointers [B,n_r]; lower [B,S]. */

@@ -1,0 +1,111 @@
+"""alpha-beta-CROWN (beta = split-constraint multipliers) and the branching hint on the GPU,
+against the reference's verbatim `run_alpha_beta_crown_mlp` outputs (golden) and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+def _c4_domains(D, dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    lo = wl.lo.expand(D, -1).contiguous()
+    up = wl.up.expand(D, -1).contiguous()
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    C = wl.C.expand(D, -1, -1).contiguous()
+    return wl, splits, spec, C, lo, up
+
+
+def test_alpha_beta_matches_reference_golden(dev, golden):
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, crown_from_trace, ibp_trace, run_alpha_beta_crown_mlp
+
+    g = golden("c4_split_alpha_beta.npz")
+    wl, splits, spec, C, _, _ = _c4_domains(24, dev)
+    state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
+    trace = ibp_trace(wl.module, spec, relu_split_state=state)
+    a0 = adaptive_alpha_from_trace(trace)
+    bounds, a_state, b_state, stats = run_alpha_beta_crown_mlp(
+        wl.module, spec, linear_spec_C=C.to(dev), relu_split_state=state, steps=10, lr=0.1,
+        warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))), per_batch_params=True)
+    # optimised bounds: Adam amplifies rounding-level differences, see tests/test_gpu_parity.py::test_c3_alpha_crown
+    assert_close(bounds.lower, g["best_lower"], "alpha-beta best lower", rtol=3e-4)
+    assert_close(bounds.upper, g["best_upper"], "alpha-beta best upper", rtol=3e-4)
+    got_m, ref_m = bounds.lower.mean(dim=1).cpu(), torch.as_tensor(g["best_lower"]).mean(dim=1)
+    assert (got_m >= ref_m - 2e-4 * ref_m.abs()).all(), "optimised objective is as good as the reference's"
+    for name, sp in zip(wl.relu_names, splits):
+        b = b_state.beta_by_relu_input[name].cpu()
+        assert float(b.min()) >= 0.0
+        assert float(b[sp == 0].abs().max()) == 0.0, "beta moves only where a split exists"
+        ref_b = torch.as_tensor(g[f"beta_{name}"])
+        # beta after 10 steps of +-lr moves: same support and the same values up to the trajectory noise
+        assert ((b > 0) == (ref_b > 0)).float().mean() > 0.98
+        assert float((b - ref_b).abs().max()) <= 0.25
+    # the returned bounds are reproduced by one strict evaluation at the returned alpha and beta
+    add = {n: -b_state.beta_by_relu_input[n] * s.to(dev).float() for n, s in zip(wl.relu_names, splits)}
+    lo_chk, up_chk = crown_from_trace(trace, C.to(dev), relu_alpha=a_state.alpha_by_relu_input, relu_pre_add_coeff_l=add)
+    assert_close(lo_chk, bounds.lower, "lower at best alpha/beta")
+    assert_close(up_chk, bounds.upper, "upper at best alpha")
+    # branching hint equals the reference's
+    got = np.array([[-1, -1] if c is None else [wl.relu_names.index(c[0]), c[1]] for c in stats.branch_choices])
+    assert (got == g["branch_choices"]).all()
+
+
+def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev):
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    D = 40  # 360 coefficient rows: the tensor-core kernels carry the beta term and its gradient
+    wl, splits, spec, C, lo, up = _c4_domains(D, dev)
+    state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
+    trace = ibp_trace(wl.module, spec, relu_split_state=state)
+    a0 = adaptive_alpha_from_trace(trace)
+    inp = O.box_input(lo, up)
+    tr = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+    # one Adam step: beta = lr where the gradient pushes it up, else 0 -- insensitive to rounding, so strict
+    r1 = alpha_crown_from_trace(trace, C.to(dev), a0, steps=1, lr=0.1, beta_splits=[state[n] for n in wl.relu_names])
+    o1 = O.alpha_crown(wl.layers, inp, C, steps=1, lr=0.1, alpha0=[a.cpu() for a in a0], splits=splits, trace=tr,
+                       optimize_beta=True, return_beta=True)
+    assert_close(r1[0], o1[0], "one-step best lower", rtol=3e-5)
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
+    # ten steps: beta must not be worse than alpha only
+    rb = alpha_crown_from_trace(trace, C.to(dev), a0, steps=10, lr=0.1, beta_splits=[state[n] for n in wl.relu_names])
+    ra = alpha_crown_from_trace(trace, C.to(dev), a0, steps=10, lr=0.1)
+    assert float(rb[0].mean()) >= float(ra[0].mean()) - 1e-3 * abs(float(ra[0].mean()))
+
+
+def test_branch_scores_match_oracle(dev):
+    from boundflow_b200.crown import branch_choices_from_trace, ibp_trace
+    from oracle import crown_oracle as O
+
+    wl, splits, spec, C, lo, up = _c4_domains(70, dev)
+    state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
+    trace = ibp_trace(wl.module, spec, relu_split_state=state)
+    got = branch_choices_from_trace(trace)
+    tr = O.forward_ibp_trace(wl.layers, O.box_input(lo, up), splits=splits)
+    ref = O.branch_choices(tr)
+    ref_named = [None if c is None else (wl.relu_names[c[0]], c[1]) for c in ref]
+    mism = [i for i, (a, b) in enumerate(zip(got, ref_named)) if a != b]
+    # a mismatch is only acceptable when two gaps are equal within rounding
+    for i in mism:
+        (ra, ja), (rb, jb) = got[i], ref_named[i]
+        ga = float(tr.pre[wl.relu_names.index(ra)][1][i, ja] - tr.pre[wl.relu_names.index(ra)][0][i, ja])
+        gb = float(tr.pre[wl.relu_names.index(rb)][1][i, jb] - tr.pre[wl.relu_names.index(rb)][0][i, jb])
+        assert abs(ga - gb) <= 1e-5 * abs(gb)
