@@ -16,7 +16,8 @@ LIB_PATH = os.path.join(_HERE, "libbf_b200.so")
 BF_OK = 0
 BF_E_INVALID, BF_E_UNSUPPORTED, BF_E_WORKSPACE, BF_E_CUDA = -1, -2, -3, -4
 SIDE_LOWER, SIDE_UPPER = 0, 1
-IN_LOWER_UPPER, IN_MID_RAD = 0, 1
+IN_LOWER_UPPER, IN_MID_RAD, IN_CENTER_DEV = 0, 1, 2
+NORM_BOX, NORM_L1, NORM_L2, NORM_INF = 0, 1, 2, 3
 OP_LINEAR, OP_CONV2D, OP_RELU, OP_FLATTEN = 1, 2, 3, 4
 REDUCE_MEAN, REDUCE_SUM = 0, 1
 
@@ -58,7 +59,10 @@ SIGNATURES = {
     "bf_chain_tc_status": (_i, [_p, C.POINTER(_i)]),
     "bf_chain_ibp": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "bf_chain_crown_workspace_bytes": (_sz, [_p, _i, _i, _i]),
-    "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _i, _p]),
+    "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _sz, _i, _i, _p]),
+    "bf_row_dual_norms": (_i, [_p, _i, _i, _i, _f, _p, _p]),
+    "bf_ibp_linear_lp": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "bf_concretize_lp": (_i, [_p, _p, _f, _i, _p, _p, _i, _i, _i, _i, _p]),
     "bf_chain_alpha_workspace_bytes": (_sz, [_p, _i, _i]),
     "bf_chain_alpha_crown": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_beta_workspace_bytes": (_sz, [_p, _i, _i]),

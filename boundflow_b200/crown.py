@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 import torch
 
 from . import _lib
-from .ir import IntervalState, input_mid_rad, normalize_input_spec
+from .ir import IntervalState, input_mid_rad, lp_ball_of, normalize_input_spec
 from .network import CudaChain, compile_chain
 
 
@@ -94,17 +94,24 @@ class ForwardTrace:
     out_u: torch.Tensor
     infeasible: torch.Tensor    # int32 [B]
     B: int
+    norm_p: int = 0             # _lib.NORM_BOX, or NORM_L1 / NORM_L2 for an Lp-ball input (then mid = centre, rad unused)
+    eps: float = 0.0
 
 
 def _prepare_input(module: Any, input_spec: Any):
     spec = normalize_input_spec(input_spec)
     center = spec.center
     device = _cuda_device(center)
-    mid, rad, lo, up = input_mid_rad(spec)
     chain = compile_chain(module, tuple(int(d) for d in center.shape[1:]), device)
     B = int(center.shape[0])
-    mid = _f32(mid, device).reshape(B, -1)
-    rad = _f32(rad, device).reshape(B, -1)
+    ball = lp_ball_of(spec)
+    if ball is not None:  # L1 / L2 ball: centre + eps; the radius tensor is only used by a conv first layer (bounding box)
+        mid = _f32(center, device).reshape(B, -1)
+        rad = torch.full_like(mid, float(ball[1]))
+    else:
+        mid, rad, _lo, _up = input_mid_rad(spec)
+        mid = _f32(mid, device).reshape(B, -1)
+        rad = _f32(rad, device).reshape(B, -1)
     return spec, chain, device, B, mid, rad, center.device
 
 
@@ -165,9 +172,18 @@ def ibp_trace(
             cons_l.append(_f32(c.lower, device).reshape(B, -1))
             cons_u.append(_f32(c.upper, device).reshape(B, -1))
     scratch = torch.empty(4 * (B * chain.max_width + 64), dtype=torch.float32, device=device)
+    ball = lp_ball_of(_spec)
+    in_b, in_mode, row_dev = rad, _lib.IN_MID_RAD, None
+    first = next((l for l in chain.layers if l.op != "flatten"), None)
+    if ball is not None and first is not None and first.op == "linear":
+        # first Linear layer on an L1/L2 ball: deviation eps * ||W_row||_q (perturbation.py:102-134)
+        W1 = first.W
+        row_dev = torch.empty(int(W1.shape[0]), dtype=torch.float32, device=device)
+        _lib.check(lib.bf_row_dual_norms(_lib.ptr(W1), int(W1.shape[0]), int(W1.shape[1]), ball[0], float(ball[1]), _lib.ptr(row_dev), _stream_ptr(device)))
+        in_b, in_mode = row_dev, _lib.IN_CENTER_DEV
     _lib.check(
         lib.bf_chain_ibp(
-            chain.handle, _lib.ptr(mid), _lib.ptr(rad), _lib.IN_MID_RAD,
+            chain.handle, _lib.ptr(mid), _lib.ptr(in_b), in_mode,
             _lib.ptr_array(splits), _lib.int_array(strides),
             _lib.ptr_array(cons_l), _lib.ptr_array(cons_u),
             _lib.ptr_array(pre_l), _lib.ptr_array(pre_u),
@@ -176,8 +192,9 @@ def ibp_trace(
         )
     )
     # keep the temporaries alive until the stream has consumed them
-    trace = ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=out_l, out_u=out_u, infeasible=infeasible, B=B)
-    trace._keep = (splits, cons_l, cons_u, scratch)  # type: ignore[attr-defined]
+    trace = ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=out_l, out_u=out_u, infeasible=infeasible, B=B,
+                         norm_p=(ball[0] if ball is not None else _lib.NORM_BOX), eps=(ball[1] if ball is not None else 0.0))
+    trace._keep = (splits, cons_l, cons_u, scratch, row_dev)  # type: ignore[attr-defined]
     return trace
 
 
@@ -235,7 +252,9 @@ def _trace_from_env(module: Any, input_spec: Any, interval_env: Mapping[str, Any
         pre_l.append(_f32(relu_pre[name].lower, device).reshape(B, -1))
         pre_u.append(_f32(relu_pre[name].upper, device).reshape(B, -1))
     z = torch.zeros(B, 1, dtype=torch.float32, device=device)
-    return ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=z, out_u=z, infeasible=torch.zeros(B, dtype=torch.int32, device=device), B=B)
+    ball = lp_ball_of(_spec)
+    return ForwardTrace(chain=chain, mid=mid, rad=rad, pre_l=pre_l, pre_u=pre_u, out_l=z, out_u=z, infeasible=torch.zeros(B, dtype=torch.int32, device=device), B=B,
+                        norm_p=(ball[0] if ball is not None else _lib.NORM_BOX), eps=(ball[1] if ball is not None else 0.0))
 
 
 def _expand_spec(C: Optional[torch.Tensor], B: int, out_dim: int, device: torch.device) -> torch.Tensor:
@@ -335,8 +354,8 @@ def crown_from_trace(
             chain.lib.bf_chain_crown(
                 chain.handle, upto, side, _lib.ptr(C),
                 _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add),
-                _lib.ptr(trace.mid), _lib.ptr(trace.rad), _lib.ptr(out),
-                _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+                _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
+                _lib.ptr(out), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
             )
         )
         outs[side] = out
@@ -414,6 +433,8 @@ def alpha_crown_from_trace(
     element best_beta list.  `beta_splits[r]` is the int8 split assignment [B,n_r] or [1,n_r]
     of ReLU r (None = no split there)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
+    if trace.norm_p != _lib.NORM_BOX:
+        raise NotImplementedError("alpha-CROWN on L1/L2 balls is not supported by the CUDA backend (boxes and L-inf balls are)")
     if spec_reduce not in ("mean", "sum"):
         raise NotImplementedError(f"spec_reduce={spec_reduce!r} is not supported by the CUDA backend (mean | sum)")
     n_out = 1

@@ -327,9 +327,14 @@ extern "C" int bf_chain_ibp(const bf_chain* chain, const float* in_a, const floa
     }
     int rc;
     if (L.op == BF_OP_LINEAR) {
-      rc = bf::launch_ibp_linear(cur_a, cur_b, mode, relu_pending, L.W, L.bias, sp, sp_stride, cl, cu, dst_l, dst_u,
-                                 infeasible, B, L.n_in, L.n_out, stream);
+      if (mode == BF_IN_CENTER_DEV)  // Lp ball on the input: in_b holds eps * dual norm of this layer's weight rows
+        rc = bf::launch_ibp_linear(cur_a, nullptr, BF_IN_MID_RAD, 0, L.W, L.bias, sp, sp_stride, cl, cu, dst_l, dst_u, infeasible, B,
+                                   L.n_in, L.n_out, cur_b, stream);
+      else
+        rc = bf::launch_ibp_linear(cur_a, cur_b, mode, relu_pending, L.W, L.bias, sp, sp_stride, cl, cu, dst_l, dst_u,
+                                   infeasible, B, L.n_in, L.n_out, nullptr, stream);
     } else {
+      BF_REQUIRE(mode != BF_IN_CENTER_DEV, BF_E_UNSUPPORTED, "bf_chain_ibp: an Lp-ball input needs a Linear first layer (give a box otherwise)");
       rc = bf::launch_ibp_conv2d(cur_a, cur_b, mode, relu_pending, L.W, L.bias, sp, sp_stride, cl, cu, dst_l, dst_u,
                                  infeasible, B, L, stream);
     }
@@ -388,9 +393,13 @@ extern "C" size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, i
 
 extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, const float* C,
                               const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
-                              const float* const* add, const float* mid, const float* rad, float* out, void* workspace,
-                              size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
-  BF_REQUIRE(chain && C && mid && rad && out && workspace, BF_E_INVALID, "bf_chain_crown: null argument");
+                              const float* const* add, const float* mid, const float* rad, int norm_p, float eps, float* out,
+                              void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+  BF_REQUIRE(chain && C && mid && out && workspace, BF_E_INVALID, "bf_chain_crown: null argument");
+  BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
+             "bf_chain_crown: bad norm");
+  BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "bf_chain_crown: a box needs its radius tensor");
+  const bool box = (norm_p == BF_NORM_BOX);
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "bf_chain_crown: bad B/S");
   BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_chain_crown: bad side");
   const int nl = (int)chain->layers.size();
@@ -427,7 +436,7 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
     }
     int rc;
     if (L.op == BF_OP_LINEAR) {
-      const bool last = (i == low);
+      const bool last = box && (i == low);  // the fused concretisation handles boxes; Lp balls concretise separately
       float* dst = last ? nullptr : ws.buf[toggle];
       rc = bf::dispatch_bwd(chain, i, curA, dpos, dneg, epos, eneg, ad, dst, ws.cacc, have_c, last ? mid : nullptr,
                             last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, &ptiles, stream);
@@ -447,6 +456,7 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
   }
   BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown: a ReLU directly on the input is not supported");
   if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
+  if (!box) return bf::launch_concretize_lp(curA, mid, have_c ? ws.cacc : nullptr, out, side, eps, norm_p, B, S, chain->n0, stream);
   return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
 }
 

@@ -18,6 +18,7 @@ struct IbpArgs {
   const float* cons_l; const float* cons_u;
   float* out_l; float* out_u; int* infeasible;
   int B, K, N; int vecK, vecN;
+  const float* row_dev;  // [N] or null: per-output deviation (eps * dual norm of the weight row), Lp-ball first layer
 };
 
 __global__ void __launch_bounds__(256) ibp_linear_kernel(IbpArgs g) {
@@ -40,7 +41,7 @@ __global__ void __launch_bounds__(256) ibp_linear_kernel(IbpArgs g) {
     creg = rreg = wreg = make_float4(0.f, 0.f, 0.f, 0.f);
     if (m < g.B && k < g.K) {
       float4 a = load4_guard(g.in_a + (size_t)m * g.K, k, g.K, vK);
-      float4 b = load4_guard(g.in_b + (size_t)m * g.K, k, g.K, vK);
+      float4 b = g.in_b ? load4_guard(g.in_b + (size_t)m * g.K, k, g.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
       if (g.in_mode == BF_IN_LOWER_UPPER) {
         if (g.relu_in) {
           a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f); a.z = fmaxf(a.z, 0.f); a.w = fmaxf(a.w, 0.f);
@@ -112,6 +113,15 @@ __global__ void __launch_bounds__(256) ibp_linear_kernel(IbpArgs g) {
       lo[j] = (accC[i][j] - accR[i][j]) + bb[j];
       up[j] = (accC[i][j] + accR[i][j]) + bb[j];
     }
+    if (g.row_dev) {  // Lp-ball first layer: deviation eps * ||W_row||_q instead of |W| * radius
+      const float4 dv = load4_guard(g.row_dev, col, g.N, vN);
+      const float d4[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo[j] -= d4[j];
+        up[j] += d4[j];
+      }
+    }
     bool bad = false;
     if (g.cons_l) {
       const float4 cl = load4_guard(g.cons_l + (size_t)row * g.N, col, g.N, vN);
@@ -146,13 +156,13 @@ __global__ void __launch_bounds__(256) ibp_linear_kernel(IbpArgs g) {
 
 int launch_ibp_linear(const float* in_a, const float* in_b, int in_mode, int relu_in, const float* W, const float* bias,
                       const int8_t* split, int split_stride, const float* cons_l, const float* cons_u, float* out_l,
-                      float* out_u, int* infeasible, int B, int K, int N, cudaStream_t stream) {
-  IbpArgs g{in_a, in_b, in_mode, relu_in, W, bias, split, split_stride, cons_l, cons_u, out_l, out_u, infeasible, B, K, N, 0, 0};
+                      float* out_u, int* infeasible, int B, int K, int N, const float* row_dev, cudaStream_t stream) {
+  IbpArgs g{in_a, in_b, in_mode, relu_in, W, bias, split, split_stride, cons_l, cons_u, out_l, out_u, infeasible, B, K, N, 0, 0, row_dev};
   g.vecK = (K % 4 == 0);
   const void* kptrs[] = {in_a, in_b, W};
   for (const void* p : kptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecK = 0;
   g.vecN = (N % 4 == 0);
-  const void* nptrs[] = {bias, cons_l, cons_u, out_l, out_u};
+  const void* nptrs[] = {bias, cons_l, cons_u, out_l, out_u, row_dev};
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   dim3 grid(ceil_div(B, IBM), ceil_div(N, IBN));
   ibp_linear_kernel<<<grid, 256, 0, stream>>>(g);
@@ -173,5 +183,102 @@ extern "C" int bf_ibp_linear(const float* in_a, const float* in_b, int in_mode, 
   BF_REQUIRE((cons_l == nullptr) == (cons_u == nullptr), BF_E_INVALID, "bf_ibp_linear: give both constraint tensors or none");
   BF_REQUIRE(!split || split_stride == 0 || split_stride == n_out, BF_E_INVALID, "bf_ibp_linear: split_stride must be 0 or n_out");
   return bf::launch_ibp_linear(in_a, in_b, in_mode, relu_in, W, bias, split, split_stride, cons_l, cons_u, out_l, out_u,
-                               infeasible, B, n_in, n_out, bf::as_stream(stream));
+                               infeasible, B, n_in, n_out, nullptr, bf::as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Lp-ball (p = 1, 2, inf) support: dual-norm row reductions
+// ---------------------------------------------------------------------------
+namespace bf {
+
+// out[r] = scale * ||rows[r, :]||_q with q the dual of p: p=inf -> sum |x|, p=2 -> sqrt(sum x^2), p=1 -> max |x|.
+// One warp per row.
+__global__ void __launch_bounds__(256) row_dual_norm_kernel(const float* __restrict__ rows, int n_rows, int n, int p, float scale,
+                                                            float* __restrict__ out) {
+  const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  float acc = 0.f;
+  for (int k = lane; k < n; k += 32) {
+    const float x = rows[(size_t)r * n + k];
+    if (p == 2) acc = fmaf(x, x, acc);
+    else if (p == 1) acc = fmaxf(acc, fabsf(x));
+    else acc += fabsf(x);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, acc, o);
+    acc = (p == 1) ? fmaxf(acc, other) : (acc + other);
+  }
+  if (lane == 0) out[r] = scale * ((p == 2) ? sqrtf(acc) : acc);
+}
+
+int launch_row_dual_norm(const float* rows, int n_rows, int n, int p, float scale, float* out, cudaStream_t stream) {
+  row_dual_norm_kernel<<<ceil_div((long long)n_rows * 32, 256), 256, 0, stream>>>(rows, n_rows, n, p, scale, out);
+  BF_CHECK_LAUNCH("row_dual_norm_kernel");
+  return BF_OK;
+}
+
+// out[m] = A[m,:].center[d,:] -/+ eps * ||A[m,:]||_q + bias_in[m]
+__global__ void __launch_bounds__(256) concretize_lp_kernel(const float* __restrict__ A, const float* __restrict__ center,
+                                                            const float* __restrict__ bias_in, float* __restrict__ out, float sgn,
+                                                            float eps, int p, int M, int S, int n0) {
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const float* a = A + (size_t)m * n0;
+  const float* c = center + (size_t)(m / S) * n0;
+  float dot = 0.f, acc = 0.f;
+  for (int k = lane; k < n0; k += 32) {
+    const float x = a[k];
+    dot = fmaf(x, c[k], dot);
+    if (p == 2) acc = fmaf(x, x, acc);
+    else if (p == 1) acc = fmaxf(acc, fabsf(x));
+    else acc += fabsf(x);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float other = __shfl_xor_sync(0xffffffffu, acc, o);
+    acc = (p == 1) ? fmaxf(acc, other) : (acc + other);
+  }
+  if (lane == 0) out[m] = dot + sgn * eps * ((p == 2) ? sqrtf(acc) : acc) + (bias_in ? bias_in[m] : 0.f);
+}
+
+int launch_concretize_lp(const float* A, const float* center, const float* bias_in, float* out, int side, float eps, int p, int B,
+                         int S, int n0, cudaStream_t stream) {
+  const int M = B * S;
+  concretize_lp_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(A, center, bias_in, out, side == BF_SIDE_LOWER ? -1.f : 1.f,
+                                                                           eps, p, M, S, n0);
+  BF_CHECK_LAUNCH("concretize_lp_kernel");
+  return BF_OK;
+}
+
+}  // namespace bf
+
+static bool lp_ok(int p) { return p == BF_NORM_INF || p == BF_NORM_L2 || p == BF_NORM_L1; }
+
+extern "C" int bf_row_dual_norms(const float* W, int n_rows, int n_cols, int p, float scale, float* out, bf_stream_t stream) {
+  BF_REQUIRE(W && out && n_rows > 0 && n_cols > 0, BF_E_INVALID, "bf_row_dual_norms: bad argument");
+  BF_REQUIRE(lp_ok(p), BF_E_INVALID, "bf_row_dual_norms: p must be BF_NORM_INF, BF_NORM_L2 or BF_NORM_L1");
+  return bf::launch_row_dual_norm(W, n_rows, n_cols, p, scale, out, bf::as_stream(stream));
+}
+
+extern "C" int bf_ibp_linear_lp(const float* center, const float* row_dev, const float* W, const float* bias, const int8_t* split,
+                                int split_stride, const float* cons_l, const float* cons_u, float* out_l, float* out_u,
+                                int* infeasible, int B, int n_in, int n_out, bf_stream_t stream) {
+  BF_REQUIRE(center && row_dev && W && out_l && out_u, BF_E_INVALID, "bf_ibp_linear_lp: null tensor");
+  BF_REQUIRE(B > 0 && n_in > 0 && n_out > 0, BF_E_INVALID, "bf_ibp_linear_lp: sizes must be positive");
+  BF_REQUIRE((cons_l == nullptr) == (cons_u == nullptr), BF_E_INVALID, "bf_ibp_linear_lp: give both constraint tensors or none");
+  return bf::launch_ibp_linear(center, nullptr, BF_IN_MID_RAD, 0, W, bias, split, split_stride, cons_l, cons_u, out_l, out_u,
+                               infeasible, B, n_in, n_out, row_dev, bf::as_stream(stream));
+}
+
+extern "C" int bf_concretize_lp(const float* A, const float* center, float eps, int p, const float* bias_in, float* out, int side,
+                                int B, int S, int n0, bf_stream_t stream) {
+  BF_REQUIRE(A && center && out, BF_E_INVALID, "bf_concretize_lp: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n0 > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "bf_concretize_lp: bad sizes");
+  BF_REQUIRE(lp_ok(p) && eps >= 0.f, BF_E_INVALID, "bf_concretize_lp: bad norm or eps");
+  BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_concretize_lp: bad side");
+  return bf::launch_concretize_lp(A, center, bias_in, out, side, eps, p, B, S, n0, bf::as_stream(stream));
 }

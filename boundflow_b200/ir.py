@@ -136,6 +136,14 @@ class InputSpec:
         return InputSpec(value_name, center, LpBallPerturbation(p="inf", eps=float(eps)))
 
     @staticmethod
+    def l2(*, value_name: str, center: torch.Tensor, eps: float) -> "InputSpec":
+        return InputSpec(value_name, center, LpBallPerturbation(p=2, eps=float(eps)))
+
+    @staticmethod
+    def l1(*, value_name: str, center: torch.Tensor, eps: float) -> "InputSpec":
+        return InputSpec(value_name, center, LpBallPerturbation(p=1, eps=float(eps)))
+
+    @staticmethod
     def box(*, value_name: str, lower: torch.Tensor, upper: torch.Tensor) -> "InputSpec":
         return InputSpec(value_name, (lower + upper) / 2.0, BoxPerturbation(lower=lower, upper=upper))
 
@@ -168,8 +176,22 @@ def input_mid_rad(spec: Any):
     if hasattr(pert, "eps"):
         p = pert.norm() if hasattr(pert, "norm") else pert._normalize_p()
         if p != "inf":
-            raise NotImplementedError("the CUDA backend bounds L-inf balls and boxes only")
+            raise NotImplementedError("midpoint/radius form exists for boxes and L-inf balls only; see lp_ball_of()")
         eps = float(pert.eps)
         c = spec.center
         return c, torch.full_like(c, eps), c - eps, c + eps
     raise TypeError(f"unsupported perturbation: {type(pert)}")
+
+
+def lp_ball_of(spec: Any):
+    """(p, eps) with p in {1, 2} when the input set is an L1 / L2 ball, else None.
+    (`LpBallPerturbation`, runtime/perturbation.py:73-222; L-inf balls are handled as boxes.)"""
+    spec = normalize_input_spec(spec)
+    pert = spec.perturbation
+    if hasattr(pert, "lower") and hasattr(pert, "upper"):
+        return None
+    if hasattr(pert, "eps"):
+        p = pert.norm() if hasattr(pert, "norm") else pert._normalize_p()
+        if p in ("1", "2"):
+            return int(p), float(pert.eps)
+    return None

@@ -35,6 +35,13 @@ typedef void* bf_stream_t; /* a cudaStream_t */
 
 #define BF_IN_LOWER_UPPER 0 /* (in_a, in_b) = (lower, upper) */
 #define BF_IN_MID_RAD 1     /* (in_a, in_b) = (midpoint, radius) */
+#define BF_IN_CENTER_DEV 2  /* bf_chain_ibp only: in_a = ball centre [B,n0], in_b = eps * dual norm of the first
+                               Linear layer's weight rows [n_1] (from bf_row_dual_norms): Lp-ball input */
+
+#define BF_NORM_BOX 0 /* per-element box given as midpoint + radius (also the L-inf ball: radius == eps) */
+#define BF_NORM_INF 3 /* Lp ball given as centre + eps, p = inf (dual norm: sum |x|) */
+#define BF_NORM_L2 2  /* p = 2 (dual norm: sqrt(sum x^2)) */
+#define BF_NORM_L1 1  /* p = 1 (dual norm: max |x|) */
 
 #define BF_OP_LINEAR 1
 #define BF_OP_CONV2D 2
@@ -179,6 +186,22 @@ int bf_crown_relu_conv2d_bwd_noalloc(const float* A, int side,
 int bf_concretize(const float* A, const float* mid, const float* rad, const float* bias_in,
                   float* out, int side, int B, int S, int n0, bf_stream_t stream);
 
+/* Lp-ball input sets (p = 1, 2, inf), the non-box branch of the reference's perturbations.
+ *   bf_row_dual_norms: out[r] = scale * ||W[r,:]||_q (q dual to p) -- the row norms of
+ *            LpBallPerturbation.concretize_matmul, boundflow/runtime/perturbation.py:102-134.
+ *   bf_ibp_linear_lp: first Linear layer on a ball: centre @ W^T + b -/+ row_dev, then the
+ *            same constraint / split clamps as bf_ibp_linear (row_dev [n_out] from bf_row_dual_norms
+ *            with scale = eps).
+ *   bf_concretize_lp: A.centre -/+ eps * ||A_row||_q + bias_in, replaces
+ *            LpBallPerturbation.concretize_affine perturbation.py:175-222 (row norms
+ *            boundflow/runtime/linear_operator.py:365-372). */
+int bf_row_dual_norms(const float* W, int n_rows, int n_cols, int p, float scale, float* out, bf_stream_t stream);
+int bf_ibp_linear_lp(const float* center, const float* row_dev, const float* W, const float* bias,
+                     const int8_t* split, int split_stride, const float* cons_l, const float* cons_u,
+                     float* out_l, float* out_u, int* infeasible, int B, int n_in, int n_out, bf_stream_t stream);
+int bf_concretize_lp(const float* A, const float* center, float eps, int p, const float* bias_in,
+                     float* out, int side, int B, int S, int n0, bf_stream_t stream);
+
 /* Verdict per domain: proven iff min over spec rows of the lower bound >= threshold - tol.
  *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895.
  * lower [B,S]; verdict int8 [B] (1 proven, 0 not); min_lower [B] or NULL. */
@@ -242,12 +265,13 @@ size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, int S, int u
  * output).  C [B,S,O] (a spec shared by all domains is expanded by the caller).
  * alpha_u/beta_u/alpha_l: HOST arrays of device pointers per ReLU, each [B,n_r] (from
  * bf_relu_relax); add: per ReLU [B,n_r] or NULL entries / NULL array (lower side only).
- * mid, rad [B,n0]; out [B,S]. */
+ * Input set: norm_p = BF_NORM_BOX with mid, rad [B,n0] (eps ignored), or an Lp ball with
+ * mid = centre [B,n0], rad = NULL and norm_p in {BF_NORM_INF, BF_NORM_L2, BF_NORM_L1}.  out [B,S]. */
 int bf_chain_crown(const bf_chain* chain, int upto_layer, int side,
                    const float* C,
                    const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
                    const float* const* add,
-                   const float* mid, const float* rad, float* out,
+                   const float* mid, const float* rad, int norm_p, float eps, float* out,
                    void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S);

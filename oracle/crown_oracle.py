@@ -48,6 +48,22 @@ class InputSet:
     rad: torch.Tensor
     lo: torch.Tensor
     up: torch.Tensor
+    p: Optional[int] = None   # 1 or 2: an Lp ball of radius eps around `mid` (then lo/up are its bounding box)
+    eps: float = 0.0
+
+
+def lp_ball(x0: torch.Tensor, eps: float, p: int) -> "InputSet":
+    """L1 / L2 ball (`LpBallPerturbation`, perturbation.py:73-222).  Its
+    bounding box is centre +- eps for every p (perturbation.py:97-100)."""
+    if p not in (1, 2):
+        raise ValueError("p must be 1 or 2 (use linf_box for the L-inf ball)")
+    rad = torch.full_like(x0, float(eps))
+    return InputSet(mid=x0, rad=rad, lo=x0 - float(eps), up=x0 + float(eps), p=int(p), eps=float(eps))
+
+
+def _dual_row_norm(A: torch.Tensor, p: int) -> torch.Tensor:
+    """Dual norm over the last axis: p=2 -> L2, p=1 -> max |.| (perturbation.py:121-126, 204-209)."""
+    return torch.linalg.vector_norm(A, ord=2, dim=-1) if p == 2 else A.abs().amax(dim=-1)
 
 
 def box_input(lo: torch.Tensor, up: torch.Tensor) -> InputSet:
@@ -72,7 +88,10 @@ def ibp_first_linear(inp: InputSet, W: torch.Tensor, b: Optional[torch.Tensor]):
     mid = inp.mid.reshape(inp.mid.shape[0], -1)
     rad = inp.rad.reshape(inp.rad.shape[0], -1)
     center = mid.matmul(W.t())
-    dev = rad.matmul(W.abs().t())
+    if inp.p is not None:  # L1/L2 ball: eps * dual row norm, the same for every batch row (perturbation.py:117-128)
+        dev = (inp.eps * _dual_row_norm(W, inp.p)).unsqueeze(0)
+    else:
+        dev = rad.matmul(W.abs().t())
     lower, upper = center - dev, center + dev
     if b is not None:
         lower, upper = lower + b, upper + b
@@ -187,7 +206,8 @@ def forward_ibp_trace(
         elif op == "flatten":
             if at_input:
                 cur_inp = InputSet(
-                    mid=cur_inp.mid.flatten(1), rad=cur_inp.rad.flatten(1), lo=cur_inp.lo.flatten(1), up=cur_inp.up.flatten(1)
+                    mid=cur_inp.mid.flatten(1), rad=cur_inp.rad.flatten(1), lo=cur_inp.lo.flatten(1), up=cur_inp.up.flatten(1),
+                    p=cur_inp.p, eps=cur_inp.eps,
                 )
             cur_l, cur_u = cur_l.flatten(1), cur_u.flatten(1)
         else:
@@ -293,7 +313,10 @@ def concretize(inp: InputSet, A, b, side: str):
     mid = inp.mid.reshape(B, 1, -1)
     rad = inp.rad.reshape(B, 1, -1)
     center = (A * mid).sum(dim=2)
-    dev = (A.abs() * rad).sum(dim=2)
+    if inp.p is not None:  # perturbation.py:201-222: eps * ||A_row||_q
+        dev = inp.eps * _dual_row_norm(A, inp.p)
+    else:
+        dev = (A.abs() * rad).sum(dim=2)
     return (center - dev + b) if side == "lower" else (center + dev + b)
 
 

@@ -130,9 +130,30 @@ def ref_crown_intermediate(module, spec, C, relu_names, chunk=512):
     return final, current
 
 
+def gen_lp_ball() -> None:
+    """L2 / L1 ball inputs: IBP and CROWN-IBP on the MLP (first layer Linear, dual-norm
+    concretisation) and on the CNN (first layer conv: bounding box in the forward pass)."""
+    out = {}
+    for tag, wl in (("c1", W.make_workload("c1")), ("c2", W.make_workload("c2", batch=4))):
+        m = ref_module(wl)
+        out[f"{tag}_input_checksum"] = checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])
+        for pname, mk, eps in (("l2", InputSpec.l2, 4.0 * wl.eps), ("l1", InputSpec.l1, 12.0 * wl.eps)):
+            spec = mk(value_name="input", center=wl.x, eps=eps)
+            ibp = PythonTaskExecutor().run_ibp(m, spec)
+            crown = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C)
+            out[f"{tag}_{pname}_eps"] = eps
+            out[f"{tag}_{pname}_ibp_lower"], out[f"{tag}_{pname}_ibp_upper"] = ibp.lower, ibp.upper
+            out[f"{tag}_{pname}_crown_lower"], out[f"{tag}_{pname}_crown_upper"] = crown.lower, crown.upper
+    save("lp_ball.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
+    if len(sys.argv) > 2 and sys.argv[2] == "lp_ball":  # regenerate this one file only
+        gen_lp_ball()
+        return
+    gen_lp_ball()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

@@ -1,0 +1,79 @@
+"""L2 / L1 ball input sets on the GPU (dual-norm first layer, dual-norm concretisation),
+against the reference's own outputs (tests/golden/lp_ball.npz) and the oracle."""
+import pytest
+import torch
+
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("tag,batch", [("c1", None), ("c2", 4)])
+@pytest.mark.parametrize("pname,p", [("l2", 2), ("l1", 1)])
+def test_lp_ball_matches_reference_golden(dev, golden, tag, batch, pname, p):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("lp_ball.npz")
+    wl = W.make_workload(tag) if batch is None else W.make_workload(tag, batch=batch)
+    mk = InputSpec.l2 if p == 2 else InputSpec.l1
+    spec = mk(value_name="input", center=wl.x.to(dev), eps=float(g[f"{tag}_{pname}_eps"]))
+    ibp = CudaTaskExecutor().run_ibp(wl.module, spec)
+    assert_close(ibp.lower, g[f"{tag}_{pname}_ibp_lower"], "ibp lower")
+    assert_close(ibp.upper, g[f"{tag}_{pname}_ibp_upper"], "ibp upper")
+    crown = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev))
+    assert_close(crown.lower, g[f"{tag}_{pname}_crown_lower"], "crown lower")
+    assert_close(crown.upper, g[f"{tag}_{pname}_crown_upper"], "crown upper")
+
+
+@pytest.mark.parametrize("p", [1, 2, 3])
+def test_lp_entry_points_against_torch(dev, p):
+    """bf_row_dual_norms and bf_concretize_lp on ragged sizes (p = 3 encodes the L-inf ball)."""
+    from boundflow_b200 import _lib
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(5 + p)
+    Wm = torch.randn(37, 301, generator=g)
+    A = torch.randn(3, 7, 301, generator=g)
+    x0 = torch.randn(3, 301, generator=g)
+    b = torch.randn(3, 7, generator=g)
+    eps = 0.37
+
+    def dual(t):
+        if p == 2:
+            return torch.linalg.vector_norm(t, ord=2, dim=-1)
+        return t.abs().amax(dim=-1) if p == 1 else t.abs().sum(dim=-1)
+
+    Wd, Ad, xd, bd = (t.to(dev).contiguous() for t in (Wm, A, x0, b))
+    s = torch.cuda.current_stream(dev).cuda_stream
+    out = torch.empty(37, device=dev)
+    _lib.check(lib.bf_row_dual_norms(_lib.ptr(Wd), 37, 301, p, eps, _lib.ptr(out), s))
+    assert_close(out, eps * dual(Wm), "row dual norms")
+    for side, sgn in ((0, -1.0), (1, 1.0)):
+        o = torch.empty(3, 7, device=dev)
+        _lib.check(lib.bf_concretize_lp(_lib.ptr(Ad), _lib.ptr(xd), eps, p, _lib.ptr(bd), _lib.ptr(o), side, 3, 7, 301, s))
+        ref = (A * x0[:, None, :]).sum(-1) + sgn * eps * dual(A) + b
+        assert_close(o, ref, f"concretize side {side}")
+
+
+def test_alpha_on_lp_ball_is_refused(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
+    from boundflow_b200.ir import InputSpec
+
+    wl = W.make_workload("c3", batch=2)
+    spec = InputSpec.l2(value_name="input", center=wl.x.to(dev), eps=0.1)
+    trace = ibp_trace(wl.module, spec)
+    with pytest.raises(NotImplementedError):
+        alpha_crown_from_trace(trace, wl.C.to(dev), adaptive_alpha_from_trace(trace), steps=1, lr=0.1)

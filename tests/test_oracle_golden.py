@@ -197,3 +197,17 @@ def test_c4_alpha_beta_and_branch_choices(golden):
     for r in range(len(splits)):
         assert float(bb[r].min()) >= 0.0
         assert float(bb[r][splits[r] == 0].abs().max()) == 0.0
+
+
+def test_lp_ball_inputs(golden):
+    """L2 / L1 balls: dual-norm first layer and concretisation (MLP), bounding-box forward pass (CNN)."""
+    g = golden("lp_ball.npz")
+    for tag, wl in (("c1", W.make_workload("c1")), ("c2", W.make_workload("c2", batch=4))):
+        assert np.allclose(workload_checksum(wl), g[f"{tag}_input_checksum"], rtol=1e-12, atol=0)
+        for pname, p in (("l2", 2), ("l1", 1)):
+            inp = O.lp_ball(wl.x, float(g[f"{tag}_{pname}_eps"]), p)
+            lower, upper, trace = O.crown_ibp(wl.layers, inp, wl.C)
+            assert_close(trace.out[0], g[f"{tag}_{pname}_ibp_lower"], f"{tag} {pname} ibp lower")
+            assert_close(trace.out[1], g[f"{tag}_{pname}_ibp_upper"], f"{tag} {pname} ibp upper")
+            assert_close(lower, g[f"{tag}_{pname}_crown_lower"], f"{tag} {pname} crown lower")
+            assert_close(upper, g[f"{tag}_{pname}_crown_upper"], f"{tag} {pname} crown upper")
