@@ -513,6 +513,110 @@ def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alph
     return grads, lower
 
 
+def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[torch.Tensor], alpha0: Sequence[torch.Tensor], *,
+                                  steps: int, lr: float, want_upper: bool = True,
+                                  beta_splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                                  beta0: Optional[Sequence[torch.Tensor]] = None):
+    """Device-resident loop with ONE alpha (and, with `beta_splits`, one beta) per neuron for the
+    whole batch; returns (best_lower, best_upper|None, best_alpha list [n_r], last alpha list,
+    best_metric [1]) and, with beta, a sixth element best_beta list [n_r]."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    if trace.norm_p != _lib.NORM_BOX:
+        raise NotImplementedError("alpha-CROWN on L1/L2 balls is not supported by the CUDA backend (boxes and L-inf balls are)")
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    C = _expand_spec(linear_spec_C, B, n_out, device)
+    S = int(C.shape[1])
+    alpha = [a.detach().to(device=device, dtype=torch.float32).reshape(n).contiguous().clone() for a, n in zip(alpha0, chain.relu_widths)]
+    best_alpha = [torch.empty_like(a) for a in alpha]
+    best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
+    best_upper = torch.empty(B, S, dtype=torch.float32, device=device) if want_upper else None
+    best_metric = torch.empty(1, dtype=torch.float32, device=device)
+    with_beta = beta_splits is not None
+    beta = best_beta = None
+    splits: List[Optional[torch.Tensor]] = []
+    strides: List[int] = []
+    if with_beta:
+        for r, n in enumerate(chain.relu_widths):
+            sp = beta_splits[r] if r < len(beta_splits) else None
+            if sp is None:
+                splits.append(None)
+                strides.append(0)
+            else:
+                t, st = _split_tensor(sp, B, n, device, chain.relu_input_names[r])
+                splits.append(t)
+                strides.append(st)
+        if beta0 is not None:
+            beta = [b.detach().to(device=device, dtype=torch.float32).reshape(n).contiguous().clone() for b, n in zip(beta0, chain.relu_widths)]
+        else:
+            beta = [torch.zeros(n, dtype=torch.float32, device=device) for n in chain.relu_widths]
+        best_beta = [b.clone() for b in beta]
+    nbytes = int(chain.lib.bf_chain_alpha_shared_workspace_bytes(chain.handle, B, S, 1 if with_beta else 0))
+    ws = _Workspace.get(device, nbytes)
+    _lib.check(
+        chain.lib.bf_chain_alpha_crown_shared(
+            chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
+            _lib.ptr_array(alpha), _lib.ptr_array(best_alpha),
+            _lib.ptr_array(beta) if with_beta else None, _lib.ptr_array(best_beta) if with_beta else None,
+            _lib.ptr_array(splits) if with_beta else None, _lib.int_array(strides) if with_beta else None,
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+            _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
+            int(steps), float(lr), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+        )
+    )
+    if with_beta:
+        return best_lower, best_upper, best_alpha, alpha, best_metric, best_beta
+    return best_lower, best_upper, best_alpha, alpha, best_metric
+
+
+def run_alpha_crown_mlp(
+    module: Any,
+    input_spec: Any,
+    *,
+    linear_spec_C: Optional[torch.Tensor] = None,
+    steps: int = 20,
+    lr: float = 0.2,
+    alpha_init: float = 0.5,
+    objective: str = "lower",
+    spec_reduce: str = "mean",
+    soft_tau: float = 1.0,
+    lb_weight: float = 1.0,
+    ub_weight: float = 1.0,
+    warm_start: Optional[Any] = None,
+    relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+):
+    """alpha-CROWN with alpha stored per ReLU neuron and shared across batch and spec rows
+    (`run_alpha_crown_mlp`, runtime/alpha_crown.py:137-261): steps+1 evaluations, Adam on
+    -mean(lower), clamp to [0,1], and the bounds / alpha of the evaluation with the best
+    whole-batch metric.  Returns (IntervalState, AlphaState, AlphaCrownStats) like the
+    reference.  The CUDA backend implements objective="lower" with spec_reduce="mean" on
+    linear (relu linear)* chains; other settings raise NotImplementedError."""
+    if objective != "lower" or spec_reduce != "mean":
+        raise NotImplementedError("the CUDA backend implements objective='lower' with spec_reduce='mean' for the shared-alpha loop")
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
+    _raise_if_infeasible(trace, "relu split")
+    chain, device = trace.chain, trace.mid.device
+    ws_map = getattr(warm_start, "alpha_by_relu_input", None) if warm_start is not None else None
+    alpha0 = []
+    for name, n, shape in zip(chain.relu_input_names, chain.relu_widths, chain.relu_shapes):
+        if ws_map is not None and name in ws_map:
+            a = torch.as_tensor(ws_map[name])
+            if a.dim() == 0:  # a scalar start broadcasts (relu_shape_utils.py:37-38)
+                a = a.expand(n)
+            if int(a.numel()) != n:
+                raise ValueError(f"warm_start alpha[{name}] has {int(a.numel())} elements, the ReLU input has shape {tuple(shape)}")
+            alpha0.append(a.detach().to(device=device, dtype=torch.float32).reshape(n))
+        else:
+            alpha0.append(torch.full((n,), float(alpha_init), dtype=torch.float32, device=device))
+    best_l, best_u, best_a, _last, _metric = shared_alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr)
+    dev = normalize_input_spec(input_spec).center.device
+    bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
+    state = AlphaState({n: a.reshape(tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
+    stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(chain.relu_input_names))
+    return bounds, state, stats
+
+
 def run_alpha_beta_crown_mlp(
     module: Any,
     input_spec: Any,
@@ -535,14 +639,13 @@ def run_alpha_beta_crown_mlp(
     Like the reference, beta (one multiplier >= 0 per split neuron and domain, start
     `beta_init` or `warm_start_beta`) is optimised together with alpha whenever a split
     assignment is given; `optimize_beta=False` freezes it at its start (the alpha-only
-    loop), `None` means "as the reference".  Differences from the reference, all explicit:
-    parameters are always per-domain (`per_batch_params=True`; the shared-parameter mode
-    raises NotImplementedError), the objective is the lower bound, and the batch-size-1
+    loop), `None` means "as the reference".  `per_batch_params=False` (the reference's
+    default) optimises one alpha / beta row shared by the whole batch with a whole-batch
+    best-of.  Differences from the reference, all explicit: the objective is the lower
+    bound (shared mode: with spec_reduce="mean"), and the batch-size-1
     first-layer infeasibility certificate (alpha_beta_crown.py:391-532) is not evaluated.
     Infeasible splits raise ValueError like the reference.
     """
-    if not per_batch_params:
-        raise NotImplementedError("the CUDA backend optimises per-domain parameters only (per_batch_params=True)")
     if objective != "lower":
         raise NotImplementedError("the CUDA backend optimises the lower bound only")
     has_split = bool(relu_split_state)
@@ -553,39 +656,50 @@ def run_alpha_beta_crown_mlp(
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, B, device = trace.chain, trace.B, trace.mid.device
-    alpha0 = []
-    for r, name in enumerate(chain.relu_input_names):
-        n = chain.relu_widths[r]
-        ws_map = getattr(warm_start_alpha, "alpha_by_relu_input", None) if warm_start_alpha is not None else None
-        if ws_map is not None and name in ws_map:
-            a, _ = _alpha_rows(ws_map[name], B, n, device, name)
-            alpha0.append(a.expand(B, n))
-        else:
-            alpha0.append(torch.full((B, n), float(alpha_init), dtype=torch.float32, device=device))
+    rows = B if per_batch_params else 1  # shared mode: one parameter row for the whole batch (alpha_beta_crown.py:183-260)
+
+    def _start(warm: Any, attr: str, init: float, what: str) -> List[torch.Tensor]:
+        out = []
+        wmap = getattr(warm, attr, None) if warm is not None else None
+        for r, name in enumerate(chain.relu_input_names):
+            n = chain.relu_widths[r]
+            if wmap is not None and name in wmap:
+                t, _ = _alpha_rows(wmap[name], rows, n, device, name)
+                if not per_batch_params and int(t.shape[0]) != 1:
+                    raise ValueError(f"warm start {what}[{name}] is batch-specific; expected the shared shape {tuple(chain.relu_shapes[r])}")
+                out.append(t.expand(rows, n))
+            else:
+                out.append(torch.full((rows, n), float(init), dtype=torch.float32, device=device))
+        return out
+
+    alpha0 = _start(warm_start_alpha, "alpha_by_relu_input", alpha_init, "alpha")
+    beta_start = _start(warm_start_beta, "beta_by_relu_input", beta_init, "beta")
     if linear_spec_C is None:
         n_out = 1
         for d in chain.output_shape:
             n_out *= int(d)
         linear_spec_C = torch.eye(n_out, dtype=torch.float32, device=device)
     dev = normalize_input_spec(input_spec).center.device
-    beta_start = []
-    wb_map = getattr(warm_start_beta, "beta_by_relu_input", None) if warm_start_beta is not None else None
-    for r, name in enumerate(chain.relu_input_names):
-        n = chain.relu_widths[r]
-        if wb_map is not None and name in wb_map:
-            bt, _ = _alpha_rows(wb_map[name], B, n, device, name)
-            beta_start.append(bt.expand(B, n))
-        else:
-            beta_start.append(torch.full((B, n), float(beta_init), dtype=torch.float32, device=device))
+    if spec_reduce != "mean" and not per_batch_params:
+        raise NotImplementedError("the shared-parameter loop of the CUDA backend implements spec_reduce='mean'")
+    loop = alpha_crown_from_trace if per_batch_params else shared_alpha_crown_from_trace
+    kw = {"spec_reduce": spec_reduce} if per_batch_params else {}
     if optimize_beta:
         beta_splits = [relu_split_state.get(n) for n in chain.relu_input_names]
-        best_l, best_u, best_a, _last, _metric, best_b = alpha_crown_from_trace(
-            trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce, beta_splits=beta_splits, beta0=beta_start)
+        best_l, best_u, best_a, _last, _metric, best_b = loop(
+            trace, linear_spec_C, alpha0, steps=steps, lr=lr, beta_splits=beta_splits, beta0=beta_start, **kw)
     else:
         if has_split and any(float(b.abs().max()) != 0.0 for b in beta_start):
             raise NotImplementedError("a frozen non-zero beta is not supported; pass optimize_beta=None/True")
-        best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
+        best_l, best_u, best_a, _last, _metric = loop(trace, linear_spec_C, alpha0, steps=steps, lr=lr, **kw)
         best_b = beta_start
+    if not per_batch_params:
+        bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
+        a_state = AlphaState({n: a.reshape(tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
+        b_state = BetaState({n: b.reshape(tuple(s)).to(dev) for n, b, s in zip(chain.relu_input_names, best_b, chain.relu_shapes)})
+        stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(chain.relu_input_names))
+        stats.branch_choices = branch_choices_from_trace(trace)  # type: ignore[attr-defined]
+        return bounds, a_state, b_state, stats
     bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
     a_state = AlphaState({n: a.reshape((B,) + tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
     b_state = BetaState({n: b.reshape((B,) + tuple(s)).to(dev) for n, b, s in zip(chain.relu_input_names, best_b, chain.relu_shapes)})

@@ -262,3 +262,119 @@ extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const 
   }
   return BF_OK;
 }
+
+// ---------------------------------------------------------------------------
+// shared-parameter mode: one alpha (and one beta) per neuron for every domain and spec row
+// ---------------------------------------------------------------------------
+namespace bf {
+
+struct SharedWs {
+  std::vector<float*> m, v, mb, vb, part;
+  size_t begin, bytes;  // extra region (after the per-domain layout), zero-initialised per call
+};
+
+static size_t shared_ws_layout(const bf_chain* c, int B, int S, bool with_beta, void* base, AlphaWs* ws, SharedWs* sw) {
+  const size_t base_bytes = alpha_ws_layout(c, B, S, with_beta, base, ws);
+  Carver cv(base);
+  cv.off = base_bytes;
+  SharedWs w;
+  w.begin = base_bytes;
+  const int chunks = shared_alpha_chunks(B);
+  for (size_t r = 0; r < c->relu_layers.size(); ++r) {
+    const size_t n = (size_t)c->layers[c->relu_layers[r]].n_in;
+    w.m.push_back(cv.take<float>(n));
+    w.v.push_back(cv.take<float>(n));
+    if (with_beta) {
+      w.mb.push_back(cv.take<float>(n));
+      w.vb.push_back(cv.take<float>(n));
+    }
+    w.part.push_back(cv.take<float>((size_t)chunks * n));
+  }
+  w.bytes = cv.off - base_bytes;
+  if (sw) *sw = w;
+  return cv.off;
+}
+
+}  // namespace bf
+
+extern "C" size_t bf_chain_alpha_shared_workspace_bytes(const bf_chain* chain, int B, int S, int with_beta) {
+  if (!chain || B <= 0 || S <= 0) return 0;
+  return bf::shared_ws_layout(chain, B, S, with_beta != 0, nullptr, nullptr, nullptr);
+}
+
+extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                           const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                           float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                           const int* split_strides, const float* mid, const float* rad, float* best_lower,
+                                           float* best_upper, float* best_metric, int steps, float lr, void* workspace,
+                                           size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+  const char* who = "bf_chain_alpha_crown_shared";
+  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && best_alpha && mid && rad && best_lower && workspace, BF_E_INVALID,
+             "%s: null argument", who);
+  BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL && steps >= 0, BF_E_INVALID, "%s: bad B/S/steps", who);
+  BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
+  const bool with_beta = beta != nullptr;
+  BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
+  bf::AlphaWs ws;
+  bf::SharedWs sw;
+  const size_t need = bf::shared_ws_layout(chain, B, S, with_beta, workspace, &ws, &sw);
+  BF_REQUIRE(workspace_bytes >= need, BF_E_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, workspace_bytes);
+  cudaStream_t stream = bf::as_stream(stream_);
+  const int R = (int)chain->relu_layers.size();
+  const long long M = (long long)B * S;
+  float* metric = best_metric ? best_metric : ws.metric;
+  char* wsb = static_cast<char*>(workspace);
+  // also clears the split term of ReLUs without a split (ws.addv lies inside the state region)
+  if (cudaMemsetAsync(wsb + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess ||
+      (sw.bytes && cudaMemsetAsync(wsb + sw.begin, 0, sw.bytes, stream) != cudaSuccess)) {
+    bf::set_error("%s: cudaMemsetAsync failed", who);
+    return BF_E_CUDA;
+  }
+  int rc;
+  auto width = [&](int r) { return chain->layers[chain->relu_layers[r]].n_in; };
+  auto stride = [&](int r) { return split_strides ? split_strides[r] : width(r); };
+  auto relax_all = [&](float* const* a) -> int {
+    for (int r = 0; r < R; ++r) {
+      int e = bf::launch_relu_relax(pre_l[r], pre_u[r], a[r], /*alpha_stride=*/0, ws.au[r], ws.bu[r], ws.sl[r], B, width(r), stream);
+      if (e != BF_OK) return e;
+    }
+    return BF_OK;
+  };
+  for (int t = 0; t <= steps; ++t) {
+    const bool last = (t == steps);
+    if ((rc = relax_all(alpha)) != BF_OK) return rc;
+    if (with_beta)
+      for (int r = 0; r < R; ++r)
+        if (splits[r] && (rc = bf::launch_shared_beta_add(beta[r], splits[r], stride(r), ws.addv[r], B, width(r), stream)) != BF_OK)
+          return rc;
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, mid, rad, ws.cur, B, S, stream);
+    if (rc != BF_OK) return rc;
+    if ((rc = bf::launch_shared_metric(ws.cur, M, metric, ws.improve, t == 0, stream)) != BF_OK) return rc;
+    if ((rc = bf::launch_copy_if(ws.cur, best_lower, M, ws.improve, stream)) != BF_OK) return rc;
+    bf::AdamScalars sc{};
+    if (!last) {
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, mid, rad, B, S, stream);
+      if (rc != BF_OK) return rc;
+      sc = bf::adam_scalars(t, lr, BF_REDUCE_SUM, S);
+      sc.grad_scale = -1.0f / (float)M;  // loss = -mean over every domain and spec row
+    }
+    for (int r = 0; r < R; ++r) {
+      rc = bf::launch_shared_adam(alpha[r], sw.m[r], sw.v[r], ws.grad[r], nullptr, 0, sw.part[r], ws.improve, best_alpha[r], sc,
+                                  last ? 0 : 1, 0, B, width(r), stream);
+      if (rc != BF_OK) return rc;
+      if (with_beta) {
+        // without a split on this ReLU the beta gradient is identically zero: snapshot only
+        const bool upd = !last && splits[r] != nullptr;
+        rc = bf::launch_shared_adam(beta[r], sw.mb[r], sw.vb[r], ws.gsum[r], splits[r], splits[r] ? stride(r) : 0, sw.part[r],
+                                    ws.improve, best_beta[r], sc, upd ? 1 : 0, 1, B, width(r), stream);
+        if (rc != BF_OK) return rc;
+      }
+    }
+  }
+  if (best_upper) {  // beta acts on the lower side only
+    if ((rc = relax_all(best_alpha)) != BF_OK) return rc;
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, mid, rad, best_upper, B, S, stream);
+    if (rc != BF_OK) return rc;
+  }
+  return BF_OK;
+}

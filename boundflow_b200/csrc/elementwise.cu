@@ -217,6 +217,122 @@ int launch_scale_copy(const float* src, float scale, float* dst, long long n, cu
   return BF_OK;
 }
 
+// ---- shared-alpha mode: one alpha per neuron for the whole batch ----------------
+// Whole-batch objective (mean of every lower bound) and strict best-of on one scalar.
+// A single block sums in a fixed order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(1024) shared_metric_kernel(const float* __restrict__ cur, long long M,
+                                                             float* __restrict__ best_metric, int* __restrict__ improve,
+                                                             int first) {
+  __shared__ float red[1024];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < M; i += blockDim.x) s += cur[i];
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int w = blockDim.x / 2; w > 0; w >>= 1) {
+    if ((int)threadIdx.x < w) red[threadIdx.x] += red[threadIdx.x + w];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float metric = red[0] / (float)M;
+    const bool imp = first || (metric > best_metric[0]);
+    if (imp) best_metric[0] = metric;
+    improve[0] = imp ? 1 : 0;
+  }
+}
+
+int launch_shared_metric(const float* cur, long long M, float* best_metric, int* improve, int first, cudaStream_t stream) {
+  shared_metric_kernel<<<1, 1024, 0, stream>>>(cur, M, best_metric, improve, first);
+  BF_CHECK_LAUNCH("shared_metric_kernel");
+  return BF_OK;
+}
+
+__global__ void copy_if_kernel(const float* __restrict__ src, float* __restrict__ dst, long long n, const int* __restrict__ flag) {
+  if (flag[0] == 0) return;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+int launch_copy_if(const float* src, float* dst, long long n, const int* flag, cudaStream_t stream) {
+  copy_if_kernel<<<ew_grid(n, 256), 256, 0, stream>>>(src, dst, n, flag);
+  BF_CHECK_LAUNCH("copy_if_kernel");
+  return BF_OK;
+}
+
+// Column sums of a per-domain gradient in two fixed-order stages: grid (column blocks, row chunks)
+// writes part[chunk, j] = sum over the chunk's rows of grad[b, j] (times -split[b, j] for a beta
+// gradient) and clears what it read.
+__global__ void __launch_bounds__(128) grad_colsum_kernel(float* __restrict__ grad, const int8_t* __restrict__ split,
+                                                          int split_stride, float* __restrict__ part, int B, int n,
+                                                          int rows_per_chunk) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const int b0 = blockIdx.y * rows_per_chunk;
+  const int b1 = min(B, b0 + rows_per_chunk);
+  float s = 0.f;
+  for (int b = b0; b < b1; ++b) {
+    const size_t i = (size_t)b * n + j;
+    const float g = grad[i];
+    s += split ? g * -(float)split[(size_t)b * split_stride + j] : g;
+    grad[i] = 0.f;
+  }
+  part[(size_t)blockIdx.y * n + j] = s;
+}
+
+// Adam on one shared parameter vector: alpha is projected to [0,1], beta to [0,inf).
+__global__ void __launch_bounds__(128) shared_adam_kernel(float* __restrict__ param, float* __restrict__ m, float* __restrict__ v,
+                                                          const float* __restrict__ part, int chunks,
+                                                          const int* __restrict__ improve, float* __restrict__ best,
+                                                          AdamScalars sc, int do_update, int is_beta, int n) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  float a = param[j];
+  if (improve[0] != 0) best[j] = a;
+  if (!do_update) return;
+  float g = 0.f;
+  for (int c = 0; c < chunks; ++c) g += part[(size_t)c * n + j];
+  g *= sc.grad_scale;
+  float mi = m[j], vi = v[j];
+  mi = mi + sc.one_minus_beta1 * (g - mi);
+  vi = vi * sc.beta2 + sc.one_minus_beta2 * g * g;
+  const float denom = sqrtf(vi) / sc.bc2_sqrt + sc.eps;
+  a = fmaxf(a - sc.lr_step * (mi / denom), 0.f);
+  if (!is_beta) a = fminf(a, 1.f);
+  m[j] = mi;
+  v[j] = vi;
+  param[j] = a;
+}
+
+int shared_alpha_chunks(int B) { return B < 64 ? B : 64; }
+
+int launch_shared_adam(float* param, float* m, float* v, float* grad, const int8_t* split, int split_stride, float* part,
+                       const int* improve, float* best, AdamScalars sc, int do_update, int is_beta, int B, int n,
+                       cudaStream_t stream) {
+  const int chunks = shared_alpha_chunks(B);
+  if (do_update) {
+    dim3 grid(ceil_div(n, 128), chunks);
+    grad_colsum_kernel<<<grid, 128, 0, stream>>>(grad, split, split_stride, part, B, n, ceil_div(B, chunks));
+    BF_CHECK_LAUNCH("grad_colsum_kernel");
+  }
+  shared_adam_kernel<<<ceil_div(n, 128), 128, 0, stream>>>(param, m, v, part, chunks, improve, best, sc, do_update, is_beta, n);
+  BF_CHECK_LAUNCH("shared_adam_kernel");
+  return BF_OK;
+}
+
+// Split term of a shared beta: add[b, j] = -beta[j] * split[b, j].
+__global__ void __launch_bounds__(128) shared_beta_add_kernel(const float* __restrict__ beta, const int8_t* __restrict__ split,
+                                                              int split_stride, float* __restrict__ add, int n) {
+  const int b = blockIdx.x;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  add[(size_t)b * n + j] = -beta[j] * (float)split[(size_t)b * split_stride + j];
+}
+
+int launch_shared_beta_add(const float* beta, const int8_t* split, int split_stride, float* add, int B, int n, cudaStream_t stream) {
+  dim3 grid(B, ceil_div(n, 128));
+  shared_beta_add_kernel<<<grid, 128, 0, stream>>>(beta, split, split_stride, add, n);
+  BF_CHECK_LAUNCH("shared_beta_add_kernel");
+  return BF_OK;
+}
+
 // ---- adaptive alpha start ------------------------------------------------------
 __global__ void alpha_adaptive_init_kernel(const float* __restrict__ l, const float* __restrict__ u, float* __restrict__ alpha,
                                            long long total) {

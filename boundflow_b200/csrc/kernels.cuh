@@ -60,6 +60,14 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
                      const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
                      cudaStream_t stream);
 int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream);
+// shared-alpha mode (one alpha per neuron for the whole batch)
+int launch_shared_metric(const float* cur, long long M, float* best_metric, int* improve, int first, cudaStream_t stream);
+int launch_copy_if(const float* src, float* dst, long long n, const int* flag, cudaStream_t stream);
+int shared_alpha_chunks(int B);
+int launch_shared_adam(float* param, float* m, float* v, float* grad, const int8_t* split, int split_stride, float* part,
+                       const int* improve, float* best, AdamScalars sc, int do_update, int is_beta, int B, int n,
+                       cudaStream_t stream);
+int launch_shared_beta_add(const float* beta, const int8_t* split, int split_stride, float* add, int B, int n, cudaStream_t stream);
 // beta parameters: snapshot, Adam step with gradient -split * gsum * grad_scale, projection to >= 0,
 // and the next split term add = -beta * split (split in {-1,0,+1}; entries with split == 0 never move)
 int launch_beta_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride, const int* improve,

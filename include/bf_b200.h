@@ -336,6 +336,31 @@ int bf_chain_alpha_grad(const bf_chain* chain,
                         float* const* grad, float* lower, int spec_reduce,
                         void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
+/* alpha(-beta)-CROWN with ONE alpha (and one beta) per neuron shared by every domain and spec row:
+ * replaces run_alpha_crown_mlp, boundflow/runtime/alpha_crown.py:137-261, and the shared-parameter
+ * mode (per_batch_params=False) of run_alpha_beta_crown_mlp, boundflow/runtime/alpha_beta_crown.py:643-941,
+ * for objective="lower", spec_reduce="mean".  steps+1 lower sweeps at the broadcast parameters;
+ * loss = -mean over all B*S lower bounds; gradient = column sums over the batch of the per-domain
+ * adjoint gradient (two fixed-order stages; beta: of -split * sum_s g); Adam; alpha clamped to [0,1],
+ * beta to >= 0; strict best-of on the scalar metric, which keeps the whole batch's bounds and the
+ * parameters of the best iteration.
+ * alpha / best_alpha (and beta / best_beta, or NULL for alpha only): HOST arrays of device pointers
+ * [n_r], updated in place; splits: HOST array of int8 device pointers [B,n_r] (row stride
+ * split_strides[r], 0 = one shared row) or NULL entries, needed with beta; best_lower [B,S];
+ * best_upper [B,S] or NULL (one upper sweep at the best alpha); best_metric: device float[1] or NULL.
+ * Workspace: bf_chain_alpha_shared_workspace_bytes(chain, B, S, with_beta). */
+size_t bf_chain_alpha_shared_workspace_bytes(const bf_chain* chain, int B, int S, int with_beta);
+int bf_chain_alpha_crown_shared(const bf_chain* chain,
+                                const float* C,
+                                const float* const* pre_l, const float* const* pre_u,
+                                float* const* alpha, float* const* best_alpha,
+                                float* const* beta, float* const* best_beta,
+                                const int8_t* const* splits, const int* split_strides,
+                                const float* mid, const float* rad,
+                                float* best_lower, float* best_upper, float* best_metric,
+                                int steps, float lr,
+                                void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

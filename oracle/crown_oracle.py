@@ -535,6 +535,60 @@ def alpha_crown(
     return best_lower, best_upper, best_alpha, trace
 
 
+def alpha_crown_shared(layers: Layers, inp: InputSet, C, *, steps: int, lr: float, alpha0: Optional[Sequence[torch.Tensor]] = None,
+                       alpha_init: float = 0.5, splits=None, trace: Optional[ForwardTrace] = None, optimize_beta: bool = False):
+    """alpha (and optionally beta) shared by every domain and spec row: `run_alpha_crown_mlp`
+    (alpha_crown.py:137-261) and the `per_batch_params=False` mode of `run_alpha_beta_crown_mlp`
+    (alpha_beta_crown.py:716-923), restated for objective="lower", spec_reduce="mean".
+    Parameters have the ReLU input's shape without the batch axis (alpha start `alpha_init`,
+    beta start 0); steps+1 evaluations; metric = mean over all lower bounds; strict best-of on
+    that scalar keeps the whole batch's bounds and parameters (alpha_crown.py:215-220,
+    alpha_beta_crown.py:877-903); loss = -metric (alpha_beta_crown.py:913), torch Adam, alpha
+    clamped to [0,1], beta to >= 0.  Returns best (lower, upper), best alpha list, trace and,
+    with `optimize_beta`, the best beta list before the trace."""
+    if trace is None:
+        trace = forward_ibp_trace(layers, inp, splits=splits)
+    B = inp.mid.shape[0]
+    dtype = inp.mid.dtype
+    alphas, betas, split_f = [], [], []
+    for r, (l, _u) in enumerate(trace.pre):
+        n = l.reshape(B, -1).shape[1]
+        a = alpha0[r].reshape(n).to(dtype).clone() if alpha0 is not None else torch.full((n,), float(alpha_init), dtype=dtype)
+        alphas.append(a.requires_grad_(True))
+        if optimize_beta:
+            betas.append(torch.zeros(n, dtype=dtype, requires_grad=True))
+            sp = splits[r] if (splits is not None and splits[r] is not None) else None
+            split_f.append(None if sp is None else sp.reshape(-1, n).expand(B, n).to(dtype))
+    opt = torch.optim.Adam(alphas + betas, lr=float(lr)) if alphas else None
+    best_metric = None
+    best = None
+    for step in range(int(steps) + 1):
+        add_l = None
+        if optimize_beta:
+            add_l = [None if sf is None else -bt.unsqueeze(0) * sf for bt, sf in zip(betas, split_f)]
+        lower, upper = crown_backward(layers, inp, trace, C, alpha=[a.unsqueeze(0).expand(B, -1) for a in alphas], add_l=add_l)
+        metric = lower.mean(dim=1).mean() if lower.dim() == 2 else lower.mean()
+        if best_metric is None or float(metric.detach()) > best_metric:
+            best_metric = float(metric.detach())
+            best = (lower.detach().clone(), upper.detach().clone(), [a.detach().clone() for a in alphas], [b.detach().clone() for b in betas])
+        if step == int(steps) or opt is None:
+            break
+        loss = -metric
+        if not loss.requires_grad:
+            break
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        with torch.no_grad():
+            for a in alphas:
+                a.clamp_(0.0, 1.0)
+            for b in betas:
+                b.clamp_(0.0)
+    if optimize_beta:
+        return best[0], best[1], best[2], best[3], trace
+    return best[0], best[1], best[2], trace
+
+
 def branch_choices(trace: ForwardTrace) -> List[Optional[Tuple[int, int]]]:
     """Widest-unstable-gap branching hint, `_branch_choices_from_relu_pre`
     (alpha_beta_crown.py:145-182): per domain the (ReLU index, neuron index) with the largest

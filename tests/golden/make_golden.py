@@ -147,13 +147,60 @@ def gen_lp_ball() -> None:
     save("lp_ball.npz", **out)
 
 
+def gen_shared_alpha() -> None:
+    """`run_alpha_crown_mlp` (alpha shared across the batch) on the c3 MLP and on split c4 domains."""
+    from boundflow.runtime.alpha_crown import run_alpha_crown_mlp
+
+    out = {}
+    wl = W.make_workload("c3", batch=8)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    b, st, _ = run_alpha_crown_mlp(ref_module(wl), spec, linear_spec_C=wl.C, steps=10, lr=0.1)
+    out["c3_input_checksum"] = checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])
+    out["c3_lower"], out["c3_upper"] = b.lower, b.upper
+    for n in wl.relu_names:
+        out[f"c3_alpha_{n}"] = st.alpha_by_relu_input[n]
+    b1, _st1, _ = run_alpha_crown_mlp(ref_module(wl), spec, linear_spec_C=wl.C, steps=1, lr=0.1)
+    out["c3_lower_1step"], out["c3_upper_1step"] = b1.lower, b1.upper
+
+    wl = W.make_workload("c4")
+    root_spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _, root_pre = _forward_ibp_trace_mlp(ref_module(wl), root_spec)
+    D = 24
+    splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
+    lo, up = wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous()
+    spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+    state = {n: s for n, s in zip(wl.relu_names, splits)}
+    C = wl.C.expand(D, -1, -1).contiguous()
+    b, st, _ = run_alpha_crown_mlp(ref_module(wl), spec, linear_spec_C=C, steps=10, lr=0.1, relu_split_state=state)
+    out["c4_input_checksum"] = checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])
+    out["c4_split_checksum"] = np.array([int(s.to(torch.int64).abs().sum()) for s in splits])
+    out["c4_lower"], out["c4_upper"] = b.lower, b.upper
+    for n in wl.relu_names:
+        out[f"c4_alpha_{n}"] = st.alpha_by_relu_input[n][::5]
+    # shared alpha AND beta: the reference's alpha-beta function in its default shared-parameter mode
+    ab, ab_a, ab_b, _ = run_alpha_beta_crown_mlp(
+        ref_module(wl), spec, linear_spec_C=C, relu_split_state=state, steps=10, lr=0.1, per_batch_params=False,
+        objective="lower", spec_reduce="mean")
+    out["c4_ab_lower"], out["c4_ab_upper"] = ab.lower, ab.upper
+    for n in wl.relu_names:
+        out[f"c4_ab_alpha_{n}"] = ab_a.alpha_by_relu_input[n][::5]
+        out[f"c4_ab_beta_{n}"] = ab_b.beta_by_relu_input[n]
+    ab1, _a1, _b1, _ = run_alpha_beta_crown_mlp(
+        ref_module(wl), spec, linear_spec_C=C, relu_split_state=state, steps=1, lr=0.1, per_batch_params=False,
+        objective="lower", spec_reduce="mean")
+    out["c4_ab_lower_1step"], out["c4_ab_upper_1step"] = ab1.lower, ab1.upper
+    save("shared_alpha.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
-    if len(sys.argv) > 2 and sys.argv[2] == "lp_ball":  # regenerate this one file only
-        gen_lp_ball()
+    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha}
+    if len(sys.argv) > 2:  # regenerate one file only
+        only[sys.argv[2]]()
         return
     gen_lp_ball()
+    gen_shared_alpha()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

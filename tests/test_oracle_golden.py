@@ -211,3 +211,51 @@ def test_lp_ball_inputs(golden):
             assert_close(trace.out[1], g[f"{tag}_{pname}_ibp_upper"], f"{tag} {pname} ibp upper")
             assert_close(lower, g[f"{tag}_{pname}_crown_lower"], f"{tag} {pname} crown lower")
             assert_close(upper, g[f"{tag}_{pname}_crown_upper"], f"{tag} {pname} crown upper")
+
+
+def test_shared_alpha(golden):
+    """`run_alpha_crown_mlp`: one alpha per neuron for the whole batch, whole-batch best-of."""
+    g = golden("shared_alpha.npz")
+    wl = W.make_workload("c3", batch=8)
+    assert np.allclose(workload_checksum(wl), g["c3_input_checksum"], rtol=1e-12, atol=0)
+    inp = O.box_input(wl.lo, wl.up)
+    lo1, up1, _a1, _ = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=1, lr=0.1)
+    assert_close(lo1, g["c3_lower_1step"], "c3 one-step lower")
+    assert_close(up1, g["c3_upper_1step"], "c3 one-step upper")
+    lo, up, a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=10, lr=0.1)
+    # the optimised trajectory amplifies rounding (see test_c3_alpha): relative tolerance 3e-4
+    assert_close(lo, g["c3_lower"], "c3 lower", rtol=3e-4)
+    assert_close(up, g["c3_upper"], "c3 upper", rtol=3e-4)
+    for r, n in enumerate(wl.relu_names):
+        assert float((a[r] - torch.as_tensor(g[f"c3_alpha_{n}"]).reshape(-1)).abs().mean()) < 2e-3
+
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 24
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    assert (np.array([int(s.to(torch.int64).abs().sum()) for s in splits]) == g["c4_split_checksum"]).all()
+    inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+    lo, up, a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C.expand(D, -1, -1), steps=10, lr=0.1, splits=splits)
+    assert_close(lo, g["c4_lower"], "c4 lower", rtol=3e-4)
+    assert_close(up, g["c4_upper"], "c4 upper", rtol=3e-4)
+
+
+def test_shared_alpha_beta(golden):
+    """`run_alpha_beta_crown_mlp(per_batch_params=False)`: shared alpha and beta on split c4 domains."""
+    g = golden("shared_alpha.npz")
+    wl = W.make_workload("c4")
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    D = 24
+    splits = W.make_split_domains(wl, root.pre, n_domains=D)
+    inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+    C = wl.C.expand(D, -1, -1)
+    lo1, up1, _a, _b, _ = O.alpha_crown_shared(wl.layers, inp, C, steps=1, lr=0.1, splits=splits, optimize_beta=True)
+    assert_close(lo1, g["c4_ab_lower_1step"], "one-step lower", rtol=3e-5)
+    assert_close(up1, g["c4_ab_upper_1step"], "one-step upper", rtol=3e-5)
+    lo, up, a, b, _ = O.alpha_crown_shared(wl.layers, inp, C, steps=10, lr=0.1, splits=splits, optimize_beta=True)
+    assert_close(lo, g["c4_ab_lower"], "lower", rtol=3e-4)
+    assert_close(up, g["c4_ab_upper"], "upper", rtol=3e-4)
+    for r, n in enumerate(wl.relu_names):
+        ref_b = torch.as_tensor(g[f"c4_ab_beta_{n}"]).reshape(-1)
+        assert float(b[r].min()) >= 0.0
+        assert float((b[r] - ref_b).abs().max()) <= 0.05
