@@ -323,16 +323,25 @@ def crown_from_trace(
     relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
     sides: Sequence[int] = (_lib.SIDE_LOWER, _lib.SIDE_UPPER),
+    identity_rows: Optional[Tuple[int, int]] = None,
 ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
-    """Backward sweep(s) on the device; returns (lower, upper) [B,S] CUDA tensors."""
+    """Backward sweep(s) on the device; returns (lower, upper) [B,S] CUDA tensors.
+    `identity_rows=(first, count)` stands for the spec whose rows are rows first..first+count-1 of
+    the identity (neuron-wise bounds of `output_value`); no spec tensor is built for it."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
     upto = chain.layers_upto(output_value)
     out_shape = chain.layers[upto - 1].out_shape
     out_dim = 1
     for d in out_shape:
         out_dim *= int(d)
-    C = _expand_spec(linear_spec_C, B, out_dim, device)
-    S = int(C.shape[1])
+    if identity_rows is not None:
+        first, S = int(identity_rows[0]), int(identity_rows[1])
+        if first < 0 or S <= 0 or first + S > out_dim:
+            raise ValueError(f"identity_rows {identity_rows} outside the value's {out_dim} neurons")
+        C = None
+    else:
+        C = _expand_spec(linear_spec_C, B, out_dim, device)
+        S = int(C.shape[1])
     n_relu = sum(1 for i in chain.relu_layer_ids if i < upto)
     au, bu, al, keep = _relaxations(trace, relu_alpha, n_relu)
     add = None
@@ -350,14 +359,15 @@ def crown_from_trace(
     outs: List[Optional[torch.Tensor]] = [None, None]
     for side in sides:
         out = torch.empty(B, S, dtype=torch.float32, device=device)
-        _lib.check(
-            chain.lib.bf_chain_crown(
-                chain.handle, upto, side, _lib.ptr(C),
-                _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add),
-                _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
-                _lib.ptr(out), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
-            )
+        tail = (
+            _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
+            _lib.ptr(out), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
+        if C is None:
+            _lib.check(chain.lib.bf_chain_crown_onehot(chain.handle, upto, side, first, *tail))
+        else:
+            _lib.check(chain.lib.bf_chain_crown(chain.handle, upto, side, _lib.ptr(C), *tail))
         outs[side] = out
     return outs[0], outs[1]
 
@@ -738,24 +748,27 @@ def run_crown_intermediate_mlp(
     trace = ibp_trace(module, input_spec)
     chain, B, device = trace.chain, trace.B, trace.mid.device
     names = chain.relu_input_names
-    cons = {n: IntervalState(lower=l, upper=u) for n, l, u in zip(names, trace.pre_l, trace.pre_u)}
+
+    def _state(k: int, l: torch.Tensor, u: torch.Tensor) -> IntervalState:
+        shape = (B,) + tuple(chain.relu_shapes[k])
+        return IntervalState(lower=l.reshape(shape), upper=u.reshape(shape))
+
     for r, name in enumerate(names):
         if r == 0:
             continue  # the first pre-activation's CROWN bound is its IBP bound
         n = chain.relu_widths[r]
         new_l = torch.empty(B, n, dtype=torch.float32, device=device)
         new_u = torch.empty(B, n, dtype=torch.float32, device=device)
-        eye = torch.eye(n, dtype=torch.float32, device=device)
         for s in range(0, n, int(chunk_rows)):
-            lo, up = crown_from_trace(trace, eye[s : s + int(chunk_rows)], output_value=name)
-            new_l[:, s : s + lo.shape[1]] = lo
-            new_u[:, s : s + up.shape[1]] = up
-        shape = (B,) + tuple(chain.relu_shapes[r])
-        cons[name] = IntervalState(lower=torch.maximum(trace.pre_l[r], new_l).reshape(shape), upper=torch.minimum(trace.pre_u[r], new_u).reshape(shape))
-        for k, nm in enumerate(names):
-            if k != r:
-                cons[nm] = IntervalState(lower=trace.pre_l[k].reshape((B,) + tuple(chain.relu_shapes[k])), upper=trace.pre_u[k].reshape((B,) + tuple(chain.relu_shapes[k])))
-        trace = ibp_trace(module, input_spec, relu_pre_constraints={nm: cons[nm] for nm in names})
+            cnt = min(int(chunk_rows), n - s)
+            lo, up = crown_from_trace(trace, None, output_value=name, identity_rows=(s, cnt))
+            new_l[:, s : s + cnt].copy_(lo)
+            new_u[:, s : s + cnt].copy_(up)
+        # the IBP sweep intersects every pre-activation with its constraint (max of the lower, min of the upper
+        # bounds), so handing it the new bounds of this ReLU and the current bounds of the others is the
+        # reference's intersect-then-re-propagate step
+        cons = {nm: _state(k, new_l, new_u) if k == r else _state(k, trace.pre_l[k], trace.pre_u[k]) for k, nm in enumerate(names)}
+        trace = ibp_trace(module, input_spec, relu_pre_constraints=cons)
         _raise_if_infeasible(trace, "ReLU pre-activation intersection")
     lo, up = crown_from_trace(trace, linear_spec_C)
     dev = normalize_input_spec(input_spec).center.device

@@ -157,6 +157,10 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
                             const float* W, const float* bias, float* A_prev, float* delta, int accumulate, int M, int S,
                             const bf_layer_desc& L, void* scratch, cudaStream_t stream);
 size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L);
+int launch_onehot_conv_rows(int first, const float* W, const float* bias, float* A_prev, float* delta, int M, int S,
+                            const bf_layer_desc& L, cudaStream_t stream);
+int launch_onehot_linear_rows(int first, const float* W, const float* bias, float* A_prev, float* delta, int M, int S, int n_in,
+                              cudaStream_t stream);
 }  // namespace bf
 
 // ---------------------------------------------------------------------------
@@ -391,11 +395,13 @@ extern "C" size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, i
   return bf::crown_ws_layout(chain, B, S, upto_layer, nullptr, nullptr);
 }
 
-extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, const float* C,
-                              const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
-                              const float* const* add, const float* mid, const float* rad, int norm_p, float eps, float* out,
-                              void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
-  BF_REQUIRE(chain && C && mid && out && workspace, BF_E_INVALID, "bf_chain_crown: null argument");
+// One sweep; `C` dense [B,S,width of the bounded value], or NULL with onehot_first >= 0: the spec rows are rows
+// onehot_first .. onehot_first+S-1 of the identity for every domain.
+static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const float* C, int onehot_first,
+                       const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                       const float* const* add, const float* mid, const float* rad, int norm_p, float eps, float* out,
+                       void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+  BF_REQUIRE(chain && (C || onehot_first >= 0) && mid && out && workspace, BF_E_INVALID, "bf_chain_crown: null argument");
   BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
              "bf_chain_crown: bad norm");
   BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "bf_chain_crown: a box needs its radius tensor");
@@ -435,7 +441,16 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
       if (add && add[pending] && side == BF_SIDE_LOWER) ad = add[pending];
     }
     int rc;
-    if (L.op == BF_OP_LINEAR) {
+    if (curA == nullptr) {
+      // identity spec rows: the first backward step copies weights instead of multiplying by them
+      BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown_onehot: the bounded value must be the output of an affine layer");
+      BF_REQUIRE(onehot_first + S <= L.n_out, BF_E_INVALID, "bf_chain_crown_onehot: rows %d..%d exceed the value's width %d",
+                 onehot_first, onehot_first + S - 1, L.n_out);
+      float* dst = ws.buf[toggle];
+      if (L.op == BF_OP_LINEAR) rc = bf::launch_onehot_linear_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L.n_in, stream);
+      else rc = bf::launch_onehot_conv_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L, stream);
+      curA = dst;
+    } else if (L.op == BF_OP_LINEAR) {
       const bool last = box && (i == low);  // the fused concretisation handles boxes; Lp balls concretise separately
       float* dst = last ? nullptr : ws.buf[toggle];
       rc = bf::dispatch_bwd(chain, i, curA, dpos, dneg, epos, eneg, ad, dst, ws.cacc, have_c, last ? mid : nullptr,
@@ -458,5 +473,23 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
   if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
   if (!box) return bf::launch_concretize_lp(curA, mid, have_c ? ws.cacc : nullptr, out, side, eps, norm_p, B, S, chain->n0, stream);
   return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
+}
+
+extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, const float* C,
+                              const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                              const float* const* add, const float* mid, const float* rad, int norm_p, float eps, float* out,
+                              void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  BF_REQUIRE(C, BF_E_INVALID, "bf_chain_crown: null argument");
+  return crown_sweep(chain, upto_layer, side, C, -1, alpha_u, beta_u, alpha_l, add, mid, rad, norm_p, eps, out, workspace,
+                     workspace_bytes, B, S, stream);
+}
+
+extern "C" int bf_chain_crown_onehot(const bf_chain* chain, int upto_layer, int side, int first_row,
+                                     const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                                     const float* const* add, const float* mid, const float* rad, int norm_p, float eps,
+                                     float* out, void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  BF_REQUIRE(first_row >= 0, BF_E_INVALID, "bf_chain_crown_onehot: negative first row");
+  return crown_sweep(chain, upto_layer, side, nullptr, first_row, alpha_u, beta_u, alpha_l, add, mid, rad, norm_p, eps, out,
+                     workspace, workspace_bytes, B, S, stream);
 }
 

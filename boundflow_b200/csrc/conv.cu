@@ -89,22 +89,56 @@ int launch_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, int rel
 }
 
 // ---------------------------------------------------------------------------
-// ReLU backward on coefficient rows (one warp per row), used in front of the
-// transposed convolution:  Lam = A * slope_sel ; delta (+)= sum A*icpt_sel + Lam*bias[channel]
+// ReLU backward on coefficient rows, in front of the transposed convolution:
+//   Lam = A * slope_sel ;  delta (+)= sum_k A*icpt_sel + Lam*bias[channel]
+// grid (row, column chunk): a block streams RELU_ROWS_CHUNK columns of one row
+// and leaves one partial sum (fixed summation order); sum_partials_kernel adds
+// the chunks of a row.
 // ---------------------------------------------------------------------------
+constexpr int RELU_ROWS_CHUNK = 4096;
+
 __global__ void __launch_bounds__(256) relu_bwd_rows_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
                                                             const float* __restrict__ dneg, const float* __restrict__ epos,
                                                             const float* __restrict__ eneg, const float* __restrict__ bias,
-                                                            int chan_size, float* __restrict__ Lam, float* __restrict__ delta,
-                                                            int accumulate, int M, int S, int n) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int m = warp; m < M; m += nwarps) {
-    const float* a = A + (size_t)m * n;
-    const size_t off = (size_t)(m / S) * n;
-    float acc = 0.f;
-    for (int k = lane; k < n; k += 32) {
+                                                            int chan_size, float* __restrict__ Lam, float* __restrict__ partial,
+                                                            float* __restrict__ delta, int accumulate, int chunk, int S, int n,
+                                                            int vec) {
+  const int m = blockIdx.x;
+  const int k0 = blockIdx.y * chunk;
+  const int k1 = min(n, k0 + chunk);
+  const float* a = A + (size_t)m * n;
+  const size_t off = (size_t)(m / S) * n;
+  float acc = 0.f;
+  if (vec) {  // n % 4 == 0 and 16-byte aligned rows: four columns per access
+    for (int k = k0 + 4 * (int)threadIdx.x; k < k1; k += 4 * 256) {
+      const float4 v4 = *reinterpret_cast<const float4*>(a + k);
+      float v[4] = {v4.x, v4.y, v4.z, v4.w};
+      float lam[4] = {v4.x, v4.y, v4.z, v4.w};
+      if (dpos) {
+        const float4 p4 = *reinterpret_cast<const float4*>(dpos + off + k), n4 = *reinterpret_cast<const float4*>(dneg + off + k);
+        const float p[4] = {p4.x, p4.y, p4.z, p4.w}, q[4] = {n4.x, n4.y, n4.z, n4.w};
+        float ep[4] = {0.f, 0.f, 0.f, 0.f}, en[4] = {0.f, 0.f, 0.f, 0.f};
+        if (epos) { const float4 e4 = *reinterpret_cast<const float4*>(epos + off + k); ep[0] = e4.x; ep[1] = e4.y; ep[2] = e4.z; ep[3] = e4.w; }
+        if (eneg) { const float4 e4 = *reinterpret_cast<const float4*>(eneg + off + k); en[0] = e4.x; en[1] = e4.y; en[2] = e4.z; en[3] = e4.w; }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const bool sel = v[c] >= 0.f;
+          lam[c] = v[c] * (sel ? p[c] : q[c]);
+          acc = fmaf(v[c], sel ? ep[c] : en[c], acc);
+        }
+      }
+      if (bias) {
+        int ch = k / chan_size, rem = k - ch * chan_size;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          acc = fmaf(lam[c], __ldg(bias + ch), acc);
+          if (++rem == chan_size) { rem = 0; ++ch; }
+        }
+      }
+      if (Lam) *reinterpret_cast<float4*>(Lam + (size_t)m * n + k) = make_float4(lam[0], lam[1], lam[2], lam[3]);
+    }
+  } else {
+    for (int k = k0 + (int)threadIdx.x; k < k1; k += 256) {
       const float v = a[k];
       float lam = v;
       if (dpos) {
@@ -116,9 +150,19 @@ __global__ void __launch_bounds__(256) relu_bwd_rows_kernel(const float* __restr
       if (bias) acc = fmaf(lam, __ldg(bias + k / chan_size), acc);
       if (Lam) Lam[(size_t)m * n + k] = lam;
     }
+  }
+  if (!partial && !delta) return;
+  __shared__ float red[8];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0 && delta) delta[m] = accumulate ? (delta[m] + acc) : acc;
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w];
+    if (partial) partial[(size_t)m * gridDim.y + blockIdx.y] = t;   // several chunks per row: summed by sum_partials_kernel
+    else delta[m] = accumulate ? (delta[m] + t) : t;                // one block per row
   }
 }
 
@@ -198,7 +242,297 @@ __global__ void __launch_bounds__(256) conv_transpose_rows_kernel(ConvTArgs g) {
   }
 }
 
-size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L) { return (size_t)M * L.n_out * sizeof(float); }
+// ---------------------------------------------------------------------------
+// Transposed convolution, row-segment form, for square kernels with equal stride and padding
+// in both directions (KS, ST, PD compile-time).  A thread owns a segment of 16 consecutive
+// input-image pixels of one image row for TCI input channels (16*TCI accumulators).  The lanes
+// of a warp are 32 different segments (image rows, or rows of further coefficient rows when the
+// image is small) of the same channel group: a coefficient read is one conflict-free 16-byte
+// word per lane, a weight read is a broadcast.  Per output channel and kernel row a thread loads
+// the NL coefficient words its segment can touch and the KS*TCI weights, and does
+// 16*KS*TCI/ST multiply-adds on registers (all indices compile-time).  The block stages, per
+// chunk of cc output channels, the zero-padded coefficient tiles [MR][cc][LH][NLT] and the weights
+// [cc][KS*KS][CIB] with cp.async into one of two buffers while it computes on the other.
+// ---------------------------------------------------------------------------
+// VEC: the coefficient tile starts on a 16-byte boundary of the image row (SH extra columns on the
+// left) so that it can be staged with 16-byte copies; needs Wo % 4 == 0.
+template <int KS, int ST, int PD, bool VEC>
+struct RowSeg {
+  static constexpr int TW = 16;                               // pixels per thread
+  static constexpr int C0 = (KS - 1 - PD + ST - 1) / ST;       // coefficient columns left of the segment's first pixel
+  static constexpr int SH = VEC ? ((C0 + 3) / 4 * 4 - C0) : 0;
+  static constexpr int C0E = C0 + SH;
+  static constexpr int NL = (((TW - 1 + PD) / ST + C0E + 1) + 3) / 4 * 4;
+  static constexpr int Q0 = SH / 4;                           // first 16-byte word of a row that holds a needed column
+  static_assert(PD <= KS - 1 && TW % ST == 0 && (TW / ST) % 4 == 0, "unsupported geometry");
+  // row pitch: a multiple of 4 words whose count of 16-byte words is odd, so that the 16-byte reads of
+  // eight consecutive tile rows (a quarter warp) fall into different bank groups
+  __host__ __device__ static int tile_w(int sx) {
+    const int w4 = (((TW * sx - 1 + PD) / ST + C0E + 1) + 3) / 4;
+    return 4 * (w4 | 1);
+  }
+  __host__ __device__ static int tile_h(int th) { return (th - 1 + PD) / ST + C0 + 1; }
+};
+
+struct RowSegArgs {
+  ConvTArgs c;
+  int sxl;      // log2 of the 16-pixel segments per image row in a block
+  int thl;      // log2 of the image rows per block
+  int mrl;      // log2 of the coefficient rows per block  (2^(sxl+thl+mrl) segments = 256 / channel groups)
+  int cigl;     // log2 of the channel groups per block (TCI channels each)
+  int cc;       // output channels staged per chunk (divides Co)
+  int tiles_x, tiles_y;
+  int rowl;     // log2 of the threads that copy one coefficient-tile row while staging
+};
+
+// Asynchronous global->shared copies; `ok == false` writes zeros instead (src is not read).
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gsrc, bool ok) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int bytes = ok ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_f32x4(float* smem_dst, const float* gsrc, bool ok) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int bytes = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int KS, int ST, int PD, int TCI, bool VEC>
+__global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_kernel(RowSegArgs a) {
+  using G = RowSeg<KS, ST, PD, VEC>;
+  extern __shared__ __align__(16) float rs_smem[];
+  const ConvTArgs& g = a.c;
+  const int sx = 1 << a.sxl, th = 1 << a.thl, MR = 1 << a.mrl;
+  const int cibl = a.cigl + (TCI == 4 ? 2 : 0);
+  const int cib = 1 << cibl;                             // input channels per block
+  const int cc = a.cc;
+  const int LH = G::tile_h(th), NLT = G::tile_w(sx);
+  const int tile = LH * NLT;
+  const int nrows = MR * cc * LH;                        // coefficient-tile rows per chunk
+  const int lam_words = nrows * NLT;                     // [MR][cc][LH][NLT]
+  const int w_words = cc * KS * KS * cib;                // [cc][KS*KS][cib]
+  const int buf_words = lam_words + w_words;
+  constexpr int ROW_ZERO = -2147483647 - 1;
+  int* row_off = reinterpret_cast<int*>(rs_smem + 2 * buf_words);  // [nrows] source offset of each tile row, ROW_ZERO: all zeros
+  const int m0 = blockIdx.x << a.mrl;
+  const int h0 = (blockIdx.y / a.tiles_x) << a.thl;
+  const int w0 = (blockIdx.y % a.tiles_x) * (G::TW * sx);
+  const int ci0 = blockIdx.z << cibl;
+  const int nsegl = a.sxl + a.thl + a.mrl;
+  const int seg = threadIdx.x & ((1 << nsegl) - 1);
+  const int cig = threadIdx.x >> nsegl;
+  const int hi = h0 + (seg & (th - 1));                 // lanes of a warp: consecutive image rows
+  const int colseg = (seg >> a.thl) & (sx - 1);
+  const int mr = seg >> (a.sxl + a.thl);
+  const int ho_lo = h0 / ST - G::C0;
+  const int wo_lo = w0 / ST - G::C0E;
+  const int howo = g.Ho * g.Wo;
+  const size_t lam_row = (size_t)g.Co * howo;
+  const bool row_ok = hi < g.Hi && (w0 + colseg * G::TW) < g.Wi && (m0 + mr) < g.M;
+
+  // source offset (floats, relative to the block's first coefficient row and the chunk's first output channel)
+  for (int row = threadIdx.x; row < nrows; row += 256) {
+    const int hl = row % LH, cm = row / LH;
+    const int co = cm % cc, smr = cm / cc;
+    const int ho = ho_lo + hl;
+    const bool ok = (m0 + smr < g.M) && ho >= 0 && ho < g.Ho;
+    row_off[row] = ok ? (int)(smr * lam_row) + co * howo + ho * g.Wo + wo_lo : ROW_ZERO;
+  }
+  __syncthreads();
+
+  // staging: 2^rowl threads copy one tile row (16-byte words when VEC), 256 >> rowl rows per step
+  const int rsub = threadIdx.x & ((1 << a.rowl) - 1);
+  const int rrow = threadIdx.x >> a.rowl;
+  const int rstep = 256 >> a.rowl;
+  const int jcol = VEC ? 4 * rsub : rsub;
+  const bool col_in = jcol < NLT;
+  const bool col_ok = col_in && (wo_lo + jcol) >= 0 && (wo_lo + jcol) < g.Wo;  // VEC: words are all-in or all-out (Wo % 4 == 0)
+  const float* lam_base = g.Lam + (size_t)m0 * lam_row;
+  // weights: thread -> fixed input channel, walks (output channel, tap)
+  const int wci = threadIdx.x & (cib - 1);
+  const int wq0 = threadIdx.x >> cibl;
+  const int wqstep = 256 >> cibl;
+  const bool wci_ok = ci0 + wci < g.Ci;
+  const float* w_base = g.W + (size_t)(ci0 + wci) * (KS * KS);
+  auto stage = [&](int buf, int co0) {
+    float* lamS = rs_smem + buf * buf_words;
+    float* wS = lamS + lam_words;
+    if (col_in) {
+      const float* src0 = lam_base + (size_t)co0 * howo + jcol;
+      for (int row = rrow; row < nrows; row += rstep) {
+        const int off = row_off[row];
+        const bool ok = col_ok && off != ROW_ZERO;
+        if (VEC) cp_async_f32x4(lamS + row * NLT + jcol, ok ? src0 + off : g.Lam, ok);
+        else cp_async_f32(lamS + row * NLT + jcol, ok ? src0 + off : g.Lam, ok);
+      }
+    }
+    for (int q = wq0; q < cc * KS * KS; q += wqstep) {
+      const int co = q / (KS * KS);
+      cp_async_f32(wS + q * cib + wci, wci_ok ? w_base + (size_t)((co0 + co) * g.Ci) * (KS * KS) + (q - co * (KS * KS)) : g.W, wci_ok);
+    }
+    cp_async_commit();
+  };
+
+  float acc[TCI][G::TW];
+#pragma unroll
+  for (int c = 0; c < TCI; ++c)
+#pragma unroll
+    for (int i = 0; i < G::TW; ++i) acc[c][i] = 0.f;
+
+  // kernel rows this image row meets: r = r_first + ST * jr (jr < JR, r < KS); they map to tile rows hl_top - jr
+  constexpr int JR = (KS + ST - 1) / ST;
+  const int r_first = (hi + PD) % ST;
+  const int hl_top = (hi + PD - r_first) / ST - ho_lo;
+  const int lam_thread = (mr * cc * LH + hl_top) * NLT + colseg * (G::TW / ST);
+  const int w_thread = r_first * KS * cib + cig * TCI;
+
+  stage(0, 0);
+  int buf = 0;
+  for (int co0 = 0; co0 < g.Co; co0 += cc, buf ^= 1) {
+    const bool more = co0 + cc < g.Co;
+    if (more) {
+      stage(buf ^ 1, co0 + cc);  // the other buffer was released by the barrier that ended the previous iteration
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (row_ok) {
+      const float* lam_t = rs_smem + buf * buf_words + lam_thread;
+      const float* w_t = rs_smem + buf * buf_words + lam_words + w_thread;
+      for (int co = 0; co < cc; ++co) {
+        const float* lam_co = lam_t + co * tile;
+        const float* w_co = w_t + co * (KS * KS) * cib;
+#pragma unroll
+        for (int jr = 0; jr < JR; ++jr) {
+          if (KS % ST != 0 && r_first + ST * jr >= KS) break;
+          float w[KS][TCI];
+#pragma unroll
+          for (int sct = 0; sct < KS; ++sct) {
+            if (TCI == 4) {
+              const float4 w4 = *reinterpret_cast<const float4*>(w_co + (jr * ST * KS + sct) * cib);
+              w[sct][0] = w4.x; w[sct][1 % TCI] = w4.y; w[sct][2 % TCI] = w4.z; w[sct][3 % TCI] = w4.w;
+            } else {
+#pragma unroll
+              for (int c = 0; c < TCI; ++c) w[sct][c] = w_co[(jr * ST * KS + sct) * cib + c];
+            }
+          }
+          const float4* lp = reinterpret_cast<const float4*>(lam_co - jr * NLT);
+          float L[G::NL];
+#pragma unroll
+          for (int q = G::Q0; q < G::NL / 4; ++q) {
+            const float4 t4 = lp[q];
+            L[4 * q + 0] = t4.x; L[4 * q + 1] = t4.y; L[4 * q + 2] = t4.z; L[4 * q + 3] = t4.w;
+          }
+#pragma unroll
+          for (int sct = 0; sct < KS; ++sct) {
+#pragma unroll
+            for (int i = 0; i < G::TW; ++i) {
+              if ((i + PD - sct) % ST == 0) {
+#pragma unroll
+                for (int c = 0; c < TCI; ++c) acc[c][i] = fmaf(L[(i + PD - sct) / ST + G::C0E], w[sct][c], acc[c][i]);
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!row_ok) return;
+  const int wleft = g.Wi - (w0 + colseg * G::TW);
+#pragma unroll
+  for (int c = 0; c < TCI; ++c) {
+    const int ci = ci0 + cig * TCI + c;
+    if (ci >= g.Ci) break;
+    float* op = g.out + (((size_t)(m0 + mr) * g.Ci + ci) * g.Hi + hi) * g.Wi + w0 + colseg * G::TW;
+    if (wleft >= G::TW && (reinterpret_cast<uintptr_t>(op) & 15u) == 0) {
+#pragma unroll
+      for (int q = 0; q < G::TW / 4; ++q)
+        reinterpret_cast<float4*>(op)[q] = make_float4(acc[c][4 * q], acc[c][4 * q + 1], acc[c][4 * q + 2], acc[c][4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < G::TW; ++i)
+        if (i < wleft) op[i] = acc[c][i];
+    }
+  }
+}
+
+static int ilog2_ceil(int v) {
+  int l = 0;
+  while ((1 << l) < v) ++l;
+  return l;
+}
+
+template <int KS, int ST, int PD, int TCI, bool VEC>
+static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
+  using G = RowSeg<KS, ST, PD, VEC>;
+  RowSegArgs a{};
+  a.c = g;
+  // channel groups per block: up to 32 input channels side by side
+  int cig = ceil_div(g.Ci, TCI);
+  if (cig > 32 / TCI) cig = 32 / TCI;
+  a.cigl = ilog2_ceil(cig);
+  const int nsegl = 8 - a.cigl;  // 256 threads
+  const int segs_row = ceil_div(g.Wi, G::TW);
+  a.sxl = ilog2_ceil(segs_row);
+  if (a.sxl > nsegl - 1) a.sxl = nsegl - 1;  // leave at least two image rows per block
+  a.thl = ilog2_ceil(g.Hi);
+  if (a.thl > nsegl - a.sxl) a.thl = nsegl - a.sxl;
+  if ((1 << a.thl) % ST != 0) return BF_E_UNSUPPORTED;
+  a.mrl = nsegl - a.sxl - a.thl;
+  a.tiles_x = ceil_div(segs_row, 1 << a.sxl);
+  a.tiles_y = ceil_div(g.Hi, 1 << a.thl);
+  const int nlt = G::tile_w(1 << a.sxl);
+  a.rowl = ilog2_ceil(VEC ? nlt / 4 : nlt);
+  if (a.rowl > 8) return BF_E_UNSUPPORTED;
+  const int cib = TCI << a.cigl;
+  const size_t per_co = ((size_t)(1 << a.mrl) * G::tile_h(1 << a.thl) * nlt + (size_t)KS * KS * cib) * sizeof(float);
+  const size_t budget = (TCI > 1 ? 48 : 32) * 1024;  // per buffer; two buffers per block, two or three blocks per SM
+  int cc = (int)(budget / per_co);
+  if (cc > 16) cc = 16;
+  if (cc > g.Co) cc = g.Co;
+  if (cc < 1) return BF_E_UNSUPPORTED;
+  while (g.Co % cc != 0) --cc;  // a divisor of Co: every chunk is full
+  a.cc = cc;
+  const size_t smem = 2 * per_co * cc + (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * sizeof(int);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    attr_done = true;
+  }
+  dim3 grid(ceil_div(g.M, 1 << a.mrl), a.tiles_x * a.tiles_y, ceil_div(g.Ci, cib));
+  if (grid.y > 65535 || grid.z > 65535) return BF_E_UNSUPPORTED;
+  conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC><<<grid, 256, smem, stream>>>(a);
+  BF_CHECK_LAUNCH("conv_transpose_rowseg_kernel");
+  return BF_OK;
+}
+
+template <int KS, int ST, int PD>
+static int launch_rowseg(const ConvTArgs& g, cudaStream_t stream) {
+  const bool vec = (g.Wo % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.Lam) & 15u) == 0);
+  if (g.Ci <= 2) return vec ? launch_rowseg_tci<KS, ST, PD, 1, true>(g, stream) : launch_rowseg_tci<KS, ST, PD, 1, false>(g, stream);
+  return vec ? launch_rowseg_tci<KS, ST, PD, 4, true>(g, stream) : launch_rowseg_tci<KS, ST, PD, 4, false>(g, stream);
+}
+
+// Row-segment kernel for the geometries it is instantiated for; BF_E_UNSUPPORTED otherwise.
+static int launch_convT_rowseg(const ConvTArgs& g, cudaStream_t stream) {
+  if (g.kh != g.kw || g.sh != g.sw || g.ph != g.pw) return BF_E_UNSUPPORTED;
+  if (g.kh == 3 && g.sh == 1 && g.ph == 1) return launch_rowseg<3, 1, 1>(g, stream);
+  if (g.kh == 4 && g.sh == 2 && g.ph == 1) return launch_rowseg<4, 2, 1>(g, stream);
+  if (g.kh == 3 && g.sh == 2 && g.ph == 1) return launch_rowseg<3, 2, 1>(g, stream);
+  if (g.kh == 5 && g.sh == 1 && g.ph == 2) return launch_rowseg<5, 1, 2>(g, stream);
+  return BF_E_UNSUPPORTED;
+}
+
+// scaled coefficients [M, n_out] followed by the per-chunk partial sums of the intercept term [M, chunks]
+static size_t relu_rows_lam_bytes(int M, int n_out) { return ((size_t)M * n_out * sizeof(float) + 255) & ~(size_t)255; }
+size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L) {
+  return relu_rows_lam_bytes(M, L.n_out) + (size_t)M * ceil_div(L.n_out, RELU_ROWS_CHUNK) * sizeof(float);
+}
 
 template <int ACC>
 static int launch_convT(const ConvTArgs& g0, cudaStream_t stream) {
@@ -230,20 +564,115 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
   const float* lam = A;
   const bool need_pro = (dpos != nullptr) || (bias != nullptr) || (delta != nullptr && !accumulate);
   if (need_pro) {
-    float* lam_out = dpos ? static_cast<float*>(scratch) : nullptr;
     BF_REQUIRE(!dpos || scratch, BF_E_WORKSPACE, "conv backward: scratch missing");
-    int blocks = ceil_div(M, 8);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    relu_bwd_rows_kernel<<<blocks, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, L.Ho * L.Wo, lam_out, delta, accumulate,
-                                                    M, S, L.n_out);
+    float* lam_out = dpos ? static_cast<float*>(scratch) : nullptr;
+    // without scratch (no ReLU) a block streams a whole row
+    const int chunk = scratch ? RELU_ROWS_CHUNK : L.n_out;
+    const int nchunks = ceil_div(L.n_out, chunk);
+    float* partial = (delta && nchunks > 1) ? reinterpret_cast<float*>(static_cast<char*>(scratch) + relu_rows_lam_bytes(M, L.n_out)) : nullptr;
+    BF_REQUIRE(nchunks <= 65535, BF_E_UNSUPPORTED, "conv backward: layer too wide");
+    const void* ptrs[] = {A, dpos, dneg, epos, eneg, lam_out};
+    int vec = (L.n_out % 4 == 0) ? 1 : 0;
+    for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = 0;
+    dim3 grid(M, nchunks);
+    relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, L.Ho * L.Wo, lam_out, partial, delta, accumulate,
+                                                  chunk, S, L.n_out, vec);
     BF_CHECK_LAUNCH("relu_bwd_rows_kernel");
+    if (partial) {
+      int rc = launch_sum_partials(accumulate ? delta : nullptr, partial, nchunks, delta, M, stream);
+      if (rc != BF_OK) return rc;
+    }
     if (dpos) lam = lam_out;
   }
   if (!A_prev) return BF_OK;
   ConvTArgs g{lam, W, A_prev, M, L.Ci, L.Hi, L.Wi, L.Co, L.Ho, L.Wo, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, 0};
+  if (getenv("BF_B200_CONV_GATHER") == nullptr) {
+    const int rc = launch_convT_rowseg(g, stream);
+    if (rc != BF_E_UNSUPPORTED) return rc;
+  }
   if (L.Ci <= 4) return launch_convT<4>(g, stream);
   if (L.Ci <= 16) return launch_convT<16>(g, stream);
   return launch_convT<32>(g, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Backward step of a conv2d layer for coefficient rows that are rows first..first+S-1 of the
+// identity (the start of an intermediate-bound sweep): row j = (co, ho, wo) maps to the kernel
+// patch W[co, :, :, :] placed at (ho*sh - ph, wo*sw - pw), the same for every domain, and its
+// bias term is bias[co].  One thread per output element; nothing is multiplied.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) onehot_conv_rows_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                                                               float* __restrict__ out, float* __restrict__ delta, int first,
+                                                               int S, int vec, ConvTArgs g) {
+  // grid (coefficient row, input channel): the row's output position is decoded once per block
+  const int m = blockIdx.x, ci = blockIdx.y;
+  const int j = first + m % S;
+  const int co = j / (g.Ho * g.Wo), rem = j - co * (g.Ho * g.Wo);
+  const int ho = rem / g.Wo, wo = rem - ho * g.Wo;
+  const int h_top = ho * g.sh - g.ph, w_left = wo * g.sw - g.pw;  // image position of kernel tap (0, 0)
+  const float* wp = W + ((size_t)co * g.Ci + ci) * g.kh * g.kw;
+  float* op = out + ((size_t)m * g.Ci + ci) * g.Hi * g.Wi;
+  if (ci == 0 && threadIdx.x == 0 && delta) delta[m] = bias ? __ldg(bias + co) : 0.f;
+  if (vec) {  // Wi % 4 == 0 and 16-byte aligned rows
+    const int w4 = g.Wi >> 2;
+    for (int p = threadIdx.x; p < g.Hi * w4; p += 256) {
+      const int hi = p / w4, wi = (p - hi * w4) << 2;
+      const int r = hi - h_top;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r >= 0 && r < g.kh) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int sc = wi + q - w_left;
+          if (sc >= 0 && sc < g.kw) v[q] = __ldg(wp + r * g.kw + sc);
+        }
+      }
+      *reinterpret_cast<float4*>(op + (size_t)hi * g.Wi + wi) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    for (int p = threadIdx.x; p < g.Hi * g.Wi; p += 256) {
+      const int hi = p / g.Wi, wi = p - hi * g.Wi;
+      const int r = hi - h_top, sc = wi - w_left;
+      op[p] = (r >= 0 && r < g.kh && sc >= 0 && sc < g.kw) ? __ldg(wp + r * g.kw + sc) : 0.f;
+    }
+  }
+}
+
+// grid-stride launch: enough blocks to fill the machine, at most one block per 256 elements
+static int onehot_grid(long long total) {
+  const long long blocks = (total + 255) / 256;
+  return (int)(blocks < 148LL * 16 ? blocks : 148LL * 16);
+}
+
+int launch_onehot_conv_rows(int first, const float* W, const float* bias, float* A_prev, float* delta, int M, int S,
+                            const bf_layer_desc& L, cudaStream_t stream) {
+  ConvTArgs g{nullptr, W, A_prev, M, L.Ci, L.Hi, L.Wi, L.Co, L.Ho, L.Wo, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, 0};
+  BF_REQUIRE(L.Ci <= 65535, BF_E_UNSUPPORTED, "conv backward: too many input channels");
+  const int vec = (L.Wi % 4 == 0 && (reinterpret_cast<uintptr_t>(A_prev) & 15u) == 0) ? 1 : 0;
+  dim3 grid(M, L.Ci);
+  onehot_conv_rows_kernel<<<grid, 256, 0, stream>>>(W, bias, A_prev, delta, first, S, vec, g);
+  BF_CHECK_LAUNCH("onehot_conv_rows_kernel");
+  return BF_OK;
+}
+
+// Same for a linear layer: coefficient row j is row j of W, its bias term bias[j].
+__global__ void __launch_bounds__(256) onehot_linear_rows_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                                                                 float* __restrict__ out, float* __restrict__ delta, int first,
+                                                                 int S, int n_in, long long total) {
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(e / n_in);
+    const int k = (int)(e - (long long)m * n_in);
+    const int j = first + m % S;
+    out[e] = __ldg(W + (size_t)j * n_in + k);
+    if (k == 0 && delta) delta[m] = bias ? __ldg(bias + j) : 0.f;
+  }
+}
+
+int launch_onehot_linear_rows(int first, const float* W, const float* bias, float* A_prev, float* delta, int M, int S, int n_in,
+                              cudaStream_t stream) {
+  const long long total = (long long)M * n_in;
+  onehot_linear_rows_kernel<<<onehot_grid(total), 256, 0, stream>>>(W, bias, A_prev, delta, first, S, n_in, total);
+  BF_CHECK_LAUNCH("onehot_linear_rows_kernel");
+  return BF_OK;
 }
 
 }  // namespace bf
@@ -270,7 +699,9 @@ extern "C" int bf_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, 
 
 // Bytes of scratch the fused ReLU + Conv2d backward needs for the scaled coefficients.
 extern "C" size_t bf_crown_relu_conv2d_bwd_scratch_bytes(int B, int S, int Co, int Ho, int Wo) {
-  return (size_t)B * S * Co * Ho * Wo * sizeof(float);
+  bf_layer_desc L{};
+  L.n_out = Co * Ho * Wo;
+  return bf::crown_bwd_conv2d_scratch_bytes(B * S, L);
 }
 
 extern "C" int bf_crown_relu_conv2d_bwd(const float* A, int side, const float* alpha_u, const float* alpha_l,

@@ -145,7 +145,7 @@ int bf_crown_relu_linear_bwd(const float* A, int side,
  * A_prev [B,S,Ci*Hi*Wi]; delta [B,S] as above.  groups = 1, dilation = 1; any kernel size,
  * stride and padding with 0 <= output_padding < stride.  `scratch` (device,
  * bf_crown_relu_conv2d_bwd_scratch_bytes) holds the ReLU-scaled coefficients between the
- * two passes; it may be NULL when no ReLU is applied. */
+ * two passes and, for wide layers, partial sums of delta; it may be NULL when no ReLU is applied. */
 size_t bf_crown_relu_conv2d_bwd_scratch_bytes(int B, int S, int Co, int Ho, int Wo);
 int bf_crown_relu_conv2d_bwd(const float* A, int side,
                              const float* alpha_u, const float* alpha_l,
@@ -163,8 +163,8 @@ int bf_crown_relu_conv2d_bwd(const float* A, int side,
  * on the request path because those calls synchronise the device.
  * The ReLU-scaled coefficients are staged in an array that is part of the library image
  * (bf_crown_relu_conv2d_bwd_noalloc_max_bytes() = 16 MiB, held on every GPU that loads the
- * library until the process exits); requests with B*S*Co*Ho*Wo*4 bytes beyond that return
- * BF_E_WORKSPACE.  The first call on each device looks up the array's device address; make
+ * library until the process exits); requests whose bf_crown_relu_conv2d_bwd_scratch_bytes
+ * (about B*S*Co*Ho*Wo*4 bytes) is beyond that return BF_E_WORKSPACE.  The first call on each device looks up the array's device address; make
  * that call with the device current and before any stream capture.  No call allocates or
  * frees memory.  The array is shared by all calls and keeps the last call's contents (every
  * element a call reads was written by that same call, so nothing needs clearing); two calls
@@ -273,6 +273,19 @@ int bf_chain_crown(const bf_chain* chain, int upto_layer, int side,
                    const float* const* add,
                    const float* mid, const float* rad, int norm_p, float eps, float* out,
                    void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+/* bf_chain_crown for spec rows that are rows first_row .. first_row+S-1 of the identity, the same
+ * for every domain: the sweeps that bound an intermediate value neuron by neuron
+ * (run_crown_ibp_mlp_from_forward_trace(output_value=name, linear_spec_C=I_chunk) as composed in
+ * boundflow/runtime/native_intermediate_refinement.py:923-973).  layers[upto_layer-1] must be the
+ * affine layer that produces the bounded value.  Its backward step then copies weight rows /
+ * kernel patches instead of multiplying an identity by them; everything else, and every other
+ * argument, is as in bf_chain_crown (same workspace size). */
+int bf_chain_crown_onehot(const bf_chain* chain, int upto_layer, int side, int first_row,
+                          const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                          const float* const* add,
+                          const float* mid, const float* rad, int norm_p, float eps, float* out,
+                          void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S);
 
