@@ -313,7 +313,9 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
   const int tile = LH * NLT;
   const int nrows = MR * cc * LH;                        // coefficient-tile rows per chunk
   const int lam_words = nrows * NLT;                     // [MR][cc][LH][NLT]
-  const int w_words = cc * KS * KS * cib;                // [cc][KS*KS][cib]
+  const int w_row = KS * cib + 4;                        // one kernel row of weights + 16 bytes: rows r and r+1 (image rows of
+                                                         // different parity read them in one instruction) fall into different banks
+  const int w_words = cc * KS * w_row;                   // [cc][KS][KS*cib + 4]
   const int buf_words = lam_words + w_words;
   constexpr int ROW_ZERO = -2147483647 - 1;
   int* row_off = reinterpret_cast<int*>(rs_smem + 2 * buf_words);  // [nrows] source offset of each tile row, ROW_ZERO: all zeros
@@ -371,7 +373,8 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
     }
     for (int q = wq0; q < cc * KS * KS; q += wqstep) {
       const int co = q / (KS * KS);
-      cp_async_f32(wS + q * cib + wci, wci_ok ? w_base + (size_t)((co0 + co) * g.Ci) * (KS * KS) + (q - co * (KS * KS)) : g.W, wci_ok);
+      const int t = q - co * (KS * KS), r = t / KS;
+      cp_async_f32(wS + (co * KS + r) * w_row + (t - r * KS) * cib + wci, wci_ok ? w_base + (size_t)((co0 + co) * g.Ci) * (KS * KS) + (q - co * (KS * KS)) : g.W, wci_ok);
     }
     cp_async_commit();
   };
@@ -387,7 +390,7 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
   const int r_first = (hi + PD) % ST;
   const int hl_top = (hi + PD - r_first) / ST - ho_lo;
   const int lam_thread = (mr * cc * LH + hl_top) * NLT + colseg * (G::TW / ST);
-  const int w_thread = r_first * KS * cib + cig * TCI;
+  const int w_thread = r_first * w_row + cig * TCI;
 
   stage(0, 0);
   int buf = 0;
@@ -405,7 +408,7 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
       const float* w_t = rs_smem + buf * buf_words + lam_words + w_thread;
       for (int co = 0; co < cc; ++co) {
         const float* lam_co = lam_t + co * tile;
-        const float* w_co = w_t + co * (KS * KS) * cib;
+        const float* w_co = w_t + co * KS * w_row;
 #pragma unroll
         for (int jr = 0; jr < JR; ++jr) {
           if (KS % ST != 0 && r_first + ST * jr >= KS) break;
@@ -413,11 +416,11 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
 #pragma unroll
           for (int sct = 0; sct < KS; ++sct) {
             if (TCI == 4) {
-              const float4 w4 = *reinterpret_cast<const float4*>(w_co + (jr * ST * KS + sct) * cib);
+              const float4 w4 = *reinterpret_cast<const float4*>(w_co + jr * ST * w_row + sct * cib);
               w[sct][0] = w4.x; w[sct][1 % TCI] = w4.y; w[sct][2 % TCI] = w4.z; w[sct][3 % TCI] = w4.w;
             } else {
 #pragma unroll
-              for (int c = 0; c < TCI; ++c) w[sct][c] = w_co[(jr * ST * KS + sct) * cib + c];
+              for (int c = 0; c < TCI; ++c) w[sct][c] = w_co[jr * ST * w_row + sct * cib + c];
             }
           }
           const float4* lp = reinterpret_cast<const float4*>(lam_co - jr * NLT);
@@ -490,7 +493,7 @@ static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
   a.rowl = ilog2_ceil(VEC ? nlt / 4 : nlt);
   if (a.rowl > 8) return BF_E_UNSUPPORTED;
   const int cib = TCI << a.cigl;
-  const size_t per_co = ((size_t)(1 << a.mrl) * G::tile_h(1 << a.thl) * nlt + (size_t)KS * KS * cib) * sizeof(float);
+  const size_t per_co = ((size_t)(1 << a.mrl) * G::tile_h(1 << a.thl) * nlt + (size_t)KS * (KS * cib + 4)) * sizeof(float);
   const size_t budget = (TCI > 1 ? 48 : 32) * 1024;  // per buffer; two buffers per block, two or three blocks per SM
   int cc = (int)(budget / per_co);
   if (cc > 16) cc = 16;
