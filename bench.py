@@ -169,12 +169,13 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def crown_bounds_secondary(world: int, rank: int, dev):
+def crown_bounds_secondary(world: int, rank: int, dev, only=None):
     """Second half of the metric: CROWN bounds/s (one bound = one (input, spec) lower bound) on the
     input-sharded configurations, whole job over all ranks, device-timed, max over ranks.
       c1: IBP + CROWN (both sides), MLP 784-100-100-10, 64 inputs
       c2: CROWN with CROWN intermediate bounds, MNIST-shaped CNN, 256 inputs
-      c3: alpha-CROWN, 20 Adam steps, MLP 784-256x5-10, 128 inputs"""
+      c3: alpha-CROWN, 20 Adam steps, MLP 784-256x5-10, 128 inputs
+      c5: CROWN with full CROWN intermediate bounds, CIFAR-shaped CNN, 64 inputs"""
     import torch.distributed as dist
 
     from boundflow_b200 import _lib
@@ -185,7 +186,9 @@ def crown_bounds_secondary(world: int, rank: int, dev):
 
     lib = _lib.load()
     out = {}
-    for name, reps in (("c1", 20), ("c2", 2), ("c3", 5)):
+    for name, reps in (("c1", 20), ("c2", 2), ("c3", 5), ("c5", 1)):
+        if only is not None and name != only:
+            continue
         wl = W.make_workload(name)
         n = wl.x.shape[0]
         a, b = shard_range(n, rank, world)
@@ -197,6 +200,8 @@ def crown_bounds_secondary(world: int, rank: int, dev):
                 res = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=C).lower
             elif name == "c2":
                 res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=512)[0].lower
+            elif name == "c5":  # about 4096 coefficient rows per sweep
+                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=max(64, 4096 // max(1, b - a)))[0].lower
             else:
                 tr = ibp_trace(wl.module, spec)
                 a0 = adaptive_alpha_from_trace(tr)
@@ -207,7 +212,7 @@ def crown_bounds_secondary(world: int, rank: int, dev):
                                       torch.cuda.current_stream().cuda_stream))
             return gather_domain_results(res, verdict, n) if world > 1 else (res, verdict)
 
-        for _ in range(2):
+        for _ in range(1 if name == "c5" else 2):
             run()
         if world > 1:
             dist.barrier()
@@ -235,6 +240,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--domains", type=int, default=DOMAINS_PER_GPU, help="subdomains per GPU per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--secondary-only", default=None, choices=["c1", "c2", "c3", "c5"],
+                    help="time only this CROWN bounds/s configuration and print its figures (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -262,6 +269,13 @@ def main():
     from boundflow_b200.ir import InputSpec
 
     lib = _lib.load()
+    if args.secondary_only:
+        sec = crown_bounds_secondary(world, rank, dev, only=args.secondary_only)
+        if rank == 0:
+            print(json.dumps({"crown_bounds_per_s": sec, "n_gpus": world}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     warmup = max(int(args.warmup), 3)
     D = int(args.domains)
     wl = W.make_workload("c4")

@@ -607,15 +607,18 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
 __global__ void __launch_bounds__(256) onehot_conv_rows_kernel(const float* __restrict__ W, const float* __restrict__ bias,
                                                                float* __restrict__ out, float* __restrict__ delta, int first,
                                                                int S, int vec, ConvTArgs g) {
-  // grid (coefficient row, input channel): the row's output position is decoded once per block
-  const int m = blockIdx.x, ci = blockIdx.y;
+  // grid (coefficient row, group of input channels): the row's output position is decoded once per block
+  const int m = blockIdx.x;
   const int j = first + m % S;
   const int co = j / (g.Ho * g.Wo), rem = j - co * (g.Ho * g.Wo);
   const int ho = rem / g.Wo, wo = rem - ho * g.Wo;
   const int h_top = ho * g.sh - g.ph, w_left = wo * g.sw - g.pw;  // image position of kernel tap (0, 0)
+  if (blockIdx.y == 0 && threadIdx.x == 0 && delta) delta[m] = bias ? __ldg(bias + co) : 0.f;
+  const int ci_per_block = (g.Ci + gridDim.y - 1) / gridDim.y;
+  const int ci_end = min(g.Ci, (int)(blockIdx.y + 1) * ci_per_block);
+  for (int ci = blockIdx.y * ci_per_block; ci < ci_end; ++ci) {
   const float* wp = W + ((size_t)co * g.Ci + ci) * g.kh * g.kw;
   float* op = out + ((size_t)m * g.Ci + ci) * g.Hi * g.Wi;
-  if (ci == 0 && threadIdx.x == 0 && delta) delta[m] = bias ? __ldg(bias + co) : 0.f;
   if (vec) {  // Wi % 4 == 0 and 16-byte aligned rows
     const int w4 = g.Wi >> 2;
     for (int p = threadIdx.x; p < g.Hi * w4; p += 256) {
@@ -638,6 +641,7 @@ __global__ void __launch_bounds__(256) onehot_conv_rows_kernel(const float* __re
       op[p] = (r >= 0 && r < g.kh && sc >= 0 && sc < g.kw) ? __ldg(wp + r * g.kw + sc) : 0.f;
     }
   }
+  }
 }
 
 // grid-stride launch: enough blocks to fill the machine, at most one block per 256 elements
@@ -651,7 +655,11 @@ int launch_onehot_conv_rows(int first, const float* W, const float* bias, float*
   ConvTArgs g{nullptr, W, A_prev, M, L.Ci, L.Hi, L.Wi, L.Co, L.Ho, L.Wo, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, 0};
   BF_REQUIRE(L.Ci <= 65535, BF_E_UNSUPPORTED, "conv backward: too many input channels");
   const int vec = (L.Wi % 4 == 0 && (reinterpret_cast<uintptr_t>(A_prev) & 15u) == 0) ? 1 : 0;
-  dim3 grid(M, L.Ci);
+  // about 16 KB of output per block once there are enough rows to fill the machine
+  int groups = L.Ci;
+  const int per_block = 16384 / (L.Hi * L.Wi * 4);
+  if (M >= 148 * 8 && per_block > 1) groups = ceil_div(L.Ci, per_block);
+  dim3 grid(M, groups);
   onehot_conv_rows_kernel<<<grid, 256, 0, stream>>>(W, bias, A_prev, delta, first, S, vec, g);
   BF_CHECK_LAUNCH("onehot_conv_rows_kernel");
   return BF_OK;
