@@ -171,3 +171,49 @@ def test_gather_world_size_2_gloo(tmp_path):
     for p in procs:
         out, _ = p.communicate(timeout=120)
         assert p.returncode == 0, out.decode()
+
+
+def test_typed_registry_routes_fused_tasks_to_the_cuda_executor():
+    """Typed Task-IR dispatch (no GPU needed: the session and the executor are fakes)."""
+    from types import SimpleNamespace as NS
+
+    from boundflow_b200.typed_backend import CudaTypedTaskBackendRegistry
+
+    calls = []
+
+    class Session:
+        def execute_fused_relu_affine_task(self, op_ids, *, output_value_ids, executor):
+            calls.append((op_ids, output_value_ids, executor))
+            return "step-result"
+
+    class Fallback:
+        def dispatch(self, task, key, *, session, template):
+            return "fallback-result"
+
+    def make(kind, second="linear_backward", n_ops=2):
+        cand = NS(candidate_id="cand0", backend=NS(value=kind), capability_id="cap0", static_legal=True)
+        refs = [NS(op_id="op_relu", kind=NS(value="relu_relaxation")), NS(op_id="op_aff", kind=NS(value=second))][:n_ops]
+        task = NS(task_id="t0", backend=NS(backend_candidate_id="cand0", capability_id="cap0"), op_refs=refs, output_value_ids=("v1", "v2"))
+        key = NS(task_id="t0", backend_candidate_id="cand0", capability_id="cap0", stable_hash=lambda: "h-" + kind + second)
+        return task, key, NS(backend_candidates=[cand])
+
+    executor = object()
+    reg = CudaTypedTaskBackendRegistry(fallback=Fallback(), executor=executor)
+    task, key, template = make("tvm_fused_tir")
+    assert reg.dispatch(task, key, session=Session(), template=template) == "step-result"
+    assert calls[-1] == (("op_relu", "op_aff"), ("v1", "v2"), executor)
+    assert reg.dispatch(task, key, session=Session(), template=template) == "step-result"
+    assert (reg.cache_misses, reg.cache_hits, reg.cuda_dispatches) == (1, 1, 2)
+    task, key, template = make("pytorch_chunked", second="conv2d_backward")
+    assert reg.dispatch(task, key, session=Session(), template=template) == "step-result"
+    task, key, template = make("reference")
+    assert reg.dispatch(task, key, session=Session(), template=template) == "fallback-result"
+    with pytest.raises(ValueError):
+        CudaTypedTaskBackendRegistry(executor=executor).dispatch(task, key, session=Session(), template=template)
+    task, key, template = make("tvm_fused_tir", n_ops=1)
+    with pytest.raises(ValueError):
+        reg.dispatch(task, key, session=Session(), template=template)
+    task, key, template = make("tvm_fused_tir")
+    key.capability_id = "other"
+    with pytest.raises(ValueError):
+        reg.dispatch(task, key, session=Session(), template=template)
