@@ -274,6 +274,55 @@ extern "C" int bf_ibp_linear_lp(const float* center, const float* row_dev, const
                                infeasible, B, n_in, n_out, row_dev, bf::as_stream(stream));
 }
 
+// ---------------------------------------------------------------------------
+// IBP linear layer whose weight differs per batch element (the output spec merged into the last
+// layer: W' = C @ W, b' = C @ b): one warp per (batch element, output row), midpoint/radius form.
+// HBM-bound: every weight is read once.
+// ---------------------------------------------------------------------------
+namespace bf {
+__global__ void __launch_bounds__(256) ibp_linear_batched_kernel(const float* __restrict__ in_l, const float* __restrict__ in_u,
+                                                                 int relu_in, const float* __restrict__ W,
+                                                                 const float* __restrict__ bias, float* __restrict__ out_l,
+                                                                 float* __restrict__ out_u, int B, int S, int n_in) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= (long long)B * S) return;
+  const int b = (int)(row / S);
+  const float* w = W + (size_t)row * n_in;
+  const float* xl = in_l + (size_t)b * n_in;
+  const float* xu = in_u + (size_t)b * n_in;
+  float c = 0.f, d = 0.f;
+  for (int i = lane; i < n_in; i += 32) {
+    float lo = xl[i], up = xu[i];
+    if (relu_in) { lo = fmaxf(lo, 0.f); up = fmaxf(up, 0.f); }
+    const float wv = w[i];
+    c = fmaf(0.5f * (lo + up), wv, c);
+    d = fmaf(0.5f * (up - lo), fabsf(wv), d);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    d += __shfl_xor_sync(0xffffffffu, d, o);
+  }
+  if (lane == 0) {
+    const float bb = bias ? bias[row] : 0.f;
+    out_l[row] = c - d + bb;
+    out_u[row] = c + d + bb;
+  }
+}
+}  // namespace bf
+
+extern "C" int bf_ibp_linear_batched(const float* in_l, const float* in_u, int relu_in, const float* W, const float* bias,
+                                     float* out_l, float* out_u, int B, int S, int n_in, bf_stream_t stream) {
+  BF_REQUIRE(in_l && in_u && W && out_l && out_u, BF_E_INVALID, "bf_ibp_linear_batched: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n_in > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "bf_ibp_linear_batched: bad sizes");
+  const long long warps = (long long)B * S;
+  bf::ibp_linear_batched_kernel<<<(int)((warps + 7) / 8), 256, 0, bf::as_stream(stream)>>>(in_l, in_u, relu_in, W, bias, out_l, out_u,
+                                                                                          B, S, n_in);
+  BF_CHECK_LAUNCH("ibp_linear_batched_kernel");
+  return BF_OK;
+}
+
 extern "C" int bf_concretize_lp(const float* A, const float* center, float eps, int p, const float* bias_in, float* out, int side,
                                 int B, int S, int n0, bf_stream_t stream) {
   BF_REQUIRE(A && center && out, BF_E_INVALID, "bf_concretize_lp: null tensor");

@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace
-from .ir import IntervalState, normalize_input_spec
+from .ir import IntervalState, input_mid_rad, normalize_input_spec
 from .network import _pair
 
 
@@ -66,6 +66,18 @@ class CudaIntervalDomain:
             return IntervalState(lower=y_l.to(x_l.device), upper=y_u.to(x_l.device))
         if op not in (None, "linear"):
             raise NotImplementedError(f"unsupported affine op for IntervalDomain: {op}")
+        if w.dim() == 3:
+            # one weight matrix per batch element [B,S,I] (spec merged into the last layer, task_executor.py:231-245)
+            S, n_in = int(w.shape[1]), int(w.shape[2])
+            if xl.dim() != 2 or int(w.shape[0]) != B or int(xl.shape[1]) != n_in:
+                raise ValueError(f"batched linear mismatch: x={tuple(xl.shape)} w={tuple(w.shape)}")
+            if b is not None and tuple(b.shape) != (B, S):
+                b = b.expand(B, S).contiguous()
+            y_l = torch.empty(B, S, dtype=torch.float32, device=device)
+            y_u = torch.empty_like(y_l)
+            _lib.check(lib.bf_ibp_linear_batched(_lib.ptr(xl), _lib.ptr(xu), relu_in, _lib.ptr(w), _lib.ptr(b), _lib.ptr(y_l), _lib.ptr(y_u),
+                                                 B, S, n_in, _stream_ptr(device)))
+            return IntervalState(lower=y_l.to(x_l.device), upper=y_u.to(x_l.device))
         lead = tuple(xl.shape[:-1])
         n_in, n_out = int(w.shape[1]), int(w.shape[0])
         x2l, x2u = xl.reshape(-1, n_in), xu.reshape(-1, n_in)
@@ -112,6 +124,11 @@ class CudaTaskExecutor:
             if len(task.output_values) != 1:
                 raise ValueError(f"task has {len(task.output_values)} outputs; specify output_value explicitly")
             output_value = task.output_values[0]
+        params = module.bindings.get("params", {})
+        last = task.ops[-1]
+        w_last = params.get(last.inputs[1]) if (last.op_type == "linear" and len(last.inputs) >= 2 and isinstance(params, dict)) else None
+        if torch.is_tensor(w_last) and w_last.dim() == 3:
+            return self._run_ibp_spec_fused(module, task, spec, output_value)
         trace = ibp_trace(module, spec)
         chain = trace.chain
         dev = spec.center.device
@@ -126,6 +143,31 @@ class CudaTaskExecutor:
             if output_value == chain.layers[chain.relu_layer_ids[r]].out_name:
                 return IntervalState(lower=trace.pre_l[r].reshape(shape).clamp_min(0).to(dev), upper=trace.pre_u[r].reshape(shape).clamp_min(0).to(dev))
         raise KeyError(f"missing value in env/params: {output_value}")
+
+    def _run_ibp_spec_fused(self, module: Any, task: Any, spec: Any, output_value: str) -> IntervalState:
+        """Module whose last Linear carries the merged output spec (weight [B,S,I], bias [B,S];
+        planner/interval_v1.py:85-163): the layers below run as a chain, the last one as the batched-W kernel."""
+        from .ir import BFTaskModule, BoundTask
+
+        last = task.ops[-1]
+        params = module.bindings["params"]
+        if output_value != last.outputs[0]:
+            raise KeyError(f"missing value in env/params: {output_value}")
+        body = list(task.ops[:-1])
+        relu_in = bool(body) and body[-1].op_type == "relu"
+        if relu_in:
+            body = body[:-1]
+        w, b = params[last.inputs[1]], (params[last.inputs[2]] if len(last.inputs) == 3 else None)
+        if not body:  # the fused layer reads the input set itself
+            _mid, _rad, lo, up = input_mid_rad(spec)
+            x = IntervalState(lower=lo.flatten(1), upper=up.flatten(1))
+        else:
+            sub_task = BoundTask(task_id=task.task_id, kind=task.kind, ops=body, input_values=list(task.input_values),
+                                 output_values=[body[-1].outputs[0]])
+            sub = BFTaskModule(tasks=[sub_task], entry_task_id=task.task_id, bindings=module.bindings)
+            x = self.run_ibp(sub, spec)
+            x = IntervalState(lower=x.lower.flatten(1), upper=x.upper.flatten(1))
+        return self.domain.affine_transformer(x, w, b, op="linear", relu_in=relu_in)
 
     # ---- one task of a scheduled task graph -------------------------------
     def run_ibp_task(self, task: Any, *, env: Dict[str, IntervalState], params: Dict[str, Any], storage_plan: Any) -> None:
@@ -161,8 +203,6 @@ class CudaTaskExecutor:
                 x = get_interval(op.inputs[0])
                 w = get_tensor(op.inputs[1])
                 b = get_tensor(op.inputs[2]) if len(op.inputs) == 3 else None
-                if torch.is_tensor(w) and w.dim() == 3 and t == "linear":
-                    raise NotImplementedError("batched-weight linear is not supported by the CUDA executor")
                 attrs = dict(op.attrs)
                 attrs["op"] = t
                 env[buf(op.outputs[0])] = self.domain.affine_transformer(x, w, b, **attrs)

@@ -195,6 +195,15 @@ int bf_concretize(const float* A, const float* mid, const float* rad, const floa
  *   bf_concretize_lp: A.centre -/+ eps * ||A_row||_q + bias_in, replaces
  *            LpBallPerturbation.concretize_affine perturbation.py:175-222 (row norms
  *            boundflow/runtime/linear_operator.py:365-372). */
+/* IBP linear layer with one weight matrix per batch element -- the output spec merged into the
+ * last layer (W' = C @ W, b' = C @ b; _fuse_linear_spec_into_last_linear,
+ * boundflow/planner/interval_v1.py:85-163), evaluated as the batched-W branch of
+ * PythonTaskExecutor.run_ibp, boundflow/runtime/task_executor.py:231-245:
+ * out = mid @ W'^T -/+ rad @ |W'|^T + b'.  in_l, in_u [B,n_in] (relu_in != 0: clamped at 0 first);
+ * W [B,S,n_in]; bias [B,S] or NULL; out_l, out_u [B,S]. */
+int bf_ibp_linear_batched(const float* in_l, const float* in_u, int relu_in, const float* W, const float* bias,
+                          float* out_l, float* out_u, int B, int S, int n_in, bf_stream_t stream);
+
 int bf_row_dual_norms(const float* W, int n_rows, int n_cols, int p, float scale, float* out, bf_stream_t stream);
 int bf_ibp_linear_lp(const float* center, const float* row_dev, const float* W, const float* bias,
                      const int8_t* split, int split_stride, const float* cons_l, const float* cons_u,

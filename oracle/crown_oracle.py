@@ -121,6 +121,21 @@ def ibp_conv2d(l, u, W, b, stride, padding):
     return y_l, y_u
 
 
+def ibp_linear_batched(l: torch.Tensor, u: torch.Tensor, W: torch.Tensor, b: Optional[torch.Tensor]):
+    """Linear layer with one weight matrix per batch element, W [B,S,I], b [B,S]: the
+    batched branch of `PythonTaskExecutor.run_ibp` (runtime/task_executor.py:231-245),
+    which evaluates a module whose last layer carries the merged output spec
+    (`_fuse_linear_spec_into_last_linear`, planner/interval_v1.py:85-163)."""
+    mid = (l + u) / 2.0
+    diff = (u - l) / 2.0
+    center = torch.bmm(mid.unsqueeze(1), W.transpose(-1, -2)).squeeze(1)
+    dev = torch.bmm(diff.unsqueeze(1), W.abs().transpose(-1, -2)).squeeze(1)
+    lower, upper = center - dev, center + dev
+    if b is not None:
+        lower, upper = lower + b, upper + b
+    return lower, upper
+
+
 def apply_relu_split(l: torch.Tensor, u: torch.Tensor, split: torch.Tensor):
     """`_apply_relu_split`, runtime/crown_ibp.py:70-98.
 

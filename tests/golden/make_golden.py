@@ -192,15 +192,44 @@ def gen_shared_alpha() -> None:
     save("shared_alpha.npz", **out)
 
 
+def spec_fused_module(wl):
+    """The workload's module with the output spec merged into its last Linear layer, as
+    `_fuse_linear_spec_into_last_linear` (planner/interval_v1.py:85-163) rewrites it."""
+    m = ref_module(wl)
+    task = m.get_entry_task()
+    last = task.ops[-1]
+    params = m.bindings["params"]
+    Wl, bl = params[last.inputs[1]], params[last.inputs[2]]
+    params["spec_W"] = torch.matmul(wl.C, Wl)
+    params["spec_b"] = torch.matmul(wl.C, bl)
+    last.inputs = [last.inputs[0], "spec_W", "spec_b"]
+    last.outputs = ["spec_out"]
+    task.output_values = ["spec_out"]
+    return m
+
+
+def gen_spec_fused_ibp() -> None:
+    """IBP of the margins C @ logits with the spec merged into the last layer (batched-W linear)."""
+    out = {}
+    for tag in ("c1", "c3"):
+        wl = W.make_workload(tag) if tag == "c1" else W.make_workload(tag, batch=8)
+        spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+        res = PythonTaskExecutor().run_ibp(spec_fused_module(wl), spec)
+        out[f"{tag}_input_checksum"] = checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])
+        out[f"{tag}_lower"], out[f"{tag}_upper"] = res.lower, res.upper
+    save("spec_fused_ibp.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
-    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha}
+    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
     gen_lp_ball()
     gen_shared_alpha()
+    gen_spec_fused_ibp()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

@@ -259,3 +259,19 @@ def test_shared_alpha_beta(golden):
         ref_b = torch.as_tensor(g[f"c4_ab_beta_{n}"]).reshape(-1)
         assert float(b[r].min()) >= 0.0
         assert float((b[r] - ref_b).abs().max()) <= 0.05
+
+
+def test_spec_fused_ibp(golden):
+    """Margins C @ logits by IBP with the spec merged into the last layer (batched-W linear)."""
+    g = golden("spec_fused_ibp.npz")
+    for tag in ("c1", "c3"):
+        wl = W.make_workload(tag) if tag == "c1" else W.make_workload(tag, batch=8)
+        assert np.allclose(workload_checksum(wl), g[f"{tag}_input_checksum"], rtol=1e-12, atol=0)
+        body = wl.layers[:-1]   # ... linear, relu | last linear
+        assert body[-1]["op"] == "relu" and wl.layers[-1]["op"] == "linear"
+        tr = O.forward_ibp_trace(body[:-1], O.box_input(wl.lo, wl.up))
+        l, u = torch.relu(tr.out[0]), torch.relu(tr.out[1])
+        Wl, bl = wl.layers[-1]["W"], wl.layers[-1]["b"]
+        lo, up = O.ibp_linear_batched(l, u, torch.matmul(wl.C, Wl), torch.matmul(wl.C, bl))
+        assert_close(lo, g[f"{tag}_lower"], f"{tag} lower")
+        assert_close(up, g[f"{tag}_upper"], f"{tag} upper")
