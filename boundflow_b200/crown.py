@@ -627,6 +627,33 @@ def run_alpha_crown_mlp(
     return bounds, state, stats
 
 
+def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapping[str, torch.Tensor], *,
+                            steps: int = 200, lr: float = 0.1, tol: float = 1e-6):
+    """Per-domain first-layer infeasibility certificate (`_is_infeasible_split_first_layer_convex_combo`,
+    alpha_beta_crown.py:391-532, which the reference runs for batch size 1; here for every domain).
+    Returns (infeasible int32 [B]: 1 found / 0 none / -1 not evaluated, best_value float [B],
+    n_halfspaces int32 [B]) as CUDA tensors.  The splits of the first ReLU over a Linear first layer
+    are used; a chain that starts otherwise, or no split on that ReLU, gives all zeros."""
+    spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
+    if lp_ball_of(spec) is not None:
+        raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
+    infeasible = torch.zeros(B, dtype=torch.int32, device=device)
+    best = torch.full((B,), float("inf"), dtype=torch.float32, device=device)
+    count = torch.zeros(B, dtype=torch.int32, device=device)
+    first = next((l for l in chain.layers if l.op != "flatten"), None)
+    if first is None or first.op != "linear" or not chain.relu_input_names or first.out_name != chain.relu_input_names[0]:
+        return infeasible, best, count
+    raw = relu_split_state.get(chain.relu_input_names[0]) if relu_split_state else None
+    if raw is None:
+        return infeasible, best, count
+    n1 = chain.relu_widths[0]
+    sp, stride = _split_tensor(raw, B, n1, device, chain.relu_input_names[0])
+    _lib.check(chain.lib.bf_first_layer_certificate(
+        _lib.ptr(sp), stride, _lib.ptr(first.W), _lib.ptr(first.b), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible), _lib.ptr(best),
+        _lib.ptr(count), int(steps), float(lr), float(tol), B, n1, chain.n0, _stream_ptr(device)))
+    return infeasible, best, count
+
+
 def run_alpha_beta_crown_mlp(
     module: Any,
     input_spec: Any,
@@ -652,8 +679,9 @@ def run_alpha_beta_crown_mlp(
     loop), `None` means "as the reference".  `per_batch_params=False` (the reference's
     default) optimises one alpha / beta row shared by the whole batch with a whole-batch
     best-of.  Differences from the reference, all explicit: the objective is the lower
-    bound (shared mode: with spec_reduce="mean"), and the batch-size-1
-    first-layer infeasibility certificate (alpha_beta_crown.py:391-532) is not evaluated.
+    bound (shared mode: with spec_reduce="mean").  For a single node the first-layer
+    infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
+    reference (Linear first layers; `first_layer_certificate` gives it for whole batches).
     Infeasible splits raise ValueError like the reference.
     """
     if objective != "lower":
@@ -663,6 +691,15 @@ def run_alpha_beta_crown_mlp(
         optimize_beta = has_split
     if optimize_beta and not has_split:
         optimize_beta = False  # nothing to constrain: beta's gradient is identically zero
+    if has_split and int(normalize_input_spec(input_spec).center.shape[0]) == 1:
+        # the reference's pre-check for a single node (alpha_beta_crown.py:693-714)
+        cert, cert_val, _cnt = first_layer_certificate(module, input_spec, relu_split_state)
+        if int(cert[0]) == 1:
+            c = normalize_input_spec(input_spec).center
+            zeros = torch.zeros((1, 1), device=c.device, dtype=c.dtype)
+            stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=(),
+                                    feasibility="infeasible", reason=f"infeasible: first-layer certificate with max {float(cert_val[0]):.3e}")
+            return IntervalState(lower=zeros, upper=zeros), AlphaState({}), BetaState({}), stats
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, B, device = trace.chain, trace.B, trace.mid.device

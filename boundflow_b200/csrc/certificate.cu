@@ -1,0 +1,167 @@
+// First-layer infeasibility certificate for ReLU-split subdomains, one block per domain.
+//
+// Every split on the first ReLU is a half-space of the INPUT: s_j * (W1[j] . x + b1[j]) >= 0.
+// If some convex combination of those half-spaces has a negative maximum over the input box,
+//     max_{x in box} (sum_i w_i a_i) . x + sum_i w_i c_i  <  0,     w on the simplex,
+// no input satisfies all of them and the domain is empty.  The weights are softmax(logits); the
+// logits take `steps` Adam steps on that maximum (value = a.mid + |a|.rad + c), stopping at the
+// first negative value.  A single half-space is tested directly.
+#include <math.h>
+
+#include "kernels.cuh"
+
+namespace bf {
+
+constexpr int CERT_MAX_M = 16;     // half-spaces per domain handled by the kernel
+constexpr int CERT_THREADS = 256;
+
+// Sum over the block in a fixed order; result valid in every thread.
+__device__ __forceinline__ float cert_block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < CERT_THREADS / 32; ++w) t += red[w];
+  return t;
+}
+
+__global__ void __launch_bounds__(CERT_THREADS) first_layer_cert_kernel(const int8_t* __restrict__ split, int split_stride,
+                                                                        const float* __restrict__ W1, const float* __restrict__ b1,
+                                                                        const float* __restrict__ mid, const float* __restrict__ rad,
+                                                                        int n1, int n0, int steps, float lr, float tol,
+                                                                        int* __restrict__ infeasible, float* __restrict__ best_value,
+                                                                        int* __restrict__ n_halfspaces) {
+  extern __shared__ __align__(16) float cert_smem[];
+  float* A = cert_smem;                      // [CERT_MAX_M][n0]  s_i * W1[j_i]
+  float* smid = A + (size_t)CERT_MAX_M * n0;  // [n0]
+  float* srad = smid + n0;                   // [n0]
+  __shared__ int idx[CERT_MAX_M];
+  __shared__ float sgn[CERT_MAX_M], cvec[CERT_MAX_M], logit[CERT_MAX_M], wgt[CERT_MAX_M], am[CERT_MAX_M], av[CERT_MAX_M];
+  __shared__ float red[CERT_THREADS / 32];
+  __shared__ int m_sh;
+  const int d = blockIdx.x;
+  const int8_t* sp = split + (size_t)d * split_stride;
+
+  // half-spaces in ascending neuron order (warp 0, ballot compaction)
+  if (threadIdx.x < 32) {
+    int count = 0;
+    for (int base = 0; base < n1; base += 32) {
+      const int j = base + threadIdx.x;
+      const int s = (j < n1) ? (int)sp[j] : 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, s != 0);
+      if (s != 0) {
+        const int pos = count + __popc(mask & ((1u << threadIdx.x) - 1u));
+        if (pos < CERT_MAX_M) { idx[pos] = j; sgn[pos] = (float)s; }
+      }
+      count += __popc(mask);
+    }
+    if (threadIdx.x == 0) m_sh = count;
+  }
+  __syncthreads();
+  const int m = m_sh;
+  if (threadIdx.x == 0 && n_halfspaces) n_halfspaces[d] = m;
+  if (m == 0 || m > CERT_MAX_M) {  // nothing to test / more half-spaces than the kernel holds: no verdict
+    if (threadIdx.x == 0) {
+      infeasible[d] = (m == 0) ? 0 : -1;
+      if (best_value) best_value[d] = INFINITY;
+    }
+    return;
+  }
+  for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
+    smid[k] = mid[(size_t)d * n0 + k];
+    srad[k] = rad[(size_t)d * n0 + k];
+  }
+  for (int i = 0; i < m; ++i)
+    for (int k = threadIdx.x; k < n0; k += CERT_THREADS) A[(size_t)i * n0 + k] = sgn[i] * __ldg(W1 + (size_t)idx[i] * n0 + k);
+  if (threadIdx.x < m) {
+    cvec[threadIdx.x] = sgn[threadIdx.x] * (b1 ? b1[idx[threadIdx.x]] : 0.f);
+    logit[threadIdx.x] = 0.f;
+    am[threadIdx.x] = 0.f;
+    av[threadIdx.x] = 0.f;
+  }
+  __syncthreads();
+
+  float best = INFINITY;
+  int found = 0;
+  const int iters = (m == 1) ? 1 : steps;
+  for (int t = 0; t < iters; ++t) {
+    // weights on the simplex
+    if (threadIdx.x == 0) {
+      float mx = logit[0];
+      for (int i = 1; i < m; ++i) mx = fmaxf(mx, logit[i]);
+      float s = 0.f;
+      for (int i = 0; i < m; ++i) { wgt[i] = expf(logit[i] - mx); s += wgt[i]; }
+      for (int i = 0; i < m; ++i) wgt[i] /= s;
+    }
+    __syncthreads();
+    // value of the combination and d value / d w_i
+    float val_p = 0.f, g_p[CERT_MAX_M];
+#pragma unroll
+    for (int i = 0; i < CERT_MAX_M; ++i) g_p[i] = 0.f;
+    for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
+      float a = 0.f;
+      for (int i = 0; i < m; ++i) a = fmaf(wgt[i], A[(size_t)i * n0 + k], a);
+      const float sg = (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f);
+      const float x = fmaf(sg, srad[k], smid[k]);  // maximiser of a . x over the box (sub-gradient 0 at a == 0)
+      val_p = fmaf(a, smid[k], val_p);
+      val_p = fmaf(fabsf(a), srad[k], val_p);
+#pragma unroll
+      for (int i = 0; i < CERT_MAX_M; ++i)
+        if (i < m) g_p[i] = fmaf(A[(size_t)i * n0 + k], x, g_p[i]);
+    }
+    float val = cert_block_sum(val_p, red);
+    float g[CERT_MAX_M];
+#pragma unroll
+    for (int i = 0; i < CERT_MAX_M; ++i) g[i] = (i < m) ? cert_block_sum(g_p[i], red) + cvec[i] : 0.f;
+    for (int i = 0; i < m; ++i) val = fmaf(wgt[i], cvec[i], val);
+    best = fminf(best, val);
+    if (val < -tol) { found = 1; break; }   // uniform across the block: every thread holds the same sums
+    if (m == 1) break;
+    // Adam on the logits (torch.optim.Adam defaults), gradient through the softmax
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float dot = 0.f;
+      for (int i = 0; i < m; ++i) dot = fmaf(wgt[i], g[i], dot);
+      const float bc1 = 1.f - powf(0.9f, (float)(t + 1)), bc2 = 1.f - powf(0.999f, (float)(t + 1));
+      for (int i = 0; i < m; ++i) {
+        const float gi = wgt[i] * (g[i] - dot);
+        am[i] = am[i] + 0.1f * (gi - am[i]);
+        av[i] = av[i] * 0.999f + 0.001f * gi * gi;
+        const float denom = sqrtf(av[i]) / sqrtf(bc2) + 1e-8f;
+        logit[i] -= (lr / bc1) * (am[i] / denom);
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    infeasible[d] = (found || best < -tol) ? 1 : 0;
+    if (best_value) best_value[d] = best;
+  }
+}
+
+}  // namespace bf
+
+extern "C" int bf_first_layer_certificate_max_halfspaces(void) { return bf::CERT_MAX_M; }
+
+extern "C" int bf_first_layer_certificate(const int8_t* split, int split_stride, const float* W1, const float* b1,
+                                          const float* mid, const float* rad, int* infeasible, float* best_value,
+                                          int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
+                                          bf_stream_t stream) {
+  BF_REQUIRE(split && W1 && mid && rad && infeasible, BF_E_INVALID, "bf_first_layer_certificate: null tensor");
+  BF_REQUIRE(B > 0 && n1 > 0 && n0 > 0 && steps > 0 && lr > 0.f && tol >= 0.f, BF_E_INVALID, "bf_first_layer_certificate: bad sizes or options");
+  BF_REQUIRE(split_stride == 0 || split_stride == n1, BF_E_INVALID, "bf_first_layer_certificate: split_stride must be 0 or n1");
+  const size_t smem = ((size_t)bf::CERT_MAX_M + 2) * n0 * sizeof(float);
+  BF_REQUIRE(smem <= 200 * 1024, BF_E_UNSUPPORTED, "bf_first_layer_certificate: input dimension %d too large for one block", n0);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(bf::first_layer_cert_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_done = true;
+  }
+  bf::first_layer_cert_kernel<<<B, bf::CERT_THREADS, smem, bf::as_stream(stream)>>>(split, split_stride, W1, b1, mid, rad, n1, n0, steps,
+                                                                                  lr, tol, infeasible, best_value, n_halfspaces);
+  BF_CHECK_LAUNCH("first_layer_cert_kernel");
+  return BF_OK;
+}

@@ -200,3 +200,50 @@ def make_split_domains(wl: Workload, root_pre: Sequence[Tuple[torch.Tensor, torc
             r, j = unstable[p]
             splits[r][d, j] = 1 if bool(sign[t]) else -1
     return splits
+
+
+def make_certificate_cases(seed: int = 1009):
+    """Small MLP 12-16-5 and split rows on its first ReLU that exercise the first-layer infeasibility
+    certificate: rows 1 and 2 of the first layer are negative multiples of row 0 (shifted down), so
+    "neuron 0 active" contradicts "neuron 1 active" (found with uniform weights) and "neuron 2 active"
+    (needs the optimiser: the best weights are 2/3, 1/3).  Returns (module, layers, x, lo, up, cases)
+    with cases = list of (name, int8 split row [16])."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    n0, n1, n2 = 12, 16, 5
+    W1 = torch.randn(n1, n0, generator=g) * math.sqrt(2.0 / n0)
+    b1 = torch.randn(n1, generator=g) * 0.1
+    W2 = torch.randn(n2, n1, generator=g) * math.sqrt(2.0 / n1)
+    b2 = torch.randn(n2, generator=g) * 0.1
+    x = torch.rand(1, n0, generator=g)
+    b1[0] = b1[0] - (W1[0] @ x[0] + b1[0])  # neuron 0 is zero at the centre: unstable over the box
+    W1[1], b1[1] = -W1[0], -b1[0] - 0.05
+    W1[2], b1[2] = -2.0 * W1[0], -2.0 * b1[0] - 0.09
+    lo, up = (x - 0.3).clamp(0, 1), (x + 0.3).clamp(0, 1)
+    params = {"W1": W1, "b1": b1, "W2": W2, "b2": b2}
+    ops = [TaskOp("linear", "fc1", ["input", "W1", "b1"], ["h1"]), TaskOp("relu", "relu1", ["h1"], ["r1"]),
+           TaskOp("linear", "fc2", ["r1", "W2", "b2"], ["out"])]
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    module = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": params})
+    layers = [{"op": "linear", "W": W1, "b": b1}, {"op": "relu"}, {"op": "linear", "W": W2, "b": b2}]
+
+    def row(**kw):
+        r = torch.zeros(n1, dtype=torch.int8)
+        for k, v in kw.items():
+            r[int(k[1:])] = v
+        return r
+
+    pre_l = (W1.clamp(min=0) @ lo[0] + W1.clamp(max=0) @ up[0] + b1)
+    pre_u = (W1.clamp(min=0) @ up[0] + W1.clamp(max=0) @ lo[0] + b1)
+    unstable = [int(j) for j in torch.nonzero((pre_l < 0) & (pre_u > 0)).reshape(-1) if int(j) > 2]
+    off = [int(j) for j in torch.nonzero(pre_u < 0).reshape(-1)]
+    cases = [
+        ("no_split", row()),
+        ("one_feasible", row(n0=1)),
+        ("pair_contradiction_uniform_weights", row(n0=1, n1=1)),
+        ("pair_contradiction_needs_steps", row(n0=1, n2=1)),
+        ("triple_with_bystander", row(**{"n0": 1, "n2": 1, f"n{unstable[0]}": -1})),
+        ("feasible_pair", row(**{f"n{unstable[0]}": 1, f"n{unstable[1]}": -1})),
+    ]
+    if off:
+        cases.append(("single_halfspace_infeasible", row(**{f"n{off[0]}": 1})))
+    return module, layers, x, lo, up, cases

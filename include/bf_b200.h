@@ -211,6 +211,23 @@ int bf_ibp_linear_lp(const float* center, const float* row_dev, const float* W, 
 int bf_concretize_lp(const float* A, const float* center, float eps, int p, const float* bias_in,
                      float* out, int side, int B, int S, int n0, bf_stream_t stream);
 
+/* First-layer infeasibility certificate per domain
+ *   replaces _is_infeasible_split_first_layer_convex_combo, boundflow/runtime/alpha_beta_crown.py:391-532
+ *            (half-spaces of a Linear first layer, _collect_first_layer_split_halfspaces 262-388), which the
+ *            reference evaluates for batch size 1 only; here every domain of the batch gets its own.
+ * split int8 [B,n1] (row stride split_stride: n1, or 0 for one shared row) on the FIRST ReLU, W1 [n1,n0],
+ * b1 [n1] or NULL, box mid/rad [B,n0].  Per domain: half-spaces s_j*(W1[j].x + b1[j]) >= 0 in ascending j;
+ * weights softmax(logits), logits start at 0; up to `steps` Adam(lr) steps on
+ * max_box (sum w_i a_i).x + sum w_i c_i, stopping at the first value < -tol (one half-space: tested directly).
+ * infeasible int32 [B]: 1 certificate found, 0 none, -1 not evaluated (more than
+ * bf_first_layer_certificate_max_halfspaces() half-spaces); best_value float [B] or NULL: smallest maximum
+ * seen; n_halfspaces int32 [B] or NULL. */
+int bf_first_layer_certificate_max_halfspaces(void);
+int bf_first_layer_certificate(const int8_t* split, int split_stride, const float* W1, const float* b1,
+                               const float* mid, const float* rad, int* infeasible, float* best_value,
+                               int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
+                               bf_stream_t stream);
+
 /* Verdict per domain: proven iff min over spec rows of the lower bound >= threshold - tol.
  *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895.
  * lower [B,S]; verdict int8 [B] (1 proven, 0 not); min_lower [B] or NULL. */

@@ -639,6 +639,43 @@ def alpha_gradient(layers: Layers, inp: InputSet, trace: ForwardTrace, C, alphas
 # ----------------------------------------------------------------------------
 # verdicts and soundness
 # ----------------------------------------------------------------------------
+def first_layer_certificate(W1: torch.Tensor, b1: Optional[torch.Tensor], inp: InputSet, split_row: torch.Tensor, *,
+                            steps: int = 200, lr: float = 0.1, tol: float = 1e-6):
+    """`_is_infeasible_split_first_layer_convex_combo` (alpha_beta_crown.py:391-532) for one domain
+    (`inp` has batch size 1) and a Linear first layer: half-spaces s_j*(W1[j].x + b1[j]) >= 0 of the
+    split neurons in ascending j (262-322); one half-space: its maximum over the input set (439-468);
+    else logits = 0, Adam(lr) on max_x (sum w_i a_i).x + sum w_i c_i with w = softmax(logits),
+    best value tracked before each update, early exit below -tol (470-512).
+    Returns (infeasible: bool, smallest value seen or None without half-spaces)."""
+    idx = torch.nonzero(split_row.reshape(-1) != 0).reshape(-1)
+    if idx.numel() == 0:
+        return False, None
+    sgn = split_row.reshape(-1)[idx].to(W1.dtype)
+    a_mat = (sgn.unsqueeze(1) * W1[idx]).detach()
+    c_vec = (sgn * (b1[idx] if b1 is not None else torch.zeros_like(sgn))).detach()
+
+    def value(a, c):
+        return concretize(inp, a.view(1, 1, -1), c.view(1, 1), "upper").squeeze()
+
+    if idx.numel() == 1:
+        v = float(value(a_mat[0], c_vec[0]))
+        return v < -float(tol), v
+    logits = torch.zeros(idx.numel(), dtype=W1.dtype, requires_grad=True)
+    opt = torch.optim.Adam([logits], lr=float(lr))
+    best = None
+    for _ in range(int(steps)):
+        w = torch.softmax(logits, dim=0)
+        ub = value((w.unsqueeze(1) * a_mat).sum(dim=0), (w * c_vec).sum())
+        v = float(ub.detach())
+        best = v if best is None or v < best else best
+        if v < -float(tol):
+            return True, best
+        opt.zero_grad(set_to_none=True)
+        ub.backward()
+        opt.step()
+    return best < -float(tol), best
+
+
 def verdict(lower: torch.Tensor, threshold: float = 0.0, tol: float = 1e-6) -> torch.Tensor:
     """bab.py:881-895: a domain is proven iff min over specs of the lower bound
     is >= threshold - tol."""

@@ -220,16 +220,40 @@ def gen_spec_fused_ibp() -> None:
     save("spec_fused_ibp.npz", **out)
 
 
+def gen_first_layer_certificate() -> None:
+    """`_is_infeasible_split_first_layer_convex_combo` on the certificate cases of workloads.py."""
+    from boundflow.runtime.alpha_beta_crown import _is_infeasible_split_first_layer_convex_combo
+
+    module, _layers, _x, lo, up, cases = W.make_certificate_cases()
+    src = module.get_entry_task()
+    ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    m = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(module.bindings["params"])})
+    spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+    out = {"names": np.array([n for n, _ in cases])}
+    flags, values = [], []
+    for _name, row in cases:
+        bad, reason, cert = _is_infeasible_split_first_layer_convex_combo(m, spec, relu_split_state={"h1": row.unsqueeze(0)})
+        flags.append(bool(bad))
+        values.append(float(cert["max_value"]) if cert is not None else np.nan)
+    out["infeasible"] = np.array(flags)
+    out["max_value"] = np.array(values)
+    out["split_rows"] = np.stack([r.numpy() for _n, r in cases])
+    save("first_layer_certificate.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
-    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp}
+    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
+            "first_layer_certificate": gen_first_layer_certificate}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
     gen_lp_ball()
     gen_shared_alpha()
     gen_spec_fused_ibp()
+    gen_first_layer_certificate()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

@@ -1,0 +1,65 @@
+"""First-layer infeasibility certificate per domain (`bf_first_layer_certificate`)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+def test_cases_match_reference_golden_and_oracle(dev, golden):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import first_layer_certificate
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    g = golden("first_layer_certificate.npz")
+    module, layers, _x, lo, up, cases = W.make_certificate_cases()
+    D = len(cases)
+    spec = InputSpec.box(value_name="input", lower=lo.expand(D, -1).contiguous().to(dev), upper=up.expand(D, -1).contiguous().to(dev))
+    rows = torch.stack([r for _n, r in cases]).to(dev)
+    flags, best, count = first_layer_certificate(module, spec, {"h1": rows})
+    flags, best, count = flags.cpu(), best.cpu(), count.cpu()
+    inp = O.box_input(lo, up)
+    for k, (name, row) in enumerate(cases):
+        assert int(count[k]) == int((row != 0).sum()), name
+        assert int(flags[k]) == int(bool(g["infeasible"][k])), name
+        o_bad, o_best = O.first_layer_certificate(layers[0]["W"], layers[0]["b"], inp, row)
+        assert bool(flags[k]) == o_bad, name
+        if o_best is not None:
+            # same trajectory as the oracle up to rounding; an exit one step apart moves the value slightly
+            assert abs(float(best[k]) - o_best) <= 0.25 * abs(o_best) + 1e-4, (name, float(best[k]), o_best)
+
+
+def test_shared_row_many_halfspaces_and_single_node_precheck(dev):
+    from boundflow_b200 import _lib
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import first_layer_certificate, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+
+    module, _layers, _x, lo, up, cases = W.make_certificate_cases()
+    case = dict(cases)
+    spec3 = InputSpec.box(value_name="input", lower=lo.expand(3, -1).contiguous().to(dev), upper=up.expand(3, -1).contiguous().to(dev))
+    # one split row shared by all domains (stride 0)
+    flags, _b, _c = first_layer_certificate(module, spec3, {"h1": case["pair_contradiction_needs_steps"].to(dev)})
+    assert flags.cpu().tolist() == [1, 1, 1]
+    assert int(_lib.load().bf_first_layer_certificate_max_halfspaces()) == 16
+    # no split on the first ReLU: nothing to test
+    wide = torch.zeros(16, dtype=torch.int8)
+    flags, _b, cnt = first_layer_certificate(module, spec3, {"h1": wide.to(dev)})
+    assert flags.cpu().tolist() == [0, 0, 0] and cnt.cpu().tolist() == [0, 0, 0]
+    # the single-node alpha-beta call returns the reference's "infeasible" result shape
+    spec1 = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    bounds, a, b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["pair_contradiction_uniform_weights"].unsqueeze(0).to(dev)},
+                                                   steps=2, lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "infeasible" and tuple(bounds.lower.shape) == (1, 1) and not a.alpha_by_relu_input
+    bounds, a, b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["feasible_pair"].unsqueeze(0).to(dev)},
+                                                   steps=2, lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 5)

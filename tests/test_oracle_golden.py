@@ -275,3 +275,17 @@ def test_spec_fused_ibp(golden):
         lo, up = O.ibp_linear_batched(l, u, torch.matmul(wl.C, Wl), torch.matmul(wl.C, bl))
         assert_close(lo, g[f"{tag}_lower"], f"{tag} lower")
         assert_close(up, g[f"{tag}_upper"], f"{tag} upper")
+
+
+def test_first_layer_certificate(golden):
+    g = golden("first_layer_certificate.npz")
+    _module, layers, _x, lo, up, cases = W.make_certificate_cases()
+    assert [n for n, _ in cases] == [str(n) for n in g["names"]]
+    inp = O.box_input(lo, up)
+    for k, (name, row) in enumerate(cases):
+        assert (row.numpy() == g["split_rows"][k]).all()
+        bad, best = O.first_layer_certificate(layers[0]["W"], layers[0]["b"], inp, row)
+        assert bad == bool(g["infeasible"][k]), name
+        if bad:
+            # the value at which the loop stopped; an early exit one step apart moves it, so compare loosely
+            assert best < -1e-6 and abs(best - float(g["max_value"][k])) <= 0.5 * abs(float(g["max_value"][k])) + 1e-3, name
