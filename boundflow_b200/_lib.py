@@ -63,6 +63,7 @@ SIGNATURES = {
     "bf_first_layer_certificate": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),
     "bf_ibp_linear_batched": (_i, [_p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _p]),
     "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _sz, _i, _i, _p]),
+    "bf_chain_crown_influence": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _p, _sz, _i, _i, _p]),
     "bf_chain_crown_onehot": (_i, [_p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _sz, _i, _i, _p]),
     "bf_row_dual_norms": (_i, [_p, _i, _i, _i, _f, _p, _p]),
     "bf_ibp_linear_lp": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),

@@ -324,10 +324,13 @@ def crown_from_trace(
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
     sides: Sequence[int] = (_lib.SIDE_LOWER, _lib.SIDE_UPPER),
     identity_rows: Optional[Tuple[int, int]] = None,
+    influence_out: Optional[List[torch.Tensor]] = None,
 ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Backward sweep(s) on the device; returns (lower, upper) [B,S] CUDA tensors.
     `identity_rows=(first, count)` stands for the spec whose rows are rows first..first+count-1 of
-    the identity (neuron-wise bounds of `output_value`); no spec tensor is built for it."""
+    the identity (neuron-wise bounds of `output_value`); no spec tensor is built for it.
+    `influence_out` (an empty list) receives, per ReLU below the bounded value, the objective
+    influence max over the swept sides and the spec rows of |A| [B,n_r] (crown_ibp.py:1810-1834)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
     upto = chain.layers_upto(output_value)
     out_shape = chain.layers[upto - 1].out_shape
@@ -357,6 +360,12 @@ def crown_from_trace(
     nbytes = int(chain.lib.bf_chain_crown_workspace_bytes(chain.handle, B, S, upto))
     ws = _Workspace.get(device, nbytes)
     outs: List[Optional[torch.Tensor]] = [None, None]
+    infl = None
+    if influence_out is not None:
+        if C is None:
+            raise NotImplementedError("objective influence needs a spec tensor")
+        infl = [torch.zeros(B, chain.relu_widths[r], dtype=torch.float32, device=device) for r in range(n_relu)]
+        influence_out.extend(infl)
     for side in sides:
         out = torch.empty(B, S, dtype=torch.float32, device=device)
         tail = (
@@ -366,6 +375,8 @@ def crown_from_trace(
         )
         if C is None:
             _lib.check(chain.lib.bf_chain_crown_onehot(chain.handle, upto, side, first, *tail))
+        elif infl is not None:
+            _lib.check(chain.lib.bf_chain_crown_influence(chain.handle, upto, side, _lib.ptr(C), *tail[:9], _lib.ptr_array(infl), *tail[9:]))
         else:
             _lib.check(chain.lib.bf_chain_crown(chain.handle, upto, side, _lib.ptr(C), *tail))
         outs[side] = out
@@ -412,6 +423,28 @@ def run_crown_ibp_mlp_from_forward_trace(
     lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
     dev = normalize_input_spec(input_spec).center.device
     return IntervalState(lower=lo.to(dev), upper=up.to(dev))
+
+
+def run_crown_ibp_mlp_with_relu_influence_from_forward_trace(
+    module: Any,
+    input_spec: Any,
+    *,
+    interval_env: Mapping[str, Any],
+    relu_pre: Mapping[str, Any],
+    linear_spec_C: torch.Tensor,
+    output_value: Optional[str] = None,
+) -> Tuple[IntervalState, Dict[str, torch.Tensor]]:
+    """Bounds plus, per ReLU input, the influence max(max_s |A_u|, max_s |A_l|) of the backward
+    coefficients that reach it (crown_ibp.py:2201-2240), shaped like the pre-activation."""
+    trace = _trace_from_env(module, input_spec, interval_env, relu_pre)
+    infl: List[torch.Tensor] = []
+    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, influence_out=infl)
+    chain, B = trace.chain, trace.B
+    dev = normalize_input_spec(input_spec).center.device
+    if len(infl) != len(relu_pre):
+        raise ValueError("ReLU objective influence coverage differs")
+    out = {n: t.reshape((B,) + tuple(s)).to(dev) for n, t, s in zip(chain.relu_input_names, infl, chain.relu_shapes)}
+    return IntervalState(lower=lo.to(dev), upper=up.to(dev)), out
 
 
 def adaptive_alpha_from_trace(trace: ForwardTrace) -> List[torch.Tensor]:

@@ -400,7 +400,8 @@ extern "C" size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, i
 static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const float* C, int onehot_first,
                        const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
                        const float* const* add, const float* mid, const float* rad, int norm_p, float eps, float* out,
-                       void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+                       void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_,
+                       float* const* influence = nullptr) {
   BF_REQUIRE(chain && (C || onehot_first >= 0) && mid && out && workspace, BF_E_INVALID, "bf_chain_crown: null argument");
   BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
              "bf_chain_crown: bad norm");
@@ -441,6 +442,11 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
       if (add && add[pending] && side == BF_SIDE_LOWER) ad = add[pending];
     }
     int rc;
+    if (influence && pending >= 0 && influence[pending]) {
+      BF_REQUIRE(curA != nullptr, BF_E_UNSUPPORTED, "bf_chain_crown_influence: no coefficients reach this ReLU");
+      rc = bf::launch_colmax_abs(curA, influence[pending], B, S, chain->layers[chain->relu_layers[pending]].n_in, stream);
+      if (rc != BF_OK) return rc;
+    }
     if (curA == nullptr) {
       // identity spec rows: the first backward step copies weights instead of multiplying by them
       BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown_onehot: the bounded value must be the output of an affine layer");
@@ -482,6 +488,16 @@ extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, c
   BF_REQUIRE(C, BF_E_INVALID, "bf_chain_crown: null argument");
   return crown_sweep(chain, upto_layer, side, C, -1, alpha_u, beta_u, alpha_l, add, mid, rad, norm_p, eps, out, workspace,
                      workspace_bytes, B, S, stream);
+}
+
+extern "C" int bf_chain_crown_influence(const bf_chain* chain, int upto_layer, int side, const float* C,
+                                        const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                                        const float* const* add, const float* mid, const float* rad, int norm_p, float eps,
+                                        float* out, float* const* influence, void* workspace, size_t workspace_bytes, int B, int S,
+                                        bf_stream_t stream) {
+  BF_REQUIRE(C && influence, BF_E_INVALID, "bf_chain_crown_influence: null argument");
+  return crown_sweep(chain, upto_layer, side, C, -1, alpha_u, beta_u, alpha_l, add, mid, rad, norm_p, eps, out, workspace,
+                     workspace_bytes, B, S, stream, influence);
 }
 
 extern "C" int bf_chain_crown_onehot(const bf_chain* chain, int upto_layer, int side, int first_row,

@@ -333,6 +333,24 @@ int launch_shared_beta_add(const float* beta, const int8_t* split, int split_str
   return BF_OK;
 }
 
+// ---- objective influence of a ReLU: out[b, j] = max(out[b, j], max_s |A[b, s, j]|) --------------
+__global__ void __launch_bounds__(256) colmax_abs_kernel(const float* __restrict__ A, float* __restrict__ out, int S, int n) {
+  const int b = blockIdx.x;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const float* a = A + (size_t)b * S * n + j;
+  float m = out[(size_t)b * n + j];
+  for (int s = 0; s < S; ++s) m = fmaxf(m, fabsf(a[(size_t)s * n]));
+  out[(size_t)b * n + j] = m;
+}
+
+int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStream_t stream) {
+  dim3 grid(B, ceil_div(n, 256));
+  colmax_abs_kernel<<<grid, 256, 0, stream>>>(A, out, S, n);
+  BF_CHECK_LAUNCH("colmax_abs_kernel");
+  return BF_OK;
+}
+
 // ---- adaptive alpha start ------------------------------------------------------
 __global__ void alpha_adaptive_init_kernel(const float* __restrict__ l, const float* __restrict__ u, float* __restrict__ alpha,
                                            long long total) {

@@ -60,6 +60,7 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
                      const float* pre_l, const float* pre_u, float* slope_l, AdamScalars sc, int do_update, int B, int n,
                      cudaStream_t stream);
 int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream);
+int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStream_t stream);
 // shared-alpha mode (one alpha per neuron for the whole batch)
 int launch_shared_metric(const float* cur, long long M, float* best_metric, int* improve, int first, cudaStream_t stream);
 int launch_copy_if(const float* src, float* dst, long long n, const int* flag, cudaStream_t stream);

@@ -300,6 +300,20 @@ int bf_chain_crown(const bf_chain* chain, int upto_layer, int side,
                    const float* mid, const float* rad, int norm_p, float eps, float* out,
                    void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
+/* bf_chain_crown that also records the objective influence of every ReLU below the bounded value:
+ * influence[r][b, j] = max(influence[r][b, j], max_s |A[b, s, j]|) with A the coefficients that reach
+ * ReLU r in this sweep.  Calling it for both sides on zero-filled buffers gives
+ * max(max_s |A_u|, max_s |A_l|), the tensor run_crown_ibp_mlp_with_relu_influence_from_forward_trace
+ * returns (boundflow/runtime/crown_ibp.py:1810-1834, 2201-2240).  influence: HOST array of device
+ * pointers [B,n_r] (NULL entries are skipped). */
+int bf_chain_crown_influence(const bf_chain* chain, int upto_layer, int side,
+                             const float* C,
+                             const float* const* alpha_u, const float* const* beta_u, const float* const* alpha_l,
+                             const float* const* add,
+                             const float* mid, const float* rad, int norm_p, float eps, float* out,
+                             float* const* influence,
+                             void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
 /* bf_chain_crown for spec rows that are rows first_row .. first_row+S-1 of the identity, the same
  * for every domain: the sweeps that bound an intermediate value neuron by neuron
  * (run_crown_ibp_mlp_from_forward_trace(output_value=name, linear_spec_C=I_chunk) as composed in

@@ -351,6 +351,7 @@ def crown_backward(
     alpha: Optional[Sequence[Optional[torch.Tensor]]] = None,
     add_l: Optional[Sequence[Optional[torch.Tensor]]] = None,
     upto: Optional[int] = None,
+    influence_out: Optional[List[torch.Tensor]] = None,
 ):
     """`_run_crown_backward_from_trace`, crown_ibp.py:1669-2051, for chains.
 
@@ -359,7 +360,9 @@ def crown_backward(
     [S,O], broadcast; or None = identity, crown_ibp.py:672-719).  `alpha[i]`
     overrides the i-th ReLU's lower slope, `add_l[i]` is the beta term added to
     the lower coefficients (alpha_beta_crown.py:615-640).  Returns (lower, upper)
-    both [B,S].
+    both [B,S].  `influence_out` (a list) receives, per ReLU in chain order, the objective
+    influence max(max_s |A_u|, max_s |A_l|) [B,n_r] of the coefficients that reach the ReLU
+    (crown_ibp.py:1810-1834).
     """
     n_layers = len(layers) if upto is None else int(upto)
     B = inp.mid.shape[0]
@@ -390,6 +393,8 @@ def crown_backward(
         elif op == "relu":
             r = relu_ids.index(idx)
             l, u = trace.pre[r]
+            if influence_out is not None:
+                influence_out.insert(0, torch.maximum(A_u.abs().amax(dim=1), A_l.abs().amax(dim=1)))
             a = alpha[r] if alpha is not None else None
             alpha_u, beta_u, alpha_l, beta_l = relu_slopes(l, u, a)
             add = add_l[r] if add_l is not None else None

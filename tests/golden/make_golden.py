@@ -242,11 +242,30 @@ def gen_first_layer_certificate() -> None:
     save("first_layer_certificate.npz", **out)
 
 
+def gen_relu_influence() -> None:
+    """`run_crown_ibp_mlp_with_relu_influence_from_forward_trace` on the MLP c1 (8 inputs) and the CNN c2 (3 inputs)."""
+    from boundflow.runtime.crown_ibp import run_crown_ibp_mlp_with_relu_influence_from_forward_trace
+
+    out = {}
+    for tag, batch in (("c1", 8), ("c2", 3)):
+        wl = W.make_workload(tag, batch=batch)
+        m = ref_module(wl)
+        spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+        interval_env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        bounds, infl = run_crown_ibp_mlp_with_relu_influence_from_forward_trace(
+            m, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=wl.C)
+        out[f"{tag}_input_checksum"] = checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])
+        out[f"{tag}_lower"], out[f"{tag}_upper"] = bounds.lower, bounds.upper
+        for n in wl.relu_names:
+            out[f"{tag}_influence_{n}"] = infl[n].reshape(batch, -1)
+    save("relu_influence.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
-            "first_layer_certificate": gen_first_layer_certificate}
+            "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
@@ -254,6 +273,7 @@ def main() -> None:
     gen_shared_alpha()
     gen_spec_fused_ibp()
     gen_first_layer_certificate()
+    gen_relu_influence()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

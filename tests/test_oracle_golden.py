@@ -289,3 +289,19 @@ def test_first_layer_certificate(golden):
         if bad:
             # the value at which the loop stopped; an early exit one step apart moves it, so compare loosely
             assert best < -1e-6 and abs(best - float(g["max_value"][k])) <= 0.5 * abs(float(g["max_value"][k])) + 1e-3, name
+
+
+def test_relu_objective_influence(golden):
+    g = golden("relu_influence.npz")
+    for tag, batch in (("c1", 8), ("c2", 3)):
+        wl = W.make_workload(tag, batch=batch)
+        assert np.allclose(workload_checksum(wl), g[f"{tag}_input_checksum"], rtol=1e-12, atol=0)
+        inp = O.box_input(wl.lo, wl.up)
+        trace = O.forward_ibp_trace(wl.layers, inp)
+        infl = []
+        lo, up = O.crown_backward(wl.layers, inp, trace, wl.C, influence_out=infl)
+        assert_close(lo, g[f"{tag}_lower"], "lower")
+        assert_close(up, g[f"{tag}_upper"], "upper")
+        assert len(infl) == len(wl.relu_names)
+        for r, n in enumerate(wl.relu_names):
+            assert_close(infl[r].reshape(batch, -1), g[f"{tag}_influence_{n}"], f"{tag} influence {n}")
