@@ -59,6 +59,11 @@ SIGNATURES = {
     "bf_chain_tc_status": (_i, [_p, C.POINTER(_i)]),
     "bf_chain_ibp": (_i, [_p, _p, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "bf_chain_crown_workspace_bytes": (_sz, [_p, _i, _i, _i]),
+    "bf_crown_relu_bwd_scratch_bytes": (_sz, [_i, _i, _i]),
+    "bf_crown_relu_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _p, _sz, _i, _i, _i, _p]),
+    "bf_accumulate": (_i, [_p, _p, C.c_longlong, _p]),
+    "bf_interval_relu": (_i, [_p, _p, _p, _p, C.c_longlong, _p]),
+    "bf_interval_add": (_i, [_p, _p, _p, _p, _p, _p, C.c_longlong, _p]),
     "bf_first_layer_certificate_max_halfspaces": (_i, []),
     "bf_first_layer_certificate": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),
     "bf_ibp_linear_batched": (_i, [_p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _p]),

@@ -383,6 +383,18 @@ def crown_from_trace(
     return outs[0], outs[1]
 
 
+def needs_graph_path(module: Any) -> bool:
+    """True when the entry task is not a chain: an op merges values (add, concat) or does not consume
+    the previous op's output (fan-out, skip connections)."""
+    task = module.get_entry_task()
+    cur = task.input_values[0] if task.input_values else None
+    for op in task.ops:
+        if op.op_type in ("add", "concat") or not op.inputs or op.inputs[0] != cur:
+            return True
+        cur = op.outputs[0]
+    return False
+
+
 def run_crown_ibp_mlp(
     module: Any,
     input_spec: Any,
@@ -394,9 +406,16 @@ def run_crown_ibp_mlp(
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
     relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
 ) -> IntervalState:
-    """IBP trace + one CROWN backward sweep per side (crown_ibp.py:2054-2133)."""
+    """IBP trace + one CROWN backward sweep per side (crown_ibp.py:2054-2133).  Graphs with add / concat /
+    fan-out go through the general graph path (`dag.py`), chains through the fused sweeps."""
     if relu_pre_add_coeff_u:
         raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
+    if needs_graph_path(module):
+        if relu_alpha or relu_pre_add_coeff_l or relu_split_state:
+            raise NotImplementedError("alpha / beta / split inputs are supported on chain graphs only")
+        from .dag import run_crown_ibp_dag
+
+        return run_crown_ibp_dag(module, input_spec, linear_spec_C=linear_spec_C, output_value=output_value)
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)

@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_
   const int lam_words = nrows * NLT;                     // [MR][cc][LH][NLT]
   const int w_row = KS * cib + 4;                        // one kernel row of weights + 16 bytes: rows r and r+1 (image rows of
                                                          // different parity read them in one instruction) fall into different banks
-  const int w_words = cc * KS * w_row;                   // [cc][KS][KS*cib + 4]
+  const int w_words = (cc * KS * w_row + 3) & ~3;        // [cc][KS][KS*cib + 4], padded so that the second buffer stays 16-byte aligned
   const int buf_words = lam_words + w_words;
   constexpr int ROW_ZERO = -2147483647 - 1;
   int* row_off = reinterpret_cast<int*>(rs_smem + 2 * buf_words);  // [nrows] source offset of each tile row, ROW_ZERO: all zeros
@@ -501,7 +501,9 @@ static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
   if (cc < 1) return BF_E_UNSUPPORTED;
   while (g.Co % cc != 0) --cc;  // a divisor of Co: every chunk is full
   a.cc = cc;
-  const size_t smem = 2 * per_co * cc + (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * sizeof(int);
+  const size_t lam_words = (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * nlt;
+  const size_t w_words = ((size_t)cc * KS * (KS * cib + 4) + 3) & ~(size_t)3;
+  const size_t smem = 2 * (lam_words + w_words) * sizeof(float) + (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * sizeof(int);
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
@@ -741,6 +743,42 @@ extern "C" int bf_crown_relu_conv2d_bwd(const float* A, int side, const float* a
   L.sh = sh; L.sw = sw; L.ph = ph; L.pw = pw; L.n_in = Ci * Hi * Wi; L.n_out = Co * Ho * Wo;
   return bf::launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, W, bias, A_prev, delta, accumulate, B * S, S, L, scratch,
                                      bf::as_stream(stream));
+}
+
+// ReLU backward alone (graphs where the ReLU's producer is not a single affine layer, e.g. after an add):
+// A_prev = A * slope_sel, delta (+)= sum A * icpt_sel (+ add term on the lower side is not needed here).
+extern "C" size_t bf_crown_relu_bwd_scratch_bytes(int B, int S, int n) {
+  return (size_t)B * S * bf::ceil_div(n, bf::RELU_ROWS_CHUNK) * sizeof(float);
+}
+
+extern "C" int bf_crown_relu_bwd(const float* A, int side, const float* alpha_u, const float* alpha_l, const float* beta_u,
+                                 const float* beta_l, float* A_prev, float* delta, int accumulate, void* scratch,
+                                 size_t scratch_bytes, int B, int S, int n, bf_stream_t stream_) {
+  BF_REQUIRE(A && alpha_u && alpha_l && A_prev, BF_E_INVALID, "bf_crown_relu_bwd: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "bf_crown_relu_bwd: bad sizes");
+  BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_crown_relu_bwd: bad side");
+  const float *dpos, *dneg, *epos, *eneg;
+  if (side == BF_SIDE_LOWER) { dpos = alpha_l; dneg = alpha_u; epos = beta_l; eneg = beta_u; }
+  else { dpos = alpha_u; dneg = alpha_l; epos = beta_u; eneg = beta_l; }
+  const int M = B * S;
+  const int nchunks = bf::ceil_div(n, bf::RELU_ROWS_CHUNK);
+  float* partial = nullptr;
+  if (delta && nchunks > 1) {
+    BF_REQUIRE(scratch && scratch_bytes >= bf_crown_relu_bwd_scratch_bytes(B, S, n), BF_E_WORKSPACE,
+               "bf_crown_relu_bwd: scratch of %zu bytes needed", bf_crown_relu_bwd_scratch_bytes(B, S, n));
+    partial = static_cast<float*>(scratch);
+  }
+  BF_REQUIRE(nchunks <= 65535, BF_E_UNSUPPORTED, "bf_crown_relu_bwd: layer too wide");
+  const void* ptrs[] = {A, dpos, dneg, epos, eneg, A_prev};
+  int vec = (n % 4 == 0) ? 1 : 0;
+  for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = 0;
+  cudaStream_t stream = bf::as_stream(stream_);
+  dim3 grid(M, nchunks);
+  bf::relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, nullptr, 1, A_prev, partial, delta, accumulate,
+                                                    bf::RELU_ROWS_CHUNK, S, n, vec);
+  BF_CHECK_LAUNCH("relu_bwd_rows_kernel");
+  if (partial) return bf::launch_sum_partials(accumulate ? delta : nullptr, partial, nchunks, delta, M, stream);
+  return BF_OK;
 }
 
 // ---------------------------------------------------------------------------

@@ -380,6 +380,49 @@ int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdi
 
 }  // namespace bf
 
+// ---- small interval / coefficient helpers for graphs that are not chains --------------------------
+namespace bf {
+__global__ void interval_relu_kernel(const float* __restrict__ l, const float* __restrict__ u, float* __restrict__ ol,
+                                     float* __restrict__ ou, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    ol[i] = fmaxf(l[i], 0.f);
+    ou[i] = fmaxf(u[i], 0.f);
+  }
+}
+__global__ void interval_add_kernel(const float* __restrict__ al, const float* __restrict__ au, const float* __restrict__ bl,
+                                    const float* __restrict__ bu, float* __restrict__ ol, float* __restrict__ ou, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    ol[i] = al[i] + bl[i];
+    ou[i] = au[i] + bu[i];
+  }
+}
+__global__ void accumulate_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
+}
+}  // namespace bf
+
+extern "C" int bf_interval_relu(const float* l, const float* u, float* out_l, float* out_u, long long n, bf_stream_t stream) {
+  BF_REQUIRE(l && u && out_l && out_u && n > 0, BF_E_INVALID, "bf_interval_relu: bad argument");
+  bf::interval_relu_kernel<<<bf::ew_grid(n, 256), 256, 0, bf::as_stream(stream)>>>(l, u, out_l, out_u, n);
+  BF_CHECK_LAUNCH("interval_relu_kernel");
+  return BF_OK;
+}
+
+extern "C" int bf_interval_add(const float* a_l, const float* a_u, const float* b_l, const float* b_u, float* out_l, float* out_u,
+                               long long n, bf_stream_t stream) {
+  BF_REQUIRE(a_l && a_u && b_l && b_u && out_l && out_u && n > 0, BF_E_INVALID, "bf_interval_add: bad argument");
+  bf::interval_add_kernel<<<bf::ew_grid(n, 256), 256, 0, bf::as_stream(stream)>>>(a_l, a_u, b_l, b_u, out_l, out_u, n);
+  BF_CHECK_LAUNCH("interval_add_kernel");
+  return BF_OK;
+}
+
+extern "C" int bf_accumulate(float* dst, const float* src, long long n, bf_stream_t stream) {
+  BF_REQUIRE(dst && src && n > 0, BF_E_INVALID, "bf_accumulate: bad argument");
+  bf::accumulate_kernel<<<bf::ew_grid(n, 256), 256, 0, bf::as_stream(stream)>>>(dst, src, n);
+  BF_CHECK_LAUNCH("accumulate_kernel");
+  return BF_OK;
+}
+
 extern "C" int bf_relu_relax(const float* l, const float* u, const float* alpha, int alpha_stride, float* alpha_u,
                              float* beta_u, float* alpha_l, int B, int n, bf_stream_t stream) {
   BF_REQUIRE(l && u && alpha_u && beta_u && alpha_l, BF_E_INVALID, "bf_relu_relax: null tensor");

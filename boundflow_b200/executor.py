@@ -18,7 +18,7 @@ from typing import Any, Dict, Optional
 import torch
 
 from . import _lib
-from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace
+from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace, needs_graph_path
 from .ir import IntervalState, input_mid_rad, normalize_input_spec
 from .network import _pair
 
@@ -92,16 +92,28 @@ class CudaIntervalDomain:
     def relu_transformer(self, state_in: Any) -> IntervalState:
         if not (hasattr(state_in, "lower") and hasattr(state_in, "upper")):
             raise TypeError(f"IntervalDomain expects IntervalState, got {type(state_in)}")
-        # The clamp itself is fused into the consuming affine kernel (relu_in); as a
-        # stand-alone transformer it is a pure elementwise view-level op.
-        return IntervalState(lower=state_in.lower.clamp_min(0), upper=state_in.upper.clamp_min(0))
+        # In chains the clamp is fused into the consuming affine kernel (relu_in); stand-alone it is one elementwise kernel.
+        lib = _lib.load()
+        device = _cuda_device(state_in.lower)
+        l, u = _f32(state_in.lower, device), _f32(state_in.upper, device)
+        ol, ou = torch.empty_like(l), torch.empty_like(u)
+        _lib.check(lib.bf_interval_relu(_lib.ptr(l), _lib.ptr(u), _lib.ptr(ol), _lib.ptr(ou), l.numel(), _stream_ptr(device)))
+        return IntervalState(lower=ol.to(state_in.lower.device), upper=ou.to(state_in.lower.device))
 
     def elementwise_transformer(self, states_in, op: str) -> IntervalState:
         if len(states_in) != 2:
             raise ValueError(f"elementwise '{op}' expects 2 inputs, got {len(states_in)}")
         a, b = states_in
         if op == "add":
-            return IntervalState(lower=a.lower + b.lower, upper=a.upper + b.upper)
+            if tuple(a.lower.shape) != tuple(b.lower.shape):
+                raise NotImplementedError("elementwise add supports exact same-shape inputs only")
+            lib = _lib.load()
+            device = _cuda_device(a.lower)
+            al, au, bl, bu = (_f32(t, device) for t in (a.lower, a.upper, b.lower, b.upper))
+            ol, ou = torch.empty_like(al), torch.empty_like(au)
+            _lib.check(lib.bf_interval_add(_lib.ptr(al), _lib.ptr(au), _lib.ptr(bl), _lib.ptr(bu), _lib.ptr(ol), _lib.ptr(ou), al.numel(),
+                                           _stream_ptr(device)))
+            return IntervalState(lower=ol.to(a.lower.device), upper=ou.to(a.lower.device))
         raise NotImplementedError(f"unsupported elementwise op: {op}")
 
 
@@ -129,6 +141,10 @@ class CudaTaskExecutor:
         w_last = params.get(last.inputs[1]) if (last.op_type == "linear" and len(last.inputs) >= 2 and isinstance(params, dict)) else None
         if torch.is_tensor(w_last) and w_last.dim() == 3:
             return self._run_ibp_spec_fused(module, task, spec, output_value)
+        if needs_graph_path(module):
+            from .dag import run_ibp_dag
+
+            return run_ibp_dag(module, spec, output_value=output_value)
         trace = ibp_trace(module, spec)
         chain = trace.chain
         dev = spec.center.device

@@ -247,3 +247,69 @@ def make_certificate_cases(seed: int = 1009):
     if off:
         cases.append(("single_halfspace_infeasible", row(**{f"n{off[0]}": 1})))
     return module, layers, x, lo, up, cases
+
+
+def make_graph_cases(seed: int = 1011):
+    """Small graphs that are not chains, shaped like the reference's end-to-end fixtures
+    (tests/test_phase7a_pr12_e2e_crown_runtime.py:98-239): a residual CNN block with a projection skip
+    (stride 1 and stride 2), an MLP whose hidden value feeds a ReLU path and a direct path (fan-out),
+    and a two-block mini ResNet.  Returns {name: (module, x, lo, up, C)}; weights are scaled He-normal."""
+    g = torch.Generator("cpu").manual_seed(seed)
+
+    def rn(*shape, fan):
+        return torch.randn(*shape, generator=g) * math.sqrt(2.0 / fan)
+
+    def mod(tid, ops, params):
+        task = BoundTask(task_id=tid, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        return BFTaskModule(tasks=[task], entry_task_id=tid, bindings={"params": params})
+
+    def box(x, eps):
+        return (x - eps).clamp(0, 1), (x + eps).clamp(0, 1)
+
+    cases = {}
+    for name, down in (("residual_s1", False), ("residual_s2", True)):
+        st, sp = ((2, 2), 4) if down else ((1, 1), 7)
+        ops = [
+            TaskOp("conv2d", "main1", ["input", "wm1", "bm1"], ["hm1"], {"stride": st, "padding": (1, 1), "dilation": (1, 1), "groups": 1}),
+            TaskOp("relu", "main_relu", ["hm1"], ["rm1"]),
+            TaskOp("conv2d", "main2", ["rm1", "wm2", "bm2"], ["hm2"], {"stride": (1, 1), "padding": (1, 1), "dilation": (1, 1), "groups": 1}),
+            TaskOp("conv2d", "skip", ["input", "ws", "bs"], ["hs"], {"stride": st, "padding": (0, 0), "dilation": (1, 1), "groups": 1}),
+            TaskOp("add", "merge", ["hm2", "hs"], ["sum"]),
+            TaskOp("relu", "out_relu", ["sum"], ["rout"]),
+            TaskOp("flatten", "flatten", ["rout"], ["flat"], {"start_dim": 1, "end_dim": -1}),
+            TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"]),
+        ]
+        params = {"wm1": rn(3, 2, 3, 3, fan=18), "bm1": rn(3, fan=200), "wm2": rn(3, 3, 3, 3, fan=27), "bm2": rn(3, fan=200),
+                  "ws": rn(3, 2, 1, 1, fan=2), "bs": rn(3, fan=200), "wh": rn(4, 3 * sp * sp, fan=3 * sp * sp), "bh": rn(4, fan=200)}
+        x = torch.rand(3, 2, 7, 7, generator=g)
+        cases[name] = (mod(name, ops, params), x) + box(x, 0.05) + (None,)
+    ops = [
+        TaskOp("linear", "shared", ["input", "w1", "b1"], ["h"]), TaskOp("relu", "relu", ["h"], ["r"]),
+        TaskOp("linear", "direct", ["h", "wd", "bd"], ["d"]), TaskOp("linear", "relu_path", ["r", "wr", "br"], ["q"]),
+        TaskOp("add", "merge", ["d", "q"], ["out"]),
+    ]
+    params = {"w1": rn(24, 10, fan=10), "b1": rn(24, fan=200), "wd": rn(6, 24, fan=24), "bd": rn(6, fan=200), "wr": rn(6, 24, fan=24), "br": rn(6, fan=200)}
+    x = torch.rand(5, 10, generator=g)
+    cases["fanout_mlp"] = (mod("fanout", ops, params), x) + box(x, 0.1) + (torch.randn(5, 3, 6, generator=g),)
+    conv = {"stride": (1, 1), "padding": (1, 1), "dilation": (1, 1), "groups": 1}
+    down = {"stride": (2, 2), "padding": (1, 1), "dilation": (1, 1), "groups": 1}
+    proj = {"stride": (2, 2), "padding": (0, 0), "dilation": (1, 1), "groups": 1}
+    ops = [
+        TaskOp("conv2d", "stem", ["input", "ws", "bs"], ["hs"], conv), TaskOp("relu", "stem_relu", ["hs"], ["r0"]),
+        TaskOp("conv2d", "b1c1", ["r0", "w11", "b11"], ["h11"], conv), TaskOp("relu", "b1_relu", ["h11"], ["r11"]),
+        TaskOp("conv2d", "b1c2", ["r11", "w12", "b12"], ["h12"], conv), TaskOp("add", "b1_add", ["r0", "h12"], ["s1"]),
+        TaskOp("relu", "b1_out", ["s1"], ["r1"]),
+        TaskOp("conv2d", "b2c1", ["r1", "w21", "b21"], ["h21"], down), TaskOp("relu", "b2_relu", ["h21"], ["r21"]),
+        TaskOp("conv2d", "b2c2", ["r21", "w22", "b22"], ["h22"], conv), TaskOp("conv2d", "b2_skip", ["r1", "wp", "bp"], ["hp"], proj),
+        TaskOp("add", "b2_add", ["h22", "hp"], ["s2"]), TaskOp("relu", "b2_out", ["s2"], ["r2"]),
+        TaskOp("flatten", "flatten", ["r2"], ["flat"], {"start_dim": 1, "end_dim": -1}),
+        TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"]),
+    ]
+    c0, c1 = 4, 6
+    params = {"ws": rn(c0, 3, 3, 3, fan=27), "bs": rn(c0, fan=200), "w11": rn(c0, c0, 3, 3, fan=9 * c0), "b11": rn(c0, fan=200),
+              "w12": rn(c0, c0, 3, 3, fan=9 * c0), "b12": rn(c0, fan=200), "w21": rn(c1, c0, 3, 3, fan=9 * c0), "b21": rn(c1, fan=200),
+              "w22": rn(c1, c1, 3, 3, fan=9 * c1), "b22": rn(c1, fan=200), "wp": rn(c1, c0, 1, 1, fan=c0), "bp": rn(c1, fan=200),
+              "wh": rn(5, c1 * 4 * 4, fan=c1 * 16), "bh": rn(5, fan=200)}
+    x = torch.rand(2, 3, 8, 8, generator=g)
+    cases["mini_resnet"] = (mod("mini_resnet", ops, params), x) + box(x, 0.02) + (None,)
+    return cases

@@ -156,6 +156,23 @@ int bf_crown_relu_conv2d_bwd(const float* A, int side,
                              int B, int S, int Ci, int Hi, int Wi, int Co, int Ho, int Wo,
                              int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
 
+/* Building blocks for graphs that are not chains (residual add, fan-out): the reference routes them in
+ * _run_crown_backward_from_trace, boundflow/runtime/crown_ibp.py:1748-2030.
+ *   bf_crown_relu_bwd: ReLU backward alone, _backprop_relu_step_dense_reference crown_ibp.py:1211-1298:
+ *            A_prev = A * slope_sel, delta (+)= sum_k A * intercept_sel.  A, A_prev [B,S,n] (may alias);
+ *            slopes [B,n]; scratch (bf_crown_relu_bwd_scratch_bytes) only for n > 4096 with delta.
+ *   bf_accumulate: dst += src, _accumulate_backward_state crown_ibp.py:879-913.
+ *   bf_interval_relu / bf_interval_add: IntervalDomain.relu_transformer / elementwise_transformer("add"),
+ *            boundflow/domains/interval.py:88-110. */
+size_t bf_crown_relu_bwd_scratch_bytes(int B, int S, int n);
+int bf_crown_relu_bwd(const float* A, int side, const float* alpha_u, const float* alpha_l,
+                      const float* beta_u, const float* beta_l, float* A_prev, float* delta, int accumulate,
+                      void* scratch, size_t scratch_bytes, int B, int S, int n, bf_stream_t stream);
+int bf_accumulate(float* dst, const float* src, long long n, bf_stream_t stream);
+int bf_interval_relu(const float* l, const float* u, float* out_l, float* out_u, long long n, bf_stream_t stream);
+int bf_interval_add(const float* a_l, const float* a_u, const float* b_l, const float* b_u,
+                    float* out_l, float* out_u, long long n, bf_stream_t stream);
+
 /* Allocation-free variant of bf_crown_relu_conv2d_bwd.  It has no counterpart in the
  * reference.  It exists for callers that cannot hand over (or obtain) device scratch when
  * they call: services whose device pool is sized at start-up and then frozen, plugins loaded

@@ -261,11 +261,28 @@ def gen_relu_influence() -> None:
     save("relu_influence.npz", **out)
 
 
+def gen_graph_cases() -> None:
+    """IBP and CROWN-IBP of the non-chain graphs of workloads.make_graph_cases (residual add, fan-out)."""
+    out = {}
+    for name, (module, _x, lo, up, C) in W.make_graph_cases().items():
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        ibp = PythonTaskExecutor().run_ibp(m, spec)
+        crown = run_crown_ibp_mlp(m, spec, linear_spec_C=C)
+        out[f"{name}_ibp_lower"], out[f"{name}_ibp_upper"] = ibp.lower, ibp.upper
+        out[f"{name}_crown_lower"], out[f"{name}_crown_upper"] = crown.lower, crown.upper
+    save("graph_cases.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
-            "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence}
+            "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
+            "graph_cases": gen_graph_cases}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
@@ -274,6 +291,7 @@ def main() -> None:
     gen_spec_fused_ibp()
     gen_first_layer_certificate()
     gen_relu_influence()
+    gen_graph_cases()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")
