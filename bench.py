@@ -62,7 +62,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu_index)],
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -337,11 +337,11 @@ def main():
     n_a, t_a = ctypes.c_int(), ctypes.c_float()
     lib.bf_kernel_timing_read(1, ctypes.byref(n_a), ctypes.byref(t_a))
     lib.bf_kernel_timing_enable(0)
-    clocks = sampler.stop() if rank == 0 else None
 
     for _ in range(2):
         step_e2e()
     ms_e2e, out_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions (resident and end-to-end)
 
     secondary = crown_bounds_secondary(world, rank, dev)
 
