@@ -163,12 +163,12 @@ struct Control {
   int abort_flag;
 };
 
-// Work split of one CTA (320 threads):
-//   warps 0-7  A producers during the main loop (4 tile rows x one 16-byte chunk per thread and
-//              k-block), then the epilogue (warp w reads TMEM lane quarter w%4, column chunks of
-//              parity w/4)
-//   warp 8     lane 0 issues the bulk copies of the packed weight images
-//   warp 9     lane 0 issues the MMAs; the warp allocates / frees tensor memory
+// Work split of one CTA (THREADS = 576):
+//   warps 0-15  A producers during the main loop (ROWS_PER_THREAD tile rows x one 16-byte chunk per
+//               thread and k-block), then the epilogue (warp w reads TMEM lane quarter w%4, column
+//               chunks w/4, w/4 + COL_PARTS, ...)
+//   warp 16     lane 0 issues the bulk copies of the packed weight images
+//   warp 17     lane 0 issues the MMAs; the warp allocates / frees tensor memory
 // A CTA owns 128 rows and up to two column sub-tiles of BN columns (accumulators side by side in
 // tensor memory), so one produced A k-block feeds two sets of MMAs.
 template <int MODE, int PRO>
