@@ -74,13 +74,13 @@ SIGNATURES = {
     "bf_ibp_linear_lp": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "bf_concretize_lp": (_i, [_p, _p, _f, _i, _p, _p, _i, _i, _i, _i, _p]),
     "bf_chain_alpha_workspace_bytes": (_sz, [_p, _i, _i]),
-    "bf_chain_alpha_crown": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_crown": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_beta_workspace_bytes": (_sz, [_p, _i, _i]),
-    "bf_chain_alpha_beta_crown": (_i, [_p] * 12 + [_p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_beta_crown": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
     "bf_branch_scores": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _p]),
-    "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_shared_workspace_bytes": (_sz, [_p, _i, _i, _i]),
-    "bf_chain_alpha_crown_shared": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_crown_shared": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _p, _sz, _i, _i, _p]),
 }
 
 _lib: Optional[C.CDLL] = None

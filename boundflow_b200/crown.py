@@ -495,8 +495,6 @@ def alpha_crown_from_trace(
     element best_beta list.  `beta_splits[r]` is the int8 split assignment [B,n_r] or [1,n_r]
     of ReLU r (None = no split there)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
-    if trace.norm_p != _lib.NORM_BOX:
-        raise NotImplementedError("alpha-CROWN on L1/L2 balls is not supported by the CUDA backend (boxes and L-inf balls are)")
     if spec_reduce not in ("mean", "sum"):
         raise NotImplementedError(f"spec_reduce={spec_reduce!r} is not supported by the CUDA backend (mean | sum)")
     n_out = 1
@@ -516,7 +514,7 @@ def alpha_crown_from_trace(
         _lib.check(
             chain.lib.bf_chain_alpha_crown(
                 chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
-                _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+                _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
                 _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
                 int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
             )
@@ -543,7 +541,7 @@ def alpha_crown_from_trace(
         chain.lib.bf_chain_alpha_beta_crown(
             chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
             _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr_array(beta), _lib.ptr_array(best_beta),
-            _lib.ptr_array(splits), _lib.int_array(strides), _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+            _lib.ptr_array(splits), _lib.int_array(strides), _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
             _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
             int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
@@ -567,7 +565,7 @@ def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alph
     _lib.check(
         chain.lib.bf_chain_alpha_grad(
             chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.ptr_array(alpha),
-            _lib.ptr(trace.mid), _lib.ptr(trace.rad), _lib.ptr_array(grads), _lib.ptr(lower),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps), _lib.ptr_array(grads), _lib.ptr(lower),
             _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM,
             _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
@@ -583,8 +581,6 @@ def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[t
     whole batch; returns (best_lower, best_upper|None, best_alpha list [n_r], last alpha list,
     best_metric [1]) and, with beta, a sixth element best_beta list [n_r]."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
-    if trace.norm_p != _lib.NORM_BOX:
-        raise NotImplementedError("alpha-CROWN on L1/L2 balls is not supported by the CUDA backend (boxes and L-inf balls are)")
     n_out = 1
     for d in chain.output_shape:
         n_out *= int(d)
@@ -622,7 +618,7 @@ def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[t
             _lib.ptr_array(alpha), _lib.ptr_array(best_alpha),
             _lib.ptr_array(beta) if with_beta else None, _lib.ptr_array(best_beta) if with_beta else None,
             _lib.ptr_array(splits) if with_beta else None, _lib.int_array(strides) if with_beta else None,
-            _lib.ptr(trace.mid), _lib.ptr(trace.rad),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
             _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
             int(steps), float(lr), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )

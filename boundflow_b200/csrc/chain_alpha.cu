@@ -65,17 +65,31 @@ static size_t alpha_ws_layout(const bf_chain* c, int B, int S, bool with_beta, v
   return cv.off;
 }
 
+// The input set of a query: a box (mid, rad) or an Lp ball (mid = centre, eps, norm_p).
+struct InputSetArg {
+  const float* mid;
+  const float* rad;
+  int norm_p;
+  float eps;
+  bool box() const { return norm_p == BF_NORM_BOX; }
+};
+
 // One lower- or upper-side sweep with the relaxations in ws; `use_add` adds the split term of
 // every ReLU to the lower coefficients (beta-CROWN).
 static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int side, bool keep_A0, bool use_add,
-                       const float* mid, const float* rad, float* out, int B, int S, cudaStream_t stream) {
+                       const InputSetArg& in, float* out, int B, int S, cudaStream_t stream) {
   const int M = B * S;
   const int R = (int)c->relu_layers.size();
+  // a box is concretised inside the last layer's epilogue; an Lp ball needs the final coefficient rows
+  const bool box = in.box();
+  const float* mid = box ? in.mid : nullptr;
+  const float* rad = box ? in.rad : nullptr;
+  if (!box) keep_A0 = true;
   int rc;
   int ptiles = 1;
   if (R == 0) {
     rc = dispatch_bwd(c, 0, C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, ws.cacc, 0, mid, rad,
-                      ws.partial, side, M, S, &ptiles, stream);
+                      box ? ws.partial : nullptr, side, M, S, &ptiles, stream);
     if (rc != BF_OK) return rc;
   } else {
     rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], ws.cacc, 0, nullptr, nullptr,
@@ -89,24 +103,31 @@ static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int
       const bool last = (r == 0);
       float* dst = last ? (keep_A0 ? ws.A0 : nullptr) : ws.Ahat[r - 1];
       rc = dispatch_bwd(c, 2 * r, ws.Ahat[r], dpos, dneg, epos, eneg, add, dst, ws.cacc, 1, last ? mid : nullptr,
-                        last ? rad : nullptr, last ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
+                        last ? rad : nullptr, (last && box) ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
       if (rc != BF_OK) return rc;
     }
   }
+  if (!box) return launch_concretize_lp(ws.A0, in.mid, ws.cacc, out, side, in.eps, in.norm_p, B, S, c->n0, stream);
   return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
 }
 
 // Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r] and, with beta,
 // sum_s g_r[b,s,j] into ws.gsum[r].
 static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* const* pre_l, const float* const* pre_u,
-                         bool with_beta, const float* mid, const float* rad, int B, int S, cudaStream_t stream) {
+                         bool with_beta, const InputSetArg& in, int B, int S, cudaStream_t stream) {
   const int M = B * S;
   const int R = (int)c->relu_layers.size();
+  if (!in.box()) {  // Lp ball: the start vector needs a row norm, so it is written over the final coefficients first
+    int rc = launch_h0_lp(ws.A0, in.mid, in.eps, in.norm_p, B, S, c->n0, stream);
+    if (rc != BF_OK) return rc;
+  }
   for (int r = 0; r < R; ++r) {
     const float* hprev = (r == 0) ? ws.A0 : ws.H[(r - 1) & 1];
     float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
-    int rc = dispatch_adjoint(c, 2 * r, hprev, r == 0, mid, rad, ws.Ahat[r], ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r],
-                              pre_u[r], hout, ws.grad[r], with_beta ? ws.gsum[r] : nullptr, M, S, stream);
+    const bool from_box = (r == 0) && in.box();  // h_0 = mid - sgn(A_0) * rad is formed in the kernel's prologue
+    int rc = dispatch_adjoint(c, 2 * r, hprev, from_box ? 1 : 0, from_box ? in.mid : nullptr, from_box ? in.rad : nullptr, ws.Ahat[r],
+                              ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r],
+                              with_beta ? ws.gsum[r] : nullptr, M, S, stream);
     if (rc != BF_OK) return rc;
   }
   return BF_OK;
@@ -140,9 +161,13 @@ extern "C" size_t bf_chain_alpha_beta_workspace_bytes(const bf_chain* chain, int
 }
 
 static int alpha_common_checks(const char* who, const bf_chain* chain, const void* C, const void* pre_l, const void* pre_u,
-                               const void* alpha, const void* mid, const void* rad, void* workspace, size_t workspace_bytes,
-                               int B, int S, bool with_beta, bf::AlphaWs* ws) {
-  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && mid && rad && workspace, BF_E_INVALID, "%s: null argument", who);
+                               const void* alpha, const void* mid, const void* rad, int norm_p, float eps, void* workspace,
+                               size_t workspace_bytes, int B, int S, bool with_beta, bf::AlphaWs* ws) {
+  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && mid && workspace, BF_E_INVALID, "%s: null argument", who);
+  BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
+             "%s: bad norm", who);
+  BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "%s: a box needs its radius tensor", who);
+  BF_REQUIRE(norm_p == BF_NORM_BOX || eps >= 0.f, BF_E_INVALID, "%s: negative eps", who);
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "%s: bad B/S", who);
   BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
   const size_t need = bf::alpha_ws_layout(chain, B, S, with_beta, workspace, ws);
@@ -153,13 +178,15 @@ static int alpha_common_checks(const char* who, const bf_chain* chain, const voi
 extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, const float* const* pre_l,
                                          const float* const* pre_u, float* const* alpha, float* const* best_alpha,
                                          float* const* beta, float* const* best_beta, const int8_t* const* splits,
-                                         const int* split_strides, const float* mid, const float* rad, float* best_lower,
-                                         float* best_upper, float* best_metric, int steps, float lr, int spec_reduce,
-                                         void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+                                         const int* split_strides, const float* mid, const float* rad, int norm_p, float eps,
+                                         float* best_lower, float* best_upper, float* best_metric, int steps, float lr,
+                                         int spec_reduce, void* workspace, size_t workspace_bytes, int B, int S,
+                                         bf_stream_t stream_) {
   const bool with_beta = beta != nullptr;
+  const bf::InputSetArg in{mid, rad, norm_p, eps};
   const char* who = with_beta ? "bf_chain_alpha_beta_crown" : "bf_chain_alpha_crown";
   bf::AlphaWs ws;
-  int rc = alpha_common_checks(who, chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S, with_beta, &ws);
+  int rc = alpha_common_checks(who, chain, C, pre_l, pre_u, alpha, mid, rad, norm_p, eps, workspace, workspace_bytes, B, S, with_beta, &ws);
   if (rc != BF_OK) return rc;
   BF_REQUIRE(best_alpha && best_lower && steps >= 0, BF_E_INVALID, "%s: null output or negative steps", who);
   BF_REQUIRE(spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_SUM, BF_E_INVALID, "%s: bad spec_reduce", who);
@@ -185,13 +212,13 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
   }
   for (int t = 0; t <= steps; ++t) {
     const bool last = (t == steps);
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, mid, rad, ws.cur, B, S, stream);
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, in, ws.cur, B, S, stream);
     if (rc != BF_OK) return rc;
     rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, B, S, stream);
     if (rc != BF_OK) return rc;
     bf::AdamScalars sc{};
     if (!last) {
-      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, mid, rad, B, S, stream);
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, spec_reduce, S);
     }
@@ -214,7 +241,7 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
       rc = bf::launch_relu_relax(pre_l[r], pre_u[r], best_alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
       if (rc != BF_OK) return rc;
     }
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, mid, rad, best_upper, B, S, stream);
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, in, best_upper, B, S, stream);
     if (rc != BF_OK) return rc;
   }
   return BF_OK;
@@ -222,21 +249,22 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
 
 extern "C" int bf_chain_alpha_crown(const bf_chain* chain, const float* C, const float* const* pre_l,
                                     const float* const* pre_u, float* const* alpha, float* const* best_alpha,
-                                    const float* mid, const float* rad, float* best_lower, float* best_upper,
-                                    float* best_metric, int steps, float lr, int spec_reduce, void* workspace,
+                                    const float* mid, const float* rad, int norm_p, float eps, float* best_lower,
+                                    float* best_upper, float* best_metric, int steps, float lr, int spec_reduce, void* workspace,
                                     size_t workspace_bytes, int B, int S, bf_stream_t stream) {
-  return bf_chain_alpha_beta_crown(chain, C, pre_l, pre_u, alpha, best_alpha, nullptr, nullptr, nullptr, nullptr, mid, rad,
-                                   best_lower, best_upper, best_metric, steps, lr, spec_reduce, workspace, workspace_bytes, B, S,
+  return bf_chain_alpha_beta_crown(chain, C, pre_l, pre_u, alpha, best_alpha, nullptr, nullptr, nullptr, nullptr, mid, rad, norm_p,
+                                   eps, best_lower, best_upper, best_metric, steps, lr, spec_reduce, workspace, workspace_bytes, B, S,
                                    stream);
 }
 
 extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const float* const* pre_l,
                                    const float* const* pre_u, const float* const* alpha, const float* mid,
-                                   const float* rad, float* const* grad, float* lower, int spec_reduce, void* workspace,
-                                   size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+                                   const float* rad, int norm_p, float eps, float* const* grad, float* lower, int spec_reduce,
+                                   void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
   bf::AlphaWs ws;
-  int rc = alpha_common_checks("bf_chain_alpha_grad", chain, C, pre_l, pre_u, alpha, mid, rad, workspace, workspace_bytes, B, S,
-                               false, &ws);
+  const bf::InputSetArg in{mid, rad, norm_p, eps};
+  int rc = alpha_common_checks("bf_chain_alpha_grad", chain, C, pre_l, pre_u, alpha, mid, rad, norm_p, eps, workspace, workspace_bytes,
+                               B, S, false, &ws);
   if (rc != BF_OK) return rc;
   BF_REQUIRE(grad && lower, BF_E_INVALID, "bf_chain_alpha_grad: null output");
   cudaStream_t stream = bf::as_stream(stream_);
@@ -250,9 +278,9 @@ extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const 
     rc = bf::launch_relu_relax(pre_l[r], pre_u[r], alpha[r], n, ws.au[r], ws.bu[r], ws.sl[r], B, n, stream);
     if (rc != BF_OK) return rc;
   }
-  rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, true, false, mid, rad, lower, B, S, stream);
+  rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, true, false, in, lower, B, S, stream);
   if (rc != BF_OK) return rc;
-  rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, false, mid, rad, B, S, stream);
+  rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, false, in, B, S, stream);
   if (rc != BF_OK) return rc;
   const float scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
   for (int r = 0; r < R; ++r) {
@@ -305,12 +333,16 @@ extern "C" size_t bf_chain_alpha_shared_workspace_bytes(const bf_chain* chain, i
 extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C, const float* const* pre_l,
                                            const float* const* pre_u, float* const* alpha, float* const* best_alpha,
                                            float* const* beta, float* const* best_beta, const int8_t* const* splits,
-                                           const int* split_strides, const float* mid, const float* rad, float* best_lower,
-                                           float* best_upper, float* best_metric, int steps, float lr, void* workspace,
-                                           size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+                                           const int* split_strides, const float* mid, const float* rad, int norm_p, float eps,
+                                           float* best_lower, float* best_upper, float* best_metric, int steps, float lr,
+                                           void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
   const char* who = "bf_chain_alpha_crown_shared";
-  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && best_alpha && mid && rad && best_lower && workspace, BF_E_INVALID,
+  BF_REQUIRE(chain && C && pre_l && pre_u && alpha && best_alpha && mid && best_lower && workspace, BF_E_INVALID,
              "%s: null argument", who);
+  BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
+             "%s: bad norm", who);
+  BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "%s: a box needs its radius tensor", who);
+  const bf::InputSetArg in{mid, rad, norm_p, eps};
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL && steps >= 0, BF_E_INVALID, "%s: bad B/S/steps", who);
   BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
   const bool with_beta = beta != nullptr;
@@ -347,13 +379,13 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
       for (int r = 0; r < R; ++r)
         if (splits[r] && (rc = bf::launch_shared_beta_add(beta[r], splits[r], stride(r), ws.addv[r], B, width(r), stream)) != BF_OK)
           return rc;
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, mid, rad, ws.cur, B, S, stream);
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, in, ws.cur, B, S, stream);
     if (rc != BF_OK) return rc;
     if ((rc = bf::launch_shared_metric(ws.cur, M, metric, ws.improve, t == 0, stream)) != BF_OK) return rc;
     if ((rc = bf::launch_copy_if(ws.cur, best_lower, M, ws.improve, stream)) != BF_OK) return rc;
     bf::AdamScalars sc{};
     if (!last) {
-      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, mid, rad, B, S, stream);
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, BF_REDUCE_SUM, S);
       sc.grad_scale = -1.0f / (float)M;  // loss = -mean over every domain and spec row
@@ -373,7 +405,7 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   }
   if (best_upper) {  // beta acts on the lower side only
     if ((rc = relax_all(best_alpha)) != BF_OK) return rc;
-    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, mid, rad, best_upper, B, S, stream);
+    rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, in, best_upper, B, S, stream);
     if (rc != BF_OK) return rc;
   }
   return BF_OK;

@@ -254,6 +254,53 @@ int launch_concretize_lp(const float* A, const float* center, const float* bias_
   return BF_OK;
 }
 
+// Derivative of the Lp-ball lower bound  A.center - eps * ||A||_q  with respect to the coefficient row,
+// written over the row itself:  H[m,k] = center[d,k] - eps * d||A[m,:]||_q / dA[m,k]
+//   q = 2: A_k / ||A||_2 (0 for a zero row);  q = inf (p = 1): sign(A_k) / #maxima at the maxima of |A|, else 0;
+//   q = 1 (p = inf): sign(A_k).   This is the start vector of the adjoint (gradient) sweep.
+__global__ void __launch_bounds__(256) h0_lp_kernel(float* __restrict__ A, const float* __restrict__ center, float eps, int p, int M,
+                                                    int S, int n0) {
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (m >= M) return;
+  float* a = A + (size_t)m * n0;
+  const float* c = center + (size_t)(m / S) * n0;
+  float acc = 0.f;
+  for (int k = lane; k < n0; k += 32) {
+    const float x = a[k];
+    if (p == 2) acc = fmaf(x, x, acc);
+    else if (p == 1) acc = fmaxf(acc, fabsf(x));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, acc, o);
+    acc = (p == 1) ? fmaxf(acc, other) : (acc + other);
+  }
+  float cnt = 0.f;
+  if (p == 1) {
+    for (int k = lane; k < n0; k += 32) cnt += (fabsf(a[k]) == acc) ? 1.f : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  }
+  const float nrm = (p == 2) ? sqrtf(acc) : acc;
+  for (int k = lane; k < n0; k += 32) {
+    const float x = a[k];
+    const float sg = (x > 0.f) ? 1.f : ((x < 0.f) ? -1.f : 0.f);
+    float g;
+    if (p == 2) g = (nrm > 0.f) ? x / nrm : 0.f;
+    else if (p == 1) g = (fabsf(x) == nrm && nrm > 0.f) ? sg / cnt : 0.f;
+    else g = sg;
+    a[k] = c[k] - eps * g;
+  }
+}
+
+int launch_h0_lp(float* A, const float* center, float eps, int p, int B, int S, int n0, cudaStream_t stream) {
+  const int M = B * S;
+  h0_lp_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(A, center, eps, p, M, S, n0);
+  BF_CHECK_LAUNCH("h0_lp_kernel");
+  return BF_OK;
+}
+
 }  // namespace bf
 
 static bool lp_ok(int p) { return p == BF_NORM_INF || p == BF_NORM_L2 || p == BF_NORM_L1; }

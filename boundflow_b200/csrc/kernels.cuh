@@ -34,6 +34,7 @@ int launch_ibp_linear(const float* in_a, const float* in_b, int in_mode, int rel
                       const int8_t* split, int split_stride, const float* cons_l, const float* cons_u, float* out_l,
                       float* out_u, int* infeasible, int B, int K, int N, const float* row_dev, cudaStream_t stream);
 int launch_row_dual_norm(const float* rows, int n_rows, int n, int p, float scale, float* out, cudaStream_t stream);
+int launch_h0_lp(float* A, const float* center, float eps, int p, int B, int S, int n0, cudaStream_t stream);
 int launch_concretize_lp(const float* A, const float* center, const float* bias_in, float* out, int side, float eps, int p, int B,
                          int S, int n0, cudaStream_t stream);
 

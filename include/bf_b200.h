@@ -345,6 +345,11 @@ int bf_chain_crown_onehot(const bf_chain* chain, int upto_layer, int side, int f
                           void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S);
+/* Input set of the alpha / beta entry points below: as in bf_chain_crown -- norm_p = BF_NORM_BOX with
+ * mid, rad [B,n0], or an Lp ball with mid = centre, rad = NULL, eps and norm_p in
+ * {BF_NORM_INF, BF_NORM_L2, BF_NORM_L1} (LpBallPerturbation.concretize_affine,
+ * boundflow/runtime/perturbation.py:175-222; the gradient sweep then starts from
+ * centre - eps * d||A_0||_q / dA_0). */
 
 /* Per-domain alpha-CROWN: steps+1 lower-bound evaluations, analytic alpha gradient,
  * Adam(lr, 0.9, 0.999, 1e-8), projection to [0,1], strict per-domain best tracking, and
@@ -361,7 +366,7 @@ int bf_chain_alpha_crown(const bf_chain* chain,
                          const float* C,
                          const float* const* pre_l, const float* const* pre_u,
                          float* const* alpha, float* const* best_alpha,
-                         const float* mid, const float* rad,
+                         const float* mid, const float* rad, int norm_p, float eps,
                          float* best_lower, float* best_upper, float* best_metric,
                          int steps, float lr, int spec_reduce,
                          void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
@@ -382,7 +387,7 @@ int bf_chain_alpha_beta_crown(const bf_chain* chain,
                               float* const* alpha, float* const* best_alpha,
                               float* const* beta, float* const* best_beta,
                               const int8_t* const* splits, const int* split_strides,
-                              const float* mid, const float* rad,
+                              const float* mid, const float* rad, int norm_p, float eps,
                               float* best_lower, float* best_upper, float* best_metric,
                               int steps, float lr, int spec_reduce,
                               void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
@@ -402,7 +407,7 @@ int bf_chain_alpha_grad(const bf_chain* chain,
                         const float* C,
                         const float* const* pre_l, const float* const* pre_u,
                         const float* const* alpha,
-                        const float* mid, const float* rad,
+                        const float* mid, const float* rad, int norm_p, float eps,
                         float* const* grad, float* lower, int spec_reduce,
                         void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
@@ -426,7 +431,7 @@ int bf_chain_alpha_crown_shared(const bf_chain* chain,
                                 float* const* alpha, float* const* best_alpha,
                                 float* const* beta, float* const* best_beta,
                                 const int8_t* const* splits, const int* split_strides,
-                                const float* mid, const float* rad,
+                                const float* mid, const float* rad, int norm_p, float eps,
                                 float* best_lower, float* best_upper, float* best_metric,
                                 int steps, float lr,
                                 void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);

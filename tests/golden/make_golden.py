@@ -277,12 +277,30 @@ def gen_graph_cases() -> None:
     save("graph_cases.npz", **out)
 
 
+def gen_lp_alpha() -> None:
+    """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
+    wl = W.make_workload("c3", batch=8)
+    m = ref_module(wl)
+    out = {"input_checksum": checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])}
+    for pname, mk, eps in (("l2", InputSpec.l2, 4.0 * wl.eps), ("l1", InputSpec.l1, 12.0 * wl.eps)):
+        spec = mk(value_name="input", center=wl.x, eps=eps)
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        a0 = adaptive_alpha(relu_pre)
+        for steps in (1, 10):
+            b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, steps=steps, lr=0.1,
+                                                   warm_start_alpha=AlphaState(alpha_by_relu_input=a0), per_batch_params=True,
+                                                   objective="lower", spec_reduce="mean")
+            out[f"{pname}_lower_{steps}"], out[f"{pname}_upper_{steps}"] = b.lower, b.upper
+        out[f"{pname}_eps"] = eps
+    save("lp_alpha.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
             "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
-            "graph_cases": gen_graph_cases}
+            "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
@@ -292,6 +310,7 @@ def main() -> None:
     gen_first_layer_certificate()
     gen_relu_influence()
     gen_graph_cases()
+    gen_lp_alpha()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

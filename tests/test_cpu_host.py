@@ -217,3 +217,38 @@ def test_typed_registry_routes_fused_tasks_to_the_cuda_executor():
     key.capability_id = "other"
     with pytest.raises(ValueError):
         reg.dispatch(task, key, session=Session(), template=template)
+
+
+def test_query_runtime_groups_chunks_and_keeps_request_order(monkeypatch):
+    """Host logic of CudaQueryRuntime.execute (no GPU: the batch executor is replaced)."""
+    from types import SimpleNamespace as NS
+
+    import torch
+
+    from boundflow_b200.ir import InputSpec
+    from boundflow_b200.query_runtime import CudaQueryRuntime
+
+    def req(qid, method, steps):
+        spec = InputSpec.box(value_name="input", lower=torch.zeros(1, 4), upper=torch.ones(1, 4))
+        payload = NS(input_spec=spec, linear_spec_c=torch.zeros(2, 3), split_by_relu_input={"h": torch.zeros(5, dtype=torch.int8)},
+                     warm_alpha_by_relu_input={}, warm_beta_by_relu_input={})
+        return NS(query=NS(query_id=qid, bound_method=NS(value=method), execution_options={"alpha_steps": steps}), payload=payload)
+
+    batches = []
+
+    def fake_batch(self, module, reqs, method):
+        batches.append((method, [r.query.query_id for r in reqs]))
+        return [f"res-{r.query.query_id}" for r in reqs]
+
+    monkeypatch.setattr(CudaQueryRuntime, "_execute_batch", fake_batch)
+    rt = CudaQueryRuntime(max_batch_size=2)
+    reqs = [req("a0", "alpha-beta-CROWN", 5), req("b0", "alpha-CROWN", 5), req("a1", "alpha-beta-CROWN", 5),
+            req("c0", "alpha-beta-CROWN", 7), req("a2", "alpha-beta-CROWN", 5)]
+    out = rt.execute(None, reqs)
+    assert out == [(r.query.query_id, f"res-{r.query.query_id}") for r in reqs]
+    # same method + options + shapes share a batch, chunked by max_batch_size; different options or methods do not mix
+    assert ("alpha-beta-CROWN", ["a0", "a1"]) in batches and ("alpha-beta-CROWN", ["a2"]) in batches
+    assert ("alpha-CROWN", ["b0"]) in batches and ("alpha-beta-CROWN", ["c0"]) in batches
+    assert rt.execute(None, []) == []
+    with pytest.raises(ValueError):
+        CudaQueryRuntime(max_batch_size=0)

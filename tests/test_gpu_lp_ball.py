@@ -67,13 +67,33 @@ def test_lp_entry_points_against_torch(dev, p):
         assert_close(o, ref, f"concretize side {side}")
 
 
-def test_alpha_on_lp_ball_is_refused(dev):
+@pytest.mark.parametrize("pname,p", [("l2", 2), ("l1", 1)])
+def test_alpha_crown_on_lp_ball_matches_reference_golden_and_oracle_gradient(dev, golden, pname, p):
     from boundflow_b200 import workloads as W
-    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, alpha_grad_from_trace, ibp_trace, run_alpha_beta_crown_mlp
     from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
 
-    wl = W.make_workload("c3", batch=2)
-    spec = InputSpec.l2(value_name="input", center=wl.x.to(dev), eps=0.1)
+    g = golden("lp_alpha.npz")
+    wl = W.make_workload("c3", batch=8)
+    mk = InputSpec.l2 if p == 2 else InputSpec.l1
+    eps = float(g[f"{pname}_eps"])
+    spec = mk(value_name="input", center=wl.x.to(dev), eps=eps)
     trace = ibp_trace(wl.module, spec)
-    with pytest.raises(NotImplementedError):
-        alpha_crown_from_trace(trace, wl.C.to(dev), adaptive_alpha_from_trace(trace), steps=1, lr=0.1)
+    a0 = adaptive_alpha_from_trace(trace)
+    warm = AlphaState(dict(zip(wl.relu_names, a0)))
+    for steps, rtol in ((1, 3e-5), (10, 3e-4)):
+        b, _a, _b, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=steps, lr=0.1,
+                                                warm_start_alpha=warm, per_batch_params=True)
+        assert_close(b.lower, g[f"{pname}_lower_{steps}"], f"lower after {steps} steps", rtol=rtol)
+        assert_close(b.upper, g[f"{pname}_upper_{steps}"], f"upper after {steps} steps", rtol=rtol)
+    # the analytic gradient (adjoint sweep started from centre - eps * d||A_0||_q/dA_0) against autograd through the oracle
+    inp = O.lp_ball(wl.x, eps, p)
+    otrace = O.forward_ibp_trace(wl.layers, inp)
+    mid_alpha = [torch.full_like(a, 0.4) for a in a0]
+    grads, lower = alpha_grad_from_trace(trace, wl.C.to(dev), mid_alpha)
+    ref_grads, ref_lower = O.alpha_gradient(wl.layers, inp, otrace, wl.C, [a.cpu() for a in mid_alpha])
+    assert_close(lower, ref_lower, "lower at alpha = 0.4", rtol=3e-5)
+    for r, (gg, rg) in enumerate(zip(grads, ref_grads)):
+        scale = float(rg.abs().max()) + 1e-12
+        assert float((gg.cpu() - rg).abs().max()) <= 2e-4 * scale + 1e-6, f"gradient of ReLU {r}"

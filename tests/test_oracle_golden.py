@@ -305,3 +305,19 @@ def test_relu_objective_influence(golden):
         assert len(infl) == len(wl.relu_names)
         for r, n in enumerate(wl.relu_names):
             assert_close(infl[r].reshape(batch, -1), g[f"{tag}_influence_{n}"], f"{tag} influence {n}")
+
+
+def test_alpha_crown_on_lp_balls(golden):
+    g = golden("lp_alpha.npz")
+    wl = W.make_workload("c3", batch=8)
+    assert np.allclose(workload_checksum(wl), g["input_checksum"], rtol=1e-12, atol=0)
+    for pname, p in (("l2", 2), ("l1", 1)):
+        inp = O.lp_ball(wl.x, float(g[f"{pname}_eps"]), p)
+        trace = O.forward_ibp_trace(wl.layers, inp)
+        a0 = O.adaptive_alpha_init(trace)
+        lo1, up1, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=1, lr=0.1, alpha0=a0, trace=trace)
+        assert_close(lo1, g[f"{pname}_lower_1"], f"{pname} one-step lower", rtol=3e-5)
+        assert_close(up1, g[f"{pname}_upper_1"], f"{pname} one-step upper", rtol=3e-5)
+        lo, up, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=10, lr=0.1, alpha0=a0, trace=trace)
+        assert_close(lo, g[f"{pname}_lower_10"], f"{pname} lower", rtol=3e-4)
+        assert_close(up, g[f"{pname}_upper_10"], f"{pname} upper", rtol=3e-4)
