@@ -649,7 +649,7 @@ def run_alpha_crown_mlp(
     -mean(lower), clamp to [0,1], and the bounds / alpha of the evaluation with the best
     whole-batch metric.  Returns (IntervalState, AlphaState, AlphaCrownStats) like the
     reference.  The CUDA backend implements objective="lower" with spec_reduce="mean" on
-    linear (relu linear)* chains; other settings raise NotImplementedError."""
+    affine (relu affine)* chains (Linear / Conv2d / flatten); other settings raise NotImplementedError."""
     if objective != "lower" or spec_reduce != "mean":
         raise NotImplementedError("the CUDA backend implements objective='lower' with spec_reduce='mean' for the shared-alpha loop")
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)

@@ -125,6 +125,20 @@ extern "C" int bf_chain_create(const bf_layer_desc* layers, int n_layers, bf_cha
     c->layers.push_back(L);
   }
   c->linear_relu_alternating = alternating && (n_layers % 2 == 1);
+  {
+    // affine (relu affine)* with flatten layers anywhere in between
+    bool ok = true, want_affine = true;
+    for (int i = 0; i < n_layers; ++i) {
+      const int op = c->layers[i].op;
+      if (op == BF_OP_FLATTEN) continue;
+      const bool is_affine = (op == BF_OP_LINEAR || op == BF_OP_CONV2D);
+      if (is_affine != want_affine) ok = false;
+      if (is_affine) c->affine_layers.push_back(i);
+      if (op == BF_OP_CONV2D) c->has_conv = true;
+      want_affine = !want_affine;
+    }
+    c->affine_relu_alternating = ok && !want_affine && c->affine_layers.size() == c->relu_layers.size() + 1;
+  }
   *out = c;
   return BF_OK;
 }

@@ -9,6 +9,13 @@
 
 namespace bf {
 
+int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                            const float* W, const float* bias, float* A_prev, float* delta, int accumulate, int M, int S,
+                            const bf_layer_desc& L, void* scratch, cudaStream_t stream);
+size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L);
+int launch_conv_forward_rows(const float* in, const float* W, const float* bias, float* out, int M, const bf_layer_desc& L,
+                             cudaStream_t stream);
+
 struct AlphaWs {
   std::vector<float*> au, bu, sl, grad, m, v, Ahat;
   std::vector<float*> gsum, mb, vb, addv;  // beta: gradient sums, Adam moments, split term -beta*s
@@ -19,6 +26,7 @@ struct AlphaWs {
   float* cur;
   float* metric;
   int* improve;
+  void* conv_scratch;  // ReLU-scaled coefficients of a conv layer's backward step
   size_t state_begin, state_bytes;  // grad/m/v (+ beta state) region, zero-initialised per call
   size_t bytes;
 };
@@ -60,6 +68,10 @@ static size_t alpha_ws_layout(const bf_chain* c, int B, int S, bool with_beta, v
   w.cur = cv.take<float>(M);
   w.metric = cv.take<float>((size_t)B);
   w.improve = cv.take<int>((size_t)B);
+  size_t conv_scratch = 0;
+  for (const bf_layer_desc& L : c->layers)
+    if (L.op == BF_OP_CONV2D) conv_scratch = std::max(conv_scratch, crown_bwd_conv2d_scratch_bytes((int)M, L));
+  w.conv_scratch = cv.take<char>(conv_scratch);
   w.bytes = cv.off;
   if (ws) *ws = w;
   return cv.off;
@@ -76,24 +88,37 @@ struct InputSetArg {
 
 // One lower- or upper-side sweep with the relaxations in ws; `use_add` adds the split term of
 // every ReLU to the lower coefficients (beta-CROWN).
+// Backward step of affine layer `layer` (Linear: tensor-core / FFMA GEMM with optional fused box concretisation;
+// Conv2d: ReLU scaling pass + transposed convolution, never fused with the concretisation).
+static int alpha_bwd_layer(const bf_chain* c, const AlphaWs& ws, int layer, const float* A, const float* dpos, const float* dneg,
+                           const float* epos, const float* eneg, const float* add, float* dst, int accumulate, const float* mid,
+                           const float* rad, float* partial, int side, int M, int S, int* ptiles, cudaStream_t stream) {
+  const bf_layer_desc& L = c->layers[layer];
+  if (L.op == BF_OP_LINEAR)
+    return dispatch_bwd(c, layer, A, dpos, dneg, epos, eneg, add, dst, ws.cacc, accumulate, mid, rad, partial, side, M, S, ptiles, stream);
+  BF_REQUIRE(add == nullptr, BF_E_UNSUPPORTED, "beta terms on conv layers are not supported");
+  return launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, L.W, L.bias, dst, ws.cacc, accumulate, M, S, L, ws.conv_scratch, stream);
+}
+
 static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int side, bool keep_A0, bool use_add,
                        const InputSetArg& in, float* out, int B, int S, cudaStream_t stream) {
   const int M = B * S;
   const int R = (int)c->relu_layers.size();
-  // a box is concretised inside the last layer's epilogue; an Lp ball needs the final coefficient rows
-  const bool box = in.box();
-  const float* mid = box ? in.mid : nullptr;
-  const float* rad = box ? in.rad : nullptr;
-  if (!box) keep_A0 = true;
+  // a box is concretised inside the last Linear layer's epilogue; an Lp ball or a conv first layer needs the final
+  // coefficient rows and a separate concretisation
+  const bool fused = in.box() && c->layers[c->affine_layers[0]].op == BF_OP_LINEAR;
+  const float* mid = fused ? in.mid : nullptr;
+  const float* rad = fused ? in.rad : nullptr;
+  if (!fused) keep_A0 = true;
   int rc;
   int ptiles = 1;
   if (R == 0) {
-    rc = dispatch_bwd(c, 0, C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, ws.cacc, 0, mid, rad,
-                      box ? ws.partial : nullptr, side, M, S, &ptiles, stream);
+    rc = alpha_bwd_layer(c, ws, c->affine_layers[0], C, nullptr, nullptr, nullptr, nullptr, nullptr, keep_A0 ? ws.A0 : nullptr, 0, mid,
+                         rad, fused ? ws.partial : nullptr, side, M, S, &ptiles, stream);
     if (rc != BF_OK) return rc;
   } else {
-    rc = dispatch_bwd(c, 2 * R, C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], ws.cacc, 0, nullptr, nullptr,
-                      nullptr, side, M, S, nullptr, stream);
+    rc = alpha_bwd_layer(c, ws, c->affine_layers[R], C, nullptr, nullptr, nullptr, nullptr, nullptr, ws.Ahat[R - 1], 0, nullptr,
+                         nullptr, nullptr, side, M, S, nullptr, stream);
     if (rc != BF_OK) return rc;
     for (int r = R - 1; r >= 0; --r) {
       const float *dpos, *dneg, *epos = nullptr, *eneg = nullptr;
@@ -102,13 +127,14 @@ static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int
       const float* add = (use_add && side == BF_SIDE_LOWER) ? ws.addv[r] : nullptr;
       const bool last = (r == 0);
       float* dst = last ? (keep_A0 ? ws.A0 : nullptr) : ws.Ahat[r - 1];
-      rc = dispatch_bwd(c, 2 * r, ws.Ahat[r], dpos, dneg, epos, eneg, add, dst, ws.cacc, 1, last ? mid : nullptr,
-                        last ? rad : nullptr, (last && box) ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
+      rc = alpha_bwd_layer(c, ws, c->affine_layers[r], ws.Ahat[r], dpos, dneg, epos, eneg, add, dst, 1, last ? mid : nullptr,
+                           last ? rad : nullptr, (last && fused) ? ws.partial : nullptr, side, M, S, last ? &ptiles : nullptr, stream);
       if (rc != BF_OK) return rc;
     }
   }
-  if (!box) return launch_concretize_lp(ws.A0, in.mid, ws.cacc, out, side, in.eps, in.norm_p, B, S, c->n0, stream);
-  return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
+  if (fused) return launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
+  if (in.box()) return launch_concretize(ws.A0, in.mid, in.rad, ws.cacc, out, side, B, S, c->n0, stream);
+  return launch_concretize_lp(ws.A0, in.mid, ws.cacc, out, side, in.eps, in.norm_p, B, S, c->n0, stream);
 }
 
 // Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r] and, with beta,
@@ -117,17 +143,32 @@ static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* cons
                          bool with_beta, const InputSetArg& in, int B, int S, cudaStream_t stream) {
   const int M = B * S;
   const int R = (int)c->relu_layers.size();
-  if (!in.box()) {  // Lp ball: the start vector needs a row norm, so it is written over the final coefficients first
-    int rc = launch_h0_lp(ws.A0, in.mid, in.eps, in.norm_p, B, S, c->n0, stream);
+  // the first Linear layer on a box forms h_0 = mid - sgn(A_0) * rad in its prologue; every other case writes the
+  // start vector over the final coefficient rows first
+  const bool h0_fused = in.box() && c->layers[c->affine_layers[0]].op == BF_OP_LINEAR;
+  if (!h0_fused) {
+    int rc = in.box() ? launch_h0_box(ws.A0, in.mid, in.rad, B, S, c->n0, stream)
+                      : launch_h0_lp(ws.A0, in.mid, in.eps, in.norm_p, B, S, c->n0, stream);
     if (rc != BF_OK) return rc;
   }
   for (int r = 0; r < R; ++r) {
+    const int layer = c->affine_layers[r];
+    const bf_layer_desc& L = c->layers[layer];
     const float* hprev = (r == 0) ? ws.A0 : ws.H[(r - 1) & 1];
-    float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
-    const bool from_box = (r == 0) && in.box();  // h_0 = mid - sgn(A_0) * rad is formed in the kernel's prologue
-    int rc = dispatch_adjoint(c, 2 * r, hprev, from_box ? 1 : 0, from_box ? in.mid : nullptr, from_box ? in.rad : nullptr, ws.Ahat[r],
-                              ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r],
-                              with_beta ? ws.gsum[r] : nullptr, M, S, stream);
+    int rc;
+    if (L.op == BF_OP_LINEAR) {
+      float* hout = (r < R - 1) ? ws.H[r & 1] : nullptr;
+      const bool from_box = (r == 0) && h0_fused;
+      rc = dispatch_adjoint(c, layer, hprev, from_box ? 1 : 0, from_box ? in.mid : nullptr, from_box ? in.rad : nullptr, ws.Ahat[r],
+                            ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r],
+                            with_beta ? ws.gsum[r] : nullptr, M, S, stream);
+    } else {
+      BF_REQUIRE(!with_beta, BF_E_UNSUPPORTED, "beta terms on conv layers are not supported");
+      float* g = ws.H[r & 1];
+      rc = launch_conv_forward_rows(hprev, L.W, L.bias, g, M, L, stream);
+      if (rc != BF_OK) return rc;
+      rc = launch_relu_adjoint_rows(g, ws.Ahat[r], ws.sl[r], ws.au[r], ws.bu[r], pre_l[r], pre_u[r], ws.grad[r], B, S, L.n_out, stream);
+    }
     if (rc != BF_OK) return rc;
   }
   return BF_OK;
@@ -169,7 +210,8 @@ static int alpha_common_checks(const char* who, const bf_chain* chain, const voi
   BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "%s: a box needs its radius tensor", who);
   BF_REQUIRE(norm_p == BF_NORM_BOX || eps >= 0.f, BF_E_INVALID, "%s: negative eps", who);
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "%s: bad B/S", who);
-  BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
+  BF_REQUIRE(chain->affine_relu_alternating, BF_E_UNSUPPORTED, "%s: only affine (relu affine)* chains are supported", who);
+  BF_REQUIRE(!(with_beta && chain->has_conv), BF_E_UNSUPPORTED, "%s: beta terms on conv layers are not supported", who);
   const size_t need = bf::alpha_ws_layout(chain, B, S, with_beta, workspace, ws);
   BF_REQUIRE(workspace_bytes >= need, BF_E_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, workspace_bytes);
   return BF_OK;
@@ -344,8 +386,9 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   BF_REQUIRE(norm_p != BF_NORM_BOX || rad != nullptr, BF_E_INVALID, "%s: a box needs its radius tensor", who);
   const bf::InputSetArg in{mid, rad, norm_p, eps};
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL && steps >= 0, BF_E_INVALID, "%s: bad B/S/steps", who);
-  BF_REQUIRE(chain->linear_relu_alternating, BF_E_UNSUPPORTED, "%s: only linear (relu linear)* chains are supported", who);
+  BF_REQUIRE(chain->affine_relu_alternating, BF_E_UNSUPPORTED, "%s: only affine (relu affine)* chains are supported", who);
   const bool with_beta = beta != nullptr;
+  BF_REQUIRE(!(with_beta && chain->has_conv), BF_E_UNSUPPORTED, "%s: beta terms on conv layers are not supported", who);
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
   bf::AlphaWs ws;
   bf::SharedWs sw;

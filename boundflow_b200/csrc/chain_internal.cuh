@@ -10,6 +10,9 @@ struct bf_chain {
   int n0 = 0;
   int max_width = 0;
   bool linear_relu_alternating = false;  // linear (relu linear)*
+  std::vector<int> affine_layers;        // layer index of every Linear / Conv2d, chain order
+  bool affine_relu_alternating = false;  // affine (relu affine)* once flatten layers are dropped
+  bool has_conv = false;
   // tensor-core path: per layer, packed hi/lo weight images for the backward (W^T as B) and
   // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
   std::vector<const unsigned char*> pk_bwd, pk_adj;

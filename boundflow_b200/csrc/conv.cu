@@ -9,6 +9,10 @@ namespace bf {
 // IBP conv2d: one thread per output element; weights are warp-uniform loads
 // (a warp covers consecutive output columns of one output channel).
 // ---------------------------------------------------------------------------
+struct ConvGeom {
+  int Ci, Hi, Wi, Co, Ho, Wo, kh, kw, sh, sw, ph, pw;
+};
+
 struct IbpConvArgs {
   const float* in_a; const float* in_b; int in_mode; int relu_in;
   const float* W; const float* bias;
@@ -85,6 +89,50 @@ int launch_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, int rel
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   ibp_conv2d_kernel<<<(int)blocks, 256, 0, stream>>>(g);
   BF_CHECK_LAUNCH("ibp_conv2d_kernel");
+  return BF_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Forward convolution of rows (the gradient sweep of the alpha optimiser pushes its adjoint
+// points through the layers in forward direction): out[m] = conv2d(in[m], W) + bias, one thread
+// per output element.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) conv_forward_rows_kernel(const float* __restrict__ in, const float* __restrict__ W,
+                                                                const float* __restrict__ bias, float* __restrict__ out,
+                                                                long long total, ConvGeom g) {
+  const long long n_out = (long long)g.Co * g.Ho * g.Wo;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int wo = (int)(idx % g.Wo);
+    const int ho = (int)((idx / g.Wo) % g.Ho);
+    const int co = (int)((idx / ((long long)g.Wo * g.Ho)) % g.Co);
+    const long long m = idx / n_out;
+    const int h0 = ho * g.sh - g.ph, w0 = wo * g.sw - g.pw;
+    float acc = 0.f;
+    for (int ci = 0; ci < g.Ci; ++ci) {
+      const float* wa = W + ((size_t)co * g.Ci + ci) * g.kh * g.kw;
+      const float* ip = in + ((size_t)m * g.Ci + ci) * g.Hi * g.Wi;
+      for (int r = 0; r < g.kh; ++r) {
+        const int hi = h0 + r;
+        if (hi < 0 || hi >= g.Hi) continue;
+        for (int sc = 0; sc < g.kw; ++sc) {
+          const int wi = w0 + sc;
+          if (wi < 0 || wi >= g.Wi) continue;
+          acc = fmaf(__ldg(ip + (size_t)hi * g.Wi + wi), __ldg(wa + r * g.kw + sc), acc);
+        }
+      }
+    }
+    out[idx] = acc + (bias ? __ldg(bias + co) : 0.f);
+  }
+}
+
+int launch_conv_forward_rows(const float* in, const float* W, const float* bias, float* out, int M, const bf_layer_desc& L,
+                             cudaStream_t stream) {
+  ConvGeom g{L.Ci, L.Hi, L.Wi, L.Co, L.Ho, L.Wo, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw};
+  const long long total = (long long)M * L.n_out;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  conv_forward_rows_kernel<<<(int)blocks, 256, 0, stream>>>(in, W, bias, out, total, g);
+  BF_CHECK_LAUNCH("conv_forward_rows_kernel");
   return BF_OK;
 }
 

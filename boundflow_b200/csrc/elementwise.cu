@@ -351,6 +351,59 @@ int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStrea
   return BF_OK;
 }
 
+// ---- gradient sweep pieces for layers without a fused epilogue (conv) --------------------------------
+// Adjoint step of one ReLU on rows: g = layer output at the adjoint point (in), h = d*g + e (out, in place),
+// grad[b,j] += sum over the domain's rows of [unstable][Ahat >= 0] Ahat*g.  One thread per (domain, neuron),
+// rows of the domain in order: no atomics.
+__global__ void __launch_bounds__(256) relu_adjoint_rows_kernel(float* __restrict__ G, const float* __restrict__ Ahat,
+                                                                const float* __restrict__ dpos, const float* __restrict__ dneg,
+                                                                const float* __restrict__ eneg, const float* __restrict__ pre_l,
+                                                                const float* __restrict__ pre_u, float* __restrict__ grad, int S,
+                                                                int n) {
+  const int b = blockIdx.x;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const size_t o = (size_t)b * n + j;
+  const float dp = dpos[o], dn = dneg[o], en = eneg ? eneg[o] : 0.f;
+  const bool amb = pre_l[o] < 0.f && pre_u[o] > 0.f;
+  float acc = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const size_t i = ((size_t)b * S + s) * n + j;
+    const float a = Ahat[i], g = G[i];
+    const bool sel = a >= 0.f;
+    if (sel && amb) acc = fmaf(a, g, acc);
+    G[i] = sel ? dp * g : fmaf(dn, g, en);
+  }
+  grad[o] += acc;
+}
+
+int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
+                             const float* pre_l, const float* pre_u, float* grad, int B, int S, int n, cudaStream_t stream) {
+  dim3 grid(B, ceil_div(n, 256));
+  relu_adjoint_rows_kernel<<<grid, 256, 0, stream>>>(G, Ahat, dpos, dneg, eneg, pre_l, pre_u, grad, S, n);
+  BF_CHECK_LAUNCH("relu_adjoint_rows_kernel");
+  return BF_OK;
+}
+
+// Start vector of the gradient sweep for a box: h0 = mid - sgn(A0) * rad, written over A0.
+__global__ void h0_box_kernel(float* __restrict__ A0, const float* __restrict__ mid, const float* __restrict__ rad, long long total,
+                              int S, int n0) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / n0;
+    const size_t o = (size_t)(m / S) * n0 + (size_t)(i - m * n0);
+    const float a = A0[i];
+    const float sg = (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f);
+    A0[i] = mid[o] - sg * rad[o];
+  }
+}
+
+int launch_h0_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, cudaStream_t stream) {
+  const long long total = (long long)B * S * n0;
+  h0_box_kernel<<<ew_grid(total, 256), 256, 0, stream>>>(A0, mid, rad, total, S, n0);
+  BF_CHECK_LAUNCH("h0_box_kernel");
+  return BF_OK;
+}
+
 // ---- adaptive alpha start ------------------------------------------------------
 __global__ void alpha_adaptive_init_kernel(const float* __restrict__ l, const float* __restrict__ u, float* __restrict__ alpha,
                                            long long total) {

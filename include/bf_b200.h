@@ -353,7 +353,7 @@ size_t bf_chain_alpha_workspace_bytes(const bf_chain* chain, int B, int S);
 
 /* Per-domain alpha-CROWN: steps+1 lower-bound evaluations, analytic alpha gradient,
  * Adam(lr, 0.9, 0.999, 1e-8), projection to [0,1], strict per-domain best tracking, and
- * one upper-bound evaluation at the best alpha.  Linear/ReLU chains only.
+ * one upper-bound evaluation at the best alpha.  Chains affine (ReLU affine)* of Linear / Conv2d layers (flatten layers anywhere); beta needs Linear layers only.
  *   replaces run_alpha_beta_crown_mlp(per_batch_params=True, objective="lower") with beta at
  *            zero, boundflow/runtime/alpha_beta_crown.py:643-941 (loop 756-923), whose gradient
  *            comes from torch autograd through crown_ibp.py:1211-1298.

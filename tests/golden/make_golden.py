@@ -295,12 +295,34 @@ def gen_lp_alpha() -> None:
     save("lp_alpha.npz", **out)
 
 
+def gen_conv_alpha() -> None:
+    """alpha-CROWN on the CNN c2 (4 inputs): per-domain parameters (alpha-beta function, adaptive start) and the
+    shared-alpha function."""
+    from boundflow.runtime.alpha_crown import run_alpha_crown_mlp
+
+    wl = W.make_workload("c2", batch=4)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    a0 = adaptive_alpha(relu_pre)
+    out = {"input_checksum": checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])}
+    for steps in (1, 6):
+        b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, steps=steps, lr=0.1,
+                                               warm_start_alpha=AlphaState(alpha_by_relu_input=a0), per_batch_params=True,
+                                               objective="lower", spec_reduce="mean")
+        out[f"per_domain_lower_{steps}"], out[f"per_domain_upper_{steps}"] = b.lower, b.upper
+        bs, _st, _ = run_alpha_crown_mlp(m, spec, linear_spec_C=wl.C, steps=steps, lr=0.1)
+        out[f"shared_lower_{steps}"], out[f"shared_upper_{steps}"] = bs.lower, bs.upper
+    save("conv_alpha.npz", **out)
+
+
 def main() -> None:
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
             "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
-            "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha}
+            "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha,
+            "conv_alpha": gen_conv_alpha}
     if len(sys.argv) > 2:  # regenerate one file only
         only[sys.argv[2]]()
         return
@@ -311,6 +333,7 @@ def main() -> None:
     gen_relu_influence()
     gen_graph_cases()
     gen_lp_alpha()
+    gen_conv_alpha()
 
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")

@@ -321,3 +321,19 @@ def test_alpha_crown_on_lp_balls(golden):
         lo, up, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=10, lr=0.1, alpha0=a0, trace=trace)
         assert_close(lo, g[f"{pname}_lower_10"], f"{pname} lower", rtol=3e-4)
         assert_close(up, g[f"{pname}_upper_10"], f"{pname} upper", rtol=3e-4)
+
+
+def test_alpha_crown_on_a_conv_chain(golden):
+    g = golden("conv_alpha.npz")
+    wl = W.make_workload("c2", batch=4)
+    assert np.allclose(workload_checksum(wl), g["input_checksum"], rtol=1e-12, atol=0)
+    inp = O.box_input(wl.lo, wl.up)
+    trace = O.forward_ibp_trace(wl.layers, inp)
+    a0 = O.adaptive_alpha_init(trace)
+    for steps, rtol in ((1, 3e-5), (6, 3e-4)):
+        lo, up, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=steps, lr=0.1, alpha0=a0, trace=trace)
+        assert_close(lo, g[f"per_domain_lower_{steps}"], f"per-domain lower {steps}", rtol=rtol)
+        assert_close(up, g[f"per_domain_upper_{steps}"], f"per-domain upper {steps}", rtol=rtol)
+        lo, up, _a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=steps, lr=0.1, trace=trace)
+        assert_close(lo, g[f"shared_lower_{steps}"], f"shared lower {steps}", rtol=rtol)
+        assert_close(up, g[f"shared_upper_{steps}"], f"shared upper {steps}", rtol=rtol)
