@@ -312,4 +312,27 @@ def make_graph_cases(seed: int = 1011):
               "wh": rn(5, c1 * 4 * 4, fan=c1 * 16), "bh": rn(5, fan=200)}
     x = torch.rand(2, 3, 8, 8, generator=g)
     cases["mini_resnet"] = (mod("mini_resnet", ops, params), x) + box(x, 0.02) + (None,)
+    # channel concatenation of two conv branches, and feature concatenation of two linear branches
+    k3 = {"stride": (1, 1), "padding": (1, 1), "dilation": (1, 1), "groups": 1}
+    k1 = {"stride": (1, 1), "padding": (0, 0), "dilation": (1, 1), "groups": 1}
+    ops = [
+        TaskOp("conv2d", "branch_a", ["input", "wa", "ba"], ["ha"], k3), TaskOp("conv2d", "branch_b", ["input", "wb", "bb"], ["hb"], k1),
+        TaskOp("concat", "cat", ["ha", "hb"], ["hc"], {"axis": 1}), TaskOp("relu", "relu1", ["hc"], ["rc"]),
+        TaskOp("conv2d", "down", ["rc", "wd", "bd"], ["hd"], down), TaskOp("relu", "relu2", ["hd"], ["rd"]),
+        TaskOp("flatten", "flatten", ["rd"], ["flat"], {"start_dim": 1, "end_dim": -1}),
+        TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"]),
+    ]
+    params = {"wa": rn(2, 3, 3, 3, fan=27), "ba": rn(2, fan=200), "wb": rn(3, 3, 1, 1, fan=3), "bb": rn(3, fan=200),
+              "wd": rn(4, 5, 3, 3, fan=45), "bd": rn(4, fan=200), "wh": rn(3, 4 * 3 * 3, fan=36), "bh": rn(3, fan=200)}
+    x = torch.rand(2, 3, 6, 6, generator=g)
+    cases["concat_cnn"] = (mod("concat_cnn", ops, params), x) + box(x, 0.03) + (None,)
+    ops = [
+        TaskOp("linear", "left", ["input", "wl", "bl"], ["hl"]), TaskOp("linear", "right", ["input", "wr", "br"], ["hr"]),
+        TaskOp("relu", "relu_l", ["hl"], ["rl"]),
+        TaskOp("concat", "cat", ["rl", "hr"], ["hc"], {"axis": -1}), TaskOp("relu", "relu_c", ["hc"], ["rc"]),
+        TaskOp("linear", "head", ["rc", "wh", "bh"], ["out"]),
+    ]
+    params = {"wl": rn(7, 9, fan=9), "bl": rn(7, fan=200), "wr": rn(5, 9, fan=9), "br": rn(5, fan=200), "wh": rn(4, 12, fan=12), "bh": rn(4, fan=200)}
+    x = torch.rand(4, 9, generator=g)
+    cases["concat_mlp"] = (mod("concat_mlp", ops, params), x) + box(x, 0.08) + (torch.randn(4, 2, 4, generator=g),)
     return cases

@@ -16,7 +16,7 @@ def dev():
     return torch.device("cuda", 0)
 
 
-@pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet"])
+@pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"])
 def test_graph_matches_reference_golden(dev, golden, name):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import needs_graph_path, run_crown_ibp_mlp
