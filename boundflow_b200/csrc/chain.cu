@@ -439,6 +439,10 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
   int toggle = 0;
   bool fused_concretize = false;
   int ptiles = 1;
+  // identity-row sweeps on conv layers keep only the window of each row that can be non-zero (see conv.cu)
+  bf::WindowGeom win{};
+  bool windowed = false;
+  const bool windows_allowed = box && influence == nullptr && getenv("BF_B200_NO_WINDOWS") == nullptr;
   for (int i = upto_layer - 1; i >= 0; --i) {
     const bf_layer_desc& L = chain->layers[i];
     if (L.op == BF_OP_FLATTEN) continue;
@@ -456,6 +460,16 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
       if (add && add[pending] && side == BF_SIDE_LOWER) ad = add[pending];
     }
     int rc;
+    if (windowed && !(L.op == BF_OP_CONV2D && pending >= 0 && ad == nullptr && win.C == L.Co && win.H == L.Ho && win.W == L.Wo &&
+                      (win.WH - 1) * L.sh + L.kh < L.Hi && (win.WW - 1) * L.sw + L.kw < L.Wi)) {
+      // the window has grown to the feature map (or the next layer is not a ReLU + conv pair): back to full rows
+      float* dense = ws.buf[toggle];
+      rc = bf::launch_window_to_dense(curA, dense, win, M, stream);
+      if (rc != BF_OK) return rc;
+      curA = dense;
+      toggle ^= 1;
+      windowed = false;
+    }
     if (influence && pending >= 0 && influence[pending]) {
       BF_REQUIRE(curA != nullptr, BF_E_UNSUPPORTED, "bf_chain_crown_influence: no coefficients reach this ReLU");
       rc = bf::launch_colmax_abs(curA, influence[pending], B, S, chain->layers[chain->relu_layers[pending]].n_in, stream);
@@ -467,8 +481,32 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
       BF_REQUIRE(onehot_first + S <= L.n_out, BF_E_INVALID, "bf_chain_crown_onehot: rows %d..%d exceed the value's width %d",
                  onehot_first, onehot_first + S - 1, L.n_out);
       float* dst = ws.buf[toggle];
-      if (L.op == BF_OP_LINEAR) rc = bf::launch_onehot_linear_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L.n_in, stream);
-      else rc = bf::launch_onehot_conv_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L, stream);
+      if (L.op == BF_OP_LINEAR) {
+        rc = bf::launch_onehot_linear_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L.n_in, stream);
+      } else if (windows_allowed && L.kh < L.Hi && L.kw < L.Wi) {
+        win = bf::WindowGeom{M, onehot_first, S, L.Ho, L.Wo, L.Ci, L.kh, L.kw, L.Hi, L.Wi, L.sh, -L.ph, L.sw, -L.pw};
+        windowed = true;
+        rc = bf::launch_onehot_conv_window(L.W, L.bias, dst, ws.cacc, win, M, L.Ci, L.kh * L.kw, stream);
+      } else {
+        rc = bf::launch_onehot_conv_rows(onehot_first, L.W, L.bias, dst, ws.cacc, M, S, L, stream);
+      }
+      curA = dst;
+    } else if (windowed && L.op == BF_OP_CONV2D && pending >= 0 && ad == nullptr && win.C == L.Co && win.H == L.Ho && win.W == L.Wo &&
+               (win.WH - 1) * L.sh + L.kh < L.Hi && (win.WW - 1) * L.sw + L.kw < L.Wi) {
+      // ReLU pass and transposed convolution in window coordinates (zero padding: the window grows by the kernel)
+      float* lam = static_cast<float*>(ws.conv_scratch);
+      rc = bf::launch_relu_bwd_window(curA, dpos, dneg, epos, eneg, L.bias, lam, ws.cacc, win, M, stream);
+      if (rc != BF_OK) return rc;
+      bf_layer_desc Lw = L;
+      Lw.Ho = win.WH; Lw.Wo = win.WW;
+      Lw.Hi = (win.WH - 1) * L.sh + L.kh; Lw.Wi = (win.WW - 1) * L.sw + L.kw;
+      Lw.ph = 0; Lw.pw = 0;
+      Lw.n_out = L.Co * Lw.Ho * Lw.Wo; Lw.n_in = L.Ci * Lw.Hi * Lw.Wi;
+      float* dst = ws.buf[toggle];
+      rc = bf::launch_crown_bwd_conv2d(lam, nullptr, nullptr, nullptr, nullptr, L.W, nullptr, dst, nullptr, 1, M, S, Lw, nullptr, stream);
+      win.C = L.Ci; win.WH = Lw.Hi; win.WW = Lw.Wi; win.H = L.Hi; win.W = L.Wi;
+      win.ty = win.ty * L.sh - L.ph; win.sy *= L.sh;
+      win.tx = win.tx * L.sw - L.pw; win.sx *= L.sw;
       curA = dst;
     } else if (L.op == BF_OP_LINEAR) {
       const bool last = box && (i == low);  // the fused concretisation handles boxes; Lp balls concretise separately
@@ -490,6 +528,7 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
     pending = -1;
   }
   BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown: a ReLU directly on the input is not supported");
+  if (windowed) return bf::launch_concretize_window(curA, mid, rad, ws.cacc, out, side, win, M, stream);
   if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
   if (!box) return bf::launch_concretize_lp(curA, mid, have_c ? ws.cacc : nullptr, out, side, eps, norm_p, B, S, chain->n0, stream);
   return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);

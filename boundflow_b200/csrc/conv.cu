@@ -577,6 +577,10 @@ static int launch_convT_rowseg(const ConvTArgs& g, cudaStream_t stream) {
   if (g.kh == 3 && g.sh == 1 && g.ph == 1) return launch_rowseg<3, 1, 1>(g, stream);
   if (g.kh == 4 && g.sh == 2 && g.ph == 1) return launch_rowseg<4, 2, 1>(g, stream);
   if (g.kh == 3 && g.sh == 2 && g.ph == 1) return launch_rowseg<3, 2, 1>(g, stream);
+  // zero padding: the windowed sweeps below run every transposed convolution in window coordinates
+  if (g.kh == 3 && g.sh == 1 && g.ph == 0) return launch_rowseg<3, 1, 0>(g, stream);
+  if (g.kh == 4 && g.sh == 2 && g.ph == 0) return launch_rowseg<4, 2, 0>(g, stream);
+  if (g.kh == 3 && g.sh == 2 && g.ph == 0) return launch_rowseg<3, 2, 0>(g, stream);
   if (g.kh == 5 && g.sh == 1 && g.ph == 2) return launch_rowseg<5, 1, 2>(g, stream);
   return BF_E_UNSUPPORTED;
 }
@@ -712,6 +716,140 @@ int launch_onehot_conv_rows(int first, const float* W, const float* bias, float*
   dim3 grid(M, groups);
   onehot_conv_rows_kernel<<<grid, 256, 0, stream>>>(W, bias, A_prev, delta, first, S, vec, g);
   BF_CHECK_LAUNCH("onehot_conv_rows_kernel");
+  return BF_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Windowed coefficient rows.  A row that started as a row of the identity on a conv layer's output is zero
+// outside a small window of every feature map below it: kh x kw after the first backward step, and
+// (WH-1)*stride + k after each further transposed convolution.  While the window is smaller than the
+// feature map the sweep keeps only the window, [M, C, WH, WW] per row, whose image position follows from
+// the row's output pixel (ho, wo):  top = ho*sy + ty, left = wo*sx + tx.  A transposed convolution in
+// window coordinates is the ordinary one with zero padding (the kernels above, geometry Ho=WH, Wo=WW);
+// what falls outside the feature map is cleared by the next ReLU pass or ignored by the concretisation.
+// ---------------------------------------------------------------------------
+
+// first backward step: the window is the kernel itself
+__global__ void __launch_bounds__(256) onehot_conv_window_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                                                                 float* __restrict__ out, float* __restrict__ delta, WindowGeom w,
+                                                                 int Ci, int kk, long long total) {
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int per = Ci * kk;
+    const int m = (int)(e / per), r = (int)(e - (long long)m * per);
+    const int cb = (w.first + m % w.S) / (w.HoB * w.WoB);
+    out[e] = __ldg(W + (size_t)cb * per + r);
+    if (r == 0 && delta) delta[m] = bias ? __ldg(bias + cb) : 0.f;
+  }
+}
+
+// ReLU backward on windows: Lam = A * slope_sel inside the feature map, 0 outside;
+// delta += sum A * icpt_sel + Lam * bias[channel].  One block per row (windows are small).
+__global__ void __launch_bounds__(256) relu_bwd_window_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
+                                                              const float* __restrict__ dneg, const float* __restrict__ epos,
+                                                              const float* __restrict__ eneg, const float* __restrict__ bias,
+                                                              float* __restrict__ Lam, float* __restrict__ delta, WindowGeom w) {
+  const int m = blockIdx.x;
+  const int j = w.first + m % w.S;
+  const int rem = j % (w.HoB * w.WoB);
+  const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
+  const int n_win = w.C * w.WH * w.WW;
+  const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
+  float acc = 0.f;
+  for (int e = threadIdx.x; e < n_win; e += 256) {
+    const int c = e / (w.WH * w.WW), r2 = e - c * (w.WH * w.WW);
+    const int Y = top + r2 / w.WW, X = left + r2 % w.WW;
+    float lam = 0.f;
+    if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
+      const float v = A[(size_t)m * n_win + e];
+      const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
+      const bool sel = v >= 0.f;
+      lam = v * (sel ? dpos[k] : dneg[k]);
+      acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
+      if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
+    }
+    Lam[(size_t)m * n_win + e] = lam;
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += red[q];
+    delta[m] += t;
+  }
+}
+
+// window -> full feature map (zeros elsewhere, what falls outside the map is dropped)
+__global__ void __launch_bounds__(256) window_to_dense_kernel(const float* __restrict__ Awin, float* __restrict__ dense, WindowGeom w) {
+  const int m = blockIdx.x;
+  const int j = w.first + m % w.S;
+  const int rem = j % (w.HoB * w.WoB);
+  const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
+  const int n = w.C * w.H * w.W, n_win = w.C * w.WH * w.WW;
+  for (int k = threadIdx.x; k < n; k += 256) {
+    const int c = k / (w.H * w.W), r2 = k - c * (w.H * w.W);
+    const int y = r2 / w.W - top, x = r2 % w.W - left;
+    dense[(size_t)m * n + k] = (y >= 0 && y < w.WH && x >= 0 && x < w.WW) ? Awin[(size_t)m * n_win + (c * w.WH + y) * w.WW + x] : 0.f;
+  }
+}
+
+// box concretisation of windows on the network input: out[m] = sum A*mid -/+ |A|*rad over the window inside the image + delta
+__global__ void __launch_bounds__(256) concretize_window_kernel(const float* __restrict__ Awin, const float* __restrict__ mid,
+                                                                const float* __restrict__ rad, const float* __restrict__ delta,
+                                                                float* __restrict__ out, float sgn, WindowGeom w) {
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (m >= w.M) return;
+  const int j = w.first + m % w.S;
+  const int rem = j % (w.HoB * w.WoB);
+  const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
+  const int n_win = w.C * w.WH * w.WW;
+  const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
+  float acc = 0.f;
+  for (int e = lane; e < n_win; e += 32) {
+    const int c = e / (w.WH * w.WW), r2 = e - c * (w.WH * w.WW);
+    const int Y = top + r2 / w.WW, X = left + r2 % w.WW;
+    if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
+      const float v = Awin[(size_t)m * n_win + e];
+      const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
+      acc = fmaf(v, mid[k], acc);
+      acc = fmaf(sgn * fabsf(v), rad[k], acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[m] = acc + (delta ? delta[m] : 0.f);
+}
+
+int launch_onehot_conv_window(const float* W, const float* bias, float* out, float* delta, const WindowGeom& w, int M, int Ci, int kk,
+                              cudaStream_t stream) {
+  const long long total = (long long)M * Ci * kk;
+  onehot_conv_window_kernel<<<onehot_grid(total), 256, 0, stream>>>(W, bias, out, delta, w, Ci, kk, total);
+  BF_CHECK_LAUNCH("onehot_conv_window_kernel");
+  return BF_OK;
+}
+
+int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                           const float* bias, float* Lam, float* delta, const WindowGeom& w, int M, cudaStream_t stream) {
+  relu_bwd_window_kernel<<<M, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  BF_CHECK_LAUNCH("relu_bwd_window_kernel");
+  return BF_OK;
+}
+
+int launch_window_to_dense(const float* Awin, float* dense, const WindowGeom& w, int M, cudaStream_t stream) {
+  window_to_dense_kernel<<<M, 256, 0, stream>>>(Awin, dense, w);
+  BF_CHECK_LAUNCH("window_to_dense_kernel");
+  return BF_OK;
+}
+
+int launch_concretize_window(const float* Awin, const float* mid, const float* rad, const float* delta, float* out, int side,
+                             const WindowGeom& w, int M, cudaStream_t stream) {
+  concretize_window_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(Awin, mid, rad, delta, out,
+                                                                               side == BF_SIDE_LOWER ? -1.f : 1.f, w);
+  BF_CHECK_LAUNCH("concretize_window_kernel");
   return BF_OK;
 }
 

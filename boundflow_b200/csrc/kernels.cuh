@@ -65,6 +65,22 @@ int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStrea
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
                              const float* pre_l, const float* pre_u, float* grad, int B, int S, int n, cudaStream_t stream);
 int launch_h0_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, cudaStream_t stream);
+// windowed coefficient rows of identity-row sweeps on conv layers (conv.cu)
+struct WindowGeom {
+  int M;                 // coefficient rows
+  int first, S;          // spec row m is identity row first + m % S of the bounded value
+  int HoB, WoB;          // spatial size of the bounded value (row j -> channel j / (HoB*WoB), pixel (ho, wo))
+  int C, WH, WW;         // window of the current value
+  int H, W;              // feature-map size of the current value
+  int sy, ty, sx, tx;    // window origin: (ho*sy + ty, wo*sx + tx)
+};
+int launch_onehot_conv_window(const float* W, const float* bias, float* out, float* delta, const WindowGeom& w, int M, int Ci, int kk,
+                              cudaStream_t stream);
+int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                           const float* bias, float* Lam, float* delta, const WindowGeom& w, int M, cudaStream_t stream);
+int launch_window_to_dense(const float* Awin, float* dense, const WindowGeom& w, int M, cudaStream_t stream);
+int launch_concretize_window(const float* Awin, const float* mid, const float* rad, const float* delta, float* out, int side,
+                             const WindowGeom& w, int M, cudaStream_t stream);
 // shared-alpha mode (one alpha per neuron for the whole batch)
 int launch_shared_metric(const float* cur, long long M, float* best_metric, int* improve, int first, cudaStream_t stream);
 int launch_copy_if(const float* src, float* dst, long long n, const int* flag, cudaStream_t stream);
