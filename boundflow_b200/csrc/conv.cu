@@ -304,9 +304,9 @@ __global__ void __launch_bounds__(256) conv_transpose_rows_kernel(ConvTArgs g) {
 // ---------------------------------------------------------------------------
 // VEC: the coefficient tile starts on a 16-byte boundary of the image row (SH extra columns on the
 // left) so that it can be staged with 16-byte copies; needs Wo % 4 == 0.
-template <int KS, int ST, int PD, bool VEC>
+template <int KS, int ST, int PD, bool VEC, int TWP = 16>
 struct RowSeg {
-  static constexpr int TW = 16;                               // pixels per thread
+  static constexpr int TW = TWP;                              // pixels per thread (16, or 8 for narrow windows)
   static constexpr int C0 = (KS - 1 - PD + ST - 1) / ST;       // coefficient columns left of the segment's first pixel
   static constexpr int SH = VEC ? ((C0 + 3) / 4 * 4 - C0) : 0;
   static constexpr int C0E = C0 + SH;
@@ -348,9 +348,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int KS, int ST, int PD, int TCI, bool VEC>
-__global__ void __launch_bounds__(256, (TCI > 1 ? 2 : 3)) conv_transpose_rowseg_kernel(RowSegArgs a) {
-  using G = RowSeg<KS, ST, PD, VEC>;
+template <int KS, int ST, int PD, int TCI, bool VEC, int TWP>
+__global__ void __launch_bounds__(256, (TCI > 1 && TWP > 8 ? 2 : 3)) conv_transpose_rowseg_kernel(RowSegArgs a) {
+  using G = RowSeg<KS, ST, PD, VEC, TWP>;
   extern __shared__ __align__(16) float rs_smem[];
   const ConvTArgs& g = a.c;
   const int sx = 1 << a.sxl, th = 1 << a.thl, MR = 1 << a.mrl;
@@ -518,9 +518,9 @@ static int ilog2_ceil(int v) {
   return l;
 }
 
-template <int KS, int ST, int PD, int TCI, bool VEC>
+template <int KS, int ST, int PD, int TCI, bool VEC, int TWP>
 static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
-  using G = RowSeg<KS, ST, PD, VEC>;
+  using G = RowSeg<KS, ST, PD, VEC, TWP>;
   RowSegArgs a{};
   a.c = g;
   // channel groups per block: up to 32 input channels side by side
@@ -554,12 +554,12 @@ static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
   const size_t smem = 2 * (lam_words + w_words) * sizeof(float) + (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * sizeof(int);
   static bool attr_done = false;
   if (!attr_done) {
-    cudaFuncSetAttribute(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    cudaFuncSetAttribute(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC, TWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
     attr_done = true;
   }
   dim3 grid(ceil_div(g.M, 1 << a.mrl), a.tiles_x * a.tiles_y, ceil_div(g.Ci, cib));
   if (grid.y > 65535 || grid.z > 65535) return BF_E_UNSUPPORTED;
-  conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC><<<grid, 256, smem, stream>>>(a);
+  conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC, TWP><<<grid, 256, smem, stream>>>(a);
   BF_CHECK_LAUNCH("conv_transpose_rowseg_kernel");
   return BF_OK;
 }
@@ -567,8 +567,11 @@ static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
 template <int KS, int ST, int PD>
 static int launch_rowseg(const ConvTArgs& g, cudaStream_t stream) {
   const bool vec = (g.Wo % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.Lam) & 15u) == 0);
-  if (g.Ci <= 2) return vec ? launch_rowseg_tci<KS, ST, PD, 1, true>(g, stream) : launch_rowseg_tci<KS, ST, PD, 1, false>(g, stream);
-  return vec ? launch_rowseg_tci<KS, ST, PD, 4, true>(g, stream) : launch_rowseg_tci<KS, ST, PD, 4, false>(g, stream);
+  if (g.Ci <= 2) return vec ? launch_rowseg_tci<KS, ST, PD, 1, true, 16>(g, stream) : launch_rowseg_tci<KS, ST, PD, 1, false, 16>(g, stream);
+  // 8-pixel segments when they waste fewer lanes than 16-pixel ones (narrow windows of the windowed sweeps)
+  const bool narrow = ((g.Wi + 7) / 8) * 8 < ((g.Wi + 15) / 16) * 16;
+  if (narrow) return vec ? launch_rowseg_tci<KS, ST, PD, 4, true, 8>(g, stream) : launch_rowseg_tci<KS, ST, PD, 4, false, 8>(g, stream);
+  return vec ? launch_rowseg_tci<KS, ST, PD, 4, true, 16>(g, stream) : launch_rowseg_tci<KS, ST, PD, 4, false, 16>(g, stream);
 }
 
 // Row-segment kernel for the geometries it is instantiated for; BF_E_UNSUPPORTED otherwise.
