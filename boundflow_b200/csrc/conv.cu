@@ -732,57 +732,62 @@ int launch_onehot_conv_rows(int first, const float* W, const float* bias, float*
 // what falls outside the feature map is cleared by the next ReLU pass or ignored by the concretisation.
 // ---------------------------------------------------------------------------
 
-// first backward step: the window is the kernel itself
+// first backward step: the window is the kernel itself (one warp per row)
 __global__ void __launch_bounds__(256) onehot_conv_window_kernel(const float* __restrict__ W, const float* __restrict__ bias,
                                                                  float* __restrict__ out, float* __restrict__ delta, WindowGeom w,
-                                                                 int Ci, int kk, long long total) {
-  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
-    const int per = Ci * kk;
-    const int m = (int)(e / per), r = (int)(e - (long long)m * per);
-    const int cb = (w.first + m % w.S) / (w.HoB * w.WoB);
-    out[e] = __ldg(W + (size_t)cb * per + r);
-    if (r == 0 && delta) delta[m] = bias ? __ldg(bias + cb) : 0.f;
-  }
+                                                                 int per) {
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (m >= w.M) return;
+  const int cb = (w.first + m % w.S) / (w.HoB * w.WoB);
+  const float* src = W + (size_t)cb * per;
+  float* dst = out + (size_t)m * per;
+  for (int r = lane; r < per; r += 32) dst[r] = __ldg(src + r);
+  if (lane == 0 && delta) delta[m] = bias ? __ldg(bias + cb) : 0.f;
 }
 
 // ReLU backward on windows: Lam = A * slope_sel inside the feature map, 0 outside;
-// delta += sum A * icpt_sel + Lam * bias[channel].  One block per row (windows are small).
+// delta += sum A * icpt_sel + Lam * bias[channel].  One warp per row (windows are small); a lane walks the
+// window with counters instead of divisions.
 __global__ void __launch_bounds__(256) relu_bwd_window_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
                                                               const float* __restrict__ dneg, const float* __restrict__ epos,
                                                               const float* __restrict__ eneg, const float* __restrict__ bias,
                                                               float* __restrict__ Lam, float* __restrict__ delta, WindowGeom w) {
-  const int m = blockIdx.x;
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (m >= w.M) return;
   const int j = w.first + m % w.S;
   const int rem = j % (w.HoB * w.WoB);
   const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
-  const int n_win = w.C * w.WH * w.WW;
+  const int plane = w.WH * w.WW;
+  const int n_win = w.C * plane;
   const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
+  const float* a = A + (size_t)m * n_win;
+  float* lo = Lam + (size_t)m * n_win;
   float acc = 0.f;
-  for (int e = threadIdx.x; e < n_win; e += 256) {
-    const int c = e / (w.WH * w.WW), r2 = e - c * (w.WH * w.WW);
-    const int Y = top + r2 / w.WW, X = left + r2 % w.WW;
+  // element e = lane + 32*t: (c, y, x) advanced incrementally
+  int c = lane / plane, r2 = lane - c * plane;
+  int y = r2 / w.WW, x = r2 - y * w.WW;
+  const int dy = 32 / w.WW, dx = 32 - dy * w.WW;  // step of 32 elements inside a plane
+  for (int e = lane; e < n_win; e += 32) {
+    const int Y = top + y, X = left + x;
     float lam = 0.f;
     if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
-      const float v = A[(size_t)m * n_win + e];
+      const float v = a[e];
       const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
       const bool sel = v >= 0.f;
       lam = v * (sel ? dpos[k] : dneg[k]);
       acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
       if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
     }
-    Lam[(size_t)m * n_win + e] = lam;
+    lo[e] = lam;
+    x += dx; y += dy;
+    if (x >= w.WW) { x -= w.WW; ++y; }
+    while (y >= w.WH) { y -= w.WH; ++c; }
   }
-  __shared__ float red[8];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) t += red[q];
-    delta[m] += t;
-  }
+  if (lane == 0) delta[m] += acc;
 }
 
 // window -> full feature map (zeros elsewhere, what falls outside the map is dropped)
@@ -829,15 +834,14 @@ __global__ void __launch_bounds__(256) concretize_window_kernel(const float* __r
 
 int launch_onehot_conv_window(const float* W, const float* bias, float* out, float* delta, const WindowGeom& w, int M, int Ci, int kk,
                               cudaStream_t stream) {
-  const long long total = (long long)M * Ci * kk;
-  onehot_conv_window_kernel<<<onehot_grid(total), 256, 0, stream>>>(W, bias, out, delta, w, Ci, kk, total);
+  onehot_conv_window_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(W, bias, out, delta, w, Ci * kk);
   BF_CHECK_LAUNCH("onehot_conv_window_kernel");
   return BF_OK;
 }
 
 int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                            const float* bias, float* Lam, float* delta, const WindowGeom& w, int M, cudaStream_t stream) {
-  relu_bwd_window_kernel<<<M, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  relu_bwd_window_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
   BF_CHECK_LAUNCH("relu_bwd_window_kernel");
   return BF_OK;
 }
