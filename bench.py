@@ -390,7 +390,7 @@ def main():
             "share_of_step": t_l.value / ms_res if ms_res else None,
         },
         "roofline_adjoint": {
-            "kernel": "crown_tc_kernel<adjoint> (gradient sweep, tcgen05 3xTF32)", "achieved": achieved_adj, "unit": "TFLOP/s",
+            "kernel": "crown_tc_adjoint_kernel (gradient sweep, feature-major tcgen05 3xTF32)", "achieved": achieved_adj, "unit": "TFLOP/s",
             "frac": (achieved_adj / fp32_equiv_peak) if achieved_adj else None, "launches": n_a.value,
             "share_of_step": t_a.value / ms_res if ms_res else None,
         },

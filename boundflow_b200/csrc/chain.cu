@@ -182,6 +182,15 @@ int launch_onehot_linear_rows(int first, const float* W, const float* bias, floa
 // ---------------------------------------------------------------------------
 namespace bf {
 
+// The feature-major adjoint kernel works on 256-row x 256-feature CTAs: it pays off once those fill the GPU;
+// smaller problems keep the row-major kernel (128-row CTAs, twice as many of them).
+static bool adjoint_feature_major(int M, int N) {
+  const char* e = getenv("BF_B200_ADJ_ROWMAJOR");  // "1": always the row-major kernel
+  if (e && e[0] == '1') return false;
+  const long long ctas = (long long)((M + 255) / 256) * ((((N + tc_adjoint_tile_rows() - 1) / tc_adjoint_tile_rows()) + 1) / 2);
+  return ctas >= 128;
+}
+
 static bool tc_allowed() {
   const char* e = getenv("BF_B200_FORCE_FFMA");
   return !(e && e[0] == '1');
@@ -219,6 +228,9 @@ int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first
   const bf_layer_desc& L = c->layers[layer];
   const int K = L.n_in, N = L.n_out;
   const unsigned char* pk = tc_weights(c, layer, true, M, K, N);
+  if (pk && adjoint_feature_major(M, N))
+    return launch_crown_adjoint_linear_tc_fm(Hprev, first_layer, mid, rad, c->pk_adj_fm[layer], L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
+                                             hout, grad, gsum, M, S, K, N, c->status, stream);
   if (pk)
     return launch_crown_adjoint_linear_tc(Hprev, first_layer, mid, rad, pk, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
                                           hout, grad, gsum, M, S, K, N, c->status, stream);
@@ -233,7 +245,8 @@ extern "C" size_t bf_chain_tc_bytes(const bf_chain* chain) {
   size_t total = 256;  // status word
   for (const bf_layer_desc& L : chain->layers)
     if (L.op == BF_OP_LINEAR)
-      total += bf::align_up(bf::tc_packed_bytes(L.n_in, L.n_out)) + bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in));
+      total += bf::align_up(bf::tc_packed_bytes(L.n_in, L.n_out)) + bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in)) +
+               bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in, bf::tc_adjoint_tile_rows()));
   return total;
 }
 
@@ -251,6 +264,7 @@ extern "C" int bf_chain_tc_prepare(bf_chain* chain, void* buffer, size_t bytes, 
   size_t off = 256;
   chain->pk_bwd.assign(chain->layers.size(), nullptr);
   chain->pk_adj.assign(chain->layers.size(), nullptr);
+  chain->pk_adj_fm.assign(chain->layers.size(), nullptr);
   for (size_t i = 0; i < chain->layers.size(); ++i) {
     const bf_layer_desc& L = chain->layers[i];
     if (L.op != BF_OP_LINEAR) continue;
@@ -264,6 +278,12 @@ extern "C" int bf_chain_tc_prepare(bf_chain* chain, void* buffer, size_t bytes, 
     off += bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in));
     rc = bf::tc_pack_weights(L.W, L.n_out, L.n_in, 0, pa, stream);
     if (rc != BF_OK) return rc;
+    // the same orientation as 128-row images (features on the MMA's M side)
+    unsigned char* pf = base + off;
+    off += bf::align_up(bf::tc_packed_bytes(L.n_out, L.n_in, bf::tc_adjoint_tile_rows()));
+    rc = bf::tc_pack_weights(L.W, L.n_out, L.n_in, 0, pf, stream, bf::tc_adjoint_tile_rows());
+    if (rc != BF_OK) return rc;
+    chain->pk_adj_fm[i] = pf;
     chain->pk_bwd[i] = pb;
     chain->pk_adj[i] = pa;
   }

@@ -15,7 +15,7 @@ struct bf_chain {
   bool has_conv = false;
   // tensor-core path: per layer, packed hi/lo weight images for the backward (W^T as B) and
   // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
-  std::vector<const unsigned char*> pk_bwd, pk_adj;
+  std::vector<const unsigned char*> pk_bwd, pk_adj, pk_adj_fm;  // pk_adj_fm: 128-row images for the feature-major adjoint kernel
   int* status = nullptr;
 };
 

@@ -23,6 +23,7 @@
 #include <stdlib.h>
 
 #include "kernels.cuh"
+#include "tc_primitives.cuh"
 
 namespace bf {
 namespace tc {
@@ -43,7 +44,6 @@ constexpr int THREADS = (PROD_WARPS + 2) * 32;
 constexpr int PREFETCH_KB = 4;              // k-blocks of L2 prefetch distance for the A operand
 constexpr int TBL_MAX = 5;                  // domains per 32 rows served from the epilogue's slope table (S >= 8)
 constexpr int STG_LD = 36;                  // leading dimension of the per-warp epilogue transpose buffer
-constexpr long long WAIT_LIMIT = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
 enum { MODE_BWD = 0, MODE_ADJ = 1 };
 enum { PRO_PLAIN = 0, PRO_RELU = 1, PRO_H0 = 2 };
@@ -69,88 +69,6 @@ struct Params {
   float* gsum;               // [D,N] or null: per-domain sums of g (beta gradient)
   int* status;               // device word, set non-zero when a wait expired
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when another thread aborted or the limit was reached.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-               "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  // K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart (SBO), LBO unused (= 1), descriptor version 1.
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  const uint32_t z = 0;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z), "r"(z), "r"(z), "r"(z)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ float tf32_rna(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-__device__ __forceinline__ float sgnf(float a) { return (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f); }
 
 // Shared-memory control block placed in front of the (1024-byte aligned) tiles.
 struct Control {
@@ -659,17 +577,26 @@ int crown_tc_partial_tiles(int N, int K) {
   return tc::COL_PARTS * ((nt + 1) / 2);  // one partial sum per CTA column and epilogue warp group
 }
 
-size_t tc_packed_bytes(int N, int K) {
+// tile_rows > 0 forces the image height (the feature-major adjoint kernel wants 128-row images)
+static void tc_pack_shape(int N, int K, int tile_rows, int* BN, int* nt, int* nkb) {
+  tc_tile_shape(N, K, BN, nt, nkb);
+  if (tile_rows > 0) {
+    *BN = tile_rows;
+    *nt = (N + tile_rows - 1) / tile_rows;
+  }
+}
+
+size_t tc_packed_bytes(int N, int K, int tile_rows) {
   int BN, nt, nkb;
-  tc_tile_shape(N, K, &BN, &nt, &nkb);
+  tc_pack_shape(N, K, tile_rows, &BN, &nt, &nkb);
   return (size_t)nt * nkb * 2 * BN * 128;
 }
 
-int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned char* out, cudaStream_t stream) {
+int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned char* out, cudaStream_t stream, int tile_rows) {
   // logical B[n][k]: transposed == 0: W is [N=rows][K=cols]; transposed != 0: W is [K=rows][N=cols]
   const int N = transposed ? cols : rows, K = transposed ? rows : cols;
   int BN, nt, nkb;
-  tc_tile_shape(N, K, &BN, &nt, &nkb);
+  tc_pack_shape(N, K, tile_rows, &BN, &nt, &nkb);
   const long long total = (long long)nt * nkb * BN * 8;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 16) blocks = 148LL * 16;

@@ -16,8 +16,8 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
                                 float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream);
 
 // crown_tc.cu (tcgen05 3xTF32 path; weights pre-packed by tc_pack_weights)
-size_t tc_packed_bytes(int N, int K);
-int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned char* out, cudaStream_t stream);
+size_t tc_packed_bytes(int N, int K, int tile_rows = 0);
+int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned char* out, cudaStream_t stream, int tile_rows = 0);
 int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                                const float* add, const unsigned char* Wpk, const float* kbias, float* A_prev, float* delta,
                                int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S, int K,
@@ -28,6 +28,14 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
                                    const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
                                    int* status, cudaStream_t stream);
 int crown_tc_partial_tiles(int N, int K);
+
+// crown_tc_adj.cu (feature-major adjoint step; weights packed with tile_rows = tc_adjoint_tile_rows())
+int tc_adjoint_tile_rows();
+int launch_crown_adjoint_linear_tc_fm(const float* Hprev, int first_layer, const float* mid, const float* rad,
+                                      const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
+                                      const float* dneg, const float* epos, const float* eneg, const float* pre_l,
+                                      const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
+                                      int* status, cudaStream_t stream);
 
 // ibp.cu
 int launch_ibp_linear(const float* in_a, const float* in_b, int in_mode, int relu_in, const float* W, const float* bias,
