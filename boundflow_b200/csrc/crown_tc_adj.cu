@@ -202,8 +202,10 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
   Control* ctl = reinterpret_cast<Control*>(tiles - 1024);
   unsigned char* s_tiles = tiles + P_STAGES * 2 * P_TILE;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * RB;
-  const int ft0 = blockIdx.y * 2;                      // first feature tile of this CTA
+  // x = feature-tile pair, y = row block: the CTAs that share a row block are launched side by side, so the
+  // second read of its rows hits L2
+  const int m0 = blockIdx.y * RB;
+  const int ft0 = blockIdx.x * 2;                      // first feature tile of this CTA
   const int nf = min(2, p.nft - ft0);                  // feature tiles handled here
   const int nbase = ft0 * FT;                          // first feature
   const uint32_t tmem_cols = (nf == 1) ? 256u : 512u;
@@ -314,10 +316,10 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
         // The CTA that will start when this wave retires reads its first k-blocks from cold HBM pages;
         // pull those lines into L2 now (L2 is shared, so it does not matter which SM runs that CTA).
         const int lin = (int)(blockIdx.x + gridDim.x * blockIdx.y) + p.wave;
-        const int nx = lin % (int)gridDim.x, ny = lin / (int)gridDim.x;
+        const int ny = lin / (int)gridDim.x;  // its row block
         if (ny < (int)gridDim.y) {
           const int r = tid >> 1, half = tid & 1;  // 256 rows x two 128-byte k-blocks
-          const int m = nx * RB + r;
+          const int m = ny * RB + r;
           if (m < p.M && (half * BK) < p.K) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.A + (size_t)m * p.K + half * BK));
         }
       }
@@ -445,7 +447,7 @@ static int tca_launch(tca::Params& p, cudaStream_t stream, const char* name) {
     }
     attr_done = true;
   }
-  dim3 grid(ceil_div(p.M, tca::RB), (p.nft + 1) / 2);
+  dim3 grid((p.nft + 1) / 2, ceil_div(p.M, tca::RB));
   tca::crown_tc_adjoint_kernel<PRO><<<grid, tca::THREADS, tca::SMEM_BYTES, stream>>>(p);
   BF_CHECK_LAUNCH(name);
   return BF_OK;
