@@ -747,47 +747,62 @@ __global__ void __launch_bounds__(256) onehot_conv_window_kernel(const float* __
 }
 
 // ReLU backward on windows: Lam = A * slope_sel inside the feature map, 0 outside;
-// delta += sum A * icpt_sel + Lam * bias[channel].  One warp per row (windows are small); a lane walks the
-// window with counters instead of divisions.
+// delta += sum A * icpt_sel + Lam * bias[channel].  T threads per row (T = 32 ... 256, by window size), 256 / T
+// rows per block; a thread walks the window with counters instead of divisions.
+template <int T>
 __global__ void __launch_bounds__(256) relu_bwd_window_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
                                                               const float* __restrict__ dneg, const float* __restrict__ epos,
                                                               const float* __restrict__ eneg, const float* __restrict__ bias,
                                                               float* __restrict__ Lam, float* __restrict__ delta, WindowGeom w) {
-  const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (m >= w.M) return;
-  const int j = w.first + m % w.S;
-  const int rem = j % (w.HoB * w.WoB);
-  const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
-  const int plane = w.WH * w.WW;
-  const int n_win = w.C * plane;
-  const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
-  const float* a = A + (size_t)m * n_win;
-  float* lo = Lam + (size_t)m * n_win;
+  __shared__ float red[8];
+  const int m = blockIdx.x * (256 / T) + threadIdx.x / T;
+  const int t = threadIdx.x % T;
+  const bool live = m < w.M;  // whole warps: T is a multiple of 32
   float acc = 0.f;
-  // element e = lane + 32*t: (c, y, x) advanced incrementally
-  int c = lane / plane, r2 = lane - c * plane;
-  int y = r2 / w.WW, x = r2 - y * w.WW;
-  const int dy = 32 / w.WW, dx = 32 - dy * w.WW;  // step of 32 elements inside a plane
-  for (int e = lane; e < n_win; e += 32) {
-    const int Y = top + y, X = left + x;
-    float lam = 0.f;
-    if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
-      const float v = a[e];
-      const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
-      const bool sel = v >= 0.f;
-      lam = v * (sel ? dpos[k] : dneg[k]);
-      acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
-      if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
+  if (live) {
+    const int j = w.first + m % w.S;
+    const int rem = j % (w.HoB * w.WoB);
+    const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
+    const int plane = w.WH * w.WW;
+    const int n_win = w.C * plane;
+    const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
+    const float* a = A + (size_t)m * n_win;
+    float* lo = Lam + (size_t)m * n_win;
+    // element e = t + T*i: (c, y, x) advanced incrementally
+    int c = t / plane, r2 = t - c * plane;
+    int y = r2 / w.WW, x = r2 - y * w.WW;
+    const int dy = T / w.WW, dx = T - dy * w.WW;  // step of T elements inside a plane
+    for (int e = t; e < n_win; e += T) {
+      const int Y = top + y, X = left + x;
+      float lam = 0.f;
+      if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
+        const float v = a[e];
+        const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
+        const bool sel = v >= 0.f;
+        lam = v * (sel ? dpos[k] : dneg[k]);
+        acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
+        if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
+      }
+      lo[e] = lam;
+      x += dx; y += dy;
+      if (x >= w.WW) { x -= w.WW; ++y; }
+      while (y >= w.WH) { y -= w.WH; ++c; }
     }
-    lo[e] = lam;
-    x += dx; y += dy;
-    if (x >= w.WW) { x -= w.WW; ++y; }
-    while (y >= w.WH) { y -= w.WH; ++c; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) delta[m] += acc;
+  if (T == 32) {
+    if (live && t == 0) delta[m] += acc;
+  } else {
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (live && t == 0) {
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < T / 32; ++i) sum += red[(threadIdx.x >> 5) + i];
+      delta[m] += sum;
+    }
+  }
 }
 
 // window -> full feature map (zeros elsewhere, what falls outside the map is dropped)
@@ -841,7 +856,15 @@ int launch_onehot_conv_window(const float* W, const float* bias, float* out, flo
 
 int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                            const float* bias, float* Lam, float* delta, const WindowGeom& w, int M, cudaStream_t stream) {
-  relu_bwd_window_kernel<<<ceil_div((long long)M * 32, 256), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  const int n_win = w.C * w.WH * w.WW;
+  if (n_win <= 512)
+    relu_bwd_window_kernel<32><<<ceil_div(M, 8), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  else if (n_win <= 1536)
+    relu_bwd_window_kernel<64><<<ceil_div(M, 4), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  else if (n_win <= 4096)
+    relu_bwd_window_kernel<128><<<ceil_div(M, 2), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  else
+    relu_bwd_window_kernel<256><<<M, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
   BF_CHECK_LAUNCH("relu_bwd_window_kernel");
   return BF_OK;
 }
