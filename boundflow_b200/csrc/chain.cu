@@ -187,6 +187,8 @@ namespace bf {
 static bool adjoint_feature_major(int M, int N) {
   const char* e = getenv("BF_B200_ADJ_ROWMAJOR");  // "1": always the row-major kernel
   if (e && e[0] == '1') return false;
+  const char* f = getenv("BF_B200_ADJ_FEATURE_MAJOR");  // "1": always the feature-major kernel
+  if (f && f[0] == '1') return true;
   const long long ctas = (long long)((M + 255) / 256) * ((((N + tc_adjoint_tile_rows() - 1) / tc_adjoint_tile_rows()) + 1) / 2);
   return ctas >= 128;
 }

@@ -83,12 +83,46 @@ __device__ __forceinline__ Slopes load_slopes(const Params& p, int d, int n, boo
 
 // ---- epilogue pieces -----------------------------------------------------------------------
 // A lane owns one feature n; rows arrive eight at a time (v[u] = g[row + u][n]).
+constexpr int TBLD = 5;                       // domains of one 32-row chunk served from the shared-memory slope table (S >= 8)
+constexpr int TBL_FLOATS = TBLD * 6 * 32;     // [domain][dpos, dneg, epos, eneg, pre_l, pre_u][lane]
+
 struct ChunkState {
-  Slopes cur, nxt;     // slopes of the current domain and of the one after it
+  Slopes cur, nxt;     // slopes of the current domain and (register path) of the one after it
   float run, run2;     // running per-domain sums: alpha gradient, g itself (beta gradient)
   int d;               // current domain
   unsigned off_st;     // byte offset of the next h element inside the CTA's row slab
+  const float* tb;     // this lane's column of the chunk's slope table, or null (register path)
+  int k, nd;           // table path: index of the current domain inside the chunk, domains in the chunk
 };
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// Starts the asynchronous copy of the slopes of the chunk's domains d0 .. d0 + nd - 1 at feature n into this lane's table column.
+__device__ __forceinline__ void table_fill(const Params& p, float* tb, int d0, int nd, int n) {
+  for (int dl = 0; dl < nd; ++dl) {
+    const size_t off = (size_t)(d0 + dl) * p.N + n;
+    const uint32_t dst = smem_u32(tb + dl * 6 * 32);
+    cp_async4(dst, p.dpos + off);
+    cp_async4(dst + 128, p.dneg + off);
+    if (p.epos) cp_async4(dst + 256, p.epos + off);
+    if (p.eneg) cp_async4(dst + 384, p.eneg + off);
+    cp_async4(dst + 512, p.pre_l + off);
+    cp_async4(dst + 640, p.pre_u + off);
+  }
+}
+
+__device__ __forceinline__ Slopes table_read(const Params& p, const float* tb, int k) {
+  const float* t = tb + k * 6 * 32;
+  Slopes s;
+  s.dp = t[0];
+  s.dn = t[32];
+  s.ep = p.epos ? t[64] : 0.f;
+  s.en = p.eneg ? t[96] : 0.f;
+  s.amb = (t[128] < 0.f && t[160] > 0.f) ? 1.f : 0.f;
+  return s;
+}
 
 __device__ __forceinline__ void row_step(ChunkState& st, float a, float g, float nb, char* __restrict__ hout_cta, unsigned rowstride,
                                          bool st_ok) {
@@ -104,6 +138,7 @@ __device__ __forceinline__ void row_step(ChunkState& st, float a, float g, float
 }
 
 // the row just processed was the last one of domain st.d inside this chunk
+template <bool TBL>
 __device__ __forceinline__ void boundary_step(const Params& p, ChunkState& st, int n, bool n_ok, int D) {
   if (n_ok) {
     atomicAdd(&p.grad[(size_t)st.d * p.N + n], st.run);
@@ -112,18 +147,23 @@ __device__ __forceinline__ void boundary_step(const Params& p, ChunkState& st, i
   st.run = 0.f;
   st.run2 = 0.f;
   ++st.d;
-  st.cur = st.nxt;
-  st.nxt = load_slopes(p, min(st.d + 1, D - 1), n, n_ok);
+  if (TBL) {
+    st.k = min(st.k + 1, st.nd - 1);
+    st.cur = table_read(p, st.tb, st.k);
+  } else {
+    st.cur = st.nxt;
+    st.nxt = load_slopes(p, min(st.d + 1, D - 1), n, n_ok);
+  }
 }
 
 // Eight existing rows with at most one domain boundary, after row B (B == 8: none): straight-line code.
-template <int B>
+template <int B, bool TBL>
 __device__ __forceinline__ void group_static(const Params& p, ChunkState& st, const float (&v)[8], const float (&ah)[8], float nb,
                                              char* __restrict__ hout_cta, unsigned rowstride, bool st_ok, int n, bool n_ok, int D) {
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     row_step(st, ah[u], v[u], nb, hout_cta, rowstride, st_ok);
-    if (u == B) boundary_step(p, st, n, n_ok, D);
+    if (u == B) boundary_step<TBL>(p, st, n, n_ok, D);
   }
 }
 
@@ -133,13 +173,25 @@ __device__ __forceinline__ void group_static(const Params& p, ChunkState& st, co
 // (rolled, to keep the code small); a group of existing rows with at most one boundary -- every
 // group when a domain has eight rows or more -- runs as straight-line code selected by the
 // boundary position, other groups row by row.  The saved coefficients of the next group are
-// loaded while the current one is processed.
+// loaded while the current one is processed.  TBL: the slopes of the chunk's domains were copied
+// to this lane's shared-memory table column (tb) ahead of time; otherwise they are loaded from
+// global memory one domain ahead.
+template <bool TBL>
 __device__ __forceinline__ void adjoint_chunk(const Params& p, uint32_t taddr, const char* __restrict__ ahat_cta,
                                               char* __restrict__ hout_cta, unsigned off, unsigned rowstride, int n, bool n_ok,
-                                              bool st_ok, float nb, int d, int D, unsigned vmask, unsigned bmask) {
+                                              bool st_ok, float nb, int d, int D, unsigned vmask, unsigned bmask, const float* tb,
+                                              int nd) {
   ChunkState st;
-  st.cur = load_slopes(p, d, n, n_ok);
-  st.nxt = load_slopes(p, min(d + 1, D - 1), n, n_ok);
+  st.tb = tb;
+  st.k = 0;
+  st.nd = nd;
+  if (TBL) {
+    st.cur = table_read(p, tb, 0);
+    st.nxt = st.cur;
+  } else {
+    st.cur = load_slopes(p, d, n, n_ok);
+    st.nxt = load_slopes(p, min(d + 1, D - 1), n, n_ok);
+  }
   st.run = 0.f;
   st.run2 = 0.f;
   st.d = d;
@@ -167,22 +219,22 @@ __device__ __forceinline__ void adjoint_chunk(const Params& p, uint32_t taddr, c
     }
     if (vm == 0xffu && (bm & (bm - 1u)) == 0u) {
       switch (bm ? (__ffs((int)bm) - 1) : 8) {
-        case 0: group_static<0>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 1: group_static<1>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 2: group_static<2>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 3: group_static<3>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 4: group_static<4>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 5: group_static<5>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 6: group_static<6>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        case 7: group_static<7>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
-        default: group_static<8>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 0: group_static<0, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 1: group_static<1, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 2: group_static<2, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 3: group_static<3, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 4: group_static<4, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 5: group_static<5, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 6: group_static<6, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        case 7: group_static<7, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
+        default: group_static<8, TBL>(p, st, v, ah, nb, hout_cta, rowstride, st_ok, n, n_ok, D); break;
       }
     } else {
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         if (vm & (1u << u)) {
           row_step(st, ah[u], v[u], nb, hout_cta, rowstride, st_ok);
-          if (bm & (1u << u)) boundary_step(p, st, n, n_ok, D);
+          if (bm & (1u << u)) boundary_step<TBL>(p, st, n, n_ok, D);
         }
       }
     }
@@ -330,25 +382,51 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
       const unsigned rowstride = (unsigned)p.N * 4u;
       const char* __restrict__ ahat_cta = reinterpret_cast<const char*>(p.Ahat + (size_t)m0 * p.N);
       char* __restrict__ hout_cta = reinterpret_cast<char*>(p.hout + (size_t)m0 * p.N);
-      for (int t = 0; t < nf; ++t) {
-        if (nbase + t * FT + q * 32 >= p.N) continue;  // warp-uniform: no feature of this quarter exists
+      // All MMAs have completed, so the pipeline stages are free: each warp keeps two slope tables there
+      // (double buffer: the next chunk's slopes are copied asynchronously while the current chunk is processed).
+      float* tbl = reinterpret_cast<float*>(tiles) + warp * (2 * TBL_FLOATS) + lane;
+      const int nchunks = 2 * nf;  // chunk i: feature tile i >> 1, row chunk part + 4 * (i & 1)
+      auto chunk_geom = [&](int i, int& t, int& rbase, int& d0, int& nd) -> bool {
+        t = i >> 1;
+        rbase = m0 + (part + (WARPS / 4) * (i & 1)) * 32;
+        if (i >= nchunks || rbase >= p.M || nbase + t * FT + q * 32 >= p.N) return false;
+        d0 = rbase / p.S;
+        nd = min(rbase + 31, p.M - 1) / p.S - d0 + 1;
+        return true;
+      };
+      auto feature_of = [&](int t) { return min(nbase + t * FT + q * 32 + lane, p.N - 1); };
+      {
+        int t, rbase, d0, nd;
+        if (chunk_geom(0, t, rbase, d0, nd) && nd <= TBLD) table_fill(p, tbl, d0, nd, feature_of(t));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
+      for (int i = 0; i < nchunks; ++i) {
+        {
+          int t, rbase, d0, nd;
+          if (chunk_geom(i + 1, t, rbase, d0, nd) && nd <= TBLD) table_fill(p, tbl + ((i + 1) & 1) * TBL_FLOATS, d0, nd, feature_of(t));
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this chunk's table has landed
+        int t, rbase, d, nd;
+        if (!chunk_geom(i, t, rbase, d, nd)) continue;
         const int n_raw = nbase + t * FT + q * 32 + lane;
         const bool n_ok = n_raw < p.N;
         const int n = min(n_raw, p.N - 1);             // addresses stay valid; stores and sums are predicated on n_ok
         const bool st_ok = n_ok && p.hout != nullptr;
         const float nb = p.nbias ? __ldg(p.nbias + n) : 0.f;
-        for (int ch = part; ch < RB / 32; ch += WARPS / 4) {
-          const int rbase = m0 + ch * 32;
-          if (rbase >= p.M) break;
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * RB + ch * 32);
-          const int rl = rbase + lane;
-          const unsigned vmask = __ballot_sync(0xffffffffu, rl < p.M);
-          const unsigned bmask = __ballot_sync(0xffffffffu, (rl + 1) % p.S == 0 || rl == p.M - 1 || lane == 31) & vmask;
-          const unsigned off = (unsigned)(ch * 32) * rowstride + (unsigned)n * 4u;
-          const int d = rbase / p.S;
-          adjoint_chunk(p, taddr, ahat_cta, hout_cta, off, rowstride, n, n_ok, st_ok, nb, d, D, vmask, bmask);
-        }
+        const int ch = (rbase - m0) >> 5;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * RB + ch * 32);
+        const int rl = rbase + lane;
+        const unsigned vmask = __ballot_sync(0xffffffffu, rl < p.M);
+        const unsigned bmask = __ballot_sync(0xffffffffu, (rl + 1) % p.S == 0 || rl == p.M - 1 || lane == 31) & vmask;
+        const unsigned off = (unsigned)(ch * 32) * rowstride + (unsigned)n * 4u;
+        const float* tb = tbl + (i & 1) * TBL_FLOATS;
+        if (nd <= TBLD)
+          adjoint_chunk<true>(p, taddr, ahat_cta, hout_cta, off, rowstride, n, n_ok, st_ok, nb, d, D, vmask, bmask, tb, nd);
+        else
+          adjoint_chunk<false>(p, taddr, ahat_cta, hout_cta, off, rowstride, n, n_ok, st_ok, nb, d, D, vmask, bmask, tb, nd);
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       tc_fence_before();
     }
   } else if (warp == COPY_WARP) {

@@ -30,6 +30,20 @@ class _ffma:
         os.environ.pop("BF_B200_FORCE_FFMA", None)
 
 
+class _adjoint_kernel:
+    """Pins the tensor-core adjoint kernel: "fm" = feature-major (features on the MMA's M side, the default
+    once its 256x256 CTAs fill the GPU), "rows" = row-major; read at every launch."""
+
+    def __init__(self, which):
+        self.var = {"fm": "BF_B200_ADJ_FEATURE_MAJOR", "rows": "BF_B200_ADJ_ROWMAJOR"}[which]
+
+    def __enter__(self):
+        os.environ[self.var] = "1"
+
+    def __exit__(self, *a):
+        os.environ.pop(self.var, None)
+
+
 def _spec(wl, dev):
     from boundflow_b200.ir import InputSpec
 
@@ -70,7 +84,8 @@ def test_tc_crown_matches_ffma_and_oracle_c3(dev):
     assert_close(up_tc, up_ref, "tc vs oracle upper")
 
 
-def test_tc_gradient_matches_ffma_and_oracle(dev):
+@pytest.mark.parametrize("adjoint", ["fm", "rows"])
+def test_tc_gradient_matches_ffma_and_oracle(dev, adjoint):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_grad_from_trace, ibp_trace
     from oracle import crown_oracle as O
@@ -81,7 +96,8 @@ def test_tc_gradient_matches_ffma_and_oracle(dev):
     trace = ibp_trace(wl.module, spec)
     a0 = adaptive_alpha_from_trace(trace)
     a0 = [0.25 + 0.5 * a for a in a0]      # interior alpha: both sign branches carry gradient
-    g_tc, lo_tc = alpha_grad_from_trace(trace, C, a0)
+    with _adjoint_kernel(adjoint):
+        g_tc, lo_tc = alpha_grad_from_trace(trace, C, a0)
     with _ffma():
         g_ff, lo_ff = alpha_grad_from_trace(trace, C, a0)
     torch.cuda.synchronize()
@@ -97,8 +113,10 @@ def test_tc_gradient_matches_ffma_and_oracle(dev):
         assert_close(g_tc[r], g_ref[r], f"grad {r} tc vs oracle", atol=2e-5 * scale, rtol=1e-4)
 
 
-@pytest.mark.parametrize("widths,B,S", [((784, 200, 136, 10), 60, 5), ((100, 72, 40, 33, 7), 300, 1), ((64, 512, 300, 10), 29, 9)])
-def test_tc_ragged_shapes(dev, widths, B, S):
+@pytest.mark.parametrize("adjoint", ["fm", "rows"])
+@pytest.mark.parametrize("widths,B,S", [((784, 200, 136, 10), 60, 5), ((100, 72, 40, 33, 7), 300, 1), ((64, 512, 300, 10), 29, 9),
+                                        ((48, 130, 260, 10), 37, 12)])
+def test_tc_ragged_shapes(dev, widths, B, S, adjoint):
     """Layer widths that are not multiples of the 32-wide k-block or the column tile,
     row counts that are not multiples of 128, and S values that put several domains in
     one 8-row group."""
@@ -126,22 +144,27 @@ def test_tc_ragged_shapes(dev, widths, B, S):
     scale = max(1.0, float(lo_ref.abs().max()))
     assert_close(lo_tc, lo_ref, "lower", atol=1e-4 + 2e-6 * scale)
     assert_close(up_tc, up_ref, "upper", atol=1e-4 + 2e-6 * scale)
-    grads, lower = alpha_grad_from_trace(trace, C.to(dev), [a.to(dev) for a in alpha])
+    with _adjoint_kernel(adjoint):
+        grads, lower = alpha_grad_from_trace(trace, C.to(dev), [a.to(dev) for a in alpha])
+    torch.cuda.synchronize()
+    assert trace.chain.tc_status() == 0
     g_ref, _ = O.alpha_gradient(layers, inp, tr, C, alpha)
     for r in range(len(grads)):
         s = max(1e-3, float(g_ref[r].abs().max()))
         assert_close(grads[r], g_ref[r], f"grad {r}", atol=3e-5 * s, rtol=1e-4)
 
 
-def test_tc_is_deterministic(dev):
+@pytest.mark.parametrize("adjoint", ["fm", "rows"])
+def test_tc_is_deterministic(dev, adjoint):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
 
     wl = W.make_workload("c3", batch=48)
     trace = ibp_trace(wl.module, _spec(wl, dev))
     a0 = adaptive_alpha_from_trace(trace)
-    r1 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
-    r2 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
+    with _adjoint_kernel(adjoint):
+        r1 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
+        r2 = alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=4, lr=0.1)
     torch.cuda.synchronize()
     assert trace.chain.tc_status() == 0
     assert torch.equal(r1[0], r2[0]) and torch.equal(r1[1], r2[1])
