@@ -59,10 +59,61 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_bwd_linear_kernel(GemmA
   }
 }
 
+// Top layer of a sweep (no ReLU in front, K = spec width <= 16): A_prev[M,N] = A[M,K] * W[K,N] and
+// delta[m] (+)= sum_k A[m,k] * kbias[k].  A store-bound pass, so no tiles: a thread keeps its four
+// columns of W in registers and walks the block's rows, whose K values sit in shared memory.
+constexpr int THIN_KMAX = 16;
+constexpr int THIN_ROWS = 64;
+__global__ void __launch_bounds__(128) crown_bwd_thin_kernel(const float* __restrict__ A, const float* __restrict__ W,
+                                                             const float* __restrict__ kbias, float* __restrict__ out,
+                                                             float* __restrict__ delta, int accumulate, int M, int K, int N) {
+  __shared__ float a_s[THIN_ROWS * THIN_KMAX];
+  const int m0 = blockIdx.x * THIN_ROWS;
+  const int rows = min(THIN_ROWS, M - m0);
+  for (int i = threadIdx.x; i < rows * K; i += blockDim.x) a_s[i] = A[(size_t)m0 * K + i];
+  __syncthreads();
+  const int cg = blockIdx.y * blockDim.x + threadIdx.x;  // group of four columns
+  if (cg * 4 < N) {
+    float4 w[THIN_KMAX];
+#pragma unroll
+    for (int k = 0; k < THIN_KMAX; ++k)
+      w[k] = (k < K) ? *reinterpret_cast<const float4*>(W + (size_t)k * N + cg * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < rows; ++r) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < THIN_KMAX; ++k) {
+        if (k < K) {
+          const float a = a_s[r * K + k];
+          acc.x = fmaf(a, w[k].x, acc.x); acc.y = fmaf(a, w[k].y, acc.y);
+          acc.z = fmaf(a, w[k].z, acc.z); acc.w = fmaf(a, w[k].w, acc.w);
+        }
+      }
+      *reinterpret_cast<float4*>(out + (size_t)(m0 + r) * N + cg * 4) = acc;
+    }
+  }
+  if (delta && blockIdx.y == 0) {
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+      float sum = 0.f;
+      if (kbias)
+        for (int k = 0; k < K; ++k) sum = fmaf(a_s[r * K + k], __ldg(kbias + k), sum);
+      delta[m0 + r] = accumulate ? delta[m0 + r] + sum : sum;
+    }
+  }
+}
+
 int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                             const float* add, const float* W, const float* kbias, float* A_prev, float* delta,
                             int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S,
                             int K, int N, cudaStream_t stream) {
+  if (!dpos && !add && !partial && A_prev && K <= THIN_KMAX && N % 4 == 0 &&
+      ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(A_prev)) & 15u) == 0) {
+    dim3 grid(ceil_div(M, THIN_ROWS), ceil_div(N / 4, 128));
+    timing_begin(0, stream);
+    crown_bwd_thin_kernel<<<grid, 128, 0, stream>>>(A, W, kbias, A_prev, delta, accumulate, M, K, N);
+    timing_end(0, stream);
+    BF_CHECK_LAUNCH("crown_bwd_thin_kernel");
+    return BF_OK;
+  }
   GemmArgs g{};
   g.A = A; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
   const void* kptrs[] = {A, dpos, dneg, epos, eneg, add, kbias};
