@@ -381,7 +381,7 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {
-            "bound": "tensor", "kernel": "crown_tc_kernel<bwd> (ReLU-backward + Linear-backward contraction, tcgen05 3xTF32; the 10-wide top layer runs as FFMA tiles)",
+            "bound": "tensor", "kernel": "crown_tc_kernel<bwd> (ReLU-backward + Linear-backward contraction, tcgen05 3xTF32; the 10-wide top layer runs as a store-bound thin kernel)",
             "achieved": achieved, "peak": fp32_equiv_peak, "unit": "TFLOP/s", "frac": (achieved / fp32_equiv_peak) if achieved else None,
             "traffic": TRAFFIC_BYTES_PER_LAUNCH * (D / 8192.0),
             "traffic_source": "ncu dram__bytes_read+write of one 512x512-layer launch at 4096 domains, scaled by rows (profiles/)",
