@@ -311,12 +311,13 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
 
     load_block(0);
     bool alive = true;
+    const int pf_kb = max(1, p.nkb - 5);  // late enough that the lines are still in L2 when the epilogue starts
     for (int kb = 0; kb < p.nkb; ++kb) {
       float4 a_cur[ROWS_PER_THREAD];
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) a_cur[i] = a_next[i];
       if (kb + 1 < p.nkb) load_block(kb + 1);
-      if (kb == 1) {
+      if (kb == pf_kb) {
         // the epilogue will read this tile's saved coefficients: start pulling their lines into L2 now
         const int lpr = nf * (FT / 32);  // 128-byte lines per row
         for (int idx = tid; idx < RB * lpr; idx += PRODUCERS) {
