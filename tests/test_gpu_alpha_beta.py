@@ -33,7 +33,19 @@ def _c4_domains(D, dev):
     return wl, splits, spec, C, lo, up
 
 
-def test_alpha_beta_matches_reference_golden(dev, golden):
+@pytest.fixture(params=["default", "feature_major"])
+def adjoint_kernel(request):
+    """Runs a test with the default choice of the tensor-core adjoint kernel (row-major at these sizes) and with the
+    feature-major kernel pinned, so that its beta-gradient sums are covered at small, ragged row counts too."""
+    import os
+
+    if request.param == "feature_major":
+        os.environ["BF_B200_ADJ_FEATURE_MAJOR"] = "1"
+    yield request.param
+    os.environ.pop("BF_B200_ADJ_FEATURE_MAJOR", None)
+
+
+def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel):
     from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, crown_from_trace, ibp_trace, run_alpha_beta_crown_mlp
 
     g = golden("c4_split_alpha_beta.npz")
@@ -67,7 +79,7 @@ def test_alpha_beta_matches_reference_golden(dev, golden):
     assert (got == g["branch_choices"]).all()
 
 
-def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev):
+def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev, adjoint_kernel):
     from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
     from oracle import crown_oracle as O
 
