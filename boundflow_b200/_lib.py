@@ -40,6 +40,9 @@ SIGNATURES = {
     "bf_launch_count": (C.c_ulonglong, []),
     "bf_kernel_timing_enable": (None, [_i]),
     "bf_kernel_timing_read": (_i, [_i, C.POINTER(_i), C.POINTER(_f)]),
+    "bf_kernel_timing_slots": (_i, []),
+    "bf_kernel_timing_slot_name": (C.c_char_p, [_i]),
+    "bf_kernel_timing_read_work": (_i, [_i, C.POINTER(_i), C.POINTER(_f), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "bf_ibp_linear": (_i, [_p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "bf_ibp_conv2d": (_i, [_p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p] + [_i] * 11 + [_p]),
     "bf_relu_relax": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _p]),
@@ -51,6 +54,7 @@ SIGNATURES = {
     "bf_crown_relu_conv2d_bwd_noalloc": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i] + [_i] * 14 + [_p]),
     "bf_concretize": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "bf_verdict": (_i, [_p, _f, _f, _p, _p, _i, _i, _p]),
+    "bf_verdict_masked": (_i, [_p, _f, _f, _p, _p, _p, _i, _i, _p]),
     "bf_chain_create": (_i, [C.POINTER(LayerDesc), _i, C.POINTER(_p)]),
     "bf_chain_destroy": (None, [_p]),
     "bf_chain_num_relu": (_i, [_p]),

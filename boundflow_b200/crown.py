@@ -98,12 +98,15 @@ class ForwardTrace:
     eps: float = 0.0
 
 
-def _prepare_input(module: Any, input_spec: Any):
+def _prepare_input(module: Any, input_spec: Any, batch: Optional[int] = None):
+    """`batch`: number of domains when the input set is given once (leading dimension 1) for all of them, as in a
+    batch of ReLU-split subdomains of one input; the row is then repeated on the device, not uploaded B times."""
     spec = normalize_input_spec(input_spec)
     center = spec.center
     device = _cuda_device(center)
     chain = compile_chain(module, tuple(int(d) for d in center.shape[1:]), device)
     B = int(center.shape[0])
+    repeat = batch is not None and int(batch) > 1 and B == 1
     ball = lp_ball_of(spec)
     if ball is not None:  # L1 / L2 ball: centre + eps; the radius tensor is only used by a conv first layer (bounding box)
         mid = _f32(center, device).reshape(B, -1)
@@ -112,6 +115,10 @@ def _prepare_input(module: Any, input_spec: Any):
         mid, rad, _lo, _up = input_mid_rad(spec)
         mid = _f32(mid, device).reshape(B, -1)
         rad = _f32(rad, device).reshape(B, -1)
+    if repeat:
+        B = int(batch)
+        mid = mid.expand(B, -1).contiguous()
+        rad = rad.expand(B, -1).contiguous()
     return spec, chain, device, B, mid, rad, center.device
 
 
@@ -140,9 +147,10 @@ def ibp_trace(
     *,
     relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
     relu_pre_constraints: Optional[Mapping[str, Any]] = None,
+    batch: Optional[int] = None,
 ) -> ForwardTrace:
-    """Run the IBP sweep on the device and keep everything there."""
-    _spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
+    """Run the IBP sweep on the device and keep everything there.  `batch`: see `_prepare_input`."""
+    _spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec, batch)
     lib = chain.lib
     R = len(chain.relu_layer_ids)
     pre_l = [torch.empty(B, n, dtype=torch.float32, device=device) for n in chain.relu_widths]
@@ -269,6 +277,8 @@ def _expand_spec(C: Optional[torch.Tensor], B: int, out_dim: int, device: torch.
         C = C.unsqueeze(0).expand(B, C.shape[0], out_dim)
     if C.dim() != 3:
         raise ValueError(f"linear_spec_C expects rank-3 [B,S,O], got {tuple(C.shape)}")
+    if int(C.shape[0]) == 1 and B > 1 and int(C.shape[2]) == out_dim:
+        C = C.expand(B, C.shape[1], out_dim)  # one spec block shared by every domain: repeated on the device
     if int(C.shape[0]) != B or int(C.shape[2]) != out_dim:
         raise ValueError(f"linear_spec_C shape mismatch: C={tuple(C.shape)} out=({B}, {out_dim})")
     return C.contiguous()
@@ -894,14 +904,23 @@ def bound_split_domains(
     the proven test at 881-895) without the whole-batch ValueError: an infeasible
     domain is flagged in `infeasible` instead (the driver's per-node fallback,
     bab.py:1400-1460, exists only to recover from that exception).  No host
-    synchronisation happens inside; tensors follow the input's device."""
-    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
+    synchronisation happens inside; tensors follow the input's device.
+
+    The subdomains of one BaB problem share the input box and the spec rows: both may be given once (`lower`/`upper`
+    of shape [1, ...], `linear_spec_C` [S,O] or [1,S,O]) with the batch size taken from the split tensors; they are
+    then repeated on the device instead of being uploaded once per subdomain."""
+    batch = None
+    if relu_split_state:
+        rows = [int(s.shape[0]) for s in relu_split_state.values() if torch.is_tensor(s) and s.dim() == 2]
+        batch = max(rows) if rows else None
+    trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state, batch=batch)
     chain, B, device = trace.chain, trace.B, trace.mid.device
     a0 = list(warm_start_alpha) if warm_start_alpha is not None else adaptive_alpha_from_trace(trace)
     best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(
         trace, linear_spec_C, a0, steps=steps, lr=lr, spec_reduce=spec_reduce, want_upper=want_upper)
     verdict = torch.empty(B, dtype=torch.int8, device=device)
-    _lib.check(chain.lib.bf_verdict(_lib.ptr(best_l), float(threshold), float(tol), _lib.ptr(verdict), None, B, int(best_l.shape[1]), _stream_ptr(device)))
+    # infeasible domains never count as proven; a NaN bound (e.g. the poison written when a tensor-core wait expired) neither
+    _lib.check(chain.lib.bf_verdict_masked(_lib.ptr(best_l), float(threshold), float(tol), _lib.ptr(trace.infeasible), _lib.ptr(verdict), None, B, int(best_l.shape[1]), _stream_ptr(device)))
     out_dev = normalize_input_spec(input_spec).center.device
     if out_dev != device:
         return DomainBatchResult(best_l.to(out_dev), None if best_u is None else best_u.to(out_dev), verdict.to(out_dev), trace.infeasible.to(out_dev), [a.to(out_dev) for a in best_a])

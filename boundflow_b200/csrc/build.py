@@ -50,19 +50,5 @@ def build(verbose: bool = False, force: bool = False) -> str:
     return LIB
 
 
-def build_mma_rate() -> str:
-    """Compiles the stand-alone tcgen05 TF32 MMA-rate micro-benchmark next to its source."""
-    out = os.path.join(HERE, "mma_rate")
-    cmd = [_nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, os.path.join(HERE, "mma_rate.cu")]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        sys.stderr.write(proc.stdout + proc.stderr)
-        raise RuntimeError("nvcc failed building mma_rate")
-    return out
-
-
 if __name__ == "__main__":
-    if "--mma-rate" in sys.argv:
-        exe = build_mma_rate()
-        sys.exit(subprocess.run([exe]).returncode)
     print(build(verbose="--verbose" in sys.argv, force=True))

@@ -155,11 +155,8 @@ extern "C" int bf_first_layer_certificate(const int8_t* split, int split_stride,
   BF_REQUIRE(split_stride == 0 || split_stride == n1, BF_E_INVALID, "bf_first_layer_certificate: split_stride must be 0 or n1");
   const size_t smem = ((size_t)bf::CERT_MAX_M + 2) * n0 * sizeof(float);
   BF_REQUIRE(smem <= 200 * 1024, BF_E_UNSUPPORTED, "bf_first_layer_certificate: input dimension %d too large for one block", n0);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(bf::first_layer_cert_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
-  }
+  static bf::SmemOptIn opt_in;
+  if (int rc = bf::ensure_dynamic_smem(bf::first_layer_cert_kernel, 200 * 1024, opt_in, "first_layer_cert_kernel")) return rc;
   bf::first_layer_cert_kernel<<<B, bf::CERT_THREADS, smem, bf::as_stream(stream)>>>(split, split_stride, W1, b1, mid, rad, n1, n0, steps,
                                                                                   lr, tol, infeasible, best_value, n_halfspaces);
   BF_CHECK_LAUNCH("first_layer_cert_kernel");

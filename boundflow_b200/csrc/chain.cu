@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <vector>
 
 #include "chain_internal.cuh"
@@ -24,43 +25,74 @@ void set_error(const char* fmt, ...) {
 }
 
 // ---- optional kernel timing ----------------------------------------------------
+// One mutex guards the slots: launches from several host threads interleave their event pairs safely
+// (a begin/end pair is matched by slot and thread: the open event index is kept per thread).
 struct TimingSlot {
   std::vector<cudaEvent_t> start, stop;
   size_t used = 0;
+  double bytes = 0.0, flops = 0.0;
 };
-static TimingSlot g_timing[2];
-static bool g_timing_on = false;
+static TimingSlot g_timing[T_SLOTS];
+static std::atomic<bool> g_timing_on{false};
+static std::mutex g_timing_mutex;
+static thread_local long long g_timing_open[T_SLOTS];  // index + 1 of this thread's open event pair per slot
 
 void timing_begin(int slot, cudaStream_t stream) {
-  if (!g_timing_on) return;
+  if (!g_timing_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
   TimingSlot& t = g_timing[slot];
+  g_timing_open[slot] = 0;
   if (t.used == t.start.size()) {
     cudaEvent_t a, b;
-    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    if (cudaEventCreate(&a) != cudaSuccess) return;
+    if (cudaEventCreate(&b) != cudaSuccess) {
+      cudaEventDestroy(a);
+      return;
+    }
     t.start.push_back(a);
     t.stop.push_back(b);
   }
   cudaEventRecord(t.start[t.used], stream);
+  g_timing_open[slot] = (long long)(++t.used);
 }
 
-void timing_end(int slot, cudaStream_t stream) {
-  if (!g_timing_on) return;
+void timing_end(int slot, cudaStream_t stream, double bytes, double flops) {
+  if (g_timing_open[slot] == 0) return;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
   TimingSlot& t = g_timing[slot];
-  if (t.used < t.stop.size()) {
-    cudaEventRecord(t.stop[t.used], stream);
-    ++t.used;
-  }
+  const size_t idx = (size_t)(g_timing_open[slot] - 1);
+  g_timing_open[slot] = 0;
+  if (idx >= t.used) return;  // the slots were reset between begin and end
+  cudaEventRecord(t.stop[idx], stream);
+  t.bytes += bytes;
+  t.flops += flops;
 }
+
+static const char* const g_timing_names[T_SLOTS] = {
+    "crown_bwd_contraction", "crown_adjoint_contraction", "crown_bwd_thin_kernel", "ibp_linear_kernel", "ibp_conv2d_kernel",
+    "adam_step_kernel", "concretize_kernel", "relu_bwd_window_kernel", "conv_transpose_kernel", "relu_bwd_rows_kernel"};
 
 }  // namespace bf
 
 extern "C" void bf_kernel_timing_enable(int on) {
-  bf::g_timing_on = on != 0;
-  for (auto& t : bf::g_timing) t.used = 0;
+  std::lock_guard<std::mutex> lock(bf::g_timing_mutex);
+  bf::g_timing_on.store(on != 0);
+  for (auto& t : bf::g_timing) {
+    t.used = 0;
+    t.bytes = 0.0;
+    t.flops = 0.0;
+  }
 }
 
-extern "C" int bf_kernel_timing_read(int slot, int* launches, float* total_ms) {
-  BF_REQUIRE(slot >= 0 && slot < 2 && launches && total_ms, BF_E_INVALID, "bf_kernel_timing_read: bad argument");
+extern "C" int bf_kernel_timing_slots(void) { return bf::T_SLOTS; }
+
+extern "C" const char* bf_kernel_timing_slot_name(int slot) {
+  return (slot >= 0 && slot < bf::T_SLOTS) ? bf::g_timing_names[slot] : "";
+}
+
+extern "C" int bf_kernel_timing_read_work(int slot, int* launches, float* total_ms, double* bytes, double* flops) {
+  BF_REQUIRE(slot >= 0 && slot < bf::T_SLOTS && launches && total_ms, BF_E_INVALID, "bf_kernel_timing_read: bad argument");
+  std::lock_guard<std::mutex> lock(bf::g_timing_mutex);
   bf::TimingSlot& t = bf::g_timing[slot];
   float sum = 0.f;
   for (size_t i = 0; i < t.used; ++i) {
@@ -74,7 +106,13 @@ extern "C" int bf_kernel_timing_read(int slot, int* launches, float* total_ms) {
   }
   *launches = (int)t.used;
   *total_ms = sum;
+  if (bytes) *bytes = t.bytes;
+  if (flops) *flops = t.flops;
   return BF_OK;
+}
+
+extern "C" int bf_kernel_timing_read(int slot, int* launches, float* total_ms) {
+  return bf_kernel_timing_read_work(slot, launches, total_ms, nullptr, nullptr);
 }
 
 
@@ -184,22 +222,28 @@ namespace bf {
 
 // The feature-major adjoint kernel works on 256-row x 256-feature CTAs: it pays off once those fill the GPU;
 // smaller problems keep the row-major kernel (128-row CTAs, twice as many of them).
-static bool adjoint_feature_major(int M, int N) {
-  const char* e = getenv("BF_B200_ADJ_ROWMAJOR");  // "1": always the row-major kernel
-  if (e && e[0] == '1') return false;
-  const char* f = getenv("BF_B200_ADJ_FEATURE_MAJOR");  // "1": always the feature-major kernel
-  if (f && f[0] == '1') return true;
+static bool env_is_one(const char* name) {
+  const char* e = getenv(name);
+  return e && e[0] == '1';
+}
+
+void refresh_switches(const bf_chain* c) {
+  c->sw.force_ffma = env_is_one("BF_B200_FORCE_FFMA");
+  c->sw.adjoint_kernel = env_is_one("BF_B200_ADJ_ROWMAJOR") ? 1 : (env_is_one("BF_B200_ADJ_FEATURE_MAJOR") ? 2 : 0);
+  c->sw.no_windows = getenv("BF_B200_NO_WINDOWS") != nullptr;
+}
+
+bool tc_may_run(const bf_chain* c, int M) { return c->status != nullptr && !c->pk_bwd.empty() && !c->sw.force_ffma && M >= 256; }
+
+static bool adjoint_feature_major(const bf_chain* c, int M, int N) {
+  if (c->sw.adjoint_kernel == 1) return false;
+  if (c->sw.adjoint_kernel == 2) return true;
   const long long ctas = (long long)((M + 255) / 256) * ((((N + tc_adjoint_tile_rows() - 1) / tc_adjoint_tile_rows()) + 1) / 2);
   return ctas >= 128;
 }
 
-static bool tc_allowed() {
-  const char* e = getenv("BF_B200_FORCE_FFMA");
-  return !(e && e[0] == '1');
-}
-
 static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoint, int M, int K, int N) {
-  if (c->pk_bwd.empty() || !tc_allowed()) return nullptr;
+  if (c->pk_bwd.empty() || c->sw.force_ffma) return nullptr;
   if (M < 256 || K < 32 || N < 32) return nullptr;  // tiny problems stay on the FFMA tiles
   return adjoint ? c->pk_adj[layer] : c->pk_bwd[layer];
 }
@@ -230,7 +274,7 @@ int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first
   const bf_layer_desc& L = c->layers[layer];
   const int K = L.n_in, N = L.n_out;
   const unsigned char* pk = tc_weights(c, layer, true, M, K, N);
-  if (pk && adjoint_feature_major(M, N))
+  if (pk && adjoint_feature_major(c, M, N))
     return launch_crown_adjoint_linear_tc_fm(Hprev, first_layer, mid, rad, c->pk_adj_fm[layer], L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
                                              hout, grad, gsum, M, S, K, N, c->status, stream);
   if (pk)
@@ -464,7 +508,8 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
   // identity-row sweeps on conv layers keep only the window of each row that can be non-zero (see conv.cu)
   bf::WindowGeom win{};
   bool windowed = false;
-  const bool windows_allowed = box && influence == nullptr && getenv("BF_B200_NO_WINDOWS") == nullptr;
+  bf::refresh_switches(chain);
+  const bool windows_allowed = box && influence == nullptr && !chain->sw.no_windows;
   for (int i = upto_layer - 1; i >= 0; --i) {
     const bf_layer_desc& L = chain->layers[i];
     if (L.op == BF_OP_FLATTEN) continue;
@@ -550,10 +595,13 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
     pending = -1;
   }
   BF_REQUIRE(pending < 0, BF_E_UNSUPPORTED, "bf_chain_crown: a ReLU directly on the input is not supported");
-  if (windowed) return bf::launch_concretize_window(curA, mid, rad, ws.cacc, out, side, win, M, stream);
-  if (fused_concretize) return bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
-  if (!box) return bf::launch_concretize_lp(curA, mid, have_c ? ws.cacc : nullptr, out, side, eps, norm_p, B, S, chain->n0, stream);
-  return bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
+  int rc;
+  if (windowed) rc = bf::launch_concretize_window(curA, mid, rad, ws.cacc, out, side, win, M, stream);
+  else if (fused_concretize) rc = bf::launch_sum_partials(ws.cacc, ws.partial, ptiles, out, M, stream);
+  else if (!box) rc = bf::launch_concretize_lp(curA, mid, have_c ? ws.cacc : nullptr, out, side, eps, norm_p, B, S, chain->n0, stream);
+  else rc = bf::launch_concretize(curA, mid, rad, have_c ? ws.cacc : nullptr, out, side, B, S, chain->n0, stream);
+  if (rc == BF_OK && bf::tc_may_run(chain, M)) rc = bf::launch_poison_on_status(chain->status, out, M, nullptr, 0, stream);
+  return rc;
 }
 
 extern "C" int bf_chain_crown(const bf_chain* chain, int upto_layer, int side, const float* C,

@@ -236,6 +236,7 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
   cudaStream_t stream = bf::as_stream(stream_);
   const int R = (int)chain->relu_layers.size();
   float* metric = best_metric ? best_metric : ws.metric;
+  bf::refresh_switches(chain);
 
   if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
     bf::set_error("%s: cudaMemsetAsync failed", who);
@@ -286,6 +287,12 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
     rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, in, best_upper, B, S, stream);
     if (rc != BF_OK) return rc;
   }
+  if (bf::tc_may_run(chain, B * S)) {  // a tensor-core wait that expired invalidates every bound of this call
+    rc = bf::launch_poison_on_status(chain->status, best_lower, (long long)B * S, best_upper, best_upper ? (long long)B * S : 0, stream);
+    if (rc != BF_OK) return rc;
+    rc = bf::launch_poison_on_status(chain->status, metric, B, nullptr, 0, stream);
+    if (rc != BF_OK) return rc;
+  }
   return BF_OK;
 }
 
@@ -309,6 +316,7 @@ extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const 
                                B, S, false, &ws);
   if (rc != BF_OK) return rc;
   BF_REQUIRE(grad && lower, BF_E_INVALID, "bf_chain_alpha_grad: null output");
+  bf::refresh_switches(chain);
   cudaStream_t stream = bf::as_stream(stream_);
   const int R = (int)chain->relu_layers.size();
   if (cudaMemsetAsync(static_cast<char*>(workspace) + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess) {
@@ -329,6 +337,10 @@ extern "C" int bf_chain_alpha_grad(const bf_chain* chain, const float* C, const 
     const int n = chain->layers[chain->relu_layers[r]].n_in;
     rc = bf::launch_scale_copy(ws.grad[r], scale, grad[r], (long long)B * n, stream);
     if (rc != BF_OK) return rc;
+    if (bf::tc_may_run(chain, B * S)) {
+      rc = bf::launch_poison_on_status(chain->status, grad[r], (long long)B * n, r == 0 ? lower : nullptr, (long long)B * S, stream);
+      if (rc != BF_OK) return rc;
+    }
   }
   return BF_OK;
 }
@@ -398,6 +410,7 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   const int R = (int)chain->relu_layers.size();
   const long long M = (long long)B * S;
   float* metric = best_metric ? best_metric : ws.metric;
+  bf::refresh_switches(chain);
   char* wsb = static_cast<char*>(workspace);
   // also clears the split term of ReLUs without a split (ws.addv lies inside the state region)
   if (cudaMemsetAsync(wsb + ws.state_begin, 0, ws.state_bytes, stream) != cudaSuccess ||
@@ -449,6 +462,12 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   if (best_upper) {  // beta acts on the lower side only
     if ((rc = relax_all(best_alpha)) != BF_OK) return rc;
     rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_UPPER, false, false, in, best_upper, B, S, stream);
+    if (rc != BF_OK) return rc;
+  }
+  if (bf::tc_may_run(chain, B * S)) {  // a tensor-core wait that expired invalidates every bound of this call
+    rc = bf::launch_poison_on_status(chain->status, best_lower, (long long)B * S, best_upper, best_upper ? (long long)B * S : 0, stream);
+    if (rc != BF_OK) return rc;
+    rc = bf::launch_poison_on_status(chain->status, metric, B, nullptr, 0, stream);
     if (rc != BF_OK) return rc;
   }
   return BF_OK;

@@ -17,6 +17,14 @@ struct bf_chain {
   // adjoint (W as B) orientation inside a caller-owned buffer, plus a device status word
   std::vector<const unsigned char*> pk_bwd, pk_adj, pk_adj_fm;  // pk_adj_fm: 128-row images for the feature-major adjoint kernel
   int* status = nullptr;
+  // A/B switches (environment variables BF_B200_*), refreshed at the start of every whole-chain call and read by
+  // the per-layer dispatch of that call
+  struct Switches {
+    bool force_ffma = false;        // BF_B200_FORCE_FFMA=1: FP32 FFMA tiles instead of the tensor-core kernels
+    int adjoint_kernel = 0;         // 0 automatic, 1 row-major (BF_B200_ADJ_ROWMAJOR=1), 2 feature-major (BF_B200_ADJ_FEATURE_MAJOR=1)
+    bool no_windows = false;        // BF_B200_NO_WINDOWS set: identity-row sweeps keep full feature maps
+  };
+  mutable Switches sw;
 };
 
 namespace bf {
@@ -35,6 +43,11 @@ struct Carver {
   }
 };
 
+
+// Re-reads the BF_B200_* environment switches into chain->sw (called once per whole-chain entry point).
+void refresh_switches(const bf_chain* c);
+// True when a sweep over M coefficient rows may have run tensor-core kernels (whose status word then guards the results).
+bool tc_may_run(const bf_chain* c, int M);
 
 // Backward contraction of linear layer `layer` (tensor-core path when the packed weights exist and the
 // problem is large enough, FFMA tiles otherwise); *ptiles receives the number of column tiles of the

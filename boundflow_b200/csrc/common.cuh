@@ -34,10 +34,45 @@ inline void count_launch(int n = 1) { g_launches.fetch_add((unsigned long long)n
     bf::count_launch();                                                         \
   } while (0)
 
-// Optional per-launch device timing of the two contraction kernels (slot 0: backward,
-// slot 1: adjoint).  Off by default; when on, a CUDA event pair brackets every launch.
+// Optional per-launch device timing of the hot kernels.  Off by default; when on, a CUDA event pair
+// brackets every launch of a kernel that has a slot, and the launcher states the algorithmic work of
+// that launch (bytes that must cross HBM, floating-point operations), so that a caller can form
+// achieved GB/s and FLOP/s per kernel over any region it runs.
+enum TimingSlotId {
+  T_BWD = 0,          // backward contraction (tcgen05 or FFMA tiles)
+  T_ADJ = 1,          // adjoint contraction
+  T_THIN = 2,         // top layer of a sweep (spec width <= 16): store-bound
+  T_IBP_LINEAR = 3,
+  T_IBP_CONV = 4,
+  T_ADAM = 5,
+  T_CONCRETIZE = 6,   // stand-alone concretisation of coefficient rows
+  T_RELU_WINDOW = 7,  // ReLU scaling of windowed coefficient rows
+  T_CONV_T = 8,       // transposed convolution
+  T_RELU_ROWS = 9,    // ReLU scaling of full coefficient rows (conv path)
+  T_SLOTS = 10
+};
 void timing_begin(int slot, cudaStream_t stream);
-void timing_end(int slot, cudaStream_t stream);
+void timing_end(int slot, cudaStream_t stream, double bytes = 0.0, double flops = 0.0);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: every launcher that needs
+// more than 48 KB keeps one of these tables (a function-local static) and raises the limit once per device.
+constexpr int MAX_DEVICES = 64;
+struct SmemOptIn {
+  std::atomic<int> bytes[MAX_DEVICES];
+};
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, int bytes, SmemOptIn& table, const char* name) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) dev = -1;
+  if (dev >= 0 && table.bytes[dev].load(std::memory_order_acquire) >= bytes) return BF_OK;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_error("%s: cannot raise the dynamic shared memory limit to %d bytes: %s", name, bytes, cudaGetErrorString(e));
+    return BF_E_CUDA;
+  }
+  if (dev >= 0) table.bytes[dev].store(bytes, std::memory_order_release);
+  return BF_OK;
+}
 
 inline cudaStream_t as_stream(bf_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 

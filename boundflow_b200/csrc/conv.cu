@@ -87,7 +87,10 @@ int launch_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, int rel
   const long long total = (long long)B * L.Co * L.Ho * L.Wo;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
+  timing_begin(T_IBP_CONV, stream);
   ibp_conv2d_kernel<<<(int)blocks, 256, 0, stream>>>(g);
+  timing_end(T_IBP_CONV, stream, 4.0 * ((double)L.Co * L.Ci * L.kh * L.kw + L.Co) + 8.0 * (double)B * (L.n_in + L.n_out),
+             4.0 * (double)total * L.Ci * L.kh * L.kw);
   BF_CHECK_LAUNCH("ibp_conv2d_kernel");
   return BF_OK;
 }
@@ -552,11 +555,8 @@ static int launch_rowseg_tci(const ConvTArgs& g, cudaStream_t stream) {
   const size_t lam_words = (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * nlt;
   const size_t w_words = ((size_t)cc * KS * (KS * cib + 4) + 3) & ~(size_t)3;
   const size_t smem = 2 * (lam_words + w_words) * sizeof(float) + (size_t)(1 << a.mrl) * cc * G::tile_h(1 << a.thl) * sizeof(int);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC, TWP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
-    attr_done = true;
-  }
+  static SmemOptIn opt_in;
+  if (int rc = ensure_dynamic_smem(conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC, TWP>, 110 * 1024, opt_in, "conv_transpose_rowseg_kernel")) return rc;
   dim3 grid(ceil_div(g.M, 1 << a.mrl), a.tiles_x * a.tiles_y, ceil_div(g.Ci, cib));
   if (grid.y > 65535 || grid.z > 65535) return BF_E_UNSUPPORTED;
   conv_transpose_rowseg_kernel<KS, ST, PD, TCI, VEC, TWP><<<grid, 256, smem, stream>>>(a);
@@ -603,11 +603,8 @@ static int launch_convT(const ConvTArgs& g0, cudaStream_t stream) {
   if (co_chunk > g.Co) co_chunk = g.Co;
   g.co_chunk = co_chunk;
   const int smem = co_chunk * taps * ACC * (int)sizeof(float);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(conv_transpose_rows_kernel<ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr_done = true;
-  }
+  static SmemOptIn opt_in;
+  if (int rc = ensure_dynamic_smem(conv_transpose_rows_kernel<ACC>, 96 * 1024, opt_in, "conv_transpose_rows_kernel")) return rc;
   BF_REQUIRE(smem <= 96 * 1024, BF_E_UNSUPPORTED, "conv backward: kernel window of %d taps is too large", taps);
   const int npix = g.Hi * g.Wi;
   const int threads = npix >= 256 ? 256 : ((npix + 31) / 32) * 32;
@@ -635,8 +632,12 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
     int vec = (L.n_out % 4 == 0) ? 1 : 0;
     for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = 0;
     dim3 grid(M, nchunks);
+    timing_begin(T_RELU_ROWS, stream);
     relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, L.Ho * L.Wo, lam_out, partial, delta, accumulate,
                                                   chunk, S, L.n_out, vec);
+    // rows in (+ out when a ReLU scales them) and the slope / intercept vectors of every domain
+    timing_end(T_RELU_ROWS, stream, (lam_out ? 8.0 : 4.0) * (double)M * L.n_out + (dpos ? 12.0 * (double)(M / S) * L.n_out : 0.0),
+               4.0 * (double)M * L.n_out);
     BF_CHECK_LAUNCH("relu_bwd_rows_kernel");
     if (partial) {
       int rc = launch_sum_partials(accumulate ? delta : nullptr, partial, nchunks, delta, M, stream);
@@ -646,13 +647,18 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
   }
   if (!A_prev) return BF_OK;
   ConvTArgs g{lam, W, A_prev, M, L.Ci, L.Hi, L.Wi, L.Co, L.Ho, L.Wo, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, 0};
-  if (getenv("BF_B200_CONV_GATHER") == nullptr) {
-    const int rc = launch_convT_rowseg(g, stream);
-    if (rc != BF_E_UNSUPPORTED) return rc;
+  static const bool gather_only = getenv("BF_B200_CONV_GATHER") != nullptr;  // A/B switch, read once per process
+  const double conv_bytes = 4.0 * (double)M * (L.n_out + L.n_in) + 4.0 * (double)L.Co * L.Ci * L.kh * L.kw;
+  const double conv_flops = 2.0 * (double)M * L.n_out * L.Ci * L.kh * L.kw;
+  timing_begin(T_CONV_T, stream);
+  int rc = gather_only ? BF_E_UNSUPPORTED : launch_convT_rowseg(g, stream);
+  if (rc == BF_E_UNSUPPORTED) {
+    if (L.Ci <= 4) rc = launch_convT<4>(g, stream);
+    else if (L.Ci <= 16) rc = launch_convT<16>(g, stream);
+    else rc = launch_convT<32>(g, stream);
   }
-  if (L.Ci <= 4) return launch_convT<4>(g, stream);
-  if (L.Ci <= 16) return launch_convT<16>(g, stream);
-  return launch_convT<32>(g, stream);
+  timing_end(T_CONV_T, stream, conv_bytes, conv_flops);
+  return rc;
 }
 
 // ---------------------------------------------------------------------------
@@ -857,6 +863,7 @@ int launch_onehot_conv_window(const float* W, const float* bias, float* out, flo
 int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                            const float* bias, float* Lam, float* delta, const WindowGeom& w, int M, cudaStream_t stream) {
   const int n_win = w.C * w.WH * w.WW;
+  timing_begin(T_RELU_WINDOW, stream);
   if (n_win <= 512)
     relu_bwd_window_kernel<32><<<ceil_div(M, 8), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
   else if (n_win <= 1536)
@@ -865,6 +872,8 @@ int launch_relu_bwd_window(const float* A, const float* dpos, const float* dneg,
     relu_bwd_window_kernel<128><<<ceil_div(M, 2), 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
   else
     relu_bwd_window_kernel<256><<<M, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, Lam, delta, w);
+  // window rows in and out; the slopes and intercepts are gathered per element (three values of the row's domain)
+  timing_end(T_RELU_WINDOW, stream, 8.0 * (double)M * n_win + 12.0 * (double)M * n_win, 4.0 * (double)M * n_win);
   BF_CHECK_LAUNCH("relu_bwd_window_kernel");
   return BF_OK;
 }
@@ -957,6 +966,9 @@ extern "C" int bf_crown_relu_conv2d_bwd(const float* A, int side, const float* a
   bf_layer_desc L{};
   L.op = BF_OP_CONV2D; L.Ci = Ci; L.Hi = Hi; L.Wi = Wi; L.Co = Co; L.Ho = Ho; L.Wo = Wo; L.kh = kh; L.kw = kw;
   L.sh = sh; L.sw = sw; L.ph = ph; L.pw = pw; L.n_in = Ci * Hi * Wi; L.n_out = Co * Ho * Wo;
+  // without slopes the scratch is optional; one that is too small for the chunked intercept sums is not used at all
+  // (a block then streams a whole coefficient row)
+  if (!relu && scratch_bytes < bf_crown_relu_conv2d_bwd_scratch_bytes(B, S, Co, Ho, Wo)) scratch = nullptr;
   return bf::launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, W, bias, A_prev, delta, accumulate, B * S, S, L, scratch,
                                      bf::as_stream(stream));
 }

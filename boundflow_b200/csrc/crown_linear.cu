@@ -108,9 +108,9 @@ int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg
   if (!dpos && !add && !partial && A_prev && K <= THIN_KMAX && N % 4 == 0 &&
       ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(A_prev)) & 15u) == 0) {
     dim3 grid(ceil_div(M, THIN_ROWS), ceil_div(N / 4, 128));
-    timing_begin(0, stream);
+    timing_begin(T_THIN, stream);
     crown_bwd_thin_kernel<<<grid, 128, 0, stream>>>(A, W, kbias, A_prev, delta, accumulate, M, K, N);
-    timing_end(0, stream);
+    timing_end(T_THIN, stream, 4.0 * (double)M * N + 4.0 * (double)M * K + 4.0 * (double)K * N, 2.0 * (double)M * K * N);
     BF_CHECK_LAUNCH("crown_bwd_thin_kernel");
     return BF_OK;
   }
@@ -126,9 +126,9 @@ int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg
   g.delta = delta; g.accumulate = accumulate;
   BwdEpilogue e{A_prev, mid, rad, partial, side};
   dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
-  timing_begin(0, stream);
+  timing_begin(T_BWD, stream);
   crown_bwd_linear_kernel<PRO_RELU><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
-  timing_end(0, stream);
+  timing_end(T_BWD, stream, 4.0 * (double)M * K + (A_prev ? 4.0 * (double)M * N : 0.0), 2.0 * (double)M * K * N);
   BF_CHECK_LAUNCH("crown_bwd_linear_kernel");
   return BF_OK;
 }
@@ -256,7 +256,7 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
                                 float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream) {
-  static bool attr_set[2] = {false, false};
+  static SmemOptIn opt_in[2];
   GemmArgs g{};
   g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
   const void* kptrs[] = {Hprev, W, mid, rad};
@@ -268,21 +268,15 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
   g.mid = mid; g.rad = rad;
   AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum};
   dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
-  timing_begin(1, stream);
+  timing_begin(T_ADJ, stream);
   if (first_layer) {
-    if (!attr_set[0]) {
-      cudaFuncSetAttribute(crown_adjoint_linear_kernel<PRO_H0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADJ_SMEM_BYTES);
-      attr_set[0] = true;
-    }
+    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_H0>, ADJ_SMEM_BYTES, opt_in[0], "crown_adjoint_linear_kernel")) return rc;
     crown_adjoint_linear_kernel<PRO_H0><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
   } else {
-    if (!attr_set[1]) {
-      cudaFuncSetAttribute(crown_adjoint_linear_kernel<PRO_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, ADJ_SMEM_BYTES);
-      attr_set[1] = true;
-    }
+    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_PLAIN>, ADJ_SMEM_BYTES, opt_in[1], "crown_adjoint_linear_kernel")) return rc;
     crown_adjoint_linear_kernel<PRO_PLAIN><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
   }
-  timing_end(1, stream);
+  timing_end(T_ADJ, stream, 4.0 * (double)M * K + 8.0 * (double)M * N, 2.0 * (double)M * K * N);
   BF_CHECK_LAUNCH("crown_adjoint_linear_kernel");
   return BF_OK;
 }

@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   const int b_bytes = 2 * p.BN * 128;                   // hi + lo image of one k-block of one sub-tile
   const uint32_t tmem_cols = (ncols <= 256) ? 256u : 512u;
   volatile int* abort_flag = &ctl->abort_flag;
+  int copies_issued = 0;  // bulk copies this thread has issued (meaningful in the copy thread only)
 
   if (tid == 0) {
     for (int s = 0; s < A_STAGES; ++s) {
@@ -470,6 +471,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
           bulk_copy_g2s(smem_u32(b_tiles + (size_t)s * b_bytes), src, (uint32_t)b_bytes, bar);
         }
       }
+      copies_issued = it;
     }
   } else {
     // ------------------------------------------------------------------ MMA issue
@@ -509,14 +511,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
   __syncthreads();
   if (ctl->abort_flag) {
     if (tid == 0 && p.status) atomicExch(p.status, 1);
-    // give bulk copies that were already issued time to land before the CTA's shared memory is released
-    if (tid == 0) {
-      for (int s = 0; s < p.b_stages; ++s) {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&ctl->b_full[s]), 0) && !mbar_try_wait(smem_u32(&ctl->b_full[s]), 1) && clock64() - t0 < 200000000LL) {
-        }
-      }
-    }
+    // bulk copies that were already issued must land before the CTA's shared memory is released
+    if (warp == COPY_WARP && lane == 0) drain_bulk_copies(ctl->b_full, p.b_stages, copies_issued);
     __syncthreads();
   }
   if (warp == MMA_WARP) {
@@ -623,15 +619,8 @@ static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char*
   const int smem = tc_smem_bytes(p.BN, &b_stages);
   p.b_stages = b_stages;
   p.ntiles = ntiles;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(tc::crown_tc_kernel<MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) {
-      set_error("%s: cannot raise the dynamic shared memory limit: %s", name, cudaGetErrorString(e));
-      return BF_E_CUDA;
-    }
-    attr_done = true;
-  }
+  static SmemOptIn opt_in;
+  if (int rc = ensure_dynamic_smem(tc::crown_tc_kernel<MODE, PRO>, 227 * 1024, opt_in, name)) return rc;
   dim3 grid(ceil_div(p.M, tc::BM), (ntiles + 1) / 2);
   tc::crown_tc_kernel<MODE, PRO><<<grid, tc::THREADS, smem, stream>>>(p);
   BF_CHECK_LAUNCH(name);
@@ -657,9 +646,9 @@ int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* d
   p.out = A_prev; p.mid_n = mid; p.rad_n = rad; p.partial = partial;
   p.conc_sign = (side == BF_SIDE_LOWER) ? -1.f : 1.f;
   p.status = status;
-  timing_begin(0, stream);
+  timing_begin(T_BWD, stream);
   int rc = tc_launch<tc::MODE_BWD, tc::PRO_RELU>(p, nt, stream, "crown_tc_kernel<bwd>");
-  timing_end(0, stream);
+  timing_end(T_BWD, stream, 4.0 * (double)M * K + (A_prev ? 4.0 * (double)M * N : 0.0), 2.0 * (double)M * K * N);
   return rc;
 }
 
@@ -682,10 +671,10 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
   p.nbias = nbias; p.Ahat = Ahat; p.e_dpos = dpos; p.e_dneg = dneg; p.e_epos = epos; p.e_eneg = eneg;
   p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad; p.gsum = gsum;
   p.status = status;
-  timing_begin(1, stream);
+  timing_begin(T_ADJ, stream);
   int rc = first_layer ? tc_launch<tc::MODE_ADJ, tc::PRO_H0>(p, nt, stream, "crown_tc_kernel<adjoint,h0>")
                        : tc_launch<tc::MODE_ADJ, tc::PRO_PLAIN>(p, nt, stream, "crown_tc_kernel<adjoint>");
-  timing_end(1, stream);
+  timing_end(T_ADJ, stream, 4.0 * (double)M * K + 8.0 * (double)M * N, 2.0 * (double)M * K * N);
   return rc;
 }
 

@@ -262,6 +262,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
   const int nbase = ft0 * FT;                          // first feature
   const uint32_t tmem_cols = (nf == 1) ? 256u : 512u;
   volatile int* abort_flag = &ctl->abort_flag;
+  int copies_issued = 0;  // bulk copies this thread has issued (meaningful in the copy thread only)
 
   if (tid == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -445,6 +446,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
           bulk_copy_g2s(smem_u32(s_tiles + (size_t)s * 2 * S_TILE), src, (uint32_t)(2 * S_TILE), bar);
         }
       }
+      copies_issued = it;
     }
   } else {
     // ------------------------------------------------------------------ MMA issue
@@ -485,14 +487,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
   __syncthreads();
   if (ctl->abort_flag) {
     if (tid == 0 && p.status) atomicExch(p.status, 1);
-    // give bulk copies that were already issued time to land before the CTA's shared memory is released
-    if (tid == 0) {
-      for (int s = 0; s < S_STAGES; ++s) {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&ctl->s_full[s]), 0) && !mbar_try_wait(smem_u32(&ctl->s_full[s]), 1) && clock64() - t0 < 200000000LL) {
-        }
-      }
-    }
+    // bulk copies that were already issued must land before the CTA's shared memory is released
+    if (warp == COPY_WARP && lane == 0) drain_bulk_copies(ctl->s_full, S_STAGES, copies_issued);
     __syncthreads();
   }
   if (warp == MMA_WARP) {
@@ -517,15 +513,8 @@ static int sm_count() {
 
 template <int PRO>
 static int tca_launch(tca::Params& p, cudaStream_t stream, const char* name) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(tca::crown_tc_adjoint_kernel<PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, tca::SMEM_BYTES);
-    if (e != cudaSuccess) {
-      set_error("%s: cannot raise the dynamic shared memory limit: %s", name, cudaGetErrorString(e));
-      return BF_E_CUDA;
-    }
-    attr_done = true;
-  }
+  static SmemOptIn opt_in;
+  if (int rc = ensure_dynamic_smem(tca::crown_tc_adjoint_kernel<PRO>, tca::SMEM_BYTES, opt_in, name)) return rc;
   dim3 grid((p.nft + 1) / 2, ceil_div(p.M, tca::RB));
   tca::crown_tc_adjoint_kernel<PRO><<<grid, tca::THREADS, tca::SMEM_BYTES, stream>>>(p);
   BF_CHECK_LAUNCH(name);
@@ -551,10 +540,10 @@ int launch_crown_adjoint_linear_tc_fm(const float* Hprev, int first_layer, const
   p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad; p.gsum = gsum;
   p.status = status;
   p.wave = sm_count();
-  timing_begin(1, stream);
+  timing_begin(T_ADJ, stream);
   int rc = first_layer ? tca_launch<tca::PRO_H0>(p, stream, "crown_tc_adjoint_kernel<h0>")
                        : tca_launch<tca::PRO_PLAIN>(p, stream, "crown_tc_adjoint_kernel");
-  timing_end(1, stream);
+  timing_end(T_ADJ, stream, 4.0 * (double)M * K + 8.0 * (double)M * N, 2.0 * (double)M * K * N);
   return rc;
 }
 

@@ -88,7 +88,10 @@ int launch_concretize(const float* A, const float* mid, const float* rad, const 
   for (const void* p : ptrs) if (reinterpret_cast<uintptr_t>(p) & 15u) vec = 0;
   int blocks = ceil_div(M, 8);
   if (blocks > 148 * 8) blocks = 148 * 8;
+  timing_begin(T_CONCRETIZE, stream);
   concretize_kernel<<<blocks, 256, 0, stream>>>(A, mid, rad, bias_in, out, side == BF_SIDE_LOWER ? -1.f : 1.f, M, S, n0, vec);
+  // every coefficient row once, the box of every domain once, one result per row
+  timing_end(T_CONCRETIZE, stream, 4.0 * (double)M * n0 + 8.0 * (double)B * n0 + 4.0 * M, 4.0 * (double)M * n0);
   BF_CHECK_LAUNCH("concretize_kernel");
   return BF_OK;
 }
@@ -195,6 +198,7 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
   bool vec = (n % 4 == 0);
   const void* ptrs[] = {alpha, m, v, grad, best_alpha, pre_l, pre_u, slope_l};
   for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = false;
+  timing_begin(T_ADAM, stream);
   if (vec) {
     dim3 grid(B, ceil_div(n / 4, 128));
     adam_step_kernel<4><<<grid, 128, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l, sc, do_update, n);
@@ -202,6 +206,10 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
     dim3 grid(B, ceil_div(n, 128));
     adam_step_kernel<1><<<grid, 128, 0, stream>>>(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l, sc, do_update, n);
   }
+  // the optimiser's own traffic: read alpha, m, v, grad and write alpha, m, v (28 B per element); the kernel also
+  // reads the pre-activation bounds, clears the gradient and writes the next lower slope and the best-alpha snapshot
+  // (up to 48 B per element in all), which replaces separate relaxation / snapshot passes
+  timing_end(T_ADAM, stream, (do_update ? 28.0 : 8.0) * (double)B * n, do_update ? 10.0 * (double)B * n : 0.0);
   BF_CHECK_LAUNCH("adam_step_kernel");
   return BF_OK;
 }
@@ -414,20 +422,47 @@ __global__ void alpha_adaptive_init_kernel(const float* __restrict__ l, const fl
 }
 
 // ---- verdicts ---------------------------------------------------------------
-__global__ void verdict_kernel(const float* __restrict__ lower, float threshold, float tol, int8_t* __restrict__ verdict,
-                               float* __restrict__ min_lower, int B, int S) {
+// A NaN on any spec row poisons the minimum (fminf alone would drop it), so such a domain is never proven;
+// a domain whose split assignment is empty (infeasible flag) carries meaningless bounds and is not proven either.
+__global__ void verdict_kernel(const float* __restrict__ lower, float threshold, float tol, const int* __restrict__ infeasible,
+                               int8_t* __restrict__ verdict, float* __restrict__ min_lower, int B, int S) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   float mn = lower[(size_t)b * S];
-  for (int k = 1; k < S; ++k) mn = fminf(mn, lower[(size_t)b * S + k]);
-  verdict[b] = (mn >= threshold - tol) ? 1 : 0;
+  for (int k = 1; k < S; ++k) {
+    const float v = lower[(size_t)b * S + k];
+    mn = (v != v || mn != mn) ? nanf("") : fminf(mn, v);
+  }
+  const bool ok = (mn >= threshold - tol) && !(infeasible && infeasible[b] != 0);
+  verdict[b] = ok ? 1 : 0;
   if (min_lower) min_lower[b] = mn;
 }
 
-int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
-                   cudaStream_t stream) {
-  verdict_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(lower, threshold, tol, verdict, min_lower, B, S);
+int launch_verdict(const float* lower, float threshold, float tol, const int* infeasible, int8_t* verdict, float* min_lower,
+                   int B, int S, cudaStream_t stream) {
+  verdict_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(lower, threshold, tol, infeasible, verdict, min_lower, B, S);
   BF_CHECK_LAUNCH("verdict_kernel");
+  return BF_OK;
+}
+
+// Results of a call whose tensor-core kernels gave up on a bounded wait are undefined: when the chain's status word
+// is set, every bound of the call is overwritten with NaN (which no verdict accepts) instead of being handed on.
+__global__ void poison_on_status_kernel(const int* __restrict__ status, float* __restrict__ a, long long na,
+                                        float* __restrict__ b, long long nb) {
+  if (*status == 0) return;
+  const float bad = nanf("");
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < na + nb; i += (long long)gridDim.x * blockDim.x) {
+    if (i < na) a[i] = bad;
+    else b[i - na] = bad;
+  }
+}
+
+int launch_poison_on_status(const int* status, float* a, long long na, float* b, long long nb, cudaStream_t stream) {
+  if (!status || (!a && !b)) return BF_OK;
+  if (!a) na = 0;
+  if (!b) nb = 0;
+  poison_on_status_kernel<<<ew_grid(na + nb, 256), 256, 0, stream>>>(status, a, na, b, nb);
+  BF_CHECK_LAUNCH("poison_on_status_kernel");
   return BF_OK;
 }
 
@@ -504,9 +539,14 @@ extern "C" int bf_concretize(const float* A, const float* mid, const float* rad,
 
 extern "C" int bf_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
                           bf_stream_t stream) {
+  return bf_verdict_masked(lower, threshold, tol, nullptr, verdict, min_lower, B, S, stream);
+}
+
+extern "C" int bf_verdict_masked(const float* lower, float threshold, float tol, const int* infeasible, int8_t* verdict,
+                                 float* min_lower, int B, int S, bf_stream_t stream) {
   BF_REQUIRE(lower && verdict, BF_E_INVALID, "bf_verdict: null tensor");
   BF_REQUIRE(B > 0 && S > 0, BF_E_INVALID, "bf_verdict: sizes must be positive");
-  return bf::launch_verdict(lower, threshold, tol, verdict, min_lower, B, S, bf::as_stream(stream));
+  return bf::launch_verdict(lower, threshold, tol, infeasible, verdict, min_lower, B, S, bf::as_stream(stream));
 }
 
 // ---- beta parameters (split-constraint multipliers) and branching scores -------------

@@ -165,7 +165,11 @@ int launch_ibp_linear(const float* in_a, const float* in_b, int in_mode, int rel
   const void* nptrs[] = {bias, cons_l, cons_u, out_l, out_u, row_dev};
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   dim3 grid(ceil_div(B, IBM), ceil_div(N, IBN));
+  timing_begin(T_IBP_LINEAR, stream);
   ibp_linear_kernel<<<grid, 256, 0, stream>>>(g);
+  // weights and bias once, the input interval once, both output bounds once (+ the split bytes)
+  timing_end(T_IBP_LINEAR, stream, 4.0 * ((double)K * N + N) + 8.0 * (double)B * (K + N) + (split ? (double)B * N : 0.0),
+             4.0 * (double)B * K * N);
   BF_CHECK_LAUNCH("ibp_linear_kernel");
   return BF_OK;
 }

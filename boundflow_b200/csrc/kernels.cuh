@@ -101,7 +101,8 @@ int launch_shared_beta_add(const float* beta, const int8_t* split, int split_str
 // and the next split term add = -beta * split (split in {-1,0,+1}; entries with split == 0 never move)
 int launch_beta_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride, const int* improve,
                      float* best_beta, float* add, AdamScalars sc, int do_update, int B, int n, cudaStream_t stream);
-int launch_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower, int B, int S,
-                   cudaStream_t stream);
+int launch_verdict(const float* lower, float threshold, float tol, const int* infeasible, int8_t* verdict, float* min_lower,
+                   int B, int S, cudaStream_t stream);
+int launch_poison_on_status(const int* status, float* a, long long na, float* b, long long nb, cudaStream_t stream);
 
 }  // namespace bf

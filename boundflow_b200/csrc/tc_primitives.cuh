@@ -51,6 +51,20 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                "r"(bytes), "r"(bar)
                : "memory");
 }
+// Teardown after an abort: waits (clock-bounded) until the bulk copies this thread issued into a `stages`-deep ring
+// have landed, so that the CTA does not release shared memory that a copy is still writing.  Copy number j used
+// stage j % stages in barrier phase (j / stages) & 1; only the last `stages` copies can still be in flight.  The
+// calling thread armed those phases itself (arrive.expect_tx), so a stage's barrier cannot move past the awaited
+// phase while this runs and try_wait on that phase's parity answers "completed" exactly when the bytes are in.
+__device__ __forceinline__ void drain_bulk_copies(unsigned long long* full_bars, int stages, int issued) {
+  for (int j = (issued > stages ? issued - stages : 0); j < issued; ++j) {
+    const uint32_t bar = smem_u32(&full_bars[j % stages]);
+    const uint32_t parity = (uint32_t)(j / stages) & 1u;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity) && clock64() - t0 < 200000000LL) {
+    }
+  }
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

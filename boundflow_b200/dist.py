@@ -9,10 +9,13 @@ code; this module is new.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+_GATHER_BUFFERS: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
@@ -39,14 +42,23 @@ def gather_domain_results(
     sizes = shard_sizes(n_total, world)
     pad = max(sizes)
     S = int(lower.shape[1])
-    send_l = torch.zeros(pad, S, dtype=lower.dtype, device=lower.device)
-    send_v = torch.zeros(pad, dtype=torch.int8, device=verdict.device)
-    send_l[: lower.shape[0]] = lower
-    send_v[: verdict.shape[0]] = verdict.to(torch.int8)
-    recv_l = torch.empty(world * pad, S, dtype=lower.dtype, device=lower.device)
-    recv_v = torch.empty(world * pad, dtype=torch.int8, device=verdict.device)
-    dist.all_gather_into_tensor(recv_l, send_l, group=group)
-    dist.all_gather_into_tensor(recv_v, send_v, group=group)
-    out_l = torch.cat([recv_l[r * pad : r * pad + sizes[r]] for r in range(world)], dim=0)
-    out_v = torch.cat([recv_v[r * pad : r * pad + sizes[r]] for r in range(world)], dim=0)
-    return out_l, out_v
+    # ONE collective per step: bounds and verdict of a domain travel as one row of S + 1 floats, gathered into a
+    # receive buffer that is kept between calls (keyed by shape, dtype and device).
+    key = (world, pad, S, lower.dtype, str(lower.device))
+    bufs = _GATHER_BUFFERS.get(key)
+    if bufs is None:
+        if len(_GATHER_BUFFERS) > 16:
+            _GATHER_BUFFERS.clear()
+        bufs = (torch.zeros(pad, S + 1, dtype=lower.dtype, device=lower.device),
+                torch.empty(world * pad, S + 1, dtype=lower.dtype, device=lower.device))
+        _GATHER_BUFFERS[key] = bufs
+    send, recv = bufs
+    n_local = int(lower.shape[0])
+    send[:n_local, :S] = lower
+    send[:n_local, S] = verdict.to(lower.dtype)
+    dist.all_gather_into_tensor(recv, send, group=group)
+    if all(s == pad for s in sizes):  # equal shards: the receive buffer already is the global order
+        rows = recv
+    else:
+        rows = torch.cat([recv[r * pad : r * pad + sizes[r]] for r in range(world)], dim=0)
+    return rows[:, :S].clone(), rows[:, S].to(torch.int8)

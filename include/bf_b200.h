@@ -57,13 +57,22 @@ const char* bf_last_error_string(void);
 /* Number of kernels this library has launched since it was loaded. */
 unsigned long long bf_launch_count(void);
 
-/* Measurement aid (no counterpart in the reference): when enabled, every launch of the
- * two contraction kernels is bracketed by a CUDA event pair on its own stream.
- * bf_kernel_timing_read waits for the recorded events and returns the number of launches and
- * their summed device time since the last enable.  slot 0: CROWN backward contraction,
- * slot 1: adjoint (gradient) contraction.  Not thread-safe; meant for benchmarks. */
+/* Measurement aid (no counterpart in the reference): when enabled, every launch of a kernel
+ * that has a timing slot is bracketed by a CUDA event pair on its own stream, and the launcher adds
+ * the algorithmic work of that launch (bytes that must cross HBM once, floating-point operations)
+ * to the slot.  bf_kernel_timing_read[_work] waits for the recorded events and returns the number
+ * of launches, their summed device time and the summed work since the last enable.
+ * Slots (bf_kernel_timing_slots() of them, named by bf_kernel_timing_slot_name):
+ *   0 CROWN backward contraction      1 adjoint (gradient) contraction   2 thin top-layer kernel
+ *   3 interval Linear                 4 interval Conv2d                  5 Adam / projection step
+ *   6 stand-alone concretisation      7 ReLU scaling of windowed rows    8 transposed convolution
+ *   9 ReLU scaling of full coefficient rows
+ * Safe to call from several host threads (one mutex guards the slots); meant for benchmarks. */
 void bf_kernel_timing_enable(int on);
+int bf_kernel_timing_slots(void);
+const char* bf_kernel_timing_slot_name(int slot);
 int bf_kernel_timing_read(int slot, int* launches, float* total_ms);
+int bf_kernel_timing_read_work(int slot, int* launches, float* total_ms, double* bytes, double* flops);
 
 /* ------------------------------------------------------------------------
  * Layer-level kernels
@@ -145,7 +154,9 @@ int bf_crown_relu_linear_bwd(const float* A, int side,
  * A_prev [B,S,Ci*Hi*Wi]; delta [B,S] as above.  groups = 1, dilation = 1; any kernel size,
  * stride and padding with 0 <= output_padding < stride.  `scratch` (device,
  * bf_crown_relu_conv2d_bwd_scratch_bytes) holds the ReLU-scaled coefficients between the
- * two passes and, for wide layers, partial sums of delta; it may be NULL when no ReLU is applied. */
+ * two passes and, for wide layers, partial sums of delta.  Without slopes (no ReLU) it is
+ * optional: NULL, or a buffer smaller than bf_crown_relu_conv2d_bwd_scratch_bytes, is simply not
+ * used; with slopes a buffer of at least that size is required (BF_E_WORKSPACE otherwise). */
 size_t bf_crown_relu_conv2d_bwd_scratch_bytes(int B, int S, int Co, int Ho, int Wo);
 int bf_crown_relu_conv2d_bwd(const float* A, int side,
                              const float* alpha_u, const float* alpha_l,
@@ -203,15 +214,6 @@ int bf_crown_relu_conv2d_bwd_noalloc(const float* A, int side,
 int bf_concretize(const float* A, const float* mid, const float* rad, const float* bias_in,
                   float* out, int side, int B, int S, int n0, bf_stream_t stream);
 
-/* Lp-ball input sets (p = 1, 2, inf), the non-box branch of the reference's perturbations.
- *   bf_row_dual_norms: out[r] = scale * ||W[r,:]||_q (q dual to p) -- the row norms of
- *            LpBallPerturbation.concretize_matmul, boundflow/runtime/perturbation.py:102-134.
- *   bf_ibp_linear_lp: first Linear layer on a ball: centre @ W^T + b -/+ row_dev, then the
- *            same constraint / split clamps as bf_ibp_linear (row_dev [n_out] from bf_row_dual_norms
- *            with scale = eps).
- *   bf_concretize_lp: A.centre -/+ eps * ||A_row||_q + bias_in, replaces
- *            LpBallPerturbation.concretize_affine perturbation.py:175-222 (row norms
- *            boundflow/runtime/linear_operator.py:365-372). */
 /* IBP linear layer with one weight matrix per batch element -- the output spec merged into the
  * last layer (W' = C @ W, b' = C @ b; _fuse_linear_spec_into_last_linear,
  * boundflow/planner/interval_v1.py:85-163), evaluated as the batched-W branch of
@@ -221,6 +223,15 @@ int bf_concretize(const float* A, const float* mid, const float* rad, const floa
 int bf_ibp_linear_batched(const float* in_l, const float* in_u, int relu_in, const float* W, const float* bias,
                           float* out_l, float* out_u, int B, int S, int n_in, bf_stream_t stream);
 
+/* Lp-ball input sets (p = 1, 2, inf), the non-box branch of the reference's perturbations.
+ *   bf_row_dual_norms: out[r] = scale * ||W[r,:]||_q (q dual to p) -- the row norms of
+ *            LpBallPerturbation.concretize_matmul, boundflow/runtime/perturbation.py:102-134.
+ *   bf_ibp_linear_lp: first Linear layer on a ball: centre @ W^T + b -/+ row_dev, then the
+ *            same constraint / split clamps as bf_ibp_linear (row_dev [n_out] from bf_row_dual_norms
+ *            with scale = eps).
+ *   bf_concretize_lp: A.centre -/+ eps * ||A_row||_q + bias_in, replaces
+ *            LpBallPerturbation.concretize_affine perturbation.py:175-222 (row norms
+ *            boundflow/runtime/linear_operator.py:365-372). */
 int bf_row_dual_norms(const float* W, int n_rows, int n_cols, int p, float scale, float* out, bf_stream_t stream);
 int bf_ibp_linear_lp(const float* center, const float* row_dev, const float* W, const float* bias,
                      const int8_t* split, int split_stride, const float* cons_l, const float* cons_u,
@@ -246,8 +257,13 @@ int bf_first_layer_certificate(const int8_t* split, int split_stride, const floa
                                bf_stream_t stream);
 
 /* Verdict per domain: proven iff min over spec rows of the lower bound >= threshold - tol.
- *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895.
- * lower [B,S]; verdict int8 [B] (1 proven, 0 not); min_lower [B] or NULL. */
+ *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895
+ *            (bounds.lower.min() then >=: a NaN bound never proves a node, and neither does it here).
+ * lower [B,S]; verdict int8 [B] (1 proven, 0 not); min_lower [B] or NULL (NaN when any row is NaN).
+ * bf_verdict_masked additionally takes the per-domain infeasible flags of the IBP sweep
+ * (int32 [B] or NULL): a flagged domain's bounds are meaningless, its verdict is 0. */
+int bf_verdict_masked(const float* lower, float threshold, float tol, const int* infeasible, int8_t* verdict,
+                      float* min_lower, int B, int S, bf_stream_t stream);
 int bf_verdict(const float* lower, float threshold, float tol, int8_t* verdict, float* min_lower,
                int B, int S, bf_stream_t stream);
 
