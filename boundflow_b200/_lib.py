@@ -38,6 +38,7 @@ SIGNATURES = {
     "bf_version": (_i, []),
     "bf_last_error_string": (C.c_char_p, []),
     "bf_launch_count": (C.c_ulonglong, []),
+    "bf_tc_launch_count": (C.c_ulonglong, []),
     "bf_kernel_timing_enable": (None, [_i]),
     "bf_kernel_timing_read": (_i, [_i, C.POINTER(_i), C.POINTER(_f)]),
     "bf_kernel_timing_slots": (_i, []),
@@ -48,6 +49,10 @@ SIGNATURES = {
     "bf_relu_relax": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _i, _p]),
     "bf_alpha_adaptive_init": (_i, [_p, _p, _p, _i, _i, _p]),
     "bf_crown_relu_linear_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "bf_linear_pack_bytes": (_sz, [_i, _i]),
+    "bf_linear_pack": (_i, [_p, _i, _i, _p, _sz, _p]),
+    "bf_linear_pack_status": (_i, [_p, C.POINTER(_i)]),
+    "bf_crown_relu_linear_bwd_packed": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "bf_crown_relu_conv2d_bwd_scratch_bytes": (_sz, [_i] * 5),
     "bf_crown_relu_conv2d_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _sz] + [_i] * 14 + [_p]),
     "bf_crown_relu_conv2d_bwd_noalloc_max_bytes": (_sz, []),
@@ -148,3 +153,46 @@ def int_array(vals: Optional[Sequence[int]]):
 
 def launch_count() -> int:
     return int(load().bf_launch_count())
+
+
+def tc_launch_count() -> int:
+    """Launches of the tcgen05 contraction kernels since the library was loaded."""
+    return int(load().bf_tc_launch_count())
+
+
+class LinearPackCache:
+    """Packed tensor-core images of Linear weights for the layer-level entry point
+    `bf_crown_relu_linear_bwd_packed`, built once per weight tensor.
+
+    An entry is keyed by the weight's storage address, shape, device and in-place version counter and
+    keeps the weight tensor itself alive, so an address can never be reused by another tensor while its
+    pack is cached.  Least recently used entries are dropped beyond `capacity`."""
+
+    MIN_ROWS, MIN_WIDTH = 256, 32  # below these sizes the library uses the FFMA tiles and needs no pack
+
+    def __init__(self, capacity: int = 32):
+        self.capacity = int(capacity)
+        self._entries: "dict[tuple, tuple]" = {}
+
+    def get(self, W, rows: int, stream_ptr: int):
+        """Device pack for weight `W` ([n_cur, n_prev], fp32, contiguous, CUDA), or None when the problem is too small."""
+        n_cur, n_prev = int(W.shape[0]), int(W.shape[1])
+        if rows < self.MIN_ROWS or n_cur < self.MIN_WIDTH or n_prev < self.MIN_WIDTH:
+            return None
+        key = (W.data_ptr(), n_cur, n_prev, W.device.index, W._version)
+        hit = self._entries.pop(key, None)
+        if hit is None:
+            import torch
+
+            lib = load()
+            nbytes = int(lib.bf_linear_pack_bytes(n_cur, n_prev))
+            pack = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+            check(lib.bf_linear_pack(W.data_ptr(), n_cur, n_prev, pack.data_ptr(), nbytes, stream_ptr))
+            hit = (W, pack)
+            while len(self._entries) >= self.capacity:
+                self._entries.pop(next(iter(self._entries)))
+        self._entries[key] = hit  # most recently used last
+        return hit[1]
+
+
+LINEAR_PACKS = LinearPackCache()

@@ -16,6 +16,7 @@ namespace bf {
 
 static thread_local char g_err[512] = "ok";
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<unsigned long long> g_tc_launches{0};
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -119,6 +120,7 @@ extern "C" int bf_kernel_timing_read(int slot, int* launches, float* total_ms) {
 extern "C" int bf_version(void) { return 100; }
 extern "C" const char* bf_last_error_string(void) { return bf::g_err; }
 extern "C" unsigned long long bf_launch_count(void) { return bf::g_launches.load(); }
+extern "C" unsigned long long bf_tc_launch_count(void) { return bf::g_tc_launches.load(); }
 
 extern "C" int bf_chain_create(const bf_layer_desc* layers, int n_layers, bf_chain** out) {
   BF_REQUIRE(layers && out && n_layers > 0, BF_E_INVALID, "bf_chain_create: null/empty layer list");

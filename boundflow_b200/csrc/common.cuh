@@ -13,6 +13,7 @@ namespace bf {
 // ---- error reporting -------------------------------------------------------
 void set_error(const char* fmt, ...);
 extern std::atomic<unsigned long long> g_launches;
+extern std::atomic<unsigned long long> g_tc_launches;  // launches of the tcgen05 contraction kernels among them
 
 inline void count_launch(int n = 1) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 

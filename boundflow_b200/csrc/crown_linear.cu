@@ -305,3 +305,67 @@ extern "C" int bf_crown_relu_linear_bwd(const float* A, int side, const float* a
   return bf::launch_crown_bwd_linear(A, dpos, dneg, epos, eneg, relu ? add : nullptr, W, bias, A_prev, delta, accumulate,
                                      nullptr, nullptr, nullptr, side, B * S, S, n_cur, n_prev, bf::as_stream(stream));
 }
+
+// ---------------------------------------------------------------------------
+// Layer-level tensor-core path: the caller packs a layer's weight once (hi/lo TF32 images in the shared-memory
+// layout of the tcgen05 kernel, preceded by a status word) and passes the pack with every call.
+// ---------------------------------------------------------------------------
+static const size_t kPackHeader = 256;  // status word + padding in front of the packed images
+
+extern "C" size_t bf_linear_pack_bytes(int n_cur, int n_prev) {
+  if (n_cur <= 0 || n_prev <= 0) return 0;
+  return kPackHeader + ((bf::tc_packed_bytes(n_prev, n_cur) + 255) & ~(size_t)255);
+}
+
+extern "C" int bf_linear_pack(const float* W, int n_cur, int n_prev, void* pack, size_t pack_bytes, bf_stream_t stream_) {
+  BF_REQUIRE(W && pack && n_cur > 0 && n_prev > 0, BF_E_INVALID, "bf_linear_pack: bad argument");
+  BF_REQUIRE((reinterpret_cast<uintptr_t>(pack) & 255u) == 0, BF_E_INVALID, "bf_linear_pack: the pack buffer must be 256-byte aligned");
+  BF_REQUIRE(pack_bytes >= bf_linear_pack_bytes(n_cur, n_prev), BF_E_WORKSPACE, "bf_linear_pack: %zu bytes needed",
+             bf_linear_pack_bytes(n_cur, n_prev));
+  cudaStream_t stream = bf::as_stream(stream_);
+  if (cudaMemsetAsync(pack, 0, kPackHeader, stream) != cudaSuccess) {
+    bf::set_error("bf_linear_pack: cudaMemsetAsync failed");
+    return BF_E_CUDA;
+  }
+  // backward: A_prev = Lambda[M, n_cur] * W[n_cur, n_prev]  ->  B[n][k] = W[k][n] (transposed read)
+  return bf::tc_pack_weights(W, n_cur, n_prev, 1, static_cast<unsigned char*>(pack) + kPackHeader, stream);
+}
+
+extern "C" int bf_linear_pack_status(const void* pack, int* status_out) {
+  BF_REQUIRE(pack && status_out, BF_E_INVALID, "bf_linear_pack_status: null argument");
+  if (cudaMemcpy(status_out, pack, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    bf::set_error("bf_linear_pack_status: cudaMemcpy failed");
+    return BF_E_CUDA;
+  }
+  return BF_OK;
+}
+
+extern "C" int bf_crown_relu_linear_bwd_packed(const float* A, int side, const float* alpha_u, const float* alpha_l,
+                                               const float* beta_u, const float* beta_l, const float* add, const float* W,
+                                               const float* bias, const void* pack, float* A_prev, float* delta, int accumulate,
+                                               int B, int S, int n_cur, int n_prev, bf_stream_t stream_) {
+  const long long M = (long long)B * S;
+  // small problems, delta-only calls and calls without a pack take the FP32 FFMA tiles
+  if (!pack || !A_prev || M < 256 || n_cur < 32 || n_prev < 32)
+    return bf_crown_relu_linear_bwd(A, side, alpha_u, alpha_l, beta_u, beta_l, add, W, bias, A_prev, delta, accumulate, B, S, n_cur,
+                                    n_prev, stream_);
+  BF_REQUIRE(A && W, BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: A and W must be non-null");
+  BF_REQUIRE(B > 0 && S > 0 && M < 2147483647LL, BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: bad sizes");
+  BF_REQUIRE(side == BF_SIDE_LOWER || side == BF_SIDE_UPPER, BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: bad side");
+  BF_REQUIRE((reinterpret_cast<uintptr_t>(pack) & 255u) == 0, BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: misaligned pack");
+  const bool relu = alpha_u || alpha_l || beta_u || beta_l;
+  BF_REQUIRE(!relu || (alpha_u && alpha_l), BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: alpha_u and alpha_l must both be given");
+  const float *dpos = nullptr, *dneg = nullptr, *epos = nullptr, *eneg = nullptr;
+  if (relu) {
+    if (side == BF_SIDE_LOWER) { dpos = alpha_l; dneg = alpha_u; epos = beta_l; eneg = beta_u; }
+    else { dpos = alpha_u; dneg = alpha_l; epos = beta_u; eneg = beta_l; }
+  }
+  cudaStream_t stream = bf::as_stream(stream_);
+  int* status = reinterpret_cast<int*>(const_cast<void*>(pack));
+  const unsigned char* images = static_cast<const unsigned char*>(pack) + kPackHeader;
+  int rc = bf::launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta, accumulate,
+                                          nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status, stream);
+  if (rc != BF_OK) return rc;
+  // a wait that expired inside the kernel invalidates the result: hand on NaN, never stale memory
+  return bf::launch_poison_on_status(status, A_prev, M * n_prev, delta, delta ? M : 0, stream);
+}

@@ -624,6 +624,7 @@ static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char*
   dim3 grid(ceil_div(p.M, tc::BM), (ntiles + 1) / 2);
   tc::crown_tc_kernel<MODE, PRO><<<grid, tc::THREADS, smem, stream>>>(p);
   BF_CHECK_LAUNCH(name);
+  g_tc_launches.fetch_add(1, std::memory_order_relaxed);
   return BF_OK;
 }
 

@@ -518,6 +518,7 @@ static int tca_launch(tca::Params& p, cudaStream_t stream, const char* name) {
   dim3 grid((p.nft + 1) / 2, ceil_div(p.M, tca::RB));
   tca::crown_tc_adjoint_kernel<PRO><<<grid, tca::THREADS, tca::SMEM_BYTES, stream>>>(p);
   BF_CHECK_LAUNCH(name);
+  g_tc_launches.fetch_add(1, std::memory_order_relaxed);
   return BF_OK;
 }
 

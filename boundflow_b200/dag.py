@@ -220,8 +220,9 @@ def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor
                 b = params[op.inputs[2]] if len(op.inputs) == 3 else None
                 n_cur, n_prev = int(W.shape[0]), int(W.shape[1])
                 Ap = torch.empty(B, S, n_prev, device=device)
-                _lib.check(lib.bf_crown_relu_linear_bwd(_lib.ptr(st.A), side, None, None, None, None, None, _lib.ptr(W), _lib.ptr(b),
-                                                        _lib.ptr(Ap), _lib.ptr(st.d), 1, B, S, n_cur, n_prev, s))
+                pack = _lib.LINEAR_PACKS.get(W, B * S, s)  # tensor-core path for large coefficient blocks
+                _lib.check(lib.bf_crown_relu_linear_bwd_packed(_lib.ptr(st.A), side, None, None, None, None, None, _lib.ptr(W), _lib.ptr(b),
+                                                               _lib.ptr(pack), _lib.ptr(Ap), _lib.ptr(st.d), 1, B, S, n_cur, n_prev, s))
                 push(op.inputs[0], Ap, st.d)
             elif t == "conv2d":
                 W = params[op.inputs[1]]

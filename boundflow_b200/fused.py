@@ -103,9 +103,11 @@ class CudaFusedCrownExecutor:
                 delta = torch.empty(D, S, dtype=torch.float32, device=device)
                 if request.kind == "linear":
                     n_cur = int(request.weight.shape[0])
-                    _lib.check(self.lib.bf_crown_relu_linear_bwd(
+                    # large regions run the tcgen05 kernel on a packed copy of the weight (cached per weight tensor)
+                    pack = _lib.LINEAR_PACKS.get(request.weight, D * S, sp)
+                    _lib.check(self.lib.bf_crown_relu_linear_bwd_packed(
                         _lib.ptr(A), side, _lib.ptr(request.alpha_u), _lib.ptr(request.alpha_l), _lib.ptr(request.beta_u),
-                        _lib.ptr(request.beta_l), None, _lib.ptr(request.weight), _lib.ptr(request.bias),
+                        _lib.ptr(request.beta_l), None, _lib.ptr(request.weight), _lib.ptr(request.bias), _lib.ptr(pack),
                         _lib.ptr(A_prev), _lib.ptr(delta), 0, D, S, n_cur, n_prev, sp))
                 else:
                     Co, Ho, Wo = (int(d) for d in request.output_shape)

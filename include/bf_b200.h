@@ -54,8 +54,10 @@ typedef void* bf_stream_t; /* a cudaStream_t */
 /* Library identity and diagnostics. */
 int bf_version(void);
 const char* bf_last_error_string(void);
-/* Number of kernels this library has launched since it was loaded. */
+/* Number of kernels this library has launched since it was loaded, and how many of those were the
+ * tcgen05 (tensor-core) contraction kernels. */
 unsigned long long bf_launch_count(void);
+unsigned long long bf_tc_launch_count(void);
 
 /* Measurement aid (no counterpart in the reference): when enabled, every launch of a kernel
  * that has a timing slot is bracketed by a CUDA event pair on its own stream, and the launcher adds
@@ -144,6 +146,28 @@ int bf_crown_relu_linear_bwd(const float* A, int side,
                              const float* W, const float* bias,
                              float* A_prev, float* delta, int accumulate,
                              int B, int S, int n_cur, int n_prev, bf_stream_t stream);
+
+/* Tensor-core variant of bf_crown_relu_linear_bwd for callers that keep a layer's weight between calls
+ * (the fused-region executor, graphs that are not chains).  No counterpart in the reference, whose
+ * contraction is a cuBLAS call made by torch.einsum (boundflow/runtime/linear_operator.py:585-586).
+ *   bf_linear_pack: splits W [n_cur,n_prev] into hi/lo TF32 parts and writes the shared-memory images of the
+ *            tcgen05 kernel, preceded by a status word, into `pack` (device, 256-byte aligned,
+ *            bf_linear_pack_bytes(n_cur, n_prev) bytes).  Repack when W changes.
+ *   bf_crown_relu_linear_bwd_packed: same arguments and results as bf_crown_relu_linear_bwd plus the pack;
+ *            runs the tcgen05 3xTF32 kernel when B*S >= 256 and both widths are >= 32, the FP32 FFMA
+ *            tiles otherwise (or when pack is NULL).  If a bounded wait inside the kernel ever expires the
+ *            outputs of that call are overwritten with NaN and the pack's status word stays non-zero
+ *            (bf_linear_pack_status, synchronous). */
+size_t bf_linear_pack_bytes(int n_cur, int n_prev);
+int bf_linear_pack(const float* W, int n_cur, int n_prev, void* pack, size_t pack_bytes, bf_stream_t stream);
+int bf_linear_pack_status(const void* pack, int* status);
+int bf_crown_relu_linear_bwd_packed(const float* A, int side,
+                                    const float* alpha_u, const float* alpha_l,
+                                    const float* beta_u, const float* beta_l,
+                                    const float* add,
+                                    const float* W, const float* bias, const void* pack,
+                                    float* A_prev, float* delta, int accumulate,
+                                    int B, int S, int n_cur, int n_prev, bf_stream_t stream);
 
 /* Fused ReLU backward + Conv2d backward (transposed convolution) for one side.
  *   replaces FusedCrownExecutor.run for kind == "conv2d", fused_crown.py:365-400
