@@ -1,6 +1,6 @@
 """Benchmark of the bound-propagation hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
 
 Workload (config c4): ReLU-split branch-and-bound subdomains of an MLP
 784-512x4-10 (fp32, He init, one input, eps 0.02, 9 margin specs).  One "step"
@@ -10,9 +10,21 @@ analytic gradients, 1 upper-bound evaluation at the best alpha), verdicts and,
 with N > 1, the all-gather of bounds and verdicts.  Metric: BaB domains bounded/s
 (whole job, all ranks).  `value` is measured with inputs resident in HBM, `e2e`
 through the public API with pinned HOST buffers (H2D and D2H inside the timed
-region).  `--impl reference` times the CPU restatement of the reference's own
-PyTorch path (the oracle; the reference is pure Python and is not installed on
-the GPU box) on a bounded sample of the same workload, on all host cores.
+region; the input box and the spec rows, shared by all subdomains of one problem,
+travel once and are repeated on the device).
+
+`--scaling strong` splits ONE 8192-subdomain batch over the N GPUs instead of
+giving every GPU its own batch.
+
+`--impl reference` times the reference's own CPU implementation of the same step
+on the host cores: the reference's functions from `oracle/_ref` (built by
+`oracle/make_ref.py`) when present, else the CPU restatement `oracle/crown_oracle.py`,
+on a bounded sample of the workload per step.
+
+Other modes (profiling aids, one JSON line each): `--secondary-only cN` times one
+CROWN bounds/s configuration, `--kernels` times single kernels on resident data and
+reports their HBM / FP32 rooflines, `--conv-layers a,b --rows R` times the fused ReLU +
+transposed-convolution layer call on the CNN configurations' layer shapes.
 """
 from __future__ import annotations
 
@@ -33,11 +45,14 @@ import torch  # noqa: E402
 DOMAINS_PER_GPU = 8192
 ALPHA_STEPS = 10
 LR = 0.1
+REFERENCE_SAMPLE = 512  # subdomains per step of the CPU arm (the same workload, a bounded sample)
 # DRAM bytes of one backward-contraction launch of a 512x512 layer at 8192 domains (M = 73728 rows):
 # ncu capture at 4096 domains (profiles/crown_tc_kernel_bwd_c4_4096domains.md) scaled x2 by the row count.
 TRAFFIC_BYTES_PER_LAUNCH = 2 * (104.8e6 + 31.7e6)
 METRIC = "bab_domains_bounded_per_s"
 UNIT = "domains/s"
+WORKLOAD = "c4: MLP 784-512x4-10, 1 input eps 0.02, ReLU-split BaB subdomains (10 split neurons each), 10 alpha-CROWN Adam steps lr 0.1, 9 margin specs"
+FFMA_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # FP32 FMA lanes x 2 flop x max SM clock
 
 
 def measured_peaks():
@@ -99,14 +114,15 @@ class ClockSampler:
 
 
 def build_host_batch(wl, root_pre, n_domains: int, rank: int):
-    """Pinned host tensors of one subdomain batch for this rank (seeded per rank)."""
+    """Pinned host tensors of one subdomain batch for this rank (seeded per rank): the input box and the spec rows of
+    the one problem the subdomains belong to, and one int8 split row per subdomain and ReLU layer."""
     from boundflow_b200 import workloads as W
 
     wl.generator = torch.Generator("cpu").manual_seed(1004_000 + rank)
     splits = W.make_split_domains(wl, root_pre, n_domains=n_domains)
-    lo = wl.lo.expand(n_domains, -1).contiguous().pin_memory()
-    up = wl.up.expand(n_domains, -1).contiguous().pin_memory()
-    C = wl.C.expand(n_domains, -1, -1).contiguous().pin_memory()
+    lo = wl.lo.contiguous().pin_memory()            # [1, 784]
+    up = wl.up.contiguous().pin_memory()
+    C = wl.C.contiguous().pin_memory()              # [1, 9, 10]
     splits = [s.pin_memory() for s in splits]
     return lo, up, C, splits
 
@@ -118,58 +134,274 @@ def sweep_flops(widths, M):
     return bwd, adj
 
 
-def cpu_baseline(sample_domains: int, reps: int = 1):
-    """The oracle (CPU restatement of the reference's PyTorch path) on a bounded sample."""
-    from boundflow_b200 import workloads as W
-    from oracle import crown_oracle as O
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's own functions (oracle/_ref) or, when that is absent, the oracle port
+# ---------------------------------------------------------------------------------------------
+class CpuArm:
+    """One c4 step (`sample` subdomains) on the host cores.  kind == "reference": the reference's
+    `_forward_ibp_trace_mlp(relu_split_state=)`, its backward primitive `run_crown_ibp_mlp_from_forward_trace(relu_alpha=)`
+    under torch autograd and torch.optim.Adam with the per-domain best-of rule of its alpha loop
+    (alpha_beta_crown.py:747-923); kind == "port": `oracle/crown_oracle.py`, the restatement of the same functions."""
 
-    torch.set_num_threads(os.cpu_count() or 1)
-    wl = W.make_workload("c4")
-    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
-    wl.generator = torch.Generator("cpu").manual_seed(1004_000)
-    splits = W.make_split_domains(wl, root.pre, n_domains=sample_domains)
-    inp = O.box_input(wl.lo.expand(sample_domains, -1).contiguous(), wl.up.expand(sample_domains, -1).contiguous())
-    C = wl.C.expand(sample_domains, -1, -1).contiguous()
-    times = []
-    for _ in range(reps):
+    def __init__(self, sample: int):
+        from boundflow_b200 import workloads as W
+
+        torch.set_num_threads(os.cpu_count() or 1)
+        self.sample = int(sample)
+        self.cores = os.cpu_count() or 1
+        wl = W.make_workload("c4")
+        self.wl = wl
+        from oracle.make_ref import ref_path
+
+        self.kind = "port"
+        p = ref_path()
+        if p is not None:
+            if p not in sys.path:
+                sys.path.insert(0, p)
+            try:
+                from boundflow.ir.task import BFTaskModule, BoundTask, TaskKind, TaskOp
+                from boundflow.runtime.crown_ibp import _forward_ibp_trace_mlp, run_crown_ibp_mlp_from_forward_trace
+                from boundflow.runtime.task_executor import InputSpec
+
+                self._fwd, self._bwd, self._InputSpec = _forward_ibp_trace_mlp, run_crown_ibp_mlp_from_forward_trace, InputSpec
+                src = wl.module.get_entry_task()
+                ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+                task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+                self.module = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(wl.module.bindings["params"])})
+                self.kind = "reference"
+            except Exception as e:  # an unusable build of oracle/_ref: say so and time the port
+                sys.stderr.write(f"bench: oracle/_ref is present but not importable ({e}); timing the oracle port instead\n")
+        from oracle import crown_oracle as O
+
+        self.O = O
+        root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+        wl.generator = torch.Generator("cpu").manual_seed(1004_000)
+        self.splits = W.make_split_domains(wl, root.pre, n_domains=self.sample)
+        self.lo = wl.lo.expand(self.sample, -1).contiguous()
+        self.up = wl.up.expand(self.sample, -1).contiguous()
+        self.C = wl.C.expand(self.sample, -1, -1).contiguous()
+
+    def describe(self) -> str:
+        what = ("the reference's own functions (oracle/_ref: _forward_ibp_trace_mlp + Adam over run_crown_ibp_mlp_from_forward_trace)"
+                if self.kind == "reference" else "oracle/crown_oracle.py, the CPU restatement of the reference's functions (oracle/_ref not built)")
+        return f"{self.sample} subdomains of the same workload per step, {what}, torch CPU ops on {self.cores} threads"
+
+    def step(self) -> float:
+        """One pass; returns seconds."""
         t0 = time.perf_counter()
-        trace = O.forward_ibp_trace(wl.layers, inp, splits=splits)
-        a0 = O.adaptive_alpha_init(trace)
-        bl, bu, _, _ = O.alpha_crown(wl.layers, inp, C, steps=ALPHA_STEPS, lr=LR, alpha0=a0, trace=trace)
-        _ = O.verdict(bl)
-        times.append(time.perf_counter() - t0)
-    times.sort()
-    t = times[len(times) // 2]
-    return sample_domains / t, t
+        if self.kind == "reference":
+            self._reference_step()
+        else:
+            O = self.O
+            inp = O.box_input(self.lo, self.up)
+            trace = O.forward_ibp_trace(self.wl.layers, inp, splits=self.splits)
+            a0 = O.adaptive_alpha_init(trace)
+            bl, _bu, _, _ = O.alpha_crown(self.wl.layers, inp, self.C, steps=ALPHA_STEPS, lr=LR, alpha0=a0, trace=trace)
+            _ = O.verdict(bl)
+        return time.perf_counter() - t0
+
+    def _reference_step(self):
+        names = self.wl.relu_names
+        spec = self._InputSpec.box(value_name="input", lower=self.lo, upper=self.up)
+        env, pre = self._fwd(self.module, spec, relu_split_state=dict(zip(names, self.splits)))
+        alphas = {}
+        for n in names:  # adaptive start: 1 where l >= 0 or (l < 0 < u and u > -l)
+            l, u = pre[n].lower, pre[n].upper
+            alphas[n] = ((l >= 0) | ((l < 0) & (u > 0) & (u > -l))).to(l.dtype).requires_grad_(True)
+        opt = torch.optim.Adam(list(alphas.values()), lr=LR)
+        best_m = best_l = None
+        for step in range(ALPHA_STEPS + 1):
+            b = self._bwd(self.module, spec, interval_env=env, relu_pre=pre, linear_spec_C=self.C, relu_alpha=alphas)
+            m = b.lower.mean(dim=1)
+            if best_m is None:
+                best_m, best_l = m.detach().clone(), b.lower.detach().clone()
+            else:
+                imp = m.detach() > best_m
+                best_m = torch.where(imp, m.detach(), best_m)
+                best_l = torch.where(imp[:, None], b.lower.detach(), best_l)
+            if step == ALPHA_STEPS:
+                break
+            opt.zero_grad(set_to_none=True)
+            (-m.sum()).backward()
+            opt.step()
+            with torch.no_grad():
+                for a in alphas.values():
+                    a.clamp_(0.0, 1.0)
+        return best_l.min(dim=1).values >= -1e-6
+
+    def baseline(self):
+        """1 warm-up pass + median of 3 passes -> (domains/s, seconds per pass)."""
+        self.step()
+        ts = sorted(self.step() for _ in range(3))
+        return self.sample / ts[1], ts[1]
+
+
+def bench_config(D: int, world: int, scaling: str):
+    n_total = D * world if scaling == "weak" else D
+    return {
+        "workload": WORKLOAD,
+        "domains_per_gpu_per_step": D if scaling == "weak" else D // world, "domains_per_step": n_total, "alpha_steps": ALPHA_STEPS,
+        "l2": "per-step working set (coefficient tensors, > 1 GB) exceeds the 126 MB L2; no explicit flush",
+        "parallelism": (f"domains sharded over {world} GPU(s), weights replicated, one all-gather of bounds+verdicts per step"
+                        + ("" if scaling == "weak" else "; ONE batch split over the GPUs (strong scaling)")),
+    }
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 2048
     t0 = time.perf_counter()
-    for _ in range(max(args.warmup, 0) and 1):
-        cpu_baseline(sample)
-    vals = []
-    for _ in range(max(1, min(args.steps, 3))):
-        v, _t = cpu_baseline(sample)
-        vals.append(v)
-    v = sum(vals) / len(vals)
-    cores = os.cpu_count() or 1
+    arm = CpuArm(REFERENCE_SAMPLE)
+    warmup, steps = max(int(args.warmup), 1), max(int(args.steps), 1)
+    for _ in range(warmup):
+        arm.step()
+    total = sum(arm.step() for _ in range(steps))
+    v = arm.sample * steps / total
     line = {
-        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals), "warmup": 1 if args.warmup else 0,
-        "ms_per_step": 1e3 * sample / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "c4: MLP 784-512x4-10, ReLU-split BaB subdomains (10 split neurons), 10 alpha-CROWN steps, 9 specs", "domains_per_step": sample},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} subdomains of the same workload per step, torch CPU ops on {cores} threads (the reference is pure Python/torch; its CPU path is restated by oracle/crown_oracle.py)"},
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": 1e3 * total / steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": bench_config(int(args.domains), max(int(args.gpus), 1), args.scaling),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": arm.describe()},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": f"a step of this arm bounds {arm.sample} of the config's subdomains (ms_per_step is that sample's time); value = subdomains/s",
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line))
 
 
-def crown_bounds_secondary(world: int, rank: int, dev, only=None):
+# ---------------------------------------------------------------------------------------------
+# kernel timing slots -> roofline objects
+# ---------------------------------------------------------------------------------------------
+def read_slots(lib):
+    """{slot name: {launches, ms, bytes, flops}} of everything timed since bf_kernel_timing_enable(1)."""
+    out = {}
+    for s in range(int(lib.bf_kernel_timing_slots())):
+        n, ms, by, fl = ctypes.c_int(), ctypes.c_float(), ctypes.c_double(), ctypes.c_double()
+        lib.bf_kernel_timing_read_work(s, ctypes.byref(n), ctypes.byref(ms), ctypes.byref(by), ctypes.byref(fl))
+        if n.value:
+            out[lib.bf_kernel_timing_slot_name(s).decode()] = {"launches": n.value, "ms": ms.value, "bytes": by.value, "flops": fl.value}
+    return out
+
+
+def hbm_roofline(name, rec, peaks, note=""):
+    gbs = rec["bytes"] / (rec["ms"] * 1e-3) / 1e9 if rec["ms"] > 0 else None
+    tf = rec["flops"] / (rec["ms"] * 1e-3) / 1e12 if rec["ms"] > 0 else None
+    r = {"kernel": name, "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"] if gbs else None,
+         "launches": rec["launches"], "avg_launch_us": 1e3 * rec["ms"] / rec["launches"], "algorithmic_bytes_per_launch": rec["bytes"] / rec["launches"],
+         "fp32_tflops": tf, "fp32_frac_of_ffma_peak": tf / FFMA_PEAK_TFLOPS if tf else None, "peak_source": f"{peaks['source']} STREAM-style copy"}
+    if note:
+        r["note"] = note
+    return r
+
+
+def kernel_rooflines(dev, peaks):
+    """Single kernels on resident data, CUDA events around every launch (the library's timing slots), inputs larger
+    than L2 or an L2 flush between launches: the HBM-bound pieces of the path at the sizes of configurations c4 and c1."""
+    from boundflow_b200 import _lib
+
+    lib = _lib.load()
+    st = torch.cuda.current_stream(dev).cuda_stream
+    g = torch.Generator("cpu").manual_seed(5)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
+    out = {}
+
+    def timed(fn, reps, flush_between):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        lib.bf_kernel_timing_enable(1)
+        for _ in range(reps):
+            if flush_between:
+                flush.fill_(1)
+            fn()
+        torch.cuda.synchronize(dev)
+        slots = read_slots(lib)
+        lib.bf_kernel_timing_enable(0)
+        return slots
+
+    # concretisation of c4's final coefficient rows: 73728 rows x 784
+    B, S, n0 = 8192, 9, 784
+    A = torch.randn(B * S, n0, generator=g).to(dev)
+    mid, rad = torch.rand(B, n0, generator=g).to(dev), torch.rand(B, n0, generator=g).to(dev) * 0.02
+    res = torch.empty(B, S, device=dev)
+    s = timed(lambda: _lib.check(lib.bf_concretize(A.data_ptr(), mid.data_ptr(), rad.data_ptr(), None, res.data_ptr(), _lib.SIDE_LOWER, B, S, n0, st)), 10, False)
+    out["concretize_kernel_c4_73728x784"] = hbm_roofline("concretize_kernel", s["concretize_kernel"], peaks, "input 231 MB > L2, no flush needed")
+    del A
+    # interval Linear layer of c4 (8192 domains, 512 -> 512, ReLU on load) and of c1 (64 inputs, 784 -> 100, weights dominate)
+    for tag, Bq, K, N, relu_in, fl in (("c4_8192x512x512", 8192, 512, 512, 1, False), ("c1_64x784x100", 64, 784, 100, 0, True)):
+        lo = torch.randn(Bq, K, generator=g).to(dev)
+        up = lo + torch.rand(Bq, K, generator=g).to(dev)
+        Wt, b = torch.randn(N, K, generator=g).to(dev), torch.randn(N, generator=g).to(dev)
+        ol, ou = torch.empty(Bq, N, device=dev), torch.empty(Bq, N, device=dev)
+        s = timed(lambda: _lib.check(lib.bf_ibp_linear(lo.data_ptr(), up.data_ptr(), _lib.IN_LOWER_UPPER, relu_in, Wt.data_ptr(), b.data_ptr(), None, 0, None, None,
+                                                       ol.data_ptr(), ou.data_ptr(), None, Bq, K, N, st)), 10, fl)
+        out[f"ibp_linear_kernel_{tag}"] = hbm_roofline("ibp_linear_kernel", s["ibp_linear_kernel"], peaks,
+                                                       "compute-bound at this batch (FP32 FFMA): see fp32_frac_of_ffma_peak" if Bq > 1000 else "L2 flushed between launches; 0.3 MB of weights: launch-latency bound")
+    # interval Conv2d of c5's second layer (64 inputs, 32x32x32 -> 32x16x16, k4 s2 p1) and c2's first at 256 inputs
+    for tag, Bq, Ci, Hi, Co, k, stv, pd in (("c5conv2_64in", 64, 32, 32, 32, 4, 2, 1), ("c2conv1_256in", 256, 1, 28, 16, 4, 2, 1)):
+        Ho = (Hi + 2 * pd - k) // stv + 1
+        lo = torch.rand(Bq, Ci * Hi * Hi, generator=g).to(dev)
+        up = lo + 0.01
+        Wc, bc = torch.randn(Co, Ci, k, k, generator=g).to(dev), torch.randn(Co, generator=g).to(dev)
+        ol, ou = torch.empty(Bq, Co * Ho * Ho, device=dev), torch.empty(Bq, Co * Ho * Ho, device=dev)
+        s = timed(lambda: _lib.check(lib.bf_ibp_conv2d(lo.data_ptr(), up.data_ptr(), _lib.IN_LOWER_UPPER, 0, Wc.data_ptr(), bc.data_ptr(), None, 0, None, None,
+                                                       ol.data_ptr(), ou.data_ptr(), None, Bq, Ci, Hi, Hi, Co, Ho, Ho, k, k, stv, stv, pd, pd, st)), 10, True)
+        out[f"ibp_conv2d_kernel_{tag}"] = hbm_roofline("ibp_conv2d_kernel", s["ibp_conv2d_kernel"], peaks, "L2 flushed between launches")
+    return out
+
+
+CONV_LAYERS = {  # name: (Co, Ho, Wo, Ci, Hi, Wi, kernel, stride, padding) of the forward layer whose transpose is applied
+    "c5conv2T": (32, 16, 16, 32, 32, 32, 4, 2, 1), "c5conv3T": (64, 16, 16, 32, 16, 16, 3, 1, 1), "c5conv4T": (64, 8, 8, 64, 16, 16, 4, 2, 1),
+    "c5conv1T": (32, 32, 32, 3, 32, 32, 3, 1, 1), "c2conv2T": (32, 7, 7, 16, 14, 14, 4, 2, 1), "c2conv1T": (16, 14, 14, 1, 28, 28, 4, 2, 1),
+}
+
+
+def conv_layer_bench(dev, names, rows, reps):
+    """One `bf_crown_relu_conv2d_bwd` call per layer shape (ReLU scaling pass + transposed convolution, one side),
+    CUDA events, multiply-accumulates per second."""
+    from boundflow_b200 import _lib
+
+    lib = _lib.load()
+    out = {}
+    for name in names:
+        Co, Ho, Wo, Ci, Hi, Wi, k, stv, pd = CONV_LAYERS[name]
+        S = 8
+        B = max(1, rows // S)
+        M = B * S
+        g = torch.Generator("cpu").manual_seed(7)
+        n = Co * Ho * Wo
+        A = torch.randn(B, S, n, generator=g).to(dev)
+        au, al, bu = (torch.rand(B, n, generator=g).to(dev) for _ in range(3))
+        bl = torch.zeros(B, n, device=dev)
+        Wc = torch.randn(Co, Ci, k, k, generator=g).to(dev)
+        bias = torch.randn(Co, generator=g).to(dev)
+        res = torch.empty(B, S, Ci * Hi * Wi, device=dev)
+        delta = torch.empty(B, S, device=dev)
+        nbytes = int(lib.bf_crown_relu_conv2d_bwd_scratch_bytes(B, S, Co, Ho, Wo))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        st = torch.cuda.current_stream(dev).cuda_stream
+
+        def run():
+            _lib.check(lib.bf_crown_relu_conv2d_bwd(
+                A.data_ptr(), _lib.SIDE_LOWER, au.data_ptr(), al.data_ptr(), bu.data_ptr(), bl.data_ptr(), Wc.data_ptr(), bias.data_ptr(),
+                res.data_ptr(), delta.data_ptr(), 0, scratch.data_ptr(), nbytes, B, S, Ci, Hi, Wi, Co, Ho, Wo, k, k, stv, stv, pd, pd, st))
+
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / reps
+        out[name] = {"rows": M, "ms": ms, "tmac_per_s": M * n * Ci * k * k / ms / 1e9}
+    return out
+
+
+def crown_bounds_secondary(world: int, rank: int, dev, only=None, with_slots=False):
     """Second half of the metric: CROWN bounds/s (one bound = one (input, spec) lower bound) on the
     input-sharded configurations, whole job over all ranks, device-timed, max over ranks.
       c1: IBP + CROWN (both sides), MLP 784-100-100-10, 64 inputs
@@ -217,6 +449,8 @@ def crown_bounds_secondary(world: int, rank: int, dev, only=None):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        if with_slots:
+            lib.bf_kernel_timing_enable(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(reps):
@@ -229,6 +463,9 @@ def crown_bounds_secondary(world: int, rank: int, dev, only=None):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         out[name] = {"bounds_per_s": n * 9 / (ms * 1e-3), "ms": ms, "inputs": n}
+        if with_slots:
+            out[name]["kernels"] = read_slots(lib)
+            lib.bf_kernel_timing_enable(0)
     return out
 
 
@@ -238,10 +475,17 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--domains", type=int, default=DOMAINS_PER_GPU, help="subdomains per GPU per step")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU bounds its own batch of --domains subdomains; strong: ONE batch of --domains is split over the GPUs")
+    ap.add_argument("--domains", type=int, default=DOMAINS_PER_GPU, help="subdomains per GPU per step (weak) or per step in all (strong)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the CROWN bounds/s configurations and the single-kernel rooflines")
     ap.add_argument("--secondary-only", default=None, choices=["c1", "c2", "c3", "c5"],
-                    help="time only this CROWN bounds/s configuration and print its figures (profiling aid)")
+                    help="time only this CROWN bounds/s configuration and print its figures with per-kernel times (profiling aid)")
+    ap.add_argument("--kernels", action="store_true", help="time single kernels on resident data and print their rooflines (profiling aid)")
+    ap.add_argument("--conv-layers", default=None, help="comma-separated layer names: time the fused ReLU + transposed-convolution call (profiling aid)")
+    ap.add_argument("--rows", type=int, default=2048, help="coefficient rows for --conv-layers")
+    ap.add_argument("--reps", type=int, default=10, help="repetitions for --conv-layers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -265,28 +509,37 @@ def main():
     from boundflow_b200 import _lib
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import bound_split_domains, ibp_trace
-    from boundflow_b200.dist import gather_domain_results
+    from boundflow_b200.dist import gather_domain_results, shard_range
     from boundflow_b200.ir import InputSpec
 
     lib = _lib.load()
+    peaks = measured_peaks()
     if args.secondary_only:
-        sec = crown_bounds_secondary(world, rank, dev, only=args.secondary_only)
+        sec = crown_bounds_secondary(world, rank, dev, only=args.secondary_only, with_slots=True)
         if rank == 0:
             print(json.dumps({"crown_bounds_per_s": sec, "n_gpus": world}))
         if world > 1:
             dist.destroy_process_group()
         return
+    if args.kernels:
+        print(json.dumps({"kernel_rooflines": kernel_rooflines(dev, peaks)}))
+        return
+    if args.conv_layers:
+        print(json.dumps({"conv_layers": conv_layer_bench(dev, args.conv_layers.split(","), args.rows, args.reps)}))
+        return
     warmup = max(int(args.warmup), 3)
-    D = int(args.domains)
+    strong = args.scaling == "strong"
+    n_total = int(args.domains) * (1 if strong else world)
+    a_lo, a_hi = shard_range(n_total, rank, world)
+    D = a_hi - a_lo  # subdomains bounded by this rank per step
     wl = W.make_workload("c4")
     names = wl.relu_names
     root = ibp_trace(wl.module, InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev)))
     root_pre = [(l.cpu(), u.cpu()) for l, u in zip(root.pre_l, root.pre_u)]
     h_lo, h_up, h_C, h_splits = build_host_batch(wl, root_pre, D, rank)
-    d_lo, d_up, d_C = h_lo.to(dev), h_up.to(dev), h_C.to(dev)
+    d_lo, d_up, d_C = h_lo.to(dev).expand(D, -1).contiguous(), h_up.to(dev).expand(D, -1).contiguous(), h_C.to(dev).expand(D, -1, -1).contiguous()
     d_splits = {n: s.to(dev) for n, s in zip(names, h_splits)}
     d_spec = InputSpec.box(value_name="input", lower=d_lo, upper=d_up)
-    n_total = D * world
 
     def step_resident():
         res = bound_split_domains(wl.module, d_spec, linear_spec_C=d_C, relu_split_state=d_splits, steps=ALPHA_STEPS, lr=LR)
@@ -294,6 +547,7 @@ def main():
         return lower, verdict, res
 
     def step_e2e():
+        # the public call fed from pinned host memory: box [1,784] x2, specs [1,9,10], one int8 split row per subdomain and layer
         spec = InputSpec.box(value_name="input", lower=h_lo.to(dev, non_blocking=True), upper=h_up.to(dev, non_blocking=True))
         res = bound_split_domains(
             wl.module, spec, linear_spec_C=h_C.to(dev, non_blocking=True),
@@ -329,21 +583,23 @@ def main():
     if rank == 0:
         sampler.start()
     lib.bf_kernel_timing_enable(1)
-    launches0 = _lib.launch_count()
+    launches0, tc0 = _lib.launch_count(), _lib.tc_launch_count()
     ms_res, out = timed(step_resident, args.steps)
-    launches = _lib.launch_count() - launches0
-    n_l, t_l = ctypes.c_int(), ctypes.c_float()
-    lib.bf_kernel_timing_read(0, ctypes.byref(n_l), ctypes.byref(t_l))
-    n_a, t_a = ctypes.c_int(), ctypes.c_float()
-    lib.bf_kernel_timing_read(1, ctypes.byref(n_a), ctypes.byref(t_a))
+    launches, tc_launches = _lib.launch_count() - launches0, _lib.tc_launch_count() - tc0
+    slots = read_slots(lib)
     lib.bf_kernel_timing_enable(0)
 
     for _ in range(2):
         step_e2e()
     ms_e2e, out_e2e = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions (resident and end-to-end)
+    tc_status = wl_status = None
+    from boundflow_b200.network import compile_chain
 
-    secondary = crown_bounds_secondary(world, rank, dev)
+    tc_status = compile_chain(wl.module, (784,), dev).tc_status()
+
+    secondary = None if args.no_secondary else crown_bounds_secondary(world, rank, dev)
+    kernels = None if (args.no_secondary or rank != 0) else kernel_rooflines(dev, peaks)
 
     if rank != 0:
         if world > 1:
@@ -353,57 +609,60 @@ def main():
     lower, verdict, res = out
     infeasible = int(res.infeasible.sum().item())
     proven = int(verdict.sum().item())
-    peaks = measured_peaks()
+    if tc_status != 0:
+        raise SystemExit("bench: a bounded wait expired inside a tensor-core kernel (status word set): results are invalid")
+    feasible_rows = lower[: res.infeasible.shape[0]][res.infeasible == 0]
+    if not bool(torch.isfinite(feasible_rows).all()):
+        raise SystemExit("bench: non-finite lower bound on a feasible subdomain")
     widths = [784, 512, 512, 512, 512, 10]
-    M = D * 9
-    bwd_flops, adj_flops = sweep_flops(widths, M)
-    sweeps_per_step = ALPHA_STEPS + 2          # 11 lower evaluations + 1 upper
-    bwd_total_flops = bwd_flops * sweeps_per_step * args.steps
-    adj_total_flops = adj_flops * ALPHA_STEPS * args.steps
+    bwd = slots.get("crown_bwd_contraction", {"launches": 0, "ms": 0.0, "bytes": 0.0, "flops": 0.0})
+    adj = slots.get("crown_adjoint_contraction", {"launches": 0, "ms": 0.0, "bytes": 0.0, "flops": 0.0})
     fp32_equiv_peak = peaks["bf16_sustained"] / 6.0  # TF32 runs at half the bf16 rate; 3 TF32 MMAs per fp32-faithful product
-    achieved = bwd_total_flops / (t_l.value * 1e-3) / 1e12 if t_l.value > 0 else None
-    achieved_adj = adj_total_flops / (t_a.value * 1e-3) / 1e12 if t_a.value > 0 else None
+    achieved = bwd["flops"] / (bwd["ms"] * 1e-3) / 1e12 if bwd["ms"] > 0 else None
+    achieved_adj = adj["flops"] / (adj["ms"] * 1e-3) / 1e12 if adj["ms"] > 0 else None
     value = n_total * args.steps / (ms_res * 1e-3)
     e2e_value = n_total * args.steps / (ms_e2e * 1e-3)
     h2d = h_lo.numel() * 4 * 2 + h_C.numel() * 4 + sum(s.numel() for s in h_splits)
     d2h = n_total * 9 * 4 + n_total + D * 4
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {
-            "workload": "c4: MLP 784-512x4-10, 1 input eps 0.02, ReLU-split BaB subdomains (10 split neurons each), 10 alpha-CROWN Adam steps lr 0.1, 9 margin specs",
-            "domains_per_gpu_per_step": D, "domains_per_step": n_total, "alpha_steps": ALPHA_STEPS,
-            "l2": "per-step working set (coefficient tensors, > 1 GB) exceeds the 126 MB L2; no explicit flush",
-            "parallelism": f"domains sharded over {world} GPU(s), weights replicated, one all-gather of bounds+verdicts per step",
-        },
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": int(launches),
+        "config": bench_config(int(args.domains), world, args.scaling),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": ms_e2e / args.steps,
+                "note": "input box [1,784] x2 and spec rows [1,9,10] travel once per step and are repeated on the device; one int8 split row per subdomain and ReLU layer"},
+        "gpu_launches": int(launches), "gpu_tensor_core_launches": int(tc_launches),
         "clocks": clocks,
         "roofline": {
-            "bound": "tensor", "kernel": "crown_tc_kernel<bwd> (ReLU-backward + Linear-backward contraction, tcgen05 3xTF32; the 10-wide top layer runs as a store-bound thin kernel)",
+            "bound": "tensor", "kernel": "crown_tc_kernel<bwd> (ReLU-backward + Linear-backward contraction, tcgen05 3xTF32)",
             "achieved": achieved, "peak": fp32_equiv_peak, "unit": "TFLOP/s", "frac": (achieved / fp32_equiv_peak) if achieved else None,
             "traffic": TRAFFIC_BYTES_PER_LAUNCH * (D / 8192.0),
             "traffic_source": "ncu dram__bytes_read+write of one 512x512-layer launch at 4096 domains, scaled by rows (profiles/)",
             "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 6 = fp32-equivalent 3xTF32 tensor peak",
-            "launches": n_l.value, "avg_launch_ms": (t_l.value / n_l.value) if n_l.value else None,
-            "share_of_step": t_l.value / ms_res if ms_res else None,
+            "launches": bwd["launches"], "avg_launch_ms": (bwd["ms"] / bwd["launches"]) if bwd["launches"] else None,
+            "algorithmic_flops_per_launch": (bwd["flops"] / bwd["launches"]) if bwd["launches"] else None,
+            "share_of_step": bwd["ms"] / ms_res if ms_res else None,
         },
         "roofline_adjoint": {
             "kernel": "crown_tc_adjoint_kernel (gradient sweep, feature-major tcgen05 3xTF32)", "achieved": achieved_adj, "unit": "TFLOP/s",
-            "frac": (achieved_adj / fp32_equiv_peak) if achieved_adj else None, "launches": n_a.value,
-            "share_of_step": t_a.value / ms_res if ms_res else None,
+            "frac": (achieved_adj / fp32_equiv_peak) if achieved_adj else None, "launches": adj["launches"],
+            "share_of_step": adj["ms"] / ms_res if ms_res else None,
         },
+        # HBM-bound kernels: inside the timed c4 step (live event pairs), and single kernels at the configurations' sizes
+        "roofline_hbm": {
+            "in_step": {n: hbm_roofline(n, slots[n], peaks) for n in ("crown_bwd_thin_kernel", "adam_step_kernel", "ibp_linear_kernel") if n in slots},
+            "single_kernels": kernels,
+        },
+        "kernel_share_of_step": {n: r["ms"] / ms_res for n, r in slots.items()},
         "crown_bounds_per_s": secondary,
-        "result_check": {"domains": n_total, "proven": proven, "infeasible_local": infeasible,
+        "result_check": {"domains": n_total, "proven": proven, "infeasible_local": infeasible, "tc_status": tc_status,
                          "mean_lower": float(lower[torch.isfinite(lower).all(dim=1)].mean().item())},
     }
     if not args.no_cpu_baseline and world == 1:
-        sample = 2048
-        v, t = cpu_baseline(sample)
-        cores = os.cpu_count() or 1
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": f"{sample} subdomains of the same workload, one pass ({t:.1f} s), torch CPU ops on {cores} threads"}
+        arm = CpuArm(REFERENCE_SAMPLE)
+        v, t = arm.baseline()
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": arm.cores, "kind": arm.kind,
+                                "sample": arm.describe() + f"; 1 warm-up pass, median of 3 ({t:.2f} s per pass)"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

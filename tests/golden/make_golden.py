@@ -1,8 +1,9 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE.
 
-Run once where the reference checkout is available:
+Run where a checkout of the reference is available (the path is required; a second argument
+regenerates one file only, e.g. `c4`, `c3`, `adam_divergence`, `lp_ball`):
 
-    python tests/golden/make_golden.py /path/to/boundflow-checkout
+    python tests/golden/make_golden.py /path/to/boundflow-checkout [name]
 
 It imports the reference's own PyTorch path (boundflow.runtime.*), feeds it the
 seeded synthetic workloads of `boundflow_b200.workloads`, and stores the
@@ -22,7 +23,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2 or not os.path.isfile(os.path.join(sys.argv[1], "boundflow", "__init__.py")):
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/boundflow-checkout [name]")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 from boundflow.domains.interval import IntervalState  # noqa: E402
@@ -165,7 +168,7 @@ def gen_shared_alpha() -> None:
     wl = W.make_workload("c4")
     root_spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
     _, root_pre = _forward_ibp_trace_mlp(ref_module(wl), root_spec)
-    D = 24
+    D = C4_DOMAINS
     splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
     lo, up = wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous()
     spec = InputSpec.box(value_name="input", lower=lo, upper=up)
@@ -316,25 +319,7 @@ def gen_conv_alpha() -> None:
     save("conv_alpha.npz", **out)
 
 
-def main() -> None:
-    torch.set_num_threads(os.cpu_count() or 1)
-    torch.manual_seed(0)
-    only = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
-            "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
-            "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha,
-            "conv_alpha": gen_conv_alpha}
-    if len(sys.argv) > 2:  # regenerate one file only
-        only[sys.argv[2]]()
-        return
-    gen_lp_ball()
-    gen_shared_alpha()
-    gen_spec_fused_ibp()
-    gen_first_layer_certificate()
-    gen_relu_influence()
-    gen_graph_cases()
-    gen_lp_alpha()
-    gen_conv_alpha()
-
+def gen_c1() -> None:
     # ---- c1: IBP + CROWN, full configuration --------------------------------
     wl = W.make_workload("c1")
     m = ref_module(wl)
@@ -354,6 +339,8 @@ def main() -> None:
         pre2_lower=relu_pre["h2"].lower, pre2_upper=relu_pre["h2"].upper,
     )
 
+
+def gen_c2() -> None:
     # ---- c2: CNN, CROWN-IBP on 8 inputs and full-CROWN intermediates on 4 ----
     wl = W.make_workload("c2", batch=8)
     m = ref_module(wl)
@@ -376,6 +363,8 @@ def main() -> None:
         **{f"pre_{n}_upper": cur[n].upper.reshape(4, -1)[:, ::7] for n in wl4.relu_names},
     )
 
+
+def gen_c3() -> None:
     # ---- c3: alpha-CROWN verbatim reference function on 8 inputs -------------
     wl = W.make_workload("c3", batch=8)
     m = ref_module(wl)
@@ -404,12 +393,17 @@ def main() -> None:
         **{f"grad0_{k}": v.grad for k, v in leaves.items()},
     )
 
-    # ---- c4: split subdomains, alpha-only loop on 24 domains -----------------
+
+C4_DOMAINS = 32  # 32 domains x 9 specs = 288 coefficient rows: enough for the tensor-core kernels (>= 256 rows)
+
+
+def gen_c4() -> None:
+    # ---- c4: split subdomains, alpha-only loop and the verbatim alpha-beta function ----
     wl = W.make_workload("c4")
     m = ref_module(wl)
     root_spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
     _, root_pre = _forward_ibp_trace_mlp(m, root_spec)
-    D = 24
+    D = C4_DOMAINS
     splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
     lo = wl.lo.expand(D, -1).contiguous()
     up = wl.up.expand(D, -1).contiguous()
@@ -445,6 +439,8 @@ def main() -> None:
         **{f"alpha_{k}": v for k, v in best_a.items()},
     )
 
+
+def gen_c5() -> None:
     # ---- c5: CIFAR-shaped CNN, CROWN-IBP on 2 inputs, full-CROWN on 1 --------
     wl = W.make_workload("c5", batch=2)
     m = ref_module(wl)
@@ -467,6 +463,8 @@ def main() -> None:
         **{f"pre_{n}_upper": cur[n].upper.reshape(1, -1)[:, ::31] for n in wl1.relu_names},
     )
 
+
+def gen_fused_region() -> None:
     # ---- fused ReLU+affine region requests (boundary B3) ---------------------
     g = torch.Generator("cpu").manual_seed(77)
     D, S, n_cur, n_prev = 5, 9, 37, 53
@@ -497,6 +495,73 @@ def main() -> None:
         lin_A_prev_u=res.A_prev_u, lin_A_prev_l=res.A_prev_l, lin_delta_u=res.bias_delta_u, lin_delta_l=res.bias_delta_l,
         conv_A_prev_u=resc.A_prev_u, conv_A_prev_l=resc.A_prev_l, conv_delta_u=resc.bias_delta_u, conv_delta_l=resc.bias_delta_l,
     )
+
+
+def _to64(module):
+    """The same module with float64 parameters."""
+    src = module.get_entry_task()
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=list(src.ops), input_values=["input"], output_values=["out"])
+    return BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": {k: v.double() for k, v in module.bindings["params"].items()}})
+
+
+def gen_adam_divergence() -> None:
+    """How far the reference's own optimised bounds move when only the arithmetic precision changes.
+
+    Adam turns a rounding-sized gradient difference into a full +-lr move of that alpha, so two correct fp32
+    implementations of the alpha loop drift apart with the step count.  This stores, for the alpha loops the tests
+    compare (c3: the verbatim alpha-beta function, 8 inputs; c4: the alpha-only loop on split subdomains), the
+    reference's best lower bounds after k = 1, 2, 5, 10 (and 20) steps computed in float32 AND in float64 on
+    identical inputs.  The tests hold the CUDA trajectory to the strict tolerance while float32 and float64 still
+    agree to it, and to twice the stored float32-vs-float64 distance afterwards."""
+    out = {}
+    # c3, verbatim alpha-beta function
+    wl = W.make_workload("c3", batch=8)
+    m32 = ref_module(wl)
+    m64 = _to64(m32)
+    for tag, m, cast in (("f32", m32, lambda t: t), ("f64", m64, lambda t: t.double())):
+        spec = InputSpec.box(value_name="input", lower=cast(wl.lo), upper=cast(wl.up))
+        _env, relu_pre = _forward_ibp_trace_mlp(m32, InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up))
+        a0 = {k: cast(v) for k, v in adaptive_alpha(relu_pre).items()}  # identical start in both precisions
+        for k in (1, 2, 5, 10, 20):
+            b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=cast(wl.C), steps=k, lr=0.1,
+                                                     warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                     per_batch_params=True, objective="lower", spec_reduce="mean")
+            out[f"c3_{tag}_lower_{k}"] = b.lower.float() if tag == "f32" else b.lower
+    # c4, alpha-only loop on the first 32 split subdomains
+    wl = W.make_workload("c4")
+    m32 = ref_module(wl)
+    m64 = _to64(m32)
+    root_spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _, root_pre = _forward_ibp_trace_mlp(m32, root_spec)
+    D = C4_DOMAINS
+    splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
+    split_state = {n: s for n, s in zip(wl.relu_names, splits)}
+    lo, up, C = wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous(), wl.C.expand(D, -1, -1).contiguous()
+    _env32, pre32 = _forward_ibp_trace_mlp(m32, InputSpec.box(value_name="input", lower=lo, upper=up), relu_split_state=split_state)
+    a0_32 = adaptive_alpha(pre32)
+    for tag, m, cast in (("f32", m32, lambda t: t), ("f64", m64, lambda t: t.double())):
+        spec = InputSpec.box(value_name="input", lower=cast(lo), upper=cast(up))
+        env, pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=split_state)
+        a0 = {k: cast(v) for k, v in a0_32.items()}
+        for k in (1, 2, 5, 10):
+            bl, _bu, _ba = ref_alpha_only_loop(m, spec, cast(C), pre, env, a0, steps=k, lr=0.1, reduce="mean")
+            out[f"c4_{tag}_lower_{k}"] = bl
+    save("adam_divergence.npz", **out)
+
+
+GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
+              "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
+              "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha, "conv_alpha": gen_conv_alpha,
+              "c1": gen_c1, "c2": gen_c2, "c3": gen_c3, "c4": gen_c4, "c5": gen_c5, "fused_region": gen_fused_region,
+              "adam_divergence": gen_adam_divergence}
+
+
+def main() -> None:
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.manual_seed(0)
+    names = sys.argv[2:] if len(sys.argv) > 2 else list(GENERATORS)  # all files, or the named ones only
+    for name in names:
+        GENERATORS[name]()
 
 
 if __name__ == "__main__":

@@ -49,7 +49,7 @@ def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel):
     from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, crown_from_trace, ibp_trace, run_alpha_beta_crown_mlp
 
     g = golden("c4_split_alpha_beta.npz")
-    wl, splits, spec, C, _, _ = _c4_domains(24, dev)
+    wl, splits, spec, C, _, _ = _c4_domains(32, dev)
     state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
     trace = ibp_trace(wl.module, spec, relu_split_state=state)
     a0 = adaptive_alpha_from_trace(trace)
