@@ -32,6 +32,11 @@ import torch.nn.functional as F
 Layers = List[dict]
 
 
+def layers_to(layers: "Layers", dtype: torch.dtype) -> "Layers":
+    """The same chain with its parameters cast to `dtype` (float64 evaluations serve as "truth" for the fp32 paths)."""
+    return [{k: (v.to(dtype) if torch.is_tensor(v) else v) for k, v in layer.items()} for layer in layers]
+
+
 # ----------------------------------------------------------------------------
 # input sets
 # ----------------------------------------------------------------------------

@@ -6,8 +6,9 @@ TEST AND BENCHMARK INFRASTRUCTURE ONLY.  Nothing under `boundflow_b200/` imports
 
 The reference (leezear2022/boundflow) is a pure-Python package whose bound-propagation path needs
 only torch and numpy.  This recipe byte-compiles every module of `<checkout>/boundflow` where it
-lies and writes the `.pyc` files (no sources) to `oracle/_ref/boundflow/...` in the legacy layout,
-from which CPython imports them without the `.py` files.  `oracle/_ref/` is git-ignored, so the
+lies and packs the `.pyc` files (no sources) into `oracle/_ref/boundflow_ref.zip` in the legacy
+layout, from which CPython's zipimport loads them without the `.py` files (one archive instead of
+loose `.pyc` files, which file-sync tools commonly skip).  `oracle/_ref/` is git-ignored, so the
 reference never enters this repository's history; it is a build output like a compiled `.so`.
 
 Users of `oracle/_ref` (all of them check that it exists and skip or fall back otherwise):
@@ -24,10 +25,13 @@ from __future__ import annotations
 import os
 import py_compile
 import sys
+import tempfile
+import zipfile
 from typing import Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+ARCHIVE = os.path.join(OUT, "boundflow_ref.zip")
 STAMP = os.path.join(OUT, "PYTHON_VERSION")
 
 
@@ -41,34 +45,39 @@ def make_ref(checkout: str, quiet: bool = False) -> str:
     src_root = os.path.join(os.path.abspath(checkout), "boundflow")
     if not os.path.isfile(os.path.join(src_root, "__init__.py")):
         raise FileNotFoundError(f"{checkout} does not contain the boundflow package")
+    os.makedirs(OUT, exist_ok=True)
     n = 0
-    for dirpath, dirnames, filenames in os.walk(src_root):
-        dirnames[:] = [d for d in dirnames if d not in ("__pycache__", "3rdparty")]
-        rel = os.path.relpath(dirpath, src_root)
-        out_dir = os.path.join(OUT, "boundflow", rel) if rel != "." else os.path.join(OUT, "boundflow")
-        for f in filenames:
-            if not f.endswith(".py"):
-                continue
-            os.makedirs(out_dir, exist_ok=True)
-            py_compile.compile(os.path.join(dirpath, f), cfile=os.path.join(out_dir, f + "c"), dfile=os.path.join("boundflow", rel, f),
-                               doraise=True, invalidation_mode=py_compile.PycInvalidationMode.UNCHECKED_HASH)
-            n += 1
+    with tempfile.TemporaryDirectory() as tmp, zipfile.ZipFile(ARCHIVE + ".tmp", "w", zipfile.ZIP_DEFLATED) as zf:
+        for dirpath, dirnames, filenames in os.walk(src_root):
+            dirnames[:] = sorted(d for d in dirnames if d not in ("__pycache__", "3rdparty"))
+            rel = os.path.relpath(dirpath, src_root)
+            pkg = "boundflow" if rel == "." else os.path.join("boundflow", rel)
+            zf.writestr(pkg + "/", "")  # explicit directory entry: packages without __init__ import as namespace portions
+            for f in sorted(filenames):
+                if not f.endswith(".py"):
+                    continue
+                cfile = os.path.join(tmp, "m.pyc")
+                py_compile.compile(os.path.join(dirpath, f), cfile=cfile, dfile=os.path.join(pkg, f), doraise=True,
+                                   invalidation_mode=py_compile.PycInvalidationMode.UNCHECKED_HASH)
+                zf.write(cfile, os.path.join(pkg, f + "c"))
+                n += 1
+    os.replace(ARCHIVE + ".tmp", ARCHIVE)
     with open(STAMP, "w") as fh:
         fh.write("%d.%d\n" % sys.version_info[:2])
     if not quiet:
-        print(f"compiled {n} modules of {src_root} into {OUT}")
-    return OUT
+        print(f"compiled {n} modules of {src_root} into {ARCHIVE}")
+    return ARCHIVE
 
 
 def ref_path() -> Optional[str]:
-    """Directory to put on sys.path to import the reference, or None when `oracle/_ref` has not been built
-    (or was built by another interpreter version)."""
-    if not os.path.isfile(os.path.join(OUT, "boundflow", "__init__.pyc")) or not os.path.isfile(STAMP):
+    """Path to put on sys.path to import the reference (the bytecode archive), or None when `oracle/_ref` has not
+    been built (or was built by another interpreter version)."""
+    if not os.path.isfile(ARCHIVE) or not os.path.isfile(STAMP):
         return None
     with open(STAMP) as fh:
         if fh.read().strip() != "%d.%d" % sys.version_info[:2]:
             return None
-    return OUT
+    return ARCHIVE
 
 
 if __name__ == "__main__":

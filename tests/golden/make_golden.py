@@ -71,7 +71,7 @@ def adaptive_alpha(relu_pre):
     return out
 
 
-def ref_alpha_only_loop(module, spec, C, relu_pre, interval_env, alpha0, *, steps, lr, reduce):
+def ref_alpha_only_loop(module, spec, C, relu_pre, interval_env, alpha0, *, steps, lr, reduce, history=None):
     """alpha-only per-domain loop built on the reference's backward primitive
     (`run_crown_ibp_mlp_from_forward_trace(relu_alpha=[B,n])`), with the update
     rule of alpha_beta_crown.py:747-923 (Adam, sum-over-domains loss, clamp,
@@ -85,6 +85,8 @@ def ref_alpha_only_loop(module, spec, C, relu_pre, interval_env, alpha0, *, step
             module, spec, interval_env=interval_env, relu_pre=relu_pre, linear_spec_C=C, relu_alpha=alphas
         )
         m = bounds.lower.mean(dim=1) if reduce == "mean" else bounds.lower.sum(dim=1)
+        if history is not None:  # the lower bounds of every iteration, for tests that must recognise near-ties of the best-of rule
+            history.append(bounds.lower.detach().clone())
         if best_m is None:
             best_m, best_l, best_u = m.detach().clone(), bounds.lower.detach().clone(), bounds.upper.detach().clone()
             best_a = {k: v.detach().clone() for k, v in alphas.items()}
@@ -512,7 +514,12 @@ def gen_adam_divergence() -> None:
     compare (c3: the verbatim alpha-beta function, 8 inputs; c4: the alpha-only loop on split subdomains), the
     reference's best lower bounds after k = 1, 2, 5, 10 (and 20) steps computed in float32 AND in float64 on
     identical inputs.  The tests hold the CUDA trajectory to the strict tolerance while float32 and float64 still
-    agree to it, and to twice the stored float32-vs-float64 distance afterwards."""
+    agree to it, and to twice the stored float32-vs-float64 distance afterwards.
+
+    The best-of rule is discrete: a domain returns the bounds of the iteration with the strictly largest objective, and
+    late iterations often differ in objective by less than rounding.  `*_hist_lower` therefore keeps the float32 lower
+    bounds of EVERY iteration of the longest run, so a test can accept any iteration whose objective ties with the best
+    one within the tolerance."""
     out = {}
     # c3, verbatim alpha-beta function
     wl = W.make_workload("c3", batch=8)
@@ -527,6 +534,11 @@ def gen_adam_divergence() -> None:
                                                      warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
                                                      per_batch_params=True, objective="lower", spec_reduce="mean")
             out[f"c3_{tag}_lower_{k}"] = b.lower.float() if tag == "f32" else b.lower
+        if tag == "f32":  # per-iteration bounds of the 20-step run (alpha-only loop = the verbatim function without splits)
+            env32, pre32 = _forward_ibp_trace_mlp(m32, spec)
+            hist = []
+            ref_alpha_only_loop(m32, spec, wl.C, pre32, env32, a0, steps=20, lr=0.1, reduce="mean", history=hist)
+            out["c3_hist_lower"] = torch.stack(hist)
     # c4, alpha-only loop on the first 32 split subdomains
     wl = W.make_workload("c4")
     m32 = ref_module(wl)
@@ -544,8 +556,11 @@ def gen_adam_divergence() -> None:
         env, pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=split_state)
         a0 = {k: cast(v) for k, v in a0_32.items()}
         for k in (1, 2, 5, 10):
-            bl, _bu, _ba = ref_alpha_only_loop(m, spec, cast(C), pre, env, a0, steps=k, lr=0.1, reduce="mean")
+            hist = [] if (tag == "f32" and k == 10) else None
+            bl, _bu, _ba = ref_alpha_only_loop(m, spec, cast(C), pre, env, a0, steps=k, lr=0.1, reduce="mean", history=hist)
             out[f"c4_{tag}_lower_{k}"] = bl
+            if hist is not None:
+                out["c4_hist_lower"] = torch.stack(hist)
     save("adam_divergence.npz", **out)
 
 
