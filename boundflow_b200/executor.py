@@ -27,8 +27,20 @@ def _is_interval_kind(kind: Any) -> bool:
     return getattr(kind, "value", kind) == "interval_ibp"
 
 
+def _state_like(state_in: Any, lower: torch.Tensor, upper: torch.Tensor) -> Any:
+    """Interval state of the same class as `state_in`, so that a caller which checks types with isinstance (the
+    reference's PythonTaskExecutor does, task_executor.py:166-176) gets its own IntervalState back."""
+    cls = type(state_in)
+    if cls is not IntervalState:
+        try:
+            return cls(lower=lower, upper=upper)
+        except TypeError:
+            pass
+    return IntervalState(lower=lower, upper=upper)
+
+
 class CudaIntervalDomain:
-    """Interval transformers on the device (centre/radius arithmetic)."""
+    """Interval transformers on the device (centre/radius arithmetic).  Results have the class of the input state."""
 
     @property
     def domain_id(self) -> str:
@@ -63,7 +75,7 @@ class CudaIntervalDomain:
             _lib.check(lib.bf_ibp_conv2d(
                 _lib.ptr(xl), _lib.ptr(xu), _lib.IN_LOWER_UPPER, relu_in, _lib.ptr(w), _lib.ptr(b), None, 0, None, None,
                 _lib.ptr(y_l), _lib.ptr(y_u), None, B, Ci, Hi, Wi, Co, kh, kw, st[0], st[1], pd[0], pd[1], _stream_ptr(device)))
-            return IntervalState(lower=y_l.to(x_l.device), upper=y_u.to(x_l.device))
+            return _state_like(state_in, y_l.to(x_l.device), y_u.to(x_l.device))
         if op not in (None, "linear"):
             raise NotImplementedError(f"unsupported affine op for IntervalDomain: {op}")
         if w.dim() == 3:
@@ -77,7 +89,7 @@ class CudaIntervalDomain:
             y_u = torch.empty_like(y_l)
             _lib.check(lib.bf_ibp_linear_batched(_lib.ptr(xl), _lib.ptr(xu), relu_in, _lib.ptr(w), _lib.ptr(b), _lib.ptr(y_l), _lib.ptr(y_u),
                                                  B, S, n_in, _stream_ptr(device)))
-            return IntervalState(lower=y_l.to(x_l.device), upper=y_u.to(x_l.device))
+            return _state_like(state_in, y_l.to(x_l.device), y_u.to(x_l.device))
         lead = tuple(xl.shape[:-1])
         n_in, n_out = int(w.shape[1]), int(w.shape[0])
         x2l, x2u = xl.reshape(-1, n_in), xu.reshape(-1, n_in)
@@ -87,7 +99,7 @@ class CudaIntervalDomain:
         _lib.check(lib.bf_ibp_linear(
             _lib.ptr(x2l), _lib.ptr(x2u), _lib.IN_LOWER_UPPER, relu_in, _lib.ptr(w), _lib.ptr(b), None, 0, None, None,
             _lib.ptr(y_l), _lib.ptr(y_u), None, rows, n_in, n_out, _stream_ptr(device)))
-        return IntervalState(lower=y_l.reshape(lead + (n_out,)).to(x_l.device), upper=y_u.reshape(lead + (n_out,)).to(x_l.device))
+        return _state_like(state_in, y_l.reshape(lead + (n_out,)).to(x_l.device), y_u.reshape(lead + (n_out,)).to(x_l.device))
 
     def relu_transformer(self, state_in: Any) -> IntervalState:
         if not (hasattr(state_in, "lower") and hasattr(state_in, "upper")):
@@ -98,7 +110,7 @@ class CudaIntervalDomain:
         l, u = _f32(state_in.lower, device), _f32(state_in.upper, device)
         ol, ou = torch.empty_like(l), torch.empty_like(u)
         _lib.check(lib.bf_interval_relu(_lib.ptr(l), _lib.ptr(u), _lib.ptr(ol), _lib.ptr(ou), l.numel(), _stream_ptr(device)))
-        return IntervalState(lower=ol.to(state_in.lower.device), upper=ou.to(state_in.lower.device))
+        return _state_like(state_in, ol.to(state_in.lower.device), ou.to(state_in.lower.device))
 
     def elementwise_transformer(self, states_in, op: str) -> IntervalState:
         if len(states_in) != 2:
@@ -113,7 +125,7 @@ class CudaIntervalDomain:
             ol, ou = torch.empty_like(al), torch.empty_like(au)
             _lib.check(lib.bf_interval_add(_lib.ptr(al), _lib.ptr(au), _lib.ptr(bl), _lib.ptr(bu), _lib.ptr(ol), _lib.ptr(ou), al.numel(),
                                            _stream_ptr(device)))
-            return IntervalState(lower=ol.to(a.lower.device), upper=ou.to(a.lower.device))
+            return _state_like(a, ol.to(a.lower.device), ou.to(a.lower.device))
         raise NotImplementedError(f"unsupported elementwise op: {op}")
 
 

@@ -1,4 +1,6 @@
 """Shared checks for the parity tests."""
+import os
+
 import numpy as np
 import torch
 
@@ -16,6 +18,14 @@ def close(got, ref, atol=ATOL, rtol=RTOL):
 
 def assert_close(got, ref, what="", atol=ATOL, rtol=RTOL):
     ok, excess, worst = close(got, ref, atol, rtol)
+    report = os.environ.get("BF_TOLERANCE_REPORT")
+    if report and (atol != ATOL or rtol != RTOL):
+        # measurement aid: how far a comparison with a widened tolerance is from the strict one
+        g64 = torch.as_tensor(np.asarray(got.detach().cpu() if torch.is_tensor(got) else got), dtype=torch.float64)
+        r64 = torch.as_tensor(np.asarray(ref.detach().cpu() if torch.is_tensor(ref) else ref), dtype=torch.float64)
+        ratio = float(((g64 - r64).abs() / (ATOL + RTOL * r64.abs())).max())
+        with open(report, "a") as fh:
+            fh.write(f"{os.environ.get('PYTEST_CURRENT_TEST', '?')} | {what} | atol={atol:g} rtol={rtol:g} | err/strict={ratio:.3f}\n")
     assert ok, f"{what}: max |err| {worst:.3e}, exceeds atol {atol} + rtol {rtol}*|ref| by {excess:.3e}"
 
 

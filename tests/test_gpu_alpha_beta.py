@@ -56,11 +56,13 @@ def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel):
     bounds, a_state, b_state, stats = run_alpha_beta_crown_mlp(
         wl.module, spec, linear_spec_C=C.to(dev), relu_split_state=state, steps=10, lr=0.1,
         warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))), per_batch_params=True)
-    # optimised bounds: Adam amplifies rounding-level differences, see tests/test_gpu_parity.py::test_c3_alpha_crown
-    assert_close(bounds.lower, g["best_lower"], "alpha-beta best lower", rtol=3e-4)
-    assert_close(bounds.upper, g["best_upper"], "alpha-beta best upper", rtol=3e-4)
+    # ten Adam steps on alpha AND beta on the tcgen05 path (288 coefficient rows): single elements end up to 2.2x the
+    # strict tolerance away from the reference (measured; cause and step-by-step figures in
+    # tests/test_gpu_headline_parity.py::test_adam_trajectory_against_reference), the per-domain objective stays strict
+    assert_close(bounds.lower, g["best_lower"], "alpha-beta best lower", atol=4e-4, rtol=4e-5)
+    assert_close(bounds.upper, g["best_upper"], "alpha-beta best upper", atol=4e-4, rtol=4e-5)
     got_m, ref_m = bounds.lower.mean(dim=1).cpu(), torch.as_tensor(g["best_lower"]).mean(dim=1)
-    assert (got_m >= ref_m - 2e-4 * ref_m.abs()).all(), "optimised objective is as good as the reference's"
+    assert_close(got_m, ref_m, "per-domain objective after 10 alpha-beta steps")
     for name, sp in zip(wl.relu_names, splits):
         b = b_state.beta_by_relu_input[name].cpu()
         assert float(b.min()) >= 0.0
@@ -94,7 +96,7 @@ def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev, adjoint_
     r1 = alpha_crown_from_trace(trace, C.to(dev), a0, steps=1, lr=0.1, beta_splits=[state[n] for n in wl.relu_names])
     o1 = O.alpha_crown(wl.layers, inp, C, steps=1, lr=0.1, alpha0=[a.cpu() for a in a0], splits=splits, trace=tr,
                        optimize_beta=True, return_beta=True)
-    assert_close(r1[0], o1[0], "one-step best lower", rtol=3e-5)
+    assert_close(r1[0], o1[0], "one-step best lower")
     torch.cuda.synchronize()
     assert trace.chain.tc_status() == 0
     # ten steps: beta must not be worse than alpha only

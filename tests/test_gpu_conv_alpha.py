@@ -27,7 +27,7 @@ def test_c2_matches_reference_golden(dev, golden):
     spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
     trace = ibp_trace(wl.module, spec)
     warm = AlphaState(dict(zip(wl.relu_names, adaptive_alpha_from_trace(trace))))
-    for steps, rtol in ((1, 3e-5), (6, 3e-4)):
+    for steps, rtol in ((1, 1e-5), (6, 1e-5)):
         b, a, _b, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=steps, lr=0.1, warm_start_alpha=warm,
                                                per_batch_params=True)
         assert_close(b.lower, g[f"per_domain_lower_{steps}"], f"per-domain lower after {steps}", rtol=rtol)
@@ -54,7 +54,7 @@ def test_conv_gradient_against_oracle_autograd(dev):
     inp = O.box_input(wl.lo, wl.up)
     otrace = O.forward_ibp_trace(wl.layers, inp)
     ref_grads, ref_lower = O.alpha_gradient(wl.layers, inp, otrace, wl.C, [a.cpu() for a in alphas])
-    assert_close(lower, ref_lower, "lower at alpha = 0.35", rtol=3e-5)
+    assert_close(lower, ref_lower, "lower at alpha = 0.35")
     for r, (gg, rg) in enumerate(zip(grads, ref_grads)):
         scale = float(rg.abs().max()) + 1e-12
         assert float((gg.cpu() - rg.reshape(3, -1)).abs().max()) <= 2e-4 * scale + 1e-6, f"gradient of ReLU {r}"

@@ -353,17 +353,15 @@ def test_c3_alpha_crown(dev, golden):
         ref = g[f"grad0_{name}"]
         scale = float(np.abs(ref).max())
         assert_close(grads[r], ref, f"grad0 {name}", atol=2e-5 * scale, rtol=1e-4)
-    # whole optimisation through the reference-shaped entry point.  20 Adam steps amplify
-    # rounding-level differences (Adam turns even 1e-7-sized gradients into +-lr moves and a
-    # moved alpha flips coefficient signs), so optimised bounds agree to ~1e-4 relative
-    # between any two fp32 implementations; single evaluations above are held to 1e-5.
+    # whole optimisation through the reference-shaped entry point: 20 Adam steps stay on the reference's own
+    # trajectory (measured 0.05 of the strict tolerance; tests/test_gpu_headline_parity.py has the step-by-step figures)
     bounds, a_state, _b, stats = run_alpha_beta_crown_mlp(
         wl.module, spec, linear_spec_C=C, steps=20, lr=0.1, warm_start_alpha=AlphaState(dict(zip(names, a0))), per_batch_params=True)
-    assert_close(bounds.lower, g["best_lower"], "alpha best lower", rtol=3e-4)
-    assert_close(bounds.upper, g["best_upper"], "alpha best upper", rtol=3e-4)
+    assert_close(bounds.lower, g["best_lower"], "alpha best lower")
+    assert_close(bounds.upper, g["best_upper"], "alpha best upper")
     assert (bounds.lower.mean(dim=1) >= lo0.mean(dim=1) - 1e-3).all(), "best-of must not be worse than step 0"
     got_m, ref_m = bounds.lower.mean(dim=1).cpu(), torch.as_tensor(g["best_lower"]).mean(dim=1)
-    assert (got_m >= ref_m - 2e-4 * ref_m.abs()).all(), "optimised objective is as good as the reference's"
+    assert (got_m >= ref_m - 1e-5 * ref_m.abs() - 1e-4).all(), "optimised objective is as good as the reference's"
     for name in names:
         a = a_state.alpha_by_relu_input[name]
         assert float(a.min()) >= 0.0 and float(a.max()) <= 1.0
@@ -373,7 +371,12 @@ def test_c3_alpha_crown(dev, golden):
     assert_close(up_chk, bounds.upper, "upper at best alpha")
     s_bounds, _, _, _ = run_alpha_beta_crown_mlp(
         wl.module, spec, linear_spec_C=C, steps=20, lr=0.1, warm_start_alpha=AlphaState(dict(zip(names, a0))), per_batch_params=True, spec_reduce="sum")
-    assert_close(s_bounds.lower, g["sum_best_lower"], "alpha(sum) best lower", rtol=3e-4)
+    # sum objective: every gradient is 9x larger relative to Adam's eps = 1e-8, so alpha entries whose exact gradient is
+    # zero move by almost +-lr with the sign of their rounding residue; any two implementations that order their
+    # operations differently separate (the CPU restatement and the reference's primitives by 5.5e-5 after 20 steps,
+    # this kernel path by 5.0e-5): compared at 1e-4 relative, and strictly on the objective
+    assert_close(s_bounds.lower, g["sum_best_lower"], "alpha(sum) best lower", rtol=1e-4)
+    assert_close(s_bounds.lower.sum(dim=1), torch.as_tensor(g["sum_best_lower"]).sum(dim=1), "alpha(sum) objective")
 
 
 def test_c4_split_domains(dev, golden):
@@ -400,9 +403,16 @@ def test_c4_split_domains(dev, golden):
     a0 = _alpha0(trace)
     lo0, _ = crown_from_trace(trace, C, relu_alpha=dict(zip(wl.relu_names, a0)), sides=(0,))
     assert_close(lo0, g["step0_lower"], "step0 lower")
+    from boundflow_b200 import _lib
+
+    tc0 = _lib.tc_launch_count()
     best_l, best_u, best_a, _, _ = alpha_crown_from_trace(trace, C, a0, steps=10, lr=0.1)
-    assert_close(best_l, g["best_lower"], "best lower", rtol=3e-4)
-    assert_close(best_u, g["best_upper"], "best upper", rtol=3e-4)
+    assert _lib.tc_launch_count() > tc0, "288 coefficient rows must run on the tensor-core kernels"
+    # ten Adam steps on the tcgen05 path: single elements drift to 1.4x the strict tolerance (the per-domain objective
+    # stays strict); measurement and cause in tests/test_gpu_headline_parity.py::test_adam_trajectory_against_reference
+    assert_close(best_l, g["best_lower"], "best lower", atol=3e-4, rtol=3e-5)
+    assert_close(best_u, g["best_upper"], "best upper", atol=3e-4, rtol=3e-5)
+    assert_close(best_l.mean(dim=1), torch.as_tensor(g["best_lower"]).mean(dim=1), "per-domain objective")
     assert (best_l.mean(dim=1) >= lo0.mean(dim=1) - 1e-2).all()
 
 
@@ -521,5 +531,5 @@ def test_c4_full_batch_properties(dev):
     inp = O.box_input(wl.lo.expand(4, -1).contiguous(), wl.up.expand(4, -1).contiguous())
     tr = O.forward_ibp_trace(wl.layers, inp, splits=[s[sel] for s in splits])
     lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, wl.C.expand(4, -1, -1), alpha=[a[sel.to(dev)].cpu() for a in best_a])
-    assert_close(best_l[sel.to(dev)], lo_ref, "oracle at returned alpha (lower)", rtol=3e-5)
-    assert_close(best_u[sel.to(dev)], up_ref, "oracle at returned alpha (upper)", rtol=3e-5)
+    assert_close(best_l[sel.to(dev)], lo_ref, "oracle at returned alpha (lower)")
+    assert_close(best_u[sel.to(dev)], up_ref, "oracle at returned alpha (upper)")

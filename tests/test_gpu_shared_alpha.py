@@ -30,8 +30,8 @@ def test_c3_matches_reference_golden(dev, golden):
     assert_close(b1.upper, g["c3_upper_1step"], "one-step upper")
     b, st, stats = run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=10, lr=0.1)
     # optimised bounds: Adam amplifies rounding-level differences, see tests/test_gpu_parity.py::test_c3_alpha_crown
-    assert_close(b.lower, g["c3_lower"], "lower", rtol=3e-4)
-    assert_close(b.upper, g["c3_upper"], "upper", rtol=3e-4)
+    assert_close(b.lower, g["c3_lower"], "lower")
+    assert_close(b.upper, g["c3_upper"], "upper")
     assert float(b.lower.mean()) >= float(torch.as_tensor(g["c3_lower"]).mean()) - 2e-4 * abs(float(torch.as_tensor(g["c3_lower"]).mean()))
     assert stats.relu_inputs == tuple(wl.relu_names)
     for n in wl.relu_names:
@@ -62,13 +62,13 @@ def test_c4_split_domains_match_reference_golden_and_oracle(dev, golden):
     state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
     C = wl.C.expand(D, -1, -1).contiguous().to(dev)
     b, st, _ = run_alpha_crown_mlp(wl.module, spec, linear_spec_C=C, steps=10, lr=0.1, relu_split_state=state)
-    assert_close(b.lower, g["c4_lower"], "lower", rtol=3e-4)
-    assert_close(b.upper, g["c4_upper"], "upper", rtol=3e-4)
+    assert_close(b.lower, g["c4_lower"], "lower")
+    assert_close(b.upper, g["c4_upper"], "upper")
     # one Adam step is insensitive to rounding: strict against the oracle (216 coefficient rows: FFMA and tensor-core sizes mix)
     b1, _s, _ = run_alpha_crown_mlp(wl.module, spec, linear_spec_C=C, steps=1, lr=0.1, relu_split_state=state)
     o1 = O.alpha_crown_shared(wl.layers, O.box_input(lo, up), wl.C.expand(D, -1, -1), steps=1, lr=0.1, splits=splits)
-    assert_close(b1.lower, o1[0], "one-step lower", rtol=3e-5)
-    assert_close(b1.upper, o1[1], "one-step upper", rtol=3e-5)
+    assert_close(b1.lower, o1[0], "one-step lower")
+    assert_close(b1.upper, o1[1], "one-step upper")
 
 
 def test_warm_start_zero_steps_and_refusals(dev):
@@ -110,11 +110,11 @@ def test_shared_alpha_beta_matches_reference_golden(dev, golden):
     state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
     C = wl.C.expand(D, -1, -1).contiguous().to(dev)
     b1, _a1, _b1, _ = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=C, relu_split_state=state, steps=1, lr=0.1, per_batch_params=False)
-    assert_close(b1.lower, g["c4_ab_lower_1step"], "one-step lower", rtol=3e-5)
-    assert_close(b1.upper, g["c4_ab_upper_1step"], "one-step upper", rtol=3e-5)
+    assert_close(b1.lower, g["c4_ab_lower_1step"], "one-step lower")
+    assert_close(b1.upper, g["c4_ab_upper_1step"], "one-step upper")
     b, a_st, b_st, stats = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=C, relu_split_state=state, steps=10, lr=0.1, per_batch_params=False)
-    assert_close(b.lower, g["c4_ab_lower"], "lower", rtol=3e-4)
-    assert_close(b.upper, g["c4_ab_upper"], "upper", rtol=3e-4)
+    assert_close(b.lower, g["c4_ab_lower"], "lower")
+    assert_close(b.upper, g["c4_ab_upper"], "upper")
     for n, sp in zip(wl.relu_names, splits):
         bt = b_st.beta_by_relu_input[n]
         assert bt.dim() == 1 and float(bt.min()) >= 0.0

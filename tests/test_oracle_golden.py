@@ -67,12 +67,12 @@ def test_c3_alpha(golden):
     assert_close(bl, g["best_lower"], "alpha best lower")
     assert_close(bu, g["best_upper"], "alpha best upper")
     sl, su, _, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=20, lr=0.1, alpha0=a0, spec_reduce="sum")
-    # 20 Adam steps amplify rounding-level differences (Adam normalises even
-    # 1e-7-sized gradients to +-lr steps, and a moved alpha flips coefficient
-    # signs downstream), so two fp32 runs that differ only in summation order
-    # agree to ~1e-4 relative, not 1e-5; the optimised bound is compared at
-    # that looser tolerance, single evaluations at the strict one.
-    assert_close(sl, g["sum_best_lower"], "alpha(sum) best lower", rtol=3e-4)
+    # The mean-objective runs above follow the reference's trajectory to 1e-7.  With the sum objective every
+    # gradient is 9x larger relative to Adam's eps = 1e-8: alpha entries whose exact gradient is zero carry a
+    # rounding residue r and move by lr * r / (|r| + 1e-8), i.e. by almost +-lr once |r| is 9x larger, with the
+    # sign of the residue -- which depends on the order of operations.  Measured distance between this
+    # restatement and the reference's primitives after 20 such steps: 5.5e-5 relative.
+    assert_close(sl, g["sum_best_lower"], "alpha(sum) best lower", rtol=1e-4)
     assert (bl.mean(dim=1) >= lo0.mean(dim=1) - 1e-6).all()
 
 
@@ -81,7 +81,7 @@ def test_c4_split_alpha(golden):
     wl = W.make_workload("c4")
     _check_inputs(wl, g)
     root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
-    D = 24
+    D = 32
     splits = W.make_split_domains(wl, root.pre, n_domains=D)
     chk = np.array([int(s.to(torch.int64).sum()) for s in splits] + [int(s.to(torch.int64).abs().sum()) for s in splits])
     assert (chk == g["split_checksum"]).all()
@@ -174,11 +174,11 @@ def test_fused_region_reference_vectors(golden):
 
 def test_c4_alpha_beta_and_branch_choices(golden):
     """The verbatim reference function `run_alpha_beta_crown_mlp` (alpha and beta optimised,
-    per-domain parameters) and its widest-gap branching hint on 24 split subdomains."""
+    per-domain parameters) and its widest-gap branching hint on 32 split subdomains."""
     g = golden("c4_split_alpha_beta.npz")
     wl = W.make_workload("c4")
     root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
-    D = 24
+    D = 32
     splits = W.make_split_domains(wl, root.pre, n_domains=D)
     inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
     C = wl.C.expand(D, -1, -1).contiguous()
@@ -224,8 +224,8 @@ def test_shared_alpha(golden):
     assert_close(up1, g["c3_upper_1step"], "c3 one-step upper")
     lo, up, a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=10, lr=0.1)
     # the optimised trajectory amplifies rounding (see test_c3_alpha): relative tolerance 3e-4
-    assert_close(lo, g["c3_lower"], "c3 lower", rtol=3e-4)
-    assert_close(up, g["c3_upper"], "c3 upper", rtol=3e-4)
+    assert_close(lo, g["c3_lower"], "c3 lower")
+    assert_close(up, g["c3_upper"], "c3 upper")
     for r, n in enumerate(wl.relu_names):
         assert float((a[r] - torch.as_tensor(g[f"c3_alpha_{n}"]).reshape(-1)).abs().mean()) < 2e-3
 
@@ -236,8 +236,8 @@ def test_shared_alpha(golden):
     assert (np.array([int(s.to(torch.int64).abs().sum()) for s in splits]) == g["c4_split_checksum"]).all()
     inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
     lo, up, a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C.expand(D, -1, -1), steps=10, lr=0.1, splits=splits)
-    assert_close(lo, g["c4_lower"], "c4 lower", rtol=3e-4)
-    assert_close(up, g["c4_upper"], "c4 upper", rtol=3e-4)
+    assert_close(lo, g["c4_lower"], "c4 lower")
+    assert_close(up, g["c4_upper"], "c4 upper")
 
 
 def test_shared_alpha_beta(golden):
@@ -250,11 +250,11 @@ def test_shared_alpha_beta(golden):
     inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
     C = wl.C.expand(D, -1, -1)
     lo1, up1, _a, _b, _ = O.alpha_crown_shared(wl.layers, inp, C, steps=1, lr=0.1, splits=splits, optimize_beta=True)
-    assert_close(lo1, g["c4_ab_lower_1step"], "one-step lower", rtol=3e-5)
-    assert_close(up1, g["c4_ab_upper_1step"], "one-step upper", rtol=3e-5)
+    assert_close(lo1, g["c4_ab_lower_1step"], "one-step lower")
+    assert_close(up1, g["c4_ab_upper_1step"], "one-step upper")
     lo, up, a, b, _ = O.alpha_crown_shared(wl.layers, inp, C, steps=10, lr=0.1, splits=splits, optimize_beta=True)
-    assert_close(lo, g["c4_ab_lower"], "lower", rtol=3e-4)
-    assert_close(up, g["c4_ab_upper"], "upper", rtol=3e-4)
+    assert_close(lo, g["c4_ab_lower"], "lower")
+    assert_close(up, g["c4_ab_upper"], "upper")
     for r, n in enumerate(wl.relu_names):
         ref_b = torch.as_tensor(g[f"c4_ab_beta_{n}"]).reshape(-1)
         assert float(b[r].min()) >= 0.0
@@ -316,11 +316,11 @@ def test_alpha_crown_on_lp_balls(golden):
         trace = O.forward_ibp_trace(wl.layers, inp)
         a0 = O.adaptive_alpha_init(trace)
         lo1, up1, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=1, lr=0.1, alpha0=a0, trace=trace)
-        assert_close(lo1, g[f"{pname}_lower_1"], f"{pname} one-step lower", rtol=3e-5)
-        assert_close(up1, g[f"{pname}_upper_1"], f"{pname} one-step upper", rtol=3e-5)
+        assert_close(lo1, g[f"{pname}_lower_1"], f"{pname} one-step lower")
+        assert_close(up1, g[f"{pname}_upper_1"], f"{pname} one-step upper")
         lo, up, _a, _ = O.alpha_crown(wl.layers, inp, wl.C, steps=10, lr=0.1, alpha0=a0, trace=trace)
-        assert_close(lo, g[f"{pname}_lower_10"], f"{pname} lower", rtol=3e-4)
-        assert_close(up, g[f"{pname}_upper_10"], f"{pname} upper", rtol=3e-4)
+        assert_close(lo, g[f"{pname}_lower_10"], f"{pname} lower")
+        assert_close(up, g[f"{pname}_upper_10"], f"{pname} upper")
 
 
 def test_alpha_crown_on_a_conv_chain(golden):
