@@ -233,6 +233,7 @@ void refresh_switches(const bf_chain* c) {
   c->sw.force_ffma = env_is_one("BF_B200_FORCE_FFMA");
   c->sw.adjoint_kernel = env_is_one("BF_B200_ADJ_ROWMAJOR") ? 1 : (env_is_one("BF_B200_ADJ_FEATURE_MAJOR") ? 2 : 0);
   c->sw.no_windows = getenv("BF_B200_NO_WINDOWS") != nullptr;
+  c->sw.persistent_bwd = env_is_one("BF_B200_BWD_PERSISTENT");
 }
 
 bool tc_may_run(const bf_chain* c, int M) { return c->status != nullptr && !c->pk_bwd.empty() && !c->sw.force_ffma && M >= 256; }
@@ -259,6 +260,11 @@ int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos
   const bf_layer_desc& L = c->layers[layer];
   const int K = L.n_out, N = L.n_in;
   const unsigned char* pk = tc_weights(c, layer, false, M, K, N);
+  if (pk && c->sw.persistent_bwd && crown_tc_persistent_supports(epos, eneg, add)) {
+    if (ptiles) *ptiles = crown_tc_persist_partial_tiles(M, N, K);
+    return launch_crown_bwd_linear_tc_persistent(A, dpos, dneg, epos, eneg, add, pk, L.bias, A_prev, delta, accumulate, mid, rad,
+                                                 partial, side, M, S, K, N, c->status, stream);
+  }
   if (pk) {
     if (ptiles) *ptiles = crown_tc_partial_tiles(N, K);
     return launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, add, pk, L.bias, A_prev, delta, accumulate, mid, rad, partial,
@@ -461,7 +467,7 @@ static size_t crown_ws_layout(const bf_chain* c, int B, int S, int upto, void* b
   float* b0 = cv.take<float>(M * maxw);
   float* b1 = cv.take<float>(M * maxw);
   float* cacc = cv.take<float>(M);
-  float* partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
+  float* partial = cv.take<float>(M * (size_t)std::max(std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)), crown_tc_persist_max_partial_tiles(c->n0)));
   char* cs = cv.take<char>(conv_scratch);
   if (ws) {
     ws->buf[0] = b0; ws->buf[1] = b1; ws->cacc = cacc; ws->partial = partial; ws->conv_scratch = cs; ws->bytes = cv.off;

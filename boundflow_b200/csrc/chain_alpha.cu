@@ -64,7 +64,7 @@ static size_t alpha_ws_layout(const bf_chain* c, int B, int S, bool with_beta, v
   w.H[0] = cv.take<float>(M * (size_t)maxw);
   w.H[1] = cv.take<float>(M * (size_t)maxw);
   w.cacc = cv.take<float>(M);
-  w.partial = cv.take<float>(M * (size_t)std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)));
+  w.partial = cv.take<float>(M * (size_t)std::max(std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)), crown_tc_persist_max_partial_tiles(c->n0)));
   w.cur = cv.take<float>(M);
   w.metric = cv.take<float>((size_t)B);
   w.improve = cv.take<int>((size_t)B);

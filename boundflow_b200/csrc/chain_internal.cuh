@@ -23,6 +23,8 @@ struct bf_chain {
     bool force_ffma = false;        // BF_B200_FORCE_FFMA=1: FP32 FFMA tiles instead of the tensor-core kernels
     int adjoint_kernel = 0;         // 0 automatic, 1 row-major (BF_B200_ADJ_ROWMAJOR=1), 2 feature-major (BF_B200_ADJ_FEATURE_MAJOR=1)
     bool no_windows = false;        // BF_B200_NO_WINDOWS set: identity-row sweeps keep full feature maps
+    bool persistent_bwd = false;    // BF_B200_BWD_PERSISTENT=1: persistent warp-specialised backward kernel (128 x 256 tiles, double-buffered
+                                    // accumulators) instead of the one-tile-per-CTA kernel; measured slower on wide layers, see crown_tc_persist.cu
   };
   mutable Switches sw;
 };

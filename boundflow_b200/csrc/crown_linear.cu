@@ -2,6 +2,8 @@
 // transformer and, on the first layer, with the concretisation) and the adjoint
 // (alpha-gradient) sweep, as FP32 FFMA tiles.
 #include "gemm_ffma.cuh"
+#include <stdlib.h>
+
 #include "kernels.cuh"
 
 namespace bf {
@@ -363,8 +365,13 @@ extern "C" int bf_crown_relu_linear_bwd_packed(const float* A, int side, const f
   cudaStream_t stream = bf::as_stream(stream_);
   int* status = reinterpret_cast<int*>(const_cast<void*>(pack));
   const unsigned char* images = static_cast<const unsigned char*>(pack) + kPackHeader;
-  int rc = bf::launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta, accumulate,
-                                          nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status, stream);
+  const char* persistent = getenv("BF_B200_BWD_PERSISTENT");
+  int rc = (!(persistent && persistent[0] == '1') || !bf::crown_tc_persistent_supports(epos, eneg, relu ? add : nullptr))
+               ? bf::launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta, accumulate,
+                                                nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status, stream)
+               : bf::launch_crown_bwd_linear_tc_persistent(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta,
+                                                           accumulate, nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status,
+                                                           stream);
   if (rc != BF_OK) return rc;
   // a wait that expired inside the kernel invalidates the result: hand on NaN, never stale memory
   return bf::launch_poison_on_status(status, A_prev, M * n_prev, delta, delta ? M : 0, stream);

@@ -246,8 +246,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
           }
         }
         float4 hi, lo;
-        hi.x = tf32_rna(a.x); hi.y = tf32_rna(a.y); hi.z = tf32_rna(a.z); hi.w = tf32_rna(a.w);
-        lo.x = tf32_rna(a.x - hi.x); lo.y = tf32_rna(a.y - hi.y); lo.z = tf32_rna(a.z - hi.z); lo.w = tf32_rna(a.w - hi.w);
+        hi.x = tf32_round(a.x); hi.y = tf32_round(a.y); hi.z = tf32_round(a.z); hi.w = tf32_round(a.w);
+        lo.x = tf32_round(a.x - hi.x); lo.y = tf32_round(a.y - hi.y); lo.z = tf32_round(a.z - hi.z); lo.w = tf32_round(a.w - hi.w);
         const int rl = rg * ROWS_PER_THREAD + i;  // row inside the tile; 8-row swizzle atoms
         const int off = (rl >> 3) * 1024 + (rl & 7) * 128 + ((c ^ (rl & 7)) << 4);
         *reinterpret_cast<float4*>(a_hi + off) = hi;
@@ -477,28 +477,22 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // descriptors of stage 0; a stage (or the lo image) further on is a plain add (the 14-bit address field cannot
+      // overflow: shared-memory addresses stay below 256 KB)
+      const uint64_t a_desc0 = make_desc(smem_u32(tiles)), b_desc0 = make_desc(smem_u32(b_tiles));
       bool ok = true;
       int it = 0;
       for (int kb = 0; kb < p.nkb && ok; ++kb) {
         const int sa = kb % A_STAGES;
         if (!mbar_wait(smem_u32(&ctl->a_full[sa]), (uint32_t)(kb / A_STAGES) & 1u, abort_flag)) { ok = false; break; }
-        const uint32_t a_hi = smem_u32(tiles + (size_t)sa * 2 * A_TILE);
-        const uint32_t a_lo = a_hi + A_TILE;
+        const uint64_t dah = a_desc0 + (uint64_t)(sa * ((2 * A_TILE) >> 4));
         for (int h = 0; h < nh; ++h, ++it) {
           const int sb = it % p.b_stages;
           if (!mbar_wait(smem_u32(&ctl->b_full[sb]), (uint32_t)(it / p.b_stages) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t b_hi = smem_u32(b_tiles + (size_t)sb * b_bytes);
-          const uint32_t b_lo = b_hi + p.BN * 128;
+          const uint64_t dbh = b_desc0 + (uint64_t)(sb * (b_bytes >> 4));
           const uint32_t d_tmem = tmem_base + (uint32_t)(h * p.BN);
-#pragma unroll
-          for (int j = 0; j < BK / 8; ++j) {
-            const uint64_t dah = make_desc(a_hi + j * 32), dal = make_desc(a_lo + j * 32);
-            const uint64_t dbh = make_desc(b_hi + j * 32), dbl = make_desc(b_lo + j * 32);
-            mma_tf32(d_tmem, dal, dbh, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-            mma_tf32(d_tmem, dah, dbl, idesc, 1u);
-            mma_tf32(d_tmem, dah, dbh, idesc, 1u);
-          }
+          mma_kblock_3xtf32(d_tmem, dah, dah + (A_TILE >> 4), dbh, dbh + (uint64_t)((p.BN * 128) >> 4), idesc, kb > 0 ? 1u : 0u);
           mma_commit(smem_u32(&ctl->b_empty[sb]));  // frees the B stage when these MMAs have read it
         }
         if (ok) mma_commit(smem_u32(&ctl->a_empty[sa]));

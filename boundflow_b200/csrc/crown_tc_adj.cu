@@ -352,8 +352,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         const float4 a = a_cur[i];
         float4 hi, lo;
-        hi.x = tf32_rna(a.x); hi.y = tf32_rna(a.y); hi.z = tf32_rna(a.z); hi.w = tf32_rna(a.w);
-        lo.x = tf32_rna(a.x - hi.x); lo.y = tf32_rna(a.y - hi.y); lo.z = tf32_rna(a.z - hi.z); lo.w = tf32_rna(a.w - hi.w);
+        hi.x = tf32_round(a.x); hi.y = tf32_round(a.y); hi.z = tf32_round(a.z); hi.w = tf32_round(a.w);
+        lo.x = tf32_round(a.x - hi.x); lo.y = tf32_round(a.y - hi.y); lo.z = tf32_round(a.z - hi.z); lo.w = tf32_round(a.w - hi.w);
         const int rl = rg * ROWS_PER_THREAD + i;  // row inside the tile; 8-row swizzle atoms
         const int off = (rl >> 3) * 1024 + (rl & 7) * 128 + ((c ^ (rl & 7)) << 4);
         *reinterpret_cast<float4*>(t_hi + off) = hi;
@@ -453,28 +453,22 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
     if (lane == 0) {
       // D[features, rows] += W_tile[features, k] * H_tile[rows, k]^T: M = 128 features, N = 256 rows, both operands K-major
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(RB >> 3) << 17) | ((uint32_t)(FT >> 4) << 24);
+      // descriptors of stage 0; a stage (or the lo image) further on is a plain add (the 14-bit address field cannot
+      // overflow: shared-memory addresses stay below 256 KB)
+      const uint64_t h_desc0 = make_desc(smem_u32(tiles)), w_desc0 = make_desc(smem_u32(s_tiles));
       bool ok = true;
       int it = 0;
       for (int kb = 0; kb < p.nkb && ok; ++kb) {
         const int sp = kb % P_STAGES;
         if (!mbar_wait(smem_u32(&ctl->p_full[sp]), (uint32_t)(kb / P_STAGES) & 1u, abort_flag)) { ok = false; break; }
-        const uint32_t h_hi = smem_u32(tiles + (size_t)sp * 2 * P_TILE);
-        const uint32_t h_lo = h_hi + P_TILE;
+        const uint64_t dhh = h_desc0 + (uint64_t)(sp * ((2 * P_TILE) >> 4));
         for (int t = 0; t < nf; ++t, ++it) {
           const int ss = it % S_STAGES;
           if (!mbar_wait(smem_u32(&ctl->s_full[ss]), (uint32_t)(it / S_STAGES) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t w_hi = smem_u32(s_tiles + (size_t)ss * 2 * S_TILE);
-          const uint32_t w_lo = w_hi + S_TILE;
+          const uint64_t dwh = w_desc0 + (uint64_t)(ss * ((2 * S_TILE) >> 4));
           const uint32_t d_tmem = tmem_base + (uint32_t)(t * RB);
-#pragma unroll
-          for (int j = 0; j < BK / 8; ++j) {
-            const uint64_t dwh = make_desc(w_hi + j * 32), dwl = make_desc(w_lo + j * 32);
-            const uint64_t dhh = make_desc(h_hi + j * 32), dhl = make_desc(h_lo + j * 32);
-            mma_tf32(d_tmem, dwl, dhh, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-            mma_tf32(d_tmem, dwh, dhl, idesc, 1u);
-            mma_tf32(d_tmem, dwh, dhh, idesc, 1u);
-          }
+          mma_kblock_3xtf32(d_tmem, dwh, dwh + (S_TILE >> 4), dhh, dhh + (P_TILE >> 4), idesc, kb > 0 ? 1u : 0u);
           mma_commit(smem_u32(&ctl->s_empty[ss]));  // frees the weight stage when these MMAs have read it
         }
         if (ok) mma_commit(smem_u32(&ctl->p_empty[sp]));

@@ -28,6 +28,16 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
                                    const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
                                    int* status, cudaStream_t stream);
 int crown_tc_partial_tiles(int N, int K);
+void tc_tile_shape(int N, int K, int* BN, int* ntiles, int* nkb);
+
+// crown_tc_persist.cu (persistent, warp-specialised backward contraction; same packed weights as crown_tc.cu)
+int launch_crown_bwd_linear_tc_persistent(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
+                                          const float* add, const unsigned char* Wpk, const float* kbias, float* A_prev,
+                                          float* delta, int accumulate, const float* mid, const float* rad, float* partial,
+                                          int side, int M, int S, int K, int N, int* status, cudaStream_t stream);
+bool crown_tc_persistent_supports(const float* epos, const float* eneg, const float* add);  // else: the classic kernel
+int crown_tc_persist_partial_tiles(int M, int N, int K);  // column tiles (= partial sums per row) for this problem
+int crown_tc_persist_max_partial_tiles(int N);            // upper bound over every M (workspace sizing)
 
 // crown_tc_adj.cu (feature-major adjoint step; weights packed with tile_rows = tc_adjoint_tile_rows())
 int tc_adjoint_tile_rows();

@@ -46,6 +46,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
+// Warp-collective bounded wait: lane 0 polls the barrier, every lane receives the outcome.  The warp leaves
+// converged (the instructions that follow a wait are often .sync.aligned: tcgen05.ld, shuffles) and only one
+// thread per warp spends shared-memory bandwidth on polling.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                "r"(bytes), "r"(bar)
@@ -82,6 +91,48 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t 
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z), "r"(z), "r"(z), "r"(z)
       : "memory");
 }
+// The twelve MMAs of one 32-wide k-block of a 3xTF32 product D += A * B (four 8-wide k-slices x {a_lo*b_hi,
+// a_hi*b_lo, a_hi*b_hi}) as ONE instruction sequence.  The issuing thread's chain of dependent instructions is what
+// limits the MMA rate next to sixteen busy producer warps, so nothing is recomputed here: the caller passes the
+// descriptors of the first slice (stage base, built once per stage with plain adds on a base descriptor) and each
+// further slice is 32 bytes = 2 descriptor units on; one predicate says whether the very first MMA accumulates.
+__device__ __forceinline__ void mma_kblock_3xtf32(uint32_t tmem_d, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
+                                                  uint32_t idesc, uint32_t accumulate_first) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pacc, pone;\n\t"
+      ".reg .b64 ah, al, bh, bl;\n\t"
+      "setp.ne.b32 pacc, %6, 0;\n\t"
+      "setp.eq.b32 pone, %7, %7;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, {%7, %7, %7, %7}, pacc;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 2;\n\t"
+      "add.u64 al, %2, 2;\n\t"
+      "add.u64 bh, %3, 2;\n\t"
+      "add.u64 bl, %4, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 4;\n\t"
+      "add.u64 al, %2, 4;\n\t"
+      "add.u64 bh, %3, 4;\n\t"
+      "add.u64 bl, %4, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 6;\n\t"
+      "add.u64 al, %2, 6;\n\t"
+      "add.u64 bh, %3, 6;\n\t"
+      "add.u64 bl, %4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7}, pone;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate_first), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -114,6 +165,10 @@ __device__ __forceinline__ float tf32_rna(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
 }
+// x rounded to TF32 precision (10 explicit mantissa bits), to nearest with ties away from zero -- what
+// cvt.rna.tf32.f32 computes for finite values -- by two integer operations; the producers need eight roundings
+// per loaded float4 and the conversion instruction runs on a slower pipe than the integer ALU.
+__device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ float sgnf(float a) { return (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f); }
 
 }  // namespace tc

@@ -170,3 +170,58 @@ def test_tc_is_deterministic(dev, adjoint):
     assert torch.equal(r1[0], r2[0]) and torch.equal(r1[1], r2[1])
     for a, b in zip(r1[2], r2[2]):
         assert torch.equal(a, b)
+
+
+def test_persistent_backward_kernel_matches_oracle(dev):
+    """The opt-in persistent warp-specialised backward kernel (double-buffered accumulators in tensor memory,
+    narrower tiles when few row blocks exist) on a problem with several tiles per CTA and on ragged small ones."""
+    import os
+
+    from boundflow_b200 import _lib
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, crown_from_trace, ibp_trace
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    os.environ["BF_B200_BWD_PERSISTENT"] = "1"
+    try:
+        for name, batch in (("c3", 40), ("c1", 64)):   # 360 and 576 rows: narrow tiles, partial row blocks
+            wl = W.make_workload(name, batch=batch)
+            trace = ibp_trace(wl.module, _spec(wl, dev))
+            a0 = adaptive_alpha_from_trace(trace)
+            t0 = _lib.tc_launch_count()
+            lo, up = crown_from_trace(trace, wl.C.to(dev), relu_alpha=dict(zip(trace.chain.relu_input_names, a0)))
+            assert _lib.tc_launch_count() > t0
+            inp = O.box_input(wl.lo, wl.up)
+            tr = O.forward_ibp_trace(wl.layers, inp)
+            lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, wl.C, alpha=[a.cpu() for a in a0])
+            assert_close(lo, lo_ref, f"{name} lower")
+            assert_close(up, up_ref, f"{name} upper")
+        # c4 at 4096 subdomains: 288 row blocks x 2 column tiles on 148 SMs -> four tiles per CTA, both accumulator buffers reused
+        wl = W.make_workload("c4")
+        D = 4096
+        root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+        g = torch.Generator("cpu").manual_seed(11)
+        splits = []
+        for r, (l, u) in enumerate(root.pre):
+            idx = torch.nonzero(((l < 0) & (u > 0)).reshape(-1)).flatten()
+            s8 = torch.zeros(D, l.shape[1], dtype=torch.int8)
+            pick = idx[torch.randint(0, len(idx), (D, 3), generator=g)]
+            s8.scatter_(1, pick, (torch.randint(0, 2, (D, 3), generator=g) * 2 - 1).to(torch.int8))
+            splits.append(s8)
+        lo_b, up_b = wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous()
+        spec = InputSpec.box(value_name="input", lower=lo_b.to(dev), upper=up_b.to(dev))
+        trace = ibp_trace(wl.module, spec, relu_split_state={n: s.to(dev) for n, s in zip(wl.relu_names, splits)})
+        a0 = adaptive_alpha_from_trace(trace)
+        C = wl.C.expand(D, -1, -1).contiguous()
+        best_l, best_u, best_a, _, _ = alpha_crown_from_trace(trace, C.to(dev), a0, steps=2, lr=0.1)
+        torch.cuda.synchronize()
+        assert trace.chain.tc_status() == 0
+        sel = torch.nonzero((trace.infeasible == 0).cpu()).flatten()[::257][:16]
+        inp = O.box_input(lo_b[sel], up_b[sel])
+        tr = O.forward_ibp_trace(wl.layers, inp, splits=[s[sel] for s in splits])
+        lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, C[sel], alpha=[a[sel.to(dev)].cpu() for a in best_a])
+        assert_close(best_l[sel.to(dev)], lo_ref, "c4 lower at the returned alpha")
+        assert_close(best_u[sel.to(dev)], up_ref, "c4 upper at the returned alpha")
+    finally:
+        os.environ.pop("BF_B200_BWD_PERSISTENT", None)
