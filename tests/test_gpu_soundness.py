@@ -1,0 +1,181 @@
+"""Soundness by sampling: every bound of every configuration holds on 10^4 points per input set.
+
+The sampler is test infrastructure: plain torch forward passes in float64 on the GPU of the same seeded networks
+(`workloads.py`), nothing of the library under test.  A bound is violated when a sampled output leaves
+[lower, upper] by more than the parity tolerance 1e-4 + 1e-5 |bound| (the bounds are fp32 results).
+
+  c1  IBP and CROWN, all 64 inputs
+  c2  CROWN with CROWN intermediate bounds, 8 inputs
+  c3  alpha-CROWN (20 Adam steps), 8 inputs
+  c4  alpha-CROWN (10 steps) on 8 ReLU-split subdomains; only samples that satisfy the split constraints count
+      (the number of survivors is reported and must reach 10^3 per subdomain)
+  c5  CROWN with full CROWN intermediate bounds, 8 inputs
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+N_SAMPLES = 10_000
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from boundflow_b200.csrc import build
+
+    build.build()
+    return torch.device("cuda", 0)
+
+
+def _layers64(layers, dev):
+    return [{k: (v.to(device=dev, dtype=torch.float64) if torch.is_tensor(v) else v) for k, v in layer.items()} for layer in layers]
+
+
+def _forward(layers, x, record_pre=False):
+    """Concrete forward pass of a chain (float64); optionally returns the inputs of every ReLU."""
+    import torch.nn.functional as F
+
+    pre = []
+    for layer in layers:
+        op = layer["op"]
+        if op == "linear":
+            x = x.matmul(layer["W"].t())
+            if layer.get("b") is not None:
+                x = x + layer["b"]
+        elif op == "conv2d":
+            x = F.conv2d(x, layer["W"], layer.get("b"), layer["stride"], layer["padding"])
+        elif op == "relu":
+            if record_pre:
+                pre.append(x.flatten(1))
+            x = torch.relu(x)
+        elif op == "flatten":
+            x = x.flatten(1)
+        else:
+            raise NotImplementedError(op)
+    return (x, pre) if record_pre else x
+
+
+def _worst_violation(layers, lo, up, C, lower, upper, dev, n=N_SAMPLES, seed=0, chunk=2500):
+    """max over inputs, samples and spec rows of (lower - y) and (y - upper), each divided by the tolerance of that bound."""
+    L = _layers64(layers, dev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    worst = 0.0
+    for b in range(lo.shape[0]):
+        lo_b, up_b = lo[b].to(dev, torch.float64), up[b].to(dev, torch.float64)
+        Cb = C[b].to(dev, torch.float64)
+        lb, ub = lower[b].to(dev, torch.float64), upper[b].to(dev, torch.float64)
+        tol_l, tol_u = 1e-4 + 1e-5 * lb.abs(), 1e-4 + 1e-5 * ub.abs()
+        for s in range(0, n, chunk):
+            m = min(chunk, n - s)
+            r = torch.rand((m,) + tuple(lo_b.shape), generator=g, device=dev, dtype=torch.float64)
+            if s == 0:
+                r[0] = 0.0   # the corners lo and up themselves
+                r[1] = 1.0
+            y = _forward(L, lo_b + r * (up_b - lo_b)).matmul(Cb.t())   # [m, S]
+            worst = max(worst, float(((lb - y) / tol_l).max()), float(((y - ub) / tol_u).max()))
+    return worst
+
+
+def test_c1_ibp_and_crown_sound_on_all_inputs(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import InputSpec
+
+    wl = W.make_workload("c1")
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    got = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev))
+    w = _worst_violation(wl.layers, wl.lo, wl.up, wl.C, got.lower, got.upper, dev, seed=1)
+    print(f"c1 CROWN: worst violation / tolerance = {w:.3f}")
+    assert w <= 1.0
+    ibp = CudaTaskExecutor().run_ibp(wl.module, spec)
+    eye = torch.eye(10).unsqueeze(0).expand(wl.x.shape[0], -1, -1)
+    w = _worst_violation(wl.layers, wl.lo, wl.up, eye, ibp.lower, ibp.upper, dev, seed=2)
+    print(f"c1 IBP: worst violation / tolerance = {w:.3f}")
+    assert w <= 1.0
+
+
+@pytest.mark.parametrize("name", ["c2", "c5"])
+def test_cnn_crown_with_intermediate_crown_sound(dev, name):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_intermediate_mlp
+    from boundflow_b200.ir import InputSpec
+
+    wl = W.make_workload(name, batch=8)
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    bounds, _pre = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), chunk_rows=512)
+    w = _worst_violation(wl.layers, wl.lo, wl.up, wl.C, bounds.lower, bounds.upper, dev, seed=3)
+    print(f"{name} CROWN with CROWN intermediates, 8 inputs x 10^4 samples: worst violation / tolerance = {w:.3f}")
+    assert w <= 1.0
+
+
+def test_c3_alpha_crown_sound(dev):
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, ibp_trace, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+
+    wl = W.make_workload("c3", batch=32)   # 288 coefficient rows: the tensor-core kernels
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    a0 = adaptive_alpha_from_trace(ibp_trace(wl.module, spec))
+    bounds, _a, _b, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=20, lr=0.1, per_batch_params=True,
+                                                warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))))
+    sel = slice(0, 8)
+    w = _worst_violation(wl.layers, wl.lo[sel], wl.up[sel], wl.C[sel], bounds.lower[sel], bounds.upper[sel], dev, seed=4)
+    print(f"c3 alpha-CROWN (20 steps): worst violation / tolerance = {w:.3f}")
+    assert w <= 1.0
+
+
+def test_c4_split_subdomains_sound_on_constraint_satisfying_samples(dev):
+    """Eight subdomains whose ten split neurons take the sign they have at a point of the box (so the subdomain is
+    not empty); samples are the box corners, uniform points and perturbations of that point at several scales, and
+    only samples that satisfy all ten split constraints are checked."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import bound_split_domains
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c4")
+    D = 32   # 288 coefficient rows: the tensor-core kernels; the first 8 subdomains are sampled
+    root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+    L = _layers64(wl.layers, dev)
+    g = torch.Generator(device=dev).manual_seed(9)
+    lo, up = wl.lo[0].to(dev, torch.float64), wl.up[0].to(dev, torch.float64)
+    anchors = lo + torch.rand((D, 784), generator=g, device=dev, dtype=torch.float64) * (up - lo)
+    _y, pre_at_anchor = _forward(L, anchors, record_pre=True)
+    unstable = [torch.nonzero(((l < 0) & (u > 0)).reshape(-1)).flatten().to(dev) for l, u in root.pre]
+    splits = [torch.zeros(D, l.shape[1], dtype=torch.int8, device=dev) for l, _ in root.pre]
+    per_layer = (3, 3, 2, 2)
+    for r, idx in enumerate(unstable):
+        pick = idx[torch.randint(0, len(idx), (D, per_layer[r]), generator=g, device=dev)]
+        sign = torch.where(pre_at_anchor[r].gather(1, pick) >= 0, 1, -1).to(torch.int8)
+        splits[r].scatter_(1, pick, sign)
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))   # one box, repeated on the device
+    res = bound_split_domains(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_split_state=dict(zip(wl.relu_names, splits)), steps=10, lr=0.1)
+    assert int(res.infeasible.sum()) == 0
+    C = wl.C[0].to(dev, torch.float64)
+    worst, fewest = 0.0, None
+    for d in range(8):
+        lb, ub = res.lower[d].to(torch.float64), res.upper[d].to(torch.float64)
+        tol_l, tol_u = 1e-4 + 1e-5 * lb.abs(), 1e-4 + 1e-5 * ub.abs()
+        survivors = 0
+        for scale in (None, 0.3, 0.1, 0.03, 0.01):
+            r = torch.rand((N_SAMPLES // 5, 784), generator=g, device=dev, dtype=torch.float64)
+            if scale is None:
+                x = lo + r * (up - lo)
+            else:
+                x = torch.minimum(torch.maximum(anchors[d] + scale * (r - 0.5) * (up - lo), lo), up)
+            x[0] = anchors[d]
+            y, pre = _forward(L, x, record_pre=True)
+            ok = torch.ones(x.shape[0], dtype=torch.bool, device=dev)
+            for rr in range(4):
+                s = splits[rr][d].to(torch.float64)
+                ok &= ~(((s > 0) & (pre[rr] < 0)) | ((s < 0) & (pre[rr] > 0))).any(dim=1)
+            survivors += int(ok.sum())
+            if ok.any():
+                yy = y[ok].matmul(C.t())
+                worst = max(worst, float(((lb - yy) / tol_l).max()), float(((yy - ub) / tol_u).max()))
+        fewest = survivors if fewest is None else min(fewest, survivors)
+    print(f"c4 alpha-CROWN on split subdomains: worst violation / tolerance = {worst:.3f}; fewest constraint-satisfying samples per subdomain = {fewest} of {N_SAMPLES}")
+    assert fewest >= 1000
+    assert worst <= 1.0
