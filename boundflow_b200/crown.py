@@ -499,14 +499,20 @@ def alpha_crown_from_trace(
     want_upper: bool = True,
     beta_splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
     beta0: Optional[Sequence[torch.Tensor]] = None,
+    soft_tau: float = 1.0,
 ):
     """Device-resident alpha (and, with `beta_splits`, beta) loop; returns (best_lower,
     best_upper|None, best_alpha list, last alpha list, best_metric) and, with beta, a sixth
     element best_beta list.  `beta_splits[r]` is the int8 split assignment [B,n_r] or [1,n_r]
     of ReLU r (None = no split there)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
-    if spec_reduce not in ("mean", "sum"):
-        raise NotImplementedError(f"spec_reduce={spec_reduce!r} is not supported by the CUDA backend (mean | sum)")
+    codes = {"mean": _lib.REDUCE_MEAN, "sum": _lib.REDUCE_SUM, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
+    if spec_reduce not in codes:
+        raise ValueError(f"spec_reduce={spec_reduce!r}: expected mean | sum | min | softmin")
+    if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
+        raise ValueError(f"soft_tau must be >0, got {soft_tau}")
+    if spec_reduce in ("min", "softmin") and beta_splits is not None:
+        raise NotImplementedError("the CUDA backend combines the min / softmin spec reductions with alpha only (no beta parameters)")
     n_out = 1
     for d in chain.output_shape:
         n_out *= int(d)
@@ -517,16 +523,17 @@ def alpha_crown_from_trace(
     best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
     best_upper = torch.empty(B, S, dtype=torch.float32, device=device) if want_upper else None
     best_metric = torch.empty(B, dtype=torch.float32, device=device)
-    reduce_code = _lib.REDUCE_MEAN if spec_reduce == "mean" else _lib.REDUCE_SUM
+    reduce_code = codes[spec_reduce]
     if beta_splits is None:
         nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, S))
         ws = _Workspace.get(device, nbytes)
         _lib.check(
-            chain.lib.bf_chain_alpha_crown(
+            chain.lib.bf_chain_alpha_beta_crown_reduce(
                 chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
-                _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
+                _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), None, None, None, None,
+                _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
                 _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
-                int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+                int(steps), float(lr), reduce_code, float(soft_tau), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
             )
         )
         return best_lower, best_upper, best_alpha, alpha, best_metric
@@ -726,6 +733,7 @@ def run_alpha_beta_crown_mlp(
     warm_start_beta: Optional[Any] = None,
     objective: str = "lower",
     spec_reduce: str = "mean",
+    soft_tau: float = 1.0,
     per_batch_params: bool = False,
     optimize_beta: Optional[bool] = None,
 ):
@@ -737,7 +745,8 @@ def run_alpha_beta_crown_mlp(
     loop), `None` means "as the reference".  `per_batch_params=False` (the reference's
     default) optimises one alpha / beta row shared by the whole batch with a whole-batch
     best-of.  Differences from the reference, all explicit: the objective is the lower
-    bound (shared mode: with spec_reduce="mean").  For a single node the first-layer
+    bound; spec_reduce mean | min | softmin (with `soft_tau`) as in the reference plus "sum" in the
+    per-domain mode, min / softmin with alpha only (no split assignment); shared mode: spec_reduce="mean".  For a single node the first-layer
     infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
     reference (Linear first layers; `first_layer_certificate` gives it for whole batches).
     Infeasible splits raise ValueError like the reference.
@@ -788,7 +797,7 @@ def run_alpha_beta_crown_mlp(
     if spec_reduce != "mean" and not per_batch_params:
         raise NotImplementedError("the shared-parameter loop of the CUDA backend implements spec_reduce='mean'")
     loop = alpha_crown_from_trace if per_batch_params else shared_alpha_crown_from_trace
-    kw = {"spec_reduce": spec_reduce} if per_batch_params else {}
+    kw = {"spec_reduce": spec_reduce, "soft_tau": soft_tau} if per_batch_params else {}
     if optimize_beta:
         beta_splits = [relu_split_state.get(n) for n in chain.relu_input_names]
         best_l, best_u, best_a, _last, _metric, best_b = loop(

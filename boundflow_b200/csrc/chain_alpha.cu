@@ -24,6 +24,7 @@ struct AlphaWs {
   float* cacc;
   float* partial;
   float* cur;
+  float* row_weight;  // [M] d objective / d lower per spec row (min / softmin objectives)
   float* metric;
   int* improve;
   void* conv_scratch;  // ReLU-scaled coefficients of a conv layer's backward step
@@ -66,6 +67,7 @@ static size_t alpha_ws_layout(const bf_chain* c, int B, int S, bool with_beta, v
   w.cacc = cv.take<float>(M);
   w.partial = cv.take<float>(M * (size_t)std::max(std::max(crown_bwd_partial_tiles(c->n0), crown_tc_partial_tiles(c->n0, 32)), crown_tc_persist_max_partial_tiles(c->n0)));
   w.cur = cv.take<float>(M);
+  w.row_weight = cv.take<float>(M);
   w.metric = cv.take<float>((size_t)B);
   w.improve = cv.take<int>((size_t)B);
   size_t conv_scratch = 0;
@@ -185,6 +187,7 @@ static AdamScalars adam_scalars(int t, float lr, int spec_reduce, int S) {
   sc.eps = 1e-8f;
   sc.one_minus_beta1 = (float)(1.0 - beta1);
   sc.one_minus_beta2 = (float)(1.0 - beta2);
+  // mean: loss = -sum_b mean_s lower; sum: -sum_b sum_s lower; min / softmin: the row weights carry d metric / d lower
   sc.grad_scale = (spec_reduce == BF_REDUCE_MEAN) ? (-1.0f / (float)S) : -1.0f;
   return sc;
 }
@@ -224,6 +227,18 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
                                          float* best_lower, float* best_upper, float* best_metric, int steps, float lr,
                                          int spec_reduce, void* workspace, size_t workspace_bytes, int B, int S,
                                          bf_stream_t stream_) {
+  return bf_chain_alpha_beta_crown_reduce(chain, C, pre_l, pre_u, alpha, best_alpha, beta, best_beta, splits, split_strides, mid, rad,
+                                          norm_p, eps, best_lower, best_upper, best_metric, steps, lr, spec_reduce, 1.0f, workspace,
+                                          workspace_bytes, B, S, stream_);
+}
+
+extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                                const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                                float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                                const int* split_strides, const float* mid, const float* rad, int norm_p,
+                                                float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
+                                                float lr, int spec_reduce, float soft_tau, void* workspace,
+                                                size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
   const bool with_beta = beta != nullptr;
   const bf::InputSetArg in{mid, rad, norm_p, eps};
   const char* who = with_beta ? "bf_chain_alpha_beta_crown" : "bf_chain_alpha_crown";
@@ -231,7 +246,10 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
   int rc = alpha_common_checks(who, chain, C, pre_l, pre_u, alpha, mid, rad, norm_p, eps, workspace, workspace_bytes, B, S, with_beta, &ws);
   if (rc != BF_OK) return rc;
   BF_REQUIRE(best_alpha && best_lower && steps >= 0, BF_E_INVALID, "%s: null output or negative steps", who);
-  BF_REQUIRE(spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_SUM, BF_E_INVALID, "%s: bad spec_reduce", who);
+  BF_REQUIRE(spec_reduce >= BF_REDUCE_MEAN && spec_reduce <= BF_REDUCE_SOFTMIN, BF_E_INVALID, "%s: bad spec_reduce", who);
+  const bool weighted = (spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN);
+  BF_REQUIRE(!weighted || !with_beta, BF_E_UNSUPPORTED, "%s: min / softmin objectives are not combined with beta parameters", who);
+  BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "%s: soft_tau must be positive", who);
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
   cudaStream_t stream = bf::as_stream(stream_);
   const int R = (int)chain->relu_layers.size();
@@ -257,10 +275,17 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
     const bool last = (t == steps);
     rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, in, ws.cur, B, S, stream);
     if (rc != BF_OK) return rc;
-    rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, B, S, stream);
+    rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, soft_tau,
+                                (weighted && !last) ? ws.row_weight : nullptr, B, S, stream);
     if (rc != BF_OK) return rc;
     bf::AdamScalars sc{};
     if (!last) {
+      if (weighted) {  // the gradient of min_s / softmin_s lower: every spec row enters with its weight
+        for (int r = 0; r < R; ++r) {
+          rc = bf::launch_scale_rows(ws.Ahat[r], ws.row_weight, (long long)B * S, chain->layers[chain->relu_layers[r]].n_in, stream);
+          if (rc != BF_OK) return rc;
+        }
+      }
       rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, spec_reduce, S);

@@ -115,24 +115,60 @@ int launch_sum_partials(const float* c, const float* partial, int ntiles, float*
 // ---- per-domain objective and strict best-of ----------------------------------
 __global__ void select_best_kernel(const float* __restrict__ cur, float* __restrict__ best_lower,
                                    float* __restrict__ best_metric, int* __restrict__ improve, int first, int spec_reduce,
-                                   int B, int S) {
+                                   float soft_tau, float* __restrict__ row_weight, int B, int S) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
-  float s = 0.f;
-  for (int k = 0; k < S; ++k) s += cur[(size_t)b * S + k];
-  const float metric = (spec_reduce == BF_REDUCE_MEAN) ? (s / (float)S) : s;
+  const float* row = cur + (size_t)b * S;
+  float metric;
+  if (spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_SUM) {
+    float s = 0.f;
+    for (int k = 0; k < S; ++k) s += row[k];
+    metric = (spec_reduce == BF_REDUCE_MEAN) ? (s / (float)S) : s;
+  } else {
+    // min: the smallest spec row; softmin: -tau * logsumexp(-x / tau).  row_weight receives d metric / d row[k]
+    // (one-hot at the first minimum, or softmax(-x / tau)): the gradient sweep weights the spec rows with it.
+    float mn = row[0];
+    int arg = 0;
+    for (int k = 1; k < S; ++k)
+      if (row[k] < mn) { mn = row[k]; arg = k; }
+    if (spec_reduce == BF_REDUCE_MIN) {
+      metric = mn;
+      if (row_weight)
+        for (int k = 0; k < S; ++k) row_weight[(size_t)b * S + k] = (k == arg) ? 1.f : 0.f;
+    } else {
+      float z = 0.f;
+      for (int k = 0; k < S; ++k) z += expf(-(row[k] - mn) / soft_tau);
+      metric = mn - soft_tau * logf(z);
+      if (row_weight)
+        for (int k = 0; k < S; ++k) row_weight[(size_t)b * S + k] = expf(-(row[k] - mn) / soft_tau) / z;
+    }
+  }
   const bool imp = first || (metric > best_metric[b]);
   if (imp) {
     best_metric[b] = metric;
-    for (int k = 0; k < S; ++k) best_lower[(size_t)b * S + k] = cur[(size_t)b * S + k];
+    for (int k = 0; k < S; ++k) best_lower[(size_t)b * S + k] = row[k];
   }
   improve[b] = imp ? 1 : 0;
 }
 
 int launch_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first,
-                       int spec_reduce, int B, int S, cudaStream_t stream) {
-  select_best_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(cur, best_lower, best_metric, improve, first, spec_reduce, B, S);
+                       int spec_reduce, float soft_tau, float* row_weight, int B, int S, cudaStream_t stream) {
+  select_best_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(cur, best_lower, best_metric, improve, first, spec_reduce, soft_tau,
+                                                           row_weight, B, S);
   BF_CHECK_LAUNCH("select_best_kernel");
+  return BF_OK;
+}
+
+// A[m, :] *= w[m]: weights the saved coefficient rows of a layer by d objective / d lower[m] before the gradient sweep
+// (min / softmin objectives; a positive factor keeps every sign decision of the sweep, a zero factor removes the row).
+__global__ void scale_rows_kernel(float* __restrict__ A, const float* __restrict__ w, long long total, int n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    A[i] *= w[i / n];
+}
+
+int launch_scale_rows(float* A, const float* w, long long M, int n, cudaStream_t stream) {
+  scale_rows_kernel<<<ew_grid(M * n, 256), 256, 0, stream>>>(A, w, M * n, n);
+  BF_CHECK_LAUNCH("scale_rows_kernel");
   return BF_OK;
 }
 

@@ -65,7 +65,8 @@ int launch_concretize(const float* A, const float* mid, const float* rad, const 
 int launch_sum_partials(const float* c, const float* partial, int ntiles, float* out, int M, cudaStream_t stream);
 // per-domain objective + strict best-of tracking (first != 0 initialises)
 int launch_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first,
-                       int spec_reduce, int B, int S, cudaStream_t stream);
+                       int spec_reduce, float soft_tau, float* row_weight, int B, int S, cudaStream_t stream);
+int launch_scale_rows(float* A, const float* w, long long M, int n, cudaStream_t stream);
 struct AdamScalars {
   float lr_step;      // lr / (1 - beta1^t)
   float bc2_sqrt;     // sqrt(1 - beta2^t)

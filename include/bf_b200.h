@@ -50,6 +50,8 @@ typedef void* bf_stream_t; /* a cudaStream_t */
 
 #define BF_REDUCE_MEAN 0 /* per-domain objective = mean over spec rows */
 #define BF_REDUCE_SUM 1  /* per-domain objective = sum over spec rows  */
+#define BF_REDUCE_MIN 2  /* per-domain objective = smallest spec row (alpha only) */
+#define BF_REDUCE_SOFTMIN 3 /* per-domain objective = -tau * logsumexp(-rows / tau) (alpha only) */
 
 /* Library identity and diagnostics. */
 int bf_version(void);
@@ -431,6 +433,21 @@ int bf_chain_alpha_beta_crown(const bf_chain* chain,
                               float* best_lower, float* best_upper, float* best_metric,
                               int steps, float lr, int spec_reduce,
                               void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+/* The same loop with every spec reduction of the reference's objective="lower" (_objective_metric / _loss,
+ * boundflow/runtime/alpha_beta_crown.py:535-612, per-domain form 787-818): spec_reduce BF_REDUCE_MEAN, _SUM,
+ * _MIN (smallest spec row) or _SOFTMIN (-soft_tau * logsumexp(-rows / soft_tau), soft_tau > 0).  For _MIN and
+ * _SOFTMIN the gradient sweep weights every spec row by d objective / d lower (one-hot at the first minimum, or
+ * softmax(-rows / soft_tau)); they take alpha only (beta == NULL). */
+int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain,
+                                     const float* C,
+                                     const float* const* pre_l, const float* const* pre_u,
+                                     float* const* alpha, float* const* best_alpha,
+                                     float* const* beta, float* const* best_beta,
+                                     const int8_t* const* splits, const int* split_strides,
+                                     const float* mid, const float* rad, int norm_p, float eps,
+                                     float* best_lower, float* best_upper, float* best_metric,
+                                     int steps, float lr, int spec_reduce, float soft_tau,
+                                     void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 /* Branching hint: per domain the ReLU (chain order) and neuron with the widest gap u - l among
  * unstable neurons (l < 0 < u); earlier ReLUs and lower indices win ties; -1/-1 when none.

@@ -485,6 +485,7 @@ def alpha_crown(
     trace: Optional[ForwardTrace] = None,
     optimize_beta: bool = False,
     return_beta: bool = False,
+    soft_tau: float = 1.0,
 ):
     """Per-domain alpha (and optionally beta) optimisation, `run_alpha_beta_crown_mlp`
     with `per_batch_params=True, objective="lower"` restated (alpha_beta_crown.py:716-923).
@@ -529,7 +530,17 @@ def alpha_crown(
         if optimize_beta:
             add_l = [None if sf is None else -bt * sf * (sf != 0).to(dtype) for bt, sf in zip(betas, split_f)]
         lower, upper = crown_backward(layers, inp, trace, C, alpha=alphas, add_l=add_l)
-        metric_b = lower.mean(dim=1) if spec_reduce == "mean" else lower.sum(dim=1)
+        # spec reductions of objective="lower" (alpha_beta_crown.py:787-805): mean | min | softmin, plus sum
+        if spec_reduce == "mean":
+            metric_b = lower.mean(dim=1)
+        elif spec_reduce == "sum":
+            metric_b = lower.sum(dim=1)
+        elif spec_reduce == "min":
+            metric_b = lower.min(dim=1).values
+        elif spec_reduce == "softmin":
+            metric_b = -float(soft_tau) * torch.logsumexp(-lower / float(soft_tau), dim=1)
+        else:
+            raise ValueError(spec_reduce)
         if best_metric is None:
             best_metric = metric_b.detach().clone()
             best_lower, best_upper = lower.detach().clone(), upper.detach().clone()

@@ -337,3 +337,19 @@ def test_alpha_crown_on_a_conv_chain(golden):
         lo, up, _a, _ = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=steps, lr=0.1, trace=trace)
         assert_close(lo, g[f"shared_lower_{steps}"], f"shared lower {steps}", rtol=rtol)
         assert_close(up, g[f"shared_upper_{steps}"], f"shared upper {steps}", rtol=rtol)
+
+
+def test_min_and_softmin_spec_reductions(golden):
+    """`run_alpha_beta_crown_mlp(spec_reduce="min" | "softmin")` of the reference (alpha_beta_crown.py:535-612, 787-818)."""
+    g = golden("spec_reduce.npz")
+    for cfg in ("c1", "c3"):
+        wl = W.make_workload(cfg, batch=8)
+        inp = O.box_input(wl.lo, wl.up)
+        trace = O.forward_ibp_trace(wl.layers, inp)
+        a0 = O.adaptive_alpha_init(trace)
+        for red in ("min", "softmin"):
+            for k in (1, 3, 10):
+                lo, up, _a, _t = O.alpha_crown(wl.layers, inp, wl.C, steps=k, lr=0.1, alpha0=a0, trace=trace, spec_reduce=red,
+                                               soft_tau=float(g[f"{cfg}_tau"]))
+                assert_close(lo, g[f"{cfg}_{red}_lower_{k}"], f"{cfg} {red} lower after {k}")
+                assert_close(up, g[f"{cfg}_{red}_upper_{k}"], f"{cfg} {red} upper after {k}")
