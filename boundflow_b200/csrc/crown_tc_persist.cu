@@ -30,8 +30,11 @@
 // tiles 50 % of the time; with every global load switched off the same kernel still needs 200 cycles per MMA because
 // the MMAs' shared-memory operand reads (12 KB per instruction) plus the producers' and the copy engine's writes
 // saturate the 128 B/clk shared-memory port.  The one-tile-per-CTA kernel sits at 88 % of that shared-memory
-// bound (448 KB per k-block in 4.0 k cycles); going beyond it needs operands that do not come from this CTA's shared
-// memory on every instruction (CTA pairs sharing the weight tile, or the coefficient operand in tensor memory).
+// bound (448 KB per k-block in 4.0 k cycles).  Sharing the weight tile between the two CTAs of a cluster (crown_tc.cu,
+// PAIR) removes a third of that traffic and was measured slower, so the producers' own latency chain (about 370
+// instructions per warp and k-block at 40 % issue utilisation, slope vectors loaded and consumed in the same
+// iteration) is the limit that counts; loading the slope vectors a k-block ahead needs 16-24 registers that 576-thread
+// CTAs do not have (spills, 256 us against 243 us).
 // The kernel stays for problems with few row blocks, where its narrower tiles (a half or a quarter of a packed
 // weight image) give more CTAs work: a 1152 x 256 x 256 layer launches 36 tiles instead of 9 and runs in 23 us
 // instead of 26 us.

@@ -136,6 +136,71 @@ __device__ __forceinline__ void mma_kblock_3xtf32(uint32_t tmem_d, uint64_t a_hi
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ----
+// The same twelve MMAs issued by the leader CTA of a pair: 256 accumulator rows (128 in each CTA's tensor memory), each
+// CTA's tensor core reads its own A tile and its own half of the B rows from its own shared memory at the offsets the
+// descriptors name, so every operand byte is read once per pair instead of once per CTA.
+__device__ __forceinline__ void mma_kblock_3xtf32_pair(uint32_t tmem_d, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
+                                                  uint32_t idesc, uint32_t accumulate_first) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pacc, pone;\n\t"
+      ".reg .b64 ah, al, bh, bl;\n\t"
+      "setp.ne.b32 pacc, %6, 0;\n\t"
+      "setp.eq.b32 pone, %7, %7;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %2, %3, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pacc;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %4, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %3, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 2;\n\t"
+      "add.u64 al, %2, 2;\n\t"
+      "add.u64 bh, %3, 2;\n\t"
+      "add.u64 bl, %4, 2;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 4;\n\t"
+      "add.u64 al, %2, 4;\n\t"
+      "add.u64 bh, %3, 4;\n\t"
+      "add.u64 bl, %4, 4;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "add.u64 ah, %1, 6;\n\t"
+      "add.u64 al, %2, 6;\n\t"
+      "add.u64 bh, %3, 6;\n\t"
+      "add.u64 bl, %4, 6;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], al, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bl, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], ah, bh, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, pone;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(a_hi), "l"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate_first), "r"(z)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(both)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// all threads of both CTAs; also orders shared-memory writes (barrier initialisation) before the peer's accesses
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   asm volatile(

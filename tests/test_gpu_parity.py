@@ -221,6 +221,20 @@ def test_verdict_kernel(dev):
     _lib.check(lib.bf_verdict(dl.data_ptr(), 0.0, 1e-6, v.data_ptr(), mn.data_ptr(), 4, 2, torch.cuda.current_stream().cuda_stream))
     assert torch.equal(v.cpu().bool(), O.verdict(lower))
     assert torch.equal(mn.cpu(), lower.min(dim=1).values)
+    # a NaN bound on any spec row never proves a domain (the reference's bounds.lower.min() >= threshold propagates
+    # NaN, bab.py:881-895), wherever the NaN sits; an infeasible-flagged domain is not proven either
+    nan = float("nan")
+    lower = torch.tensor([[0.5, nan, 0.7], [nan, 0.2, 0.3], [0.4, 0.2, nan], [0.4, 0.2, 0.1], [0.9, 0.8, 0.7]])
+    dl = lower.to(dev)
+    v = torch.empty(5, dtype=torch.int8, device=dev)
+    mn = torch.empty(5, device=dev)
+    _lib.check(lib.bf_verdict(dl.data_ptr(), 0.0, 1e-6, v.data_ptr(), mn.data_ptr(), 5, 3, torch.cuda.current_stream().cuda_stream))
+    assert v.cpu().tolist() == [0, 0, 0, 1, 1]
+    assert torch.equal(v.cpu().bool(), O.verdict(lower))
+    assert torch.isnan(mn.cpu()[:3]).all() and mn.cpu()[3:].tolist() == pytest.approx([0.1, 0.7])
+    infeasible = torch.tensor([0, 0, 0, 0, 1], dtype=torch.int32, device=dev)
+    _lib.check(lib.bf_verdict_masked(dl.data_ptr(), 0.0, 1e-6, infeasible.data_ptr(), v.data_ptr(), None, 5, 3, torch.cuda.current_stream().cuda_stream))
+    assert v.cpu().tolist() == [0, 0, 0, 1, 0]
 
 
 # ---------------------------------------------------------------------------
@@ -533,3 +547,41 @@ def test_c4_full_batch_properties(dev):
     lo_ref, up_ref = O.crown_backward(wl.layers, inp, tr, wl.C.expand(4, -1, -1), alpha=[a[sel.to(dev)].cpu() for a in best_a])
     assert_close(best_l[sel.to(dev)], lo_ref, "oracle at returned alpha (lower)")
     assert_close(best_u[sel.to(dev)], up_ref, "oracle at returned alpha (upper)")
+
+
+def test_conv_backward_ignores_undersized_scratch_without_slopes(dev):
+    """Without slopes the scratch of bf_crown_relu_conv2d_bwd is optional: a buffer that is too small for the chunked
+    intercept sums of a wide layer (here 8 * 24 * 24 = 4608 > 4096 elements per row) must not be written past its end;
+    the call then streams whole rows and gives the result of the full-size-scratch call.  With slopes the same buffer
+    is refused."""
+    from boundflow_b200 import _lib
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(3)
+    D, S, Co, Ho, Ci, k, st, pd = 2, 3, 8, 24, 2, 3, 1, 1
+    Hi = (Ho - 1) * st - 2 * pd + k
+    n = Co * Ho * Ho
+    A = torch.randn(D, S, n, generator=g).to(dev)
+    W = torch.randn(Co, Ci, k, k, generator=g).to(dev)
+    b = torch.randn(Co, generator=g).to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for nbytes in (int(lib.bf_crown_relu_conv2d_bwd_scratch_bytes(D, S, Co, Ho, Ho)), 16):
+        scratch = torch.zeros(max(nbytes, 16) + 64, dtype=torch.uint8, device=dev)
+        A_prev = torch.empty(D, S, Ci * Hi * Hi, device=dev)
+        delta = torch.empty(D, S, device=dev)
+        _lib.check(lib.bf_crown_relu_conv2d_bwd(A.data_ptr(), _lib.SIDE_LOWER, None, None, None, None, W.data_ptr(), b.data_ptr(), A_prev.data_ptr(),
+                                                delta.data_ptr(), 0, scratch.data_ptr(), nbytes, D, S, Ci, Hi, Hi, Co, Ho, Ho, k, k, st, st, pd, pd, stream))
+        torch.cuda.synchronize()
+        if nbytes == 16:
+            assert int(scratch[16:].sum()) == 0, "bytes behind the 16-byte scratch were written"
+        outs.append((A_prev, delta))
+    assert_close(outs[1][0], outs[0][0], "A_prev with an undersized scratch")
+    assert_close(outs[1][1], outs[0][1], "delta with an undersized scratch")
+    want = (A.reshape(D * S, Co, Ho * Ho).sum(dim=2) * b.view(1, -1)).sum(dim=1).reshape(D, S)
+    assert_close(outs[1][1], want, "bias term")
+    slopes = torch.rand(D, n, generator=g).to(dev)
+    small = torch.zeros(16, dtype=torch.uint8, device=dev)
+    rc = lib.bf_crown_relu_conv2d_bwd(A.data_ptr(), _lib.SIDE_LOWER, slopes.data_ptr(), slopes.data_ptr(), None, None, W.data_ptr(), b.data_ptr(),
+                                      outs[0][0].data_ptr(), outs[0][1].data_ptr(), 0, small.data_ptr(), 16, D, S, Ci, Hi, Hi, Co, Ho, Ho, k, k, st, st, pd, pd, stream)
+    assert rc == _lib.BF_E_WORKSPACE

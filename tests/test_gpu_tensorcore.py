@@ -172,9 +172,12 @@ def test_tc_is_deterministic(dev, adjoint):
         assert torch.equal(a, b)
 
 
-def test_persistent_backward_kernel_matches_oracle(dev):
-    """The opt-in persistent warp-specialised backward kernel (double-buffered accumulators in tensor memory,
-    narrower tiles when few row blocks exist) on a problem with several tiles per CTA and on ragged small ones."""
+@pytest.mark.parametrize("switch", ["BF_B200_BWD_PERSISTENT", "BF_B200_BWD_PAIRS"])
+def test_opt_in_backward_kernels_match_oracle(dev, switch):
+    """The two opt-in variants of the backward contraction on a problem with several tiles per CTA and on ragged
+    small ones: the persistent warp-specialised kernel (double-buffered accumulators in tensor memory, narrower tiles
+    when few row blocks exist) and the CTA-pair kernel (clusters of two row blocks, tcgen05 cta_group::2, each CTA
+    holding half of every weight image; 360 rows = 3 row blocks leave one pair with an empty second CTA)."""
     import os
 
     from boundflow_b200 import _lib
@@ -183,7 +186,7 @@ def test_persistent_backward_kernel_matches_oracle(dev):
     from boundflow_b200.ir import InputSpec
     from oracle import crown_oracle as O
 
-    os.environ["BF_B200_BWD_PERSISTENT"] = "1"
+    os.environ[switch] = "1"
     try:
         for name, batch in (("c3", 40), ("c1", 64)):   # 360 and 576 rows: narrow tiles, partial row blocks
             wl = W.make_workload(name, batch=batch)
@@ -224,4 +227,4 @@ def test_persistent_backward_kernel_matches_oracle(dev):
         assert_close(best_l[sel.to(dev)], lo_ref, "c4 lower at the returned alpha")
         assert_close(best_u[sel.to(dev)], up_ref, "c4 upper at the returned alpha")
     finally:
-        os.environ.pop("BF_B200_BWD_PERSISTENT", None)
+        os.environ.pop(switch, None)

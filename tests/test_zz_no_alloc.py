@@ -66,6 +66,19 @@ def test_noalloc_conv_backward_matches_scratch_variant_twice():
             assert_close(got_A, ref_A, "A_prev")
             assert_close(got_d, ref_d, "delta")
             assert torch.equal(got_A, ref_A) and torch.equal(got_d, ref_d)  # same kernels, same order: bit-equal
+            # and against the CPU oracle, so that this file stands on its own: ReLU backward of this side's rows
+            # (crown_ibp.py:1262-1298) followed by the transposed convolution and its bias term (crown_ibp.py:1106-1173)
+            from oracle import crown_oracle as O
+
+            c = case
+            A, au, bu, al = (c[k].cpu() for k in ("A", "au", "bu", "al"))
+            zero_b, zeros = torch.zeros(c["D"], c["S"]), torch.zeros_like(bu)
+            A_u, A_l, b_u, b_l = O.relu_backward(A, A, zero_b, zero_b, au, bu, al, zeros)
+            lam, icpt = (A_l, b_l) if side == _lib.SIDE_LOWER else (A_u, b_u)
+            want_A, want_d = O.conv2d_backward(lam, icpt, c["W"].cpu(), c["b"].cpu(), (c["st"], c["st"]), (c["pd"], c["pd"]),
+                                               (c["Ci"], c["Hi"], c["Hi"]), (c["Co"], c["Ho"], c["Ho"]))
+            assert_close(got_A, want_A, "A_prev vs oracle")
+            assert_close(got_d, want_d, "delta vs oracle")
 
 
 def test_noalloc_rejects_oversized_requests():
