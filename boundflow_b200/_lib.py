@@ -20,6 +20,7 @@ IN_LOWER_UPPER, IN_MID_RAD, IN_CENTER_DEV = 0, 1, 2
 NORM_BOX, NORM_L1, NORM_L2, NORM_INF = 0, 1, 2, 3
 OP_LINEAR, OP_CONV2D, OP_RELU, OP_FLATTEN = 1, 2, 3, 4
 REDUCE_MEAN, REDUCE_SUM, REDUCE_MIN, REDUCE_SOFTMIN = 0, 1, 2, 3
+OBJECTIVE_GAP, OBJECTIVE_BOTH = 2, 3
 
 _p = C.c_void_p
 _i = C.c_int
@@ -87,6 +88,7 @@ SIGNATURES = {
     "bf_chain_alpha_beta_workspace_bytes": (_sz, [_p, _i, _i]),
     "bf_chain_alpha_beta_crown": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_beta_crown_reduce": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _f, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_crown_objective": (_i, [_p] * 8 + [_i, _f, _p, _p, _i, _f, _i, _i, _f, _f, _f, _p, _sz, _i, _i, _p]),
     "bf_branch_scores": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _p]),
     "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_shared_workspace_bytes": (_sz, [_p, _i, _i, _i]),

@@ -500,12 +500,24 @@ def alpha_crown_from_trace(
     beta_splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
     beta0: Optional[Sequence[torch.Tensor]] = None,
     soft_tau: float = 1.0,
+    objective: str = "lower",
+    lb_weight: float = 1.0,
+    ub_weight: float = 1.0,
 ):
     """Device-resident alpha (and, with `beta_splits`, beta) loop; returns (best_lower,
     best_upper|None, best_alpha list, last alpha list, best_metric) and, with beta, a sixth
     element best_beta list.  `beta_splits[r]` is the int8 split assignment [B,n_r] or [1,n_r]
-    of ReLU r (None = no split there)."""
+    of ReLU r (None = no split there).
+
+    `objective` follows run_alpha_beta_crown_mlp (alpha_beta_crown.py:807-818): "lower" | "upper" | "gap" |
+    "both" (with lb_weight / ub_weight).  As there, the beta term enters the lower objective only: the other
+    objectives run alpha-only and hand the start beta back unchanged."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
+    if objective not in ("lower", "upper", "gap", "both"):
+        raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
+    if objective != "lower":
+        return _alpha_crown_other_objective(trace, linear_spec_C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce, soft_tau=soft_tau,
+                                            objective=objective, lb_weight=lb_weight, ub_weight=ub_weight, beta_splits=beta_splits, beta0=beta0)
     codes = {"mean": _lib.REDUCE_MEAN, "sum": _lib.REDUCE_SUM, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
     if spec_reduce not in codes:
         raise ValueError(f"spec_reduce={spec_reduce!r}: expected mean | sum | min | softmin")
@@ -564,6 +576,51 @@ def alpha_crown_from_trace(
         )
     )
     return best_lower, best_upper, best_alpha, alpha, best_metric, best_beta
+
+
+def _alpha_crown_other_objective(trace, linear_spec_C, alpha0, *, steps, lr, spec_reduce, soft_tau, objective, lb_weight, ub_weight,
+                                 beta_splits, beta0):
+    """objective "upper" = the lower loop on the negated spec rows (upper(C) = -lower(-C)); "gap" and "both" evaluate
+    the rows and their negations side by side (2S rows per domain) through bf_chain_alpha_crown_objective."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    if spec_reduce not in ("mean", "min", "softmin"):
+        raise ValueError(f"spec_reduce={spec_reduce!r}: objective {objective!r} takes mean | min | softmin")
+    if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
+        raise ValueError(f"soft_tau must be >0, got {soft_tau}")
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    C = _expand_spec(linear_spec_C, B, n_out, device)
+    S = int(C.shape[1])
+    tail = ()
+    if beta_splits is not None:  # no beta term on these objectives: the start values come back unchanged
+        beta = ([b.detach().to(device=device, dtype=torch.float32).reshape(-1, n).expand(B, n).contiguous().clone() for b, n in zip(beta0, chain.relu_widths)]
+                if beta0 is not None else [torch.zeros(B, n, dtype=torch.float32, device=device) for n in chain.relu_widths])
+        tail = (beta,)
+    if objective == "upper":
+        lo, up, best_alpha, alpha, metric = alpha_crown_from_trace(trace, -C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce,
+                                                                   want_upper=True, soft_tau=soft_tau)
+        return (-up, -lo, best_alpha, alpha, metric) + tail
+    if float(lb_weight) < 0.0 or float(ub_weight) < 0.0:
+        raise NotImplementedError("the CUDA backend takes non-negative lb_weight / ub_weight (a row weight must not flip the sign decisions of the gradient sweep)")
+    C2 = torch.cat([C, -C], dim=1).contiguous()
+    alpha = [a.detach().to(device=device, dtype=torch.float32).reshape(-1, n).expand(B, n).contiguous().clone() for a, n in zip(alpha0, chain.relu_widths)]
+    best_alpha = [torch.empty_like(a) for a in alpha]
+    best_rows = torch.empty(B, 2 * S, dtype=torch.float32, device=device)
+    best_metric = torch.empty(B, dtype=torch.float32, device=device)
+    codes = {"mean": _lib.REDUCE_MEAN, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
+    nbytes = int(chain.lib.bf_chain_alpha_workspace_bytes(chain.handle, B, 2 * S))
+    ws = _Workspace.get(device, nbytes)
+    _lib.check(
+        chain.lib.bf_chain_alpha_crown_objective(
+            chain.handle, _lib.ptr(C2), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.ptr_array(alpha), _lib.ptr_array(best_alpha),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
+            _lib.ptr(best_rows), _lib.ptr(best_metric), int(steps), float(lr),
+            _lib.OBJECTIVE_GAP if objective == "gap" else _lib.OBJECTIVE_BOTH, codes[spec_reduce], float(soft_tau), float(lb_weight), float(ub_weight),
+            _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+        )
+    )
+    return (best_rows[:, :S].contiguous(), -best_rows[:, S:], best_alpha, alpha, best_metric) + tail
 
 
 def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alpha: Sequence[torch.Tensor], *, spec_reduce: str = "mean"):
@@ -736,6 +793,8 @@ def run_alpha_beta_crown_mlp(
     soft_tau: float = 1.0,
     per_batch_params: bool = False,
     optimize_beta: Optional[bool] = None,
+    lb_weight: float = 1.0,
+    ub_weight: float = 1.0,
 ):
     """Per-domain alpha-beta optimisation (alpha_beta_crown.py:643-941).
 
@@ -744,15 +803,19 @@ def run_alpha_beta_crown_mlp(
     assignment is given; `optimize_beta=False` freezes it at its start (the alpha-only
     loop), `None` means "as the reference".  `per_batch_params=False` (the reference's
     default) optimises one alpha / beta row shared by the whole batch with a whole-batch
-    best-of.  Differences from the reference, all explicit: the objective is the lower
-    bound; spec_reduce mean | min | softmin (with `soft_tau`) as in the reference plus "sum" in the
-    per-domain mode, min / softmin with alpha only (no split assignment); shared mode: spec_reduce="mean".  For a single node the first-layer
+    best-of.  Per-domain mode: objective lower | upper | gap | both (lb_weight / ub_weight >= 0) and
+    spec_reduce mean | min | softmin (with `soft_tau`) as in the reference, plus "sum" for the lower
+    objective; min / softmin and the upper / gap / both objectives run alpha only (the reference applies the
+    beta term to objective="lower" alone, and its min / softmin with beta is not built here).  Shared mode:
+    objective="lower", spec_reduce="mean".  For a single node the first-layer
     infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
     reference (Linear first layers; `first_layer_certificate` gives it for whole batches).
     Infeasible splits raise ValueError like the reference.
     """
-    if objective != "lower":
-        raise NotImplementedError("the CUDA backend optimises the lower bound only")
+    if objective not in ("lower", "upper", "gap", "both"):
+        raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
+    if objective != "lower" and not per_batch_params:
+        raise NotImplementedError("the shared-parameter loop of the CUDA backend optimises the lower bound only")
     has_split = bool(relu_split_state)
     if optimize_beta is None:
         optimize_beta = has_split
@@ -797,7 +860,8 @@ def run_alpha_beta_crown_mlp(
     if spec_reduce != "mean" and not per_batch_params:
         raise NotImplementedError("the shared-parameter loop of the CUDA backend implements spec_reduce='mean'")
     loop = alpha_crown_from_trace if per_batch_params else shared_alpha_crown_from_trace
-    kw = {"spec_reduce": spec_reduce, "soft_tau": soft_tau} if per_batch_params else {}
+    kw = ({"spec_reduce": spec_reduce, "soft_tau": soft_tau, "objective": objective, "lb_weight": lb_weight, "ub_weight": ub_weight}
+          if per_batch_params else {})
     if optimize_beta:
         beta_splits = [relu_split_state.get(n) for n in chain.relu_input_names]
         best_l, best_u, best_a, _last, _metric, best_b = loop(

@@ -232,22 +232,25 @@ extern "C" int bf_chain_alpha_beta_crown(const bf_chain* chain, const float* C, 
                                           workspace_bytes, B, S, stream_);
 }
 
-extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const float* C, const float* const* pre_l,
-                                                const float* const* pre_u, float* const* alpha, float* const* best_alpha,
-                                                float* const* beta, float* const* best_beta, const int8_t* const* splits,
-                                                const int* split_strides, const float* mid, const float* rad, int norm_p,
-                                                float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
-                                                float lr, int spec_reduce, float soft_tau, void* workspace,
-                                                size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
+// The per-domain loop behind every entry point.  objective 0: maximise reduce(lower) over the S rows as given;
+// BF_OBJECTIVE_GAP / _BOTH: the S rows are S/2 spec rows followed by their negations (see bf_chain_alpha_crown_objective).
+static int alpha_loop(const char* who, const bf_chain* chain, const float* C, const float* const* pre_l,
+                      const float* const* pre_u, float* const* alpha, float* const* best_alpha, float* const* beta,
+                      float* const* best_beta, const int8_t* const* splits, const int* split_strides, const float* mid,
+                      const float* rad, int norm_p, float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
+                      float lr, int objective, float lb_weight, float ub_weight, int spec_reduce, float soft_tau, void* workspace,
+                      size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
   const bool with_beta = beta != nullptr;
+  const bool paired = objective != 0;
   const bf::InputSetArg in{mid, rad, norm_p, eps};
-  const char* who = with_beta ? "bf_chain_alpha_beta_crown" : "bf_chain_alpha_crown";
   bf::AlphaWs ws;
   int rc = alpha_common_checks(who, chain, C, pre_l, pre_u, alpha, mid, rad, norm_p, eps, workspace, workspace_bytes, B, S, with_beta, &ws);
   if (rc != BF_OK) return rc;
   BF_REQUIRE(best_alpha && best_lower && steps >= 0, BF_E_INVALID, "%s: null output or negative steps", who);
   BF_REQUIRE(spec_reduce >= BF_REDUCE_MEAN && spec_reduce <= BF_REDUCE_SOFTMIN, BF_E_INVALID, "%s: bad spec_reduce", who);
-  const bool weighted = (spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN);
+  const bool weighted = paired || (spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN);
+  BF_REQUIRE(!paired || (S % 2 == 0 && spec_reduce != BF_REDUCE_SUM && !best_upper), BF_E_INVALID,
+             "%s: paired rows need an even row count, no separate upper output and a mean / min / softmin reduction", who);
   BF_REQUIRE(!weighted || !with_beta, BF_E_UNSUPPORTED, "%s: min / softmin objectives are not combined with beta parameters", who);
   BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "%s: soft_tau must be positive", who);
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
@@ -275,8 +278,10 @@ extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const flo
     const bool last = (t == steps);
     rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, in, ws.cur, B, S, stream);
     if (rc != BF_OK) return rc;
-    rc = bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, soft_tau,
-                                (weighted && !last) ? ws.row_weight : nullptr, B, S, stream);
+    float* row_weight = (weighted && !last) ? ws.row_weight : nullptr;
+    rc = paired ? bf::launch_select_best_paired(ws.cur, best_lower, metric, ws.improve, t == 0, objective, spec_reduce, soft_tau,
+                                                lb_weight, ub_weight, row_weight, B, S / 2, stream)
+                : bf::launch_select_best(ws.cur, best_lower, metric, ws.improve, t == 0, spec_reduce, soft_tau, row_weight, B, S, stream);
     if (rc != BF_OK) return rc;
     bf::AdamScalars sc{};
     if (!last) {
@@ -288,7 +293,7 @@ extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const flo
       }
       rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
       if (rc != BF_OK) return rc;
-      sc = bf::adam_scalars(t, lr, spec_reduce, S);
+      sc = bf::adam_scalars(t, lr, paired ? BF_REDUCE_SUM : spec_reduce, S);  // row weights already carry 1/S of a paired mean
     }
     for (int r = 0; r < R; ++r) {
       const int n = chain->layers[chain->relu_layers[r]].n_in;
@@ -319,6 +324,32 @@ extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const flo
     if (rc != BF_OK) return rc;
   }
   return BF_OK;
+}
+
+extern "C" int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                                const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                                float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                                const int* split_strides, const float* mid, const float* rad, int norm_p,
+                                                float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
+                                                float lr, int spec_reduce, float soft_tau, void* workspace,
+                                                size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  return alpha_loop(beta ? "bf_chain_alpha_beta_crown" : "bf_chain_alpha_crown", chain, C, pre_l, pre_u, alpha, best_alpha, beta,
+                    best_beta, splits, split_strides, mid, rad, norm_p, eps, best_lower, best_upper, best_metric, steps, lr, 0, 1.f,
+                    1.f, spec_reduce, soft_tau, workspace, workspace_bytes, B, S, stream);
+}
+
+extern "C" int bf_chain_alpha_crown_objective(const bf_chain* chain, const float* C_paired, const float* const* pre_l,
+                                              const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                              const float* mid, const float* rad, int norm_p, float eps, float* best_rows,
+                                              float* best_metric, int steps, float lr, int objective, int spec_reduce,
+                                              float soft_tau, float lb_weight, float ub_weight, void* workspace,
+                                              size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  BF_REQUIRE(objective == BF_OBJECTIVE_GAP || objective == BF_OBJECTIVE_BOTH, BF_E_INVALID,
+             "bf_chain_alpha_crown_objective: objective must be BF_OBJECTIVE_GAP or BF_OBJECTIVE_BOTH");
+  BF_REQUIRE(S > 0, BF_E_INVALID, "bf_chain_alpha_crown_objective: S must be positive");
+  return alpha_loop("bf_chain_alpha_crown_objective", chain, C_paired, pre_l, pre_u, alpha, best_alpha, nullptr, nullptr, nullptr,
+                    nullptr, mid, rad, norm_p, eps, best_rows, nullptr, best_metric, steps, lr, objective, lb_weight, ub_weight,
+                    spec_reduce, soft_tau, workspace, workspace_bytes, B, 2 * S, stream);
 }
 
 extern "C" int bf_chain_alpha_crown(const bf_chain* chain, const float* C, const float* const* pre_l,

@@ -159,6 +159,70 @@ int launch_select_best(const float* cur, float* best_lower, float* best_metric, 
   return BF_OK;
 }
 
+// Objectives that also involve the upper bound.  The caller evaluates 2S spec rows per domain, the S rows c_s followed
+// by their negations, so cur[b, s] is the lower bound of row s and cur[b, S + s] is minus its upper bound; with
+// reduce() = mean | min | softmin over s (upper-side max / softmax are min / softmin of the negated values):
+//   both:  metric = lb_weight * reduce(cur[b, :S]) + ub_weight * reduce(cur[b, S:])
+//   gap:   metric = reduce(cur[b, :S] + cur[b, S:])                    (= -reduce_max(upper - lower))
+// row_weight receives d metric / d cur[b, j] for all 2S rows (the gradient sweep weights the saved rows with it).
+__device__ __forceinline__ float reduce_pass(const float* x, const float* y, int S, int spec_reduce, float tau, float* w, float scale) {
+  // value of reduce(x + y) (y may be null); w (if given) receives scale * d value / d x[k]
+  auto at = [&](int k) { return y ? x[k] + y[k] : x[k]; };
+  if (spec_reduce == BF_REDUCE_MEAN) {
+    float s = 0.f;
+    for (int k = 0; k < S; ++k) s += at(k);
+    if (w) for (int k = 0; k < S; ++k) w[k] = scale / (float)S;
+    return s / (float)S;
+  }
+  float mn = at(0);
+  int arg = 0;
+  for (int k = 1; k < S; ++k) {
+    const float v = at(k);
+    if (v < mn) { mn = v; arg = k; }
+  }
+  if (spec_reduce == BF_REDUCE_MIN) {
+    if (w) for (int k = 0; k < S; ++k) w[k] = (k == arg) ? scale : 0.f;
+    return mn;
+  }
+  float z = 0.f;
+  for (int k = 0; k < S; ++k) z += expf(-(at(k) - mn) / tau);
+  if (w) for (int k = 0; k < S; ++k) w[k] = scale * expf(-(at(k) - mn) / tau) / z;
+  return mn - tau * logf(z);
+}
+
+__global__ void select_best_paired_kernel(const float* __restrict__ cur, float* __restrict__ best_rows, float* __restrict__ best_metric,
+                                          int* __restrict__ improve, int first, int objective, int spec_reduce, float soft_tau,
+                                          float lb_weight, float ub_weight, float* __restrict__ row_weight, int B, int S) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const float* lo = cur + (size_t)b * 2 * S;
+  const float* nu = lo + S;
+  float* w = row_weight ? row_weight + (size_t)b * 2 * S : nullptr;
+  float metric;
+  if (objective == BF_OBJECTIVE_BOTH) {
+    metric = lb_weight * reduce_pass(lo, nullptr, S, spec_reduce, soft_tau, w, lb_weight);
+    metric += ub_weight * reduce_pass(nu, nullptr, S, spec_reduce, soft_tau, w ? w + S : nullptr, ub_weight);
+  } else {  // gap
+    metric = reduce_pass(lo, nu, S, spec_reduce, soft_tau, w, 1.f);
+    if (w) for (int k = 0; k < S; ++k) w[S + k] = w[k];
+  }
+  const bool imp = first || (metric > best_metric[b]);
+  if (imp) {
+    best_metric[b] = metric;
+    for (int k = 0; k < 2 * S; ++k) best_rows[(size_t)b * 2 * S + k] = lo[k];
+  }
+  improve[b] = imp ? 1 : 0;
+}
+
+int launch_select_best_paired(const float* cur, float* best_rows, float* best_metric, int* improve, int first, int objective,
+                              int spec_reduce, float soft_tau, float lb_weight, float ub_weight, float* row_weight, int B, int S,
+                              cudaStream_t stream) {
+  select_best_paired_kernel<<<ceil_div(B, 128), 128, 0, stream>>>(cur, best_rows, best_metric, improve, first, objective, spec_reduce,
+                                                                  soft_tau, lb_weight, ub_weight, row_weight, B, S);
+  BF_CHECK_LAUNCH("select_best_paired_kernel");
+  return BF_OK;
+}
+
 // A[m, :] *= w[m]: weights the saved coefficient rows of a layer by d objective / d lower[m] before the gradient sweep
 // (min / softmin objectives; a positive factor keeps every sign decision of the sweep, a zero factor removes the row).
 __global__ void scale_rows_kernel(float* __restrict__ A, const float* __restrict__ w, long long total, int n) {

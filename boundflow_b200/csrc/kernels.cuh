@@ -66,6 +66,10 @@ int launch_sum_partials(const float* c, const float* partial, int ntiles, float*
 // per-domain objective + strict best-of tracking (first != 0 initialises)
 int launch_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first,
                        int spec_reduce, float soft_tau, float* row_weight, int B, int S, cudaStream_t stream);
+// the same for paired spec rows (S rows followed by their negations) and the gap / both objectives
+int launch_select_best_paired(const float* cur, float* best_rows, float* best_metric, int* improve, int first, int objective,
+                              int spec_reduce, float soft_tau, float lb_weight, float ub_weight, float* row_weight, int B, int S,
+                              cudaStream_t stream);
 int launch_scale_rows(float* A, const float* w, long long M, int n, cudaStream_t stream);
 struct AdamScalars {
   float lr_step;      // lr / (1 - beta1^t)

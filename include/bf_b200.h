@@ -53,6 +53,9 @@ typedef void* bf_stream_t; /* a cudaStream_t */
 #define BF_REDUCE_MIN 2  /* per-domain objective = smallest spec row (alpha only) */
 #define BF_REDUCE_SOFTMIN 3 /* per-domain objective = -tau * logsumexp(-rows / tau) (alpha only) */
 
+#define BF_OBJECTIVE_GAP 2  /* minimise reduce(upper - lower) */
+#define BF_OBJECTIVE_BOTH 3 /* maximise lb_weight * reduce(lower) - ub_weight * reduce(upper) */
+
 /* Library identity and diagnostics. */
 int bf_version(void);
 const char* bf_last_error_string(void);
@@ -448,6 +451,26 @@ int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain,
                                      float* best_lower, float* best_upper, float* best_metric,
                                      int steps, float lr, int spec_reduce, float soft_tau,
                                      void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+
+/* The alpha loop for the objectives that involve both bounds (objective="gap" | "both" of
+ * run_alpha_beta_crown_mlp, boundflow/runtime/alpha_beta_crown.py:807-818 with _objective_metric / _loss 535-612;
+ * these objectives carry no beta term, 763-785).  The caller passes PAIRED spec rows: C is [B, 2S, n_out] holding
+ * the S rows c_s of every domain followed by their negations -c_s, so that row S+s's lower bound is minus row s's
+ * upper bound and one lower-side sweep with one gradient sweep serves both bounds.  best_rows [B, 2S] receives, per
+ * domain, the rows of its best iteration: lower = best_rows[:, :S], upper = -best_rows[:, S:].  objective is
+ * BF_OBJECTIVE_GAP or BF_OBJECTIVE_BOTH, spec_reduce BF_REDUCE_MEAN, _MIN or _SOFTMIN (upper-side max / softmax are
+ * taken as min / softmin of the negated rows); lb_weight / ub_weight apply to BF_OBJECTIVE_BOTH.
+ * objective="upper" needs no entry point of its own: it is objective="lower" on the negated rows -C.
+ * Workspace: bf_chain_alpha_workspace_bytes(chain, B, 2 * S). */
+int bf_chain_alpha_crown_objective(const bf_chain* chain,
+                                   const float* C_paired,
+                                   const float* const* pre_l, const float* const* pre_u,
+                                   float* const* alpha, float* const* best_alpha,
+                                   const float* mid, const float* rad, int norm_p, float eps,
+                                   float* best_rows, float* best_metric,
+                                   int steps, float lr, int objective, int spec_reduce, float soft_tau,
+                                   float lb_weight, float ub_weight,
+                                   void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 /* Branching hint: per domain the ReLU (chain order) and neuron with the widest gap u - l among
  * unstable neurons (l < 0 < u); earlier ReLUs and lower indices win ties; -1/-1 when none.

@@ -486,9 +486,17 @@ def alpha_crown(
     optimize_beta: bool = False,
     return_beta: bool = False,
     soft_tau: float = 1.0,
+    objective: str = "lower",
+    lb_weight: float = 1.0,
+    ub_weight: float = 1.0,
 ):
     """Per-domain alpha (and optionally beta) optimisation, `run_alpha_beta_crown_mlp`
-    with `per_batch_params=True, objective="lower"` restated (alpha_beta_crown.py:716-923).
+    with `per_batch_params=True` restated (alpha_beta_crown.py:716-923).
+    Objectives (alpha_beta_crown.py:807-818): "lower" maximises reduce(lower), "upper" minimises
+    reduce(upper), "gap" minimises reduce(upper - lower), "both" maximises
+    lb_weight * reduce(lower) - ub_weight * reduce(upper); upper-side reductions take max / softmax
+    where the lower side takes min / softmin (787-805).  The beta term enters the lower objective
+    only (763-785): the other objectives run the alpha-only evaluation.
     With `optimize_beta` every ReLU also gets a per-domain beta >= 0 (start 0) whose
     split term -beta*s*[s != 0] is added to the lower coefficients
     (`_beta_to_relu_pre_add_coeff`, alpha_beta_crown.py:615-640) and which the same Adam
@@ -527,20 +535,33 @@ def alpha_crown(
     best_beta: List[torch.Tensor] = []
     for step in range(int(steps) + 1):
         add_l = None
-        if optimize_beta:
+        if optimize_beta and objective == "lower":
             add_l = [None if sf is None else -bt * sf * (sf != 0).to(dtype) for bt, sf in zip(betas, split_f)]
         lower, upper = crown_backward(layers, inp, trace, C, alpha=alphas, add_l=add_l)
-        # spec reductions of objective="lower" (alpha_beta_crown.py:787-805): mean | min | softmin, plus sum
-        if spec_reduce == "mean":
-            metric_b = lower.mean(dim=1)
-        elif spec_reduce == "sum":
-            metric_b = lower.sum(dim=1)
-        elif spec_reduce == "min":
-            metric_b = lower.min(dim=1).values
-        elif spec_reduce == "softmin":
-            metric_b = -float(soft_tau) * torch.logsumexp(-lower / float(soft_tau), dim=1)
-        else:
+
+        # spec reductions (alpha_beta_crown.py:787-805): mean | min | softmin, plus sum
+        def _reduce(x, direction):
+            if spec_reduce == "mean":
+                return x.mean(dim=1)
+            if spec_reduce == "sum":
+                return x.sum(dim=1)
+            if spec_reduce == "min":
+                return x.min(dim=1).values if direction == "min" else x.max(dim=1).values
+            if spec_reduce == "softmin":
+                tau = float(soft_tau)
+                return -tau * torch.logsumexp(-x / tau, dim=1) if direction == "min" else tau * torch.logsumexp(x / tau, dim=1)
             raise ValueError(spec_reduce)
+
+        if objective == "lower":
+            metric_b = _reduce(lower, "min")
+        elif objective == "upper":
+            metric_b = -_reduce(upper, "max")
+        elif objective == "gap":
+            metric_b = -_reduce(upper - lower, "max")
+        elif objective == "both":
+            metric_b = float(lb_weight) * _reduce(lower, "min") - float(ub_weight) * _reduce(upper, "max")
+        else:
+            raise ValueError(objective)
         if best_metric is None:
             best_metric = metric_b.detach().clone()
             best_lower, best_upper = lower.detach().clone(), upper.detach().clone()

@@ -585,11 +585,35 @@ def gen_spec_reduce() -> None:
     save("spec_reduce.npz", **out)
 
 
+def gen_objectives() -> None:
+    """The reference's alpha loop with the upper, gap and both objectives (alpha_beta_crown.py:535-612, 807-818),
+    per-domain parameters, on c1 (8 inputs) and c3 (8 inputs) after 1, 3 and 10 steps: mean reduction for each
+    objective, plus min and softmin for gap and both (weights 1.0 / 0.5 for both)."""
+    out = {}
+    for cfg, tau in (("c1", 0.5), ("c3", 50.0)):
+        wl = W.make_workload(cfg, batch=8)
+        m = ref_module(wl)
+        spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        a0 = adaptive_alpha(relu_pre)
+        out[f"{cfg}_tau"] = np.array(tau)
+        for obj, red in (("upper", "mean"), ("gap", "mean"), ("both", "mean"), ("upper", "min"), ("gap", "min"), ("both", "softmin"),
+                         ("gap", "softmin")):
+            for k in (1, 3, 10):
+                b, a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, steps=k, lr=0.1, per_batch_params=True, objective=obj,
+                                                        warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                        spec_reduce=red, soft_tau=tau, lb_weight=1.0, ub_weight=0.5)
+                out[f"{cfg}_{obj}_{red}_lower_{k}"] = b.lower
+                out[f"{cfg}_{obj}_{red}_upper_{k}"] = b.upper
+    save("objectives.npz", **out)
+
+
 GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fused_ibp": gen_spec_fused_ibp,
               "first_layer_certificate": gen_first_layer_certificate, "relu_influence": gen_relu_influence,
               "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha, "conv_alpha": gen_conv_alpha,
               "c1": gen_c1, "c2": gen_c2, "c3": gen_c3, "c4": gen_c4, "c5": gen_c5, "fused_region": gen_fused_region,
-              "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce}
+              "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce,
+              "objectives": gen_objectives}
 
 
 def main() -> None:

@@ -353,3 +353,23 @@ def test_min_and_softmin_spec_reductions(golden):
                                                soft_tau=float(g[f"{cfg}_tau"]))
                 assert_close(lo, g[f"{cfg}_{red}_lower_{k}"], f"{cfg} {red} lower after {k}")
                 assert_close(up, g[f"{cfg}_{red}_upper_{k}"], f"{cfg} {red} upper after {k}")
+
+
+OBJECTIVE_CASES = (("upper", "mean"), ("gap", "mean"), ("both", "mean"), ("upper", "min"), ("gap", "min"), ("both", "softmin"), ("gap", "softmin"))
+
+
+def test_upper_gap_both_objectives(golden):
+    """`run_alpha_beta_crown_mlp(objective="upper" | "gap" | "both")` of the reference (alpha_beta_crown.py:535-612, 807-818),
+    lb_weight 1.0 and ub_weight 0.5."""
+    g = golden("objectives.npz")
+    for cfg in ("c1", "c3"):
+        wl = W.make_workload(cfg, batch=8)
+        inp = O.box_input(wl.lo, wl.up)
+        trace = O.forward_ibp_trace(wl.layers, inp)
+        a0 = O.adaptive_alpha_init(trace)
+        for obj, red in OBJECTIVE_CASES:
+            for k in (1, 3, 10):
+                lo, up, _a, _t = O.alpha_crown(wl.layers, inp, wl.C, steps=k, lr=0.1, alpha0=a0, trace=trace, spec_reduce=red,
+                                               soft_tau=float(g[f"{cfg}_tau"]), objective=obj, lb_weight=1.0, ub_weight=0.5)
+                assert_close(lo, g[f"{cfg}_{obj}_{red}_lower_{k}"], f"{cfg} {obj}/{red} lower after {k}")
+                assert_close(up, g[f"{cfg}_{obj}_{red}_upper_{k}"], f"{cfg} {obj}/{red} upper after {k}")
