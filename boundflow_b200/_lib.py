@@ -89,6 +89,7 @@ SIGNATURES = {
     "bf_chain_alpha_beta_crown": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_beta_crown_reduce": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _f, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_crown_objective": (_i, [_p] * 8 + [_i, _f, _p, _p, _i, _f, _i, _i, _f, _f, _f, _p, _sz, _i, _i, _p]),
+    "bf_conv2d_dense_rows": (_i, [_p, _p, _p, _i, _p, _p] + [_i] * 12 + [_p]),
     "bf_branch_scores": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _p]),
     "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_shared_workspace_bytes": (_sz, [_p, _i, _i, _i]),

@@ -754,8 +754,10 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
     """Per-domain first-layer infeasibility certificate (`_is_infeasible_split_first_layer_convex_combo`,
     alpha_beta_crown.py:391-532, which the reference runs for batch size 1; here for every domain).
     Returns (infeasible int32 [B]: 1 found / 0 none / -1 not evaluated, best_value float [B],
-    n_halfspaces int32 [B]) as CUDA tensors.  The splits of the first ReLU over a Linear first layer
-    are used; a chain that starts otherwise, or no split on that ReLU, gives all zeros."""
+    n_halfspaces int32 [B]) as CUDA tensors.  The splits of the first ReLU over a Linear or Conv2d first
+    layer are used (conv: the half-space row of a split neuron is its filter placed in the input image,
+    alpha_beta_crown.py:325-387; only the rows of neurons that are split somewhere in the batch are formed);
+    a chain that starts otherwise, or no split on that ReLU, gives all zeros."""
     spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
     if lp_ball_of(spec) is not None:
         raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
@@ -763,13 +765,31 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
     best = torch.full((B,), float("inf"), dtype=torch.float32, device=device)
     count = torch.zeros(B, dtype=torch.int32, device=device)
     first = next((l for l in chain.layers if l.op != "flatten"), None)
-    if first is None or first.op != "linear" or not chain.relu_input_names or first.out_name != chain.relu_input_names[0]:
+    if first is None or first.op not in ("linear", "conv2d") or not chain.relu_input_names or first.out_name != chain.relu_input_names[0]:
         return infeasible, best, count
     raw = relu_split_state.get(chain.relu_input_names[0]) if relu_split_state else None
     if raw is None:
         return infeasible, best, count
     n1 = chain.relu_widths[0]
     sp, stride = _split_tensor(raw, B, n1, device, chain.relu_input_names[0])
+    if first.op == "conv2d":
+        cols = torch.nonzero((sp != 0).any(dim=0)).flatten()   # neurons split in at least one domain, ascending
+        if int(cols.numel()) == 0:
+            return infeasible, best, count
+        U = int(cols.numel())
+        rows = cols.to(torch.int32).contiguous()
+        W_rows = torch.empty(U, chain.n0, dtype=torch.float32, device=device)
+        b_rows = torch.empty(U, dtype=torch.float32, device=device)
+        (Ci, Hi, Wi), (Co, Ho, Wo) = first.in_shape, first.out_shape
+        _lib.check(chain.lib.bf_conv2d_dense_rows(
+            _lib.ptr(first.W), _lib.ptr(first.b), _lib.ptr(rows), U, _lib.ptr(W_rows), _lib.ptr(b_rows), int(Ci), int(Hi), int(Wi), int(Co), int(Ho),
+            int(Wo), int(first.W.shape[2]), int(first.W.shape[3]), int(first.stride[0]), int(first.stride[1]), int(first.padding[0]),
+            int(first.padding[1]), _stream_ptr(device)))
+        sp_sub = sp[:, cols].contiguous()
+        _lib.check(chain.lib.bf_first_layer_certificate(
+            _lib.ptr(sp_sub), 0 if stride == 0 else U, _lib.ptr(W_rows), _lib.ptr(b_rows), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible),
+            _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, U, chain.n0, _stream_ptr(device)))
+        return infeasible, best, count
     _lib.check(chain.lib.bf_first_layer_certificate(
         _lib.ptr(sp), stride, _lib.ptr(first.W), _lib.ptr(first.b), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible), _lib.ptr(best),
         _lib.ptr(count), int(steps), float(lr), float(tol), B, n1, chain.n0, _stream_ptr(device)))

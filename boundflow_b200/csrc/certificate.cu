@@ -162,3 +162,49 @@ extern "C" int bf_first_layer_certificate(const int8_t* split, int split_stride,
   BF_CHECK_LAUNCH("first_layer_cert_kernel");
   return BF_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Half-space rows of a Conv2d first layer: out[r, :] = the row of the layer's dense matrix that produces output
+// neuron rows[r] = (co, ho, wo), i.e. the filter W[co] placed at (ho*sh - ph, wo*sw - pw) in the [Ci,Hi,Wi] input
+// (zero elsewhere, taps outside the image dropped), and out_b[r] = bias[co].  One block per requested row.
+// ---------------------------------------------------------------------------
+namespace bf {
+
+__global__ void __launch_bounds__(256) conv_dense_rows_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                                                              const int* __restrict__ rows, float* __restrict__ out,
+                                                              float* __restrict__ out_b, int Ci, int Hi, int Wi, int Co, int Ho,
+                                                              int Wo, int kh, int kw, int sh, int sw, int ph, int pw) {
+  const int r = blockIdx.x;
+  const int j = rows[r];
+  const int n0 = Ci * Hi * Wi;
+  float* o = out + (size_t)r * n0;
+  const bool valid = j >= 0 && j < Co * Ho * Wo;  // an index outside the layer gives a zero row
+  const int co = valid ? j / (Ho * Wo) : 0;
+  const int rem = valid ? j - co * (Ho * Wo) : 0;
+  const int y0 = (rem / Wo) * sh - ph, x0 = (rem % Wo) * sw - pw;
+  for (int i = threadIdx.x; i < n0; i += blockDim.x) {
+    const int ci = i / (Hi * Wi);
+    const int p = i - ci * (Hi * Wi);
+    const int ky = p / Wi - y0, kx = p % Wi - x0;
+    float v = 0.f;
+    if (valid && ky >= 0 && ky < kh && kx >= 0 && kx < kw) v = W[(((size_t)co * Ci + ci) * kh + ky) * kw + kx];
+    o[i] = v;
+  }
+  if (threadIdx.x == 0 && out_b) out_b[r] = (valid && bias) ? bias[co] : 0.f;
+}
+
+}  // namespace bf
+
+extern "C" int bf_conv2d_dense_rows(const float* W, const float* bias, const int* rows, int n_rows, float* out_W, float* out_b,
+                                    int Ci, int Hi, int Wi, int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw,
+                                    bf_stream_t stream) {
+  BF_REQUIRE(W && rows && out_W, BF_E_INVALID, "bf_conv2d_dense_rows: null tensor");
+  BF_REQUIRE(n_rows > 0 && Ci > 0 && Hi > 0 && Wi > 0 && Co > 0 && Ho > 0 && Wo > 0 && kh > 0 && kw > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0,
+             BF_E_INVALID, "bf_conv2d_dense_rows: bad sizes");
+  BF_REQUIRE((long long)Ci * Hi * Wi < 2147483647LL && (long long)Co * Ho * Wo < 2147483647LL, BF_E_UNSUPPORTED,
+             "bf_conv2d_dense_rows: layer too large");
+  bf::conv_dense_rows_kernel<<<n_rows, 256, 0, bf::as_stream(stream)>>>(W, bias, rows, out_W, out_b, Ci, Hi, Wi, Co, Ho, Wo, kh, kw, sh, sw,
+                                                                         ph, pw);
+  BF_CHECK_LAUNCH("conv_dense_rows_kernel");
+  return BF_OK;
+}

@@ -209,7 +209,7 @@ int launch_ibp_conv2d(const float* in_a, const float* in_b, int in_mode, int rel
                       float* out_u, int* infeasible, int B, const bf_layer_desc& L, cudaStream_t stream);
 int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                             const float* W, const float* bias, float* A_prev, float* delta, int accumulate, int M, int S,
-                            const bf_layer_desc& L, void* scratch, cudaStream_t stream);
+                            const bf_layer_desc& L, void* scratch, cudaStream_t stream, const float* add = nullptr);
 size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L);
 int launch_onehot_conv_rows(int first, const float* W, const float* bias, float* A_prev, float* delta, int M, int S,
                             const bf_layer_desc& L, cudaStream_t stream);
@@ -591,10 +591,9 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
       if (last) fused_concretize = true;
       curA = dst;
     } else {
-      BF_REQUIRE(ad == nullptr, BF_E_UNSUPPORTED, "bf_chain_crown: beta terms on conv layers are not supported");
       float* dst = ws.buf[toggle];
       rc = bf::launch_crown_bwd_conv2d(curA, dpos, dneg, epos, eneg, L.W, L.bias, dst, ws.cacc, have_c, M, S, L,
-                                       ws.conv_scratch, stream);
+                                       ws.conv_scratch, stream, ad);
       curA = dst;
     }
     if (rc != BF_OK) return rc;

@@ -11,7 +11,7 @@ namespace bf {
 
 int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                             const float* W, const float* bias, float* A_prev, float* delta, int accumulate, int M, int S,
-                            const bf_layer_desc& L, void* scratch, cudaStream_t stream);
+                            const bf_layer_desc& L, void* scratch, cudaStream_t stream, const float* add = nullptr);
 size_t crown_bwd_conv2d_scratch_bytes(int M, const bf_layer_desc& L);
 int launch_conv_forward_rows(const float* in, const float* W, const float* bias, float* out, int M, const bf_layer_desc& L,
                              cudaStream_t stream);
@@ -98,8 +98,7 @@ static int alpha_bwd_layer(const bf_chain* c, const AlphaWs& ws, int layer, cons
   const bf_layer_desc& L = c->layers[layer];
   if (L.op == BF_OP_LINEAR)
     return dispatch_bwd(c, layer, A, dpos, dneg, epos, eneg, add, dst, ws.cacc, accumulate, mid, rad, partial, side, M, S, ptiles, stream);
-  BF_REQUIRE(add == nullptr, BF_E_UNSUPPORTED, "beta terms on conv layers are not supported");
-  return launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, L.W, L.bias, dst, ws.cacc, accumulate, M, S, L, ws.conv_scratch, stream);
+  return launch_crown_bwd_conv2d(A, dpos, dneg, epos, eneg, L.W, L.bias, dst, ws.cacc, accumulate, M, S, L, ws.conv_scratch, stream, add);
 }
 
 static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int side, bool keep_A0, bool use_add,
@@ -165,11 +164,11 @@ static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* cons
                             ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r],
                             with_beta ? ws.gsum[r] : nullptr, M, S, stream);
     } else {
-      BF_REQUIRE(!with_beta, BF_E_UNSUPPORTED, "beta terms on conv layers are not supported");
       float* g = ws.H[r & 1];
       rc = launch_conv_forward_rows(hprev, L.W, L.bias, g, M, L, stream);
       if (rc != BF_OK) return rc;
-      rc = launch_relu_adjoint_rows(g, ws.Ahat[r], ws.sl[r], ws.au[r], ws.bu[r], pre_l[r], pre_u[r], ws.grad[r], B, S, L.n_out, stream);
+      rc = launch_relu_adjoint_rows(g, ws.Ahat[r], ws.sl[r], ws.au[r], ws.bu[r], pre_l[r], pre_u[r], ws.grad[r],
+                                    with_beta ? ws.gsum[r] : nullptr, B, S, L.n_out, stream);
     }
     if (rc != BF_OK) return rc;
   }
@@ -214,7 +213,6 @@ static int alpha_common_checks(const char* who, const bf_chain* chain, const voi
   BF_REQUIRE(norm_p == BF_NORM_BOX || eps >= 0.f, BF_E_INVALID, "%s: negative eps", who);
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL, BF_E_INVALID, "%s: bad B/S", who);
   BF_REQUIRE(chain->affine_relu_alternating, BF_E_UNSUPPORTED, "%s: only affine (relu affine)* chains are supported", who);
-  BF_REQUIRE(!(with_beta && chain->has_conv), BF_E_UNSUPPORTED, "%s: beta terms on conv layers are not supported", who);
   const size_t need = bf::alpha_ws_layout(chain, B, S, with_beta, workspace, ws);
   BF_REQUIRE(workspace_bytes >= need, BF_E_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, workspace_bytes);
   return BF_OK;
@@ -456,7 +454,6 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   BF_REQUIRE(B > 0 && S > 0 && (long long)B * S < 2147483647LL && steps >= 0, BF_E_INVALID, "%s: bad B/S/steps", who);
   BF_REQUIRE(chain->affine_relu_alternating, BF_E_UNSUPPORTED, "%s: only affine (relu affine)* chains are supported", who);
   const bool with_beta = beta != nullptr;
-  BF_REQUIRE(!(with_beta && chain->has_conv), BF_E_UNSUPPORTED, "%s: beta terms on conv layers are not supported", who);
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
   bf::AlphaWs ws;
   bf::SharedWs sw;

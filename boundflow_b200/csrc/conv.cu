@@ -141,7 +141,7 @@ int launch_conv_forward_rows(const float* in, const float* W, const float* bias,
 
 // ---------------------------------------------------------------------------
 // ReLU backward on coefficient rows, in front of the transposed convolution:
-//   Lam = A * slope_sel ;  delta (+)= sum_k A*icpt_sel + Lam*bias[channel]
+//   Lam = A * slope_sel (+ add, the split term of beta-CROWN) ;  delta (+)= sum_k A*icpt_sel + Lam*bias[channel]
 // grid (row, column chunk): a block streams RELU_ROWS_CHUNK columns of one row
 // and leaves one partial sum (fixed summation order); sum_partials_kernel adds
 // the chunks of a row.
@@ -150,8 +150,9 @@ constexpr int RELU_ROWS_CHUNK = 4096;
 
 __global__ void __launch_bounds__(256) relu_bwd_rows_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
                                                             const float* __restrict__ dneg, const float* __restrict__ epos,
-                                                            const float* __restrict__ eneg, const float* __restrict__ bias,
-                                                            int chan_size, float* __restrict__ Lam, float* __restrict__ partial,
+                                                            const float* __restrict__ eneg, const float* __restrict__ add,
+                                                            const float* __restrict__ bias, int chan_size,
+                                                            float* __restrict__ Lam, float* __restrict__ partial,
                                                             float* __restrict__ delta, int accumulate, int chunk, int S, int n,
                                                             int vec) {
   const int m = blockIdx.x;
@@ -177,6 +178,10 @@ __global__ void __launch_bounds__(256) relu_bwd_rows_kernel(const float* __restr
           lam[c] = v[c] * (sel ? p[c] : q[c]);
           acc = fmaf(v[c], sel ? ep[c] : en[c], acc);
         }
+        if (add) {
+          const float4 a4 = *reinterpret_cast<const float4*>(add + off + k);
+          lam[0] += a4.x; lam[1] += a4.y; lam[2] += a4.z; lam[3] += a4.w;
+        }
       }
       if (bias) {
         int ch = k / chan_size, rem = k - ch * chan_size;
@@ -197,6 +202,7 @@ __global__ void __launch_bounds__(256) relu_bwd_rows_kernel(const float* __restr
         lam = v * (sel ? dpos[off + k] : dneg[off + k]);
         const float e = sel ? (epos ? epos[off + k] : 0.f) : (eneg ? eneg[off + k] : 0.f);
         acc = fmaf(v, e, acc);
+        if (add) lam += add[off + k];
       }
       if (bias) acc = fmaf(lam, __ldg(bias + k / chan_size), acc);
       if (Lam) Lam[(size_t)m * n + k] = lam;
@@ -617,7 +623,7 @@ static int launch_convT(const ConvTArgs& g0, cudaStream_t stream) {
 
 int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                             const float* W, const float* bias, float* A_prev, float* delta, int accumulate, int M, int S,
-                            const bf_layer_desc& L, void* scratch, cudaStream_t stream) {
+                            const bf_layer_desc& L, void* scratch, cudaStream_t stream, const float* add = nullptr) {
   const float* lam = A;
   const bool need_pro = (dpos != nullptr) || (bias != nullptr) || (delta != nullptr && !accumulate);
   if (need_pro) {
@@ -628,12 +634,12 @@ int launch_crown_bwd_conv2d(const float* A, const float* dpos, const float* dneg
     const int nchunks = ceil_div(L.n_out, chunk);
     float* partial = (delta && nchunks > 1) ? reinterpret_cast<float*>(static_cast<char*>(scratch) + relu_rows_lam_bytes(M, L.n_out)) : nullptr;
     BF_REQUIRE(nchunks <= 65535, BF_E_UNSUPPORTED, "conv backward: layer too wide");
-    const void* ptrs[] = {A, dpos, dneg, epos, eneg, lam_out};
+    const void* ptrs[] = {A, dpos, dneg, epos, eneg, add, lam_out};
     int vec = (L.n_out % 4 == 0) ? 1 : 0;
     for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = 0;
     dim3 grid(M, nchunks);
     timing_begin(T_RELU_ROWS, stream);
-    relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, bias, L.Ho * L.Wo, lam_out, partial, delta, accumulate,
+    relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, dpos ? add : nullptr, bias, L.Ho * L.Wo, lam_out, partial, delta, accumulate,
                                                   chunk, S, L.n_out, vec);
     // rows in (+ out when a ReLU scales them) and the slope / intercept vectors of every domain
     timing_end(T_RELU_ROWS, stream, (lam_out ? 8.0 : 4.0) * (double)M * L.n_out + (dpos ? 12.0 * (double)(M / S) * L.n_out : 0.0),
@@ -1002,7 +1008,7 @@ extern "C" int bf_crown_relu_bwd(const float* A, int side, const float* alpha_u,
   for (const void* q : ptrs) if (reinterpret_cast<uintptr_t>(q) & 15u) vec = 0;
   cudaStream_t stream = bf::as_stream(stream_);
   dim3 grid(M, nchunks);
-  bf::relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, nullptr, 1, A_prev, partial, delta, accumulate,
+  bf::relu_bwd_rows_kernel<<<grid, 256, 0, stream>>>(A, dpos, dneg, epos, eneg, nullptr, nullptr, 1, A_prev, partial, delta, accumulate,
                                                     bf::RELU_ROWS_CHUNK, S, n, vec);
   BF_CHECK_LAUNCH("relu_bwd_rows_kernel");
   if (partial) return bf::launch_sum_partials(accumulate ? delta : nullptr, partial, nchunks, delta, M, stream);

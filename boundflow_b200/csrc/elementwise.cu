@@ -461,34 +461,38 @@ int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStrea
 
 // ---- gradient sweep pieces for layers without a fused epilogue (conv) --------------------------------
 // Adjoint step of one ReLU on rows: g = layer output at the adjoint point (in), h = d*g + e (out, in place),
-// grad[b,j] += sum over the domain's rows of [unstable][Ahat >= 0] Ahat*g.  One thread per (domain, neuron),
+// grad[b,j] += sum over the domain's rows of [unstable][Ahat >= 0] Ahat*g and, with beta parameters,
+// gsum[b,j] += sum over the domain's rows of g (the beta gradient is -split * gsum).  One thread per (domain, neuron),
 // rows of the domain in order: no atomics.
 __global__ void __launch_bounds__(256) relu_adjoint_rows_kernel(float* __restrict__ G, const float* __restrict__ Ahat,
                                                                 const float* __restrict__ dpos, const float* __restrict__ dneg,
                                                                 const float* __restrict__ eneg, const float* __restrict__ pre_l,
-                                                                const float* __restrict__ pre_u, float* __restrict__ grad, int S,
-                                                                int n) {
+                                                                const float* __restrict__ pre_u, float* __restrict__ grad,
+                                                                float* __restrict__ gsum, int S, int n) {
   const int b = blockIdx.x;
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   if (j >= n) return;
   const size_t o = (size_t)b * n + j;
   const float dp = dpos[o], dn = dneg[o], en = eneg ? eneg[o] : 0.f;
   const bool amb = pre_l[o] < 0.f && pre_u[o] > 0.f;
-  float acc = 0.f;
+  float acc = 0.f, gs = 0.f;
   for (int s = 0; s < S; ++s) {
     const size_t i = ((size_t)b * S + s) * n + j;
     const float a = Ahat[i], g = G[i];
     const bool sel = a >= 0.f;
+    gs += g;
     if (sel && amb) acc = fmaf(a, g, acc);
     G[i] = sel ? dp * g : fmaf(dn, g, en);
   }
   grad[o] += acc;
+  if (gsum) gsum[o] += gs;
 }
 
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
-                             const float* pre_l, const float* pre_u, float* grad, int B, int S, int n, cudaStream_t stream) {
+                             const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
+                             cudaStream_t stream) {
   dim3 grid(B, ceil_div(n, 256));
-  relu_adjoint_rows_kernel<<<grid, 256, 0, stream>>>(G, Ahat, dpos, dneg, eneg, pre_l, pre_u, grad, S, n);
+  relu_adjoint_rows_kernel<<<grid, 256, 0, stream>>>(G, Ahat, dpos, dneg, eneg, pre_l, pre_u, grad, gsum, S, n);
   BF_CHECK_LAUNCH("relu_adjoint_rows_kernel");
   return BF_OK;
 }

@@ -86,7 +86,8 @@ int launch_adam_step(float* alpha, float* m, float* v, float* grad, const int* i
 int launch_scale_copy(const float* src, float scale, float* dst, long long n, cudaStream_t stream);
 int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStream_t stream);
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
-                             const float* pre_l, const float* pre_u, float* grad, int B, int S, int n, cudaStream_t stream);
+                             const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
+                             cudaStream_t stream);
 int launch_h0_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, cudaStream_t stream);
 // windowed coefficient rows of identity-row sweeps on conv layers (conv.cu)
 struct WindowGeom {

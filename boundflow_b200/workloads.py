@@ -249,6 +249,52 @@ def make_certificate_cases(seed: int = 1009):
     return module, layers, x, lo, up, cases
 
 
+def make_conv_certificate_cases(seed: int = 1013):
+    """Small CNN (1x6x6 -> conv 4 channels k3 s1 p1 -> ReLU -> flatten -> Linear 5) and split rows on its first
+    ReLU for the first-layer infeasibility certificate over a Conv2d first layer: filter 1 is minus filter 0 (shifted
+    down) and filter 2 is minus twice filter 0, so at one pixel "channel 0 active" contradicts "channel 1 active"
+    (uniform weights) and "channel 2 active" (needs the optimiser); a border pixel exercises the taps that fall into
+    the padding.  Returns (module, layers, x, lo, up, cases) with cases = list of (name, int8 split row [144])."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    Co, H = 4, 6
+    Wc = torch.randn(Co, 1, 3, 3, generator=g) * math.sqrt(2.0 / 9)
+    bc = torch.randn(Co, generator=g) * 0.1
+    x = torch.rand(1, 1, H, H, generator=g)
+    z0 = torch.nn.functional.conv2d(x, Wc[:1], None, 1, 1)[0, 0]
+    bc[0] = -z0[2, 3]  # channel 0 is zero at pixel (2,3) at the centre: unstable over the box
+    Wc[1], bc[1] = -Wc[0], -bc[0] - 0.05
+    Wc[2], bc[2] = -2.0 * Wc[0], -2.0 * bc[0] - 0.09
+    W2 = torch.randn(5, Co * H * H, generator=g) * math.sqrt(2.0 / (Co * H * H))
+    b2 = torch.randn(5, generator=g) * 0.1
+    lo, up = (x - 0.3).clamp(0, 1), (x + 0.3).clamp(0, 1)
+    params = {"Wc": Wc, "bc": bc, "W2": W2, "b2": b2}
+    ops = [TaskOp("conv2d", "conv1", ["input", "Wc", "bc"], ["h1"], attrs={"stride": 1, "padding": 1}),
+           TaskOp("relu", "relu1", ["h1"], ["r1"]), TaskOp("flatten", "flat", ["r1"], ["f1"], attrs={"start_dim": 1, "end_dim": -1}),
+           TaskOp("linear", "fc", ["f1", "W2", "b2"], ["out"])]
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    module = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": params})
+    layers = [{"op": "conv2d", "W": Wc, "b": bc, "stride": (1, 1), "padding": (1, 1)}, {"op": "relu"}, {"op": "flatten"},
+              {"op": "linear", "W": W2, "b": b2}]
+
+    def row(*entries):
+        r = torch.zeros(Co * H * H, dtype=torch.int8)
+        for (c, h, w, v) in entries:
+            r[(c * H + h) * H + w] = v
+        return r
+
+    cases = [
+        ("no_split", row()),
+        ("one_feasible", row((0, 2, 3, 1))),
+        ("pair_contradiction_uniform_weights", row((0, 2, 3, 1), (1, 2, 3, 1))),
+        ("pair_contradiction_needs_steps", row((0, 2, 3, 1), (2, 2, 3, 1))),
+        ("border_pixel_contradiction", row((0, 0, 0, 1), (1, 0, 0, 1))),
+        ("different_pixels", row((0, 2, 3, 1), (1, 4, 1, 1))),
+        ("triple_with_bystander", row((0, 2, 3, 1), (2, 2, 3, 1), (3, 1, 1, -1))),
+        ("feasible_pair", row((0, 2, 3, 1), (3, 1, 1, -1))),
+    ]
+    return module, layers, x, lo, up, cases
+
+
 def make_graph_cases(seed: int = 1011):
     """Small graphs that are not chains, shaped like the reference's end-to-end fixtures
     (tests/test_phase7a_pr12_e2e_crown_runtime.py:98-239): a residual CNN block with a projection skip

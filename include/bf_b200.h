@@ -285,6 +285,18 @@ int bf_first_layer_certificate(const int8_t* split, int split_stride, const floa
                                int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
                                bf_stream_t stream);
 
+/* Half-space rows of a Conv2d FIRST layer for the certificate above
+ *   replaces the conv2d branch of _collect_first_layer_split_halfspaces, boundflow/runtime/alpha_beta_crown.py:325-387
+ *            (one-hot row through DenseLinearOperator.conv2d_right(...).to_dense()).
+ * rows int32 [n_rows]: flat indices (co*Ho + ho)*Wo + wo of the layer's outputs, usually the split neurons of the
+ * batch in ascending order; out_W [n_rows, Ci*Hi*Wi] receives the filter W[co] (OIHW) placed at
+ * (ho*sh - ph, wo*sw - pw), out_b [n_rows] or NULL receives bias[co] (0 without bias).  The result, with the split
+ * columns gathered in the same order, is what bf_first_layer_certificate takes as W1 / b1 / split.  groups = 1,
+ * dilation = 1. */
+int bf_conv2d_dense_rows(const float* W, const float* bias, const int* rows, int n_rows, float* out_W, float* out_b,
+                         int Ci, int Hi, int Wi, int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw,
+                         bf_stream_t stream);
+
 /* Verdict per domain: proven iff min over spec rows of the lower bound >= threshold - tol.
  *   replaces the node test in solve_bab_mlp, boundflow/runtime/bab.py:881-895
  *            (bounds.lower.min() then >=: a NaN bound never proves a node, and neither does it here).

@@ -325,6 +325,16 @@ def conv2d_backward(A, b, W, bias, stride, padding, in_shape, out_shape):
     return prev.reshape(B, S, -1), b_out
 
 
+def conv2d_dense_rows(W, bias, stride, padding, in_shape, out_shape):
+    """Dense matrix [C_o*H_o*W_o, C_i*H_i*W_i] and bias vector of a Conv2d layer, the rows that the reference's
+    first-layer certificate builds one at a time for a conv first layer (alpha_beta_crown.py:346-387: a one-hot
+    coefficient row through `DenseLinearOperator.conv2d_right(...).to_dense()`, bias = bias[channel])."""
+    n1 = int(out_shape[0]) * int(out_shape[1]) * int(out_shape[2])
+    eye = torch.eye(n1, dtype=W.dtype).reshape(1, n1, n1)
+    rows, bvec = conv2d_backward(eye, torch.zeros(1, n1, dtype=W.dtype), W, bias, stride, padding, in_shape, out_shape)
+    return rows[0], bvec[0]
+
+
 def concretize(inp: InputSet, A, b, side: str):
     """`BoxPerturbation.concretize_affine`, perturbation.py:327-359:
     lower = A.mid - |A|.rad + b, upper = A.mid + |A|.rad + b.  (L-inf ball:

@@ -247,6 +247,29 @@ def gen_first_layer_certificate() -> None:
     save("first_layer_certificate.npz", **out)
 
 
+def gen_conv_certificate() -> None:
+    """`_is_infeasible_split_first_layer_convex_combo` over a Conv2d first layer (alpha_beta_crown.py:325-387) on
+    the cases of workloads.make_conv_certificate_cases."""
+    from boundflow.runtime.alpha_beta_crown import _is_infeasible_split_first_layer_convex_combo
+
+    module, _layers, _x, lo, up, cases = W.make_conv_certificate_cases()
+    src = module.get_entry_task()
+    ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+    task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    m = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(module.bindings["params"])})
+    spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+    out = {"names": np.array([n for n, _ in cases])}
+    flags, values = [], []
+    for _name, row in cases:
+        bad, reason, cert = _is_infeasible_split_first_layer_convex_combo(m, spec, relu_split_state={"h1": row.reshape(1, 4, 6, 6)})
+        flags.append(bool(bad))
+        values.append(float(cert["max_value"]) if cert is not None else np.nan)
+    out["infeasible"] = np.array(flags)
+    out["max_value"] = np.array(values)
+    out["split_rows"] = np.stack([r.numpy() for _n, r in cases])
+    save("conv_certificate.npz", **out)
+
+
 def gen_relu_influence() -> None:
     """`run_crown_ibp_mlp_with_relu_influence_from_forward_trace` on the MLP c1 (8 inputs) and the CNN c2 (3 inputs)."""
     from boundflow.runtime.crown_ibp import run_crown_ibp_mlp_with_relu_influence_from_forward_trace
@@ -319,6 +342,41 @@ def gen_conv_alpha() -> None:
         bs, _st, _ = run_alpha_crown_mlp(m, spec, linear_spec_C=wl.C, steps=steps, lr=0.1)
         out[f"shared_lower_{steps}"], out[f"shared_upper_{steps}"] = bs.lower, bs.upper
     save("conv_alpha.npz", **out)
+
+
+def gen_conv_beta() -> None:
+    """alpha-beta-CROWN on the CNN c2 (4 inputs) with three split neurons per ReLU and input (two conv ReLUs and
+    one Linear ReLU): the reference's per-domain function after 1, 3 and 8 steps, and its shared-parameter mode
+    after 3 steps.  The split assignment is stored with the outputs."""
+    wl = W.make_workload("c2", batch=4)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    g = torch.Generator().manual_seed(3)
+    splits = {}
+    for name, st in relu_pre.items():
+        s8 = torch.zeros(st.lower.shape, dtype=torch.int8)
+        fl, fu, fs = st.lower.reshape(4, -1), st.upper.reshape(4, -1), s8.view(4, -1)
+        for b in range(4):
+            idx = torch.nonzero((fl[b] < 0) & (fu[b] > 0)).flatten()
+            pick = idx[torch.randint(0, len(idx), (3,), generator=g)]
+            fs[b, pick] = (torch.randint(0, 2, (3,), generator=g) * 2 - 1).to(torch.int8)
+        splits[name] = s8
+    _env, pre_split = _forward_ibp_trace_mlp(m, spec, relu_split_state=splits)
+    a0 = adaptive_alpha(pre_split)
+    out = {"input_checksum": checksum(wl.x, wl.C, *[p for p in wl.module.bindings["params"].values()])}
+    for name, s8 in splits.items():
+        out[f"split_{name}"] = s8.reshape(4, -1)
+    for steps in (1, 3, 8):
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, relu_split_state=splits, steps=steps, lr=0.1,
+                                                 warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                 per_batch_params=True, objective="lower", spec_reduce="mean")
+        out[f"per_domain_lower_{steps}"], out[f"per_domain_upper_{steps}"] = b.lower, b.upper
+        for name, v in bt.beta_by_relu_input.items():
+            out[f"per_domain_beta_{name}_{steps}"] = v.reshape(4, -1)
+    b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=False)
+    out["shared_lower_3"], out["shared_upper_3"] = b.lower, b.upper
+    save("conv_beta.npz", **out)
 
 
 def gen_c1() -> None:
@@ -613,7 +671,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "graph_cases": gen_graph_cases, "lp_alpha": gen_lp_alpha, "conv_alpha": gen_conv_alpha,
               "c1": gen_c1, "c2": gen_c2, "c3": gen_c3, "c4": gen_c4, "c5": gen_c5, "fused_region": gen_fused_region,
               "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce,
-              "objectives": gen_objectives}
+              "objectives": gen_objectives, "conv_beta": gen_conv_beta,
+              "conv_certificate": gen_conv_certificate}
 
 
 def main() -> None:

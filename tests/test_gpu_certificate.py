@@ -63,3 +63,51 @@ def test_shared_row_many_halfspaces_and_single_node_precheck(dev):
     bounds, a, b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["feasible_pair"].unsqueeze(0).to(dev)},
                                                    steps=2, lr=0.1, per_batch_params=True)
     assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 5)
+
+
+def test_conv_first_layer_cases_match_reference_golden_and_oracle(dev, golden):
+    """Conv2d first layer: the half-space rows of the neurons that are split somewhere in the batch come from
+    `bf_conv2d_dense_rows` (checked against the oracle's dense matrix), the certificate itself from the same kernel."""
+    from boundflow_b200 import _lib
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import first_layer_certificate, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    g = golden("conv_certificate.npz")
+    module, layers, _x, lo, up, cases = W.make_conv_certificate_cases()
+    conv = layers[0]
+    Wd, bd = O.conv2d_dense_rows(conv["W"], conv["b"], conv["stride"], conv["padding"], (1, 6, 6), (4, 6, 6))
+    # the row kernel on every neuron plus one index outside the layer (zero row)
+    lib = _lib.load()
+    idx = torch.arange(145, dtype=torch.int32, device=dev)
+    rows = torch.full((145, 36), float("nan"), device=dev)
+    rb = torch.full((145,), float("nan"), device=dev)
+    Wc, bc = conv["W"].to(dev).contiguous(), conv["b"].to(dev).contiguous()
+    _lib.check(lib.bf_conv2d_dense_rows(Wc.data_ptr(), bc.data_ptr(), idx.data_ptr(), 145, rows.data_ptr(), rb.data_ptr(), 1, 6, 6, 4, 6, 6, 3, 3,
+                                        1, 1, 1, 1, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(rows[:144].cpu(), Wd) and torch.equal(rb[:144].cpu(), bd)
+    assert float(rows[144].abs().max()) == 0.0 and float(rb[144]) == 0.0
+    D = len(cases)
+    spec = InputSpec.box(value_name="input", lower=lo.expand(D, -1, -1, -1).contiguous().to(dev), upper=up.expand(D, -1, -1, -1).contiguous().to(dev))
+    split = torch.stack([r for _n, r in cases]).reshape(D, 4, 6, 6).to(dev)
+    flags, best, count = first_layer_certificate(module, spec, {"h1": split})
+    flags, best, count = flags.cpu(), best.cpu(), count.cpu()
+    inp = O.box_input(lo.reshape(1, -1), up.reshape(1, -1))
+    for k, (name, row) in enumerate(cases):
+        assert int(count[k]) == int((row != 0).sum()), name
+        assert int(flags[k]) == int(bool(g["infeasible"][k])), name
+        o_bad, o_best = O.first_layer_certificate(Wd, bd, inp, row)
+        assert bool(flags[k]) == o_bad, name
+        if o_best is not None:
+            assert abs(float(best[k]) - o_best) <= 0.25 * abs(o_best) + 1e-4, (name, float(best[k]), o_best)
+    # the single-node pre-check of the alpha-beta function on a conv first layer
+    case = dict(cases)
+    spec1 = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    _bounds, a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["border_pixel_contradiction"].reshape(1, 4, 6, 6).to(dev)},
+                                                    steps=2, lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "infeasible" and not a.alpha_by_relu_input
+    bounds, _a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["feasible_pair"].reshape(1, 4, 6, 6).to(dev)},
+                                                    steps=2, lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 5)

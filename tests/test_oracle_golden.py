@@ -373,3 +373,47 @@ def test_upper_gap_both_objectives(golden):
                                                soft_tau=float(g[f"{cfg}_tau"]), objective=obj, lb_weight=1.0, ub_weight=0.5)
                 assert_close(lo, g[f"{cfg}_{obj}_{red}_lower_{k}"], f"{cfg} {obj}/{red} lower after {k}")
                 assert_close(up, g[f"{cfg}_{obj}_{red}_upper_{k}"], f"{cfg} {obj}/{red} upper after {k}")
+
+
+def _conv_beta_splits(g, wl):
+    shapes = {"h1": (16, 14, 14), "h2": (32, 7, 7), "h3": (100,)}
+    return [torch.from_numpy(np.asarray(g[f"split_{n}"])).to(torch.int8).reshape((4,) + shapes[n]) for n in wl.relu_names]
+
+
+def test_alpha_beta_crown_on_a_conv_chain(golden):
+    """`run_alpha_beta_crown_mlp(relu_split_state=...)` of the reference on the CNN c2: beta parameters on conv ReLUs
+    (alpha_beta_crown.py:615-640 with the conv backward step crown_ibp.py:1106-1173)."""
+    g = golden("conv_beta.npz")
+    wl = W.make_workload("c2", batch=4)
+    assert np.allclose(workload_checksum(wl), g["input_checksum"], rtol=1e-12, atol=0)
+    assert list(wl.relu_names) == ["h1", "h2", "h3"]
+    splits = _conv_beta_splits(g, wl)
+    inp = O.box_input(wl.lo, wl.up)
+    trace = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+    a0 = O.adaptive_alpha_init(trace)
+    for steps in (1, 3, 8):
+        lo, up, _a, beta, _t = O.alpha_crown(wl.layers, inp, wl.C, steps=steps, lr=0.1, alpha0=a0, trace=trace, splits=splits,
+                                             optimize_beta=True, return_beta=True)
+        assert_close(lo, g[f"per_domain_lower_{steps}"], f"per-domain lower {steps}")
+        assert_close(up, g[f"per_domain_upper_{steps}"], f"per-domain upper {steps}")
+        for n, b in zip(wl.relu_names, beta):
+            assert_close(b.reshape(4, -1), g[f"per_domain_beta_{n}_{steps}"], f"beta {n} after {steps}", atol=1e-5)
+    lo, up, _a, _b, _t = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=3, lr=0.1, trace=trace, splits=splits, optimize_beta=True)
+    assert_close(lo, g["shared_lower_3"], "shared lower 3")
+    assert_close(up, g["shared_upper_3"], "shared upper 3")
+
+
+def test_first_layer_certificate_over_a_conv_first_layer(golden):
+    """The conv2d branch of the reference's half-space collection (alpha_beta_crown.py:325-387)."""
+    g = golden("conv_certificate.npz")
+    _module, layers, _x, lo, up, cases = W.make_conv_certificate_cases()
+    assert [n for n, _ in cases] == [str(n) for n in g["names"]]
+    conv = layers[0]
+    Wd, bd = O.conv2d_dense_rows(conv["W"], conv["b"], conv["stride"], conv["padding"], (1, 6, 6), (4, 6, 6))
+    inp = O.box_input(lo.reshape(1, -1), up.reshape(1, -1))
+    for k, (name, row) in enumerate(cases):
+        assert (row.numpy() == g["split_rows"][k]).all()
+        bad, best = O.first_layer_certificate(Wd, bd, inp, row)
+        assert bad == bool(g["infeasible"][k]), name
+        if bad:
+            assert best < -1e-6 and abs(best - float(g["max_value"][k])) <= 0.5 * abs(float(g["max_value"][k])) + 1e-3, name
