@@ -421,11 +421,10 @@ def run_crown_ibp_mlp(
     if relu_pre_add_coeff_u:
         raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
     if needs_graph_path(module):
-        if relu_alpha or relu_pre_add_coeff_l or relu_split_state:
-            raise NotImplementedError("alpha / beta / split inputs are supported on chain graphs only")
         from .dag import run_crown_ibp_dag
 
-        return run_crown_ibp_dag(module, input_spec, linear_spec_C=linear_spec_C, output_value=output_value)
+        return run_crown_ibp_dag(module, input_spec, linear_spec_C=linear_spec_C, output_value=output_value, relu_alpha=relu_alpha,
+                                 relu_pre_add_coeff_l=relu_pre_add_coeff_l, relu_split_state=relu_split_state)
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
@@ -796,6 +795,32 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
     return infeasible, best, count
 
 
+def _run_alpha_beta_crown_graph(module, input_spec, *, linear_spec_C, relu_split_state, steps, lr, alpha_init, beta_init, warm_start_alpha,
+                                warm_start_beta, objective, spec_reduce, per_batch_params, optimize_beta):
+    """`run_alpha_beta_crown_mlp` on a graph that is not a chain (residual add, concat, fan-out): the per-domain loop
+    of `dag.alpha_beta_crown_dag`.  The reference accepts these graphs because its sweep is the generic graph backward
+    under autograd (crown_ibp.py:1669-2051)."""
+    from .dag import alpha_beta_crown_dag
+
+    if objective != "lower" or not per_batch_params:
+        raise NotImplementedError("the graph path of the CUDA backend implements objective='lower' with per_batch_params=True")
+    a0 = getattr(warm_start_alpha, "alpha_by_relu_input", None) if warm_start_alpha is not None else None
+    b0 = getattr(warm_start_beta, "beta_by_relu_input", None) if warm_start_beta is not None else None
+    if relu_split_state and not optimize_beta and b0 is not None and any(float(torch.as_tensor(b).abs().max()) != 0.0 for b in b0.values()):
+        raise NotImplementedError("a frozen non-zero beta is not supported; pass optimize_beta=None/True")
+    best_l, best_u, best_a, best_b, tr = alpha_beta_crown_dag(module, input_spec, linear_spec_C, steps=steps, lr=lr, alpha0=a0, alpha_init=alpha_init,
+                                                              relu_split_state=relu_split_state, optimize_beta=optimize_beta, beta0=b0,
+                                                              beta_init=beta_init, spec_reduce=spec_reduce)
+    dev = normalize_input_spec(input_spec).center.device
+    B = tr.B
+    bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
+    names = list(best_a)
+    a_state = AlphaState({n: best_a[n].reshape((B,) + tuple(tr.shape[n])).to(dev) for n in names})
+    b_state = BetaState({n: best_b[n].reshape((B,) + tuple(tr.shape[n])).to(dev) for n in names})
+    stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(names))
+    return bounds, a_state, b_state, stats
+
+
 def run_alpha_beta_crown_mlp(
     module: Any,
     input_spec: Any,
@@ -841,6 +866,11 @@ def run_alpha_beta_crown_mlp(
         optimize_beta = has_split
     if optimize_beta and not has_split:
         optimize_beta = False  # nothing to constrain: beta's gradient is identically zero
+    if needs_graph_path(module):
+        return _run_alpha_beta_crown_graph(module, input_spec, linear_spec_C=linear_spec_C, relu_split_state=relu_split_state, steps=steps, lr=lr,
+                                           alpha_init=alpha_init, beta_init=beta_init, warm_start_alpha=warm_start_alpha,
+                                           warm_start_beta=warm_start_beta, objective=objective, spec_reduce=spec_reduce,
+                                           per_batch_params=per_batch_params, optimize_beta=bool(optimize_beta))
     if has_split and int(normalize_input_spec(input_spec).center.shape[0]) == 1:
         # the reference's pre-check for a single node (alpha_beta_crown.py:693-714)
         cert, cert_val, _cnt = first_layer_certificate(module, input_spec, relu_split_state)

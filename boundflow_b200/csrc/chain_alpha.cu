@@ -525,3 +525,76 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   }
   return BF_OK;
 }
+
+// ---------------------------------------------------------------------------
+// The pieces of the per-domain alpha / beta loop as separate entry points, for graphs that are not chains: the
+// caller walks its graph and calls these per value (ReLU split, adjoint start vector, forward convolution of rows,
+// ReLU adjoint step, objective / best-of, Adam steps).
+// ---------------------------------------------------------------------------
+extern "C" int bf_relu_split_apply(float* l, float* u, const int8_t* split, int split_stride, int* infeasible, int B, int n,
+                                   bf_stream_t stream) {
+  BF_REQUIRE(l && u && split, BF_E_INVALID, "bf_relu_split_apply: null tensor");
+  BF_REQUIRE(B > 0 && n > 0 && (split_stride == 0 || split_stride == n), BF_E_INVALID, "bf_relu_split_apply: bad sizes");
+  return bf::launch_relu_split_apply(l, u, split, split_stride, infeasible, B, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, bf_stream_t stream) {
+  BF_REQUIRE(A && v, BF_E_INVALID, "bf_rows_add_broadcast: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n > 0 && (v_stride == 0 || v_stride == n), BF_E_INVALID, "bf_rows_add_broadcast: bad sizes");
+  return bf::launch_rows_add_broadcast(A, v, v_stride, B, S, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_adjoint_start_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, bf_stream_t stream) {
+  BF_REQUIRE(A0 && mid && rad, BF_E_INVALID, "bf_adjoint_start_box: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n0 > 0, BF_E_INVALID, "bf_adjoint_start_box: bad sizes");
+  return bf::launch_h0_box(A0, mid, rad, B, S, n0, bf::as_stream(stream));
+}
+
+extern "C" int bf_rows_conv2d_fwd(const float* in, const float* W, const float* bias, float* out, int M, int Ci, int Hi, int Wi,
+                                  int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream) {
+  BF_REQUIRE(in && W && out, BF_E_INVALID, "bf_rows_conv2d_fwd: null tensor");
+  BF_REQUIRE(M > 0 && Ci > 0 && Hi > 0 && Wi > 0 && Co > 0 && Ho > 0 && Wo > 0 && kh > 0 && kw > 0 && sh > 0 && sw > 0 && ph >= 0 && pw >= 0,
+             BF_E_INVALID, "bf_rows_conv2d_fwd: bad sizes");
+  bf_layer_desc L{};
+  L.op = BF_OP_CONV2D; L.W = W; L.bias = bias;
+  L.Ci = Ci; L.Hi = Hi; L.Wi = Wi; L.Co = Co; L.Ho = Ho; L.Wo = Wo; L.kh = kh; L.kw = kw; L.sh = sh; L.sw = sw; L.ph = ph; L.pw = pw;
+  L.n_in = Ci * Hi * Wi; L.n_out = Co * Ho * Wo;
+  return bf::launch_conv_forward_rows(in, W, bias, out, M, L, bf::as_stream(stream));
+}
+
+extern "C" int bf_relu_adjoint_rows(float* G, const float* Ahat, const float* alpha_u, const float* alpha_l, const float* beta_u,
+                                    const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
+                                    bf_stream_t stream) {
+  BF_REQUIRE(G && Ahat && alpha_u && alpha_l && pre_l && pre_u && grad, BF_E_INVALID, "bf_relu_adjoint_rows: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n > 0, BF_E_INVALID, "bf_relu_adjoint_rows: bad sizes");
+  return bf::launch_relu_adjoint_rows(G, Ahat, alpha_l, alpha_u, beta_u, pre_l, pre_u, grad, gsum, B, S, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_alpha_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first, int spec_reduce,
+                                    float soft_tau, float* row_weight, int B, int S, bf_stream_t stream) {
+  BF_REQUIRE(cur && best_lower && best_metric && improve, BF_E_INVALID, "bf_alpha_select_best: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && spec_reduce >= BF_REDUCE_MEAN && spec_reduce <= BF_REDUCE_SOFTMIN, BF_E_INVALID,
+             "bf_alpha_select_best: bad sizes or reduction");
+  BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "bf_alpha_select_best: soft_tau must be positive");
+  return bf::launch_select_best(cur, best_lower, best_metric, improve, first, spec_reduce, soft_tau, row_weight, B, S, bf::as_stream(stream));
+}
+
+extern "C" int bf_alpha_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
+                                  const float* pre_l, const float* pre_u, float* slope_l, int t, float lr, int spec_reduce, int S,
+                                  int do_update, int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(alpha && m && v && grad && improve && best_alpha && pre_l && pre_u && slope_l, BF_E_INVALID,
+             "bf_alpha_adam_step: null tensor");
+  BF_REQUIRE(B > 0 && n > 0 && S > 0 && t >= 0 && lr > 0.f, BF_E_INVALID, "bf_alpha_adam_step: bad sizes or options");
+  return bf::launch_adam_step(alpha, m, v, grad, improve, best_alpha, pre_l, pre_u, slope_l, bf::adam_scalars(t, lr, spec_reduce, S),
+                              do_update, B, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_beta_adam_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride,
+                                 const int* improve, float* best_beta, float* add, int t, float lr, int spec_reduce, int S,
+                                 int do_update, int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(beta && m && v && gsum && split && add, BF_E_INVALID, "bf_beta_adam_step: null tensor");
+  BF_REQUIRE(B > 0 && n > 0 && S > 0 && t >= 0 && lr > 0.f && (split_stride == 0 || split_stride == n), BF_E_INVALID,
+             "bf_beta_adam_step: bad sizes or options");
+  return bf::launch_beta_step(beta, m, v, gsum, split, split_stride, improve, best_beta, add, bf::adam_scalars(t, lr, spec_reduce, S),
+                              do_update, B, n, bf::as_stream(stream));
+}

@@ -752,3 +752,52 @@ extern "C" int bf_branch_scores(const float* const* pre_l, const float* const* p
   }
   return BF_OK;
 }
+
+// ---- building blocks for graphs that are not chains ---------------------------------------------
+namespace bf {
+
+// ReLU split on the bounds of a value: s = +1 -> l = max(l, 0); s = -1 -> u = min(u, 0); a domain with l > u
+// afterwards on any neuron is flagged.  One block row per domain.
+__global__ void __launch_bounds__(256) relu_split_apply_kernel(float* __restrict__ l, float* __restrict__ u,
+                                                               const int8_t* __restrict__ split, int split_stride,
+                                                               int* __restrict__ infeasible, int n) {
+  const int b = blockIdx.x;
+  bool bad = false;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < n; j += gridDim.y * blockDim.x) {
+    const size_t o = (size_t)b * n + j;
+    const int s = split[(size_t)b * split_stride + j];
+    float lo = l[o], up = u[o];
+    if (s > 0) lo = fmaxf(lo, 0.f);
+    if (s < 0) up = fminf(up, 0.f);
+    l[o] = lo;
+    u[o] = up;
+    bad |= lo > up;
+  }
+  if (infeasible && __syncthreads_or(bad ? 1 : 0) && threadIdx.x == 0) atomicOr(&infeasible[b], 1);
+}
+
+int launch_relu_split_apply(float* l, float* u, const int8_t* split, int split_stride, int* infeasible, int B, int n,
+                            cudaStream_t stream) {
+  dim3 grid(B, std::min(ceil_div(n, 256), 64));
+  relu_split_apply_kernel<<<grid, 256, 0, stream>>>(l, u, split, split_stride, infeasible, n);
+  BF_CHECK_LAUNCH("relu_split_apply_kernel");
+  return BF_OK;
+}
+
+// A[b, s, :] += v[b, :] (v_stride = n) or += v[:] (v_stride = 0)
+__global__ void rows_add_broadcast_kernel(float* __restrict__ A, const float* __restrict__ v, int v_stride, long long total, int S,
+                                          int n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / n;
+    A[i] += v[(size_t)(m / S) * v_stride + (size_t)(i - m * n)];
+  }
+}
+
+int launch_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, cudaStream_t stream) {
+  const long long total = (long long)B * S * n;
+  rows_add_broadcast_kernel<<<ew_grid(total, 256), 256, 0, stream>>>(A, v, v_stride, total, S, n);
+  BF_CHECK_LAUNCH("rows_add_broadcast_kernel");
+  return BF_OK;
+}
+
+}  // namespace bf

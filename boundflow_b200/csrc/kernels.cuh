@@ -120,5 +120,9 @@ int launch_beta_step(float* beta, float* m, float* v, float* gsum, const int8_t*
 int launch_verdict(const float* lower, float threshold, float tol, const int* infeasible, int8_t* verdict, float* min_lower,
                    int B, int S, cudaStream_t stream);
 int launch_poison_on_status(const int* status, float* a, long long na, float* b, long long nb, cudaStream_t stream);
+// building blocks for graphs that are not chains
+int launch_relu_split_apply(float* l, float* u, const int8_t* split, int split_stride, int* infeasible, int B, int n,
+                            cudaStream_t stream);
+int launch_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, cudaStream_t stream);
 
 }  // namespace bf

@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Mapping, Optional, Tuple
 import torch
 
 from . import _lib
-from .crown import _cuda_device, _f32, _stream_ptr
+from .crown import _alpha_rows, _cuda_device, _f32, _split_tensor, _stream_ptr
 from .ir import IntervalState, input_mid_rad, lp_ball_of, normalize_input_spec
 
 
@@ -47,6 +47,10 @@ class DagTrace:
     upper: Dict[str, torch.Tensor] = field(default_factory=dict)
     shape: Dict[str, Tuple[int, ...]] = field(default_factory=dict)
     relu_inputs: List[str] = field(default_factory=list)
+    # bounds of every ReLU input after its split (crown_ibp.py:210-214); the value's own entry stays unsplit
+    pre_l: Dict[str, torch.Tensor] = field(default_factory=dict)
+    pre_u: Dict[str, torch.Tensor] = field(default_factory=dict)
+    infeasible: Optional[torch.Tensor] = None  # int32 [B]: a split left some neuron with lower > upper
     B: int = 0
     mid: Optional[torch.Tensor] = None
     rad: Optional[torch.Tensor] = None
@@ -62,8 +66,9 @@ def _params(module: Any, device: torch.device) -> Dict[str, torch.Tensor]:
     return out
 
 
-def forward_ibp_dag(module: Any, input_spec: Any) -> DagTrace:
-    """One IBP pass over the ops in order (`_forward_ibp_trace_mlp`, crown_ibp.py:101-342, without splits)."""
+def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Mapping[str, torch.Tensor]] = None) -> DagTrace:
+    """One IBP pass over the ops in order (`_forward_ibp_trace_mlp`, crown_ibp.py:101-342); `relu_split_state` maps
+    the name of a ReLU input to its int8 split assignment ([B, *shape] or one shared row)."""
     lib = _lib.load()
     spec = normalize_input_spec(input_spec)
     if lp_ball_of(spec) is not None:
@@ -74,6 +79,7 @@ def forward_ibp_dag(module: Any, input_spec: Any) -> DagTrace:
     mid, rad, lo, up = input_mid_rad(spec)
     B = int(spec.center.shape[0])
     tr = DagTrace(B=B, input_name=spec.value_name)
+    tr.infeasible = torch.zeros(B, dtype=torch.int32, device=device)
     tr.mid, tr.rad = _f32(mid, device).reshape(B, -1), _f32(rad, device).reshape(B, -1)
     tr.lower[spec.value_name], tr.upper[spec.value_name] = _f32(lo, device).reshape(B, -1), _f32(up, device).reshape(B, -1)
     tr.shape[spec.value_name] = tuple(int(d) for d in spec.center.shape[1:])
@@ -110,8 +116,16 @@ def forward_ibp_dag(module: Any, input_spec: Any) -> DagTrace:
         elif t == "relu":
             x = op.inputs[0]
             tr.relu_inputs.append(x)
-            yl, yu = torch.empty_like(tr.lower[x]), torch.empty_like(tr.upper[x])
-            _lib.check(lib.bf_interval_relu(_lib.ptr(tr.lower[x]), _lib.ptr(tr.upper[x]), _lib.ptr(yl), _lib.ptr(yu), yl.numel(), s))
+            pl, pu = tr.lower[x], tr.upper[x]
+            sp = relu_split_state.get(x) if relu_split_state else None
+            if sp is not None:
+                n = _numel(tr.shape[x])
+                t8, stride = _split_tensor(sp, B, n, device, x)
+                pl, pu = pl.clone(), pu.clone()
+                _lib.check(lib.bf_relu_split_apply(_lib.ptr(pl), _lib.ptr(pu), _lib.ptr(t8), stride, _lib.ptr(tr.infeasible), B, n, s))
+            tr.pre_l[x], tr.pre_u[x] = pl, pu
+            yl, yu = torch.empty_like(pl), torch.empty_like(pu)
+            _lib.check(lib.bf_interval_relu(_lib.ptr(pl), _lib.ptr(pu), _lib.ptr(yl), _lib.ptr(yu), yl.numel(), s))
             tr.lower[out], tr.upper[out], tr.shape[out] = yl, yu, tr.shape[x]
         elif t == "add":
             a, b2 = op.inputs
@@ -161,132 +175,343 @@ class _State:
         self.A, self.d = A, d
 
 
-def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor], *, output_value: Optional[str] = None,
-              trace: Optional[DagTrace] = None) -> Tuple[torch.Tensor, torch.Tensor, DagTrace]:
-    """CROWN-IBP on a graph: IBP bounds for every ReLU input, then one backward sweep per side.
-    Returns (lower, upper) [B,S] CUDA tensors and the forward trace."""
-    lib = _lib.load()
-    spec = normalize_input_spec(input_spec)
-    tr = trace if trace is not None else forward_ibp_dag(module, spec)
+def _spec_rows(linear_spec_C: Optional[torch.Tensor], B: int, n_out: int, device: torch.device) -> torch.Tensor:
+    if linear_spec_C is None:
+        return torch.eye(n_out, dtype=torch.float32, device=device).unsqueeze(0).expand(B, n_out, n_out).contiguous()
+    C = _f32(linear_spec_C, device)
+    C = (C.unsqueeze(0).expand(B, -1, -1) if C.dim() == 2 else C).contiguous()
+    if int(C.shape[0]) != B or int(C.shape[2]) != n_out:
+        raise ValueError(f"linear_spec_C shape {tuple(C.shape)} does not match batch {B} and output width {n_out}")
+    return C
+
+
+def _relax(lib, tr: DagTrace, relu_alpha: Optional[Mapping[str, torch.Tensor]], s) -> Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]:
+    """Slopes / intercepts of every ReLU from its (split) pre-activation bounds; alpha overrides the lower slope of
+    unstable neurons (crown_ibp.py:1176-1208)."""
+    device, B = tr.mid.device, tr.B
+    relax = {}
+    for x in tr.relu_inputs:
+        if x in relax:
+            continue
+        n = _numel(tr.shape[x])
+        au, bu, al = (torch.empty(B, n, device=device) for _ in range(3))
+        a, stride = (None, 0)
+        if relu_alpha is not None and x in relu_alpha and relu_alpha[x] is not None:
+            a, stride = _alpha_rows(relu_alpha[x], B, n, device, x)
+        _lib.check(lib.bf_relu_relax(_lib.ptr(tr.pre_l[x]), _lib.ptr(tr.pre_u[x]), _lib.ptr(a), stride, _lib.ptr(au), _lib.ptr(bu), _lib.ptr(al), B, n, s))
+        relax[x] = (au, bu, al)
+    return relax
+
+
+def _sweep(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], relax, C: torch.Tensor, side: int, output_value: str, *,
+           add_l: Optional[Mapping[str, torch.Tensor]] = None, ahat: Optional[Dict[str, torch.Tensor]] = None):
+    """One backward sweep of one side.  Returns (bounds [B,S], final coefficients [B,S,n0]).  `add_l[x]` ([B,n], the
+    split term of beta-CROWN) is added to the lower coefficients behind ReLU x; `ahat` (a dict) receives the
+    coefficients that arrive at every ReLU's output, which the gradient sweep needs."""
     device, B = tr.mid.device, tr.B
     task = module.get_entry_task()
-    params = _params(module, device)
+    S = int(C.shape[1])
+    s = _stream_ptr(device)
+    dynamic = set(tr.lower) - set(params)
+    adj: Dict[str, _State] = {output_value: _State(C.clone(), torch.zeros(B, S, device=device))}
+
+    def push(name: str, A: torch.Tensor, d: torch.Tensor) -> None:
+        cur = adj.get(name)
+        if cur is None:
+            adj[name] = _State(A, d)
+            return
+        _lib.check(lib.bf_accumulate(_lib.ptr(cur.A), _lib.ptr(A), A.numel(), s))
+        _lib.check(lib.bf_accumulate(_lib.ptr(cur.d), _lib.ptr(d), d.numel(), s))
+
+    for op in reversed(task.ops):
+        out = op.outputs[0]
+        st = adj.pop(out, None)
+        if st is None:
+            continue
+        t = op.op_type
+        if t == "linear":
+            W = params[op.inputs[1]]
+            b = params[op.inputs[2]] if len(op.inputs) == 3 else None
+            n_cur, n_prev = int(W.shape[0]), int(W.shape[1])
+            Ap = torch.empty(B, S, n_prev, device=device)
+            pack = _lib.LINEAR_PACKS.get(W, B * S, s)  # tensor-core path for large coefficient blocks
+            _lib.check(lib.bf_crown_relu_linear_bwd_packed(_lib.ptr(st.A), side, None, None, None, None, None, _lib.ptr(W), _lib.ptr(b),
+                                                           _lib.ptr(pack), _lib.ptr(Ap), _lib.ptr(st.d), 1, B, S, n_cur, n_prev, s))
+            push(op.inputs[0], Ap, st.d)
+        elif t == "conv2d":
+            W = params[op.inputs[1]]
+            b = params[op.inputs[2]] if len(op.inputs) == 3 else None
+            Ci, Hi, Wi = tr.shape[op.inputs[0]]
+            Co, Ho, Wo = tr.shape[out]
+            kh, kw = int(W.shape[2]), int(W.shape[3])
+            sth, pdh = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
+            Ap = torch.empty(B, S, Ci * Hi * Wi, device=device)
+            nb = int(lib.bf_crown_relu_conv2d_bwd_scratch_bytes(B, S, Co, Ho, Wo))
+            scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device=device)
+            _lib.check(lib.bf_crown_relu_conv2d_bwd(_lib.ptr(st.A), side, None, None, None, None, _lib.ptr(W), _lib.ptr(b), _lib.ptr(Ap),
+                                                    _lib.ptr(st.d), 1, _lib.ptr(scratch), scratch.numel(), B, S, Ci, Hi, Wi, Co, Ho, Wo,
+                                                    kh, kw, sth[0], sth[1], pdh[0], pdh[1], s))
+            push(op.inputs[0], Ap, st.d)
+        elif t == "relu":
+            x = op.inputs[0]
+            n = _numel(tr.shape[x])
+            au, bu, al = relax[x]
+            zb = torch.zeros(B, n, device=device)
+            nb = int(lib.bf_crown_relu_bwd_scratch_bytes(B, S, n))
+            scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device=device)
+            Ap = torch.empty_like(st.A)
+            _lib.check(lib.bf_crown_relu_bwd(_lib.ptr(st.A), side, _lib.ptr(au), _lib.ptr(al), _lib.ptr(bu), _lib.ptr(zb), _lib.ptr(Ap),
+                                             _lib.ptr(st.d), 1, _lib.ptr(scratch), scratch.numel(), B, S, n, s))
+            if ahat is not None:
+                ahat[x] = st.A  # left untouched by the call above
+            if add_l is not None and side == _lib.SIDE_LOWER and add_l.get(x) is not None:
+                _lib.check(lib.bf_rows_add_broadcast(_lib.ptr(Ap), _lib.ptr(add_l[x]), n, B, S, n, s))
+            push(x, Ap, st.d)
+        elif t == "add":
+            d = st.d
+            dyn = []
+            for nm in op.inputs:
+                if nm in dynamic:
+                    dyn.append(nm)
+                else:  # a constant operand adds A . value to the bias (crown_ibp.py:1948-1950)
+                    const = tr.lower[nm].reshape(B, 1, -1)
+                    d = d + (st.A * const).sum(dim=2)
+            for k, nm in enumerate(dyn):
+                # the same coefficients for every operand; the bias travels with the first one only
+                push(nm, st.A.clone() if k + 1 < len(dyn) or nm in adj else st.A, d if k == 0 else torch.zeros_like(d))
+        elif t in ("flatten", "reshape"):
+            push(op.inputs[0], st.A, st.d)
+        elif t == "concat":
+            start = 0
+            for k, nm in enumerate(op.inputs):
+                w = _numel(tr.shape[nm])
+                push(nm, st.A[:, :, start : start + w].contiguous(), st.d if k == 0 else torch.zeros_like(st.d))
+                start += w
+        else:
+            raise NotImplementedError(f"run_crown_ibp_mlp unsupported op_type in backward: {t}")
+    if tr.input_name not in adj:
+        raise RuntimeError(f"backward did not reach input value {tr.input_name}")
+    fin = adj[tr.input_name]
+    res = torch.empty(B, S, device=device)
+    _lib.check(lib.bf_concretize(_lib.ptr(fin.A), _lib.ptr(tr.mid), _lib.ptr(tr.rad), _lib.ptr(fin.d), _lib.ptr(res), side, B, S,
+                                 int(tr.mid.shape[1]), s))
+    return res, fin.A
+
+
+def _output_value(module: Any, tr: DagTrace, output_value: Optional[str]) -> str:
+    task = module.get_entry_task()
     if output_value is None:
         if len(task.output_values) != 1:
             raise ValueError(f"task has {len(task.output_values)} outputs; specify output_value explicitly")
         output_value = task.output_values[0]
     if output_value not in tr.shape:
         raise KeyError(f"missing value in interval_env/params: {output_value}")
-    n_out = _numel(tr.shape[output_value])
-    if linear_spec_C is None:
-        C = torch.eye(n_out, dtype=torch.float32, device=device).unsqueeze(0).expand(B, n_out, n_out).contiguous()
-    else:
-        C = _f32(linear_spec_C, device)
-        C = (C.unsqueeze(0).expand(B, -1, -1) if C.dim() == 2 else C).contiguous()
-        if int(C.shape[0]) != B or int(C.shape[2]) != n_out:
-            raise ValueError(f"linear_spec_C shape {tuple(C.shape)} does not match batch {B} and output width {n_out}")
+    return output_value
+
+
+def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor], *, output_value: Optional[str] = None,
+              trace: Optional[DagTrace] = None, relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+              relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
+              relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, DagTrace]:
+    """CROWN-IBP on a graph: IBP bounds for every ReLU input (with the ReLU splits, if any), then one backward sweep
+    per side; `relu_alpha` overrides the lower slopes of unstable neurons, `relu_pre_add_coeff_l` is added to the lower
+    coefficients behind a ReLU (crown_ibp.py:2136-2152).  Returns (lower, upper) [B,S] CUDA tensors and the trace."""
+    lib = _lib.load()
+    spec = normalize_input_spec(input_spec)
+    tr = trace if trace is not None else forward_ibp_dag(module, spec, relu_split_state)
+    if int(tr.infeasible.sum()) != 0:
+        raise ValueError("infeasible relu split: lower > upper")
+    device, B = tr.mid.device, tr.B
+    params = _params(module, device)
+    output_value = _output_value(module, tr, output_value)
+    C = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
+    s = _stream_ptr(device)
+    relax = _relax(lib, tr, relu_alpha, s)
+    add_l = None
+    if relu_pre_add_coeff_l:
+        add_l = {x: _f32(v, device).reshape(-1, _numel(tr.shape[x])).expand(B, -1).contiguous() for x, v in relu_pre_add_coeff_l.items() if v is not None}
+    lo, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=add_l)
+    up, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
+    return lo, up, tr
+
+
+def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], relax, A0: torch.Tensor, ahat: Dict[str, torch.Tensor],
+                     grad: Dict[str, torch.Tensor], gsum: Optional[Dict[str, torch.Tensor]], S: int) -> None:
+    """Gradient sweep: the lower bound of row s equals C[s] . f_s(h0), where f_s is the network with every ReLU
+    replaced by the line the backward sweep chose for that row and h0 = mid - sgn(A0) * rad.  Pushing h0 forward through
+    the graph gives, at every ReLU input, the value g with d lower / d alpha = [l<0<u][Ahat>=0] Ahat * g and
+    d lower / d add = g (`bf_relu_adjoint_rows` accumulates both per domain)."""
+    device, B = tr.mid.device, tr.B
+    task = module.get_entry_task()
+    s = _stream_ptr(device)
+    _lib.check(lib.bf_adjoint_start_box(_lib.ptr(A0), _lib.ptr(tr.mid), _lib.ptr(tr.rad), B, S, int(tr.mid.shape[1]), s))
+    h: Dict[str, torch.Tensor] = {tr.input_name: A0}
+    for op in task.ops:
+        t, out = op.op_type, op.outputs[0]
+        if t == "linear":
+            x = op.inputs[0]
+            if x not in h:
+                continue
+            W = params[op.inputs[1]]
+            b = params[op.inputs[2]] if len(op.inputs) == 3 else None
+            n_out, n_in = int(W.shape[0]), int(W.shape[1])
+            Wt = _TRANSPOSED.get(W)
+            g = torch.empty(B, S, n_out, device=device)
+            # rows x W^T: the backward entry point on the transposed weight, no slopes, no bias term
+            _lib.check(lib.bf_crown_relu_linear_bwd(_lib.ptr(h[x]), _lib.SIDE_LOWER, None, None, None, None, None, _lib.ptr(Wt), None,
+                                                    _lib.ptr(g), None, 0, B, S, n_in, n_out, s))
+            if b is not None:
+                _lib.check(lib.bf_rows_add_broadcast(_lib.ptr(g), _lib.ptr(b), 0, B, S, n_out, s))
+            h[out] = g
+        elif t == "conv2d":
+            x = op.inputs[0]
+            if x not in h:
+                continue
+            W = params[op.inputs[1]]
+            b = params[op.inputs[2]] if len(op.inputs) == 3 else None
+            Ci, Hi, Wi = tr.shape[x]
+            Co, Ho, Wo = tr.shape[out]
+            sth, pdh = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
+            g = torch.empty(B, S, Co * Ho * Wo, device=device)
+            _lib.check(lib.bf_rows_conv2d_fwd(_lib.ptr(h[x]), _lib.ptr(W), _lib.ptr(b), _lib.ptr(g), B * S, Ci, Hi, Wi, Co, Ho, Wo, int(W.shape[2]),
+                                              int(W.shape[3]), sth[0], sth[1], pdh[0], pdh[1], s))
+            h[out] = g
+        elif t == "relu":
+            x = op.inputs[0]
+            if x not in h or x not in ahat:   # no coefficients arrived here: the value does not reach the output
+                continue
+            n = _numel(tr.shape[x])
+            au, bu, al = relax[x]
+            G = h[x].clone()                  # x may feed other ops as well
+            _lib.check(lib.bf_relu_adjoint_rows(_lib.ptr(G), _lib.ptr(ahat[x]), _lib.ptr(au), _lib.ptr(al), _lib.ptr(bu), _lib.ptr(tr.pre_l[x]),
+                                                _lib.ptr(tr.pre_u[x]), _lib.ptr(grad[x]), _lib.ptr(gsum[x]) if gsum is not None else None, B, S, n, s))
+            h[out] = G
+        elif t == "add":
+            terms = [nm for nm in op.inputs if nm in h]
+            if not terms:
+                continue
+            acc = h[terms[0]].clone()
+            for nm in terms[1:]:
+                _lib.check(lib.bf_accumulate(_lib.ptr(acc), _lib.ptr(h[nm]), acc.numel(), s))
+            for nm in op.inputs:
+                if nm in params and nm not in h:   # constant operand
+                    c = params[nm].reshape(-1).contiguous()
+                    _lib.check(lib.bf_rows_add_broadcast(_lib.ptr(acc), _lib.ptr(c), 0, B, S, int(c.numel()), s))
+            h[out] = acc
+        elif t in ("flatten", "reshape"):
+            if op.inputs[0] in h:
+                h[out] = h[op.inputs[0]]
+        elif t == "concat":
+            if all(nm in h for nm in op.inputs):
+                h[out] = torch.cat([h[nm] for nm in op.inputs], dim=2)
+        else:
+            raise NotImplementedError(f"unsupported op_type in the gradient sweep: {t}")
+
+
+class _TransposedWeights:
+    """W^T copies for the forward Linear step of the gradient sweep, per weight tensor (same lifetime rule as the
+    packed-weight cache: keyed by storage pointer, shape and version)."""
+
+    def __init__(self):
+        self._cache: Dict[Tuple[int, Tuple[int, ...], int], torch.Tensor] = {}
+
+    def get(self, W: torch.Tensor) -> torch.Tensor:
+        key = (W.data_ptr(), tuple(W.shape), int(W._version))
+        t = self._cache.get(key)
+        if t is None:
+            if len(self._cache) > 256:
+                self._cache.clear()
+            t = self._cache[key] = W.t().contiguous()
+        return t
+
+
+_TRANSPOSED = _TransposedWeights()
+
+
+def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor], *, steps: int, lr: float,
+                         alpha0: Optional[Mapping[str, torch.Tensor]] = None, alpha_init: float = 0.5,
+                         relu_split_state: Optional[Mapping[str, torch.Tensor]] = None, optimize_beta: bool = False,
+                         beta0: Optional[Mapping[str, torch.Tensor]] = None, beta_init: float = 0.0, spec_reduce: str = "mean",
+                         output_value: Optional[str] = None):
+    """Per-domain alpha (and beta) loop on a graph that is not a chain: `run_alpha_beta_crown_mlp(per_batch_params=True,
+    objective="lower")` (alpha_beta_crown.py:716-923), whose sweep is the reference's generic graph backward.  steps + 1
+    evaluations; each is one lower sweep that keeps the coefficients at every ReLU, the per-domain objective with strict
+    best-of, one gradient sweep and one Adam step per ReLU.  Returns (best_lower, best_upper, best_alpha dict,
+    best_beta dict, trace); alpha / beta are [B, n] per ReLU input name."""
+    lib = _lib.load()
+    codes = {"mean": _lib.REDUCE_MEAN, "sum": _lib.REDUCE_SUM}
+    if spec_reduce not in codes:
+        raise NotImplementedError("the graph path of the CUDA backend implements spec_reduce mean | sum")
+    spec = normalize_input_spec(input_spec)
+    tr = forward_ibp_dag(module, spec, relu_split_state)
+    if int(tr.infeasible.sum()) != 0:
+        raise ValueError("infeasible relu split: lower > upper")
+    device, B = tr.mid.device, tr.B
+    params = _params(module, device)
+    output_value = _output_value(module, tr, output_value)
+    C = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
     S = int(C.shape[1])
     s = _stream_ptr(device)
-    # ReLU relaxations from the IBP pre-activations
-    relax: Dict[str, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
-    for x in tr.relu_inputs:
-        n = _numel(tr.shape[x])
-        au, bu, al = (torch.empty(B, n, device=device) for _ in range(3))
-        _lib.check(lib.bf_relu_relax(_lib.ptr(tr.lower[x]), _lib.ptr(tr.upper[x]), None, 0, _lib.ptr(au), _lib.ptr(bu), _lib.ptr(al), B, n, s))
-        relax[x] = (au, bu, al)
-    zero_beta: Dict[int, torch.Tensor] = {}
-    dynamic = set(tr.lower) - set(params)
+    names = list(dict.fromkeys(tr.relu_inputs))
+    width = {x: _numel(tr.shape[x]) for x in names}
 
-    outs = []
-    for side in (_lib.SIDE_LOWER, _lib.SIDE_UPPER):
-        adj: Dict[str, _State] = {output_value: _State(C.clone(), torch.zeros(B, S, device=device))}
+    def start(raw, x, init):
+        n = width[x]
+        if raw is not None and x in raw and raw[x] is not None:
+            t, _ = _alpha_rows(raw[x], B, n, device, x)
+            return t.expand(B, n).contiguous().clone()
+        return torch.full((B, n), float(init), dtype=torch.float32, device=device)
 
-        def push(name: str, A: torch.Tensor, d: torch.Tensor) -> None:
-            cur = adj.get(name)
-            if cur is None:
-                adj[name] = _State(A, d)
-                return
-            _lib.check(lib.bf_accumulate(_lib.ptr(cur.A), _lib.ptr(A), A.numel(), s))
-            _lib.check(lib.bf_accumulate(_lib.ptr(cur.d), _lib.ptr(d), d.numel(), s))
-
-        for op in reversed(task.ops):
-            out = op.outputs[0]
-            st = adj.pop(out, None)
-            if st is None:
-                continue
-            t = op.op_type
-            if t == "linear":
-                W = params[op.inputs[1]]
-                b = params[op.inputs[2]] if len(op.inputs) == 3 else None
-                n_cur, n_prev = int(W.shape[0]), int(W.shape[1])
-                Ap = torch.empty(B, S, n_prev, device=device)
-                pack = _lib.LINEAR_PACKS.get(W, B * S, s)  # tensor-core path for large coefficient blocks
-                _lib.check(lib.bf_crown_relu_linear_bwd_packed(_lib.ptr(st.A), side, None, None, None, None, None, _lib.ptr(W), _lib.ptr(b),
-                                                               _lib.ptr(pack), _lib.ptr(Ap), _lib.ptr(st.d), 1, B, S, n_cur, n_prev, s))
-                push(op.inputs[0], Ap, st.d)
-            elif t == "conv2d":
-                W = params[op.inputs[1]]
-                b = params[op.inputs[2]] if len(op.inputs) == 3 else None
-                Ci, Hi, Wi = tr.shape[op.inputs[0]]
-                Co, Ho, Wo = tr.shape[out]
-                kh, kw = int(W.shape[2]), int(W.shape[3])
-                sth, pdh = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
-                Ap = torch.empty(B, S, Ci * Hi * Wi, device=device)
-                nb = int(lib.bf_crown_relu_conv2d_bwd_scratch_bytes(B, S, Co, Ho, Wo))
-                scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device=device)
-                _lib.check(lib.bf_crown_relu_conv2d_bwd(_lib.ptr(st.A), side, None, None, None, None, _lib.ptr(W), _lib.ptr(b), _lib.ptr(Ap),
-                                                        _lib.ptr(st.d), 1, _lib.ptr(scratch), scratch.numel(), B, S, Ci, Hi, Wi, Co, Ho, Wo,
-                                                        kh, kw, sth[0], sth[1], pdh[0], pdh[1], s))
-                push(op.inputs[0], Ap, st.d)
-            elif t == "relu":
-                x = op.inputs[0]
-                n = _numel(tr.shape[x])
-                au, bu, al = relax[x]
-                zb = zero_beta.get(n)
-                if zb is None:
-                    zb = zero_beta[n] = torch.zeros(B, n, device=device)
-                nb = int(lib.bf_crown_relu_bwd_scratch_bytes(B, S, n))
-                scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device=device)
-                Ap = torch.empty_like(st.A)
-                _lib.check(lib.bf_crown_relu_bwd(_lib.ptr(st.A), side, _lib.ptr(au), _lib.ptr(al), _lib.ptr(bu), _lib.ptr(zb), _lib.ptr(Ap),
-                                                 _lib.ptr(st.d), 1, _lib.ptr(scratch), scratch.numel(), B, S, n, s))
-                push(x, Ap, st.d)
-            elif t == "add":
-                d = st.d
-                dyn = []
-                for nm in op.inputs:
-                    if nm in dynamic:
-                        dyn.append(nm)
-                    else:  # a constant operand adds A . value to the bias (crown_ibp.py:1948-1950)
-                        const = tr.lower[nm].reshape(B, 1, -1)
-                        d = d + (st.A * const).sum(dim=2)
-                for k, nm in enumerate(dyn):
-                    # the same coefficients for every operand; the bias travels with the first one only
-                    push(nm, st.A.clone() if k + 1 < len(dyn) or nm in adj else st.A, d if k == 0 else torch.zeros_like(d))
-            elif t in ("flatten", "reshape"):
-                push(op.inputs[0], st.A, st.d)
-            elif t == "concat":
-                start = 0
-                for k, nm in enumerate(op.inputs):
-                    w = _numel(tr.shape[nm])
-                    push(nm, st.A[:, :, start : start + w].contiguous(), st.d if k == 0 else torch.zeros_like(st.d))
-                    start += w
-            else:
-                raise NotImplementedError(f"run_crown_ibp_mlp unsupported op_type in backward: {t}")
-        if tr.input_name not in adj:
-            raise RuntimeError(f"backward did not reach input value {tr.input_name}")
-        fin = adj[tr.input_name]
-        res = torch.empty(B, S, device=device)
-        _lib.check(lib.bf_concretize(_lib.ptr(fin.A), _lib.ptr(tr.mid), _lib.ptr(tr.rad), _lib.ptr(fin.d), _lib.ptr(res), side, B, S,
-                                     int(tr.mid.shape[1]), s))
-        outs.append(res)
-    return outs[0], outs[1], tr
+    zeros = lambda x: torch.zeros(B, width[x], dtype=torch.float32, device=device)  # noqa: E731
+    alpha = {x: start(alpha0, x, alpha_init) for x in names}
+    best_alpha = {x: alpha[x].clone() for x in names}
+    m, v, grad, slope = ({x: zeros(x) for x in names} for _ in range(4))
+    with_beta = bool(optimize_beta and relu_split_state)
+    beta = {x: start(beta0, x, beta_init) for x in names}
+    best_beta = {x: beta[x].clone() for x in names}
+    splits: Dict[str, Tuple[torch.Tensor, int]] = {}
+    if with_beta:
+        mb, vb, gsum, addv = ({x: zeros(x) for x in names} for _ in range(4))
+        for x in names:
+            sp = relu_split_state.get(x)
+            splits[x] = _split_tensor(sp, B, width[x], device, x) if sp is not None else (torch.zeros(1, width[x], dtype=torch.int8, device=device), 0)
+        for x in names:  # split term of the start beta
+            _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]), splits[x][1],
+                                             None, None, _lib.ptr(addv[x]), 0, float(lr), codes[spec_reduce], S, 0, B, width[x], s))
+    best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
+    best_metric = torch.empty(B, dtype=torch.float32, device=device)
+    improve = torch.zeros(B, dtype=torch.int32, device=device)
+    for t in range(int(steps) + 1):
+        last = t == int(steps)
+        relax = _relax(lib, tr, alpha, s)
+        ahat: Dict[str, torch.Tensor] = {}
+        cur, A0 = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=addv if with_beta else None, ahat=ahat)
+        _lib.check(lib.bf_alpha_select_best(_lib.ptr(cur), _lib.ptr(best_lower), _lib.ptr(best_metric), _lib.ptr(improve), 1 if t == 0 else 0,
+                                            codes[spec_reduce], 1.0, None, B, S, s))
+        if not last:
+            _adjoint_forward(lib, module, tr, params, relax, A0, ahat, grad, gsum if with_beta else None, S)
+        for x in names:
+            n = width[x]
+            _lib.check(lib.bf_alpha_adam_step(_lib.ptr(alpha[x]), _lib.ptr(m[x]), _lib.ptr(v[x]), _lib.ptr(grad[x]), _lib.ptr(improve), _lib.ptr(best_alpha[x]),
+                                              _lib.ptr(tr.pre_l[x]), _lib.ptr(tr.pre_u[x]), _lib.ptr(slope[x]), t, float(lr), codes[spec_reduce], S,
+                                              0 if last else 1, B, n, s))
+            if with_beta:
+                _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]),
+                                                 splits[x][1], _lib.ptr(improve), _lib.ptr(best_beta[x]), _lib.ptr(addv[x]), t, float(lr),
+                                                 codes[spec_reduce], S, 0 if last else 1, B, n, s))
+    # the upper bound of each domain's best iteration: the upper sweep at its best alpha (beta acts on the lower side only)
+    relax = _relax(lib, tr, best_alpha, s)
+    best_upper, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
+    return best_lower, best_upper, best_alpha, best_beta, tr
 
 
 def run_crown_ibp_dag(module: Any, input_spec: Any, *, linear_spec_C: Optional[torch.Tensor] = None,
-                      output_value: Optional[str] = None) -> IntervalState:
+                      output_value: Optional[str] = None, relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
+                      relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+                      relu_split_state: Optional[Mapping[str, torch.Tensor]] = None) -> IntervalState:
     """`run_crown_ibp_mlp` (crown_ibp.py:2054-2133) for graphs with add / concat / fan-out."""
-    lo, up, _tr = crown_dag(module, input_spec, linear_spec_C, output_value=output_value)
+    lo, up, _tr = crown_dag(module, input_spec, linear_spec_C, output_value=output_value, relu_split_state=relu_split_state,
+                            relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
     dev = normalize_input_spec(input_spec).center.device
     return IntervalState(lower=lo.to(dev), upper=up.to(dev))
 

@@ -484,6 +484,54 @@ int bf_chain_alpha_crown_objective(const bf_chain* chain,
                                    float lb_weight, float ub_weight,
                                    void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
+/* The pieces of the per-domain alpha / beta loop as separate entry points, for graphs that are not chains (residual
+ * add, concat, fan-out): the reference's alpha-beta function accepts such graphs because its sweep is the generic
+ * _run_crown_backward_from_trace (boundflow/runtime/crown_ibp.py:1669-2051) under autograd; here the caller walks the
+ * graph and calls, per value, the layer-level backward entry points above plus:
+ *   bf_relu_split_apply   _apply_relu_split, crown_ibp.py:70-98, on the bounds of one ReLU input, in place: split +1
+ *                         clamps l to >= 0, -1 clamps u to <= 0; infeasible[b] (int32, may be NULL) is OR-ed with
+ *                         "some neuron has l > u".  split int8 [B,n] (stride n) or [1,n] (stride 0).
+ *   bf_rows_add_broadcast A[b,s,:] += v[b,:] (v_stride = n) or v[:] (v_stride = 0): the split term -beta*s added to the
+ *                         lower coefficients after a ReLU backward step (alpha_beta_crown.py:615-640), and the bias of a
+ *                         forward Linear step on rows.
+ *   bf_adjoint_start_box  start of the gradient sweep: A0 [B,S,n0] (final lower coefficients) becomes
+ *                         h0 = mid - sgn(A0) * rad in place, the point at which the lower bound is attained.
+ *   bf_rows_conv2d_fwd    forward convolution of M rows [M,Ci,Hi,Wi] -> [M,Co,Ho,Wo] (+ bias): the gradient sweep's
+ *                         step through a Conv2d layer.  (A Linear layer on rows is bf_crown_relu_linear_bwd without
+ *                         slopes on the transposed weight, plus bf_rows_add_broadcast for the bias.)
+ *   bf_relu_adjoint_rows  G [B,S,n] holds the relaxed network's value at a ReLU input (the forward image of h0), Ahat
+ *                         [B,S,n] the lower coefficients that arrived at the ReLU's output in the backward sweep:
+ *                         grad[b,j] += sum_s [l<0<u][Ahat>=0] Ahat*G, gsum[b,j] += sum_s G (NULL without beta), then G
+ *                         becomes the ReLU's output on the chosen line (alpha_l*G where Ahat >= 0, alpha_u*G + beta_u
+ *                         elsewhere), in place.
+ *   bf_alpha_select_best  per-domain objective reduce_s(cur[b,s]) (BF_REDUCE_*), strict best-of against best_metric
+ *                         (first != 0 initialises), improve[b] flags, best_lower rows copied on improvement;
+ *                         row_weight [B,S] or NULL receives d objective / d cur for _MIN / _SOFTMIN
+ *                         (alpha_beta_crown.py:787-902).
+ *   bf_alpha_adam_step    torch.optim.Adam step t (0-based; betas 0.9 / 0.999, eps 1e-8) on alpha with gradient
+ *                         grad * (-1/S for _MEAN, -1 otherwise), projection to [0,1], grad cleared; best_alpha receives
+ *                         the alpha BEFORE the step where improve[b] != 0; slope_l receives the next lower slope
+ *                         (0 if u <= 0, 1 if l >= 0, alpha otherwise); do_update == 0 only snapshots (913-923).
+ *   bf_beta_adam_step     the same for beta >= 0 with gradient -split * gsum (gsum cleared), and add = -beta*split
+ *                         for the next sweep; improve / best_beta may be NULL. */
+int bf_relu_split_apply(float* l, float* u, const int8_t* split, int split_stride, int* infeasible, int B, int n,
+                        bf_stream_t stream);
+int bf_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, bf_stream_t stream);
+int bf_adjoint_start_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, bf_stream_t stream);
+int bf_rows_conv2d_fwd(const float* in, const float* W, const float* bias, float* out, int M, int Ci, int Hi, int Wi,
+                       int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
+int bf_relu_adjoint_rows(float* G, const float* Ahat, const float* alpha_u, const float* alpha_l, const float* beta_u,
+                         const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
+                         bf_stream_t stream);
+int bf_alpha_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first, int spec_reduce,
+                         float soft_tau, float* row_weight, int B, int S, bf_stream_t stream);
+int bf_alpha_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
+                       const float* pre_l, const float* pre_u, float* slope_l, int t, float lr, int spec_reduce, int S,
+                       int do_update, int B, int n, bf_stream_t stream);
+int bf_beta_adam_step(float* beta, float* m, float* v, float* gsum, const int8_t* split, int split_stride,
+                      const int* improve, float* best_beta, float* add, int t, float lr, int spec_reduce, int S,
+                      int do_update, int B, int n, bf_stream_t stream);
+
 /* Branching hint: per domain the ReLU (chain order) and neuron with the widest gap u - l among
  * unstable neurons (l < 0 < u); earlier ReLUs and lower indices win ties; -1/-1 when none.
  *   replaces _branch_choices_from_relu_pre, boundflow/runtime/alpha_beta_crown.py:145-182.

@@ -1,0 +1,223 @@
+"""CPU restatement of the reference's bound propagation on single-task graphs that are not chains
+(residual add, concat, fan-out).  TEST INFRASTRUCTURE ONLY: nothing in the product imports this file.
+
+It follows `_forward_ibp_trace_mlp` (boundflow/runtime/crown_ibp.py:101-342) for the interval pass and the generic
+backward sweep `_run_crown_backward_from_trace` (crown_ibp.py:1669-2051) for CROWN: one coefficient state per VALUE,
+ops walked in reverse, `add` handing the same coefficients to both operands and its bias to the first dynamic one
+(`_split_bias_once`, 922-937), `concat` slicing along the channel axis (1978-2030), a value with several consumers
+summing what arrives (`_accumulate_backward_state`, 879-913).  The alpha / beta loop is the per-domain mode of
+`run_alpha_beta_crown_mlp` (boundflow/runtime/alpha_beta_crown.py:716-923) with torch autograd through the sweep,
+exactly as the reference does it.  Pinned by tests/golden/graph_cases.npz and tests/golden/graph_alpha.npz, both
+generated from the reference.  The per-op arithmetic is shared with oracle/crown_oracle.py.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Mapping, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import crown_oracle as O
+
+
+def _pair(v) -> Tuple[int, int]:
+    if isinstance(v, (tuple, list)):
+        return int(v[0]), int(v[1])
+    return int(v), int(v)
+
+
+def _task(module: Any):
+    return module.get_entry_task()
+
+
+def _params(module: Any, dtype) -> Dict[str, torch.Tensor]:
+    return {k: torch.as_tensor(v).to(dtype) for k, v in module.bindings.get("params", {}).items()}
+
+
+def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_name: str = "input", splits: Optional[Mapping[str, torch.Tensor]] = None):
+    """Interval pass.  Returns (env, relu_pre): name -> (lower, upper) in the value's own shape; relu_pre holds the
+    bounds of every ReLU input AFTER its split (crown_ibp.py:210-214), env[x] stays unsplit."""
+    dtype = lo.dtype
+    P = _params(module, dtype)
+    env: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {input_name: (lo, up)}
+    relu_pre: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
+    B = lo.shape[0]
+
+    def get(name):
+        if name in env:
+            return env[name]
+        c = P[name]
+        c = c.unsqueeze(0).expand((B,) + tuple(c.shape)) if c.dim() == 0 or c.shape[0] != B else c
+        return (c, c)
+
+    for op in _task(module).ops:
+        t, out = op.op_type, op.outputs[0]
+        if t == "linear":
+            l, u = get(op.inputs[0])
+            W = P[op.inputs[1]]
+            b = P[op.inputs[2]] if len(op.inputs) == 3 else None
+            if op.inputs[0] == input_name:
+                env[out] = O.ibp_first_linear(O.box_input(l.reshape(B, -1), u.reshape(B, -1)), W, b)
+            else:
+                env[out] = O.ibp_linear(l.reshape(B, -1), u.reshape(B, -1), W, b)
+        elif t == "conv2d":
+            l, u = get(op.inputs[0])
+            W = P[op.inputs[1]]
+            b = P[op.inputs[2]] if len(op.inputs) == 3 else None
+            env[out] = O.ibp_conv2d(l, u, W, b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)))
+        elif t == "relu":
+            x = op.inputs[0]
+            l, u = get(x)
+            if splits is not None and x in splits and splits[x] is not None:
+                l, u, _infeasible = O.apply_relu_split(l, u, splits[x])
+            relu_pre[x] = (l, u)
+            env[out] = (l.clamp(min=0), u.clamp(min=0))
+        elif t == "add":
+            (al, au), (bl, bu) = get(op.inputs[0]), get(op.inputs[1])
+            env[out] = (al + bl, au + bu)
+        elif t in ("flatten", "reshape"):
+            l, u = get(op.inputs[0])
+            shp = (B, -1) if t == "flatten" else (B,) + tuple(int(d) for d in op.attrs.get("shape", ()))[1:]
+            env[out] = (l.reshape(shp), u.reshape(shp))
+        elif t == "concat":
+            ls, us = zip(*[get(n) for n in op.inputs])
+            env[out] = (torch.cat(ls, dim=1), torch.cat(us, dim=1))
+        else:
+            raise NotImplementedError(t)
+    return env, relu_pre
+
+
+def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: str = "input", output_name: Optional[str] = None,
+                         alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None):
+    """Backward sweep for both sides and box concretisation.  C [B,S,n_out]; alpha / add_l: name of the ReLU input ->
+    [B, n] (flattened).  Returns (lower, upper) [B,S]; differentiable in alpha and add_l."""
+    task = _task(module)
+    dtype = lo.dtype
+    P = _params(module, dtype)
+    B, S = C.shape[0], C.shape[1]
+    out_name = output_name or task.output_values[0]
+    shape = {n: tuple(v[0].shape[1:]) for n, v in env.items()}
+    zero = torch.zeros(B, S, dtype=dtype)
+    # state per value: [A_u, A_l, b_u, b_l], coefficients flattened to [B,S,n]
+    adj: Dict[str, List[torch.Tensor]] = {out_name: [C, C, zero, zero]}
+
+    def push(name, Au, Al, bu, bl):
+        if name in adj:
+            s = adj[name]
+            adj[name] = [s[0] + Au, s[1] + Al, s[2] + bu, s[3] + bl]
+        else:
+            adj[name] = [Au, Al, bu, bl]
+
+    for op in reversed(task.ops):
+        out = op.outputs[0]
+        st = adj.pop(out, None)
+        if st is None:
+            continue
+        Au, Al, bu, bl = st
+        t = op.op_type
+        if t == "linear":
+            W = P[op.inputs[1]]
+            b = P[op.inputs[2]] if len(op.inputs) == 3 else None
+            Au2, bu2 = O.linear_backward(Au, bu, W, b)
+            Al2, bl2 = O.linear_backward(Al, bl, W, b)
+            push(op.inputs[0], Au2, Al2, bu2, bl2)
+        elif t == "conv2d":
+            W = P[op.inputs[1]]
+            b = P[op.inputs[2]] if len(op.inputs) == 3 else None
+            st_, pd_ = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
+            Au2, bu2 = O.conv2d_backward(Au, bu, W, b, st_, pd_, shape[op.inputs[0]], shape[out])
+            Al2, bl2 = O.conv2d_backward(Al, bl, W, b, st_, pd_, shape[op.inputs[0]], shape[out])
+            push(op.inputs[0], Au2, Al2, bu2, bl2)
+        elif t == "relu":
+            x = op.inputs[0]
+            l, u = relu_pre[x]
+            a = alpha.get(x) if alpha is not None else None
+            au_, bu_, al_, bl_ = O.relu_slopes(l, u, a)
+            ad = add_l.get(x) if add_l is not None else None
+            Au2, Al2, bu2, bl2 = O.relu_backward(Au, Al, bu, bl, au_, bu_, al_, bl_, add_l=ad)
+            push(x, Au2, Al2, bu2, bl2)
+        elif t == "add":
+            dyn = [n for n in op.inputs if n in env]
+            for n in op.inputs:
+                if n not in env:  # constant operand: A . value joins the bias (crown_ibp.py:1948-1950)
+                    c = P[n].reshape(1, 1, -1)
+                    bu, bl = bu + (Au * c).sum(dim=2), bl + (Al * c).sum(dim=2)
+            for k, n in enumerate(dyn):
+                push(n, Au, Al, bu if k == 0 else torch.zeros_like(bu), bl if k == 0 else torch.zeros_like(bl))
+        elif t in ("flatten", "reshape"):
+            push(op.inputs[0], Au, Al, bu, bl)
+        elif t == "concat":
+            start = 0
+            for k, n in enumerate(op.inputs):
+                w = 1
+                for d in shape[n]:
+                    w *= int(d)
+                push(n, Au[:, :, start : start + w], Al[:, :, start : start + w], bu if k == 0 else torch.zeros_like(bu),
+                     bl if k == 0 else torch.zeros_like(bl))
+                start += w
+        else:
+            raise NotImplementedError(t)
+    Au, Al, bu, bl = adj[input_name]
+    inp = O.box_input(lo.reshape(B, -1), up.reshape(B, -1))
+    return O.concretize(inp, Al, bl, "lower"), O.concretize(inp, Au, bu, "upper")
+
+
+def adaptive_alpha_init_graph(relu_pre) -> Dict[str, torch.Tensor]:
+    """alpha start 1 where l >= 0 or (l < 0 < u and u > -l), else 0 (native_alpha_beta_optimizer_schedule.py:644-656)."""
+    out = {}
+    for x, (l, u) in relu_pre.items():
+        B = l.shape[0]
+        lf, uf = l.reshape(B, -1), u.reshape(B, -1)
+        out[x] = ((lf >= 0) | ((lf < 0) & (uf > 0) & (uf > -lf))).to(l.dtype)
+    return out
+
+
+def alpha_crown_graph(module: Any, lo, up, C, *, steps: int, lr: float, alpha0: Optional[Mapping[str, torch.Tensor]] = None,
+                      alpha_init: float = 0.5, splits: Optional[Mapping[str, torch.Tensor]] = None, optimize_beta: bool = False,
+                      input_name: str = "input"):
+    """Per-domain alpha (and beta) loop on a graph: `run_alpha_beta_crown_mlp(per_batch_params=True, objective="lower",
+    spec_reduce="mean")`, alpha_beta_crown.py:716-923.  Returns (best_lower, best_upper, best_alpha dict, best_beta dict)."""
+    env, relu_pre = forward_ibp_graph(module, lo, up, input_name=input_name, splits=splits)
+    B, dtype = lo.shape[0], lo.dtype
+    names = list(relu_pre)
+    alphas, betas, split_f = {}, {}, {}
+    for x in names:
+        n = relu_pre[x][0].reshape(B, -1).shape[1]
+        a = alpha0[x].reshape(-1, n).expand(B, n).to(dtype).clone() if alpha0 is not None and x in alpha0 else torch.full((B, n), float(alpha_init), dtype=dtype)
+        alphas[x] = a.requires_grad_(True)
+        if optimize_beta:
+            betas[x] = torch.zeros(B, n, dtype=dtype, requires_grad=True)
+            sp = splits.get(x) if splits is not None else None
+            split_f[x] = None if sp is None else sp.reshape(-1, n).expand(B, n).to(dtype)
+    opt = torch.optim.Adam(list(alphas.values()) + list(betas.values()), lr=float(lr))
+    best = None
+    for step in range(int(steps) + 1):
+        add_l = None
+        if optimize_beta:
+            add_l = {x: (-betas[x] * split_f[x]) for x in names if split_f[x] is not None}
+        lower, upper = crown_backward_graph(module, env, relu_pre, C, lo, up, input_name=input_name, alpha=alphas, add_l=add_l)
+        metric_b = lower.mean(dim=1)
+        if best is None:
+            best = [metric_b.detach().clone(), lower.detach().clone(), upper.detach().clone(), {x: a.detach().clone() for x, a in alphas.items()},
+                    {x: b.detach().clone() for x, b in betas.items()}]
+        else:
+            imp = metric_b.detach() > best[0]
+            best[0] = torch.where(imp, metric_b.detach(), best[0])
+            best[1] = torch.where(imp.unsqueeze(1), lower.detach(), best[1])
+            best[2] = torch.where(imp.unsqueeze(1), upper.detach(), best[2])
+            best[3] = {x: torch.where(imp.unsqueeze(1), a.detach(), best[3][x]) for x, a in alphas.items()}
+            best[4] = {x: torch.where(imp.unsqueeze(1), b.detach(), best[4][x]) for x, b in betas.items()}
+        if step == int(steps):
+            break
+        loss = -metric_b.sum()
+        if not loss.requires_grad:
+            break
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        with torch.no_grad():
+            for a in alphas.values():
+                a.clamp_(0.0, 1.0)
+            for b in betas.values():
+                b.clamp_(0.0)
+    return best[1], best[2], best[3], best[4]

@@ -305,6 +305,51 @@ def gen_graph_cases() -> None:
     save("graph_cases.npz", **out)
 
 
+def gen_graph_alpha() -> None:
+    """The reference's per-domain alpha loop (adaptive start; 1 and 4 steps) and its alpha-beta loop with two split
+    neurons per ReLU and input (3 steps) on the non-chain graphs of workloads.make_graph_cases.  The split
+    assignments and the split-aware adaptive start are stored with the outputs."""
+    out = {}
+    g = torch.Generator().manual_seed(17)
+    for name, (module, _x, lo, up, C) in W.make_graph_cases().items():
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        a0 = adaptive_alpha(relu_pre)
+        B = int(lo.shape[0])
+        for steps in (1, 4):
+            b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, steps=steps, lr=0.1, per_batch_params=True,
+                                                   warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}))
+            out[f"{name}_alpha_lower_{steps}"], out[f"{name}_alpha_upper_{steps}"] = b.lower, b.upper
+        splits = {}
+        for x, st in relu_pre.items():
+            s8 = torch.zeros(st.lower.shape, dtype=torch.int8)
+            fl, fu, fs = st.lower.reshape(B, -1), st.upper.reshape(B, -1), s8.view(B, -1)
+            for bi in range(B):
+                idx = torch.nonzero((fl[bi] < 0) & (fu[bi] > 0)).flatten()
+                if len(idx) == 0:
+                    continue
+                pick = idx[torch.randint(0, len(idx), (2,), generator=g)]
+                fs[bi, pick] = (torch.randint(0, 2, (2,), generator=g) * 2 - 1).to(torch.int8)
+            splits[x] = s8
+            out[f"{name}_split_{x}"] = s8.reshape(B, -1)
+        try:
+            _env, pre_split = _forward_ibp_trace_mlp(m, spec, relu_split_state=splits)
+        except ValueError as e:  # an infeasible draw: record it, the tests skip the split part of this graph
+            out[f"{name}_split_infeasible"] = np.array(1)
+            continue
+        a1 = adaptive_alpha(pre_split)
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=True,
+                                                 warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a1.items()}))
+        out[f"{name}_beta_lower_3"], out[f"{name}_beta_upper_3"] = b.lower, b.upper
+        for x, v in bt.beta_by_relu_input.items():
+            out[f"{name}_beta_{x}_3"] = v.reshape(B, -1)
+    save("graph_alpha.npz", **out)
+
+
 def gen_lp_alpha() -> None:
     """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
     wl = W.make_workload("c3", batch=8)
@@ -672,7 +717,7 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "c1": gen_c1, "c2": gen_c2, "c3": gen_c3, "c4": gen_c4, "c5": gen_c5, "fused_region": gen_fused_region,
               "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce,
               "objectives": gen_objectives, "conv_beta": gen_conv_beta,
-              "conv_certificate": gen_conv_certificate}
+              "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha}
 
 
 def main() -> None:

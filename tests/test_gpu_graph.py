@@ -37,17 +37,69 @@ def test_graph_matches_reference_golden(dev, golden, name):
     assert bool((crown.lower <= crown.upper + 1e-5).all())
 
 
-def test_chain_modules_keep_the_fused_path_and_unsupported_inputs_are_refused(dev):
+def test_chain_modules_keep_the_fused_path_and_unsupported_modes_are_refused(dev):
     from boundflow_b200 import workloads as W
-    from boundflow_b200.crown import needs_graph_path, run_crown_ibp_mlp
+    from boundflow_b200.crown import needs_graph_path, run_alpha_beta_crown_mlp
     from boundflow_b200.ir import InputSpec
 
     assert not needs_graph_path(W.make_workload("c1").module)
     assert not needs_graph_path(W.make_workload("c2", batch=1).module)
-    module, _x, lo, up, _C = W.make_graph_cases()["fanout_mlp"]
+    module, _x, lo, up, C = W.make_graph_cases()["fanout_mlp"]
     spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    with pytest.raises(NotImplementedError):   # shared parameters on a graph
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=False)
     with pytest.raises(NotImplementedError):
-        run_crown_ibp_mlp(module, spec, relu_split_state={"h": torch.zeros(5, 24, dtype=torch.int8, device=dev)})
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="gap")
+
+
+@pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"])
+def test_graph_alpha_and_alpha_beta_match_reference_golden(dev, golden, name):
+    """The per-domain alpha loop and the alpha-beta loop with ReLU splits on graphs that are not chains, against the
+    reference's `run_alpha_beta_crown_mlp` outputs (tests/golden/graph_alpha.npz), plus plain CROWN with a split and an
+    explicit alpha against the graph oracle."""
+    import numpy as np
+
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from boundflow_b200.dag import forward_ibp_dag
+    from boundflow_b200.ir import InputSpec
+    from oracle import graph_oracle as GO
+
+    g = golden("graph_alpha.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    Cd = None if C is None else C.to(dev)
+    tr = forward_ibp_dag(module, spec)
+    adaptive = lambda t: {x: ((t.pre_l[x] >= 0) | ((t.pre_l[x] < 0) & (t.pre_u[x] > 0) & (t.pre_u[x] > -t.pre_l[x]))).float() for x in t.pre_l}  # noqa: E731
+    a0 = adaptive(tr)
+    for steps in (1, 4):
+        b, a, _bt, stats = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=steps, lr=0.1, per_batch_params=True,
+                                                   warm_start_alpha=AlphaState(dict(a0)))
+        assert_close(b.lower.reshape(B, -1), g[f"{name}_alpha_lower_{steps}"].reshape(B, -1), f"alpha lower after {steps}")
+        assert_close(b.upper.reshape(B, -1), g[f"{name}_alpha_upper_{steps}"].reshape(B, -1), f"alpha upper after {steps}")
+        assert set(a.alpha_by_relu_input) == set(tr.pre_l) == set(stats.relu_inputs)
+    splits = {x: torch.from_numpy(np.asarray(g[f"{name}_split_{x}"])).to(torch.int8).to(dev) for x in tr.pre_l}
+    tr_s = forward_ibp_dag(module, spec, splits)
+    assert int(tr_s.infeasible.sum()) == 0
+    b, _a, bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=True,
+                                            warm_start_alpha=AlphaState(adaptive(tr_s)))
+    assert_close(b.lower.reshape(B, -1), g[f"{name}_beta_lower_3"].reshape(B, -1), "alpha-beta lower after 3")
+    assert_close(b.upper.reshape(B, -1), g[f"{name}_beta_upper_3"].reshape(B, -1), "alpha-beta upper after 3")
+    for x in tr.pre_l:
+        assert_close(bt.beta_by_relu_input[x].reshape(B, -1), g[f"{name}_beta_{x}_3"], f"beta {x} after 3", atol=1e-5)
+    # plain CROWN with splits, an explicit alpha and a lower-side add term, against the graph oracle
+    gen = torch.Generator("cpu").manual_seed(3)
+    alpha = {x: torch.rand(B, int(tr.pre_l[x].shape[1]), generator=gen) for x in tr.pre_l}
+    add = {x: -0.05 * torch.rand(B, int(tr.pre_l[x].shape[1]), generator=gen) * splits[x].cpu().float() for x in tr.pre_l}
+    got = run_crown_ibp_mlp(module, spec, linear_spec_C=Cd, relu_split_state=splits, relu_alpha={x: a.to(dev) for x, a in alpha.items()},
+                            relu_pre_add_coeff_l={x: a.to(dev) for x, a in add.items()})
+    env, pre = GO.forward_ibp_graph(module, lo, up, splits={x: s.cpu() for x, s in splits.items()})
+    n_out = env["out"][0].reshape(B, -1).shape[1]
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+    ref_l, ref_u = GO.crown_backward_graph(module, env, pre, Cb, lo, up, alpha=alpha, add_l=add)
+    assert_close(got.lower.reshape(B, -1), ref_l, "CROWN lower with split, alpha and add term")
+    assert_close(got.upper.reshape(B, -1), ref_u, "CROWN upper with split, alpha and add term")
 
 
 def test_building_blocks_against_torch(dev):

@@ -2,6 +2,7 @@
 made by tests/golden/make_golden.py) and against the literal known-answer cases of
 the reference's own tests."""
 import numpy as np
+import pytest
 import torch
 
 from boundflow_b200 import workloads as W
@@ -417,3 +418,39 @@ def test_first_layer_certificate_over_a_conv_first_layer(golden):
         assert bad == bool(g["infeasible"][k]), name
         if bad:
             assert best < -1e-6 and abs(best - float(g["max_value"][k])) <= 0.5 * abs(float(g["max_value"][k])) + 1e-3, name
+
+
+GRAPH_NAMES = ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"]
+
+
+@pytest.mark.parametrize("name", GRAPH_NAMES)
+def test_graph_oracle_crown_and_alpha_beta(golden, name):
+    """oracle/graph_oracle.py against the reference on the non-chain graphs: CROWN-IBP (graph_cases.npz), the per-domain
+    alpha loop and the alpha-beta loop with splits (graph_alpha.npz)."""
+    from oracle import graph_oracle as GO
+
+    gc, ga = golden("graph_cases.npz"), golden("graph_alpha.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = lo.shape[0]
+    env, relu_pre = GO.forward_ibp_graph(module, lo, up)
+    out_l, out_u = env["out"]
+    assert_close(out_l, gc[f"{name}_ibp_lower"], "ibp lower")
+    assert_close(out_u, gc[f"{name}_ibp_upper"], "ibp upper")
+    n_out = out_l.reshape(B, -1).shape[1]
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+    lower, upper = GO.crown_backward_graph(module, env, relu_pre, Cb, lo, up)
+    assert_close(lower, gc[f"{name}_crown_lower"].reshape(B, -1), "crown lower")
+    assert_close(upper, gc[f"{name}_crown_upper"].reshape(B, -1), "crown upper")
+    a0 = GO.adaptive_alpha_init_graph(relu_pre)
+    for steps in (1, 4):
+        lo_a, up_a, _a, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=steps, lr=0.1, alpha0=a0)
+        assert_close(lo_a, ga[f"{name}_alpha_lower_{steps}"].reshape(B, -1), f"alpha lower after {steps}")
+        assert_close(up_a, ga[f"{name}_alpha_upper_{steps}"].reshape(B, -1), f"alpha upper after {steps}")
+    splits = {x: torch.from_numpy(np.asarray(ga[f"{name}_split_{x}"])).to(torch.int8) for x in relu_pre}
+    _env, pre_split = GO.forward_ibp_graph(module, lo, up, splits=splits)
+    a1 = GO.adaptive_alpha_init_graph(pre_split)
+    lo_b, up_b, _a, beta = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, alpha0=a1, splits=splits, optimize_beta=True)
+    assert_close(lo_b, ga[f"{name}_beta_lower_3"].reshape(B, -1), "alpha-beta lower after 3")
+    assert_close(up_b, ga[f"{name}_beta_upper_3"].reshape(B, -1), "alpha-beta upper after 3")
+    for x, b in beta.items():
+        assert_close(b, ga[f"{name}_beta_{x}_3"], f"beta {x} after 3", atol=1e-5)
