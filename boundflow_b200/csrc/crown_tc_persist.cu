@@ -27,14 +27,14 @@
 // (crown_tc.cu, 128 x 512 tiles).  Per-role cycle counts (clock64 around every wait, CTA 0) show why: a 128 x 256
 // tile halves the MMA work that one produced coefficient block feeds (12 MMAs instead of 24), the producers need
 // about 4 k clock cycles per 128 x 32 block whether it feeds 12 or 24 MMAs, so the MMA thread waits for coefficient
-// tiles 50 % of the time; with every global load switched off the same kernel still needs 200 cycles per MMA because
-// the MMAs' shared-memory operand reads (12 KB per instruction) plus the producers' and the copy engine's writes
-// saturate the 128 B/clk shared-memory port.  The one-tile-per-CTA kernel sits at 88 % of that shared-memory
-// bound (448 KB per k-block in 4.0 k cycles).  Sharing the weight tile between the two CTAs of a cluster (crown_tc.cu,
-// PAIR) removes a third of that traffic and was measured slower, so the producers' own latency chain (about 370
-// instructions per warp and k-block at 40 % issue utilisation, slope vectors loaded and consumed in the same
-// iteration) is the limit that counts; loading the slope vectors a k-block ahead needs 16-24 registers that 576-thread
-// CTAs do not have (spills, 256 us against 243 us).
+// tiles 50 % of the time.  Further measurements on the same layer: with the producers doing nothing but arriving on
+// their barrier (no loads, no transform, no stores) this kernel reaches 173 us (223 TFLOP/s fp32-equivalent; 201 us
+// with its weight copies on, which a 128 x 256 tile needs twice as often per MMA), i.e. 140 clock cycles per MMA plus
+// about 20 % of barrier round trips with two coefficient stages - so the one-tile-per-CTA kernel (196-200 TFLOP/s with
+// the full prologue) is within about 12 % of what this pipeline structure can give.  Tried on the one-tile kernel
+// without gain: CTA pairs sharing the weight tile (crown_tc.cu, PAIR: 277 us against 243 us per launch), the slope
+// vectors loaded a k-block ahead in registers (96-register cap of 576-thread CTAs, spills: 256 us) or software-
+// pipelined per row (247.5 us against 247.8 us).
 // The kernel stays for problems with few row blocks, where its narrower tiles (a half or a quarter of a packed
 // weight image) give more CTAs work: a 1152 x 256 x 256 layer launches 36 tiles instead of 9 and runs in 23 us
 // instead of 26 us.
