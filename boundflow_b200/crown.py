@@ -577,6 +577,45 @@ def alpha_crown_from_trace(
     return best_lower, best_upper, best_alpha, alpha, best_metric, best_beta
 
 
+def _shared_alpha_other(trace, linear_spec_C, alpha0, *, steps, lr, objective, spec_reduce, soft_tau, lb_weight, ub_weight):
+    """Shared-alpha loop for the objectives / reductions beyond lower / mean (bf_chain_alpha_crown_shared_objective)."""
+    chain, B, device = trace.chain, trace.B, trace.mid.device
+    if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
+        raise ValueError(f"soft_tau must be >0, got {soft_tau}")
+    if float(lb_weight) < 0.0 or float(ub_weight) < 0.0:
+        raise NotImplementedError("the CUDA backend takes non-negative lb_weight / ub_weight")
+    n_out = 1
+    for d in chain.output_shape:
+        n_out *= int(d)
+    C = _expand_spec(linear_spec_C, B, n_out, device)
+    S = int(C.shape[1])
+    codes = {"mean": _lib.REDUCE_MEAN, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
+    alpha = [a.detach().to(device=device, dtype=torch.float32).reshape(n).contiguous().clone() for a, n in zip(alpha0, chain.relu_widths)]
+    best_alpha = [torch.empty_like(a) for a in alpha]
+    best_metric = torch.empty(1, dtype=torch.float32, device=device)
+    paired = objective in ("gap", "both")
+    rows_C = torch.cat([C, -C], dim=1).contiguous() if paired else (-C if objective == "upper" else C)
+    n_rows = 2 * S if paired else S
+    best_rows = torch.empty(B, n_rows, dtype=torch.float32, device=device)
+    best_upper = None if paired else torch.empty(B, S, dtype=torch.float32, device=device)
+    nbytes = int(chain.lib.bf_chain_alpha_shared_workspace_bytes(chain.handle, B, n_rows, 0))
+    ws = _Workspace.get(device, nbytes)
+    obj_code = {"lower": 0, "upper": 0, "gap": _lib.OBJECTIVE_GAP, "both": _lib.OBJECTIVE_BOTH}[objective]
+    _lib.check(
+        chain.lib.bf_chain_alpha_crown_shared_objective(
+            chain.handle, _lib.ptr(rows_C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.ptr_array(alpha), _lib.ptr_array(best_alpha),
+            _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
+            _lib.ptr(best_rows), _lib.ptr(best_upper), _lib.ptr(best_metric), int(steps), float(lr), obj_code, codes[spec_reduce], float(soft_tau),
+            float(lb_weight), float(ub_weight), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+        )
+    )
+    if paired:
+        return best_rows[:, :S].contiguous(), -best_rows[:, S:], best_alpha, alpha, best_metric
+    if objective == "upper":
+        return -best_upper, -best_rows, best_alpha, alpha, best_metric
+    return best_rows, best_upper, best_alpha, alpha, best_metric
+
+
 def _alpha_crown_other_objective(trace, linear_spec_C, alpha0, *, steps, lr, spec_reduce, soft_tau, objective, lb_weight, ub_weight,
                                  beta_splits, beta0):
     """objective "upper" = the lower loop on the negated spec rows (upper(C) = -lower(-C)); "gap" and "both" evaluate
@@ -649,11 +688,23 @@ def alpha_grad_from_trace(trace: ForwardTrace, linear_spec_C: torch.Tensor, alph
 def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[torch.Tensor], alpha0: Sequence[torch.Tensor], *,
                                   steps: int, lr: float, want_upper: bool = True,
                                   beta_splits: Optional[Sequence[Optional[torch.Tensor]]] = None,
-                                  beta0: Optional[Sequence[torch.Tensor]] = None):
+                                  beta0: Optional[Sequence[torch.Tensor]] = None, objective: str = "lower", spec_reduce: str = "mean",
+                                  soft_tau: float = 1.0, lb_weight: float = 1.0, ub_weight: float = 1.0):
     """Device-resident loop with ONE alpha (and, with `beta_splits`, one beta) per neuron for the
     whole batch; returns (best_lower, best_upper|None, best_alpha list [n_r], last alpha list,
-    best_metric [1]) and, with beta, a sixth element best_beta list [n_r]."""
+    best_metric [1]) and, with beta, a sixth element best_beta list [n_r].  `objective` lower | upper | gap | both
+    and `spec_reduce` mean | min | softmin as in run_alpha_crown_mlp (alpha_crown.py:93-134); anything but
+    lower / mean runs alpha only."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
+    if objective not in ("lower", "upper", "gap", "both"):
+        raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
+    if spec_reduce not in ("mean", "min", "softmin"):
+        raise ValueError(f"spec_reduce={spec_reduce!r}: the shared-parameter loop takes mean | min | softmin")
+    if objective != "lower" or spec_reduce != "mean":
+        if beta_splits is not None:
+            raise NotImplementedError("the CUDA backend combines beta parameters with objective='lower', spec_reduce='mean' in the shared-parameter loop")
+        return _shared_alpha_other(trace, linear_spec_C, alpha0, steps=steps, lr=lr, objective=objective, spec_reduce=spec_reduce,
+                                   soft_tau=soft_tau, lb_weight=lb_weight, ub_weight=ub_weight)
     n_out = 1
     for d in chain.output_shape:
         n_out *= int(d)
@@ -721,10 +772,8 @@ def run_alpha_crown_mlp(
     (`run_alpha_crown_mlp`, runtime/alpha_crown.py:137-261): steps+1 evaluations, Adam on
     -mean(lower), clamp to [0,1], and the bounds / alpha of the evaluation with the best
     whole-batch metric.  Returns (IntervalState, AlphaState, AlphaCrownStats) like the
-    reference.  The CUDA backend implements objective="lower" with spec_reduce="mean" on
-    affine (relu affine)* chains (Linear / Conv2d / flatten); other settings raise NotImplementedError."""
-    if objective != "lower" or spec_reduce != "mean":
-        raise NotImplementedError("the CUDA backend implements objective='lower' with spec_reduce='mean' for the shared-alpha loop")
+    reference, for objective lower | upper | gap | both and spec_reduce mean | min | softmin, on
+    affine (relu affine)* chains (Linear / Conv2d / flatten)."""
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, device = trace.chain, trace.mid.device
@@ -740,7 +789,9 @@ def run_alpha_crown_mlp(
             alpha0.append(a.detach().to(device=device, dtype=torch.float32).reshape(n))
         else:
             alpha0.append(torch.full((n,), float(alpha_init), dtype=torch.float32, device=device))
-    best_l, best_u, best_a, _last, _metric = shared_alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr)
+    best_l, best_u, best_a, _last, _metric = shared_alpha_crown_from_trace(trace, linear_spec_C, alpha0, steps=steps, lr=lr, objective=objective,
+                                                                           spec_reduce=spec_reduce, soft_tau=soft_tau, lb_weight=lb_weight,
+                                                                           ub_weight=ub_weight)
     dev = normalize_input_spec(input_spec).center.device
     bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
     state = AlphaState({n: a.reshape(tuple(s)).to(dev) for n, a, s in zip(chain.relu_input_names, best_a, chain.relu_shapes)})
@@ -852,15 +903,13 @@ def run_alpha_beta_crown_mlp(
     spec_reduce mean | min | softmin (with `soft_tau`) as in the reference, plus "sum" for the lower
     objective; min / softmin and the upper / gap / both objectives run alpha only (the reference applies the
     beta term to objective="lower" alone, and its min / softmin with beta is not built here).  Shared mode:
-    objective="lower", spec_reduce="mean".  For a single node the first-layer
+    the same objectives and mean | min | softmin, with beta for objective="lower", spec_reduce="mean".  For a single node the first-layer
     infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
     reference (Linear first layers; `first_layer_certificate` gives it for whole batches).
     Infeasible splits raise ValueError like the reference.
     """
     if objective not in ("lower", "upper", "gap", "both"):
         raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
-    if objective != "lower" and not per_batch_params:
-        raise NotImplementedError("the shared-parameter loop of the CUDA backend optimises the lower bound only")
     has_split = bool(relu_split_state)
     if optimize_beta is None:
         optimize_beta = has_split
@@ -907,12 +956,13 @@ def run_alpha_beta_crown_mlp(
             n_out *= int(d)
         linear_spec_C = torch.eye(n_out, dtype=torch.float32, device=device)
     dev = normalize_input_spec(input_spec).center.device
-    if spec_reduce != "mean" and not per_batch_params:
-        raise NotImplementedError("the shared-parameter loop of the CUDA backend implements spec_reduce='mean'")
     loop = alpha_crown_from_trace if per_batch_params else shared_alpha_crown_from_trace
-    kw = ({"spec_reduce": spec_reduce, "soft_tau": soft_tau, "objective": objective, "lb_weight": lb_weight, "ub_weight": ub_weight}
-          if per_batch_params else {})
-    if optimize_beta:
+    kw = {"spec_reduce": spec_reduce, "soft_tau": soft_tau, "objective": objective, "lb_weight": lb_weight, "ub_weight": ub_weight}
+    if objective != "lower":
+        # the beta term enters the lower objective only (alpha_beta_crown.py:763-785): alpha-only evaluation, beta handed back
+        best_l, best_u, best_a, _last, _metric = loop(trace, linear_spec_C, alpha0, steps=steps, lr=lr, **kw)
+        best_b = beta_start
+    elif optimize_beta:
         beta_splits = [relu_split_state.get(n) for n in chain.relu_input_names]
         best_l, best_u, best_a, _last, _metric, best_b = loop(
             trace, linear_spec_C, alpha0, steps=steps, lr=lr, beta_splits=beta_splits, beta0=beta_start, **kw)

@@ -406,6 +406,10 @@ namespace bf {
 
 struct SharedWs {
   std::vector<float*> m, v, mb, vb, part;
+  // per-domain objective values and scratch of the reductions / objectives other than the plain mean
+  float* dom_metric;
+  float* dom_rows;
+  int* dom_improve;
   size_t begin, bytes;  // extra region (after the per-domain layout), zero-initialised per call
 };
 
@@ -426,6 +430,9 @@ static size_t shared_ws_layout(const bf_chain* c, int B, int S, bool with_beta, 
     }
     w.part.push_back(cv.take<float>((size_t)chunks * n));
   }
+  w.dom_metric = cv.take<float>((size_t)B);
+  w.dom_rows = cv.take<float>((size_t)B * S);
+  w.dom_improve = cv.take<int>((size_t)B);
   w.bytes = cv.off - base_bytes;
   if (sw) *sw = w;
   return cv.off;
@@ -438,13 +445,14 @@ extern "C" size_t bf_chain_alpha_shared_workspace_bytes(const bf_chain* chain, i
   return bf::shared_ws_layout(chain, B, S, with_beta != 0, nullptr, nullptr, nullptr);
 }
 
-extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C, const float* const* pre_l,
-                                           const float* const* pre_u, float* const* alpha, float* const* best_alpha,
-                                           float* const* beta, float* const* best_beta, const int8_t* const* splits,
-                                           const int* split_strides, const float* mid, const float* rad, int norm_p, float eps,
-                                           float* best_lower, float* best_upper, float* best_metric, int steps, float lr,
-                                           void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
-  const char* who = "bf_chain_alpha_crown_shared";
+// objective 0: reduce(lower) over the S rows as given; BF_OBJECTIVE_GAP / _BOTH: the S rows are S/2 spec rows followed by
+// their negations.  The whole-batch metric is the mean over the domains of the per-domain objective.
+static int shared_loop(const char* who, const bf_chain* chain, const float* C, const float* const* pre_l,
+                       const float* const* pre_u, float* const* alpha, float* const* best_alpha, float* const* beta,
+                       float* const* best_beta, const int8_t* const* splits, const int* split_strides, const float* mid,
+                       const float* rad, int norm_p, float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
+                       float lr, int objective, float lb_weight, float ub_weight, int spec_reduce, float soft_tau, void* workspace,
+                       size_t workspace_bytes, int B, int S, bf_stream_t stream_) {
   BF_REQUIRE(chain && C && pre_l && pre_u && alpha && best_alpha && mid && best_lower && workspace, BF_E_INVALID,
              "%s: null argument", who);
   BF_REQUIRE(norm_p == BF_NORM_BOX || norm_p == BF_NORM_INF || norm_p == BF_NORM_L2 || norm_p == BF_NORM_L1, BF_E_INVALID,
@@ -455,6 +463,13 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   BF_REQUIRE(chain->affine_relu_alternating, BF_E_UNSUPPORTED, "%s: only affine (relu affine)* chains are supported", who);
   const bool with_beta = beta != nullptr;
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
+  const bool paired = objective != 0;
+  const bool weighted = paired || spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN;
+  BF_REQUIRE(spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN, BF_E_INVALID,
+             "%s: spec_reduce must be mean, min or softmin", who);
+  BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "%s: soft_tau must be positive", who);
+  BF_REQUIRE(!paired || (S % 2 == 0 && !best_upper), BF_E_INVALID, "%s: paired rows need an even row count and no separate upper output", who);
+  BF_REQUIRE(!weighted || !with_beta, BF_E_UNSUPPORTED, "%s: min / softmin and the gap / both objectives are not combined with beta parameters", who);
   bf::AlphaWs ws;
   bf::SharedWs sw;
   const size_t need = bf::shared_ws_layout(chain, B, S, with_beta, workspace, &ws, &sw);
@@ -490,14 +505,29 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
           return rc;
     rc = bf::alpha_sweep(chain, ws, C, BF_SIDE_LOWER, !last, with_beta, in, ws.cur, B, S, stream);
     if (rc != BF_OK) return rc;
-    if ((rc = bf::launch_shared_metric(ws.cur, M, metric, ws.improve, t == 0, stream)) != BF_OK) return rc;
+    if (!weighted) {
+      if ((rc = bf::launch_shared_metric(ws.cur, M, metric, ws.improve, t == 0, stream)) != BF_OK) return rc;
+    } else {
+      // per-domain objective and d objective / d row (first = 1: no per-domain best-of here), then the batch mean
+      float* row_weight = last ? nullptr : ws.row_weight;
+      rc = paired ? bf::launch_select_best_paired(ws.cur, sw.dom_rows, sw.dom_metric, sw.dom_improve, 1, objective, spec_reduce, soft_tau,
+                                                  lb_weight, ub_weight, row_weight, B, S / 2, stream)
+                  : bf::launch_select_best(ws.cur, sw.dom_rows, sw.dom_metric, sw.dom_improve, 1, spec_reduce, soft_tau, row_weight, B, S, stream);
+      if (rc != BF_OK) return rc;
+      if ((rc = bf::launch_shared_metric(sw.dom_metric, B, metric, ws.improve, t == 0, stream)) != BF_OK) return rc;
+    }
     if ((rc = bf::launch_copy_if(ws.cur, best_lower, M, ws.improve, stream)) != BF_OK) return rc;
     bf::AdamScalars sc{};
     if (!last) {
+      if (weighted) {
+        for (int r = 0; r < R; ++r)
+          if ((rc = bf::launch_scale_rows(ws.Ahat[r], ws.row_weight, M, width(r), stream)) != BF_OK) return rc;
+      }
       rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, BF_REDUCE_SUM, S);
-      sc.grad_scale = -1.0f / (float)M;  // loss = -mean over every domain and spec row
+      // loss = -mean over every domain and spec row; with row weights (which sum to the objective's weight per domain): -mean over domains
+      sc.grad_scale = weighted ? (-1.0f / (float)B) : (-1.0f / (float)M);
     }
     for (int r = 0; r < R; ++r) {
       rc = bf::launch_shared_adam(alpha[r], sw.m[r], sw.v[r], ws.grad[r], nullptr, 0, sw.part[r], ws.improve, best_alpha[r], sc,
@@ -524,6 +554,32 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
     if (rc != BF_OK) return rc;
   }
   return BF_OK;
+}
+
+extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                           const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                           float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                           const int* split_strides, const float* mid, const float* rad, int norm_p, float eps,
+                                           float* best_lower, float* best_upper, float* best_metric, int steps, float lr,
+                                           void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  return shared_loop("bf_chain_alpha_crown_shared", chain, C, pre_l, pre_u, alpha, best_alpha, beta, best_beta, splits, split_strides,
+                     mid, rad, norm_p, eps, best_lower, best_upper, best_metric, steps, lr, 0, 1.f, 1.f, BF_REDUCE_MEAN, 1.f, workspace,
+                     workspace_bytes, B, S, stream);
+}
+
+extern "C" int bf_chain_alpha_crown_shared_objective(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                                     const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                                     const float* mid, const float* rad, int norm_p, float eps, float* best_rows,
+                                                     float* best_upper, float* best_metric, int steps, float lr, int objective,
+                                                     int spec_reduce, float soft_tau, float lb_weight, float ub_weight,
+                                                     void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  const char* who = "bf_chain_alpha_crown_shared_objective";
+  BF_REQUIRE(objective == 0 || objective == BF_OBJECTIVE_GAP || objective == BF_OBJECTIVE_BOTH, BF_E_INVALID,
+             "%s: objective must be 0 (lower), BF_OBJECTIVE_GAP or BF_OBJECTIVE_BOTH", who);
+  BF_REQUIRE(S > 0, BF_E_INVALID, "%s: S must be positive", who);
+  return shared_loop(who, chain, C, pre_l, pre_u, alpha, best_alpha, nullptr, nullptr, nullptr, nullptr, mid, rad, norm_p, eps, best_rows,
+                     objective == 0 ? best_upper : nullptr, best_metric, steps, lr, objective, lb_weight, ub_weight, spec_reduce,
+                     soft_tau, workspace, workspace_bytes, B, objective == 0 ? S : 2 * S, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -575,6 +575,21 @@ int bf_chain_alpha_crown_shared(const bf_chain* chain,
                                 float* best_lower, float* best_upper, float* best_metric,
                                 int steps, float lr,
                                 void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+/* The shared-alpha loop with the other objectives and spec reductions of run_alpha_crown_mlp
+ * (boundflow/runtime/alpha_crown.py:93-134, 137-261: `objective`, `spec_reduce`, `soft_tau`, `lb_weight`, `ub_weight`):
+ * the whole-batch metric is the mean over the domains of the per-domain objective.  objective 0 = "lower" on the S rows
+ * as given (spec_reduce BF_REDUCE_MEAN, _MIN or _SOFTMIN; best_rows [B,S], best_upper [B,S] or NULL); BF_OBJECTIVE_GAP /
+ * _BOTH take PAIRED rows like bf_chain_alpha_crown_objective (C [B,2S,n_out], best_rows [B,2S], best_upper ignored;
+ * workspace for 2*S rows); "upper" is "lower" on the negated rows.  Alpha only. */
+int bf_chain_alpha_crown_shared_objective(const bf_chain* chain,
+                                          const float* C,
+                                          const float* const* pre_l, const float* const* pre_u,
+                                          float* const* alpha, float* const* best_alpha,
+                                          const float* mid, const float* rad, int norm_p, float eps,
+                                          float* best_rows, float* best_upper, float* best_metric,
+                                          int steps, float lr, int objective, int spec_reduce, float soft_tau,
+                                          float lb_weight, float ub_weight,
+                                          void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -603,7 +603,9 @@ def alpha_crown(
 
 
 def alpha_crown_shared(layers: Layers, inp: InputSet, C, *, steps: int, lr: float, alpha0: Optional[Sequence[torch.Tensor]] = None,
-                       alpha_init: float = 0.5, splits=None, trace: Optional[ForwardTrace] = None, optimize_beta: bool = False):
+                       alpha_init: float = 0.5, splits=None, trace: Optional[ForwardTrace] = None, optimize_beta: bool = False,
+                       objective: str = "lower", spec_reduce: str = "mean", soft_tau: float = 1.0, lb_weight: float = 1.0,
+                       ub_weight: float = 1.0):
     """alpha (and optionally beta) shared by every domain and spec row: `run_alpha_crown_mlp`
     (alpha_crown.py:137-261) and the `per_batch_params=False` mode of `run_alpha_beta_crown_mlp`
     (alpha_beta_crown.py:716-923), restated for objective="lower", spec_reduce="mean".
@@ -634,7 +636,26 @@ def alpha_crown_shared(layers: Layers, inp: InputSet, C, *, steps: int, lr: floa
         if optimize_beta:
             add_l = [None if sf is None else -bt.unsqueeze(0) * sf for bt, sf in zip(betas, split_f)]
         lower, upper = crown_backward(layers, inp, trace, C, alpha=[a.unsqueeze(0).expand(B, -1) for a in alphas], add_l=add_l)
-        metric = lower.mean(dim=1).mean() if lower.dim() == 2 else lower.mean()
+
+        # `_reduce_over_specs` / `_objective_metric`, alpha_crown.py:67-112: per-domain reduction, then the batch mean
+        def _reduce(x, direction):
+            if spec_reduce == "mean":
+                return x.mean()
+            if spec_reduce == "min":
+                return (x.min(dim=1).values if direction == "min" else x.max(dim=1).values).mean()
+            tau = float(soft_tau)
+            return ((-tau * torch.logsumexp(-x / tau, dim=1)) if direction == "min" else (tau * torch.logsumexp(x / tau, dim=1))).mean()
+
+        if objective == "lower":
+            metric = _reduce(lower, "min")
+        elif objective == "upper":
+            metric = -_reduce(upper, "max")
+        elif objective == "gap":
+            metric = -_reduce(upper - lower, "max")
+        elif objective == "both":
+            metric = float(lb_weight) * _reduce(lower, "min") - float(ub_weight) * _reduce(upper, "max")
+        else:
+            raise ValueError(objective)
         if best_metric is None or float(metric.detach()) > best_metric:
             best_metric = float(metric.detach())
             best = (lower.detach().clone(), upper.detach().clone(), [a.detach().clone() for a in alphas], [b.detach().clone() for b in betas])

@@ -247,6 +247,29 @@ def gen_first_layer_certificate() -> None:
     save("first_layer_certificate.npz", **out)
 
 
+SHARED_OBJECTIVE_CASES = (("lower", "min"), ("lower", "softmin"), ("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("both", "mean"))
+
+
+def gen_shared_objectives() -> None:
+    """The reference's shared-alpha function `run_alpha_crown_mlp` (alpha_crown.py:137-261) with the objectives and spec
+    reductions beyond lower / mean, on c1 (8 inputs) and the CNN c2 (4 inputs), after 1 and 6 steps (lb_weight 1.0,
+    ub_weight 0.5)."""
+    from boundflow.runtime.alpha_crown import run_alpha_crown_mlp
+
+    out = {}
+    for cfg, batch, tau in (("c1", 8, 0.5), ("c2", 4, 20.0)):
+        wl = W.make_workload(cfg, batch=batch)
+        m = ref_module(wl)
+        spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+        out[f"{cfg}_tau"] = np.array(tau)
+        for obj, red in SHARED_OBJECTIVE_CASES:
+            for k in (1, 6):
+                b, _st, _ = run_alpha_crown_mlp(m, spec, linear_spec_C=wl.C, steps=k, lr=0.1, objective=obj, spec_reduce=red, soft_tau=tau,
+                                                lb_weight=1.0, ub_weight=0.5)
+                out[f"{cfg}_{obj}_{red}_lower_{k}"], out[f"{cfg}_{obj}_{red}_upper_{k}"] = b.lower, b.upper
+    save("shared_objectives.npz", **out)
+
+
 def gen_conv_certificate() -> None:
     """`_is_infeasible_split_first_layer_convex_combo` over a Conv2d first layer (alpha_beta_crown.py:325-387) on
     the cases of workloads.make_conv_certificate_cases."""
@@ -717,7 +740,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "c1": gen_c1, "c2": gen_c2, "c3": gen_c3, "c4": gen_c4, "c5": gen_c5, "fused_region": gen_fused_region,
               "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce,
               "objectives": gen_objectives, "conv_beta": gen_conv_beta,
-              "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha}
+              "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha,
+              "shared_objectives": gen_shared_objectives}
 
 
 def main() -> None:

@@ -82,3 +82,31 @@ def test_tensor_core_rows_split_domains_and_argument_errors(dev):
         alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=1, lr=0.1, objective="gap", spec_reduce="sum")
     with pytest.raises(NotImplementedError):
         alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=1, lr=0.1, objective="both", ub_weight=-1.0)
+
+
+SHARED_CASES = (("lower", "min"), ("lower", "softmin"), ("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("both", "mean"))
+
+
+@pytest.mark.parametrize("cfg,batch", [("c1", 8), ("c2", 4)])
+def test_shared_alpha_objectives_match_reference_golden(dev, golden, cfg, batch):
+    """The shared-alpha loop (`run_alpha_crown_mlp`) with the objectives and reductions beyond lower / mean, on an
+    MLP and on a CNN, against tests/golden/shared_objectives.npz (lb_weight 1.0, ub_weight 0.5)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_alpha_beta_crown_mlp, run_alpha_crown_mlp
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("shared_objectives.npz")
+    wl = W.make_workload(cfg, batch=batch)
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    for obj, red in SHARED_CASES:
+        for k in (1, 6):
+            b, st, stats = run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=k, lr=0.1, objective=obj, spec_reduce=red,
+                                               soft_tau=float(g[f"{cfg}_tau"]), lb_weight=1.0, ub_weight=0.5)
+            assert stats.objective == obj and stats.spec_reduce == red
+            assert_close(b.lower, g[f"{cfg}_{obj}_{red}_lower_{k}"], f"{cfg} shared {obj}/{red} lower after {k}")
+            assert_close(b.upper, g[f"{cfg}_{obj}_{red}_upper_{k}"], f"{cfg} shared {obj}/{red} upper after {k}")
+    # the alpha-beta function in its shared mode takes the same route (alpha start 0.5 in both functions)
+    b, _a, _bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=6, lr=0.1, per_batch_params=False, objective="gap",
+                                             spec_reduce="min", soft_tau=float(g[f"{cfg}_tau"]))
+    assert_close(b.lower, g[f"{cfg}_gap_min_lower_6"], f"{cfg} alpha-beta function, shared gap/min lower")
+    assert_close(b.upper, g[f"{cfg}_gap_min_upper_6"], f"{cfg} alpha-beta function, shared gap/min upper")

@@ -454,3 +454,21 @@ def test_graph_oracle_crown_and_alpha_beta(golden, name):
     assert_close(up_b, ga[f"{name}_beta_upper_3"].reshape(B, -1), "alpha-beta upper after 3")
     for x, b in beta.items():
         assert_close(b, ga[f"{name}_beta_{x}_3"], f"beta {x} after 3", atol=1e-5)
+
+
+SHARED_OBJECTIVE_CASES = (("lower", "min"), ("lower", "softmin"), ("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("both", "mean"))
+
+
+def test_shared_alpha_objectives_and_reductions(golden):
+    """`run_alpha_crown_mlp(objective=..., spec_reduce=...)` of the reference (alpha_crown.py:67-134, 137-261)."""
+    g = golden("shared_objectives.npz")
+    for cfg, batch in (("c1", 8), ("c2", 4)):
+        wl = W.make_workload(cfg, batch=batch)
+        inp = O.box_input(wl.lo, wl.up)
+        trace = O.forward_ibp_trace(wl.layers, inp)
+        for obj, red in SHARED_OBJECTIVE_CASES:
+            for k in (1, 6):
+                lo, up, _a, _t = O.alpha_crown_shared(wl.layers, inp, wl.C, steps=k, lr=0.1, trace=trace, objective=obj, spec_reduce=red,
+                                                      soft_tau=float(g[f"{cfg}_tau"]), lb_weight=1.0, ub_weight=0.5)
+                assert_close(lo, g[f"{cfg}_{obj}_{red}_lower_{k}"], f"{cfg} shared {obj}/{red} lower after {k}")
+                assert_close(up, g[f"{cfg}_{obj}_{red}_upper_{k}"], f"{cfg} shared {obj}/{red} upper after {k}")
