@@ -234,9 +234,11 @@ void refresh_switches(const bf_chain* c) {
   c->sw.adjoint_kernel = env_is_one("BF_B200_ADJ_ROWMAJOR") ? 1 : (env_is_one("BF_B200_ADJ_FEATURE_MAJOR") ? 2 : 0);
   c->sw.no_windows = getenv("BF_B200_NO_WINDOWS") != nullptr;
   c->sw.persistent_bwd = env_is_one("BF_B200_BWD_PERSISTENT");
+  const char* rows = getenv("BF_B200_TC_MIN_ROWS");
+  c->sw.tc_min_rows = (rows && atoi(rows) > 0) ? atoi(rows) : 256;
 }
 
-bool tc_may_run(const bf_chain* c, int M) { return c->status != nullptr && !c->pk_bwd.empty() && !c->sw.force_ffma && M >= 256; }
+bool tc_may_run(const bf_chain* c, int M) { return c->status != nullptr && !c->pk_bwd.empty() && !c->sw.force_ffma && M >= c->sw.tc_min_rows; }
 
 static bool adjoint_feature_major(const bf_chain* c, int M, int N) {
   if (c->sw.adjoint_kernel == 1) return false;
@@ -247,7 +249,7 @@ static bool adjoint_feature_major(const bf_chain* c, int M, int N) {
 
 static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoint, int M, int K, int N) {
   if (c->pk_bwd.empty() || c->sw.force_ffma) return nullptr;
-  if (M < 256 || K < 32 || N < 32) return nullptr;  // tiny problems stay on the FFMA tiles
+  if (M < c->sw.tc_min_rows || K < 32 || N < 32) return nullptr;  // tiny problems stay on the FFMA tiles
   return adjoint ? c->pk_adj[layer] : c->pk_bwd[layer];
 }
 

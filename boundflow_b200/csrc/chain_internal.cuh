@@ -25,6 +25,7 @@ struct bf_chain {
     bool no_windows = false;        // BF_B200_NO_WINDOWS set: identity-row sweeps keep full feature maps
     bool persistent_bwd = false;    // BF_B200_BWD_PERSISTENT=1: persistent warp-specialised backward kernel (128 x 256 tiles, double-buffered
                                     // accumulators) instead of the one-tile-per-CTA kernel; measured slower on wide layers, see crown_tc_persist.cu
+    int tc_min_rows = 256;          // coefficient rows from which Linear layers run on the tensor-core kernels (BF_B200_TC_MIN_ROWS)
   };
   mutable Switches sw;
 };

@@ -87,10 +87,14 @@ def test_warm_start_zero_steps_and_refusals(dev):
     bw, stw, _ = run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), steps=0, warm_start=warm)
     for n in wl.relu_names:
         assert float((stw.alpha_by_relu_input[n] - 0.25).abs().max()) == 0.0
-    with pytest.raises(NotImplementedError):
-        run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), objective="gap")
-    with pytest.raises(NotImplementedError):
-        run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), spec_reduce="softmin")
+    # the other objectives and reductions run (tests/test_gpu_objectives.py pins them); unknown names and a
+    # non-positive softmin temperature raise like the reference
+    with pytest.raises(ValueError):
+        run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), objective="tightest")
+    with pytest.raises(ValueError):
+        run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), spec_reduce="softmin", soft_tau=0.0)
+    with pytest.raises(ValueError):
+        run_alpha_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), spec_reduce="sum")
 
 
 def test_shared_alpha_beta_matches_reference_golden(dev, golden):
