@@ -221,3 +221,35 @@ def alpha_crown_graph(module: Any, lo, up, C, *, steps: int, lr: float, alpha0: 
             for b in betas.values():
                 b.clamp_(0.0)
     return best[1], best[2], best[3], best[4]
+
+
+def concrete_forward_graph(module: Any, x: torch.Tensor, *, input_name: str = "input", record_pre: bool = False):
+    """Plain forward pass of the graph at concrete points x (any dtype / device); with `record_pre` also returns the
+    inputs of every ReLU (name -> tensor), which the soundness tests use to keep the samples that satisfy a split."""
+    P = {k: torch.as_tensor(v).to(dtype=x.dtype, device=x.device) for k, v in module.bindings.get("params", {}).items()}
+    env = {input_name: x}
+    pre = {}
+    B = x.shape[0]
+    get = lambda n: env[n] if n in env else P[n]  # noqa: E731
+    for op in _task(module).ops:
+        t, out = op.op_type, op.outputs[0]
+        if t == "linear":
+            y = get(op.inputs[0]).reshape(B, -1).matmul(P[op.inputs[1]].t())
+            env[out] = y + P[op.inputs[2]] if len(op.inputs) == 3 else y
+        elif t == "conv2d":
+            b = P[op.inputs[2]] if len(op.inputs) == 3 else None
+            env[out] = F.conv2d(get(op.inputs[0]), P[op.inputs[1]], b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)))
+        elif t == "relu":
+            pre[op.inputs[0]] = get(op.inputs[0])
+            env[out] = torch.relu(get(op.inputs[0]))
+        elif t == "add":
+            env[out] = get(op.inputs[0]) + get(op.inputs[1])
+        elif t in ("flatten", "reshape"):
+            v = get(op.inputs[0])
+            env[out] = v.reshape(B, -1) if t == "flatten" else v.reshape((B,) + tuple(int(d) for d in op.attrs.get("shape", ()))[1:])
+        elif t == "concat":
+            env[out] = torch.cat([get(n) for n in op.inputs], dim=1)
+        else:
+            raise NotImplementedError(t)
+    y = env[_task(module).output_values[0]]
+    return (y, pre) if record_pre else y

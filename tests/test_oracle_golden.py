@@ -437,6 +437,8 @@ def test_graph_oracle_crown_and_alpha_beta(golden, name):
     assert_close(out_l, gc[f"{name}_ibp_lower"], "ibp lower")
     assert_close(out_u, gc[f"{name}_ibp_upper"], "ibp upper")
     n_out = out_l.reshape(B, -1).shape[1]
+    y_mid = GO.concrete_forward_graph(module, (lo + up) / 2)   # the sampler of the soundness tests: inside the interval bounds
+    assert bool((y_mid >= out_l - 1e-5).all()) and bool((y_mid <= out_u + 1e-5).all())
     Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
     lower, upper = GO.crown_backward_graph(module, env, relu_pre, Cb, lo, up)
     assert_close(lower, gc[f"{name}_crown_lower"].reshape(B, -1), "crown lower")
