@@ -236,6 +236,7 @@ void refresh_switches(const bf_chain* c) {
   c->sw.persistent_bwd = env_is_one("BF_B200_BWD_PERSISTENT");
   const char* rows = getenv("BF_B200_TC_MIN_ROWS");
   c->sw.tc_min_rows = (rows && atoi(rows) > 0) ? atoi(rows) : 256;
+  c->sw.tc_auto = !(rows && atoi(rows) > 0);
 }
 
 bool tc_may_run(const bf_chain* c, int M) { return c->status != nullptr && !c->pk_bwd.empty() && !c->sw.force_ffma && M >= c->sw.tc_min_rows; }
@@ -250,6 +251,7 @@ static bool adjoint_feature_major(const bf_chain* c, int M, int N) {
 static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoint, int M, int K, int N) {
   if (c->pk_bwd.empty() || c->sw.force_ffma) return nullptr;
   if (M < c->sw.tc_min_rows || K < 32 || N < 32) return nullptr;  // tiny problems stay on the FFMA tiles
+  if (c->sw.tc_auto && ffma_fits_one_wave(M, N)) return nullptr;   // so do layers whose 64 x 64 tiles fit one wave
   return adjoint ? c->pk_adj[layer] : c->pk_bwd[layer];
 }
 
@@ -272,7 +274,7 @@ int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos
     return launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, add, pk, L.bias, A_prev, delta, accumulate, mid, rad, partial,
                                       side, M, S, K, N, c->status, stream);
   }
-  if (ptiles) *ptiles = crown_bwd_partial_tiles(N);
+  if (ptiles) *ptiles = crown_bwd_partial_tiles(N, M);
   return launch_crown_bwd_linear(A, dpos, dneg, epos, eneg, add, L.W, L.bias, A_prev, delta, accumulate, mid, rad, partial, side,
                                  M, S, K, N, stream);
 }

@@ -26,6 +26,8 @@ struct bf_chain {
     bool persistent_bwd = false;    // BF_B200_BWD_PERSISTENT=1: persistent warp-specialised backward kernel (128 x 256 tiles, double-buffered
                                     // accumulators) instead of the one-tile-per-CTA kernel; measured slower on wide layers, see crown_tc_persist.cu
     int tc_min_rows = 256;          // coefficient rows from which Linear layers run on the tensor-core kernels (BF_B200_TC_MIN_ROWS)
+    bool tc_auto = true;            // BF_B200_TC_MIN_ROWS unset: in addition, a layer whose 64 x 64 FFMA tiles fit one wave (two CTAs per
+                                    // SM) stays on the FFMA kernels, which are faster there and follow the reference's fp32 rounding
   };
   mutable Switches sw;
 };

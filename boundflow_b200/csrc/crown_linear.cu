@@ -19,23 +19,23 @@ struct BwdEpilogue {
   int side;              // BF_SIDE_LOWER: a*mid - |a|*rad ; BF_SIDE_UPPER: a*mid + |a|*rad
 };
 
-template <int PRO>
+template <int PRO, int MH, int NH>
 __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_bwd_linear_kernel(GemmArgs g, BwdEpilogue e) {
   __shared__ __align__(16) float smem[MAINLOOP_SMEM_FLOATS];
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * (64 * MH), n0 = blockIdx.y * (64 * NH);
   float acc[8][8];
-  gemm_mainloop<PRO, false>(g, m0, n0, acc, smem);
+  gemm_mainloop<PRO, false, MH, NH>(g, m0, n0, acc, smem);
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const bool vN = g.vecN != 0;
   const float sgn = (e.side == BF_SIDE_LOWER) ? -1.f : 1.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4 * MH; ++i) {
     const int row = m0 + tile_row(ty, i);
     const bool row_ok = row < g.M;
     float p = 0.f;
 #pragma unroll
-    for (int jb = 0; jb < 2; ++jb) {
+    for (int jb = 0; jb < NH; ++jb) {
       const int col = n0 + tile_col(tx, jb);
       const float4 v = make_float4(acc[i][jb * 4 + 0], acc[i][jb * 4 + 1], acc[i][jb * 4 + 2], acc[i][jb * 4 + 3]);
       if (row_ok && col < g.N) {
@@ -103,6 +103,14 @@ __global__ void __launch_bounds__(128) crown_bwd_thin_kernel(const float* __rest
   }
 }
 
+// 128 x 128 tiles leave most of the 148 SMs idle on small problems: below one CTA per SM the kernels switch to 64 x 64 tiles
+bool ffma_small_tiles(int M, int N) { return (long long)ceil_div(M, BM) * ceil_div(N, BN) < 148; }
+
+// Measured on B200 (c3: 1152 x 256 x 256 layers, 20 Adam steps): 8.9 ms on these tiles against 9.7 ms on the tcgen05
+// kernels, whose per-launch time of 23-36 us is a serial k-loop on 9-36 CTAs; at 144 rows 6.3 against 7.3 ms.  Beyond one
+// wave the tensor-core kernels win.
+bool ffma_fits_one_wave(int M, int N) { return (long long)ceil_div(M, 64) * ceil_div(N, 64) <= 2 * 148; }
+
 int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                             const float* add, const float* W, const float* kbias, float* A_prev, float* delta,
                             int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S,
@@ -127,15 +135,21 @@ int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg
   g.dpos = dpos; g.dneg = dneg; g.epos = epos; g.eneg = eneg; g.add = add; g.kbias = kbias;
   g.delta = delta; g.accumulate = accumulate;
   BwdEpilogue e{A_prev, mid, rad, partial, side};
-  dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
   timing_begin(T_BWD, stream);
-  crown_bwd_linear_kernel<PRO_RELU><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
+  if (ffma_small_tiles(M, N)) {  // 64 x 64 tiles: four times as many CTAs
+    dim3 grid(ceil_div(M, 64), ceil_div(N, 64));
+    crown_bwd_linear_kernel<PRO_RELU, 1, 1><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
+  } else {
+    dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
+    crown_bwd_linear_kernel<PRO_RELU, 2, 2><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
+  }
   timing_end(T_BWD, stream, 4.0 * (double)M * K + (A_prev ? 4.0 * (double)M * N : 0.0), 2.0 * (double)M * K * N);
   BF_CHECK_LAUNCH("crown_bwd_linear_kernel");
   return BF_OK;
 }
 
-int crown_bwd_partial_tiles(int N) { return ceil_div(N, BN); }
+// column tiles (= concretisation partial sums per row) of the backward kernel for this problem; M <= 0: the largest count
+int crown_bwd_partial_tiles(int N, int M) { return (M <= 0 || ffma_small_tiles(M, N)) ? ceil_div(N, 64) : ceil_div(N, BN); }
 
 // ---------------------------------------------------------------------------
 // Adjoint (gradient) sweep: g[M,N] = h_prev[M,K] * W[N,K]^T + b[N]
@@ -151,7 +165,7 @@ struct AdjEpilogue {
   const float* pre_l;  // [D,N]
   const float* pre_u;  // [D,N]
   float* hout;         // [M,N] or nullptr (last ReLU layer needs no adjoint point)
-  float* grad;         // [D,N], accumulated with atomicAdd (at most two tiles touch one entry when S <= 128)
+  float* grad;         // [D,N], accumulated with atomicAdd (at most two row tiles touch one entry when S <= the tile height, 64 or 128)
   float* gsum;         // [D,N] or nullptr: sum over the domain's rows of g (beta gradient), same accumulation
 };
 
@@ -159,22 +173,23 @@ constexpr int STAGE_LD = BN + 1;
 constexpr int ADJ_SMEM_BYTES = BM * STAGE_LD * (int)sizeof(float);
 static_assert(ADJ_SMEM_BYTES >= MAINLOOP_SMEM_FLOATS * (int)sizeof(float), "stage buffer must cover the main loop slabs");
 
-template <int PRO>
+template <int PRO, int MH, int NH>
 __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(GemmArgs g, AdjEpilogue e) {
   extern __shared__ __align__(16) float dsmem[];
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  constexpr int TM = 64 * MH, TN = 64 * NH;
+  const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
   float acc[8][8];
-  gemm_mainloop<PRO, true>(g, m0, n0, acc, dsmem);
+  gemm_mainloop<PRO, true, MH, NH>(g, m0, n0, acc, dsmem);
   // the main loop ends with __syncthreads(): the slabs may now be overwritten by the stage tile
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const bool vN = g.vecN != 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4 * MH; ++i) {
     const int rl = tile_row(ty, i);
     const int row = m0 + rl;
 #pragma unroll
-    for (int jb = 0; jb < 2; ++jb) {
+    for (int jb = 0; jb < NH; ++jb) {
       const int cl = tile_col(tx, jb);
       const int col = n0 + cl;
       float c4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -210,13 +225,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
   __syncthreads();
 
   // Deterministic per-domain reduction over the spec rows that fall inside this tile.
-  const int c = tid & (BN - 1);
-  const int half = tid >> 7;
-  const int m_end = min(m0 + BM, g.M);
+  const int c = tid % TN;                 // column of this thread in the reductions
+  const int half = tid / TN;              // domains are dealt round-robin to the GEMM_THREADS / TN thread groups
+  constexpr int GROUPS = GEMM_THREADS / TN;
+  const int m_end = min(m0 + TM, g.M);
   const int d_first = m0 / g.S;
   const int d_last = (m_end - 1) / g.S;
   const int col = n0 + c;
-  for (int d = d_first + half; d <= d_last; d += 2) {
+  for (int d = d_first + half; d <= d_last; d += GROUPS) {
     const int r_lo = max(d * g.S, m0) - m0;
     const int r_hi = min((d + 1) * g.S, m_end) - m0;
     float s = 0.f;
@@ -228,11 +244,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
   if (e.gsum != nullptr) {
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4 * MH; ++i) {
       const int rl = tile_row(ty, i);
       const int row = m0 + rl;
 #pragma unroll
-      for (int jb = 0; jb < 2; ++jb) {
+      for (int jb = 0; jb < NH; ++jb) {
         const int cl = tile_col(tx, jb);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -244,7 +260,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
       }
     }
     __syncthreads();
-    for (int d = d_first + half; d <= d_last; d += 2) {
+    for (int d = d_first + half; d <= d_last; d += GROUPS) {
       const int r_lo = max(d * g.S, m0) - m0;
       const int r_hi = min((d + 1) * g.S, m_end) - m0;
       float s = 0.f;
@@ -258,7 +274,7 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
                                 float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream) {
-  static SmemOptIn opt_in[2];
+  static SmemOptIn opt_in[4];
   GemmArgs g{};
   g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
   const void* kptrs[] = {Hprev, W, mid, rad};
@@ -269,15 +285,22 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   g.mid = mid; g.rad = rad;
   AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum};
-  dim3 grid(ceil_div(M, BM), ceil_div(N, BN));
+  const bool small = ffma_small_tiles(M, N);
+  dim3 grid(ceil_div(M, small ? 64 : BM), ceil_div(N, small ? 64 : BN));
   timing_begin(T_ADJ, stream);
-  if (first_layer) {
-    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_H0>, ADJ_SMEM_BYTES, opt_in[0], "crown_adjoint_linear_kernel")) return rc;
-    crown_adjoint_linear_kernel<PRO_H0><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
-  } else {
-    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_PLAIN>, ADJ_SMEM_BYTES, opt_in[1], "crown_adjoint_linear_kernel")) return rc;
-    crown_adjoint_linear_kernel<PRO_PLAIN><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);
+#define BF_ADJ_LAUNCH(PRO_, MH_, slot)                                                                                          \
+  {                                                                                                                             \
+    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_, MH_, MH_>, ADJ_SMEM_BYTES, opt_in[slot],                 \
+                                     "crown_adjoint_linear_kernel"))                                                            \
+      return rc;                                                                                                                \
+    crown_adjoint_linear_kernel<PRO_, MH_, MH_><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);                          \
   }
+  if (first_layer) {
+    if (small) BF_ADJ_LAUNCH(PRO_H0, 1, 0) else BF_ADJ_LAUNCH(PRO_H0, 2, 1)
+  } else {
+    if (small) BF_ADJ_LAUNCH(PRO_PLAIN, 1, 2) else BF_ADJ_LAUNCH(PRO_PLAIN, 2, 3)
+  }
+#undef BF_ADJ_LAUNCH
   timing_end(T_ADJ, stream, 4.0 * (double)M * K + 8.0 * (double)M * N, 2.0 * (double)M * K * N);
   BF_CHECK_LAUNCH("crown_adjoint_linear_kernel");
   return BF_OK;
@@ -347,8 +370,12 @@ extern "C" int bf_crown_relu_linear_bwd_packed(const float* A, int side, const f
                                                const float* bias, const void* pack, float* A_prev, float* delta, int accumulate,
                                                int B, int S, int n_cur, int n_prev, bf_stream_t stream_) {
   const long long M = (long long)B * S;
-  // small problems, delta-only calls and calls without a pack take the FP32 FFMA tiles
-  if (!pack || !A_prev || M < 256 || n_cur < 32 || n_prev < 32)
+  // small problems, delta-only calls and calls without a pack take the FP32 FFMA tiles; so does (unless BF_B200_TC_MIN_ROWS
+  // pins a plain row threshold) a problem whose 64 x 64 FFMA tiles fit one wave
+  const char* rows_env = getenv("BF_B200_TC_MIN_ROWS");
+  const int min_rows = (rows_env && atoi(rows_env) > 0) ? atoi(rows_env) : 256;
+  const bool one_wave = !(rows_env && atoi(rows_env) > 0) && M < 2147483647LL && bf::ffma_fits_one_wave((int)M, n_prev);
+  if (!pack || !A_prev || M < min_rows || one_wave || n_cur < 32 || n_prev < 32)
     return bf_crown_relu_linear_bwd(A, side, alpha_u, alpha_l, beta_u, beta_l, add, W, bias, A_prev, delta, accumulate, B, S, n_cur,
                                     n_prev, stream_);
   BF_REQUIRE(A && W, BF_E_INVALID, "bf_crown_relu_linear_bwd_packed: A and W must be non-null");

@@ -2,7 +2,11 @@
 // adjoint (gradient) sweep.  One CTA computes a 128x128 tile of
 //   C[M,N] = f(A)[M,K] * B[K,N]
 // with a 16-deep k-slab double-buffered through shared memory; every thread owns
-// an 8x8 micro-tile (two 4-row groups x two 4-column groups).  `f` is the
+// an 8x8 micro-tile (two 4-row groups x two 4-column groups).  The template parameters
+// MH / NH (1 or 2) give the number of 64-row / 64-column halves a CTA computes: 64x64,
+// 64x128 or 128x64 tiles (4x4 ... 4x8 micro-tiles, same thread mapping, the unused half
+// simply absent) put four times as many CTAs on problems whose 128x128 tiles would leave
+// most SMs idle.  `f` is the
 // per-element prologue applied while the A slab moves global -> shared:
 //   PRO_PLAIN : identity                    (top linear layer, adjoint hidden layers)
 //   PRO_RELU  : ReLU backward transformer   (sign-select slope, intercept and bias row sums)
@@ -47,7 +51,7 @@ struct GemmArgs {
 
 __device__ __forceinline__ float sgnf(float a) { return (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f); }
 
-template <int PRO, bool B_NT>
+template <int PRO, bool B_NT, int MH = 2, int NH = 2>
 __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, const int n0, float (&acc)[8][8],
                                               float* __restrict__ smem) {
   const int tid = threadIdx.x;
@@ -66,9 +70,9 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
   float rowacc[2] = {0.f, 0.f};
-  int dom[2];
+  int dom[2] = {0, 0};
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < MH; ++i) {
     int m = m0 + lrow + i * 64;
     dom[i] = (m < g.M) ? (m / g.S) : 0;
   }
@@ -78,7 +82,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   auto load_slab = [&](int kt) {
     const int k = kt * BK + lkc;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < MH; ++i) {
       const int m = m0 + lrow + i * 64;
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
       if (m < g.M && k < g.K) {
@@ -123,7 +127,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     }
     if (B_NT) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NH; ++i) {
         const int n = n0 + lrow + i * 64;
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
         if (n < g.N && k < g.K) b = load4_guard(g.Bm + (size_t)n * g.K, k, g.K, vK);
@@ -135,7 +139,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
         const int kk = kt * BK + bkr + i * 8;
         const int n = n0 + bnc;
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (kk < g.K && n < g.N) b = load4_guard(g.Bm + (size_t)kk * g.N, n, g.N, vN);
+        if (kk < g.K && n < g.N && bnc < 64 * NH) b = load4_guard(g.Bm + (size_t)kk * g.N, n, g.N, vN);
         breg[i] = b;
       }
     }
@@ -145,7 +149,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     float* as = As + stage * SLAB;
     float* bs = Bs + stage * SLAB;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < MH; ++i) {
       const int r = lrow + i * 64;
       as[(lkc + 0) * LDS + r] = areg[i].x;
       as[(lkc + 1) * LDS + r] = areg[i].y;
@@ -154,7 +158,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     }
     if (B_NT) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < NH; ++i) {
         const int r = lrow + i * 64;
         bs[(lkc + 0) * LDS + r] = breg[i].x;
         bs[(lkc + 1) * LDS + r] = breg[i].y;
@@ -179,15 +183,16 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       const float4 a0 = *reinterpret_cast<const float4*>(&as[kk * LDS + ty * 4]);
-      const float4 a1 = *reinterpret_cast<const float4*>(&as[kk * LDS + 64 + ty * 4]);
       const float4 b0 = *reinterpret_cast<const float4*>(&bs[kk * LDS + tx * 4]);
-      const float4 b1 = *reinterpret_cast<const float4*>(&bs[kk * LDS + 64 + tx * 4]);
+      float4 a1 = a0, b1 = b0;
+      if (MH == 2) a1 = *reinterpret_cast<const float4*>(&as[kk * LDS + 64 + ty * 4]);
+      if (NH == 2) b1 = *reinterpret_cast<const float4*>(&bs[kk * LDS + 64 + tx * 4]);
       const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < 4 * MH; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4 * NH; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
     if (kt + 1 < nk) store_slab(stage ^ 1);
     __syncthreads();
@@ -196,7 +201,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   // Row sums of the prologue: the 4 threads that loaded one row are adjacent lanes.
   if (PRO == PRO_RELU) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < MH; ++i) {
       float v = rowacc[i];
       v += __shfl_xor_sync(0xffffffffu, v, 1);
       v += __shfl_xor_sync(0xffffffffu, v, 2);

@@ -9,7 +9,9 @@ int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg
                             const float* add, const float* W, const float* kbias, float* A_prev, float* delta,
                             int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S,
                             int K, int N, cudaStream_t stream);
-int crown_bwd_partial_tiles(int N);
+int crown_bwd_partial_tiles(int N, int M = 0);  // M <= 0: the largest count any M gives (workspace sizing)
+// true when the 64 x 64 tiles of the FFMA contraction kernels cover an [M,N] result in one wave (two CTAs per SM)
+bool ffma_fits_one_wave(int M, int N);
 int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,

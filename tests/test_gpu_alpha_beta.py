@@ -45,7 +45,7 @@ def adjoint_kernel(request):
     os.environ.pop("BF_B200_ADJ_FEATURE_MAJOR", None)
 
 
-def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel):
+def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel, tc_from_256_rows):
     from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, crown_from_trace, ibp_trace, run_alpha_beta_crown_mlp
 
     g = golden("c4_split_alpha_beta.npz")
@@ -81,7 +81,7 @@ def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel):
     assert (got == g["branch_choices"]).all()
 
 
-def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev, adjoint_kernel):
+def test_beta_improves_over_alpha_only_and_matches_oracle_one_step(dev, adjoint_kernel, tc_from_256_rows):
     from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
     from oracle import crown_oracle as O
 

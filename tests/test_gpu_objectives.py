@@ -5,7 +5,7 @@ import torch
 
 from tests.helpers import assert_close
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("tc_from_256_rows")]
 
 CASES = (("upper", "mean"), ("gap", "mean"), ("both", "mean"), ("upper", "min"), ("gap", "min"), ("both", "softmin"), ("gap", "softmin"))
 

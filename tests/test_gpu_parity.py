@@ -393,7 +393,7 @@ def test_c3_alpha_crown(dev, golden):
     assert_close(s_bounds.lower.sum(dim=1), torch.as_tensor(g["sum_best_lower"]).sum(dim=1), "alpha(sum) objective")
 
 
-def test_c4_split_domains(dev, golden):
+def test_c4_split_domains(dev, golden, tc_from_256_rows):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import alpha_crown_from_trace, crown_from_trace, ibp_trace
     from oracle import crown_oracle as O

@@ -149,7 +149,7 @@ def test_run_ibp_scheduled_multitask_module_with_cuda_executor(dev):
 
 
 @pytest.mark.parametrize("widths,B", [((12, 20, 16, 5), 3), ((64, 512, 512, 10), 40)])
-def test_reference_crown_with_cuda_fused_executor(dev, widths, B):
+def test_reference_crown_with_cuda_fused_executor(dev, widths, B, tc_from_256_rows):
     """The reference's CROWN sweep (torch on the GPU) with every planned ReLU->affine region handed to the CUDA
     executor; the second case (360 coefficient rows, 512-wide layers) must reach the tcgen05 kernel."""
     from boundflow.runtime.crown_ibp import run_crown_ibp_mlp

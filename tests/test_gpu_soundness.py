@@ -110,7 +110,7 @@ def test_cnn_crown_with_intermediate_crown_sound(dev, name):
     assert w <= 1.0
 
 
-def test_c3_alpha_crown_sound(dev):
+def test_c3_alpha_crown_sound(dev, tc_from_256_rows):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, ibp_trace, run_alpha_beta_crown_mlp
     from boundflow_b200.ir import InputSpec
@@ -126,7 +126,7 @@ def test_c3_alpha_crown_sound(dev):
     assert w <= 1.0
 
 
-def test_c4_split_subdomains_sound_on_constraint_satisfying_samples(dev):
+def test_c4_split_subdomains_sound_on_constraint_satisfying_samples(dev, tc_from_256_rows):
     """Eight subdomains whose ten split neurons take the sign they have at a point of the box (so the subdomain is
     not empty); samples are the box corners, uniform points and perturbations of that point at several scales, and
     only samples that satisfy all ten split constraints are checked."""

@@ -5,7 +5,7 @@ import torch
 
 from tests.helpers import assert_close
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("tc_from_256_rows")]
 
 
 @pytest.fixture(scope="module")
