@@ -181,9 +181,33 @@ def test_c4_split_subdomains_sound_on_constraint_satisfying_samples(dev, tc_from
     assert worst <= 1.0
 
 
-def _split_soundness(name, fwd, lo, up, splits_flat, C, lower, upper, dev, n=N_SAMPLES, seed=0):
-    """Worst violation / tolerance over the samples of each input's box that satisfy that input's ReLU splits, and the
-    fewest surviving samples.  `fwd(x) -> (y [m, n_out], pre: name -> [m, ...])` in float64; splits_flat: name -> [B, n]."""
+def _anchored_splits(fwd, lo, up, unstable, dev, per_relu=3, seed=0):
+    """A split assignment per input that is satisfiable by construction: `per_relu` unstable neurons of every ReLU take the
+    sign their pre-activation has at an anchor point of the box.  unstable: name -> bool [B, n].  Returns (anchors, name ->
+    int8 [B, n])."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    B = lo.shape[0]
+    lo64, up64 = lo.to(dev, torch.float64), up.to(dev, torch.float64)
+    anchors = lo64 + torch.rand(lo64.shape, generator=g, device=dev, dtype=torch.float64) * (up64 - lo64)
+    _y, pre = fwd(anchors)
+    splits = {}
+    for x, mask in unstable.items():
+        s8 = torch.zeros(mask.shape, dtype=torch.int8, device=dev)
+        p = pre[x].reshape(B, -1)
+        for b in range(B):
+            idx = torch.nonzero(mask[b].to(dev)).flatten()
+            if len(idx) == 0:
+                continue
+            pick = idx[torch.randint(0, len(idx), (per_relu,), generator=g, device=dev)]
+            s8[b, pick] = torch.where(p[b, pick] >= 0, 1, -1).to(torch.int8)
+        splits[x] = s8
+    return anchors, splits
+
+
+def _split_soundness(name, fwd, lo, up, anchors, splits_flat, C, lower, upper, dev, n=N_SAMPLES, seed=0):
+    """Worst violation / tolerance over the samples that satisfy each input's ReLU splits (uniform points of the box and
+    perturbations of the anchor at several scales), and the fewest surviving samples per input.
+    `fwd(x) -> (y, pre: name -> tensor)` in float64; splits_flat: name -> int8 [B, n]."""
     g = torch.Generator(device=dev).manual_seed(seed)
     worst, fewest = 0.0, None
     B = lo.shape[0]
@@ -192,69 +216,74 @@ def _split_soundness(name, fwd, lo, up, splits_flat, C, lower, upper, dev, n=N_S
         Cb = C[b].to(dev, torch.float64)
         lb, ub = lower[b].to(dev, torch.float64), upper[b].to(dev, torch.float64)
         tol_l, tol_u = 1e-4 + 1e-5 * lb.abs(), 1e-4 + 1e-5 * ub.abs()
-        r = torch.rand((n,) + tuple(lo_b.shape), generator=g, device=dev, dtype=torch.float64)
-        y, pre = fwd(lo_b + r * (up_b - lo_b))
-        ok = torch.ones(n, dtype=torch.bool, device=dev)
-        for x, s in splits_flat.items():
-            sb = s[b].to(dev, torch.float64)
-            p = pre[x].reshape(n, -1)
-            ok &= ~(((sb > 0) & (p < 0)) | ((sb < 0) & (p > 0))).any(dim=1)
-        k = int(ok.sum())
-        fewest = k if fewest is None else min(fewest, k)
-        if k:
-            yy = y[ok].reshape(k, -1).matmul(Cb.t())
-            worst = max(worst, float(((lb - yy) / tol_l).max()), float(((yy - ub) / tol_u).max()))
+        survivors = 0
+        for scale in (None, 0.3, 0.1, 0.03, 0.01):
+            m = n // 5
+            r = torch.rand((m,) + tuple(lo_b.shape), generator=g, device=dev, dtype=torch.float64)
+            x = lo_b + r * (up_b - lo_b) if scale is None else torch.minimum(torch.maximum(anchors[b] + scale * (r - 0.5) * (up_b - lo_b), lo_b), up_b)
+            x[0] = anchors[b]
+            y, pre = fwd(x)
+            ok = torch.ones(m, dtype=torch.bool, device=dev)
+            for xn, s in splits_flat.items():
+                sb = s[b].to(dev, torch.float64)
+                p = pre[xn].reshape(m, -1)
+                ok &= ~(((sb > 0) & (p < 0)) | ((sb < 0) & (p > 0))).any(dim=1)
+            k = int(ok.sum())
+            survivors += k
+            if k:
+                yy = y[ok].reshape(k, -1).matmul(Cb.t())
+                worst = max(worst, float(((lb - yy) / tol_l).max()), float(((yy - ub) / tol_u).max()))
+        fewest = survivors if fewest is None else min(fewest, survivors)
     print(f"{name}: worst violation / tolerance = {worst:.3f}; fewest split-satisfying samples per input = {fewest} of {n}")
     return worst, fewest
 
 
-def test_conv_alpha_beta_with_splits_sound(dev, golden):
-    """alpha-beta-CROWN on the CNN c2 with the split assignment of tests/golden/conv_beta.npz (beta parameters on both
-    conv ReLUs and the Linear ReLU), 8 Adam steps."""
-    import numpy as np
-
+def test_conv_alpha_beta_with_splits_sound(dev):
+    """alpha-beta-CROWN on the CNN c2 (4 inputs) with three split neurons on each conv ReLU and on the Linear ReLU
+    (beta parameters on all three), 8 Adam steps."""
     from boundflow_b200 import workloads as W
-    from boundflow_b200.crown import run_alpha_beta_crown_mlp
+    from boundflow_b200.crown import ibp_trace, run_alpha_beta_crown_mlp
     from boundflow_b200.ir import InputSpec
 
-    g = golden("conv_beta.npz")
     wl = W.make_workload("c2", batch=4)
     shapes = {"h1": (16, 14, 14), "h2": (32, 7, 7), "h3": (100,)}
-    flat = {n: torch.from_numpy(np.asarray(g[f"split_{n}"])).to(torch.int8) for n in wl.relu_names}
-    splits = {n: flat[n].reshape((4,) + shapes[n]).to(dev) for n in wl.relu_names}
     spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
-    b, _a, _bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_split_state=splits, steps=8, lr=0.1, per_batch_params=True)
+    tr = ibp_trace(wl.module, spec)
+    unstable = {n: (tr.pre_l[r] < 0) & (tr.pre_u[r] > 0) for r, n in enumerate(wl.relu_names)}
     L = _layers64(wl.layers, dev)
 
     def fwd(x):
         y, pre = _forward(L, x, record_pre=True)
         return y, dict(zip(wl.relu_names, pre))
 
-    worst, fewest = _split_soundness("c2 alpha-beta with splits", fwd, wl.lo, wl.up, flat, wl.C, b.lower, b.upper, dev, seed=21)
-    assert fewest >= 100 and worst <= 1.0
+    anchors, flat = _anchored_splits(fwd, wl.lo, wl.up, unstable, dev, seed=20)
+    splits = {n: flat[n].reshape((4,) + shapes[n]) for n in wl.relu_names}
+    b, _a, bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_split_state=splits, steps=8, lr=0.1, per_batch_params=True)
+    assert any(float(v.abs().max()) > 0 for v in bt.beta_by_relu_input.values()), "beta never moved"
+    worst, fewest = _split_soundness("c2 alpha-beta with splits", fwd, wl.lo, wl.up, anchors, flat, wl.C, b.lower, b.upper, dev, seed=21)
+    assert fewest >= 1000 and worst <= 1.0
 
 
 @pytest.mark.parametrize("name", ["residual_s2", "mini_resnet", "concat_cnn", "fanout_mlp"])
-def test_graph_alpha_beta_with_splits_sound(dev, golden, name):
-    """alpha-beta-CROWN on graphs that are not chains, with the split assignment of tests/golden/graph_alpha.npz."""
-    import numpy as np
-
+def test_graph_alpha_beta_with_splits_sound(dev, name):
+    """alpha-beta-CROWN on graphs that are not chains, two split neurons per ReLU and input, 6 Adam steps."""
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import run_alpha_beta_crown_mlp
     from boundflow_b200.dag import forward_ibp_dag
     from boundflow_b200.ir import InputSpec
     from oracle import graph_oracle as GO
 
-    g = golden("graph_alpha.npz")
     module, _x, lo, up, C = W.make_graph_cases()[name]
     B = int(lo.shape[0])
     spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
     tr = forward_ibp_dag(module, spec)
-    flat = {x: torch.from_numpy(np.asarray(g[f"{name}_split_{x}"])).to(torch.int8) for x in tr.pre_l}
-    b, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=None if C is None else C.to(dev),
-                                             relu_split_state={x: s.to(dev) for x, s in flat.items()}, steps=6, lr=0.1, per_batch_params=True)
+    unstable = {x: (tr.pre_l[x] < 0) & (tr.pre_u[x] > 0) for x in tr.pre_l}
+    fwd = lambda x: GO.concrete_forward_graph(module, x, record_pre=True)  # noqa: E731
+    anchors, flat = _anchored_splits(fwd, lo, up, unstable, dev, per_relu=2, seed=30)
+    b, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=None if C is None else C.to(dev), relu_split_state=flat, steps=6, lr=0.1,
+                                             per_batch_params=True)
     n_out = int(b.lower.reshape(B, -1).shape[1])
     Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
-    fwd = lambda x: GO.concrete_forward_graph(module, x, record_pre=True)  # noqa: E731
-    worst, fewest = _split_soundness(f"{name} alpha-beta with splits", fwd, lo, up, flat, Cb, b.lower.reshape(B, -1), b.upper.reshape(B, -1), dev, seed=22)
-    assert fewest >= 100 and worst <= 1.0
+    worst, fewest = _split_soundness(f"{name} alpha-beta with splits", fwd, lo, up, anchors, flat, Cb, b.lower.reshape(B, -1), b.upper.reshape(B, -1),
+                                     dev, seed=31)
+    assert fewest >= 1000 and worst <= 1.0
