@@ -132,3 +132,66 @@ def test_building_blocks_against_torch(dev):
     xd = x.to(dev)
     _lib.check(lib.bf_accumulate(xd.data_ptr(), y.to(dev).data_ptr(), 1000, s))
     assert_close(xd, x + y, "accumulate")
+
+
+def test_graph_loop_building_blocks_against_torch(dev):
+    """bf_relu_split_apply, bf_rows_add_broadcast, bf_adjoint_start_box, bf_rows_conv2d_fwd, bf_relu_adjoint_rows and
+    bf_conv2d_dense_rows against plain torch expressions of their definitions."""
+    import torch.nn.functional as F
+
+    from boundflow_b200 import _lib
+
+    lib = _lib.load()
+    g = torch.Generator("cpu").manual_seed(23)
+    s = torch.cuda.current_stream(dev).cuda_stream
+    B, S, n = 3, 5, 70
+    # split on bounds, with one domain made infeasible on purpose (l > 0 there and the split says "inactive")
+    l = torch.randn(B, n, generator=g) - 0.3
+    u = l + torch.rand(B, n, generator=g) * 2
+    sp = torch.randint(-1, 2, (B, n), generator=g).to(torch.int8)
+    l[1, 7], u[1, 7], sp[1, 7] = 0.5, 0.9, -1
+    ld, ud, spd = l.to(dev).clone(), u.to(dev).clone(), sp.to(dev)
+    bad = torch.zeros(B, dtype=torch.int32, device=dev)
+    _lib.check(lib.bf_relu_split_apply(ld.data_ptr(), ud.data_ptr(), spd.data_ptr(), n, bad.data_ptr(), B, n, s))
+    want_l = torch.where(sp > 0, l.clamp(min=0), l)
+    want_u = torch.where(sp < 0, u.clamp(max=0), u)
+    assert torch.equal(ld.cpu(), want_l) and torch.equal(ud.cpu(), want_u)
+    assert bad.cpu().tolist() == (want_l > want_u).any(dim=1).int().tolist() and bad.cpu().tolist()[1] == 1
+    # broadcast add, per domain and shared
+    A = torch.randn(B, S, n, generator=g)
+    v = torch.randn(B, n, generator=g)
+    Ad, vd, v0d = A.to(dev).clone(), v.to(dev), v[0].to(dev).contiguous()   # device operands stay referenced until the calls have run
+    _lib.check(lib.bf_rows_add_broadcast(Ad.data_ptr(), vd.data_ptr(), n, B, S, n, s))
+    assert torch.equal(Ad.cpu(), A + v.unsqueeze(1))
+    Ad = A.to(dev).clone()
+    _lib.check(lib.bf_rows_add_broadcast(Ad.data_ptr(), v0d.data_ptr(), 0, B, S, n, s))
+    assert torch.equal(Ad.cpu(), A + v[0])
+    # adjoint start vector
+    mid, rad = torch.rand(B, n, generator=g), torch.rand(B, n, generator=g) * 0.1
+    A[0, 0, :5] = 0.0
+    Ad, midd, radd = A.to(dev).clone(), mid.to(dev), rad.to(dev)
+    _lib.check(lib.bf_adjoint_start_box(Ad.data_ptr(), midd.data_ptr(), radd.data_ptr(), B, S, n, s))
+    assert torch.equal(Ad.cpu(), mid.unsqueeze(1) - torch.sign(A) * rad.unsqueeze(1))
+    # forward convolution of rows
+    Ci, Hi, Co, k, st, pd = 3, 9, 4, 3, 2, 1
+    Ho = (Hi + 2 * pd - k) // st + 1
+    X = torch.randn(B * S, Ci, Hi, Hi, generator=g)
+    Wc, bc = torch.randn(Co, Ci, k, k, generator=g), torch.randn(Co, generator=g)
+    out = torch.empty(B * S, Co, Ho, Ho, device=dev)
+    Xd, Wd, bd = X.to(dev), Wc.to(dev), bc.to(dev)
+    _lib.check(lib.bf_rows_conv2d_fwd(Xd.data_ptr(), Wd.data_ptr(), bd.data_ptr(), out.data_ptr(), B * S, Ci, Hi, Hi, Co, Ho, Ho,
+                                      k, k, st, st, pd, pd, s))
+    assert_close(out, F.conv2d(X, Wc, bc, st, pd), "rows conv2d forward", atol=1e-5)
+    # ReLU adjoint step with both gradient sums
+    G, Ah = torch.randn(B, S, n, generator=g), torch.randn(B, S, n, generator=g)
+    au, al, bu = torch.rand(B, n, generator=g), torch.rand(B, n, generator=g), torch.rand(B, n, generator=g)
+    grad0, gsum0 = torch.randn(B, n, generator=g), torch.randn(B, n, generator=g)
+    Gd, gr, gs = G.to(dev).clone(), grad0.to(dev).clone(), gsum0.to(dev).clone()
+    Ahd, aud, ald, bud, l2d, u2d = (x.to(dev).contiguous() for x in (Ah, au, al, bu, l, u))
+    _lib.check(lib.bf_relu_adjoint_rows(Gd.data_ptr(), Ahd.data_ptr(), aud.data_ptr(), ald.data_ptr(), bud.data_ptr(), l2d.data_ptr(),
+                                        u2d.data_ptr(), gr.data_ptr(), gs.data_ptr(), B, S, n, s))
+    sel = Ah >= 0
+    amb = ((l < 0) & (u > 0)).unsqueeze(1)
+    assert_close(Gd, torch.where(sel, al.unsqueeze(1) * G, au.unsqueeze(1) * G + bu.unsqueeze(1)), "relu adjoint output", atol=1e-6)
+    assert_close(gr, grad0 + (torch.where(sel & amb, Ah * G, torch.zeros_like(G))).sum(dim=1), "alpha gradient sums", atol=1e-5)
+    assert_close(gs, gsum0 + G.sum(dim=1), "beta gradient sums", atol=1e-5)
