@@ -409,20 +409,24 @@ def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Ten
 
 
 class _TransposedWeights:
-    """W^T copies for the forward Linear step of the gradient sweep, per weight tensor (same lifetime rule as the
-    packed-weight cache: keyed by storage pointer, shape and version)."""
+    """W^T copies for the forward Linear step of the gradient sweep, one per weight tensor.  Like the packed-weight
+    cache, an entry is keyed by storage address, shape, device and in-place version counter and keeps the weight tensor
+    itself alive, so an address cannot be reused by another tensor while its transpose is cached; least recently used
+    entries are dropped beyond `capacity`."""
 
-    def __init__(self):
-        self._cache: Dict[Tuple[int, Tuple[int, ...], int], torch.Tensor] = {}
+    def __init__(self, capacity: int = 32):
+        self.capacity = int(capacity)
+        self._entries: Dict[Tuple[int, Tuple[int, ...], Optional[int], int], Tuple[torch.Tensor, torch.Tensor]] = {}
 
     def get(self, W: torch.Tensor) -> torch.Tensor:
-        key = (W.data_ptr(), tuple(W.shape), int(W._version))
-        t = self._cache.get(key)
-        if t is None:
-            if len(self._cache) > 256:
-                self._cache.clear()
-            t = self._cache[key] = W.t().contiguous()
-        return t
+        key = (W.data_ptr(), tuple(W.shape), W.device.index, int(W._version))
+        hit = self._entries.pop(key, None)
+        if hit is None:
+            hit = (W, W.t().contiguous())
+            while len(self._entries) >= self.capacity:
+                self._entries.pop(next(iter(self._entries)))
+        self._entries[key] = hit  # most recently used last
+        return hit[1]
 
 
 _TRANSPOSED = _TransposedWeights()
