@@ -234,6 +234,7 @@ void refresh_switches(const bf_chain* c) {
   c->sw.adjoint_kernel = env_is_one("BF_B200_ADJ_ROWMAJOR") ? 1 : (env_is_one("BF_B200_ADJ_FEATURE_MAJOR") ? 2 : 0);
   c->sw.no_windows = getenv("BF_B200_NO_WINDOWS") != nullptr;
   c->sw.persistent_bwd = env_is_one("BF_B200_BWD_PERSISTENT");
+  c->sw.pair_bwd = env_is_one("BF_B200_BWD_PAIRS");
   const char* rows = getenv("BF_B200_TC_MIN_ROWS");
   c->sw.tc_min_rows = (rows && atoi(rows) > 0) ? atoi(rows) : 256;
   c->sw.tc_auto = !(rows && atoi(rows) > 0);
@@ -272,7 +273,7 @@ int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos
   if (pk) {
     if (ptiles) *ptiles = crown_tc_partial_tiles(N, K);
     return launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, add, pk, L.bias, A_prev, delta, accumulate, mid, rad, partial,
-                                      side, M, S, K, N, c->status, stream);
+                                      side, M, S, K, N, c->status, stream, c->sw.pair_bwd);
   }
   if (ptiles) *ptiles = crown_bwd_partial_tiles(N, M);
   return launch_crown_bwd_linear(A, dpos, dneg, epos, eneg, add, L.W, L.bias, A_prev, delta, accumulate, mid, rad, partial, side,

@@ -25,6 +25,7 @@ struct bf_chain {
     bool no_windows = false;        // BF_B200_NO_WINDOWS set: identity-row sweeps keep full feature maps
     bool persistent_bwd = false;    // BF_B200_BWD_PERSISTENT=1: persistent warp-specialised backward kernel (128 x 256 tiles, double-buffered
                                     // accumulators) instead of the one-tile-per-CTA kernel; measured slower on wide layers, see crown_tc_persist.cu
+    bool pair_bwd = false;          // BF_B200_BWD_PAIRS=1: backward contraction as CTA pairs (tcgen05 cta_group::2); measured slower, A/B switch
     int tc_min_rows = 256;          // coefficient rows from which Linear layers run on the tensor-core kernels (BF_B200_TC_MIN_ROWS)
     bool tc_auto = true;            // BF_B200_TC_MIN_ROWS unset: in addition, a layer whose 64 x 64 FFMA tiles fit one wave (two CTAs per
                                     // SM) stays on the FFMA kernels, which are faster there and follow the reference's fp32 rounding

@@ -393,9 +393,10 @@ extern "C" int bf_crown_relu_linear_bwd_packed(const float* A, int side, const f
   int* status = reinterpret_cast<int*>(const_cast<void*>(pack));
   const unsigned char* images = static_cast<const unsigned char*>(pack) + kPackHeader;
   const char* persistent = getenv("BF_B200_BWD_PERSISTENT");
+  const char* pairs_env = getenv("BF_B200_BWD_PAIRS");
   int rc = (!(persistent && persistent[0] == '1') || !bf::crown_tc_persistent_supports(epos, eneg, relu ? add : nullptr))
                ? bf::launch_crown_bwd_linear_tc(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta, accumulate,
-                                                nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status, stream)
+                                                nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status, stream, pairs_env && pairs_env[0] == '1')
                : bf::launch_crown_bwd_linear_tc_persistent(A, dpos, dneg, epos, eneg, relu ? add : nullptr, images, bias, A_prev, delta,
                                                            accumulate, nullptr, nullptr, nullptr, side, (int)M, S, n_cur, n_prev, status,
                                                            stream);

@@ -706,7 +706,7 @@ static int tc_launch(tc::Params& p, int ntiles, cudaStream_t stream, const char*
 int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                                const float* add, const unsigned char* Wpk, const float* kbias, float* A_prev, float* delta,
                                int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S, int K,
-                               int N, int* status, cudaStream_t stream) {
+                               int N, int* status, cudaStream_t stream, bool cta_pairs) {
   tc::Params p{};
   int nt;
   tc_tile_shape(N, K, &p.BN, &nt, &p.nkb);
@@ -723,9 +723,8 @@ int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* d
   p.conc_sign = (side == BF_SIDE_LOWER) ? -1.f : 1.f;
   p.status = status;
   timing_begin(T_BWD, stream);
-  // BF_B200_BWD_PAIRS=1: run the row blocks as CTA pairs (tcgen05 cta_group::2)
-  const char* pairs_env = getenv("BF_B200_BWD_PAIRS");
-  const bool pairs = pairs_env && pairs_env[0] == '1' && M > tc::BM;
+  // cta_pairs (BF_B200_BWD_PAIRS=1, read by the callers once per call): the row blocks run as CTA pairs (tcgen05 cta_group::2)
+  const bool pairs = cta_pairs && M > tc::BM;
   int rc = pairs ? tc_launch<tc::MODE_BWD, tc::PRO_RELU, true>(p, nt, stream, "crown_tc_kernel<bwd,pair>")
                  : tc_launch<tc::MODE_BWD, tc::PRO_RELU>(p, nt, stream, "crown_tc_kernel<bwd>");
   timing_end(T_BWD, stream, 4.0 * (double)M * K + (A_prev ? 4.0 * (double)M * N : 0.0), 2.0 * (double)M * K * N);

@@ -23,7 +23,7 @@ int tc_pack_weights(const float* W, int rows, int cols, int transposed, unsigned
 int launch_crown_bwd_linear_tc(const float* A, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                                const float* add, const unsigned char* Wpk, const float* kbias, float* A_prev, float* delta,
                                int accumulate, const float* mid, const float* rad, float* partial, int side, int M, int S, int K,
-                               int N, int* status, cudaStream_t stream);
+                               int N, int* status, cudaStream_t stream, bool cta_pairs = false);
 int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const float* mid, const float* rad,
                                    const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
                                    const float* dneg, const float* epos, const float* eneg, const float* pre_l,
