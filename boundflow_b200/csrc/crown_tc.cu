@@ -158,6 +158,12 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     const int rg = tid >> 3;      // row pair of this thread
     const int row0 = m0 + rg * ROWS_PER_THREAD;
     const bool vK = p.vecK != 0;
+    // every k-block is complete and 16-byte aligned (the usual case): loads need no bounds logic
+    const bool fastK = vK && (p.K % BK == 0);
+    auto ldk = [&](const float* row, int k) -> float4 {
+      if (fastK) return __ldg(reinterpret_cast<const float4*>(row + k));
+      return (k < p.K) ? load4_guard(row, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
     const bool want_delta = (PRO == PRO_RELU) && p.delta != nullptr && blockIdx.y == 0;
     int dom[ROWS_PER_THREAD];
 #pragma unroll
@@ -172,11 +178,10 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
     float4 a_next[ROWS_PER_THREAD];
     auto load_block = [&](int kb) {
       const int k = kb * BK + c * 4;
-      const bool ok = k < p.K;
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         const int m = row0 + i;
-        a_next[i] = (m < p.M && ok) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
+        a_next[i] = (m < p.M) ? ldk(p.A + (size_t)m * p.K, k) : make_float4(0.f, 0.f, 0.f, 0.f);
         if (c == 0 && m < p.M && (kb + PREFETCH_KB) * BK < p.K)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(p.A + (size_t)m * p.K + (size_t)(kb + PREFETCH_KB) * BK));
       }
@@ -204,24 +209,24 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
       float4 kbv = z4;
       float4 sv[ROWS_PER_THREAD][5];  // dpos, dneg, epos|mid, eneg|rad, add of each row's domain
       if (PRO == PRO_RELU) {
-        if (want_delta && p.kbias && ok) kbv = load4_guard(p.kbias, k, p.K, vK);
+        if (want_delta && p.kbias) kbv = ldk(p.kbias, k);
         if (p.dpos) {
 #pragma unroll
           for (int i = 0; i < ROWS_PER_THREAD; ++i) {
             const size_t off = (size_t)dom[i] * p.K;
-            sv[i][0] = ok ? load4_guard(p.dpos + off, k, p.K, vK) : z4;
-            sv[i][1] = ok ? load4_guard(p.dneg + off, k, p.K, vK) : z4;
-            sv[i][2] = (ok && want_delta && p.epos) ? load4_guard(p.epos + off, k, p.K, vK) : z4;
-            sv[i][3] = (ok && want_delta && p.eneg) ? load4_guard(p.eneg + off, k, p.K, vK) : z4;
-            sv[i][4] = (ok && p.add) ? load4_guard(p.add + off, k, p.K, vK) : z4;
+            sv[i][0] = ldk(p.dpos + off, k);
+            sv[i][1] = ldk(p.dneg + off, k);
+            sv[i][2] = (want_delta && p.epos) ? ldk(p.epos + off, k) : z4;
+            sv[i][3] = (want_delta && p.eneg) ? ldk(p.eneg + off, k) : z4;
+            sv[i][4] = p.add ? ldk(p.add + off, k) : z4;
           }
         }
       } else if (PRO == PRO_H0) {
 #pragma unroll
         for (int i = 0; i < ROWS_PER_THREAD; ++i) {
           const size_t off = (size_t)dom[i] * p.K;
-          sv[i][2] = ok ? load4_guard(p.mid_k + off, k, p.K, vK) : z4;
-          sv[i][3] = ok ? load4_guard(p.rad_k + off, k, p.K, vK) : z4;
+          sv[i][2] = ldk(p.mid_k + off, k);
+          sv[i][3] = ldk(p.rad_k + off, k);
         }
       }
 

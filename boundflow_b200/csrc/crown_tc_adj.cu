@@ -293,6 +293,12 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
     const int rg = tid >> 3;      // row group of this thread
     const int row0 = m0 + rg * ROWS_PER_THREAD;
     const bool vK = p.vecK != 0;
+    // every k-block is complete and 16-byte aligned (the usual case): loads need no bounds logic
+    const bool fastK = vK && (p.K % BK == 0);
+    auto ldk = [&](const float* row, int k) -> float4 {
+      if (fastK) return __ldg(reinterpret_cast<const float4*>(row + k));
+      return (k < p.K) ? load4_guard(row, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
     int dom[ROWS_PER_THREAD];
 #pragma unroll
     for (int i = 0; i < ROWS_PER_THREAD; ++i) dom[i] = (row0 + i < p.M) ? ((row0 + i) / p.S) : 0;
@@ -300,11 +306,10 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
     float4 a_next[ROWS_PER_THREAD];
     auto load_block = [&](int kb) {
       const int k = kb * BK + c * 4;
-      const bool ok = k < p.K;
 #pragma unroll
       for (int i = 0; i < ROWS_PER_THREAD; ++i) {
         const int m = row0 + i;
-        a_next[i] = (m < p.M && ok) ? load4_guard(p.A + (size_t)m * p.K, k, p.K, vK) : make_float4(0.f, 0.f, 0.f, 0.f);
+        a_next[i] = (m < p.M) ? ldk(p.A + (size_t)m * p.K, k) : make_float4(0.f, 0.f, 0.f, 0.f);
         if (c == 0 && m < p.M && (kb + PREFETCH_KB) * BK < p.K)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(p.A + (size_t)m * p.K + (size_t)(kb + PREFETCH_KB) * BK));
       }
@@ -333,8 +338,8 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_adjoint_kernel(Params p) 
         for (int i = 0; i < ROWS_PER_THREAD; ++i) {
           if (row0 + i < p.M && ok) {
             const size_t off = (size_t)dom[i] * p.K;
-            const float4 md = load4_guard(p.mid_k + off, k, p.K, vK);
-            const float4 rd = load4_guard(p.rad_k + off, k, p.K, vK);
+            const float4 md = ldk(p.mid_k + off, k);
+            const float4 rd = ldk(p.rad_k + off, k);
             // lanes of this float4 beyond K stay 0: a, mid and rad were all loaded guarded
             float4 a = a_cur[i];
             a.x = md.x - sgnf(a.x) * rd.x; a.y = md.y - sgnf(a.y) * rd.y;
