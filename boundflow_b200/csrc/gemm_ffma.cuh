@@ -78,27 +78,21 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   }
 
   float4 areg[2], breg[2];
+  // Small tiles (MH == 1) run with one CTA of 8 warps on an SM, so nothing hides a load's latency: there the slab that is
+  // loaded while the current one is multiplied stays RAW in registers (coefficients and the slope / intercept vectors of
+  // the row's domain) and the prologue is applied right before the slab goes to shared memory, after the multiply loop.
+  // The large tiles (several CTAs per SM, 128 registers in use) apply the prologue at load time as before.
+  constexpr bool DEFER = (MH == 1);
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 kbr = z4, dpr[MH], dnr[MH], epr[MH], enr[MH], adr[MH];  // PRO_H0 keeps mid / rad in dpr / dnr
+  bool live[MH];
 
-  auto load_slab = [&](int kt) {
-    const int k = kt * BK + lkc;
-#pragma unroll
-    for (int i = 0; i < MH; ++i) {
-      const int m = m0 + lrow + i * 64;
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (m < g.M && k < g.K) {
-        a = load4_guard(g.A + (size_t)m * g.K, k, g.K, vK);
-        if (PRO == PRO_RELU) {
-          float4 kb = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (g.kbias) kb = load4_guard(g.kbias, k, g.K, vK);
-          if (g.dpos) {
-            const size_t off = (size_t)dom[i] * g.K;
-            const float4 dp = load4_guard(g.dpos + off, k, g.K, vK);
-            const float4 dn = load4_guard(g.dneg + off, k, g.K, vK);
-            float4 ep = make_float4(0.f, 0.f, 0.f, 0.f), en = ep, ad = ep;
-            if (g.epos) ep = load4_guard(g.epos + off, k, g.K, vK);
-            if (g.eneg) en = load4_guard(g.eneg + off, k, g.K, vK);
-            if (g.add) ad = load4_guard(g.add + off, k, g.K, vK);
-            float r = rowacc[i];
+  // the per-element prologue of row slot i; same operations in the same order wherever it runs
+  auto prologue = [&](int i, float4 a, const float4& kb, const float4& dp, const float4& dn, const float4& ep, const float4& en,
+                      const float4& ad) -> float4 {
+    if (PRO == PRO_RELU) {
+      if (g.dpos) {
+        float r = rowacc[i];
 #define BF_RELU_SEL(c)                                   \
   {                                                      \
     const bool sel = a.c >= 0.f;                         \
@@ -107,23 +101,50 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     r = fmaf(lam, kb.c, r);                              \
     a.c = lam;                                           \
   }
-            BF_RELU_SEL(x) BF_RELU_SEL(y) BF_RELU_SEL(z) BF_RELU_SEL(w)
+        BF_RELU_SEL(x) BF_RELU_SEL(y) BF_RELU_SEL(z) BF_RELU_SEL(w)
 #undef BF_RELU_SEL
-            rowacc[i] = r;
-          } else {
-            rowacc[i] += a.x * kb.x + a.y * kb.y + a.z * kb.z + a.w * kb.w;
+        rowacc[i] = r;
+      } else {
+        rowacc[i] += a.x * kb.x + a.y * kb.y + a.z * kb.z + a.w * kb.w;
+      }
+    } else if (PRO == PRO_H0) {
+      a.x = dp.x - sgnf(a.x) * dn.x;
+      a.y = dp.y - sgnf(a.y) * dn.y;
+      a.z = dp.z - sgnf(a.z) * dn.z;
+      a.w = dp.w - sgnf(a.w) * dn.w;
+    }
+    return a;
+  };
+
+  auto load_slab = [&](int kt) {
+    const int k = kt * BK + lkc;
+#pragma unroll
+    for (int i = 0; i < MH; ++i) {
+      const int m = m0 + lrow + i * 64;
+      const bool ok = m < g.M && k < g.K;
+      float4 a = z4, kb = z4, dp = z4, dn = z4, ep = z4, en = z4, ad = z4;
+      if (ok) {
+        a = load4_guard(g.A + (size_t)m * g.K, k, g.K, vK);
+        const size_t off = (size_t)dom[i] * g.K;
+        if (PRO == PRO_RELU) {
+          if (g.kbias) kb = load4_guard(g.kbias, k, g.K, vK);
+          if (g.dpos) {
+            dp = load4_guard(g.dpos + off, k, g.K, vK);
+            dn = load4_guard(g.dneg + off, k, g.K, vK);
+            if (g.epos) ep = load4_guard(g.epos + off, k, g.K, vK);
+            if (g.eneg) en = load4_guard(g.eneg + off, k, g.K, vK);
+            if (g.add) ad = load4_guard(g.add + off, k, g.K, vK);
           }
         } else if (PRO == PRO_H0) {
-          const size_t off = (size_t)dom[i] * g.K;
-          const float4 md = load4_guard(g.mid + off, k, g.K, vK);
-          const float4 rd = load4_guard(g.rad + off, k, g.K, vK);
-          a.x = md.x - sgnf(a.x) * rd.x;
-          a.y = md.y - sgnf(a.y) * rd.y;
-          a.z = md.z - sgnf(a.z) * rd.z;
-          a.w = md.w - sgnf(a.w) * rd.w;
+          dp = load4_guard(g.mid + off, k, g.K, vK);
+          dn = load4_guard(g.rad + off, k, g.K, vK);
         }
       }
-      areg[i] = a;
+      if (DEFER) {
+        areg[i] = a; kbr = kb; dpr[i] = dp; dnr[i] = dn; epr[i] = ep; enr[i] = en; adr[i] = ad; live[i] = ok;
+      } else {
+        areg[i] = ok ? prologue(i, a, kb, dp, dn, ep, en, ad) : a;
+      }
     }
     if (B_NT) {
 #pragma unroll
@@ -142,6 +163,15 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
         if (kk < g.K && n < g.N && bnc < 64 * NH) b = load4_guard(g.Bm + (size_t)kk * g.N, n, g.N, vN);
         breg[i] = b;
       }
+    }
+  };
+
+  // applies the deferred prologue to the slab held in registers (small tiles)
+  auto finish_slab = [&]() {
+    if (DEFER) {
+#pragma unroll
+      for (int i = 0; i < MH; ++i)
+        if (live[i]) areg[i] = prologue(i, areg[i], kbr, dpr[i], dnr[i], epr[i], enr[i], adr[i]);
     }
   };
 
@@ -173,6 +203,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
 
   const int nk = (g.K + BK - 1) / BK;
   load_slab(0);
+  finish_slab();
   store_slab(0);
   __syncthreads();
   for (int kt = 0; kt < nk; ++kt) {
@@ -194,7 +225,10 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
 #pragma unroll
         for (int j = 0; j < 4 * NH; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
-    if (kt + 1 < nk) store_slab(stage ^ 1);
+    if (kt + 1 < nk) {
+      finish_slab();
+      store_slab(stage ^ 1);
+    }
     __syncthreads();
   }
 
