@@ -110,3 +110,33 @@ def test_shared_alpha_objectives_match_reference_golden(dev, golden, cfg, batch)
                                              spec_reduce="min", soft_tau=float(g[f"{cfg}_tau"]))
     assert_close(b.lower, g[f"{cfg}_gap_min_lower_6"], f"{cfg} alpha-beta function, shared gap/min lower")
     assert_close(b.upper, g[f"{cfg}_gap_min_upper_6"], f"{cfg} alpha-beta function, shared gap/min upper")
+
+
+def test_single_spec_row_and_single_input_against_oracle(dev):
+    """Edge shapes of the objective kernels: one input with one spec row (every reduction degenerates to the row itself)
+    and one input with nine rows, per-domain and shared parameters, against the oracle."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace, shared_alpha_crown_from_trace
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    wl = W.make_workload("c1", batch=1)
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    trace = ibp_trace(wl.module, spec)
+    a0 = adaptive_alpha_from_trace(trace)
+    inp = O.box_input(wl.lo, wl.up)
+    tr = O.forward_ibp_trace(wl.layers, inp)
+    for C in (wl.C[:, :1], wl.C):
+        for obj, red in (("both", "min"), ("gap", "softmin"), ("upper", "min"), ("lower", "softmin")):
+            got = alpha_crown_from_trace(trace, C.to(dev), a0, steps=3, lr=0.1, objective=obj, spec_reduce=red, soft_tau=0.7, lb_weight=1.0, ub_weight=2.0)
+            ref_l, ref_u, _a, _t = O.alpha_crown(wl.layers, inp, C, steps=3, lr=0.1, alpha0=[a.cpu() for a in a0], trace=tr, objective=obj,
+                                                 spec_reduce=red, soft_tau=0.7, lb_weight=1.0, ub_weight=2.0)
+            assert_close(got[0], ref_l, f"per-domain {obj}/{red} lower, S={C.shape[1]}")
+            assert_close(got[1], ref_u, f"per-domain {obj}/{red} upper, S={C.shape[1]}")
+            a_sh = [torch.full((n,), 0.5, device=dev) for n in trace.chain.relu_widths]
+            got = shared_alpha_crown_from_trace(trace, C.to(dev), a_sh, steps=3, lr=0.1, objective=obj, spec_reduce=red, soft_tau=0.7, lb_weight=1.0,
+                                                ub_weight=2.0)
+            ref_l, ref_u, _a, _t = O.alpha_crown_shared(wl.layers, inp, C, steps=3, lr=0.1, trace=tr, objective=obj, spec_reduce=red, soft_tau=0.7,
+                                                        lb_weight=1.0, ub_weight=2.0)
+            assert_close(got[0], ref_l, f"shared {obj}/{red} lower, S={C.shape[1]}")
+            assert_close(got[1], ref_u, f"shared {obj}/{red} upper, S={C.shape[1]}")
