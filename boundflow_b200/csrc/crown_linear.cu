@@ -22,7 +22,8 @@ struct BwdEpilogue {
 template <int PRO, int MH, int NH>
 __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_bwd_linear_kernel(GemmArgs g, BwdEpilogue e) {
   __shared__ __align__(16) float smem[MAINLOOP_SMEM_FLOATS];
-  const int m0 = blockIdx.x * (64 * MH), n0 = blockIdx.y * (64 * NH);
+  constexpr int TM = (MH == 0) ? 32 : 64 * MH, MR = (MH == 0) ? 2 : 4 * MH;
+  const int m0 = blockIdx.x * TM, n0 = blockIdx.y * (64 * NH);
   float acc[8][8];
   gemm_mainloop<PRO, false, MH, NH>(g, m0, n0, acc, smem);
 
@@ -30,8 +31,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_bwd_linear_kernel(GemmA
   const bool vN = g.vecN != 0;
   const float sgn = (e.side == BF_SIDE_LOWER) ? -1.f : 1.f;
 #pragma unroll
-  for (int i = 0; i < 4 * MH; ++i) {
-    const int row = m0 + tile_row(ty, i);
+  for (int i = 0; i < MR; ++i) {
+    const int row = m0 + tile_row<MH>(ty, i);
     const bool row_ok = row < g.M;
     float p = 0.f;
 #pragma unroll
@@ -105,6 +106,8 @@ __global__ void __launch_bounds__(128) crown_bwd_thin_kernel(const float* __rest
 
 // 128 x 128 tiles leave most of the 148 SMs idle on small problems: below one CTA per SM the kernels switch to 64 x 64 tiles
 bool ffma_small_tiles(int M, int N) { return (long long)ceil_div(M, BM) * ceil_div(N, BN) < 148; }
+// ... and 32 x 64 tiles when even the 64 x 64 tiles give fewer CTAs than SMs
+static bool ffma_quarter_tiles(int M, int N) { return ffma_small_tiles(M, N) && M > 32 && (long long)ceil_div(M, 64) * ceil_div(N, 64) < 148; }
 
 // Measured on B200 (c3: 1152 x 256 x 256 layers, 20 Adam steps): 8.9 ms on these tiles against 9.7 ms on the tcgen05
 // kernels, whose per-launch time of 23-36 us is a serial k-loop on 9-36 CTAs; at 144 rows 6.3 against 7.3 ms.  Beyond one
@@ -136,7 +139,10 @@ int launch_crown_bwd_linear(const float* A, const float* dpos, const float* dneg
   g.delta = delta; g.accumulate = accumulate;
   BwdEpilogue e{A_prev, mid, rad, partial, side};
   timing_begin(T_BWD, stream);
-  if (ffma_small_tiles(M, N)) {  // 64 x 64 tiles: four times as many CTAs
+  if (ffma_quarter_tiles(M, N)) {  // 32 x 64 tiles
+    dim3 grid(ceil_div(M, 32), ceil_div(N, 64));
+    crown_bwd_linear_kernel<PRO_RELU, 0, 1><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
+  } else if (ffma_small_tiles(M, N)) {  // 64 x 64 tiles: four times as many CTAs
     dim3 grid(ceil_div(M, 64), ceil_div(N, 64));
     crown_bwd_linear_kernel<PRO_RELU, 1, 1><<<grid, GEMM_THREADS, 0, stream>>>(g, e);
   } else {
@@ -165,7 +171,7 @@ struct AdjEpilogue {
   const float* pre_l;  // [D,N]
   const float* pre_u;  // [D,N]
   float* hout;         // [M,N] or nullptr (last ReLU layer needs no adjoint point)
-  float* grad;         // [D,N], accumulated with atomicAdd (at most two row tiles touch one entry when S <= the tile height, 64 or 128)
+  float* grad;         // [D,N], accumulated with atomicAdd (at most two row tiles touch one entry when S <= the tile height: 32, 64 or 128)
   float* gsum;         // [D,N] or nullptr: sum over the domain's rows of g (beta gradient), same accumulation
 };
 
@@ -176,7 +182,7 @@ static_assert(ADJ_SMEM_BYTES >= MAINLOOP_SMEM_FLOATS * (int)sizeof(float), "stag
 template <int PRO, int MH, int NH>
 __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(GemmArgs g, AdjEpilogue e) {
   extern __shared__ __align__(16) float dsmem[];
-  constexpr int TM = 64 * MH, TN = 64 * NH;
+  constexpr int TM = (MH == 0) ? 32 : 64 * MH, TN = 64 * NH, MR = (MH == 0) ? 2 : 4 * MH;
   const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
   float acc[8][8];
   gemm_mainloop<PRO, true, MH, NH>(g, m0, n0, acc, dsmem);
@@ -185,8 +191,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const bool vN = g.vecN != 0;
 #pragma unroll
-  for (int i = 0; i < 4 * MH; ++i) {
-    const int rl = tile_row(ty, i);
+  for (int i = 0; i < MR; ++i) {
+    const int rl = tile_row<MH>(ty, i);
     const int row = m0 + rl;
 #pragma unroll
     for (int jb = 0; jb < NH; ++jb) {
@@ -244,8 +250,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
   if (e.gsum != nullptr) {
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < 4 * MH; ++i) {
-      const int rl = tile_row(ty, i);
+    for (int i = 0; i < MR; ++i) {
+      const int rl = tile_row<MH>(ty, i);
       const int row = m0 + rl;
 #pragma unroll
       for (int jb = 0; jb < NH; ++jb) {
@@ -274,7 +280,7 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
                                 float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream) {
-  static SmemOptIn opt_in[4];
+  static SmemOptIn opt_in[6];
   GemmArgs g{};
   g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
   const void* kptrs[] = {Hprev, W, mid, rad};
@@ -285,20 +291,21 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   g.mid = mid; g.rad = rad;
   AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum};
-  const bool small = ffma_small_tiles(M, N);
-  dim3 grid(ceil_div(M, small ? 64 : BM), ceil_div(N, small ? 64 : BN));
+  // 32-row tiles only while a domain's S rows still touch at most two row tiles (two atomic addends commute: deterministic sums)
+  const bool small = ffma_small_tiles(M, N), quarter = ffma_quarter_tiles(M, N) && S <= 32;
+  dim3 grid(ceil_div(M, quarter ? 32 : (small ? 64 : BM)), ceil_div(N, small ? 64 : BN));
   timing_begin(T_ADJ, stream);
-#define BF_ADJ_LAUNCH(PRO_, MH_, slot)                                                                                          \
+#define BF_ADJ_LAUNCH(PRO_, MH_, NH_, slot)                                                                                     \
   {                                                                                                                             \
-    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_, MH_, MH_>, ADJ_SMEM_BYTES, opt_in[slot],                 \
+    if (int rc = ensure_dynamic_smem(crown_adjoint_linear_kernel<PRO_, MH_, NH_>, ADJ_SMEM_BYTES, opt_in[slot],                 \
                                      "crown_adjoint_linear_kernel"))                                                            \
       return rc;                                                                                                                \
-    crown_adjoint_linear_kernel<PRO_, MH_, MH_><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);                          \
+    crown_adjoint_linear_kernel<PRO_, MH_, NH_><<<grid, GEMM_THREADS, ADJ_SMEM_BYTES, stream>>>(g, e);                          \
   }
   if (first_layer) {
-    if (small) BF_ADJ_LAUNCH(PRO_H0, 1, 0) else BF_ADJ_LAUNCH(PRO_H0, 2, 1)
+    if (quarter) BF_ADJ_LAUNCH(PRO_H0, 0, 1, 4) else if (small) BF_ADJ_LAUNCH(PRO_H0, 1, 1, 0) else BF_ADJ_LAUNCH(PRO_H0, 2, 2, 1)
   } else {
-    if (small) BF_ADJ_LAUNCH(PRO_PLAIN, 1, 2) else BF_ADJ_LAUNCH(PRO_PLAIN, 2, 3)
+    if (quarter) BF_ADJ_LAUNCH(PRO_PLAIN, 0, 1, 5) else if (small) BF_ADJ_LAUNCH(PRO_PLAIN, 1, 1, 2) else BF_ADJ_LAUNCH(PRO_PLAIN, 2, 2, 3)
   }
 #undef BF_ADJ_LAUNCH
   timing_end(T_ADJ, stream, 4.0 * (double)M * K + 8.0 * (double)M * N, 2.0 * (double)M * K * N);

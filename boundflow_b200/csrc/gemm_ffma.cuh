@@ -6,7 +6,8 @@
 // MH / NH (1 or 2) give the number of 64-row / 64-column halves a CTA computes: 64x64,
 // 64x128 or 128x64 tiles (4x4 ... 4x8 micro-tiles, same thread mapping, the unused half
 // simply absent) put four times as many CTAs on problems whose 128x128 tiles would leave
-// most SMs idle.  `f` is the
+// most SMs idle; MH == 0 stands for 32 rows (2x4 micro-tiles, 32x64 tiles) for problems that
+// still do not give every SM a CTA.  `f` is the
 // per-element prologue applied while the A slab moves global -> shared:
 //   PRO_PLAIN : identity                    (top linear layer, adjoint hidden layers)
 //   PRO_RELU  : ReLU backward transformer   (sign-select slope, intercept and bias row sums)
@@ -69,10 +70,13 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
+  constexpr int LROWS = (MH == 0) ? 1 : MH;   // tile rows a loader thread owns (rows lrow, lrow + 64)
+  constexpr int MR = (MH == 0) ? 2 : 4 * MH;  // micro-tile rows of a thread
+  const bool a_loader = (MH != 0) || lrow < 32;  // 32-row tiles: half of the threads load coefficient rows
   float rowacc[2] = {0.f, 0.f};
   int dom[2] = {0, 0};
 #pragma unroll
-  for (int i = 0; i < MH; ++i) {
+  for (int i = 0; i < LROWS; ++i) {
     int m = m0 + lrow + i * 64;
     dom[i] = (m < g.M) ? (m / g.S) : 0;
   }
@@ -82,10 +86,10 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   // loaded while the current one is multiplied stays RAW in registers (coefficients and the slope / intercept vectors of
   // the row's domain) and the prologue is applied right before the slab goes to shared memory, after the multiply loop.
   // The large tiles (several CTAs per SM, 128 registers in use) apply the prologue at load time as before.
-  constexpr bool DEFER = (MH == 1);
+  constexpr bool DEFER = (MH <= 1);
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 kbr = z4, dpr[MH], dnr[MH], epr[MH], enr[MH], adr[MH];  // PRO_H0 keeps mid / rad in dpr / dnr
-  bool live[MH];
+  float4 kbr = z4, dpr[LROWS], dnr[LROWS], epr[LROWS], enr[LROWS], adr[LROWS];  // PRO_H0 keeps mid / rad in dpr / dnr
+  bool live[LROWS];
 
   // the per-element prologue of row slot i; same operations in the same order wherever it runs
   auto prologue = [&](int i, float4 a, const float4& kb, const float4& dp, const float4& dn, const float4& ep, const float4& en,
@@ -119,9 +123,9 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   auto load_slab = [&](int kt) {
     const int k = kt * BK + lkc;
 #pragma unroll
-    for (int i = 0; i < MH; ++i) {
+    for (int i = 0; i < LROWS; ++i) {
       const int m = m0 + lrow + i * 64;
-      const bool ok = m < g.M && k < g.K;
+      const bool ok = a_loader && m < g.M && k < g.K;
       float4 a = z4, kb = z4, dp = z4, dn = z4, ep = z4, en = z4, ad = z4;
       if (ok) {
         a = load4_guard(g.A + (size_t)m * g.K, k, g.K, vK);
@@ -170,7 +174,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   auto finish_slab = [&]() {
     if (DEFER) {
 #pragma unroll
-      for (int i = 0; i < MH; ++i)
+      for (int i = 0; i < LROWS; ++i)
         if (live[i]) areg[i] = prologue(i, areg[i], kbr, dpr[i], dnr[i], epr[i], enr[i], adr[i]);
     }
   };
@@ -179,8 +183,9 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     float* as = As + stage * SLAB;
     float* bs = Bs + stage * SLAB;
 #pragma unroll
-    for (int i = 0; i < MH; ++i) {
+    for (int i = 0; i < LROWS; ++i) {
       const int r = lrow + i * 64;
+      if (!a_loader) continue;
       as[(lkc + 0) * LDS + r] = areg[i].x;
       as[(lkc + 1) * LDS + r] = areg[i].y;
       as[(lkc + 2) * LDS + r] = areg[i].z;
@@ -213,7 +218,13 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
     const float* bs = Bs + stage * SLAB;
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
-      const float4 a0 = *reinterpret_cast<const float4*>(&as[kk * LDS + ty * 4]);
+      float4 a0;
+      if (MH == 0) {
+        const float2 a2 = *reinterpret_cast<const float2*>(&as[kk * LDS + ty * 2]);
+        a0 = make_float4(a2.x, a2.y, 0.f, 0.f);
+      } else {
+        a0 = *reinterpret_cast<const float4*>(&as[kk * LDS + ty * 4]);
+      }
       const float4 b0 = *reinterpret_cast<const float4*>(&bs[kk * LDS + tx * 4]);
       float4 a1 = a0, b1 = b0;
       if (MH == 2) a1 = *reinterpret_cast<const float4*>(&as[kk * LDS + 64 + ty * 4]);
@@ -221,7 +232,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
       const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 4 * MH; ++i)
+      for (int i = 0; i < MR; ++i)
 #pragma unroll
         for (int j = 0; j < 4 * NH; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
@@ -235,20 +246,24 @@ __device__ __forceinline__ void gemm_mainloop(const GemmArgs& g, const int m0, c
   // Row sums of the prologue: the 4 threads that loaded one row are adjacent lanes.
   if (PRO == PRO_RELU) {
 #pragma unroll
-    for (int i = 0; i < MH; ++i) {
+    for (int i = 0; i < LROWS; ++i) {
       float v = rowacc[i];
       v += __shfl_xor_sync(0xffffffffu, v, 1);
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       const int m = m0 + lrow + i * 64;
-      if (g.delta != nullptr && blockIdx.y == 0 && (tid & 3) == 0 && m < g.M) {
+      if (g.delta != nullptr && blockIdx.y == 0 && (tid & 3) == 0 && a_loader && m < g.M) {
         g.delta[m] = g.accumulate ? (g.delta[m] + v) : v;
       }
     }
   }
 }
 
-// Row / column of micro-tile element (i, j) inside the 128x128 CTA tile.
-__device__ __forceinline__ int tile_row(int ty, int i) { return (i < 4) ? (ty * 4 + i) : (64 + ty * 4 + (i - 4)); }
+// Row / column of micro-tile element (i, j) inside the CTA tile (MH == 0: 32-row tiles, two rows per thread).
+template <int MH = 2>
+__device__ __forceinline__ int tile_row(int ty, int i) {
+  if (MH == 0) return ty * 2 + i;
+  return (i < 4) ? (ty * 4 + i) : (64 + ty * 4 + (i - 4));
+}
 __device__ __forceinline__ int tile_col(int tx, int jb) { return jb * 64 + tx * 4; }
 
 }  // namespace bf
