@@ -246,7 +246,10 @@ static bool adjoint_feature_major(const bf_chain* c, int M, int N) {
   if (c->sw.adjoint_kernel == 1) return false;
   if (c->sw.adjoint_kernel == 2) return true;
   const long long ctas = (long long)((M + 255) / 256) * ((((N + tc_adjoint_tile_rows() - 1) / tc_adjoint_tile_rows()) + 1) / 2);
-  return ctas >= 128;
+  // measured: with the GPU filled the feature-major kernel wins; below that it still wins on layers of 512 and more features
+  // (two feature CTAs per row block: c4 with 384-1024 subdomains 5.95-6.23 against 6.64-6.90 ms per call), the row-major
+  // kernel on narrower ones (256 features, 9216-18432 rows: 4.7 against 5.2 ms)
+  return ctas >= 128 || N >= 512;
 }
 
 static const unsigned char* tc_weights(const bf_chain* c, int layer, bool adjoint, int M, int K, int N) {
