@@ -33,16 +33,16 @@ def _c4_domains(D, dev):
     return wl, splits, spec, C, lo, up
 
 
-@pytest.fixture(params=["default", "feature_major"])
+@pytest.fixture(params=["row_major", "feature_major"])
 def adjoint_kernel(request):
-    """Runs a test with the default choice of the tensor-core adjoint kernel (row-major at these sizes) and with the
-    feature-major kernel pinned, so that its beta-gradient sums are covered at small, ragged row counts too."""
+    """Runs a test with each tensor-core adjoint kernel pinned (the default picks the feature-major one on layers of 512
+    and more features), so that the beta-gradient sums of both are covered at small, ragged row counts."""
     import os
 
-    if request.param == "feature_major":
-        os.environ["BF_B200_ADJ_FEATURE_MAJOR"] = "1"
+    var = "BF_B200_ADJ_FEATURE_MAJOR" if request.param == "feature_major" else "BF_B200_ADJ_ROWMAJOR"
+    os.environ[var] = "1"
     yield request.param
-    os.environ.pop("BF_B200_ADJ_FEATURE_MAJOR", None)
+    os.environ.pop(var, None)
 
 
 def test_alpha_beta_matches_reference_golden(dev, golden, adjoint_kernel, tc_from_256_rows):
