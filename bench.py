@@ -24,7 +24,9 @@ on a bounded sample of the workload per step.
 Other modes (profiling aids, one JSON line each): `--secondary-only cN` times one
 CROWN bounds/s configuration, `--kernels` times single kernels on resident data and
 reports their HBM / FP32 rooflines, `--conv-layers a,b --rows R` times the fused ReLU +
-transposed-convolution layer call on the CNN configurations' layer shapes.
+transposed-convolution layer call on the CNN configurations' layer shapes,
+`--linear-layer D,S,n_cur,n_prev` times the ReLU + Linear backward layer call on one
+synthetic layer (the kernel is chosen by the library's environment switches).
 """
 from __future__ import annotations
 
@@ -357,6 +359,44 @@ CONV_LAYERS = {  # name: (Co, Ho, Wo, Ci, Hi, Wi, kernel, stride, padding) of th
 }
 
 
+def linear_layer_bench(dev, shape, reps):
+    """Times the layer-level ReLU backward + Linear backward entry point (`bf_crown_relu_linear_bwd_packed`) on one
+    synthetic layer `domains,specs,n_cur,n_prev`; the environment switches (BF_B200_BWD_PERSISTENT, BF_B200_BWD_PAIRS,
+    BF_B200_FORCE_FFMA, BF_B200_TC_MIN_ROWS) select the kernel.  Result checked against a torch expression."""
+    from boundflow_b200 import _lib
+
+    B, S, K, N = (int(x) for x in shape.split(","))
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(1)
+    A = torch.randn(B, S, K, generator=g).to(dev)
+    au, al, bu = (torch.rand(B, K, generator=g).to(dev) for _ in range(3))
+    Wt = (torch.randn(K, N, generator=g) * 0.05).to(dev)
+    bias = torch.randn(K, generator=g).to(dev)
+    out, delta = torch.empty(B, S, N, device=dev), torch.empty(B, S, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    nb = int(lib.bf_linear_pack_bytes(K, N))
+    pack = torch.empty(nb, dtype=torch.uint8, device=dev)
+    _lib.check(lib.bf_linear_pack(Wt.data_ptr(), K, N, pack.data_ptr(), nb, st))
+
+    def call():
+        _lib.check(lib.bf_crown_relu_linear_bwd_packed(A.data_ptr(), 0, au.data_ptr(), al.data_ptr(), bu.data_ptr(), None, None, Wt.data_ptr(),
+                                                       bias.data_ptr(), pack.data_ptr(), out.data_ptr(), delta.data_ptr(), 0, B, S, K, N, st))
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    ref = torch.where(A >= 0, A * al[:, None, :], A * au[:, None, :]) @ Wt
+    return {"shape": [B, S, K, N], "rows": B * S, "us_per_launch": ms * 1e3, "tflops_fp32_equivalent": 2.0 * B * S * K * N / ms / 1e9,
+            "max_abs_err_vs_torch": float((out - ref).abs().max()), "tc_launches": int(_lib.tc_launch_count())}
+
+
 def conv_layer_bench(dev, names, rows, reps):
     """One `bf_crown_relu_conv2d_bwd` call per layer shape (ReLU scaling pass + transposed convolution, one side),
     CUDA events, multiply-accumulates per second."""
@@ -484,6 +524,7 @@ def main():
                     help="time only this CROWN bounds/s configuration and print its figures with per-kernel times (profiling aid)")
     ap.add_argument("--kernels", action="store_true", help="time single kernels on resident data and print their rooflines (profiling aid)")
     ap.add_argument("--conv-layers", default=None, help="comma-separated layer names: time the fused ReLU + transposed-convolution call (profiling aid)")
+    ap.add_argument("--linear-layer", default=None, help="domains,specs,n_cur,n_prev: time the ReLU + Linear backward entry point on one layer (profiling aid)")
     ap.add_argument("--rows", type=int, default=2048, help="coefficient rows for --conv-layers")
     ap.add_argument("--reps", type=int, default=10, help="repetitions for --conv-layers")
     args = ap.parse_args()
@@ -526,6 +567,9 @@ def main():
         return
     if args.conv_layers:
         print(json.dumps({"conv_layers": conv_layer_bench(dev, args.conv_layers.split(","), args.rows, args.reps)}))
+        return
+    if args.linear_layer:
+        print(json.dumps({"linear_layer": linear_layer_bench(dev, args.linear_layer, args.reps)}))
         return
     warmup = max(int(args.warmup), 3)
     strong = args.scaling == "strong"

@@ -23,11 +23,12 @@
 // freed and the kernel returns; nothing traps.
 //
 // Status: opt-in (environment variable BF_B200_BWD_PERSISTENT=1), not the default.  Measured on B200 on a
-// 73728 x 512 x 512 layer (8192 subdomains x 9 specs): 369 us against 196 us for the one-tile-per-CTA kernel
-// (crown_tc.cu, 128 x 512 tiles).  Per-role cycle counts (clock64 around every wait, CTA 0) show why: a 128 x 256
-// tile halves the MMA work that one produced coefficient block feeds (12 MMAs instead of 24), the producers need
-// about 4 k clock cycles per 128 x 32 block whether it feeds 12 or 24 MMAs, so the MMA thread waits for coefficient
-// tiles 50 % of the time.  Further measurements on the same layer: with the producers doing nothing but arriving on
+// 73728 x 512 x 512 layer (8192 subdomains x 9 specs): 233 us against 190 us for the one-tile-per-CTA kernel
+// (crown_tc.cu, 128 x 512 tiles).  Per-role cycle counts of an instrumented build (clock64 around every wait, CTA 0;
+// the stamps slow that build to 369 us, so they give shares, not absolute times) show why: a 128 x 256 tile halves
+// the MMA work that one produced coefficient block feeds (12 MMAs instead of 24) while the producers need the same time
+// per 128 x 32 block whether it feeds 12 or 24 MMAs, so the MMA thread waits for coefficient tiles half of the time.
+// Further measurements with the same build on the same layer: with the producers doing nothing but arriving on
 // their barrier (no loads, no transform, no stores) this kernel reaches 173 us (223 TFLOP/s fp32-equivalent; 201 us
 // with its weight copies on, which a 128 x 256 tile needs twice as often per MMA), i.e. 140 clock cycles per MMA plus
 // about 20 % of barrier round trips with two coefficient stages - so the one-tile-per-CTA kernel (196-200 TFLOP/s with
