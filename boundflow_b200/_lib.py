@@ -98,6 +98,13 @@ SIGNATURES = {
     "bf_alpha_select_best": (_i, [_p, _p, _p, _p, _i, _i, _f, _p, _i, _i, _p]),
     "bf_alpha_adam_step": (_i, [_p] * 9 + [_i, _f, _i, _i, _i, _i, _i, _p]),
     "bf_beta_adam_step": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _f, _i, _i, _i, _i, _i, _p]),
+    "bf_alpha_select_best_paired": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _f, _p, _i, _i, _p]),
+    "bf_rows_scale": (_i, [_p, _p, C.c_longlong, _i, _p]),
+    "bf_shared_metric": (_i, [_p, C.c_longlong, _p, _p, _i, _p]),
+    "bf_copy_if": (_i, [_p, _p, C.c_longlong, _p, _p]),
+    "bf_shared_adam_scratch_floats": (_sz, [_i, _i]),
+    "bf_shared_adam_step": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _f, _f, _i, _i, _i, _i, _p]),
+    "bf_shared_beta_add": (_i, [_p, _p, _i, _p, _i, _i, _p]),
     "bf_chain_alpha_crown_shared_objective": (_i, [_p] * 8 + [_i, _f, _p, _p, _p, _i, _f, _i, _i, _f, _f, _f, _p, _sz, _i, _i, _p]),
     "bf_branch_scores": (_i, [_p, _p, _p, _i, _p, _p, _p, _i, _p]),
     "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _i, _p, _sz, _i, _i, _p]),

@@ -773,7 +773,14 @@ def run_alpha_crown_mlp(
     -mean(lower), clamp to [0,1], and the bounds / alpha of the evaluation with the best
     whole-batch metric.  Returns (IntervalState, AlphaState, AlphaCrownStats) like the
     reference, for objective lower | upper | gap | both and spec_reduce mean | min | softmin, on
-    affine (relu affine)* chains (Linear / Conv2d / flatten)."""
+    affine (relu affine)* chains (Linear / Conv2d / flatten) and, through the per-value graph loop, on graphs with
+    add / concat / fan-out."""
+    if needs_graph_path(module):
+        bounds, state, _beta, stats = _run_alpha_beta_crown_graph(
+            module, input_spec, linear_spec_C=linear_spec_C, relu_split_state=relu_split_state, steps=steps, lr=lr, alpha_init=alpha_init,
+            beta_init=0.0, warm_start_alpha=warm_start, warm_start_beta=None, objective=objective, spec_reduce=spec_reduce, soft_tau=soft_tau,
+            lb_weight=lb_weight, ub_weight=ub_weight, per_batch_params=False, optimize_beta=False)
+        return bounds, state, stats
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, device = trace.chain, trace.mid.device
@@ -807,7 +814,12 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
     n_halfspaces int32 [B]) as CUDA tensors.  The splits of the first ReLU over a Linear or Conv2d first
     layer are used (conv: the half-space row of a split neuron is its filter placed in the input image,
     alpha_beta_crown.py:325-387; only the rows of neurons that are split somewhere in the batch are formed);
-    a chain that starts otherwise, or no split on that ReLU, gives all zeros."""
+    a chain that starts otherwise, or no split on that ReLU, gives all zeros.  On a graph that is not a chain every
+    ReLU fed by a Linear / Conv2d op on the input value contributes its half-spaces (`dag.first_layer_certificate_dag`)."""
+    if needs_graph_path(module):
+        from .dag import first_layer_certificate_dag
+
+        return first_layer_certificate_dag(module, input_spec, relu_split_state, steps=steps, lr=lr, tol=tol)
     spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
     if lp_ball_of(spec) is not None:
         raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
@@ -847,27 +859,28 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
 
 
 def _run_alpha_beta_crown_graph(module, input_spec, *, linear_spec_C, relu_split_state, steps, lr, alpha_init, beta_init, warm_start_alpha,
-                                warm_start_beta, objective, spec_reduce, per_batch_params, optimize_beta):
-    """`run_alpha_beta_crown_mlp` on a graph that is not a chain (residual add, concat, fan-out): the per-domain loop
-    of `dag.alpha_beta_crown_dag`.  The reference accepts these graphs because its sweep is the generic graph backward
-    under autograd (crown_ibp.py:1669-2051)."""
+                                warm_start_beta, objective, spec_reduce, soft_tau, lb_weight, ub_weight, per_batch_params, optimize_beta):
+    """`run_alpha_beta_crown_mlp` on a graph that is not a chain (residual add, concat, fan-out): the loop of
+    `dag.alpha_beta_crown_dag`, per-domain or shared parameters, every objective and reduction of the chain path.  The
+    reference accepts these graphs because its sweep is the generic graph backward under autograd
+    (crown_ibp.py:1669-2051)."""
     from .dag import alpha_beta_crown_dag
 
-    if objective != "lower" or not per_batch_params:
-        raise NotImplementedError("the graph path of the CUDA backend implements objective='lower' with per_batch_params=True")
     a0 = getattr(warm_start_alpha, "alpha_by_relu_input", None) if warm_start_alpha is not None else None
     b0 = getattr(warm_start_beta, "beta_by_relu_input", None) if warm_start_beta is not None else None
-    if relu_split_state and not optimize_beta and b0 is not None and any(float(torch.as_tensor(b).abs().max()) != 0.0 for b in b0.values()):
+    if relu_split_state and not optimize_beta and objective == "lower" and b0 is not None and any(
+            float(torch.as_tensor(b).abs().max()) != 0.0 for b in b0.values()):
         raise NotImplementedError("a frozen non-zero beta is not supported; pass optimize_beta=None/True")
     best_l, best_u, best_a, best_b, tr = alpha_beta_crown_dag(module, input_spec, linear_spec_C, steps=steps, lr=lr, alpha0=a0, alpha_init=alpha_init,
                                                               relu_split_state=relu_split_state, optimize_beta=optimize_beta, beta0=b0,
-                                                              beta_init=beta_init, spec_reduce=spec_reduce)
+                                                              beta_init=beta_init, spec_reduce=spec_reduce, soft_tau=soft_tau, objective=objective,
+                                                              lb_weight=lb_weight, ub_weight=ub_weight, per_batch_params=per_batch_params)
     dev = normalize_input_spec(input_spec).center.device
-    B = tr.B
+    lead = (tr.B,) if per_batch_params else ()
     bounds = IntervalState(lower=best_l.to(dev), upper=best_u.to(dev))
     names = list(best_a)
-    a_state = AlphaState({n: best_a[n].reshape((B,) + tuple(tr.shape[n])).to(dev) for n in names})
-    b_state = BetaState({n: best_b[n].reshape((B,) + tuple(tr.shape[n])).to(dev) for n in names})
+    a_state = AlphaState({n: best_a[n].reshape(lead + tuple(tr.shape[n])).to(dev) for n in names})
+    b_state = BetaState({n: best_b[n].reshape(lead + tuple(tr.shape[n])).to(dev) for n in names})
     stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(names))
     return bounds, a_state, b_state, stats
 
@@ -905,7 +918,8 @@ def run_alpha_beta_crown_mlp(
     beta term to objective="lower" alone, and its min / softmin with beta is not built here).  Shared mode:
     the same objectives and mean | min | softmin, with beta for objective="lower", spec_reduce="mean".  For a single node the first-layer
     infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
-    reference (Linear first layers; `first_layer_certificate` gives it for whole batches).
+    reference (`first_layer_certificate` gives it for whole batches).  Graphs that are not chains (residual add,
+    concat, fan-out) take the same arguments through the per-value loop of `dag.alpha_beta_crown_dag`.
     Infeasible splits raise ValueError like the reference.
     """
     if objective not in ("lower", "upper", "gap", "both"):
@@ -915,11 +929,6 @@ def run_alpha_beta_crown_mlp(
         optimize_beta = has_split
     if optimize_beta and not has_split:
         optimize_beta = False  # nothing to constrain: beta's gradient is identically zero
-    if needs_graph_path(module):
-        return _run_alpha_beta_crown_graph(module, input_spec, linear_spec_C=linear_spec_C, relu_split_state=relu_split_state, steps=steps, lr=lr,
-                                           alpha_init=alpha_init, beta_init=beta_init, warm_start_alpha=warm_start_alpha,
-                                           warm_start_beta=warm_start_beta, objective=objective, spec_reduce=spec_reduce,
-                                           per_batch_params=per_batch_params, optimize_beta=bool(optimize_beta))
     if has_split and int(normalize_input_spec(input_spec).center.shape[0]) == 1:
         # the reference's pre-check for a single node (alpha_beta_crown.py:693-714)
         cert, cert_val, _cnt = first_layer_certificate(module, input_spec, relu_split_state)
@@ -929,6 +938,12 @@ def run_alpha_beta_crown_mlp(
             stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=(),
                                     feasibility="infeasible", reason=f"infeasible: first-layer certificate with max {float(cert_val[0]):.3e}")
             return IntervalState(lower=zeros, upper=zeros), AlphaState({}), BetaState({}), stats
+    if needs_graph_path(module):
+        return _run_alpha_beta_crown_graph(module, input_spec, linear_spec_C=linear_spec_C, relu_split_state=relu_split_state, steps=steps, lr=lr,
+                                           alpha_init=alpha_init, beta_init=beta_init, warm_start_alpha=warm_start_alpha,
+                                           warm_start_beta=warm_start_beta, objective=objective, spec_reduce=spec_reduce, soft_tau=soft_tau,
+                                           lb_weight=lb_weight, ub_weight=ub_weight, per_batch_params=per_batch_params,
+                                           optimize_beta=bool(optimize_beta))
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
     chain, B, device = trace.chain, trace.B, trace.mid.device

@@ -654,3 +654,58 @@ extern "C" int bf_beta_adam_step(float* beta, float* m, float* v, float* gsum, c
   return bf::launch_beta_step(beta, m, v, gsum, split, split_stride, improve, best_beta, add, bf::adam_scalars(t, lr, spec_reduce, S),
                               do_update, B, n, bf::as_stream(stream));
 }
+
+extern "C" int bf_alpha_select_best_paired(const float* cur, float* best_rows, float* best_metric, int* improve, int first,
+                                           int objective, int spec_reduce, float soft_tau, float lb_weight, float ub_weight,
+                                           float* row_weight, int B, int S, bf_stream_t stream) {
+  BF_REQUIRE(cur && best_rows && best_metric && improve, BF_E_INVALID, "bf_alpha_select_best_paired: null tensor");
+  BF_REQUIRE(objective == BF_OBJECTIVE_GAP || objective == BF_OBJECTIVE_BOTH, BF_E_INVALID,
+             "bf_alpha_select_best_paired: objective must be BF_OBJECTIVE_GAP or BF_OBJECTIVE_BOTH");
+  BF_REQUIRE(B > 0 && S > 0 && (spec_reduce == BF_REDUCE_MEAN || spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN),
+             BF_E_INVALID, "bf_alpha_select_best_paired: bad sizes or reduction");
+  BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "bf_alpha_select_best_paired: soft_tau must be positive");
+  BF_REQUIRE(lb_weight >= 0.f && ub_weight >= 0.f, BF_E_UNSUPPORTED, "bf_alpha_select_best_paired: negative objective weight");
+  return bf::launch_select_best_paired(cur, best_rows, best_metric, improve, first, objective, spec_reduce, soft_tau, lb_weight, ub_weight,
+                                       row_weight, B, S, bf::as_stream(stream));
+}
+
+extern "C" int bf_rows_scale(float* A, const float* w, long long M, int n, bf_stream_t stream) {
+  BF_REQUIRE(A && w, BF_E_INVALID, "bf_rows_scale: null tensor");
+  BF_REQUIRE(M > 0 && n > 0, BF_E_INVALID, "bf_rows_scale: bad sizes");
+  return bf::launch_scale_rows(A, w, M, n, bf::as_stream(stream));
+}
+
+extern "C" int bf_shared_metric(const float* values, long long M, float* best_metric, int* improve, int first, bf_stream_t stream) {
+  BF_REQUIRE(values && best_metric && improve, BF_E_INVALID, "bf_shared_metric: null tensor");
+  BF_REQUIRE(M > 0, BF_E_INVALID, "bf_shared_metric: bad size");
+  return bf::launch_shared_metric(values, M, best_metric, improve, first, bf::as_stream(stream));
+}
+
+extern "C" int bf_copy_if(const float* src, float* dst, long long n, const int* flag, bf_stream_t stream) {
+  BF_REQUIRE(src && dst && flag, BF_E_INVALID, "bf_copy_if: null tensor");
+  BF_REQUIRE(n > 0, BF_E_INVALID, "bf_copy_if: bad size");
+  return bf::launch_copy_if(src, dst, n, flag, bf::as_stream(stream));
+}
+
+extern "C" size_t bf_shared_adam_scratch_floats(int B, int n) {
+  if (B <= 0 || n <= 0) return 0;
+  return (size_t)bf::shared_alpha_chunks(B) * (size_t)n;
+}
+
+extern "C" int bf_shared_adam_step(float* param, float* m, float* v, float* grad, const int8_t* split, int split_stride, float* scratch,
+                                   const int* improve, float* best, int t, float lr, float grad_scale, int do_update, int is_beta,
+                                   int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(param && m && v && grad && scratch && improve && best, BF_E_INVALID, "bf_shared_adam_step: null tensor");
+  BF_REQUIRE(B > 0 && n > 0 && t >= 0 && lr > 0.f && (split == nullptr || split_stride == 0 || split_stride == n), BF_E_INVALID,
+             "bf_shared_adam_step: bad sizes or options");
+  bf::AdamScalars sc = bf::adam_scalars(t, lr, BF_REDUCE_SUM, 1);
+  sc.grad_scale = grad_scale;
+  return bf::launch_shared_adam(param, m, v, grad, split, split_stride, scratch, improve, best, sc, do_update, is_beta, B, n,
+                                bf::as_stream(stream));
+}
+
+extern "C" int bf_shared_beta_add(const float* beta, const int8_t* split, int split_stride, float* add, int B, int n, bf_stream_t stream) {
+  BF_REQUIRE(beta && split && add, BF_E_INVALID, "bf_shared_beta_add: null tensor");
+  BF_REQUIRE(B > 0 && n > 0 && (split_stride == 0 || split_stride == n), BF_E_INVALID, "bf_shared_beta_add: bad sizes");
+  return bf::launch_shared_beta_add(beta, split, split_stride, add, B, n, bf::as_stream(stream));
+}

@@ -436,16 +436,34 @@ def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[t
                          alpha0: Optional[Mapping[str, torch.Tensor]] = None, alpha_init: float = 0.5,
                          relu_split_state: Optional[Mapping[str, torch.Tensor]] = None, optimize_beta: bool = False,
                          beta0: Optional[Mapping[str, torch.Tensor]] = None, beta_init: float = 0.0, spec_reduce: str = "mean",
-                         output_value: Optional[str] = None):
-    """Per-domain alpha (and beta) loop on a graph that is not a chain: `run_alpha_beta_crown_mlp(per_batch_params=True,
-    objective="lower")` (alpha_beta_crown.py:716-923), whose sweep is the reference's generic graph backward.  steps + 1
-    evaluations; each is one lower sweep that keeps the coefficients at every ReLU, the per-domain objective with strict
-    best-of, one gradient sweep and one Adam step per ReLU.  Returns (best_lower, best_upper, best_alpha dict,
-    best_beta dict, trace); alpha / beta are [B, n] per ReLU input name."""
+                         soft_tau: float = 1.0, objective: str = "lower", lb_weight: float = 1.0, ub_weight: float = 1.0,
+                         per_batch_params: bool = True, output_value: Optional[str] = None):
+    """alpha (and beta) loop on a graph that is not a chain: `run_alpha_beta_crown_mlp` (alpha_beta_crown.py:716-923),
+    whose sweep is the reference's generic graph backward.  steps + 1 evaluations; each is one lower sweep that keeps
+    the coefficients at every ReLU, the objective with strict best-of, one gradient sweep and one Adam step per ReLU.
+
+    `per_batch_params=True`: one parameter row and one best-of per domain; False: one row shared by the batch and a
+    whole-batch best-of on the mean of the per-domain objectives.  `objective` lower | upper | gap | both (807-818):
+    upper runs on the negated spec rows, gap / both on the rows followed by their negations (2S rows per domain, row
+    weights from the objective's derivative scale the kept coefficients before the gradient sweep).  `spec_reduce`
+    mean | min | softmin (787-805), plus sum for lower.  beta enters objective="lower" with mean / sum only.
+    Returns (best_lower, best_upper, best_alpha dict, best_beta dict, trace); alpha / beta are [B, n] ([1, n] in the
+    shared mode) per ReLU input name."""
     lib = _lib.load()
-    codes = {"mean": _lib.REDUCE_MEAN, "sum": _lib.REDUCE_SUM}
-    if spec_reduce not in codes:
-        raise NotImplementedError("the graph path of the CUDA backend implements spec_reduce mean | sum")
+    codes = {"mean": _lib.REDUCE_MEAN, "sum": _lib.REDUCE_SUM, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
+    if objective not in ("lower", "upper", "gap", "both"):
+        raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
+    if spec_reduce not in codes or (spec_reduce == "sum" and (objective != "lower" or not per_batch_params)):
+        raise ValueError(f"spec_reduce={spec_reduce!r}: expected mean | min | softmin (sum with the per-domain lower objective only)")
+    if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
+        raise ValueError(f"soft_tau must be >0, got {soft_tau}")
+    paired = objective in ("gap", "both")
+    if paired and (float(lb_weight) < 0.0 or float(ub_weight) < 0.0):
+        raise NotImplementedError("the CUDA backend takes non-negative lb_weight / ub_weight (a row weight must not flip the sign decisions of the gradient sweep)")
+    weighted = paired or spec_reduce in ("min", "softmin")
+    with_beta = bool(optimize_beta and relu_split_state and objective == "lower")
+    if with_beta and weighted:
+        raise NotImplementedError("the CUDA backend combines the min / softmin spec reductions with alpha only (no beta parameters)")
     spec = normalize_input_spec(input_spec)
     tr = forward_ibp_dag(module, spec, relu_split_state)
     if int(tr.infeasible.sum()) != 0:
@@ -453,60 +471,199 @@ def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[t
     device, B = tr.mid.device, tr.B
     params = _params(module, device)
     output_value = _output_value(module, tr, output_value)
-    C = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
+    C0 = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
+    S0 = int(C0.shape[1])
+    C = -C0 if objective == "upper" else (torch.cat([C0, -C0], dim=1).contiguous() if paired else C0)
     S = int(C.shape[1])
+    M = B * S
     s = _stream_ptr(device)
     names = list(dict.fromkeys(tr.relu_inputs))
     width = {x: _numel(tr.shape[x]) for x in names}
+    rows = B if per_batch_params else 1
 
     def start(raw, x, init):
         n = width[x]
         if raw is not None and x in raw and raw[x] is not None:
-            t, _ = _alpha_rows(raw[x], B, n, device, x)
-            return t.expand(B, n).contiguous().clone()
-        return torch.full((B, n), float(init), dtype=torch.float32, device=device)
+            t, _ = _alpha_rows(raw[x], rows, n, device, x)
+            if not per_batch_params and int(t.shape[0]) != 1:
+                raise ValueError(f"warm start [{x}] is batch-specific; expected the shared shape {tuple(tr.shape[x])}")
+            return t.expand(rows, n).contiguous().clone()
+        return torch.full((rows, n), float(init), dtype=torch.float32, device=device)
 
-    zeros = lambda x: torch.zeros(B, width[x], dtype=torch.float32, device=device)  # noqa: E731
+    zeros = lambda x, r=B: torch.zeros(r, width[x], dtype=torch.float32, device=device)  # noqa: E731
     alpha = {x: start(alpha0, x, alpha_init) for x in names}
     best_alpha = {x: alpha[x].clone() for x in names}
-    m, v, grad, slope = ({x: zeros(x) for x in names} for _ in range(4))
-    with_beta = bool(optimize_beta and relu_split_state)
+    m, v = ({x: zeros(x, rows) for x in names} for _ in range(2))
+    grad, slope = ({x: zeros(x) for x in names} for _ in range(2))
     beta = {x: start(beta0, x, beta_init) for x in names}
     best_beta = {x: beta[x].clone() for x in names}
-    splits: Dict[str, Tuple[torch.Tensor, int]] = {}
+    splits: Dict[str, Tuple[Optional[torch.Tensor], int]] = {}
     if with_beta:
-        mb, vb, gsum, addv = ({x: zeros(x) for x in names} for _ in range(4))
+        mb, vb = ({x: zeros(x, rows) for x in names} for _ in range(2))
+        gsum, addv = ({x: zeros(x) for x in names} for _ in range(2))
         for x in names:
             sp = relu_split_state.get(x)
-            splits[x] = _split_tensor(sp, B, width[x], device, x) if sp is not None else (torch.zeros(1, width[x], dtype=torch.int8, device=device), 0)
-        for x in names:  # split term of the start beta
-            _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]), splits[x][1],
-                                             None, None, _lib.ptr(addv[x]), 0, float(lr), codes[spec_reduce], S, 0, B, width[x], s))
-    best_lower = torch.empty(B, S, dtype=torch.float32, device=device)
-    best_metric = torch.empty(B, dtype=torch.float32, device=device)
-    improve = torch.zeros(B, dtype=torch.int32, device=device)
+            if sp is not None:
+                splits[x] = _split_tensor(sp, B, width[x], device, x)
+            else:
+                splits[x] = (torch.zeros(1, width[x], dtype=torch.int8, device=device), 0) if per_batch_params else (None, 0)
+        if per_batch_params:
+            for x in names:  # split term of the start beta
+                _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]),
+                                                 splits[x][1], None, None, _lib.ptr(addv[x]), 0, float(lr), codes[spec_reduce], S, 0, B, width[x], s))
+    best_rows = torch.empty(B, S, dtype=torch.float32, device=device)
+    best_metric = torch.empty(rows, dtype=torch.float32, device=device)
+    improve = torch.zeros(rows, dtype=torch.int32, device=device)
+    row_weight = torch.empty(B, S, dtype=torch.float32, device=device) if weighted else None
+    if not per_batch_params:
+        scratch = torch.empty(max(int(lib.bf_shared_adam_scratch_floats(B, width[x])) for x in names) if names else 1, dtype=torch.float32, device=device)
+        if weighted:
+            dom_rows = torch.empty(B, S, dtype=torch.float32, device=device)
+            dom_metric = torch.empty(B, dtype=torch.float32, device=device)
+            dom_improve = torch.zeros(B, dtype=torch.int32, device=device)
+    obj_code = _lib.OBJECTIVE_GAP if objective == "gap" else _lib.OBJECTIVE_BOTH
+    # d loss / d lower of the Adam steps: row weights already carry 1/S of a paired mean
+    per_domain_reduce = _lib.REDUCE_SUM if paired else codes[spec_reduce]
+    shared_scale = (-1.0 / B) if weighted else (-1.0 / M)
+
+    def select(cur, rows_out, metric_out, improve_out, first, rw):
+        if paired:
+            _lib.check(lib.bf_alpha_select_best_paired(_lib.ptr(cur), _lib.ptr(rows_out), _lib.ptr(metric_out), _lib.ptr(improve_out), first, obj_code,
+                                                       codes[spec_reduce], float(soft_tau), float(lb_weight), float(ub_weight), _lib.ptr(rw), B, S0, s))
+        else:
+            _lib.check(lib.bf_alpha_select_best(_lib.ptr(cur), _lib.ptr(rows_out), _lib.ptr(metric_out), _lib.ptr(improve_out), first,
+                                                codes[spec_reduce], float(soft_tau), _lib.ptr(rw), B, S, s))
+
     for t in range(int(steps) + 1):
         last = t == int(steps)
         relax = _relax(lib, tr, alpha, s)
+        if with_beta and not per_batch_params:
+            for x in names:
+                if splits[x][0] is not None:
+                    _lib.check(lib.bf_shared_beta_add(_lib.ptr(beta[x]), _lib.ptr(splits[x][0]), splits[x][1], _lib.ptr(addv[x]), B, width[x], s))
         ahat: Dict[str, torch.Tensor] = {}
         cur, A0 = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=addv if with_beta else None, ahat=ahat)
-        _lib.check(lib.bf_alpha_select_best(_lib.ptr(cur), _lib.ptr(best_lower), _lib.ptr(best_metric), _lib.ptr(improve), 1 if t == 0 else 0,
-                                            codes[spec_reduce], 1.0, None, B, S, s))
+        rw = row_weight if (weighted and not last) else None
+        if per_batch_params:
+            select(cur, best_rows, best_metric, improve, 1 if t == 0 else 0, rw)
+        else:
+            if weighted:  # per-domain objective and its derivative (no per-domain best-of), then the batch mean
+                select(cur, dom_rows, dom_metric, dom_improve, 1, rw)
+                _lib.check(lib.bf_shared_metric(_lib.ptr(dom_metric), B, _lib.ptr(best_metric), _lib.ptr(improve), 1 if t == 0 else 0, s))
+            else:
+                _lib.check(lib.bf_shared_metric(_lib.ptr(cur), M, _lib.ptr(best_metric), _lib.ptr(improve), 1 if t == 0 else 0, s))
+            _lib.check(lib.bf_copy_if(_lib.ptr(cur), _lib.ptr(best_rows), M, _lib.ptr(improve), s))
         if not last:
+            if weighted:
+                done = set()
+                for x, A in ahat.items():
+                    if A.data_ptr() not in done:
+                        done.add(A.data_ptr())
+                        _lib.check(lib.bf_rows_scale(_lib.ptr(A), _lib.ptr(row_weight), M, width[x], s))
             _adjoint_forward(lib, module, tr, params, relax, A0, ahat, grad, gsum if with_beta else None, S)
+        upd = 0 if last else 1
         for x in names:
             n = width[x]
-            _lib.check(lib.bf_alpha_adam_step(_lib.ptr(alpha[x]), _lib.ptr(m[x]), _lib.ptr(v[x]), _lib.ptr(grad[x]), _lib.ptr(improve), _lib.ptr(best_alpha[x]),
-                                              _lib.ptr(tr.pre_l[x]), _lib.ptr(tr.pre_u[x]), _lib.ptr(slope[x]), t, float(lr), codes[spec_reduce], S,
-                                              0 if last else 1, B, n, s))
-            if with_beta:
-                _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]),
-                                                 splits[x][1], _lib.ptr(improve), _lib.ptr(best_beta[x]), _lib.ptr(addv[x]), t, float(lr),
-                                                 codes[spec_reduce], S, 0 if last else 1, B, n, s))
-    # the upper bound of each domain's best iteration: the upper sweep at its best alpha (beta acts on the lower side only)
+            if per_batch_params:
+                _lib.check(lib.bf_alpha_adam_step(_lib.ptr(alpha[x]), _lib.ptr(m[x]), _lib.ptr(v[x]), _lib.ptr(grad[x]), _lib.ptr(improve), _lib.ptr(best_alpha[x]),
+                                                  _lib.ptr(tr.pre_l[x]), _lib.ptr(tr.pre_u[x]), _lib.ptr(slope[x]), t, float(lr), per_domain_reduce, S,
+                                                  upd, B, n, s))
+                if with_beta:
+                    _lib.check(lib.bf_beta_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(splits[x][0]),
+                                                     splits[x][1], _lib.ptr(improve), _lib.ptr(best_beta[x]), _lib.ptr(addv[x]), t, float(lr),
+                                                     per_domain_reduce, S, upd, B, n, s))
+            else:
+                _lib.check(lib.bf_shared_adam_step(_lib.ptr(alpha[x]), _lib.ptr(m[x]), _lib.ptr(v[x]), _lib.ptr(grad[x]), None, 0, _lib.ptr(scratch),
+                                                   _lib.ptr(improve), _lib.ptr(best_alpha[x]), t, float(lr), shared_scale, upd, 0, B, n, s))
+                if with_beta:
+                    sp, st = splits[x]  # without a split on this ReLU the beta gradient is identically zero: snapshot only
+                    _lib.check(lib.bf_shared_adam_step(_lib.ptr(beta[x]), _lib.ptr(mb[x]), _lib.ptr(vb[x]), _lib.ptr(gsum[x]), _lib.ptr(sp), st,
+                                                       _lib.ptr(scratch), _lib.ptr(improve), _lib.ptr(best_beta[x]), t, float(lr), shared_scale,
+                                                       upd if sp is not None else 0, 1, B, n, s))
+    if paired:
+        return best_rows[:, :S0].contiguous(), -best_rows[:, S0:], best_alpha, best_beta, tr
+    # the other side at each domain's best alpha (beta acts on the lower side only)
     relax = _relax(lib, tr, best_alpha, s)
-    best_upper, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
-    return best_lower, best_upper, best_alpha, best_beta, tr
+    other, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
+    if objective == "upper":
+        return -other, -best_rows, best_alpha, best_beta, tr
+    return best_rows, other, best_alpha, best_beta, tr
+
+
+def first_layer_certificate_dag(module: Any, input_spec: Any, relu_split_state: Mapping[str, torch.Tensor], *, steps: int = 200,
+                                lr: float = 0.1, tol: float = 1e-6):
+    """First-layer infeasibility certificate on a graph (`_is_infeasible_split_first_layer_convex_combo`,
+    alpha_beta_crown.py:255-532): every ReLU whose input is produced by a Linear or Conv2d op that reads the input value
+    contributes the half-spaces of its split neurons (264-387); the rows of all of them are stacked and handed to the
+    certificate kernel.  Returns (infeasible int32 [B]: 1 found / 0 none, best_value [B], n_halfspaces int32 [B])."""
+    lib = _lib.load()
+    spec = normalize_input_spec(input_spec)
+    if lp_ball_of(spec) is not None:
+        raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
+    device = _cuda_device(spec.center)
+    B = int(spec.center.shape[0])
+    mid, rad, _lo, _up = input_mid_rad(spec)
+    mid, rad = _f32(mid, device).reshape(B, -1).contiguous(), _f32(rad, device).reshape(B, -1).contiguous()
+    n0 = int(mid.shape[1])
+    infeasible = torch.zeros(B, dtype=torch.int32, device=device)
+    best = torch.full((B,), float("inf"), dtype=torch.float32, device=device)
+    count = torch.zeros(B, dtype=torch.int32, device=device)
+    task = module.get_entry_task()
+    params = _params(module, device)
+    producer = {op.outputs[0]: op for op in task.ops}
+    in_shape = tuple(int(d) for d in spec.center.shape[1:])
+    s = _stream_ptr(device)
+    W_parts, b_parts, sp_parts, per_domain = [], [], [], False
+    seen = set()
+    for op in task.ops:
+        if op.op_type != "relu" or op.inputs[0] in seen:
+            continue
+        x = op.inputs[0]
+        seen.add(x)
+        raw = relu_split_state.get(x) if relu_split_state else None
+        prod = producer.get(x)
+        if raw is None or prod is None or prod.op_type not in ("linear", "conv2d") or not prod.inputs or prod.inputs[0] != spec.value_name:
+            continue
+        W = params[prod.inputs[1]]
+        b = params[prod.inputs[2]] if len(prod.inputs) == 3 else None
+        if prod.op_type == "linear":
+            n1 = int(W.shape[0])
+        else:
+            if len(in_shape) != 3:
+                continue
+            Ci, Hi, Wi = in_shape
+            kh, kw = int(W.shape[2]), int(W.shape[3])
+            sth, pdh = _pair(prod.attrs.get("stride", 1)), _pair(prod.attrs.get("padding", 0))
+            Co = int(W.shape[0])
+            Ho, Wo = (Hi + 2 * pdh[0] - kh) // sth[0] + 1, (Wi + 2 * pdh[1] - kw) // sth[1] + 1
+            n1 = Co * Ho * Wo
+        sp, stride = _split_tensor(raw, B, n1, device, x)
+        cols = torch.nonzero((sp != 0).any(dim=0)).flatten()   # neurons split in at least one domain, ascending
+        U = int(cols.numel())
+        if U == 0:
+            continue
+        if prod.op_type == "linear":
+            W_rows = W.index_select(0, cols).contiguous()
+            b_rows = b.index_select(0, cols).contiguous() if b is not None else torch.zeros(U, dtype=torch.float32, device=device)
+        else:
+            W_rows = torch.empty(U, n0, dtype=torch.float32, device=device)
+            b_rows = torch.empty(U, dtype=torch.float32, device=device)
+            rows = cols.to(torch.int32).contiguous()
+            _lib.check(lib.bf_conv2d_dense_rows(_lib.ptr(W), _lib.ptr(b), _lib.ptr(rows), U, _lib.ptr(W_rows), _lib.ptr(b_rows), Ci, Hi, Wi, Co, Ho, Wo,
+                                                kh, kw, sth[0], sth[1], pdh[0], pdh[1], s))
+        W_parts.append(W_rows)
+        b_parts.append(b_rows)
+        sp_parts.append(sp[:, cols])
+        per_domain = per_domain or stride != 0
+    if not W_parts:
+        return infeasible, best, count
+    rows_sp = B if per_domain else 1
+    W_all, b_all = torch.cat(W_parts, dim=0).contiguous(), torch.cat(b_parts, dim=0).contiguous()
+    sp_all = torch.cat([p.expand(rows_sp, -1) for p in sp_parts], dim=1).contiguous()
+    U = int(W_all.shape[0])
+    _lib.check(lib.bf_first_layer_certificate(_lib.ptr(sp_all), U if per_domain else 0, _lib.ptr(W_all), _lib.ptr(b_all), _lib.ptr(mid), _lib.ptr(rad),
+                                              _lib.ptr(infeasible), _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, U, n0, s))
+    return infeasible, best, count
 
 
 def run_crown_ibp_dag(module: Any, input_spec: Any, *, linear_spec_C: Optional[torch.Tensor] = None,

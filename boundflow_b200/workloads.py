@@ -295,6 +295,62 @@ def make_conv_certificate_cases(seed: int = 1013):
     return module, layers, x, lo, up, cases
 
 
+def make_graph_certificate_cases(kind: str = "linear", seed: int = 1019):
+    """Two-branch graph for the first-layer infeasibility certificate on a graph that is not a chain: branches "ha" (6
+    neurons) and "hb" (2 neurons) both read the input, a ReLU on each, concat, Linear head.  kind "linear": the input is a
+    vector of 8 and the branches are Linear ops; kind "conv": the input is 2x2x2 and the branches are Conv2d ops with
+    2x2 kernels (one output pixel, the same weights reshaped), so both kinds pose the same half-spaces.  Row 0 of
+    branch a is pinned to be unstable; row 0 of branch b is minus that row (so "ha[0] active" contradicts "hb[0] active"
+    across the two ReLUs, uniform weights) and row 1 is minus twice the row (needs the optimiser).
+    Returns (module, x, lo, up, cases) with cases = list of (name, {"ha": int8 [6], "hb": int8 [2]})."""
+    if kind not in ("linear", "conv"):
+        raise ValueError(kind)
+    g = torch.Generator("cpu").manual_seed(seed)
+    Wa = torch.randn(6, 8, generator=g) * 0.5
+    ba = torch.randn(6, generator=g) * 0.1
+    x = torch.rand(1, 8, generator=g)
+    ba[0] = -float(Wa[0] @ x.reshape(-1))   # ha[0] is zero at the centre: unstable over the box
+    Wb = torch.stack([-Wa[0], -2.0 * Wa[0]])
+    bb = torch.stack([-ba[0] - 0.05, -2.0 * ba[0] - 0.09])
+    Wh = torch.randn(3, 8, generator=g) * 0.5
+    bh = torch.randn(3, generator=g) * 0.1
+    lo, up = (x - 0.3).clamp(0, 1), (x + 0.3).clamp(0, 1)
+    if kind == "linear":
+        ops = [TaskOp("linear", "branch_a", ["input", "Wa", "ba"], ["ha"]), TaskOp("relu", "relu_a", ["ha"], ["ra"]),
+               TaskOp("linear", "branch_b", ["input", "Wb", "bb"], ["hb"]), TaskOp("relu", "relu_b", ["hb"], ["rb"]),
+               TaskOp("concat", "cat", ["ra", "rb"], ["hc"], {"axis": 1}), TaskOp("linear", "head", ["hc", "Wh", "bh"], ["out"])]
+        params = {"Wa": Wa, "ba": ba, "Wb": Wb, "bb": bb, "Wh": Wh, "bh": bh}
+    else:
+        k2 = {"stride": (1, 1), "padding": (0, 0), "dilation": (1, 1), "groups": 1}
+        ops = [TaskOp("conv2d", "branch_a", ["input", "Wa", "ba"], ["ha"], k2), TaskOp("relu", "relu_a", ["ha"], ["ra"]),
+               TaskOp("conv2d", "branch_b", ["input", "Wb", "bb"], ["hb"], k2), TaskOp("relu", "relu_b", ["hb"], ["rb"]),
+               TaskOp("concat", "cat", ["ra", "rb"], ["hc"], {"axis": 1}),
+               TaskOp("flatten", "flatten", ["hc"], ["flat"], {"start_dim": 1, "end_dim": -1}), TaskOp("linear", "head", ["flat", "Wh", "bh"], ["out"])]
+        params = {"Wa": Wa.reshape(6, 2, 2, 2).clone(), "ba": ba, "Wb": Wb.reshape(2, 2, 2, 2).clone(), "bb": bb, "Wh": Wh, "bh": bh}
+        x, lo, up = x.reshape(1, 2, 2, 2), lo.reshape(1, 2, 2, 2), up.reshape(1, 2, 2, 2)
+    task = BoundTask(task_id="graph_cert", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    module = BFTaskModule(tasks=[task], entry_task_id="graph_cert", bindings={"params": params})
+
+    def rows(a=(), b=()):
+        ra, rb = torch.zeros(6, dtype=torch.int8), torch.zeros(2, dtype=torch.int8)
+        for i, v in a:
+            ra[i] = v
+        for i, v in b:
+            rb[i] = v
+        return {"ha": ra, "hb": rb}
+
+    cases = [
+        ("no_split", rows()),
+        ("one_feasible", rows(a=[(0, 1)])),
+        ("cross_branch_contradiction_uniform_weights", rows(a=[(0, 1)], b=[(0, 1)])),
+        ("cross_branch_contradiction_needs_steps", rows(a=[(0, 1)], b=[(1, 1)])),
+        ("cross_branch_feasible", rows(a=[(0, 1)], b=[(0, -1)])),
+        ("second_branch_only", rows(b=[(0, 1), (1, 1)])),
+        ("triple_with_bystander", rows(a=[(0, 1), (3, -1)], b=[(1, 1)])),
+    ]
+    return module, x, lo, up, cases
+
+
 def make_graph_cases(seed: int = 1011):
     """Small graphs that are not chains, shaped like the reference's end-to-end fixtures
     (tests/test_phase7a_pr12_e2e_crown_runtime.py:98-239): a residual CNN block with a projection skip

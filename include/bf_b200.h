@@ -532,6 +532,34 @@ int bf_beta_adam_step(float* beta, float* m, float* v, float* gsum, const int8_t
                       const int* improve, float* best_beta, float* add, int t, float lr, int spec_reduce, int S,
                       int do_update, int B, int n, bf_stream_t stream);
 
+/* The remaining pieces, for the other objectives and the shared-parameter mode on such graphs:
+ *   bf_alpha_select_best_paired  cur [B,2S] holds the lower bounds of S spec rows followed by those of their negations
+ *                         (upper[b,s] = -cur[b,S+s]); per-domain objective BF_OBJECTIVE_GAP = -reduce_s(upper - lower) or
+ *                         BF_OBJECTIVE_BOTH = lb_weight * reduce_s(lower) - ub_weight * reduce_s(upper) with reduce = mean |
+ *                         min (max on the upper side) | softmin (alpha_beta_crown.py:787-818), strict best-of as above;
+ *                         row_weight [B,2S] or NULL receives d objective / d cur (all >= 0 for weights >= 0).
+ *   bf_rows_scale         A[r,:] *= w[r] for M rows of n: the row weights applied to the coefficients kept at every ReLU
+ *                         before the gradient sweep.
+ *   bf_shared_metric      whole-batch metric mean(values[0..M)) with strict best-of against best_metric[0]; improve[0]
+ *                         (alpha_crown.py:215-220; first != 0 initialises).
+ *   bf_copy_if            dst = src when flag[0] != 0 (the batch's best bounds).
+ *   bf_shared_adam_step   Adam step t on ONE parameter row [n] shared by the batch: gradient = grad_scale * sum_b grad[b,j]
+ *                         (times -split[b,j] when `split` is given: a shared beta), grad cleared; alpha projected to [0,1],
+ *                         beta (is_beta != 0) to >= 0; best receives the parameter BEFORE the step when improve[0] != 0;
+ *                         scratch holds bf_shared_adam_scratch_floats(B, n) floats; do_update == 0 only snapshots.
+ *   bf_shared_beta_add    add[b,j] = -beta[j] * split[b,j]: the split term of a shared beta for the next sweep. */
+int bf_alpha_select_best_paired(const float* cur, float* best_rows, float* best_metric, int* improve, int first, int objective,
+                                int spec_reduce, float soft_tau, float lb_weight, float ub_weight, float* row_weight, int B,
+                                int S, bf_stream_t stream);
+int bf_rows_scale(float* A, const float* w, long long M, int n, bf_stream_t stream);
+int bf_shared_metric(const float* values, long long M, float* best_metric, int* improve, int first, bf_stream_t stream);
+int bf_copy_if(const float* src, float* dst, long long n, const int* flag, bf_stream_t stream);
+size_t bf_shared_adam_scratch_floats(int B, int n);
+int bf_shared_adam_step(float* param, float* m, float* v, float* grad, const int8_t* split, int split_stride, float* scratch,
+                        const int* improve, float* best, int t, float lr, float grad_scale, int do_update, int is_beta, int B,
+                        int n, bf_stream_t stream);
+int bf_shared_beta_add(const float* beta, const int8_t* split, int split_stride, float* add, int B, int n, bf_stream_t stream);
+
 /* Branching hint: per domain the ReLU (chain order) and neuron with the widest gap u - l among
  * unstable neurons (l < 0 < u); earlier ReLUs and lower indices win ties; -1/-1 when none.
  *   replaces _branch_choices_from_relu_pre, boundflow/runtime/alpha_beta_crown.py:145-182.

@@ -174,42 +174,80 @@ def adaptive_alpha_init_graph(relu_pre) -> Dict[str, torch.Tensor]:
 
 def alpha_crown_graph(module: Any, lo, up, C, *, steps: int, lr: float, alpha0: Optional[Mapping[str, torch.Tensor]] = None,
                       alpha_init: float = 0.5, splits: Optional[Mapping[str, torch.Tensor]] = None, optimize_beta: bool = False,
-                      input_name: str = "input"):
-    """Per-domain alpha (and beta) loop on a graph: `run_alpha_beta_crown_mlp(per_batch_params=True, objective="lower",
-    spec_reduce="mean")`, alpha_beta_crown.py:716-923.  Returns (best_lower, best_upper, best_alpha dict, best_beta dict)."""
+                      input_name: str = "input", objective: str = "lower", spec_reduce: str = "mean", soft_tau: float = 1.0,
+                      lb_weight: float = 1.0, ub_weight: float = 1.0, per_batch_params: bool = True):
+    """alpha (and beta) loop on a graph: `run_alpha_beta_crown_mlp`, alpha_beta_crown.py:716-923, with per-domain
+    parameters and best-of (`per_batch_params=True`) or one parameter row for the batch and a whole-batch best-of on
+    the mean of the per-domain objectives (False; `run_alpha_crown_mlp`, alpha_crown.py:137-261, is this mode without
+    beta).  Objectives lower | upper | gap | both (807-818), reductions mean | sum | min | softmin over the spec rows
+    (787-805; max / softmax on the upper side); beta enters the lower objective only (763-785).
+    Returns (best_lower, best_upper, best_alpha dict, best_beta dict)."""
     env, relu_pre = forward_ibp_graph(module, lo, up, input_name=input_name, splits=splits)
     B, dtype = lo.shape[0], lo.dtype
     names = list(relu_pre)
+    rows = B if per_batch_params else 1
+    use_beta = bool(optimize_beta and objective == "lower")
     alphas, betas, split_f = {}, {}, {}
     for x in names:
         n = relu_pre[x][0].reshape(B, -1).shape[1]
-        a = alpha0[x].reshape(-1, n).expand(B, n).to(dtype).clone() if alpha0 is not None and x in alpha0 else torch.full((B, n), float(alpha_init), dtype=dtype)
+        a = (alpha0[x].reshape(-1, n).expand(rows, n).to(dtype).clone() if alpha0 is not None and x in alpha0
+             else torch.full((rows, n), float(alpha_init), dtype=dtype))
         alphas[x] = a.requires_grad_(True)
-        if optimize_beta:
-            betas[x] = torch.zeros(B, n, dtype=dtype, requires_grad=True)
+        if use_beta:
+            betas[x] = torch.zeros(rows, n, dtype=dtype, requires_grad=True)
             sp = splits.get(x) if splits is not None else None
             split_f[x] = None if sp is None else sp.reshape(-1, n).expand(B, n).to(dtype)
     opt = torch.optim.Adam(list(alphas.values()) + list(betas.values()), lr=float(lr))
+
+    def reduce(x, direction):
+        if spec_reduce == "mean":
+            return x.mean(dim=1)
+        if spec_reduce == "sum":
+            return x.sum(dim=1)
+        if spec_reduce == "min":
+            return x.min(dim=1).values if direction == "min" else x.max(dim=1).values
+        if spec_reduce == "softmin":
+            tau = float(soft_tau)
+            return -tau * torch.logsumexp(-x / tau, dim=1) if direction == "min" else tau * torch.logsumexp(x / tau, dim=1)
+        raise ValueError(spec_reduce)
+
     best = None
     for step in range(int(steps) + 1):
         add_l = None
-        if optimize_beta:
+        if use_beta:
             add_l = {x: (-betas[x] * split_f[x]) for x in names if split_f[x] is not None}
-        lower, upper = crown_backward_graph(module, env, relu_pre, C, lo, up, input_name=input_name, alpha=alphas, add_l=add_l)
-        metric_b = lower.mean(dim=1)
-        if best is None:
-            best = [metric_b.detach().clone(), lower.detach().clone(), upper.detach().clone(), {x: a.detach().clone() for x, a in alphas.items()},
-                    {x: b.detach().clone() for x, b in betas.items()}]
+        a_rows = {x: a.expand(B, -1) for x, a in alphas.items()}
+        lower, upper = crown_backward_graph(module, env, relu_pre, C, lo, up, input_name=input_name, alpha=a_rows, add_l=add_l)
+        if objective == "lower":
+            metric_b = reduce(lower, "min")
+        elif objective == "upper":
+            metric_b = -reduce(upper, "max")
+        elif objective == "gap":
+            metric_b = -reduce(upper - lower, "max")
+        elif objective == "both":
+            metric_b = float(lb_weight) * reduce(lower, "min") - float(ub_weight) * reduce(upper, "max")
         else:
-            imp = metric_b.detach() > best[0]
-            best[0] = torch.where(imp, metric_b.detach(), best[0])
-            best[1] = torch.where(imp.unsqueeze(1), lower.detach(), best[1])
-            best[2] = torch.where(imp.unsqueeze(1), upper.detach(), best[2])
-            best[3] = {x: torch.where(imp.unsqueeze(1), a.detach(), best[3][x]) for x, a in alphas.items()}
-            best[4] = {x: torch.where(imp.unsqueeze(1), b.detach(), best[4][x]) for x, b in betas.items()}
+            raise ValueError(objective)
+        snap = lambda d: {x: t.detach().clone() for x, t in d.items()}  # noqa: E731
+        if per_batch_params:
+            m = metric_b.detach()
+            if best is None:
+                best = [m.clone(), lower.detach().clone(), upper.detach().clone(), snap(alphas), snap(betas)]
+            else:
+                imp = m > best[0]
+                best[0] = torch.where(imp, m, best[0])
+                best[1] = torch.where(imp.unsqueeze(1), lower.detach(), best[1])
+                best[2] = torch.where(imp.unsqueeze(1), upper.detach(), best[2])
+                best[3] = {x: torch.where(imp.unsqueeze(1), a.detach(), best[3][x]) for x, a in alphas.items()}
+                best[4] = {x: torch.where(imp.unsqueeze(1), b.detach(), best[4][x]) for x, b in betas.items()}
+            loss = -metric_b.sum()
+        else:
+            metric = metric_b.mean()
+            if best is None or float(metric.detach()) > best[0]:
+                best = [float(metric.detach()), lower.detach().clone(), upper.detach().clone(), snap(alphas), snap(betas)]
+            loss = -metric
         if step == int(steps):
             break
-        loss = -metric_b.sum()
         if not loss.requires_grad:
             break
         opt.zero_grad(set_to_none=True)

@@ -293,6 +293,31 @@ def gen_conv_certificate() -> None:
     save("conv_certificate.npz", **out)
 
 
+def gen_graph_certificate() -> None:
+    """`_is_infeasible_split_first_layer_convex_combo` on the two-branch graphs of workloads.make_graph_certificate_cases
+    (half-spaces from two ReLUs that both sit on the input value; Linear and Conv2d branches)."""
+    from boundflow.runtime.alpha_beta_crown import _is_infeasible_split_first_layer_convex_combo
+
+    out = {}
+    for kind in ("linear", "conv"):
+        module, _x, lo, up, cases = W.make_graph_certificate_cases(kind)
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        shape = {"ha": (1, 6) if kind == "linear" else (1, 6, 1, 1), "hb": (1, 2) if kind == "linear" else (1, 2, 1, 1)}
+        flags, values = [], []
+        for _name, rows in cases:
+            bad, _reason, cert = _is_infeasible_split_first_layer_convex_combo(m, spec, relu_split_state={k: v.reshape(shape[k]) for k, v in rows.items()})
+            flags.append(bool(bad))
+            values.append(float(cert["max_value"]) if cert is not None else np.nan)
+        out[f"{kind}_names"] = np.array([n for n, _ in cases])
+        out[f"{kind}_infeasible"] = np.array(flags)
+        out[f"{kind}_max_value"] = np.array(values)
+    save("graph_certificate.npz", **out)
+
+
 def gen_relu_influence() -> None:
     """`run_crown_ibp_mlp_with_relu_influence_from_forward_trace` on the MLP c1 (8 inputs) and the CNN c2 (3 inputs)."""
     from boundflow.runtime.crown_ibp import run_crown_ibp_mlp_with_relu_influence_from_forward_trace
@@ -371,6 +396,53 @@ def gen_graph_alpha() -> None:
         for x, v in bt.beta_by_relu_input.items():
             out[f"{name}_beta_{x}_3"] = v.reshape(B, -1)
     save("graph_alpha.npz", **out)
+
+
+GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
+GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
+
+
+def gen_graph_objectives() -> None:
+    """The reference on the non-chain graphs of workloads.make_graph_cases beyond the per-domain lower / mean loop:
+    per-domain parameters with the other objectives and reductions (adaptive start; 1 and 4 steps; lb_weight 1.0,
+    ub_weight 0.5; tau 3.0), the shared-parameter mode (`per_batch_params=False`, start 0.5, 4 steps) for four
+    objective x reduction pairs, the shared-parameter function `run_alpha_crown_mlp` (lower / mean, 4 steps), and
+    shared alpha + beta with the split assignments stored in graph_alpha.npz (3 steps)."""
+    from boundflow.runtime.alpha_crown import run_alpha_crown_mlp
+
+    prev = np.load(os.path.join(HERE, "graph_alpha.npz"))
+    out = {"tau": np.array(3.0)}
+    kw = {"soft_tau": 3.0, "lb_weight": 1.0, "ub_weight": 0.5}
+    for name, (module, _x, lo, up, C) in W.make_graph_cases().items():
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        a0 = adaptive_alpha(relu_pre)
+        B = int(lo.shape[0])
+        for obj, red in GRAPH_OBJECTIVE_CASES:
+            for steps in (1, 4):
+                b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, steps=steps, lr=0.1, per_batch_params=True, objective=obj,
+                                                       spec_reduce=red, warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                       **kw)
+                out[f"{name}_{obj}_{red}_lower_{steps}"], out[f"{name}_{obj}_{red}_upper_{steps}"] = b.lower, b.upper
+        for obj, red in GRAPH_SHARED_CASES:
+            b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, steps=4, lr=0.1, per_batch_params=False, objective=obj, spec_reduce=red, **kw)
+            out[f"{name}_shared_{obj}_{red}_lower_4"], out[f"{name}_shared_{obj}_{red}_upper_4"] = b.lower, b.upper
+        b, st, _ = run_alpha_crown_mlp(m, spec, linear_spec_C=C, steps=4, lr=0.1)
+        out[f"{name}_alpha_crown_lower_4"], out[f"{name}_alpha_crown_upper_4"] = b.lower, b.upper
+        for x, v in st.alpha_by_relu_input.items():
+            out[f"{name}_alpha_crown_alpha_{x}"] = v.reshape(-1)
+        if f"{name}_split_infeasible" in prev.files:
+            continue
+        splits = {x: torch.from_numpy(prev[f"{name}_split_{x}"]).to(torch.int8).reshape(relu_pre[x].lower.shape) for x in relu_pre}
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=False)
+        out[f"{name}_shared_beta_lower_3"], out[f"{name}_shared_beta_upper_3"] = b.lower, b.upper
+        for x, v in bt.beta_by_relu_input.items():
+            out[f"{name}_shared_beta_{x}_3"] = v.reshape(-1)
+    save("graph_objectives.npz", **out)
 
 
 def gen_lp_alpha() -> None:
@@ -741,7 +813,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "adam_divergence": gen_adam_divergence, "spec_reduce": gen_spec_reduce,
               "objectives": gen_objectives, "conv_beta": gen_conv_beta,
               "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha,
-              "shared_objectives": gen_shared_objectives}
+              "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
+              "graph_certificate": gen_graph_certificate}
 
 
 def main() -> None:

@@ -111,3 +111,50 @@ def test_conv_first_layer_cases_match_reference_golden_and_oracle(dev, golden):
     bounds, _a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["feasible_pair"].reshape(1, 4, 6, 6).to(dev)},
                                                     steps=2, lr=0.1, per_batch_params=True)
     assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 5)
+
+
+@pytest.mark.parametrize("kind", ["linear", "conv"])
+def test_two_input_branches_of_a_graph_match_reference_golden_and_oracle(dev, golden, kind):
+    """A graph that is not a chain: two ReLUs sit on ops that read the input value, and a contradiction may span both
+    (tests/golden/graph_certificate.npz).  All cases as one batch of domains, then the single-node pre-check."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import first_layer_certificate, needs_graph_path, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    g = golden("graph_certificate.npz")
+    module, _x, lo, up, cases = W.make_graph_certificate_cases(kind)
+    assert needs_graph_path(module)
+    D = len(cases)
+    rep = (D,) + (-1,) * (lo.dim() - 1)
+    spec = InputSpec.box(value_name="input", lower=lo.expand(*rep).contiguous().to(dev), upper=up.expand(*rep).contiguous().to(dev))
+    tail = () if kind == "linear" else (1, 1)
+    split = {k: torch.stack([rows[k] for _n, rows in cases]).reshape((D, -1) + tail).to(dev) for k in ("ha", "hb")}
+    flags, best, count = first_layer_certificate(module, spec, split)
+    flags, best, count = flags.cpu(), best.cpu(), count.cpu()
+    P = module.bindings["params"]
+    Wd, bd = torch.cat([P["Wa"].reshape(6, -1), P["Wb"].reshape(2, -1)]), torch.cat([P["ba"], P["bb"]])
+    inp = O.box_input(lo.reshape(1, -1), up.reshape(1, -1))
+    for k, (name, rows) in enumerate(cases):
+        row = torch.cat([rows["ha"], rows["hb"]])
+        assert int(count[k]) == int((row != 0).sum()), name
+        assert int(flags[k]) == int(bool(g[f"{kind}_infeasible"][k])), name
+        o_bad, o_best = O.first_layer_certificate(Wd, bd, inp, row)
+        assert bool(flags[k]) == o_bad, name
+        if o_best is not None:
+            assert abs(float(best[k]) - o_best) <= 0.25 * abs(o_best) + 1e-4, (name, float(best[k]), o_best)
+    # one split row shared by the batch on one branch, per-domain rows on the other
+    mixed = {"ha": dict(cases)["cross_branch_contradiction_needs_steps"]["ha"].to(dev), "hb": split["hb"]}
+    flags2, _b, _c = first_layer_certificate(module, spec, mixed)
+    want = [int(bool((rows["hb"] == 1).any())) for _n, rows in cases]   # ha[0] active contradicts either neuron of hb being active
+    assert flags2.cpu().tolist() == want
+    # the single-node pre-check of the alpha-beta function on a graph
+    case = dict(cases)
+    spec1 = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    one = lambda rows: {k: v.reshape((1, -1) + tail).to(dev) for k, v in rows.items()}  # noqa: E731
+    bounds, a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state=one(case["cross_branch_contradiction_uniform_weights"]), steps=2,
+                                                   lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "infeasible" and tuple(bounds.lower.shape) == (1, 1) and not a.alpha_by_relu_input
+    bounds, a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state=one(case["cross_branch_feasible"]), steps=2, lr=0.1,
+                                                   per_batch_params=True)
+    assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 3)

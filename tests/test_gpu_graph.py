@@ -46,10 +46,16 @@ def test_chain_modules_keep_the_fused_path_and_unsupported_modes_are_refused(dev
     assert not needs_graph_path(W.make_workload("c2", batch=1).module)
     module, _x, lo, up, C = W.make_graph_cases()["fanout_mlp"]
     spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
-    with pytest.raises(NotImplementedError):   # shared parameters on a graph
-        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=False)
-    with pytest.raises(NotImplementedError):
-        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="gap")
+    with pytest.raises(ValueError):
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="tightest")
+    with pytest.raises(ValueError):            # sum goes with the per-domain lower objective only
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="gap", spec_reduce="sum")
+    with pytest.raises(NotImplementedError):   # a negative weight would flip the sign decisions of the gradient sweep
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="both", ub_weight=-1.0)
+    split = {"h": torch.zeros(5, 24, dtype=torch.int8, device=dev)}
+    split["h"][:, 0] = 1
+    with pytest.raises(NotImplementedError):   # min / softmin with beta parameters
+        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), relu_split_state=split, steps=1, lr=0.1, per_batch_params=True, spec_reduce="min")
 
 
 @pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"])
@@ -100,6 +106,57 @@ def test_graph_alpha_and_alpha_beta_match_reference_golden(dev, golden, name):
     ref_l, ref_u = GO.crown_backward_graph(module, env, pre, Cb, lo, up, alpha=alpha, add_l=add)
     assert_close(got.lower.reshape(B, -1), ref_l, "CROWN lower with split, alpha and add term")
     assert_close(got.upper.reshape(B, -1), ref_u, "CROWN upper with split, alpha and add term")
+
+
+GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
+GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
+
+
+@pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"])
+def test_graph_objectives_and_shared_mode_match_reference_golden(dev, golden, name):
+    """On graphs that are not chains: the upper / gap / both objectives and the min / softmin reductions with per-domain
+    parameters, the shared-parameter mode of `run_alpha_beta_crown_mlp` (with and without beta) and `run_alpha_crown_mlp`,
+    against the reference's outputs (tests/golden/graph_objectives.npz; lb_weight 1.0, ub_weight 0.5)."""
+    import numpy as np
+
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, run_alpha_beta_crown_mlp, run_alpha_crown_mlp
+    from boundflow_b200.dag import forward_ibp_dag
+    from boundflow_b200.ir import InputSpec
+
+    g, ga = golden("graph_objectives.npz"), golden("graph_alpha.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    Cd = None if C is None else C.to(dev)
+    tr = forward_ibp_dag(module, spec)
+    a0 = {x: ((tr.pre_l[x] >= 0) | ((tr.pre_l[x] < 0) & (tr.pre_u[x] > 0) & (tr.pre_u[x] > -tr.pre_l[x]))).float() for x in tr.pre_l}
+    kw = {"soft_tau": float(g["tau"]), "lb_weight": 1.0, "ub_weight": 0.5}
+    for obj, red in GRAPH_OBJECTIVE_CASES:
+        for steps in (1, 4):
+            b, a, _bt, stats = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=steps, lr=0.1, per_batch_params=True, objective=obj,
+                                                       spec_reduce=red, warm_start_alpha=AlphaState(dict(a0)), **kw)
+            assert stats.objective == obj and stats.spec_reduce == red
+            assert_close(b.lower.reshape(B, -1), g[f"{name}_{obj}_{red}_lower_{steps}"].reshape(B, -1), f"{obj}/{red} lower after {steps}")
+            assert_close(b.upper.reshape(B, -1), g[f"{name}_{obj}_{red}_upper_{steps}"].reshape(B, -1), f"{obj}/{red} upper after {steps}")
+    for obj, red in GRAPH_SHARED_CASES:
+        b, a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=4, lr=0.1, per_batch_params=False, objective=obj, spec_reduce=red, **kw)
+        assert_close(b.lower.reshape(B, -1), g[f"{name}_shared_{obj}_{red}_lower_4"].reshape(B, -1), f"shared {obj}/{red} lower")
+        assert_close(b.upper.reshape(B, -1), g[f"{name}_shared_{obj}_{red}_upper_4"].reshape(B, -1), f"shared {obj}/{red} upper")
+        for x, v in a.alpha_by_relu_input.items():   # the ReLU input's shape without the batch axis
+            assert tuple(v.shape) == tuple(tr.shape[x])
+    b, st, stats = run_alpha_crown_mlp(module, spec, linear_spec_C=Cd, steps=4, lr=0.1)
+    assert_close(b.lower.reshape(B, -1), g[f"{name}_alpha_crown_lower_4"].reshape(B, -1), "run_alpha_crown_mlp lower")
+    assert_close(b.upper.reshape(B, -1), g[f"{name}_alpha_crown_upper_4"].reshape(B, -1), "run_alpha_crown_mlp upper")
+    for x, v in st.alpha_by_relu_input.items():
+        assert_close(v.reshape(-1), g[f"{name}_alpha_crown_alpha_{x}"], f"shared alpha {x}", atol=1e-5)
+    if f"{name}_shared_beta_lower_3" in g:
+        splits = {x: torch.from_numpy(np.asarray(ga[f"{name}_split_{x}"])).to(torch.int8).to(dev) for x in tr.pre_l}
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=False)
+        assert_close(b.lower.reshape(B, -1), g[f"{name}_shared_beta_lower_3"].reshape(B, -1), "shared alpha-beta lower after 3")
+        assert_close(b.upper.reshape(B, -1), g[f"{name}_shared_beta_upper_3"].reshape(B, -1), "shared alpha-beta upper after 3")
+        for x in tr.pre_l:
+            assert_close(bt.beta_by_relu_input[x].reshape(-1), g[f"{name}_shared_beta_{x}_3"], f"shared beta {x} after 3", atol=1e-5)
 
 
 def test_building_blocks_against_torch(dev):

@@ -420,6 +420,25 @@ def test_first_layer_certificate_over_a_conv_first_layer(golden):
             assert best < -1e-6 and abs(best - float(g["max_value"][k])) <= 0.5 * abs(float(g["max_value"][k])) + 1e-3, name
 
 
+@pytest.mark.parametrize("kind", ["linear", "conv"])
+def test_first_layer_certificate_over_two_input_branches(golden, kind):
+    """Half-spaces collected from two ReLUs that both sit on the input value (alpha_beta_crown.py:264-387): the oracle's
+    certificate on the stacked rows of both branches against the reference (graph_certificate.npz)."""
+    g = golden("graph_certificate.npz")
+    module, _x, lo, up, cases = W.make_graph_certificate_cases(kind)
+    assert [n for n, _ in cases] == [str(n) for n in g[f"{kind}_names"]]
+    P = module.bindings["params"]
+    Wd = torch.cat([P["Wa"].reshape(6, -1), P["Wb"].reshape(2, -1)])
+    bd = torch.cat([P["ba"], P["bb"]])
+    inp = O.box_input(lo.reshape(1, -1), up.reshape(1, -1))
+    for k, (name, rows) in enumerate(cases):
+        bad, best = O.first_layer_certificate(Wd, bd, inp, torch.cat([rows["ha"], rows["hb"]]))
+        assert bad == bool(g[f"{kind}_infeasible"][k]), name
+        if bad:
+            ref = float(g[f"{kind}_max_value"][k])
+            assert best < -1e-6 and abs(best - ref) <= 0.5 * abs(ref) + 1e-3, name
+
+
 GRAPH_NAMES = ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"]
 
 
@@ -456,6 +475,48 @@ def test_graph_oracle_crown_and_alpha_beta(golden, name):
     assert_close(up_b, ga[f"{name}_beta_upper_3"].reshape(B, -1), "alpha-beta upper after 3")
     for x, b in beta.items():
         assert_close(b, ga[f"{name}_beta_{x}_3"], f"beta {x} after 3", atol=1e-5)
+
+
+GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
+GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
+
+
+@pytest.mark.parametrize("name", GRAPH_NAMES)
+def test_graph_oracle_objectives_and_shared_mode(golden, name):
+    """oracle/graph_oracle.py against the reference on the non-chain graphs (graph_objectives.npz): the other
+    objectives and reductions with per-domain parameters, the shared-parameter mode, and shared alpha + beta."""
+    from oracle import graph_oracle as GO
+
+    g, ga = golden("graph_objectives.npz"), golden("graph_alpha.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = lo.shape[0]
+    env, relu_pre = GO.forward_ibp_graph(module, lo, up)
+    n_out = env["out"][0].reshape(B, -1).shape[1]
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+    a0 = GO.adaptive_alpha_init_graph(relu_pre)
+    kw = {"soft_tau": float(g["tau"]), "lb_weight": 1.0, "ub_weight": 0.5}
+    for obj, red in GRAPH_OBJECTIVE_CASES:
+        for steps in (1, 4):
+            lo_a, up_a, _a, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=steps, lr=0.1, alpha0=a0, objective=obj, spec_reduce=red, **kw)
+            assert_close(lo_a, g[f"{name}_{obj}_{red}_lower_{steps}"].reshape(B, -1), f"{obj}/{red} lower after {steps}")
+            assert_close(up_a, g[f"{name}_{obj}_{red}_upper_{steps}"].reshape(B, -1), f"{obj}/{red} upper after {steps}")
+    for obj, red in GRAPH_SHARED_CASES:
+        lo_a, up_a, _a, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=4, lr=0.1, objective=obj, spec_reduce=red, per_batch_params=False, **kw)
+        assert_close(lo_a, g[f"{name}_shared_{obj}_{red}_lower_4"].reshape(B, -1), f"shared {obj}/{red} lower")
+        assert_close(up_a, g[f"{name}_shared_{obj}_{red}_upper_4"].reshape(B, -1), f"shared {obj}/{red} upper")
+    # `run_alpha_crown_mlp` is the shared mode with lower / mean
+    lo_a, up_a, al, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=4, lr=0.1, per_batch_params=False)
+    assert_close(lo_a, g[f"{name}_alpha_crown_lower_4"].reshape(B, -1), "run_alpha_crown_mlp lower")
+    assert_close(up_a, g[f"{name}_alpha_crown_upper_4"].reshape(B, -1), "run_alpha_crown_mlp upper")
+    for x, a in al.items():
+        assert_close(a.reshape(-1), g[f"{name}_alpha_crown_alpha_{x}"], f"shared alpha {x}", atol=1e-5)
+    if f"{name}_shared_beta_lower_3" in g:
+        splits = {x: torch.from_numpy(np.asarray(ga[f"{name}_split_{x}"])).to(torch.int8) for x in relu_pre}
+        lo_b, up_b, _a, beta = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, splits=splits, optimize_beta=True, per_batch_params=False)
+        assert_close(lo_b, g[f"{name}_shared_beta_lower_3"].reshape(B, -1), "shared alpha-beta lower after 3")
+        assert_close(up_b, g[f"{name}_shared_beta_upper_3"].reshape(B, -1), "shared alpha-beta upper after 3")
+        for x, b in beta.items():
+            assert_close(b.reshape(-1), g[f"{name}_shared_beta_{x}_3"], f"shared beta {x} after 3", atol=1e-5)
 
 
 SHARED_OBJECTIVE_CASES = (("lower", "min"), ("lower", "softmin"), ("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("both", "mean"))
