@@ -94,7 +94,7 @@ SIGNATURES = {
     "bf_rows_add_broadcast": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "bf_adjoint_start_box": (_i, [_p, _p, _p, _i, _i, _i, _p]),
     "bf_rows_conv2d_fwd": (_i, [_p, _p, _p, _p] + [_i] * 13 + [_p]),
-    "bf_relu_adjoint_rows": (_i, [_p] * 9 + [_i, _i, _i, _p]),
+    "bf_relu_adjoint_rows": (_i, [_p] * 10 + [_i, _i, _i, _p]),
     "bf_alpha_select_best": (_i, [_p, _p, _p, _p, _i, _i, _f, _p, _i, _i, _p]),
     "bf_alpha_adam_step": (_i, [_p] * 9 + [_i, _f, _i, _i, _i, _i, _i, _p]),
     "bf_beta_adam_step": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _f, _i, _i, _i, _i, _i, _p]),
@@ -110,6 +110,7 @@ SIGNATURES = {
     "bf_chain_alpha_grad": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _i, _p, _sz, _i, _i, _p]),
     "bf_chain_alpha_shared_workspace_bytes": (_sz, [_p, _i, _i, _i]),
     "bf_chain_alpha_crown_shared": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _p, _sz, _i, _i, _p]),
+    "bf_chain_alpha_beta_crown_shared_reduce": (_i, [_p] * 12 + [_i, _f, _p, _p, _p, _i, _f, _i, _f, _p, _sz, _i, _i, _p]),
 }
 
 _lib: Optional[C.CDLL] = None

@@ -522,8 +522,6 @@ def alpha_crown_from_trace(
         raise ValueError(f"spec_reduce={spec_reduce!r}: expected mean | sum | min | softmin")
     if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
         raise ValueError(f"soft_tau must be >0, got {soft_tau}")
-    if spec_reduce in ("min", "softmin") and beta_splits is not None:
-        raise NotImplementedError("the CUDA backend combines the min / softmin spec reductions with alpha only (no beta parameters)")
     n_out = 1
     for d in chain.output_shape:
         n_out *= int(d)
@@ -566,12 +564,12 @@ def alpha_crown_from_trace(
     nbytes = int(chain.lib.bf_chain_alpha_beta_workspace_bytes(chain.handle, B, S))
     ws = _Workspace.get(device, nbytes)
     _lib.check(
-        chain.lib.bf_chain_alpha_beta_crown(
+        chain.lib.bf_chain_alpha_beta_crown_reduce(
             chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
             _lib.ptr_array(alpha), _lib.ptr_array(best_alpha), _lib.ptr_array(beta), _lib.ptr_array(best_beta),
             _lib.ptr_array(splits), _lib.int_array(strides), _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
             _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
-            int(steps), float(lr), reduce_code, _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+            int(steps), float(lr), reduce_code, float(soft_tau), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
     )
     return best_lower, best_upper, best_alpha, alpha, best_metric, best_beta
@@ -693,16 +691,18 @@ def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[t
     """Device-resident loop with ONE alpha (and, with `beta_splits`, one beta) per neuron for the
     whole batch; returns (best_lower, best_upper|None, best_alpha list [n_r], last alpha list,
     best_metric [1]) and, with beta, a sixth element best_beta list [n_r].  `objective` lower | upper | gap | both
-    and `spec_reduce` mean | min | softmin as in run_alpha_crown_mlp (alpha_crown.py:93-134); anything but
-    lower / mean runs alpha only."""
+    and `spec_reduce` mean | min | softmin as in run_alpha_crown_mlp (alpha_crown.py:93-134); beta enters the
+    lower objective only (any reduction)."""
     chain, B, device = trace.chain, trace.B, trace.mid.device
     if objective not in ("lower", "upper", "gap", "both"):
         raise ValueError(f"objective={objective!r}: expected lower | upper | gap | both")
     if spec_reduce not in ("mean", "min", "softmin"):
         raise ValueError(f"spec_reduce={spec_reduce!r}: the shared-parameter loop takes mean | min | softmin")
-    if objective != "lower" or spec_reduce != "mean":
+    if spec_reduce == "softmin" and float(soft_tau) <= 0.0:
+        raise ValueError(f"soft_tau must be >0, got {soft_tau}")
+    if objective != "lower" or (spec_reduce != "mean" and beta_splits is None):
         if beta_splits is not None:
-            raise NotImplementedError("the CUDA backend combines beta parameters with objective='lower', spec_reduce='mean' in the shared-parameter loop")
+            raise NotImplementedError("the beta term enters objective='lower' only (alpha_beta_crown.py:763-785)")
         return _shared_alpha_other(trace, linear_spec_C, alpha0, steps=steps, lr=lr, objective=objective, spec_reduce=spec_reduce,
                                    soft_tau=soft_tau, lb_weight=lb_weight, ub_weight=ub_weight)
     n_out = 1
@@ -736,15 +736,16 @@ def shared_alpha_crown_from_trace(trace: ForwardTrace, linear_spec_C: Optional[t
         best_beta = [b.clone() for b in beta]
     nbytes = int(chain.lib.bf_chain_alpha_shared_workspace_bytes(chain.handle, B, S, 1 if with_beta else 0))
     ws = _Workspace.get(device, nbytes)
+    codes = {"mean": _lib.REDUCE_MEAN, "min": _lib.REDUCE_MIN, "softmin": _lib.REDUCE_SOFTMIN}
     _lib.check(
-        chain.lib.bf_chain_alpha_crown_shared(
+        chain.lib.bf_chain_alpha_beta_crown_shared_reduce(
             chain.handle, _lib.ptr(C), _lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u),
             _lib.ptr_array(alpha), _lib.ptr_array(best_alpha),
             _lib.ptr_array(beta) if with_beta else None, _lib.ptr_array(best_beta) if with_beta else None,
             _lib.ptr_array(splits) if with_beta else None, _lib.int_array(strides) if with_beta else None,
             _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
             _lib.ptr(best_lower), _lib.ptr(best_upper), _lib.ptr(best_metric),
-            int(steps), float(lr), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
+            int(steps), float(lr), codes[spec_reduce], float(soft_tau), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
     )
     if with_beta:
@@ -914,9 +915,8 @@ def run_alpha_beta_crown_mlp(
     default) optimises one alpha / beta row shared by the whole batch with a whole-batch
     best-of.  Per-domain mode: objective lower | upper | gap | both (lb_weight / ub_weight >= 0) and
     spec_reduce mean | min | softmin (with `soft_tau`) as in the reference, plus "sum" for the lower
-    objective; min / softmin and the upper / gap / both objectives run alpha only (the reference applies the
-    beta term to objective="lower" alone, and its min / softmin with beta is not built here).  Shared mode:
-    the same objectives and mean | min | softmin, with beta for objective="lower", spec_reduce="mean".  For a single node the first-layer
+    objective; the upper / gap / both objectives run alpha only (the reference applies the beta term to
+    objective="lower" alone, with any reduction).  Shared mode: the same objectives and mean | min | softmin.  For a single node the first-layer
     infeasibility certificate (alpha_beta_crown.py:391-532) is evaluated first, as in the
     reference (`first_layer_certificate` gives it for whole batches).  Graphs that are not chains (residual add,
     concat, fan-out) take the same arguments through the per-value loop of `dag.alpha_beta_crown_dag`.

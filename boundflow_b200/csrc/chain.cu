@@ -286,18 +286,19 @@ int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos
 int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid,
                             const float* rad, const float* Ahat, const float* dpos, const float* dneg, const float* epos,
                             const float* eneg, const float* pre_l, const float* pre_u, float* hout, float* grad, float* gsum,
-                            int M, int S, cudaStream_t stream) {
+                            int M, int S, cudaStream_t stream, const float* gw) {
   const bf_layer_desc& L = c->layers[layer];
   const int K = L.n_in, N = L.n_out;
   const unsigned char* pk = tc_weights(c, layer, true, M, K, N);
-  if (pk && adjoint_feature_major(c, M, N))
+  // gw (row weights of the beta sums, min / softmin with beta parameters) is implemented by the row-major and FFMA kernels
+  if (pk && gw == nullptr && adjoint_feature_major(c, M, N))
     return launch_crown_adjoint_linear_tc_fm(Hprev, first_layer, mid, rad, c->pk_adj_fm[layer], L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
                                              hout, grad, gsum, M, S, K, N, c->status, stream);
   if (pk)
     return launch_crown_adjoint_linear_tc(Hprev, first_layer, mid, rad, pk, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u,
-                                          hout, grad, gsum, M, S, K, N, c->status, stream);
+                                          hout, grad, gsum, M, S, K, N, c->status, stream, gw);
   return launch_crown_adjoint_linear(Hprev, first_layer, mid, rad, L.W, L.bias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout,
-                                     grad, gsum, M, S, K, N, stream);
+                                     grad, gsum, M, S, K, N, stream, gw);
 }
 
 }  // namespace bf

@@ -139,9 +139,9 @@ static int alpha_sweep(const bf_chain* c, const AlphaWs& ws, const float* C, int
 }
 
 // Adjoint sweep: accumulates d(sum_s lower[b,s])/d(alpha_r[b,j]) into ws.grad[r] and, with beta,
-// sum_s g_r[b,s,j] into ws.gsum[r].
+// sum_s gw[b,s] * g_r[b,s,j] (gw null: weight 1) into ws.gsum[r].
 static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* const* pre_l, const float* const* pre_u,
-                         bool with_beta, const InputSetArg& in, int B, int S, cudaStream_t stream) {
+                         bool with_beta, const InputSetArg& in, int B, int S, cudaStream_t stream, const float* gw = nullptr) {
   const int M = B * S;
   const int R = (int)c->relu_layers.size();
   // the first Linear layer on a box forms h_0 = mid - sgn(A_0) * rad in its prologue; every other case writes the
@@ -162,13 +162,13 @@ static int alpha_adjoint(const bf_chain* c, const AlphaWs& ws, const float* cons
       const bool from_box = (r == 0) && h0_fused;
       rc = dispatch_adjoint(c, layer, hprev, from_box ? 1 : 0, from_box ? in.mid : nullptr, from_box ? in.rad : nullptr, ws.Ahat[r],
                             ws.sl[r], ws.au[r], nullptr, ws.bu[r], pre_l[r], pre_u[r], hout, ws.grad[r],
-                            with_beta ? ws.gsum[r] : nullptr, M, S, stream);
+                            with_beta ? ws.gsum[r] : nullptr, M, S, stream, with_beta ? gw : nullptr);
     } else {
       float* g = ws.H[r & 1];
       rc = launch_conv_forward_rows(hprev, L.W, L.bias, g, M, L, stream);
       if (rc != BF_OK) return rc;
       rc = launch_relu_adjoint_rows(g, ws.Ahat[r], ws.sl[r], ws.au[r], ws.bu[r], pre_l[r], pre_u[r], ws.grad[r],
-                                    with_beta ? ws.gsum[r] : nullptr, B, S, L.n_out, stream);
+                                    with_beta ? ws.gsum[r] : nullptr, B, S, L.n_out, stream, with_beta ? gw : nullptr);
     }
     if (rc != BF_OK) return rc;
   }
@@ -249,7 +249,7 @@ static int alpha_loop(const char* who, const bf_chain* chain, const float* C, co
   const bool weighted = paired || (spec_reduce == BF_REDUCE_MIN || spec_reduce == BF_REDUCE_SOFTMIN);
   BF_REQUIRE(!paired || (S % 2 == 0 && spec_reduce != BF_REDUCE_SUM && !best_upper), BF_E_INVALID,
              "%s: paired rows need an even row count, no separate upper output and a mean / min / softmin reduction", who);
-  BF_REQUIRE(!weighted || !with_beta, BF_E_UNSUPPORTED, "%s: min / softmin objectives are not combined with beta parameters", who);
+  BF_REQUIRE(!paired || !with_beta, BF_E_UNSUPPORTED, "%s: the gap / both objectives carry no beta term", who);
   BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "%s: soft_tau must be positive", who);
   BF_REQUIRE(!with_beta || (best_beta && splits), BF_E_INVALID, "%s: beta needs best_beta and the split assignment", who);
   cudaStream_t stream = bf::as_stream(stream_);
@@ -289,7 +289,7 @@ static int alpha_loop(const char* who, const bf_chain* chain, const float* C, co
           if (rc != BF_OK) return rc;
         }
       }
-      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream, weighted ? ws.row_weight : nullptr);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, paired ? BF_REDUCE_SUM : spec_reduce, S);  // row weights already carry 1/S of a paired mean
     }
@@ -469,7 +469,7 @@ static int shared_loop(const char* who, const bf_chain* chain, const float* C, c
              "%s: spec_reduce must be mean, min or softmin", who);
   BF_REQUIRE(spec_reduce != BF_REDUCE_SOFTMIN || soft_tau > 0.f, BF_E_INVALID, "%s: soft_tau must be positive", who);
   BF_REQUIRE(!paired || (S % 2 == 0 && !best_upper), BF_E_INVALID, "%s: paired rows need an even row count and no separate upper output", who);
-  BF_REQUIRE(!weighted || !with_beta, BF_E_UNSUPPORTED, "%s: min / softmin and the gap / both objectives are not combined with beta parameters", who);
+  BF_REQUIRE(!paired || !with_beta, BF_E_UNSUPPORTED, "%s: the gap / both objectives carry no beta term", who);
   bf::AlphaWs ws;
   bf::SharedWs sw;
   const size_t need = bf::shared_ws_layout(chain, B, S, with_beta, workspace, &ws, &sw);
@@ -523,7 +523,7 @@ static int shared_loop(const char* who, const bf_chain* chain, const float* C, c
         for (int r = 0; r < R; ++r)
           if ((rc = bf::launch_scale_rows(ws.Ahat[r], ws.row_weight, M, width(r), stream)) != BF_OK) return rc;
       }
-      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream);
+      rc = bf::alpha_adjoint(chain, ws, pre_l, pre_u, with_beta, in, B, S, stream, weighted ? ws.row_weight : nullptr);
       if (rc != BF_OK) return rc;
       sc = bf::adam_scalars(t, lr, BF_REDUCE_SUM, S);
       // loss = -mean over every domain and spec row; with row weights (which sum to the objective's weight per domain): -mean over domains
@@ -565,6 +565,18 @@ extern "C" int bf_chain_alpha_crown_shared(const bf_chain* chain, const float* C
   return shared_loop("bf_chain_alpha_crown_shared", chain, C, pre_l, pre_u, alpha, best_alpha, beta, best_beta, splits, split_strides,
                      mid, rad, norm_p, eps, best_lower, best_upper, best_metric, steps, lr, 0, 1.f, 1.f, BF_REDUCE_MEAN, 1.f, workspace,
                      workspace_bytes, B, S, stream);
+}
+
+extern "C" int bf_chain_alpha_beta_crown_shared_reduce(const bf_chain* chain, const float* C, const float* const* pre_l,
+                                                       const float* const* pre_u, float* const* alpha, float* const* best_alpha,
+                                                       float* const* beta, float* const* best_beta, const int8_t* const* splits,
+                                                       const int* split_strides, const float* mid, const float* rad, int norm_p,
+                                                       float eps, float* best_lower, float* best_upper, float* best_metric, int steps,
+                                                       float lr, int spec_reduce, float soft_tau, void* workspace,
+                                                       size_t workspace_bytes, int B, int S, bf_stream_t stream) {
+  return shared_loop("bf_chain_alpha_beta_crown_shared_reduce", chain, C, pre_l, pre_u, alpha, best_alpha, beta, best_beta, splits,
+                     split_strides, mid, rad, norm_p, eps, best_lower, best_upper, best_metric, steps, lr, 0, 1.f, 1.f, spec_reduce,
+                     soft_tau, workspace, workspace_bytes, B, S, stream);
 }
 
 extern "C" int bf_chain_alpha_crown_shared_objective(const bf_chain* chain, const float* C, const float* const* pre_l,
@@ -619,11 +631,13 @@ extern "C" int bf_rows_conv2d_fwd(const float* in, const float* W, const float* 
 }
 
 extern "C" int bf_relu_adjoint_rows(float* G, const float* Ahat, const float* alpha_u, const float* alpha_l, const float* beta_u,
-                                    const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
+                                    const float* pre_l, const float* pre_u, float* grad, float* gsum, const float* row_weight, int B,
+                                    int S, int n,
                                     bf_stream_t stream) {
   BF_REQUIRE(G && Ahat && alpha_u && alpha_l && pre_l && pre_u && grad, BF_E_INVALID, "bf_relu_adjoint_rows: null tensor");
   BF_REQUIRE(B > 0 && S > 0 && n > 0, BF_E_INVALID, "bf_relu_adjoint_rows: bad sizes");
-  return bf::launch_relu_adjoint_rows(G, Ahat, alpha_l, alpha_u, beta_u, pre_l, pre_u, grad, gsum, B, S, n, bf::as_stream(stream));
+  return bf::launch_relu_adjoint_rows(G, Ahat, alpha_l, alpha_u, beta_u, pre_l, pre_u, grad, gsum, B, S, n, bf::as_stream(stream),
+                                      gsum ? row_weight : nullptr);
 }
 
 extern "C" int bf_alpha_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first, int spec_reduce,

@@ -64,6 +64,6 @@ int dispatch_bwd(const bf_chain* c, int layer, const float* A, const float* dpos
 int dispatch_adjoint(const bf_chain* c, int layer, const float* Hprev, int first_layer, const float* mid, const float* rad,
                      const float* Ahat, const float* dpos, const float* dneg, const float* epos, const float* eneg,
                      const float* pre_l, const float* pre_u, float* hout, float* grad, float* gsum, int M, int S,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const float* gw = nullptr);
 
 }  // namespace bf

@@ -173,6 +173,7 @@ struct AdjEpilogue {
   float* hout;         // [M,N] or nullptr (last ReLU layer needs no adjoint point)
   float* grad;         // [D,N], accumulated with atomicAdd (at most two row tiles touch one entry when S <= the tile height: 32, 64 or 128)
   float* gsum;         // [D,N] or nullptr: sum over the domain's rows of g (beta gradient), same accumulation
+  const float* gw;     // [M] or nullptr: weight of each row in gsum (d objective / d row for min / softmin)
 };
 
 constexpr int STAGE_LD = BN + 1;
@@ -261,6 +262,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
           const int cc = n0 + cl + q;
           float gg = 0.f;
           if (row < g.M && cc < g.N) gg = acc[i][jb * 4 + q] + (e.nbias ? __ldg(e.nbias + cc) : 0.f);
+          if (e.gw != nullptr && row < g.M) gg *= __ldg(e.gw + row);
           dsmem[rl * STAGE_LD + cl + q] = gg;
         }
       }
@@ -279,7 +281,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) crown_adjoint_linear_kernel(G
 int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
-                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream) {
+                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream,
+                                const float* gw) {
   static SmemOptIn opt_in[6];
   GemmArgs g{};
   g.A = Hprev; g.Bm = W; g.M = M; g.N = N; g.K = K; g.S = S;
@@ -290,7 +293,7 @@ int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float
   g.vecN = (N % 4 == 0);
   for (const void* p : nptrs) if (p && (reinterpret_cast<uintptr_t>(p) & 15u)) g.vecN = 0;
   g.mid = mid; g.rad = rad;
-  AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum};
+  AdjEpilogue e{nbias, Ahat, dpos, dneg, epos, eneg, pre_l, pre_u, hout, grad, gsum, gw};
   // 32-row tiles only while a domain's S rows still touch at most two row tiles (two atomic addends commute: deterministic sums)
   const bool small = ffma_small_tiles(M, N), quarter = ffma_quarter_tiles(M, N) && S <= 32;
   dim3 grid(ceil_div(M, quarter ? 32 : (small ? 64 : BM)), ceil_div(N, small ? 64 : BN));

@@ -67,6 +67,7 @@ struct Params {
   const float* nbias; const float* Ahat; const float* e_dpos; const float* e_dneg; const float* e_epos; const float* e_eneg;
   const float* pre_l; const float* pre_u; float* hout; float* grad;
   float* gsum;               // [D,N] or null: per-domain sums of g (beta gradient)
+  const float* gw;           // [M] or null: weight of each row in gsum (d objective / d row for min / softmin)
   int* status;               // device word, set non-zero when a wait expired
 };
 
@@ -479,7 +480,7 @@ __global__ void __launch_bounds__(THREADS, 1) crown_tc_kernel(Params p) {
                 run = 0.f;
                 run_d = d;
               }
-              run += stg2[r * 33 + lane];
+              run = p.gw ? fmaf(__ldg(p.gw + row_base + r), stg2[r * 33 + lane], run) : run + stg2[r * 33 + lane];
             }
             if (run_d >= 0 && colj < p.N) atomicAdd(&p.gsum[(size_t)run_d * p.N + colj], run);
           }
@@ -740,7 +741,7 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
                                    const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
                                    const float* dneg, const float* epos, const float* eneg, const float* pre_l,
                                    const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
-                                   int* status, cudaStream_t stream) {
+                                   int* status, cudaStream_t stream, const float* gw) {
   tc::Params p{};
   int nt;
   tc_tile_shape(N, K, &p.BN, &nt, &p.nkb);
@@ -753,7 +754,7 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
   for (const void* q : nptrs) if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) p.vecN = 0;
   p.mid_k = mid; p.rad_k = rad;
   p.nbias = nbias; p.Ahat = Ahat; p.e_dpos = dpos; p.e_dneg = dneg; p.e_epos = epos; p.e_eneg = eneg;
-  p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad; p.gsum = gsum;
+  p.pre_l = pre_l; p.pre_u = pre_u; p.hout = hout; p.grad = grad; p.gsum = gsum; p.gw = gw;
   p.status = status;
   timing_begin(T_ADJ, stream);
   int rc = first_layer ? tc_launch<tc::MODE_ADJ, tc::PRO_H0>(p, nt, stream, "crown_tc_kernel<adjoint,h0>")

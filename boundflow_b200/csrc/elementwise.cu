@@ -462,13 +462,14 @@ int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStrea
 // ---- gradient sweep pieces for layers without a fused epilogue (conv) --------------------------------
 // Adjoint step of one ReLU on rows: g = layer output at the adjoint point (in), h = d*g + e (out, in place),
 // grad[b,j] += sum over the domain's rows of [unstable][Ahat >= 0] Ahat*g and, with beta parameters,
-// gsum[b,j] += sum over the domain's rows of g (the beta gradient is -split * gsum).  One thread per (domain, neuron),
+// gsum[b,j] += sum over the domain's rows of g, each row times gw[b*S+s] when gw is given (the beta gradient is
+// -split * gsum; gw carries d objective / d row for min / softmin).  One thread per (domain, neuron),
 // rows of the domain in order: no atomics.
 __global__ void __launch_bounds__(256) relu_adjoint_rows_kernel(float* __restrict__ G, const float* __restrict__ Ahat,
                                                                 const float* __restrict__ dpos, const float* __restrict__ dneg,
                                                                 const float* __restrict__ eneg, const float* __restrict__ pre_l,
                                                                 const float* __restrict__ pre_u, float* __restrict__ grad,
-                                                                float* __restrict__ gsum, int S, int n) {
+                                                                float* __restrict__ gsum, const float* __restrict__ gw, int S, int n) {
   const int b = blockIdx.x;
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   if (j >= n) return;
@@ -480,7 +481,7 @@ __global__ void __launch_bounds__(256) relu_adjoint_rows_kernel(float* __restric
     const size_t i = ((size_t)b * S + s) * n + j;
     const float a = Ahat[i], g = G[i];
     const bool sel = a >= 0.f;
-    gs += g;
+    gs = gw ? fmaf(gw[(size_t)b * S + s], g, gs) : gs + g;
     if (sel && amb) acc = fmaf(a, g, acc);
     G[i] = sel ? dp * g : fmaf(dn, g, en);
   }
@@ -490,9 +491,9 @@ __global__ void __launch_bounds__(256) relu_adjoint_rows_kernel(float* __restric
 
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
                              const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const float* gw) {
   dim3 grid(B, ceil_div(n, 256));
-  relu_adjoint_rows_kernel<<<grid, 256, 0, stream>>>(G, Ahat, dpos, dneg, eneg, pre_l, pre_u, grad, gsum, S, n);
+  relu_adjoint_rows_kernel<<<grid, 256, 0, stream>>>(G, Ahat, dpos, dneg, eneg, pre_l, pre_u, grad, gsum, gw, S, n);
   BF_CHECK_LAUNCH("relu_adjoint_rows_kernel");
   return BF_OK;
 }

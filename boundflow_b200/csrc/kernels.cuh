@@ -15,7 +15,8 @@ bool ffma_fits_one_wave(int M, int N);
 int launch_crown_adjoint_linear(const float* Hprev, int first_layer, const float* mid, const float* rad, const float* W,
                                 const float* nbias, const float* Ahat, const float* dpos, const float* dneg,
                                 const float* epos, const float* eneg, const float* pre_l, const float* pre_u,
-                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream);
+                                float* hout, float* grad, float* gsum, int M, int S, int K, int N, cudaStream_t stream,
+                                const float* gw = nullptr);
 
 // crown_tc.cu (tcgen05 3xTF32 path; weights pre-packed by tc_pack_weights)
 size_t tc_packed_bytes(int N, int K, int tile_rows = 0);
@@ -28,7 +29,7 @@ int launch_crown_adjoint_linear_tc(const float* Hprev, int first_layer, const fl
                                    const unsigned char* Wpk, const float* nbias, const float* Ahat, const float* dpos,
                                    const float* dneg, const float* epos, const float* eneg, const float* pre_l,
                                    const float* pre_u, float* hout, float* grad, float* gsum, int M, int S, int K, int N,
-                                   int* status, cudaStream_t stream);
+                                   int* status, cudaStream_t stream, const float* gw = nullptr);
 int crown_tc_partial_tiles(int N, int K);
 void tc_tile_shape(int N, int K, int* BN, int* ntiles, int* nkb);
 
@@ -89,7 +90,7 @@ int launch_scale_copy(const float* src, float scale, float* dst, long long n, cu
 int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStream_t stream);
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
                              const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const float* gw = nullptr);
 int launch_h0_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, cudaStream_t stream);
 // windowed coefficient rows of identity-row sweeps on conv layers (conv.cu)
 struct WindowGeom {

@@ -336,11 +336,13 @@ def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor
 
 
 def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], relax, A0: torch.Tensor, ahat: Dict[str, torch.Tensor],
-                     grad: Dict[str, torch.Tensor], gsum: Optional[Dict[str, torch.Tensor]], S: int) -> None:
+                     grad: Dict[str, torch.Tensor], gsum: Optional[Dict[str, torch.Tensor]], S: int,
+                     row_weight: Optional[torch.Tensor] = None) -> None:
     """Gradient sweep: the lower bound of row s equals C[s] . f_s(h0), where f_s is the network with every ReLU
     replaced by the line the backward sweep chose for that row and h0 = mid - sgn(A0) * rad.  Pushing h0 forward through
     the graph gives, at every ReLU input, the value g with d lower / d alpha = [l<0<u][Ahat>=0] Ahat * g and
-    d lower / d add = g (`bf_relu_adjoint_rows` accumulates both per domain)."""
+    d lower / d add = g (`bf_relu_adjoint_rows` accumulates both per domain; `row_weight` [B,S] weights the rows of the
+    second sum, the first one is weighted through `ahat`)."""
     device, B = tr.mid.device, tr.B
     task = module.get_entry_task()
     s = _stream_ptr(device)
@@ -384,7 +386,8 @@ def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Ten
             au, bu, al = relax[x]
             G = h[x].clone()                  # x may feed other ops as well
             _lib.check(lib.bf_relu_adjoint_rows(_lib.ptr(G), _lib.ptr(ahat[x]), _lib.ptr(au), _lib.ptr(al), _lib.ptr(bu), _lib.ptr(tr.pre_l[x]),
-                                                _lib.ptr(tr.pre_u[x]), _lib.ptr(grad[x]), _lib.ptr(gsum[x]) if gsum is not None else None, B, S, n, s))
+                                                _lib.ptr(tr.pre_u[x]), _lib.ptr(grad[x]), _lib.ptr(gsum[x]) if gsum is not None else None,
+                                                _lib.ptr(row_weight) if (gsum is not None and row_weight is not None) else None, B, S, n, s))
             h[out] = G
         elif t == "add":
             terms = [nm for nm in op.inputs if nm in h]
@@ -446,7 +449,7 @@ def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[t
     whole-batch best-of on the mean of the per-domain objectives.  `objective` lower | upper | gap | both (807-818):
     upper runs on the negated spec rows, gap / both on the rows followed by their negations (2S rows per domain, row
     weights from the objective's derivative scale the kept coefficients before the gradient sweep).  `spec_reduce`
-    mean | min | softmin (787-805), plus sum for lower.  beta enters objective="lower" with mean / sum only.
+    mean | min | softmin (787-805), plus sum for lower.  beta enters objective="lower" only (763-785).
     Returns (best_lower, best_upper, best_alpha dict, best_beta dict, trace); alpha / beta are [B, n] ([1, n] in the
     shared mode) per ReLU input name."""
     lib = _lib.load()
@@ -462,8 +465,6 @@ def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[t
         raise NotImplementedError("the CUDA backend takes non-negative lb_weight / ub_weight (a row weight must not flip the sign decisions of the gradient sweep)")
     weighted = paired or spec_reduce in ("min", "softmin")
     with_beta = bool(optimize_beta and relu_split_state and objective == "lower")
-    if with_beta and weighted:
-        raise NotImplementedError("the CUDA backend combines the min / softmin spec reductions with alpha only (no beta parameters)")
     spec = normalize_input_spec(input_spec)
     tr = forward_ibp_dag(module, spec, relu_split_state)
     if int(tr.infeasible.sum()) != 0:
@@ -560,7 +561,7 @@ def alpha_beta_crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[t
                     if A.data_ptr() not in done:
                         done.add(A.data_ptr())
                         _lib.check(lib.bf_rows_scale(_lib.ptr(A), _lib.ptr(row_weight), M, width[x], s))
-            _adjoint_forward(lib, module, tr, params, relax, A0, ahat, grad, gsum if with_beta else None, S)
+            _adjoint_forward(lib, module, tr, params, relax, A0, ahat, grad, gsum if with_beta else None, S, row_weight if weighted else None)
         upd = 0 if last else 1
         for x in names:
             n = width[x]

@@ -50,8 +50,8 @@ typedef void* bf_stream_t; /* a cudaStream_t */
 
 #define BF_REDUCE_MEAN 0 /* per-domain objective = mean over spec rows */
 #define BF_REDUCE_SUM 1  /* per-domain objective = sum over spec rows  */
-#define BF_REDUCE_MIN 2  /* per-domain objective = smallest spec row (alpha only) */
-#define BF_REDUCE_SOFTMIN 3 /* per-domain objective = -tau * logsumexp(-rows / tau) (alpha only) */
+#define BF_REDUCE_MIN 2  /* per-domain objective = smallest spec row */
+#define BF_REDUCE_SOFTMIN 3 /* per-domain objective = -tau * logsumexp(-rows / tau) */
 
 #define BF_OBJECTIVE_GAP 2  /* minimise reduce(upper - lower) */
 #define BF_OBJECTIVE_BOTH 3 /* maximise lb_weight * reduce(lower) - ub_weight * reduce(upper) */
@@ -452,7 +452,9 @@ int bf_chain_alpha_beta_crown(const bf_chain* chain,
  * boundflow/runtime/alpha_beta_crown.py:535-612, per-domain form 787-818): spec_reduce BF_REDUCE_MEAN, _SUM,
  * _MIN (smallest spec row) or _SOFTMIN (-soft_tau * logsumexp(-rows / soft_tau), soft_tau > 0).  For _MIN and
  * _SOFTMIN the gradient sweep weights every spec row by d objective / d lower (one-hot at the first minimum, or
- * softmax(-rows / soft_tau)); they take alpha only (beta == NULL). */
+ * softmax(-rows / soft_tau)): the weights scale the coefficients kept at every ReLU (alpha gradient) and, with beta
+ * parameters, the per-domain sums of the adjoint values (beta gradient; these layers then run on the row-major
+ * tensor-core adjoint kernel or the FFMA tiles, which carry the row weight). */
 int bf_chain_alpha_beta_crown_reduce(const bf_chain* chain,
                                      const float* C,
                                      const float* const* pre_l, const float* const* pre_u,
@@ -501,7 +503,8 @@ int bf_chain_alpha_crown_objective(const bf_chain* chain,
  *                         slopes on the transposed weight, plus bf_rows_add_broadcast for the bias.)
  *   bf_relu_adjoint_rows  G [B,S,n] holds the relaxed network's value at a ReLU input (the forward image of h0), Ahat
  *                         [B,S,n] the lower coefficients that arrived at the ReLU's output in the backward sweep:
- *                         grad[b,j] += sum_s [l<0<u][Ahat>=0] Ahat*G, gsum[b,j] += sum_s G (NULL without beta), then G
+ *                         grad[b,j] += sum_s [l<0<u][Ahat>=0] Ahat*G, gsum[b,j] += sum_s row_weight[b,s]*G (gsum NULL
+ *                         without beta; row_weight NULL = 1, else d objective / d row for min / softmin), then G
  *                         becomes the ReLU's output on the chosen line (alpha_l*G where Ahat >= 0, alpha_u*G + beta_u
  *                         elsewhere), in place.
  *   bf_alpha_select_best  per-domain objective reduce_s(cur[b,s]) (BF_REDUCE_*), strict best-of against best_metric
@@ -521,8 +524,8 @@ int bf_adjoint_start_box(float* A0, const float* mid, const float* rad, int B, i
 int bf_rows_conv2d_fwd(const float* in, const float* W, const float* bias, float* out, int M, int Ci, int Hi, int Wi,
                        int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
 int bf_relu_adjoint_rows(float* G, const float* Ahat, const float* alpha_u, const float* alpha_l, const float* beta_u,
-                         const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
-                         bf_stream_t stream);
+                         const float* pre_l, const float* pre_u, float* grad, float* gsum, const float* row_weight, int B,
+                         int S, int n, bf_stream_t stream);
 int bf_alpha_select_best(const float* cur, float* best_lower, float* best_metric, int* improve, int first, int spec_reduce,
                          float soft_tau, float* row_weight, int B, int S, bf_stream_t stream);
 int bf_alpha_adam_step(float* alpha, float* m, float* v, float* grad, const int* improve, float* best_alpha,
@@ -618,6 +621,20 @@ int bf_chain_alpha_crown_shared_objective(const bf_chain* chain,
                                           int steps, float lr, int objective, int spec_reduce, float soft_tau,
                                           float lb_weight, float ub_weight,
                                           void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
+/* bf_chain_alpha_crown_shared with the min / softmin spec reductions of the lower objective AND beta parameters
+ * (run_alpha_beta_crown_mlp(per_batch_params=False, spec_reduce=...), boundflow/runtime/alpha_beta_crown.py:787-805): the
+ * per-row weights d objective / d lower scale the kept coefficients (alpha gradient) and the per-domain sums of the
+ * adjoint values (beta gradient).  spec_reduce BF_REDUCE_MEAN | _MIN | _SOFTMIN; other arguments as above. */
+int bf_chain_alpha_beta_crown_shared_reduce(const bf_chain* chain,
+                                            const float* C,
+                                            const float* const* pre_l, const float* const* pre_u,
+                                            float* const* alpha, float* const* best_alpha,
+                                            float* const* beta, float* const* best_beta,
+                                            const int8_t* const* splits, const int* split_strides,
+                                            const float* mid, const float* rad, int norm_p, float eps,
+                                            float* best_lower, float* best_upper, float* best_metric,
+                                            int steps, float lr, int spec_reduce, float soft_tau,
+                                            void* workspace, size_t workspace_bytes, int B, int S, bf_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -783,6 +783,78 @@ def gen_spec_reduce() -> None:
     save("spec_reduce.npz", **out)
 
 
+def gen_beta_reduce() -> None:
+    """beta parameters together with the min / softmin spec reductions of the lower objective
+    (`run_alpha_beta_crown_mlp(relu_split_state=..., spec_reduce=...)`, alpha_beta_crown.py:763-805): the split subdomains of
+    c4 (8 and 40 domains; adaptive start; 1, 3 and 6 steps; per-domain parameters, and shared parameters on the 8), the CNN
+    c2 with the split assignment of conv_beta.npz (4 steps), and two non-chain graphs with the splits of graph_alpha.npz."""
+    out = {"c4_tau": np.array(20.0), "c2_tau": np.array(20.0), "graph_tau": np.array(3.0)}
+    for D in (8, 40):
+        wl = W.make_workload("c4")
+        m = ref_module(wl)
+        _, root_pre = _forward_ibp_trace_mlp(m, InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up))
+        splits = W.make_split_domains(wl, [(root_pre[n].lower, root_pre[n].upper) for n in wl.relu_names], n_domains=D)
+        spec = InputSpec.box(value_name="input", lower=wl.lo.expand(D, -1).contiguous(), upper=wl.up.expand(D, -1).contiguous())
+        state = dict(zip(wl.relu_names, splits))
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=state)
+        a0 = adaptive_alpha(relu_pre)
+        C = wl.C.expand(D, -1, -1).contiguous()
+        for red in ("min", "softmin"):
+            for k in (1, 3, 6):
+                b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=state, steps=k, lr=0.1, per_batch_params=True,
+                                                        warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                        spec_reduce=red, soft_tau=20.0)
+                out[f"c4_{D}_{red}_lower_{k}"], out[f"c4_{D}_{red}_upper_{k}"] = b.lower, b.upper
+                for n, v in bt.beta_by_relu_input.items():
+                    out[f"c4_{D}_{red}_beta_{n}_{k}"] = v
+            if D == 8:
+                b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=state, steps=4, lr=0.1, per_batch_params=False,
+                                                        spec_reduce=red, soft_tau=20.0)
+                out[f"c4_8_shared_{red}_lower_4"], out[f"c4_8_shared_{red}_upper_4"] = b.lower, b.upper
+                for n, v in bt.beta_by_relu_input.items():
+                    out[f"c4_8_shared_{red}_beta_{n}_4"] = v.reshape(-1)
+    cb = np.load(os.path.join(HERE, "conv_beta.npz"))
+    wl = W.make_workload("c2", batch=4)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    shapes = {"h1": (4, 16, 14, 14), "h2": (4, 32, 7, 7), "h3": (4, 100)}
+    state = {n: torch.from_numpy(cb[f"split_{n}"]).to(torch.int8).reshape(shapes[n]) for n in wl.relu_names}
+    _env, relu_pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=state)
+    a0 = adaptive_alpha(relu_pre)
+    for red in ("min", "softmin"):
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=wl.C, relu_split_state=state, steps=4, lr=0.1, per_batch_params=True,
+                                                warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                spec_reduce=red, soft_tau=20.0)
+        out[f"c2_{red}_lower_4"], out[f"c2_{red}_upper_4"] = b.lower, b.upper
+        for n, v in bt.beta_by_relu_input.items():
+            out[f"c2_{red}_beta_{n}_4"] = v.reshape(4, -1)
+    ga = np.load(os.path.join(HERE, "graph_alpha.npz"))
+    cases = W.make_graph_cases()
+    for name in ("fanout_mlp", "residual_s1"):
+        module, _x, lo, up, C = cases[name]
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        _env, pre0 = _forward_ibp_trace_mlp(m, spec)
+        state = {x: torch.from_numpy(ga[f"{name}_split_{x}"]).to(torch.int8).reshape(pre0[x].lower.shape) for x in pre0}
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec, relu_split_state=state)
+        a0 = adaptive_alpha(relu_pre)
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=state, steps=3, lr=0.1, per_batch_params=True,
+                                                warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}),
+                                                spec_reduce="softmin", soft_tau=3.0)
+        out[f"{name}_softmin_lower_3"], out[f"{name}_softmin_upper_3"] = b.lower, b.upper
+        for x, v in bt.beta_by_relu_input.items():
+            out[f"{name}_softmin_beta_{x}_3"] = v.reshape(int(lo.shape[0]), -1)
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, relu_split_state=state, steps=3, lr=0.1, per_batch_params=False,
+                                                spec_reduce="min")
+        out[f"{name}_shared_min_lower_3"], out[f"{name}_shared_min_upper_3"] = b.lower, b.upper
+        for x, v in bt.beta_by_relu_input.items():
+            out[f"{name}_shared_min_beta_{x}_3"] = v.reshape(-1)
+    save("beta_reduce.npz", **out)
+
+
 def gen_objectives() -> None:
     """The reference's alpha loop with the upper, gap and both objectives (alpha_beta_crown.py:535-612, 807-818),
     per-domain parameters, on c1 (8 inputs) and c3 (8 inputs) after 1, 3 and 10 steps: mean reduction for each
@@ -814,7 +886,7 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "objectives": gen_objectives, "conv_beta": gen_conv_beta,
               "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha,
               "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
-              "graph_certificate": gen_graph_certificate}
+              "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce}
 
 
 def main() -> None:

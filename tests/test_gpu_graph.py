@@ -52,10 +52,6 @@ def test_chain_modules_keep_the_fused_path_and_unsupported_modes_are_refused(dev
         run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="gap", spec_reduce="sum")
     with pytest.raises(NotImplementedError):   # a negative weight would flip the sign decisions of the gradient sweep
         run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), steps=1, lr=0.1, per_batch_params=True, objective="both", ub_weight=-1.0)
-    split = {"h": torch.zeros(5, 24, dtype=torch.int8, device=dev)}
-    split["h"][:, 0] = 1
-    with pytest.raises(NotImplementedError):   # min / softmin with beta parameters
-        run_alpha_beta_crown_mlp(module, spec, linear_spec_C=C.to(dev), relu_split_state=split, steps=1, lr=0.1, per_batch_params=True, spec_reduce="min")
 
 
 @pytest.mark.parametrize("name", ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"])
@@ -246,9 +242,16 @@ def test_graph_loop_building_blocks_against_torch(dev):
     Gd, gr, gs = G.to(dev).clone(), grad0.to(dev).clone(), gsum0.to(dev).clone()
     Ahd, aud, ald, bud, l2d, u2d = (x.to(dev).contiguous() for x in (Ah, au, al, bu, l, u))
     _lib.check(lib.bf_relu_adjoint_rows(Gd.data_ptr(), Ahd.data_ptr(), aud.data_ptr(), ald.data_ptr(), bud.data_ptr(), l2d.data_ptr(),
-                                        u2d.data_ptr(), gr.data_ptr(), gs.data_ptr(), B, S, n, s))
+                                        u2d.data_ptr(), gr.data_ptr(), gs.data_ptr(), None, B, S, n, s))
     sel = Ah >= 0
     amb = ((l < 0) & (u > 0)).unsqueeze(1)
     assert_close(Gd, torch.where(sel, al.unsqueeze(1) * G, au.unsqueeze(1) * G + bu.unsqueeze(1)), "relu adjoint output", atol=1e-6)
     assert_close(gr, grad0 + (torch.where(sel & amb, Ah * G, torch.zeros_like(G))).sum(dim=1), "alpha gradient sums", atol=1e-5)
     assert_close(gs, gsum0 + G.sum(dim=1), "beta gradient sums", atol=1e-5)
+    # the same step with a weight per row on the beta sums (min / softmin objectives with beta parameters)
+    rw = torch.rand(B, S, generator=g)
+    Gd, gr, gs, rwd = G.to(dev).clone(), grad0.to(dev).clone(), gsum0.to(dev).clone(), rw.to(dev)
+    _lib.check(lib.bf_relu_adjoint_rows(Gd.data_ptr(), Ahd.data_ptr(), aud.data_ptr(), ald.data_ptr(), bud.data_ptr(), l2d.data_ptr(),
+                                        u2d.data_ptr(), gr.data_ptr(), gs.data_ptr(), rwd.data_ptr(), B, S, n, s))
+    assert_close(gr, grad0 + (torch.where(sel & amb, Ah * G, torch.zeros_like(G))).sum(dim=1), "alpha gradient sums (weighted call)", atol=1e-5)
+    assert_close(gs, gsum0 + (rw.unsqueeze(2) * G).sum(dim=1), "weighted beta gradient sums", atol=1e-5)

@@ -38,7 +38,7 @@ def test_matches_reference_golden(dev, golden, cfg, reduce):
 
 
 def test_tensor_core_rows_and_argument_errors(dev):
-    """288 coefficient rows (tcgen05 kernels) against the oracle; min / softmin refuse beta and a non-positive tau."""
+    """288 coefficient rows (tcgen05 kernels) against the oracle; min / softmin refuse a non-positive tau."""
     from boundflow_b200 import _lib
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import adaptive_alpha_from_trace, alpha_crown_from_trace, ibp_trace
@@ -60,5 +60,109 @@ def test_tensor_core_rows_and_argument_errors(dev):
         assert_close(got[1], ref_u, f"{red} upper, 2 steps")
     with pytest.raises(ValueError):
         alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=1, lr=0.1, spec_reduce="softmin", soft_tau=0.0)
-    with pytest.raises(NotImplementedError):
-        alpha_crown_from_trace(trace, wl.C.to(dev), a0, steps=1, lr=0.1, spec_reduce="min", beta_splits=[None] * 5)
+
+
+@pytest.fixture(params=["default", "row_major", "ffma"])
+def adjoint_route(request):
+    """The weighted beta sums live in the row-major tensor-core adjoint kernel, the FFMA kernel and the conv ReLU step;
+    the default dispatch must route a weighted call away from the feature-major kernel by itself."""
+    import os
+
+    var = {"row_major": "BF_B200_ADJ_ROWMAJOR", "ffma": "BF_B200_FORCE_FFMA"}.get(request.param)
+    if var:
+        os.environ[var] = "1"
+    yield request.param
+    if var:
+        os.environ.pop(var, None)
+
+
+def test_beta_with_min_and_softmin_matches_reference_golden(dev, golden, adjoint_route):
+    """beta parameters together with min / softmin (tests/golden/beta_reduce.npz): c4 subdomains with per-domain parameters
+    (8 domains: FFMA tiles; 40 domains = 360 rows: tcgen05 kernels) and shared parameters."""
+    from boundflow_b200 import _lib
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, ibp_trace, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    g = golden("beta_reduce.npz")
+    tau = float(g["c4_tau"])
+    for D, steps in ((8, (1, 3, 6)), (40, (1, 3, 6))):
+        wl = W.make_workload("c4")
+        root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+        splits = W.make_split_domains(wl, root.pre, n_domains=D)
+        spec = InputSpec.box(value_name="input", lower=wl.lo.expand(D, -1).contiguous().to(dev), upper=wl.up.expand(D, -1).contiguous().to(dev))
+        state = {n: sp.to(dev) for n, sp in zip(wl.relu_names, splits)}
+        a0 = adaptive_alpha_from_trace(ibp_trace(wl.module, spec, relu_split_state=state))
+        C = wl.C.expand(D, -1, -1).contiguous().to(dev)
+        for red in ("min", "softmin"):
+            for k in steps:
+                t0 = _lib.tc_launch_count()
+                b, _a, bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=C, relu_split_state=state, steps=k, lr=0.1, per_batch_params=True,
+                                                        warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))), spec_reduce=red, soft_tau=tau)
+                if D == 40 and adjoint_route != "ffma":
+                    assert _lib.tc_launch_count() > t0
+                # on the tcgen05 path (3xTF32) six Adam steps leave single elements up to a few strict tolerances away
+                wide = {"atol": 4e-4, "rtol": 4e-5} if (D == 40 and k == 6 and adjoint_route != "ffma") else {}
+                assert_close(b.lower, g[f"c4_{D}_{red}_lower_{k}"], f"c4 {D} domains {red} lower after {k}", **wide)
+                assert_close(b.upper, g[f"c4_{D}_{red}_upper_{k}"], f"c4 {D} domains {red} upper after {k}", **wide)
+                # beta is an Adam iterate: strict on the FFMA path up to 3 steps; the tcgen05 path is 3.3x the strict tolerance
+                # away after 3 steps (measured), and after 6 steps single entries differ by a normalised step on either path
+                on_tc = D == 40 and adjoint_route != "ffma"
+                for n in wl.relu_names:
+                    assert_close(bt.beta_by_relu_input[n], g[f"c4_{D}_{red}_beta_{n}_{k}"], f"beta {n} after {k}",
+                                 atol=2e-2 if k == 6 else (1e-4 if on_tc else 1e-5))
+            if D == 8:
+                b, _a, bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=C, relu_split_state=state, steps=4, lr=0.1, per_batch_params=False,
+                                                        spec_reduce=red, soft_tau=tau)
+                assert_close(b.lower, g[f"c4_8_shared_{red}_lower_4"], f"c4 shared {red} lower")
+                assert_close(b.upper, g[f"c4_8_shared_{red}_upper_4"], f"c4 shared {red} upper")
+                for n in wl.relu_names:
+                    assert_close(bt.beta_by_relu_input[n].reshape(-1), g[f"c4_8_shared_{red}_beta_{n}_4"], f"shared beta {n}", atol=1e-5)
+
+
+def test_beta_with_min_and_softmin_on_a_cnn_and_on_graphs(dev, golden):
+    """The same combination through the conv ReLU step (c2 with the split assignment of conv_beta.npz) and through the
+    per-value graph loop (splits of graph_alpha.npz), per-domain and shared parameters."""
+    import numpy as np
+
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, adaptive_alpha_from_trace, ibp_trace, run_alpha_beta_crown_mlp
+    from boundflow_b200.dag import forward_ibp_dag
+    from boundflow_b200.ir import InputSpec
+
+    g, cb, ga = golden("beta_reduce.npz"), golden("conv_beta.npz"), golden("graph_alpha.npz")
+    wl = W.make_workload("c2", batch=4)
+    shapes = {"h1": (16, 14, 14), "h2": (32, 7, 7), "h3": (100,)}
+    state = {n: torch.from_numpy(np.asarray(cb[f"split_{n}"])).to(torch.int8).reshape((4,) + shapes[n]).to(dev) for n in wl.relu_names}
+    spec = InputSpec.box(value_name="input", lower=wl.lo.to(dev), upper=wl.up.to(dev))
+    a0 = adaptive_alpha_from_trace(ibp_trace(wl.module, spec, relu_split_state=state))
+    for red in ("min", "softmin"):
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_split_state=state, steps=4, lr=0.1,
+                                                per_batch_params=True, warm_start_alpha=AlphaState(dict(zip(wl.relu_names, a0))), spec_reduce=red,
+                                                soft_tau=float(g["c2_tau"]))
+        assert_close(b.lower, g[f"c2_{red}_lower_4"], f"c2 {red} lower")
+        assert_close(b.upper, g[f"c2_{red}_upper_4"], f"c2 {red} upper")
+        for n in wl.relu_names:
+            assert_close(bt.beta_by_relu_input[n].reshape(4, -1), g[f"c2_{red}_beta_{n}_4"], f"c2 beta {n}", atol=1e-5)
+    for name in ("fanout_mlp", "residual_s1"):
+        module, _x, lo, up, C = W.make_graph_cases()[name]
+        B = int(lo.shape[0])
+        spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+        Cd = None if C is None else C.to(dev)
+        tr0 = forward_ibp_dag(module, spec)
+        splits = {x: torch.from_numpy(np.asarray(ga[f"{name}_split_{x}"])).to(torch.int8).to(dev) for x in tr0.pre_l}
+        tr = forward_ibp_dag(module, spec, splits)
+        a1 = {x: ((tr.pre_l[x] >= 0) | ((tr.pre_l[x] < 0) & (tr.pre_u[x] > 0) & (tr.pre_u[x] > -tr.pre_l[x]))).float() for x in tr.pre_l}
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=True,
+                                                warm_start_alpha=AlphaState(a1), spec_reduce="softmin", soft_tau=float(g["graph_tau"]))
+        assert_close(b.lower.reshape(B, -1), g[f"{name}_softmin_lower_3"].reshape(B, -1), f"{name} softmin lower")
+        assert_close(b.upper.reshape(B, -1), g[f"{name}_softmin_upper_3"].reshape(B, -1), f"{name} softmin upper")
+        for x in tr.pre_l:
+            assert_close(bt.beta_by_relu_input[x].reshape(B, -1), g[f"{name}_softmin_beta_{x}_3"], f"{name} beta {x}", atol=1e-5)
+        b, _a, bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, relu_split_state=splits, steps=3, lr=0.1, per_batch_params=False,
+                                                spec_reduce="min")
+        assert_close(b.lower.reshape(B, -1), g[f"{name}_shared_min_lower_3"].reshape(B, -1), f"{name} shared min lower")
+        assert_close(b.upper.reshape(B, -1), g[f"{name}_shared_min_upper_3"].reshape(B, -1), f"{name} shared min upper")
+        for x in tr.pre_l:
+            assert_close(bt.beta_by_relu_input[x].reshape(-1), g[f"{name}_shared_min_beta_{x}_3"], f"{name} shared beta {x}", atol=1e-5)

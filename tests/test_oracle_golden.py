@@ -477,6 +477,73 @@ def test_graph_oracle_crown_and_alpha_beta(golden, name):
         assert_close(b, ga[f"{name}_beta_{x}_3"], f"beta {x} after 3", atol=1e-5)
 
 
+def test_beta_with_min_and_softmin_reductions(golden):
+    """beta parameters together with the min / softmin reductions of the lower objective (alpha_beta_crown.py:763-805):
+    the oracles against the reference on c4 subdomains, the CNN c2 and two non-chain graphs (beta_reduce.npz)."""
+    from oracle import graph_oracle as GO
+
+    g = golden("beta_reduce.npz")
+    tau = float(g["c4_tau"])
+    for D, steps in ((8, (1, 3, 6)), (40, (3,))):
+        wl = W.make_workload("c4")
+        root = O.forward_ibp_trace(wl.layers, O.box_input(wl.lo, wl.up))
+        splits = W.make_split_domains(wl, root.pre, n_domains=D)
+        inp = O.box_input(wl.lo.expand(D, -1).contiguous(), wl.up.expand(D, -1).contiguous())
+        tr = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+        a0 = O.adaptive_alpha_init(tr)
+        C = wl.C.expand(D, -1, -1).contiguous()
+        for red in ("min", "softmin"):
+            for k in steps:
+                lo, up, _a, beta, _t = O.alpha_crown(wl.layers, inp, C, steps=k, lr=0.1, alpha0=a0, splits=splits, trace=tr, optimize_beta=True,
+                                                     return_beta=True, spec_reduce=red, soft_tau=tau)
+                assert_close(lo, g[f"c4_{D}_{red}_lower_{k}"], f"c4 {D} domains {red} lower after {k}")
+                assert_close(up, g[f"c4_{D}_{red}_upper_{k}"], f"c4 {D} domains {red} upper after {k}")
+                for n, b in zip(wl.relu_names, beta):
+                    assert_close(b, g[f"c4_{D}_{red}_beta_{n}_{k}"], f"beta {n}", atol=1e-5)
+            if D == 8:
+                lo, up, _a, beta, _t = O.alpha_crown_shared(wl.layers, inp, C, steps=4, lr=0.1, splits=splits, trace=tr, optimize_beta=True,
+                                                            spec_reduce=red, soft_tau=tau)
+                assert_close(lo, g[f"c4_8_shared_{red}_lower_4"], f"c4 shared {red} lower")
+                assert_close(up, g[f"c4_8_shared_{red}_upper_4"], f"c4 shared {red} upper")
+                for n, b in zip(wl.relu_names, beta):
+                    assert_close(b, g[f"c4_8_shared_{red}_beta_{n}_4"], f"shared beta {n}", atol=1e-5)
+    cb = golden("conv_beta.npz")
+    wl = W.make_workload("c2", batch=4)
+    inp = O.box_input(wl.lo, wl.up)
+    splits = [torch.from_numpy(np.asarray(cb[f"split_{n}"])).to(torch.int8).reshape(4, -1) for n in wl.relu_names]
+    tr = O.forward_ibp_trace(wl.layers, inp, splits=splits)
+    a0 = O.adaptive_alpha_init(tr)
+    for red in ("min", "softmin"):
+        lo, up, _a, beta, _t = O.alpha_crown(wl.layers, inp, wl.C, steps=4, lr=0.1, alpha0=a0, splits=splits, trace=tr, optimize_beta=True,
+                                             return_beta=True, spec_reduce=red, soft_tau=float(g["c2_tau"]))
+        assert_close(lo, g[f"c2_{red}_lower_4"], f"c2 {red} lower")
+        assert_close(up, g[f"c2_{red}_upper_4"], f"c2 {red} upper")
+        for n, b in zip(wl.relu_names, beta):
+            assert_close(b.reshape(4, -1), g[f"c2_{red}_beta_{n}_4"], f"c2 beta {n}", atol=1e-5)
+    ga = golden("graph_alpha.npz")
+    for name in ("fanout_mlp", "residual_s1"):
+        module, _x, lo, up, C = W.make_graph_cases()[name]
+        B = lo.shape[0]
+        env, relu_pre = GO.forward_ibp_graph(module, lo, up)
+        n_out = env["out"][0].reshape(B, -1).shape[1]
+        Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+        splits = {x: torch.from_numpy(np.asarray(ga[f"{name}_split_{x}"])).to(torch.int8) for x in relu_pre}
+        _env, pre_split = GO.forward_ibp_graph(module, lo, up, splits=splits)
+        a1 = GO.adaptive_alpha_init_graph(pre_split)
+        lo_b, up_b, _a, beta = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, alpha0=a1, splits=splits, optimize_beta=True,
+                                                    spec_reduce="softmin", soft_tau=float(g["graph_tau"]))
+        assert_close(lo_b, g[f"{name}_softmin_lower_3"].reshape(B, -1), f"{name} softmin lower")
+        assert_close(up_b, g[f"{name}_softmin_upper_3"].reshape(B, -1), f"{name} softmin upper")
+        for x, b in beta.items():
+            assert_close(b, g[f"{name}_softmin_beta_{x}_3"], f"{name} beta {x}", atol=1e-5)
+        lo_b, up_b, _a, beta = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, splits=splits, optimize_beta=True, spec_reduce="min",
+                                                    per_batch_params=False)
+        assert_close(lo_b, g[f"{name}_shared_min_lower_3"].reshape(B, -1), f"{name} shared min lower")
+        assert_close(up_b, g[f"{name}_shared_min_upper_3"].reshape(B, -1), f"{name} shared min upper")
+        for x, b in beta.items():
+            assert_close(b.reshape(-1), g[f"{name}_shared_min_beta_{x}_3"], f"{name} shared beta {x}", atol=1e-5)
+
+
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
 GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
 
