@@ -76,6 +76,7 @@ SIGNATURES = {
     "bf_interval_add": (_i, [_p, _p, _p, _p, _p, _p, C.c_longlong, _p]),
     "bf_first_layer_certificate_max_halfspaces": (_i, []),
     "bf_first_layer_certificate": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),
+    "bf_first_layer_certificate_lp": (_i, [_p, _i, _p, _p, _p, _f, _i, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),
     "bf_ibp_linear_batched": (_i, [_p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _p]),
     "bf_chain_crown": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _sz, _i, _i, _p]),
     "bf_chain_crown_influence": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _p, _p, _p, _sz, _i, _i, _p]),
@@ -93,6 +94,7 @@ SIGNATURES = {
     "bf_relu_split_apply": (_i, [_p, _p, _p, _i, _p, _i, _i, _p]),
     "bf_rows_add_broadcast": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "bf_adjoint_start_box": (_i, [_p, _p, _p, _i, _i, _i, _p]),
+    "bf_adjoint_start_lp": (_i, [_p, _p, _f, _i, _i, _i, _i, _p]),
     "bf_rows_conv2d_fwd": (_i, [_p, _p, _p, _p] + [_i] * 13 + [_p]),
     "bf_relu_adjoint_rows": (_i, [_p] * 10 + [_i, _i, _i, _p]),
     "bf_alpha_select_best": (_i, [_p, _p, _p, _p, _i, _i, _f, _p, _i, _i, _p]),

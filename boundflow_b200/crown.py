@@ -815,15 +815,26 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
     n_halfspaces int32 [B]) as CUDA tensors.  The splits of the first ReLU over a Linear or Conv2d first
     layer are used (conv: the half-space row of a split neuron is its filter placed in the input image,
     alpha_beta_crown.py:325-387; only the rows of neurons that are split somewhere in the batch are formed);
-    a chain that starts otherwise, or no split on that ReLU, gives all zeros.  On a graph that is not a chain every
+    a chain that starts otherwise, or no split on that ReLU, gives all zeros.  Boxes, L-inf, L2 and L1 balls.  On a graph that is not a chain every
     ReLU fed by a Linear / Conv2d op on the input value contributes its half-spaces (`dag.first_layer_certificate_dag`)."""
     if needs_graph_path(module):
         from .dag import first_layer_certificate_dag
 
         return first_layer_certificate_dag(module, input_spec, relu_split_state, steps=steps, lr=lr, tol=tol)
     spec, chain, device, B, mid, rad, _ = _prepare_input(module, input_spec)
-    if lp_ball_of(spec) is not None:
-        raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
+    ball = lp_ball_of(spec)
+
+    def certificate(sp_t, sp_stride, W_rows, b_rows, n_rows):
+        """Box / L-inf: maximum over the box; L1 / L2 ball: centre term + eps * dual norm (mid holds the centre then)."""
+        if ball is not None:
+            _lib.check(chain.lib.bf_first_layer_certificate_lp(
+                _lib.ptr(sp_t), sp_stride, _lib.ptr(W_rows), _lib.ptr(b_rows), _lib.ptr(mid), float(ball[1]), int(ball[0]), _lib.ptr(infeasible),
+                _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, n_rows, chain.n0, _stream_ptr(device)))
+        else:
+            _lib.check(chain.lib.bf_first_layer_certificate(
+                _lib.ptr(sp_t), sp_stride, _lib.ptr(W_rows), _lib.ptr(b_rows), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible), _lib.ptr(best),
+                _lib.ptr(count), int(steps), float(lr), float(tol), B, n_rows, chain.n0, _stream_ptr(device)))
+
     infeasible = torch.zeros(B, dtype=torch.int32, device=device)
     best = torch.full((B,), float("inf"), dtype=torch.float32, device=device)
     count = torch.zeros(B, dtype=torch.int32, device=device)
@@ -849,13 +860,9 @@ def first_layer_certificate(module: Any, input_spec: Any, relu_split_state: Mapp
             int(Wo), int(first.W.shape[2]), int(first.W.shape[3]), int(first.stride[0]), int(first.stride[1]), int(first.padding[0]),
             int(first.padding[1]), _stream_ptr(device)))
         sp_sub = sp[:, cols].contiguous()
-        _lib.check(chain.lib.bf_first_layer_certificate(
-            _lib.ptr(sp_sub), 0 if stride == 0 else U, _lib.ptr(W_rows), _lib.ptr(b_rows), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible),
-            _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, U, chain.n0, _stream_ptr(device)))
+        certificate(sp_sub, 0 if stride == 0 else U, W_rows, b_rows, U)
         return infeasible, best, count
-    _lib.check(chain.lib.bf_first_layer_certificate(
-        _lib.ptr(sp), stride, _lib.ptr(first.W), _lib.ptr(first.b), _lib.ptr(mid), _lib.ptr(rad), _lib.ptr(infeasible), _lib.ptr(best),
-        _lib.ptr(count), int(steps), float(lr), float(tol), B, n1, chain.n0, _stream_ptr(device)))
+    certificate(sp, stride, first.W, first.b, n1)
     return infeasible, best, count
 
 

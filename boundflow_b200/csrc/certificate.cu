@@ -5,7 +5,8 @@
 //     max_{x in box} (sum_i w_i a_i) . x + sum_i w_i c_i  <  0,     w on the simplex,
 // no input satisfies all of them and the domain is empty.  The weights are softmax(logits); the
 // logits take `steps` Adam steps on that maximum (value = a.mid + |a|.rad + c), stopping at the
-// first negative value.  A single half-space is tested directly.
+// first negative value.  A single half-space is tested directly.  On an L1 / L2 ball the maximum of a combination is
+// a.centre + eps * ||a||_q (q dual to p), attained at centre + eps * (the unit-ball point aligned with a).
 #include <math.h>
 
 #include "kernels.cuh"
@@ -31,13 +32,13 @@ __device__ __forceinline__ float cert_block_sum(float v, float* red) {
 __global__ void __launch_bounds__(CERT_THREADS) first_layer_cert_kernel(const int8_t* __restrict__ split, int split_stride,
                                                                         const float* __restrict__ W1, const float* __restrict__ b1,
                                                                         const float* __restrict__ mid, const float* __restrict__ rad,
-                                                                        int n1, int n0, int steps, float lr, float tol,
-                                                                        int* __restrict__ infeasible, float* __restrict__ best_value,
-                                                                        int* __restrict__ n_halfspaces) {
+                                                                        int norm_p, float eps, int n1, int n0, int steps, float lr,
+                                                                        float tol, int* __restrict__ infeasible,
+                                                                        float* __restrict__ best_value, int* __restrict__ n_halfspaces) {
   extern __shared__ __align__(16) float cert_smem[];
   float* A = cert_smem;                      // [CERT_MAX_M][n0]  s_i * W1[j_i]
   float* smid = A + (size_t)CERT_MAX_M * n0;  // [n0]
-  float* srad = smid + n0;                   // [n0]
+  float* srad = smid + n0;                   // [n0] box radius; on an Lp ball: the combination a of the current iteration
   __shared__ int idx[CERT_MAX_M];
   __shared__ float sgn[CERT_MAX_M], cvec[CERT_MAX_M], logit[CERT_MAX_M], wgt[CERT_MAX_M], am[CERT_MAX_M], av[CERT_MAX_M];
   __shared__ float red[CERT_THREADS / 32];
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(CERT_THREADS) first_layer_cert_kernel(const in
   }
   for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
     smid[k] = mid[(size_t)d * n0 + k];
-    srad[k] = rad[(size_t)d * n0 + k];
+    srad[k] = (norm_p == BF_NORM_BOX) ? rad[(size_t)d * n0 + k] : 0.f;
   }
   for (int i = 0; i < m; ++i)
     for (int k = threadIdx.x; k < n0; k += CERT_THREADS) A[(size_t)i * n0 + k] = sgn[i] * __ldg(W1 + (size_t)idx[i] * n0 + k);
@@ -101,18 +102,61 @@ __global__ void __launch_bounds__(CERT_THREADS) first_layer_cert_kernel(const in
     float val_p = 0.f, g_p[CERT_MAX_M];
 #pragma unroll
     for (int i = 0; i < CERT_MAX_M; ++i) g_p[i] = 0.f;
-    for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
-      float a = 0.f;
-      for (int i = 0; i < m; ++i) a = fmaf(wgt[i], A[(size_t)i * n0 + k], a);
-      const float sg = (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f);
-      const float x = fmaf(sg, srad[k], smid[k]);  // maximiser of a . x over the box (sub-gradient 0 at a == 0)
-      val_p = fmaf(a, smid[k], val_p);
-      val_p = fmaf(fabsf(a), srad[k], val_p);
+    float val;
+    if (norm_p == BF_NORM_BOX) {
+      for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
+        float a = 0.f;
+        for (int i = 0; i < m; ++i) a = fmaf(wgt[i], A[(size_t)i * n0 + k], a);
+        const float sg = (a > 0.f) ? 1.f : ((a < 0.f) ? -1.f : 0.f);
+        const float x = fmaf(sg, srad[k], smid[k]);  // maximiser of a . x over the box (sub-gradient 0 at a == 0)
+        val_p = fmaf(a, smid[k], val_p);
+        val_p = fmaf(fabsf(a), srad[k], val_p);
 #pragma unroll
-      for (int i = 0; i < CERT_MAX_M; ++i)
-        if (i < m) g_p[i] = fmaf(A[(size_t)i * n0 + k], x, g_p[i]);
+        for (int i = 0; i < CERT_MAX_M; ++i)
+          if (i < m) g_p[i] = fmaf(A[(size_t)i * n0 + k], x, g_p[i]);
+      }
+      val = cert_block_sum(val_p, red);
+    } else {
+      // L2 ball: dual norm ||a||_2, maximiser centre + eps * a / ||a||_2; L1 ball: dual norm max |a_k|, maximiser
+      // centre + eps * sign(a_k) / (number of maxima) at the maxima (the sub-gradient torch's amax backward takes)
+      float nrm_p = 0.f;
+      for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
+        float a = 0.f;
+        for (int i = 0; i < m; ++i) a = fmaf(wgt[i], A[(size_t)i * n0 + k], a);
+        srad[k] = a;
+        val_p = fmaf(a, smid[k], val_p);
+        nrm_p = (norm_p == BF_NORM_L2) ? fmaf(a, a, nrm_p) : fmaxf(nrm_p, fabsf(a));
+      }
+      float nrm, cnt = 1.f;
+      if (norm_p == BF_NORM_L2) {
+        nrm = sqrtf(cert_block_sum(nrm_p, red));
+      } else {
+        // block maximum through the sum helper: every thread contributes its maximum once per candidate round
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nrm_p = fmaxf(nrm_p, __shfl_xor_sync(0xffffffffu, nrm_p, o));
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = nrm_p;
+        __syncthreads();
+        nrm = red[0];
+#pragma unroll
+        for (int w = 1; w < CERT_THREADS / 32; ++w) nrm = fmaxf(nrm, red[w]);
+        __syncthreads();
+        float c_p = 0.f;
+        for (int k = threadIdx.x; k < n0; k += CERT_THREADS) c_p += (fabsf(srad[k]) == nrm) ? 1.f : 0.f;
+        cnt = fmaxf(cert_block_sum(c_p, red), 1.f);
+      }
+      for (int k = threadIdx.x; k < n0; k += CERT_THREADS) {
+        const float a = srad[k];
+        float dir;
+        if (norm_p == BF_NORM_L2) dir = (nrm > 0.f) ? a / nrm : 0.f;
+        else dir = (fabsf(a) == nrm && nrm > 0.f) ? ((a > 0.f) ? 1.f : -1.f) / cnt : 0.f;
+        const float x = fmaf(eps, dir, smid[k]);
+#pragma unroll
+        for (int i = 0; i < CERT_MAX_M; ++i)
+          if (i < m) g_p[i] = fmaf(A[(size_t)i * n0 + k], x, g_p[i]);
+      }
+      val = cert_block_sum(val_p, red) + eps * nrm;
     }
-    float val = cert_block_sum(val_p, red);
     float g[CERT_MAX_M];
 #pragma unroll
     for (int i = 0; i < CERT_MAX_M; ++i) g[i] = (i < m) ? cert_block_sum(g_p[i], red) + cvec[i] : 0.f;
@@ -146,19 +190,40 @@ __global__ void __launch_bounds__(CERT_THREADS) first_layer_cert_kernel(const in
 
 extern "C" int bf_first_layer_certificate_max_halfspaces(void) { return bf::CERT_MAX_M; }
 
+static int first_layer_certificate(const char* who, const int8_t* split, int split_stride, const float* W1, const float* b1,
+                                   const float* mid, const float* rad, int norm_p, float eps, int* infeasible, float* best_value,
+                                   int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0, bf_stream_t stream);
+
 extern "C" int bf_first_layer_certificate(const int8_t* split, int split_stride, const float* W1, const float* b1,
                                           const float* mid, const float* rad, int* infeasible, float* best_value,
                                           int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
                                           bf_stream_t stream) {
-  BF_REQUIRE(split && W1 && mid && rad && infeasible, BF_E_INVALID, "bf_first_layer_certificate: null tensor");
-  BF_REQUIRE(B > 0 && n1 > 0 && n0 > 0 && steps > 0 && lr > 0.f && tol >= 0.f, BF_E_INVALID, "bf_first_layer_certificate: bad sizes or options");
-  BF_REQUIRE(split_stride == 0 || split_stride == n1, BF_E_INVALID, "bf_first_layer_certificate: split_stride must be 0 or n1");
+  BF_REQUIRE(rad, BF_E_INVALID, "bf_first_layer_certificate: null tensor");
+  return first_layer_certificate("bf_first_layer_certificate", split, split_stride, W1, b1, mid, rad, BF_NORM_BOX, 0.f, infeasible,
+                                 best_value, n_halfspaces, steps, lr, tol, B, n1, n0, stream);
+}
+
+extern "C" int bf_first_layer_certificate_lp(const int8_t* split, int split_stride, const float* W1, const float* b1,
+                                             const float* center, float eps, int p, int* infeasible, float* best_value,
+                                             int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
+                                             bf_stream_t stream) {
+  BF_REQUIRE((p == BF_NORM_L1 || p == BF_NORM_L2) && eps >= 0.f, BF_E_INVALID, "bf_first_layer_certificate_lp: p must be BF_NORM_L1 or BF_NORM_L2, eps >= 0");
+  return first_layer_certificate("bf_first_layer_certificate_lp", split, split_stride, W1, b1, center, nullptr, p, eps, infeasible,
+                                 best_value, n_halfspaces, steps, lr, tol, B, n1, n0, stream);
+}
+
+static int first_layer_certificate(const char* who, const int8_t* split, int split_stride, const float* W1, const float* b1,
+                                   const float* mid, const float* rad, int norm_p, float eps, int* infeasible, float* best_value,
+                                   int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0, bf_stream_t stream) {
+  BF_REQUIRE(split && W1 && mid && infeasible, BF_E_INVALID, "%s: null tensor", who);
+  BF_REQUIRE(B > 0 && n1 > 0 && n0 > 0 && steps > 0 && lr > 0.f && tol >= 0.f, BF_E_INVALID, "%s: bad sizes or options", who);
+  BF_REQUIRE(split_stride == 0 || split_stride == n1, BF_E_INVALID, "%s: split_stride must be 0 or n1", who);
   const size_t smem = ((size_t)bf::CERT_MAX_M + 2) * n0 * sizeof(float);
-  BF_REQUIRE(smem <= 200 * 1024, BF_E_UNSUPPORTED, "bf_first_layer_certificate: input dimension %d too large for one block", n0);
+  BF_REQUIRE(smem <= 200 * 1024, BF_E_UNSUPPORTED, "%s: input dimension %d too large for one block", who, n0);
   static bf::SmemOptIn opt_in;
   if (int rc = bf::ensure_dynamic_smem(bf::first_layer_cert_kernel, 200 * 1024, opt_in, "first_layer_cert_kernel")) return rc;
-  bf::first_layer_cert_kernel<<<B, bf::CERT_THREADS, smem, bf::as_stream(stream)>>>(split, split_stride, W1, b1, mid, rad, n1, n0, steps,
-                                                                                  lr, tol, infeasible, best_value, n_halfspaces);
+  bf::first_layer_cert_kernel<<<B, bf::CERT_THREADS, smem, bf::as_stream(stream)>>>(split, split_stride, W1, b1, mid, rad, norm_p, eps, n1, n0,
+                                                                                  steps, lr, tol, infeasible, best_value, n_halfspaces);
   BF_CHECK_LAUNCH("first_layer_cert_kernel");
   return BF_OK;
 }

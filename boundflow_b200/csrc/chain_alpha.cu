@@ -618,6 +618,13 @@ extern "C" int bf_adjoint_start_box(float* A0, const float* mid, const float* ra
   return bf::launch_h0_box(A0, mid, rad, B, S, n0, bf::as_stream(stream));
 }
 
+extern "C" int bf_adjoint_start_lp(float* A0, const float* center, float eps, int p, int B, int S, int n0, bf_stream_t stream) {
+  BF_REQUIRE(A0 && center, BF_E_INVALID, "bf_adjoint_start_lp: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n0 > 0 && eps >= 0.f && (p == BF_NORM_L1 || p == BF_NORM_L2 || p == BF_NORM_INF), BF_E_INVALID,
+             "bf_adjoint_start_lp: bad sizes, eps or norm");
+  return bf::launch_h0_lp(A0, center, eps, p, B, S, n0, bf::as_stream(stream));
+}
+
 extern "C" int bf_rows_conv2d_fwd(const float* in, const float* W, const float* bias, float* out, int M, int Ci, int Hi, int Wi,
                                   int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream) {
   BF_REQUIRE(in && W && out, BF_E_INVALID, "bf_rows_conv2d_fwd: null tensor");

@@ -55,6 +55,8 @@ class DagTrace:
     mid: Optional[torch.Tensor] = None
     rad: Optional[torch.Tensor] = None
     input_name: str = ""
+    norm_p: int = 0     # _lib.NORM_BOX, or 1 / 2 for an L1 / L2 ball (then mid = centre and rad = eps, the bounding box)
+    eps: float = 0.0
 
 
 def _params(module: Any, device: torch.device) -> Dict[str, torch.Tensor]:
@@ -71,17 +73,25 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
     the name of a ReLU input to its int8 split assignment ([B, *shape] or one shared row)."""
     lib = _lib.load()
     spec = normalize_input_spec(input_spec)
-    if lp_ball_of(spec) is not None:
-        raise NotImplementedError("the graph path supports boxes and L-inf balls")
+    ball = lp_ball_of(spec)
     device = _cuda_device(spec.center)
     task = module.get_entry_task()
     params = _params(module, device)
-    mid, rad, lo, up = input_mid_rad(spec)
     B = int(spec.center.shape[0])
     tr = DagTrace(B=B, input_name=spec.value_name)
     tr.infeasible = torch.zeros(B, dtype=torch.int32, device=device)
-    tr.mid, tr.rad = _f32(mid, device).reshape(B, -1), _f32(rad, device).reshape(B, -1)
-    tr.lower[spec.value_name], tr.upper[spec.value_name] = _f32(lo, device).reshape(B, -1), _f32(up, device).reshape(B, -1)
+    if ball is not None:
+        # L1 / L2 ball (LpBallPerturbation, perturbation.py:73-222): a Linear op on the input value uses the dual row norms,
+        # every other consumer the bounding box centre -/+ eps (crown_ibp.py:126-134, 173-175)
+        tr.norm_p, tr.eps = int(ball[0]), float(ball[1])
+        tr.mid = _f32(spec.center, device).reshape(B, -1).contiguous()
+        tr.rad = torch.full_like(tr.mid, tr.eps)
+        tr.lower[spec.value_name], tr.upper[spec.value_name] = tr.mid - tr.eps, tr.mid + tr.eps
+    else:
+        mid, rad, lo, up = input_mid_rad(spec)
+        tr.mid, tr.rad = _f32(mid, device).reshape(B, -1), _f32(rad, device).reshape(B, -1)
+        tr.lower[spec.value_name], tr.upper[spec.value_name] = _f32(lo, device).reshape(B, -1), _f32(up, device).reshape(B, -1)
+    input_views = {spec.value_name}   # the input value and its flatten / reshape views (crown_ibp.py:267-330)
     tr.shape[spec.value_name] = tuple(int(d) for d in spec.center.shape[1:])
     s = _stream_ptr(device)
     for op in task.ops:
@@ -90,15 +100,21 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
             x = op.inputs[0]
             W = params[op.inputs[1]]
             b = params[op.inputs[2]] if len(op.inputs) == 3 else None
-            at_input = x == spec.value_name
+            at_input = x in input_views
             if t == "linear":
                 n_in, n_out = int(W.shape[1]), int(W.shape[0])
                 if _numel(tr.shape[x]) != n_in:
                     raise ValueError(f"linear '{op.name}': weight {tuple(W.shape)} does not match input shape {tr.shape[x]}")
                 yl, yu = torch.empty(B, n_out, device=device), torch.empty(B, n_out, device=device)
-                a, bb, mode = (tr.mid, tr.rad, _lib.IN_MID_RAD) if at_input else (tr.lower[x], tr.upper[x], _lib.IN_LOWER_UPPER)
-                _lib.check(lib.bf_ibp_linear(_lib.ptr(a), _lib.ptr(bb), mode, 0, _lib.ptr(W), _lib.ptr(b), None, 0, None, None,
-                                             _lib.ptr(yl), _lib.ptr(yu), None, B, n_in, n_out, s))
+                if at_input and ball is not None:
+                    row_dev = torch.empty(n_out, dtype=torch.float32, device=device)
+                    _lib.check(lib.bf_row_dual_norms(_lib.ptr(W), n_out, n_in, tr.norm_p, tr.eps, _lib.ptr(row_dev), s))
+                    _lib.check(lib.bf_ibp_linear_lp(_lib.ptr(tr.mid), _lib.ptr(row_dev), _lib.ptr(W), _lib.ptr(b), None, 0, None, None,
+                                                    _lib.ptr(yl), _lib.ptr(yu), None, B, n_in, n_out, s))
+                else:
+                    a, bb, mode = (tr.mid, tr.rad, _lib.IN_MID_RAD) if at_input else (tr.lower[x], tr.upper[x], _lib.IN_LOWER_UPPER)
+                    _lib.check(lib.bf_ibp_linear(_lib.ptr(a), _lib.ptr(bb), mode, 0, _lib.ptr(W), _lib.ptr(b), None, 0, None, None,
+                                                 _lib.ptr(yl), _lib.ptr(yu), None, B, n_in, n_out, s))
                 tr.shape[out] = (n_out,)
             else:
                 if int(op.attrs.get("groups", 1)) != 1 or _pair(op.attrs.get("dilation", 1)) != (1, 1):
@@ -152,6 +168,8 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
                 if _numel(shp) != _numel(tr.shape[x]):
                     raise NotImplementedError("reshape must keep the batch axis and the element count")
             tr.lower[out], tr.upper[out], tr.shape[out] = tr.lower[x], tr.upper[x], shp
+            if x in input_views:
+                input_views.add(out)
         elif t == "concat":
             if int(op.attrs.get("axis", 1)) not in (1, -len(tr.shape[op.inputs[0]])):
                 raise NotImplementedError("concat is supported along the channel axis (axis=1) only")
@@ -293,8 +311,12 @@ def _sweep(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], rela
         raise RuntimeError(f"backward did not reach input value {tr.input_name}")
     fin = adj[tr.input_name]
     res = torch.empty(B, S, device=device)
-    _lib.check(lib.bf_concretize(_lib.ptr(fin.A), _lib.ptr(tr.mid), _lib.ptr(tr.rad), _lib.ptr(fin.d), _lib.ptr(res), side, B, S,
-                                 int(tr.mid.shape[1]), s))
+    if tr.norm_p != _lib.NORM_BOX:
+        _lib.check(lib.bf_concretize_lp(_lib.ptr(fin.A), _lib.ptr(tr.mid), tr.eps, tr.norm_p, _lib.ptr(fin.d), _lib.ptr(res), side, B, S,
+                                        int(tr.mid.shape[1]), s))
+    else:
+        _lib.check(lib.bf_concretize(_lib.ptr(fin.A), _lib.ptr(tr.mid), _lib.ptr(tr.rad), _lib.ptr(fin.d), _lib.ptr(res), side, B, S,
+                                     int(tr.mid.shape[1]), s))
     return res, fin.A
 
 
@@ -346,7 +368,10 @@ def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Ten
     device, B = tr.mid.device, tr.B
     task = module.get_entry_task()
     s = _stream_ptr(device)
-    _lib.check(lib.bf_adjoint_start_box(_lib.ptr(A0), _lib.ptr(tr.mid), _lib.ptr(tr.rad), B, S, int(tr.mid.shape[1]), s))
+    if tr.norm_p != _lib.NORM_BOX:
+        _lib.check(lib.bf_adjoint_start_lp(_lib.ptr(A0), _lib.ptr(tr.mid), tr.eps, tr.norm_p, B, S, int(tr.mid.shape[1]), s))
+    else:
+        _lib.check(lib.bf_adjoint_start_box(_lib.ptr(A0), _lib.ptr(tr.mid), _lib.ptr(tr.rad), B, S, int(tr.mid.shape[1]), s))
     h: Dict[str, torch.Tensor] = {tr.input_name: A0}
     for op in task.ops:
         t, out = op.op_type, op.outputs[0]
@@ -599,12 +624,14 @@ def first_layer_certificate_dag(module: Any, input_spec: Any, relu_split_state: 
     certificate kernel.  Returns (infeasible int32 [B]: 1 found / 0 none, best_value [B], n_halfspaces int32 [B])."""
     lib = _lib.load()
     spec = normalize_input_spec(input_spec)
-    if lp_ball_of(spec) is not None:
-        raise NotImplementedError("the first-layer certificate is implemented for boxes and L-inf balls")
+    ball = lp_ball_of(spec)
     device = _cuda_device(spec.center)
     B = int(spec.center.shape[0])
-    mid, rad, _lo, _up = input_mid_rad(spec)
-    mid, rad = _f32(mid, device).reshape(B, -1).contiguous(), _f32(rad, device).reshape(B, -1).contiguous()
+    if ball is not None:
+        mid, rad = _f32(spec.center, device).reshape(B, -1).contiguous(), None
+    else:
+        mid, rad, _lo, _up = input_mid_rad(spec)
+        mid, rad = _f32(mid, device).reshape(B, -1).contiguous(), _f32(rad, device).reshape(B, -1).contiguous()
     n0 = int(mid.shape[1])
     infeasible = torch.zeros(B, dtype=torch.int32, device=device)
     best = torch.full((B,), float("inf"), dtype=torch.float32, device=device)
@@ -662,8 +689,13 @@ def first_layer_certificate_dag(module: Any, input_spec: Any, relu_split_state: 
     W_all, b_all = torch.cat(W_parts, dim=0).contiguous(), torch.cat(b_parts, dim=0).contiguous()
     sp_all = torch.cat([p.expand(rows_sp, -1) for p in sp_parts], dim=1).contiguous()
     U = int(W_all.shape[0])
-    _lib.check(lib.bf_first_layer_certificate(_lib.ptr(sp_all), U if per_domain else 0, _lib.ptr(W_all), _lib.ptr(b_all), _lib.ptr(mid), _lib.ptr(rad),
-                                              _lib.ptr(infeasible), _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, U, n0, s))
+    if ball is not None:
+        _lib.check(lib.bf_first_layer_certificate_lp(_lib.ptr(sp_all), U if per_domain else 0, _lib.ptr(W_all), _lib.ptr(b_all), _lib.ptr(mid), float(ball[1]),
+                                                     int(ball[0]), _lib.ptr(infeasible), _lib.ptr(best), _lib.ptr(count), int(steps), float(lr),
+                                                     float(tol), B, U, n0, s))
+    else:
+        _lib.check(lib.bf_first_layer_certificate(_lib.ptr(sp_all), U if per_domain else 0, _lib.ptr(W_all), _lib.ptr(b_all), _lib.ptr(mid), _lib.ptr(rad),
+                                                  _lib.ptr(infeasible), _lib.ptr(best), _lib.ptr(count), int(steps), float(lr), float(tol), B, U, n0, s))
     return infeasible, best, count
 
 

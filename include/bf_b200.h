@@ -284,6 +284,13 @@ int bf_first_layer_certificate(const int8_t* split, int split_stride, const floa
                                const float* mid, const float* rad, int* infeasible, float* best_value,
                                int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
                                bf_stream_t stream);
+/* The same on an L1 / L2 ball (p = BF_NORM_L1 | BF_NORM_L2) around center [B,n0]: the maximum of a combination is
+ * a.center + eps * ||a||_q, LpBallPerturbation.concretize_affine boundflow/runtime/perturbation.py:175-222 (the reference's
+ * certificate calls spec.perturbation.concretize_affine, alpha_beta_crown.py:439-441, 476-478). */
+int bf_first_layer_certificate_lp(const int8_t* split, int split_stride, const float* W1, const float* b1,
+                                  const float* center, float eps, int p, int* infeasible, float* best_value,
+                                  int* n_halfspaces, int steps, float lr, float tol, int B, int n1, int n0,
+                                  bf_stream_t stream);
 
 /* Half-space rows of a Conv2d FIRST layer for the certificate above
  *   replaces the conv2d branch of _collect_first_layer_split_halfspaces, boundflow/runtime/alpha_beta_crown.py:325-387
@@ -498,6 +505,9 @@ int bf_chain_alpha_crown_objective(const bf_chain* chain,
  *                         forward Linear step on rows.
  *   bf_adjoint_start_box  start of the gradient sweep: A0 [B,S,n0] (final lower coefficients) becomes
  *                         h0 = mid - sgn(A0) * rad in place, the point at which the lower bound is attained.
+ *   bf_adjoint_start_lp   the same for an Lp ball (p = BF_NORM_L1 | _L2 | _INF): h0 = centre - eps * (the unit-ball point
+ *                         that attains the dual norm of the row), LpBallPerturbation.concretize_affine
+ *                         perturbation.py:175-222.
  *   bf_rows_conv2d_fwd    forward convolution of M rows [M,Ci,Hi,Wi] -> [M,Co,Ho,Wo] (+ bias): the gradient sweep's
  *                         step through a Conv2d layer.  (A Linear layer on rows is bf_crown_relu_linear_bwd without
  *                         slopes on the transposed weight, plus bf_rows_add_broadcast for the bias.)
@@ -521,6 +531,7 @@ int bf_relu_split_apply(float* l, float* u, const int8_t* split, int split_strid
                         bf_stream_t stream);
 int bf_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, bf_stream_t stream);
 int bf_adjoint_start_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, bf_stream_t stream);
+int bf_adjoint_start_lp(float* A0, const float* center, float eps, int p, int B, int S, int n0, bf_stream_t stream);
 int bf_rows_conv2d_fwd(const float* in, const float* W, const float* bias, float* out, int M, int Ci, int Hi, int Wi,
                        int Co, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw, bf_stream_t stream);
 int bf_relu_adjoint_rows(float* G, const float* Ahat, const float* alpha_u, const float* alpha_l, const float* beta_u,

@@ -34,12 +34,25 @@ def _params(module: Any, dtype) -> Dict[str, torch.Tensor]:
     return {k: torch.as_tensor(v).to(dtype) for k, v in module.bindings.get("params", {}).items()}
 
 
-def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_name: str = "input", splits: Optional[Mapping[str, torch.Tensor]] = None):
+def _input_set(lo: torch.Tensor, up: torch.Tensor, ball):
+    """The input set as the chain oracle's InputSet: the box [lo, up], or with ball = (p, eps) the L1 / L2 ball around the
+    box's midpoint (lo / up are then its bounding box centre -/+ eps)."""
+    B = lo.shape[0]
+    if ball is None:
+        return O.box_input(lo.reshape(B, -1), up.reshape(B, -1))
+    return O.lp_ball(((lo + up) / 2.0).reshape(B, -1), float(ball[1]), int(ball[0]))
+
+
+def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_name: str = "input", splits: Optional[Mapping[str, torch.Tensor]] = None,
+                      ball=None):
     """Interval pass.  Returns (env, relu_pre): name -> (lower, upper) in the value's own shape; relu_pre holds the
-    bounds of every ReLU input AFTER its split (crown_ibp.py:210-214), env[x] stays unsplit."""
+    bounds of every ReLU input AFTER its split (crown_ibp.py:210-214), env[x] stays unsplit.  With `ball` = (p, eps) a
+    Linear op on the input value (or a flatten / reshape of it) uses the ball's dual row norms (perturbation.py:102-134),
+    every other consumer the bounding box (crown_ibp.py:126-134, 173-175)."""
     dtype = lo.dtype
     P = _params(module, dtype)
     env: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {input_name: (lo, up)}
+    views = {input_name}
     relu_pre: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {}
     B = lo.shape[0]
 
@@ -56,8 +69,8 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
             l, u = get(op.inputs[0])
             W = P[op.inputs[1]]
             b = P[op.inputs[2]] if len(op.inputs) == 3 else None
-            if op.inputs[0] == input_name:
-                env[out] = O.ibp_first_linear(O.box_input(l.reshape(B, -1), u.reshape(B, -1)), W, b)
+            if op.inputs[0] in views:
+                env[out] = O.ibp_first_linear(_input_set(l, u, ball), W, b)
             else:
                 env[out] = O.ibp_linear(l.reshape(B, -1), u.reshape(B, -1), W, b)
         elif t == "conv2d":
@@ -79,6 +92,8 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
             l, u = get(op.inputs[0])
             shp = (B, -1) if t == "flatten" else (B,) + tuple(int(d) for d in op.attrs.get("shape", ()))[1:]
             env[out] = (l.reshape(shp), u.reshape(shp))
+            if op.inputs[0] in views:
+                views.add(out)
         elif t == "concat":
             ls, us = zip(*[get(n) for n in op.inputs])
             env[out] = (torch.cat(ls, dim=1), torch.cat(us, dim=1))
@@ -88,7 +103,7 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
 
 
 def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: str = "input", output_name: Optional[str] = None,
-                         alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None):
+                         alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None, ball=None):
     """Backward sweep for both sides and box concretisation.  C [B,S,n_out]; alpha / add_l: name of the ReLU input ->
     [B, n] (flattened).  Returns (lower, upper) [B,S]; differentiable in alpha and add_l."""
     task = _task(module)
@@ -158,7 +173,7 @@ def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: s
         else:
             raise NotImplementedError(t)
     Au, Al, bu, bl = adj[input_name]
-    inp = O.box_input(lo.reshape(B, -1), up.reshape(B, -1))
+    inp = _input_set(lo, up, ball)
     return O.concretize(inp, Al, bl, "lower"), O.concretize(inp, Au, bu, "upper")
 
 
@@ -175,14 +190,14 @@ def adaptive_alpha_init_graph(relu_pre) -> Dict[str, torch.Tensor]:
 def alpha_crown_graph(module: Any, lo, up, C, *, steps: int, lr: float, alpha0: Optional[Mapping[str, torch.Tensor]] = None,
                       alpha_init: float = 0.5, splits: Optional[Mapping[str, torch.Tensor]] = None, optimize_beta: bool = False,
                       input_name: str = "input", objective: str = "lower", spec_reduce: str = "mean", soft_tau: float = 1.0,
-                      lb_weight: float = 1.0, ub_weight: float = 1.0, per_batch_params: bool = True):
+                      lb_weight: float = 1.0, ub_weight: float = 1.0, per_batch_params: bool = True, ball=None):
     """alpha (and beta) loop on a graph: `run_alpha_beta_crown_mlp`, alpha_beta_crown.py:716-923, with per-domain
     parameters and best-of (`per_batch_params=True`) or one parameter row for the batch and a whole-batch best-of on
     the mean of the per-domain objectives (False; `run_alpha_crown_mlp`, alpha_crown.py:137-261, is this mode without
     beta).  Objectives lower | upper | gap | both (807-818), reductions mean | sum | min | softmin over the spec rows
     (787-805; max / softmax on the upper side); beta enters the lower objective only (763-785).
     Returns (best_lower, best_upper, best_alpha dict, best_beta dict)."""
-    env, relu_pre = forward_ibp_graph(module, lo, up, input_name=input_name, splits=splits)
+    env, relu_pre = forward_ibp_graph(module, lo, up, input_name=input_name, splits=splits, ball=ball)
     B, dtype = lo.shape[0], lo.dtype
     names = list(relu_pre)
     rows = B if per_batch_params else 1
@@ -217,7 +232,7 @@ def alpha_crown_graph(module: Any, lo, up, C, *, steps: int, lr: float, alpha0: 
         if use_beta:
             add_l = {x: (-betas[x] * split_f[x]) for x in names if split_f[x] is not None}
         a_rows = {x: a.expand(B, -1) for x, a in alphas.items()}
-        lower, upper = crown_backward_graph(module, env, relu_pre, C, lo, up, input_name=input_name, alpha=a_rows, add_l=add_l)
+        lower, upper = crown_backward_graph(module, env, relu_pre, C, lo, up, input_name=input_name, alpha=a_rows, add_l=add_l, ball=ball)
         if objective == "lower":
             metric_b = reduce(lower, "min")
         elif objective == "upper":

@@ -318,6 +318,39 @@ def gen_graph_certificate() -> None:
     save("graph_certificate.npz", **out)
 
 
+def gen_lp_certificate() -> None:
+    """`_is_infeasible_split_first_layer_convex_combo` on L2 / L1 balls (the maximum of a combination is then
+    a.centre + eps * dual norm): the MLP cases, the Conv2d-first-layer cases and the two-branch graph cases of workloads.py."""
+    from boundflow.runtime.alpha_beta_crown import _is_infeasible_split_first_layer_convex_combo
+
+    def rebuild(module):
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id="t0", kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        return BFTaskModule(tasks=[task], entry_task_id="t0", bindings={"params": dict(module.bindings["params"])})
+
+    out = {}
+    module, _layers, x, _lo, _up, cases = W.make_certificate_cases()
+    mlp = (rebuild(module), x, [(n, {"h1": r.unsqueeze(0)}) for n, r in cases])
+    module, _layers, x, _lo, _up, cases = W.make_conv_certificate_cases()
+    cnn = (rebuild(module), x, [(n, {"h1": r.reshape(1, 4, 6, 6)}) for n, r in cases])
+    module, x, _lo, _up, cases = W.make_graph_certificate_cases("linear")
+    graph = (rebuild(module), x, [(n, {k: v.reshape(1, -1) for k, v in rows.items()}) for n, rows in cases])
+    for tag, (m, x, named) in (("mlp", mlp), ("cnn", cnn), ("graph", graph)):
+        for pname, mk, eps in (("l2", InputSpec.l2, 0.5), ("l1", InputSpec.l1, 1.0)):
+            spec = mk(value_name="input", center=x, eps=eps)
+            flags, values = [], []
+            for _name, state in named:
+                bad, _reason, cert = _is_infeasible_split_first_layer_convex_combo(m, spec, relu_split_state=state)
+                flags.append(bool(bad))
+                values.append(float(cert["max_value"]) if cert is not None else np.nan)
+            out[f"{tag}_{pname}_eps"] = np.array(eps)
+            out[f"{tag}_{pname}_infeasible"] = np.array(flags)
+            out[f"{tag}_{pname}_max_value"] = np.array(values)
+        out[f"{tag}_names"] = np.array([n for n, _ in named])
+    save("lp_certificate.npz", **out)
+
+
 def gen_relu_influence() -> None:
     """`run_crown_ibp_mlp_with_relu_influence_from_forward_trace` on the MLP c1 (8 inputs) and the CNN c2 (3 inputs)."""
     from boundflow.runtime.crown_ibp import run_crown_ibp_mlp_with_relu_influence_from_forward_trace
@@ -443,6 +476,35 @@ def gen_graph_objectives() -> None:
         for x, v in bt.beta_by_relu_input.items():
             out[f"{name}_shared_beta_{x}_3"] = v.reshape(-1)
     save("graph_objectives.npz", **out)
+
+
+GRAPH_LP_CASES = ("fanout_mlp", "concat_mlp", "residual_s1")
+
+
+def gen_graph_lp() -> None:
+    """L2 / L1 ball inputs on three of the non-chain graphs (Linear ops on the input: dual row norms; Conv2d ops on the
+    input: bounding box): IBP of the output, CROWN-IBP, and the per-domain alpha loop (adaptive start, 3 steps)."""
+    out = {}
+    cases = W.make_graph_cases()
+    for name in GRAPH_LP_CASES:
+        module, x, _lo, _up, C = cases[name]
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        for pname, mk, eps in (("l2", InputSpec.l2, 0.25), ("l1", InputSpec.l1, 0.6)):
+            spec = mk(value_name="input", center=x, eps=eps)
+            ibp = PythonTaskExecutor().run_ibp(m, spec)
+            crown = run_crown_ibp_mlp(m, spec, linear_spec_C=C)
+            _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+            a0 = adaptive_alpha(relu_pre)
+            b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, steps=3, lr=0.1, per_batch_params=True,
+                                                   warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}))
+            out[f"{name}_{pname}_eps"] = np.array(eps)
+            out[f"{name}_{pname}_ibp_lower"], out[f"{name}_{pname}_ibp_upper"] = ibp.lower, ibp.upper
+            out[f"{name}_{pname}_crown_lower"], out[f"{name}_{pname}_crown_upper"] = crown.lower, crown.upper
+            out[f"{name}_{pname}_alpha_lower_3"], out[f"{name}_{pname}_alpha_upper_3"] = b.lower, b.upper
+    save("graph_lp.npz", **out)
 
 
 def gen_lp_alpha() -> None:
@@ -886,7 +948,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "objectives": gen_objectives, "conv_beta": gen_conv_beta,
               "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha,
               "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
-              "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce}
+              "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce,
+              "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate}
 
 
 def main() -> None:

@@ -158,3 +158,48 @@ def test_two_input_branches_of_a_graph_match_reference_golden_and_oracle(dev, go
     bounds, a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state=one(case["cross_branch_feasible"]), steps=2, lr=0.1,
                                                    per_batch_params=True)
     assert stats.feasibility == "unknown" and tuple(bounds.lower.shape) == (1, 3)
+
+
+@pytest.mark.parametrize("pname,p", [("l2", 2), ("l1", 1)])
+def test_lp_ball_inputs_match_reference_golden_and_oracle(dev, golden, pname, p):
+    """L2 / L1 ball inputs (tests/golden/lp_certificate.npz): a Linear first layer, a Conv2d first layer and the two-branch
+    graph, every case family as one batch of domains; then the single-node pre-check of the alpha-beta function."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import first_layer_certificate, run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from oracle import crown_oracle as O
+
+    g = golden("lp_certificate.npz")
+    mk = InputSpec.l2 if p == 2 else InputSpec.l1
+
+    def check(tag, module, x, split, Wd, bd, rows):
+        D = len(rows)
+        eps = float(g[f"{tag}_{pname}_eps"])
+        spec = mk(value_name="input", center=x.expand((D,) + tuple(x.shape[1:])).contiguous().to(dev), eps=eps)
+        flags, best, count = first_layer_certificate(module, spec, split)
+        flags, best, count = flags.cpu(), best.cpu(), count.cpu()
+        inp = O.lp_ball(x.reshape(1, -1), eps, p)
+        for k, (name, row) in enumerate(rows):
+            assert int(count[k]) == int((row != 0).sum()), (tag, name)
+            assert int(flags[k]) == int(bool(g[f"{tag}_{pname}_infeasible"][k])), (tag, name)
+            o_bad, o_best = O.first_layer_certificate(Wd, bd, inp, row)
+            assert bool(flags[k]) == o_bad, (tag, name)
+            if o_best is not None:
+                assert abs(float(best[k]) - o_best) <= 0.25 * abs(o_best) + 1e-4, (tag, name, float(best[k]), o_best)
+
+    module, layers, x, _lo, _up, cases = W.make_certificate_cases()
+    check("mlp", module, x, {"h1": torch.stack([r for _n, r in cases]).to(dev)}, layers[0]["W"], layers[0]["b"], cases)
+    case = dict(cases)
+    spec1 = mk(value_name="input", center=x.to(dev), eps=float(g[f"mlp_{pname}_eps"]))
+    bounds, a, _b, stats = run_alpha_beta_crown_mlp(module, spec1, relu_split_state={"h1": case["pair_contradiction_uniform_weights"].unsqueeze(0).to(dev)},
+                                                   steps=2, lr=0.1, per_batch_params=True)
+    assert stats.feasibility == "infeasible" and tuple(bounds.lower.shape) == (1, 1) and not a.alpha_by_relu_input
+    cmodule, layers, x, _lo, _up, cases = W.make_conv_certificate_cases()
+    conv = layers[0]
+    Wd, bd = O.conv2d_dense_rows(conv["W"], conv["b"], conv["stride"], conv["padding"], (1, 6, 6), (4, 6, 6))
+    check("cnn", cmodule, x, {"h1": torch.stack([r for _n, r in cases]).reshape(len(cases), 4, 6, 6).to(dev)}, Wd, bd, cases)
+    gmodule, x, _lo, _up, cases = W.make_graph_certificate_cases("linear")
+    P = gmodule.bindings["params"]
+    rows = [(n, torch.cat([r["ha"], r["hb"]])) for n, r in cases]
+    split = {k: torch.stack([r[k] for _n, r in cases]).to(dev) for k in ("ha", "hb")}
+    check("graph", gmodule, x, split, torch.cat([P["Wa"], P["Wb"]]), torch.cat([P["ba"], P["bb"]]), rows)

@@ -97,3 +97,34 @@ def test_alpha_crown_on_lp_ball_matches_reference_golden_and_oracle_gradient(dev
     for r, (gg, rg) in enumerate(zip(grads, ref_grads)):
         scale = float(rg.abs().max()) + 1e-12
         assert float((gg.cpu() - rg).abs().max()) <= 2e-4 * scale + 1e-6, f"gradient of ReLU {r}"
+
+
+@pytest.mark.parametrize("name", ["fanout_mlp", "concat_mlp", "residual_s1"])
+@pytest.mark.parametrize("pname,p", [("l2", 2), ("l1", 1)])
+def test_lp_ball_on_graphs_matches_reference_golden(dev, golden, name, pname, p):
+    """L2 / L1 balls on graphs that are not chains (tests/golden/graph_lp.npz): a Linear op on the input value uses the
+    dual row norms, a Conv2d op the bounding box; the sweep ends in the Lp concretisation and the gradient sweep
+    starts from the Lp adjoint point."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from boundflow_b200.dag import forward_ibp_dag
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("graph_lp.npz")
+    module, x, _lo, _up, C = W.make_graph_cases()[name]
+    B = int(x.shape[0])
+    mk = InputSpec.l2 if p == 2 else InputSpec.l1
+    spec = mk(value_name="input", center=x.to(dev), eps=float(g[f"{name}_{pname}_eps"]))
+    Cd = None if C is None else C.to(dev)
+    ibp = CudaTaskExecutor().run_ibp(module, spec)
+    assert_close(ibp.lower.reshape(B, -1), g[f"{name}_{pname}_ibp_lower"].reshape(B, -1), "ibp lower")
+    assert_close(ibp.upper.reshape(B, -1), g[f"{name}_{pname}_ibp_upper"].reshape(B, -1), "ibp upper")
+    crown = run_crown_ibp_mlp(module, spec, linear_spec_C=Cd)
+    assert_close(crown.lower.reshape(B, -1), g[f"{name}_{pname}_crown_lower"].reshape(B, -1), "crown lower")
+    assert_close(crown.upper.reshape(B, -1), g[f"{name}_{pname}_crown_upper"].reshape(B, -1), "crown upper")
+    tr = forward_ibp_dag(module, spec)
+    a0 = {k: ((tr.pre_l[k] >= 0) | ((tr.pre_l[k] < 0) & (tr.pre_u[k] > 0) & (tr.pre_u[k] > -tr.pre_l[k]))).float() for k in tr.pre_l}
+    b, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=3, lr=0.1, per_batch_params=True, warm_start_alpha=AlphaState(a0))
+    assert_close(b.lower.reshape(B, -1), g[f"{name}_{pname}_alpha_lower_3"].reshape(B, -1), "alpha lower after 3")
+    assert_close(b.upper.reshape(B, -1), g[f"{name}_{pname}_alpha_upper_3"].reshape(B, -1), "alpha upper after 3")

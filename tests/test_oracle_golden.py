@@ -439,6 +439,35 @@ def test_first_layer_certificate_over_two_input_branches(golden, kind):
             assert best < -1e-6 and abs(best - ref) <= 0.5 * abs(ref) + 1e-3, name
 
 
+def _lp_certificate_problems():
+    """(tag, dense first-layer rows, biases, centre, [(name, split row over those rows)]) of the three case families."""
+    module, layers, x, _lo, _up, cases = W.make_certificate_cases()
+    yield "mlp", layers[0]["W"], layers[0]["b"], x, cases
+    _module, layers, x, _lo, _up, cases = W.make_conv_certificate_cases()
+    conv = layers[0]
+    Wd, bd = O.conv2d_dense_rows(conv["W"], conv["b"], conv["stride"], conv["padding"], (1, 6, 6), (4, 6, 6))
+    yield "cnn", Wd, bd, x, cases
+    module, x, _lo, _up, cases = W.make_graph_certificate_cases("linear")
+    P = module.bindings["params"]
+    yield "graph", torch.cat([P["Wa"], P["Wb"]]), torch.cat([P["ba"], P["bb"]]), x, [(n, torch.cat([r["ha"], r["hb"]])) for n, r in cases]
+
+
+def test_first_layer_certificate_on_lp_balls(golden):
+    """The certificate's maximum over an L2 / L1 ball is a.centre + eps * dual norm (alpha_beta_crown.py:439-441, 476-478
+    call the perturbation's concretize_affine); MLP, Conv2d first layer and two-branch graph cases (lp_certificate.npz)."""
+    g = golden("lp_certificate.npz")
+    for tag, Wd, bd, x, cases in _lp_certificate_problems():
+        assert [n for n, _ in cases] == [str(n) for n in g[f"{tag}_names"]]
+        for pname, p in (("l2", 2), ("l1", 1)):
+            inp = O.lp_ball(x.reshape(1, -1), float(g[f"{tag}_{pname}_eps"]), p)
+            for k, (name, row) in enumerate(cases):
+                bad, best = O.first_layer_certificate(Wd, bd, inp, row)
+                assert bad == bool(g[f"{tag}_{pname}_infeasible"][k]), (tag, pname, name)
+                if bad:
+                    ref = float(g[f"{tag}_{pname}_max_value"][k])
+                    assert best < -1e-6 and abs(best - ref) <= 0.5 * abs(ref) + 1e-3, (tag, pname, name)
+
+
 GRAPH_NAMES = ["residual_s1", "residual_s2", "fanout_mlp", "mini_resnet", "concat_cnn", "concat_mlp"]
 
 
@@ -542,6 +571,31 @@ def test_beta_with_min_and_softmin_reductions(golden):
         assert_close(up_b, g[f"{name}_shared_min_upper_3"].reshape(B, -1), f"{name} shared min upper")
         for x, b in beta.items():
             assert_close(b.reshape(-1), g[f"{name}_shared_min_beta_{x}_3"], f"{name} shared beta {x}", atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["fanout_mlp", "concat_mlp", "residual_s1"])
+def test_graph_oracle_on_lp_balls(golden, name):
+    """L2 / L1 ball inputs on non-chain graphs (graph_lp.npz): IBP of the output, CROWN-IBP, the per-domain alpha loop."""
+    from oracle import graph_oracle as GO
+
+    g = golden("graph_lp.npz")
+    module, x, _lo, _up, C = W.make_graph_cases()[name]
+    B = x.shape[0]
+    for pname, p in (("l2", 2), ("l1", 1)):
+        eps = float(g[f"{name}_{pname}_eps"])
+        lo, up, ball = x - eps, x + eps, (p, eps)
+        env, relu_pre = GO.forward_ibp_graph(module, lo, up, ball=ball)
+        assert_close(env["out"][0], g[f"{name}_{pname}_ibp_lower"], f"{pname} ibp lower")
+        assert_close(env["out"][1], g[f"{name}_{pname}_ibp_upper"], f"{pname} ibp upper")
+        n_out = env["out"][0].reshape(B, -1).shape[1]
+        Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+        lower, upper = GO.crown_backward_graph(module, env, relu_pre, Cb, lo, up, ball=ball)
+        assert_close(lower, g[f"{name}_{pname}_crown_lower"].reshape(B, -1), f"{pname} crown lower")
+        assert_close(upper, g[f"{name}_{pname}_crown_upper"].reshape(B, -1), f"{pname} crown upper")
+        a0 = GO.adaptive_alpha_init_graph(relu_pre)
+        lo_a, up_a, _a, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, alpha0=a0, ball=ball)
+        assert_close(lo_a, g[f"{name}_{pname}_alpha_lower_3"].reshape(B, -1), f"{pname} alpha lower after 3")
+        assert_close(up_a, g[f"{name}_{pname}_alpha_upper_3"].reshape(B, -1), f"{pname} alpha upper after 3")
 
 
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
