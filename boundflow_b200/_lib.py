@@ -102,6 +102,7 @@ SIGNATURES = {
     "bf_beta_adam_step": (_i, [_p, _p, _p, _p, _p, _i, _p, _p, _p, _i, _f, _i, _i, _i, _i, _i, _p]),
     "bf_alpha_select_best_paired": (_i, [_p, _p, _p, _p, _i, _i, _i, _f, _f, _f, _p, _i, _i, _p]),
     "bf_rows_scale": (_i, [_p, _p, C.c_longlong, _i, _p]),
+    "bf_rows_colmax_abs": (_i, [_p, _p, _i, _i, _i, _p]),
     "bf_shared_metric": (_i, [_p, C.c_longlong, _p, _p, _i, _p]),
     "bf_copy_if": (_i, [_p, _p, C.c_longlong, _p, _p]),
     "bf_shared_adam_scratch_floats": (_sz, [_i, _i]),

@@ -222,10 +222,54 @@ def forward_ibp_trace_mlp(
     """Reference-shaped result: (interval_env, relu_pre) keyed by value name.
 
     Raises ValueError when any domain's split or constraint is infeasible, as
-    the reference does (crown_ibp.py:92-95, 205-208)."""
+    the reference does (crown_ibp.py:92-95, 205-208).  Graphs that are not chains go through `dag.forward_ibp_dag`."""
+    if needs_graph_path(module):
+        return _graph_trace_to_env(module, input_spec, relu_split_state, relu_pre_constraints)
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state, relu_pre_constraints=relu_pre_constraints)
     _raise_if_infeasible(trace, "relu split")
     return _trace_to_env(trace, normalize_input_spec(input_spec).center.device)
+
+
+def _graph_trace_to_env(module: Any, input_spec: Any, relu_split_state, relu_pre_constraints):
+    """(interval_env, relu_pre) of a graph that is not a chain: every value of the graph, shaped like the value."""
+    from .dag import forward_ibp_dag
+
+    tr = forward_ibp_dag(module, input_spec, relu_split_state, relu_pre_constraints)
+    if int(tr.infeasible.sum()) != 0:
+        raise ValueError("infeasible relu split: lower > upper")
+    dev = normalize_input_spec(input_spec).center.device
+    params = module.bindings.get("params", {})
+    env: Dict[str, IntervalState] = {}
+    for name, lo in tr.lower.items():
+        if name in params:
+            continue
+        shape = (tr.B,) + tuple(tr.shape[name])
+        env[name] = IntervalState(lower=lo.reshape(shape).to(dev), upper=tr.upper[name].reshape(shape).to(dev))
+    relu_pre = {x: IntervalState(lower=tr.pre_l[x].reshape((tr.B,) + tuple(tr.shape[x])).to(dev),
+                                 upper=tr.pre_u[x].reshape((tr.B,) + tuple(tr.shape[x])).to(dev)) for x in dict.fromkeys(tr.relu_inputs)}
+    env["__trace__"] = tr  # type: ignore[assignment]
+    return env, relu_pre
+
+
+def _graph_trace_from_env(module: Any, input_spec: Any, interval_env: Mapping[str, Any], relu_pre: Mapping[str, Any]):
+    """The device trace of a graph for a backward-only call: the one `forward_ibp_trace_mlp` left in `interval_env` when
+    its ReLU bounds are still the caller's, else a fresh interval pass whose ReLU bounds are replaced by `relu_pre`."""
+    from .dag import DagTrace, forward_ibp_dag
+
+    spec = normalize_input_spec(input_spec)
+    B = int(spec.center.shape[0])
+    tr = interval_env.get("__trace__") if isinstance(interval_env, Mapping) else None
+    if isinstance(tr, DagTrace) and tr.B == B and set(relu_pre) == set(tr.pre_l) and all(
+            relu_pre[x].lower.data_ptr() == tr.pre_l[x].data_ptr() for x in tr.pre_l):
+        return tr
+    tr = forward_ibp_dag(module, spec)
+    device = tr.mid.device
+    for x in dict.fromkeys(tr.relu_inputs):
+        if x not in relu_pre:
+            raise KeyError(f"missing relu pre-activation bounds for value: {x}")
+        tr.pre_l[x] = _f32(relu_pre[x].lower, device).reshape(B, -1).contiguous()
+        tr.pre_u[x] = _f32(relu_pre[x].upper, device).reshape(B, -1).contiguous()
+    return tr
 
 
 def _trace_to_env(trace: ForwardTrace, out_device: torch.device):
@@ -447,6 +491,14 @@ def run_crown_ibp_mlp_from_forward_trace(
     """Backward-only CROWN given a forward trace (crown_ibp.py:2136-2230)."""
     if relu_pre_add_coeff_u:
         raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
+    if needs_graph_path(module):
+        from .dag import crown_dag
+
+        lo, up, _tr = crown_dag(module, input_spec, linear_spec_C, output_value=output_value,
+                                trace=_graph_trace_from_env(module, input_spec, interval_env, relu_pre), relu_alpha=relu_alpha,
+                                relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+        dev = normalize_input_spec(input_spec).center.device
+        return IntervalState(lower=lo.to(dev), upper=up.to(dev))
     trace = _trace_from_env(module, input_spec, interval_env, relu_pre)
     lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
     dev = normalize_input_spec(input_spec).center.device
@@ -464,6 +516,16 @@ def run_crown_ibp_mlp_with_relu_influence_from_forward_trace(
 ) -> Tuple[IntervalState, Dict[str, torch.Tensor]]:
     """Bounds plus, per ReLU input, the influence max(max_s |A_u|, max_s |A_l|) of the backward
     coefficients that reach it (crown_ibp.py:2201-2240), shaped like the pre-activation."""
+    if needs_graph_path(module):
+        from .dag import crown_influence_dag
+
+        lo, up, infl_d, tr = crown_influence_dag(module, input_spec, linear_spec_C, output_value=output_value,
+                                                 trace=_graph_trace_from_env(module, input_spec, interval_env, relu_pre))
+        if set(infl_d) != set(relu_pre):
+            raise ValueError("ReLU objective influence coverage differs")
+        dev = normalize_input_spec(input_spec).center.device
+        return (IntervalState(lower=lo.to(dev), upper=up.to(dev)),
+                {n: infl_d[n].reshape((tr.B,) + tuple(tr.shape[n])).to(dev) for n in relu_pre})
     trace = _trace_from_env(module, input_spec, interval_env, relu_pre)
     infl: List[torch.Tensor] = []
     lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, influence_out=infl)

@@ -696,6 +696,12 @@ extern "C" int bf_rows_scale(float* A, const float* w, long long M, int n, bf_st
   return bf::launch_scale_rows(A, w, M, n, bf::as_stream(stream));
 }
 
+extern "C" int bf_rows_colmax_abs(const float* A, float* out, int B, int S, int n, bf_stream_t stream) {
+  BF_REQUIRE(A && out, BF_E_INVALID, "bf_rows_colmax_abs: null tensor");
+  BF_REQUIRE(B > 0 && S > 0 && n > 0, BF_E_INVALID, "bf_rows_colmax_abs: bad sizes");
+  return bf::launch_colmax_abs(A, out, B, S, n, bf::as_stream(stream));
+}
+
 extern "C" int bf_shared_metric(const float* values, long long M, float* best_metric, int* improve, int first, bf_stream_t stream) {
   BF_REQUIRE(values && best_metric && improve, BF_E_INVALID, "bf_shared_metric: null tensor");
   BF_REQUIRE(M > 0, BF_E_INVALID, "bf_shared_metric: bad size");

@@ -68,9 +68,12 @@ def _params(module: Any, device: torch.device) -> Dict[str, torch.Tensor]:
     return out
 
 
-def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Mapping[str, torch.Tensor]] = None) -> DagTrace:
+def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+                    relu_pre_constraints: Optional[Mapping[str, Any]] = None) -> DagTrace:
     """One IBP pass over the ops in order (`_forward_ibp_trace_mlp`, crown_ibp.py:101-342); `relu_split_state` maps
-    the name of a ReLU input to its int8 split assignment ([B, *shape] or one shared row)."""
+    the name of a ReLU input to its int8 split assignment ([B, *shape] or one shared row); `relu_pre_constraints` maps
+    every ReLU input, in graph order, to an interval that its bounds are intersected with before the split
+    (crown_ibp.py:186-209, 338-341)."""
     lib = _lib.load()
     spec = normalize_input_spec(input_spec)
     ball = lp_ball_of(spec)
@@ -133,6 +136,16 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
             x = op.inputs[0]
             tr.relu_inputs.append(x)
             pl, pu = tr.lower[x], tr.upper[x]
+            if relu_pre_constraints is not None:
+                c = relu_pre_constraints.get(x)
+                shape_x = (B,) + tuple(tr.shape[x])
+                if (c is None or not hasattr(c, "lower") or tuple(c.lower.shape) != shape_x or tuple(c.upper.shape) != shape_x
+                        or not bool(torch.isfinite(c.lower).all()) or not bool(torch.isfinite(c.upper).all()) or not bool((c.lower <= c.upper).all())):
+                    raise ValueError(f"ReLU pre-activation constraint schema differs for {x}")
+                pl = torch.maximum(pl, _f32(c.lower, device).reshape(B, -1))
+                pu = torch.minimum(pu, _f32(c.upper, device).reshape(B, -1))
+                if bool((pl > pu).any()):
+                    raise ValueError(f"infeasible ReLU pre-activation intersection for {x}")
             sp = relu_split_state.get(x) if relu_split_state else None
             if sp is not None:
                 n = _numel(tr.shape[x])
@@ -181,6 +194,8 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
             tr.shape[out] = (sum(sh[0] for sh in shapes),) + tuple(shapes[0][1:])
         else:
             raise NotImplementedError(f"unsupported op_type in the CUDA graph backend: {t}")
+    if relu_pre_constraints is not None and tuple(relu_pre_constraints) != tuple(dict.fromkeys(tr.relu_inputs)):
+        raise ValueError("ReLU pre-activation constraint identities differ")
     return tr
 
 
@@ -355,6 +370,35 @@ def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor
     lo, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=add_l)
     up, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
     return lo, up, tr
+
+
+def crown_influence_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor], *, output_value: Optional[str] = None,
+                        trace: Optional[DagTrace] = None):
+    """CROWN-IBP on a graph plus, per ReLU input, max(max_s |A_u|, max_s |A_l|) of the coefficients that arrive at the
+    ReLU's output in the two sweeps (`run_crown_ibp_mlp_with_relu_influence_from_forward_trace`, crown_ibp.py:1810-1834,
+    2201-2240).  Returns (lower, upper, {name: [B, n]}, trace); a ReLU the sweep never reaches has no entry."""
+    lib = _lib.load()
+    spec = normalize_input_spec(input_spec)
+    tr = trace if trace is not None else forward_ibp_dag(module, spec)
+    device, B = tr.mid.device, tr.B
+    params = _params(module, device)
+    output_value = _output_value(module, tr, output_value)
+    C = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
+    S = int(C.shape[1])
+    s = _stream_ptr(device)
+    relax = _relax(lib, tr, None, s)
+    at_l: Dict[str, torch.Tensor] = {}
+    at_u: Dict[str, torch.Tensor] = {}
+    lo, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, ahat=at_l)
+    up, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value, ahat=at_u)
+    influence: Dict[str, torch.Tensor] = {}
+    for x in at_l:
+        n = _numel(tr.shape[x])
+        out = torch.zeros(B, n, dtype=torch.float32, device=device)
+        for A in (at_l[x], at_u[x]):
+            _lib.check(lib.bf_rows_colmax_abs(_lib.ptr(A), _lib.ptr(out), B, S, n, s))
+        influence[x] = out
+    return lo, up, influence, tr
 
 
 def _adjoint_forward(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], relax, A0: torch.Tensor, ahat: Dict[str, torch.Tensor],

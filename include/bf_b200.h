@@ -554,6 +554,8 @@ int bf_beta_adam_step(float* beta, float* m, float* v, float* gsum, const int8_t
  *                         row_weight [B,2S] or NULL receives d objective / d cur (all >= 0 for weights >= 0).
  *   bf_rows_scale         A[r,:] *= w[r] for M rows of n: the row weights applied to the coefficients kept at every ReLU
  *                         before the gradient sweep.
+ *   bf_rows_colmax_abs    out[b,j] = max(out[b,j], max_s |A[b,s,j]|): the objective influence of a ReLU from the
+ *                         coefficients that reach it (crown_ibp.py:1810-1834), one call per side.
  *   bf_shared_metric      whole-batch metric mean(values[0..M)) with strict best-of against best_metric[0]; improve[0]
  *                         (alpha_crown.py:215-220; first != 0 initialises).
  *   bf_copy_if            dst = src when flag[0] != 0 (the batch's best bounds).
@@ -566,6 +568,7 @@ int bf_alpha_select_best_paired(const float* cur, float* best_rows, float* best_
                                 int spec_reduce, float soft_tau, float lb_weight, float ub_weight, float* row_weight, int B,
                                 int S, bf_stream_t stream);
 int bf_rows_scale(float* A, const float* w, long long M, int n, bf_stream_t stream);
+int bf_rows_colmax_abs(const float* A, float* out, int B, int S, int n, bf_stream_t stream);
 int bf_shared_metric(const float* values, long long M, float* best_metric, int* improve, int first, bf_stream_t stream);
 int bf_copy_if(const float* src, float* dst, long long n, const int* flag, bf_stream_t stream);
 size_t bf_shared_adam_scratch_floats(int B, int n);

@@ -44,11 +44,12 @@ def _input_set(lo: torch.Tensor, up: torch.Tensor, ball):
 
 
 def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_name: str = "input", splits: Optional[Mapping[str, torch.Tensor]] = None,
-                      ball=None):
+                      ball=None, constraints: Optional[Mapping[str, Tuple[torch.Tensor, torch.Tensor]]] = None):
     """Interval pass.  Returns (env, relu_pre): name -> (lower, upper) in the value's own shape; relu_pre holds the
     bounds of every ReLU input AFTER its split (crown_ibp.py:210-214), env[x] stays unsplit.  With `ball` = (p, eps) a
     Linear op on the input value (or a flatten / reshape of it) uses the ball's dual row norms (perturbation.py:102-134),
-    every other consumer the bounding box (crown_ibp.py:126-134, 173-175)."""
+    every other consumer the bounding box (crown_ibp.py:126-134, 173-175).  `constraints[x]` = (lower, upper) is
+    intersected with the bounds of ReLU input x before its split (crown_ibp.py:186-209)."""
     dtype = lo.dtype
     P = _params(module, dtype)
     env: Dict[str, Tuple[torch.Tensor, torch.Tensor]] = {input_name: (lo, up)}
@@ -81,6 +82,11 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
         elif t == "relu":
             x = op.inputs[0]
             l, u = get(x)
+            if constraints is not None:
+                cl, cu = constraints[x]
+                l, u = torch.maximum(l, cl.reshape(l.shape)), torch.minimum(u, cu.reshape(u.shape))
+                if bool((l > u).any()):
+                    raise ValueError(f"infeasible ReLU pre-activation intersection for {x}")
             if splits is not None and x in splits and splits[x] is not None:
                 l, u, _infeasible = O.apply_relu_split(l, u, splits[x])
             relu_pre[x] = (l, u)
@@ -103,7 +109,8 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
 
 
 def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: str = "input", output_name: Optional[str] = None,
-                         alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None, ball=None):
+                         alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None, ball=None,
+                         influence_out: Optional[Dict[str, torch.Tensor]] = None):
     """Backward sweep for both sides and box concretisation.  C [B,S,n_out]; alpha / add_l: name of the ReLU input ->
     [B, n] (flattened).  Returns (lower, upper) [B,S]; differentiable in alpha and add_l."""
     task = _task(module)
@@ -146,6 +153,8 @@ def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: s
         elif t == "relu":
             x = op.inputs[0]
             l, u = relu_pre[x]
+            if influence_out is not None:  # crown_ibp.py:1810-1834: the coefficients that arrive at the ReLU's output
+                influence_out[x] = torch.maximum(Au.abs().amax(dim=1), Al.abs().amax(dim=1)).detach()
             a = alpha.get(x) if alpha is not None else None
             au_, bu_, al_, bl_ = O.relu_slopes(l, u, a)
             ad = add_l.get(x) if add_l is not None else None

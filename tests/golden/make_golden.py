@@ -507,6 +507,42 @@ def gen_graph_lp() -> None:
     save("graph_lp.npz", **out)
 
 
+GRAPH_TRACE_CASES = ("fanout_mlp", "mini_resnet", "concat_cnn")
+
+
+def gen_graph_trace() -> None:
+    """The trace-level functions on non-chain graphs: `_forward_ibp_trace_mlp` with `relu_pre_constraints` (every ReLU
+    interval shrunk by 10 % of its width on both ends), `run_crown_ibp_mlp_from_forward_trace` on that trace, and
+    `run_crown_ibp_mlp_with_relu_influence_from_forward_trace` on the unconstrained one."""
+    from boundflow.runtime.crown_ibp import run_crown_ibp_mlp_with_relu_influence_from_forward_trace
+
+    out = {}
+    cases = W.make_graph_cases()
+    for name in GRAPH_TRACE_CASES:
+        module, _x, lo, up, C = cases[name]
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        B = int(lo.shape[0])
+        n_out = int(env["out"].lower.reshape(B, -1).shape[1])
+        Cb = C if C is not None else torch.eye(n_out).unsqueeze(0).expand(B, -1, -1).contiguous()
+        cons = {x: IntervalState(lower=st.lower + 0.1 * (st.upper - st.lower), upper=st.upper - 0.1 * (st.upper - st.lower)) for x, st in relu_pre.items()}
+        env2, pre2 = _forward_ibp_trace_mlp(m, spec, relu_pre_constraints=cons)
+        for x, st in pre2.items():
+            out[f"{name}_cons_pre_{x}_lower"], out[f"{name}_cons_pre_{x}_upper"] = st.lower.reshape(B, -1), st.upper.reshape(B, -1)
+        out[f"{name}_cons_out_lower"], out[f"{name}_cons_out_upper"] = env2["out"].lower, env2["out"].upper
+        crown = run_crown_ibp_mlp_from_forward_trace(m, spec, interval_env=env2, relu_pre=pre2, linear_spec_C=Cb)
+        out[f"{name}_cons_crown_lower"], out[f"{name}_cons_crown_upper"] = crown.lower, crown.upper
+        bounds, infl = run_crown_ibp_mlp_with_relu_influence_from_forward_trace(m, spec, interval_env=env, relu_pre=relu_pre, linear_spec_C=Cb)
+        out[f"{name}_infl_lower"], out[f"{name}_infl_upper"] = bounds.lower, bounds.upper
+        for x, v in infl.items():
+            out[f"{name}_infl_{x}"] = v.reshape(B, -1)
+    save("graph_trace.npz", **out)
+
+
 def gen_lp_alpha() -> None:
     """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
     wl = W.make_workload("c3", batch=8)
@@ -949,7 +985,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "conv_certificate": gen_conv_certificate, "graph_alpha": gen_graph_alpha,
               "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
               "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce,
-              "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate}
+              "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate,
+              "graph_trace": gen_graph_trace}
 
 
 def main() -> None:

@@ -155,6 +155,59 @@ def test_graph_objectives_and_shared_mode_match_reference_golden(dev, golden, na
             assert_close(bt.beta_by_relu_input[x].reshape(-1), g[f"{name}_shared_beta_{x}_3"], f"shared beta {x} after 3", atol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["fanout_mlp", "mini_resnet", "concat_cnn"])
+def test_trace_level_functions_on_graphs_match_reference_golden(dev, golden, name):
+    """`forward_ibp_trace_mlp(relu_pre_constraints=...)`, `run_crown_ibp_mlp_from_forward_trace` (with the trace it left in
+    the environment, and with bounds handed over as plain tensors) and the ReLU-influence variant on graphs that are
+    not chains (tests/golden/graph_trace.npz)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import (forward_ibp_trace_mlp, run_crown_ibp_mlp_from_forward_trace,
+                                      run_crown_ibp_mlp_with_relu_influence_from_forward_trace)
+    from boundflow_b200.ir import InputSpec, IntervalState
+
+    g = golden("graph_trace.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    env, relu_pre = forward_ibp_trace_mlp(module, spec)
+    n_out = int(env["out"].lower.reshape(B, -1).shape[1])
+    Cd = (C if C is not None else torch.eye(n_out).unsqueeze(0).expand(B, -1, -1).contiguous()).to(dev)
+    cons = {x: IntervalState(lower=st.lower + 0.1 * (st.upper - st.lower), upper=st.upper - 0.1 * (st.upper - st.lower)) for x, st in relu_pre.items()}
+    env2, pre2 = forward_ibp_trace_mlp(module, spec, relu_pre_constraints=cons)
+    for x, st in pre2.items():
+        assert tuple(st.lower.shape) == tuple(relu_pre[x].lower.shape)
+        assert_close(st.lower.reshape(B, -1), g[f"{name}_cons_pre_{x}_lower"], f"constrained pre {x} lower")
+        assert_close(st.upper.reshape(B, -1), g[f"{name}_cons_pre_{x}_upper"], f"constrained pre {x} upper")
+    assert_close(env2["out"].lower, g[f"{name}_cons_out_lower"], "constrained ibp lower")
+    assert_close(env2["out"].upper, g[f"{name}_cons_out_upper"], "constrained ibp upper")
+    crown = run_crown_ibp_mlp_from_forward_trace(module, spec, interval_env=env2, relu_pre=pre2, linear_spec_C=Cd)
+    assert_close(crown.lower.reshape(B, -1), g[f"{name}_cons_crown_lower"].reshape(B, -1), "crown on the constrained trace, lower")
+    assert_close(crown.upper.reshape(B, -1), g[f"{name}_cons_crown_upper"].reshape(B, -1), "crown on the constrained trace, upper")
+    # bounds handed over as copies (no device trace to reuse): the same result
+    plain_env = {k: v for k, v in env2.items() if k != "__trace__"}
+    plain_pre = {x: IntervalState(lower=st.lower.clone(), upper=st.upper.clone()) for x, st in pre2.items()}
+    again = run_crown_ibp_mlp_from_forward_trace(module, spec, interval_env=plain_env, relu_pre=plain_pre, linear_spec_C=Cd)
+    assert_close(again.lower, crown.lower, "crown from copied bounds, lower")
+    assert_close(again.upper, crown.upper, "crown from copied bounds, upper")
+    bounds, infl = run_crown_ibp_mlp_with_relu_influence_from_forward_trace(module, spec, interval_env=env, relu_pre=relu_pre, linear_spec_C=Cd)
+    assert_close(bounds.lower.reshape(B, -1), g[f"{name}_infl_lower"].reshape(B, -1), "influence call lower")
+    assert_close(bounds.upper.reshape(B, -1), g[f"{name}_infl_upper"].reshape(B, -1), "influence call upper")
+    assert list(infl) == list(relu_pre)
+    for x, v in infl.items():
+        assert tuple(v.shape) == tuple(relu_pre[x].lower.shape)
+        assert_close(v.reshape(B, -1), g[f"{name}_infl_{x}"], f"influence {x}")
+    # constraint errors as in the reference
+    bad = dict(cons)
+    first = next(iter(bad))
+    bad[first] = IntervalState(lower=relu_pre[first].upper + 1.0, upper=relu_pre[first].upper + 2.0)
+    with pytest.raises(ValueError, match="infeasible ReLU pre-activation intersection"):
+        forward_ibp_trace_mlp(module, spec, relu_pre_constraints=bad)
+    with pytest.raises(ValueError, match="schema differs"):
+        forward_ibp_trace_mlp(module, spec, relu_pre_constraints={x: IntervalState(lower=st.lower[:, :1], upper=st.upper[:, :1]) for x, st in cons.items()})
+    with pytest.raises(ValueError, match="identities differ"):
+        forward_ibp_trace_mlp(module, spec, relu_pre_constraints={**cons, "not_a_relu_input": cons[first]})
+
+
 def test_building_blocks_against_torch(dev):
     """bf_crown_relu_bwd (incl. rows wider than one chunk) and bf_accumulate."""
     from boundflow_b200 import _lib

@@ -598,6 +598,36 @@ def test_graph_oracle_on_lp_balls(golden, name):
         assert_close(up_a, g[f"{name}_{pname}_alpha_upper_3"].reshape(B, -1), f"{pname} alpha upper after 3")
 
 
+@pytest.mark.parametrize("name", ["fanout_mlp", "mini_resnet", "concat_cnn"])
+def test_graph_oracle_trace_level_functions(golden, name):
+    """`_forward_ibp_trace_mlp(relu_pre_constraints=...)`, `run_crown_ibp_mlp_from_forward_trace` and the ReLU-influence
+    variant on non-chain graphs (graph_trace.npz)."""
+    from oracle import graph_oracle as GO
+
+    g = golden("graph_trace.npz")
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = lo.shape[0]
+    env, relu_pre = GO.forward_ibp_graph(module, lo, up)
+    n_out = env["out"][0].reshape(B, -1).shape[1]
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+    cons = {x: (l + 0.1 * (u - l), u - 0.1 * (u - l)) for x, (l, u) in relu_pre.items()}
+    env2, pre2 = GO.forward_ibp_graph(module, lo, up, constraints=cons)
+    for x, (l, u) in pre2.items():
+        assert_close(l.reshape(B, -1), g[f"{name}_cons_pre_{x}_lower"], f"constrained pre {x} lower")
+        assert_close(u.reshape(B, -1), g[f"{name}_cons_pre_{x}_upper"], f"constrained pre {x} upper")
+    assert_close(env2["out"][0], g[f"{name}_cons_out_lower"], "constrained ibp lower")
+    assert_close(env2["out"][1], g[f"{name}_cons_out_upper"], "constrained ibp upper")
+    lower, upper = GO.crown_backward_graph(module, env2, pre2, Cb, lo, up)
+    assert_close(lower, g[f"{name}_cons_crown_lower"].reshape(B, -1), "crown on the constrained trace, lower")
+    assert_close(upper, g[f"{name}_cons_crown_upper"].reshape(B, -1), "crown on the constrained trace, upper")
+    infl = {}
+    lower, upper = GO.crown_backward_graph(module, env, relu_pre, Cb, lo, up, influence_out=infl)
+    assert_close(lower, g[f"{name}_infl_lower"].reshape(B, -1), "influence call lower")
+    assert set(infl) == set(relu_pre)
+    for x, v in infl.items():
+        assert_close(v.reshape(B, -1), g[f"{name}_infl_{x}"], f"influence {x}")
+
+
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
 GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
 
