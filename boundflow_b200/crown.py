@@ -378,6 +378,7 @@ def crown_from_trace(
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
     sides: Sequence[int] = (_lib.SIDE_LOWER, _lib.SIDE_UPPER),
     identity_rows: Optional[Tuple[int, int]] = None,
+    relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None,
     influence_out: Optional[List[torch.Tensor]] = None,
 ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Backward sweep(s) on the device; returns (lower, upper) [B,S] CUDA tensors.
@@ -401,16 +402,20 @@ def crown_from_trace(
         S = int(C.shape[1])
     n_relu = sum(1 for i in chain.relu_layer_ids if i < upto)
     au, bu, al, keep = _relaxations(trace, relu_alpha, n_relu)
-    add = None
-    if relu_pre_add_coeff_l:
-        add = [None] * n_relu
+    def add_terms(raw):
+        """Per ReLU the term added to one side's coefficients behind it ([B,n] or one shared row), or None."""
+        if not raw:
+            return None
+        terms = [None] * n_relu
         for r in range(n_relu):
             name = chain.relu_input_names[r]
-            if name in relu_pre_add_coeff_l:
-                t = relu_pre_add_coeff_l[name]
-                t = t.detach().to(device=device, dtype=torch.float32)
+            if name in raw and raw[name] is not None:
+                t = raw[name].detach().to(device=device, dtype=torch.float32)
                 n = chain.relu_widths[r]
-                add[r] = (t.reshape(1, n).expand(B, n) if t.numel() == n else t.reshape(B, n)).contiguous()
+                terms[r] = (t.reshape(1, n).expand(B, n) if t.numel() == n else t.reshape(B, n)).contiguous()
+        return terms
+
+    add_by_side = {_lib.SIDE_LOWER: add_terms(relu_pre_add_coeff_l), _lib.SIDE_UPPER: add_terms(relu_pre_add_coeff_u)}
     nbytes = int(chain.lib.bf_chain_crown_workspace_bytes(chain.handle, B, S, upto))
     ws = _Workspace.get(device, nbytes)
     outs: List[Optional[torch.Tensor]] = [None, None]
@@ -423,7 +428,7 @@ def crown_from_trace(
     for side in sides:
         out = torch.empty(B, S, dtype=torch.float32, device=device)
         tail = (
-            _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add),
+            _lib.ptr_array(au), _lib.ptr_array(bu), _lib.ptr_array(al), _lib.ptr_array(add_by_side[side]),
             _lib.ptr(trace.mid), _lib.ptr(trace.rad) if trace.norm_p == _lib.NORM_BOX else None, int(trace.norm_p), float(trace.eps),
             _lib.ptr(out), _lib.ptr(ws), ws.numel(), B, S, _stream_ptr(device),
         )
@@ -462,16 +467,16 @@ def run_crown_ibp_mlp(
 ) -> IntervalState:
     """IBP trace + one CROWN backward sweep per side (crown_ibp.py:2054-2133).  Graphs with add / concat /
     fan-out go through the general graph path (`dag.py`), chains through the fused sweeps."""
-    if relu_pre_add_coeff_u:
-        raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
     if needs_graph_path(module):
         from .dag import run_crown_ibp_dag
 
         return run_crown_ibp_dag(module, input_spec, linear_spec_C=linear_spec_C, output_value=output_value, relu_alpha=relu_alpha,
-                                 relu_pre_add_coeff_l=relu_pre_add_coeff_l, relu_split_state=relu_split_state)
+                                 relu_pre_add_coeff_l=relu_pre_add_coeff_l, relu_pre_add_coeff_u=relu_pre_add_coeff_u,
+                                 relu_split_state=relu_split_state)
     trace = ibp_trace(module, input_spec, relu_split_state=relu_split_state)
     _raise_if_infeasible(trace, "relu split")
-    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l,
+                              relu_pre_add_coeff_u=relu_pre_add_coeff_u)
     dev = normalize_input_spec(input_spec).center.device
     return IntervalState(lower=lo.to(dev), upper=up.to(dev))
 
@@ -489,18 +494,17 @@ def run_crown_ibp_mlp_from_forward_trace(
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
 ) -> IntervalState:
     """Backward-only CROWN given a forward trace (crown_ibp.py:2136-2230)."""
-    if relu_pre_add_coeff_u:
-        raise NotImplementedError("relu_pre_add_coeff_u is not supported by the CUDA backend")
     if needs_graph_path(module):
         from .dag import crown_dag
 
         lo, up, _tr = crown_dag(module, input_spec, linear_spec_C, output_value=output_value,
                                 trace=_graph_trace_from_env(module, input_spec, interval_env, relu_pre), relu_alpha=relu_alpha,
-                                relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+                                relu_pre_add_coeff_l=relu_pre_add_coeff_l, relu_pre_add_coeff_u=relu_pre_add_coeff_u)
         dev = normalize_input_spec(input_spec).center.device
         return IntervalState(lower=lo.to(dev), upper=up.to(dev))
     trace = _trace_from_env(module, input_spec, interval_env, relu_pre)
-    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+    lo, up = crown_from_trace(trace, linear_spec_C, output_value=output_value, relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l,
+                              relu_pre_add_coeff_u=relu_pre_add_coeff_u)
     dev = normalize_input_spec(input_spec).center.device
     return IntervalState(lower=lo.to(dev), upper=up.to(dev))
 

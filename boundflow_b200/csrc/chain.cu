@@ -541,7 +541,7 @@ static int crown_sweep(const bf_chain* chain, int upto_layer, int side, const fl
     if (pending >= 0) {
       if (side == BF_SIDE_LOWER) { dpos = alpha_l[pending]; dneg = alpha_u[pending]; eneg = beta_u[pending]; }
       else { dpos = alpha_u[pending]; dneg = alpha_l[pending]; epos = beta_u[pending]; }
-      if (add && add[pending] && side == BF_SIDE_LOWER) ad = add[pending];
+      if (add && add[pending]) ad = add[pending];  // the caller passes the add terms of the side it asks for
     }
     int rc;
     if (windowed && !(L.op == BF_OP_CONV2D && pending >= 0 && ad == nullptr && win.C == L.Co && win.H == L.Ho && win.W == L.Wo &&

@@ -238,8 +238,8 @@ def _relax(lib, tr: DagTrace, relu_alpha: Optional[Mapping[str, torch.Tensor]], 
 
 def _sweep(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], relax, C: torch.Tensor, side: int, output_value: str, *,
            add_l: Optional[Mapping[str, torch.Tensor]] = None, ahat: Optional[Dict[str, torch.Tensor]] = None):
-    """One backward sweep of one side.  Returns (bounds [B,S], final coefficients [B,S,n0]).  `add_l[x]` ([B,n], the
-    split term of beta-CROWN) is added to the lower coefficients behind ReLU x; `ahat` (a dict) receives the
+    """One backward sweep of one side.  Returns (bounds [B,S], final coefficients [B,S,n0]).  `add_l[x]` ([B,n], e.g. the
+    split term of beta-CROWN on the lower side) is added to this side's coefficients behind ReLU x; `ahat` (a dict) receives the
     coefficients that arrive at every ReLU's output, which the gradient sweep needs."""
     device, B = tr.mid.device, tr.B
     task = module.get_entry_task()
@@ -297,7 +297,7 @@ def _sweep(lib, module: Any, tr: DagTrace, params: Dict[str, torch.Tensor], rela
                                              _lib.ptr(st.d), 1, _lib.ptr(scratch), scratch.numel(), B, S, n, s))
             if ahat is not None:
                 ahat[x] = st.A  # left untouched by the call above
-            if add_l is not None and side == _lib.SIDE_LOWER and add_l.get(x) is not None:
+            if add_l is not None and add_l.get(x) is not None:
                 _lib.check(lib.bf_rows_add_broadcast(_lib.ptr(Ap), _lib.ptr(add_l[x]), n, B, S, n, s))
             push(x, Ap, st.d)
         elif t == "add":
@@ -349,10 +349,12 @@ def _output_value(module: Any, tr: DagTrace, output_value: Optional[str]) -> str
 def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor], *, output_value: Optional[str] = None,
               trace: Optional[DagTrace] = None, relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
               relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
-              relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, DagTrace]:
+              relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+              relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor, DagTrace]:
     """CROWN-IBP on a graph: IBP bounds for every ReLU input (with the ReLU splits, if any), then one backward sweep
-    per side; `relu_alpha` overrides the lower slopes of unstable neurons, `relu_pre_add_coeff_l` is added to the lower
-    coefficients behind a ReLU (crown_ibp.py:2136-2152).  Returns (lower, upper) [B,S] CUDA tensors and the trace."""
+    per side; `relu_alpha` overrides the lower slopes of unstable neurons, `relu_pre_add_coeff_l` / `_u` is added to the
+    lower / upper coefficients behind a ReLU (crown_ibp.py:1270-1296, 2136-2152).  Returns (lower, upper) [B,S] CUDA
+    tensors and the trace."""
     lib = _lib.load()
     spec = normalize_input_spec(input_spec)
     tr = trace if trace is not None else forward_ibp_dag(module, spec, relu_split_state)
@@ -364,11 +366,13 @@ def crown_dag(module: Any, input_spec: Any, linear_spec_C: Optional[torch.Tensor
     C = _spec_rows(linear_spec_C, B, _numel(tr.shape[output_value]), device)
     s = _stream_ptr(device)
     relax = _relax(lib, tr, relu_alpha, s)
-    add_l = None
-    if relu_pre_add_coeff_l:
-        add_l = {x: _f32(v, device).reshape(-1, _numel(tr.shape[x])).expand(B, -1).contiguous() for x, v in relu_pre_add_coeff_l.items() if v is not None}
-    lo, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=add_l)
-    up, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value)
+    def terms(raw):
+        if not raw:
+            return None
+        return {x: _f32(v, device).reshape(-1, _numel(tr.shape[x])).expand(B, -1).contiguous() for x, v in raw.items() if v is not None}
+
+    lo, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_LOWER, output_value, add_l=terms(relu_pre_add_coeff_l))
+    up, _ = _sweep(lib, module, tr, params, relax, C, _lib.SIDE_UPPER, output_value, add_l=terms(relu_pre_add_coeff_u))
     return lo, up, tr
 
 
@@ -746,10 +750,11 @@ def first_layer_certificate_dag(module: Any, input_spec: Any, relu_split_state: 
 def run_crown_ibp_dag(module: Any, input_spec: Any, *, linear_spec_C: Optional[torch.Tensor] = None,
                       output_value: Optional[str] = None, relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
                       relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
-                      relu_split_state: Optional[Mapping[str, torch.Tensor]] = None) -> IntervalState:
+                      relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+                      relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None) -> IntervalState:
     """`run_crown_ibp_mlp` (crown_ibp.py:2054-2133) for graphs with add / concat / fan-out."""
     lo, up, _tr = crown_dag(module, input_spec, linear_spec_C, output_value=output_value, relu_split_state=relu_split_state,
-                            relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l)
+                            relu_alpha=relu_alpha, relu_pre_add_coeff_l=relu_pre_add_coeff_l, relu_pre_add_coeff_u=relu_pre_add_coeff_u)
     dev = normalize_input_spec(input_spec).center.device
     return IntervalState(lower=lo.to(dev), upper=up.to(dev))
 

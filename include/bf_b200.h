@@ -371,7 +371,8 @@ size_t bf_chain_crown_workspace_bytes(const bf_chain* chain, int B, int S, int u
  * Bounds C @ (output of layers[0:upto_layer]) (upto_layer = number of layers for the chain
  * output).  C [B,S,O] (a spec shared by all domains is expanded by the caller).
  * alpha_u/beta_u/alpha_l: HOST arrays of device pointers per ReLU, each [B,n_r] (from
- * bf_relu_relax); add: per ReLU [B,n_r] or NULL entries / NULL array (lower side only).
+ * bf_relu_relax); add: per ReLU [B,n_r] or NULL entries / NULL array, added to the coefficients of the requested side
+ * behind the ReLU (relu_pre_add_coeff_l for BF_SIDE_LOWER, relu_pre_add_coeff_u for BF_SIDE_UPPER, crown_ibp.py:1270-1296).
  * Input set: norm_p = BF_NORM_BOX with mid, rad [B,n0] (eps ignored), or an Lp ball with
  * mid = centre [B,n0], rad = NULL and norm_p in {BF_NORM_INF, BF_NORM_L2, BF_NORM_L1}.  out [B,S]. */
 int bf_chain_crown(const bf_chain* chain, int upto_layer, int side,

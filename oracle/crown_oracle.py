@@ -367,6 +367,7 @@ def crown_backward(
     add_l: Optional[Sequence[Optional[torch.Tensor]]] = None,
     upto: Optional[int] = None,
     influence_out: Optional[List[torch.Tensor]] = None,
+    add_u: Optional[Sequence[Optional[torch.Tensor]]] = None,
 ):
     """`_run_crown_backward_from_trace`, crown_ibp.py:1669-2051, for chains.
 
@@ -413,7 +414,8 @@ def crown_backward(
             a = alpha[r] if alpha is not None else None
             alpha_u, beta_u, alpha_l, beta_l = relu_slopes(l, u, a)
             add = add_l[r] if add_l is not None else None
-            A_u, A_l, b_u, b_l = relu_backward(A_u, A_l, b_u, b_l, alpha_u, beta_u, alpha_l, beta_l, None, add)
+            add_up = add_u[r] if add_u is not None else None  # relu_pre_add_coeff_u, crown_ibp.py:1270-1278
+            A_u, A_l, b_u, b_l = relu_backward(A_u, A_l, b_u, b_l, alpha_u, beta_u, alpha_l, beta_l, add_up, add)
         elif op == "flatten":
             pass  # coefficients are kept flattened; reshape is a view (crown_ibp.py:1093-1103)
         else:

@@ -110,7 +110,7 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
 
 def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: str = "input", output_name: Optional[str] = None,
                          alpha: Optional[Mapping[str, torch.Tensor]] = None, add_l: Optional[Mapping[str, torch.Tensor]] = None, ball=None,
-                         influence_out: Optional[Dict[str, torch.Tensor]] = None):
+                         influence_out: Optional[Dict[str, torch.Tensor]] = None, add_u: Optional[Mapping[str, torch.Tensor]] = None):
     """Backward sweep for both sides and box concretisation.  C [B,S,n_out]; alpha / add_l: name of the ReLU input ->
     [B, n] (flattened).  Returns (lower, upper) [B,S]; differentiable in alpha and add_l."""
     task = _task(module)
@@ -158,7 +158,8 @@ def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: s
             a = alpha.get(x) if alpha is not None else None
             au_, bu_, al_, bl_ = O.relu_slopes(l, u, a)
             ad = add_l.get(x) if add_l is not None else None
-            Au2, Al2, bu2, bl2 = O.relu_backward(Au, Al, bu, bl, au_, bu_, al_, bl_, add_l=ad)
+            ad_u = add_u.get(x) if add_u is not None else None
+            Au2, Al2, bu2, bl2 = O.relu_backward(Au, Al, bu, bl, au_, bu_, al_, bl_, add_u=ad_u, add_l=ad)
             push(x, Au2, Al2, bu2, bl2)
         elif t == "add":
             dyn = [n for n in op.inputs if n in env]

@@ -543,6 +543,41 @@ def gen_graph_trace() -> None:
     save("graph_trace.npz", **out)
 
 
+def gen_add_coeff() -> None:
+    """`run_crown_ibp_mlp(relu_pre_add_coeff_u=..., relu_pre_add_coeff_l=...)` (crown_ibp.py:1270-1296): seeded terms of both
+    signs behind every ReLU of the MLP c1 (8 inputs; per-input rows on the first ReLU, one shared row on the second)
+    and of the fan-out graph."""
+    out = {}
+    g = torch.Generator().manual_seed(23)
+    wl = W.make_workload("c1", batch=8)
+    m = ref_module(wl)
+    spec = InputSpec.box(value_name="input", lower=wl.lo, upper=wl.up)
+    _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    add_u, add_l = {}, {}
+    for k, (x, st) in enumerate(relu_pre.items()):
+        shape = tuple(st.lower.shape) if k == 0 else tuple(st.lower.shape[1:])
+        add_u[x], add_l[x] = 0.05 * torch.randn(shape, generator=g), 0.05 * torch.randn(shape, generator=g)
+        out[f"c1_add_u_{x}"], out[f"c1_add_l_{x}"] = add_u[x], add_l[x]
+    b = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C, relu_pre_add_coeff_u=add_u, relu_pre_add_coeff_l=add_l)
+    out["c1_lower"], out["c1_upper"] = b.lower, b.upper
+    b = run_crown_ibp_mlp(m, spec, linear_spec_C=wl.C, relu_pre_add_coeff_u=add_u)
+    out["c1_u_only_lower"], out["c1_u_only_upper"] = b.lower, b.upper
+    module, _x, lo, up, C = W.make_graph_cases()["fanout_mlp"]
+    src = module.get_entry_task()
+    ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+    task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+    m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+    spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+    _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+    add_u = {x: 0.05 * torch.randn(tuple(st.lower.shape), generator=g) for x, st in relu_pre.items()}
+    add_l = {x: 0.05 * torch.randn(tuple(st.lower.shape), generator=g) for x, st in relu_pre.items()}
+    for x in relu_pre:
+        out[f"fanout_add_u_{x}"], out[f"fanout_add_l_{x}"] = add_u[x], add_l[x]
+    b = run_crown_ibp_mlp(m, spec, linear_spec_C=C, relu_pre_add_coeff_u=add_u, relu_pre_add_coeff_l=add_l)
+    out["fanout_lower"], out["fanout_upper"] = b.lower, b.upper
+    save("add_coeff.npz", **out)
+
+
 def gen_lp_alpha() -> None:
     """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
     wl = W.make_workload("c3", batch=8)
@@ -986,7 +1021,7 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
               "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce,
               "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate,
-              "graph_trace": gen_graph_trace}
+              "graph_trace": gen_graph_trace, "add_coeff": gen_add_coeff}
 
 
 def main() -> None:

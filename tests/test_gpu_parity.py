@@ -292,6 +292,33 @@ def test_c1_identity_spec_and_shared_spec(dev):
     assert_close(got2.upper, up2, "h2 upper")
 
 
+def test_add_coefficients_on_both_sides(dev, golden):
+    """`relu_pre_add_coeff_u` / `_l` of `run_crown_ibp_mlp` (crown_ibp.py:1270-1296): a term added to the upper / lower
+    coefficients behind a ReLU, per input or as one shared row; the MLP c1 and the fan-out graph (tests/golden/add_coeff.npz)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_crown_ibp_mlp
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("add_coeff.npz")
+    wl = W.make_workload("c1", batch=8)
+    spec = _spec(wl, dev)
+    add_u = {n: torch.as_tensor(g[f"c1_add_u_{n}"]).to(dev) for n in wl.relu_names}
+    add_l = {n: torch.as_tensor(g[f"c1_add_l_{n}"]).to(dev) for n in wl.relu_names}
+    b = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_pre_add_coeff_u=add_u, relu_pre_add_coeff_l=add_l)
+    assert_close(b.lower, g["c1_lower"], "c1 lower with both terms")
+    assert_close(b.upper, g["c1_upper"], "c1 upper with both terms")
+    b = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=wl.C.to(dev), relu_pre_add_coeff_u=add_u)
+    assert_close(b.lower, g["c1_u_only_lower"], "c1 lower with the upper term only")
+    assert_close(b.upper, g["c1_u_only_upper"], "c1 upper with the upper term only")
+    module, _x, lo, up, C = W.make_graph_cases()["fanout_mlp"]
+    gspec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    gu = {"h": torch.as_tensor(g["fanout_add_u_h"]).to(dev)}
+    gl = {"h": torch.as_tensor(g["fanout_add_l_h"]).to(dev)}
+    b = run_crown_ibp_mlp(module, gspec, linear_spec_C=C.to(dev), relu_pre_add_coeff_u=gu, relu_pre_add_coeff_l=gl)
+    assert_close(b.lower, g["fanout_lower"], "fan-out graph lower")
+    assert_close(b.upper, g["fanout_upper"], "fan-out graph upper")
+
+
 def test_c2_cnn(dev, golden):
     from boundflow_b200 import workloads as W
     from boundflow_b200.crown import run_crown_ibp_mlp, run_crown_intermediate_mlp

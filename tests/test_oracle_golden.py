@@ -628,6 +628,34 @@ def test_graph_oracle_trace_level_functions(golden, name):
         assert_close(v.reshape(B, -1), g[f"{name}_infl_{x}"], f"influence {x}")
 
 
+def test_add_coefficients_on_both_sides(golden):
+    """`relu_pre_add_coeff_u` / `_l` (crown_ibp.py:1270-1296) on the MLP c1 and on the fan-out graph (add_coeff.npz)."""
+    from oracle import graph_oracle as GO
+
+    g = golden("add_coeff.npz")
+    wl = W.make_workload("c1", batch=8)
+    inp = O.box_input(wl.lo, wl.up)
+    tr = O.forward_ibp_trace(wl.layers, inp)
+    rows = lambda key, n: torch.as_tensor(g[key]).reshape(-1, n).expand(8, n)  # noqa: E731
+    widths = [l.shape[1] for l, _u in tr.pre]
+    add_u = [rows(f"c1_add_u_{n}", w) for n, w in zip(wl.relu_names, widths)]
+    add_l = [rows(f"c1_add_l_{n}", w) for n, w in zip(wl.relu_names, widths)]
+    lo, up = O.crown_backward(wl.layers, inp, tr, wl.C, add_l=add_l, add_u=add_u)
+    assert_close(lo, g["c1_lower"], "c1 lower with both terms")
+    assert_close(up, g["c1_upper"], "c1 upper with both terms")
+    lo, up = O.crown_backward(wl.layers, inp, tr, wl.C, add_u=add_u)
+    assert_close(lo, g["c1_u_only_lower"], "c1 lower with the upper term only")
+    assert_close(up, g["c1_u_only_upper"], "c1 upper with the upper term only")
+    module, _x, blo, bup, C = W.make_graph_cases()["fanout_mlp"]
+    B = blo.shape[0]
+    env, relu_pre = GO.forward_ibp_graph(module, blo, bup)
+    gu = {x: torch.as_tensor(g[f"fanout_add_u_{x}"]).reshape(B, -1) for x in relu_pre}
+    gl = {x: torch.as_tensor(g[f"fanout_add_l_{x}"]).reshape(B, -1) for x in relu_pre}
+    lo, up = GO.crown_backward_graph(module, env, relu_pre, C, blo, bup, add_l=gl, add_u=gu)
+    assert_close(lo, g["fanout_lower"], "fan-out graph lower")
+    assert_close(up, g["fanout_upper"], "fan-out graph upper")
+
+
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
 GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
 
