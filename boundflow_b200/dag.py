@@ -24,6 +24,7 @@ import torch
 from . import _lib
 from .crown import _alpha_rows, _cuda_device, _f32, _split_tensor, _stream_ptr
 from .ir import IntervalState, input_mid_rad, lp_ball_of, normalize_input_spec
+from .network import dense_conv_weight
 
 
 def _numel(shape) -> int:
@@ -60,11 +61,22 @@ class DagTrace:
 
 
 def _params(module: Any, device: torch.device) -> Dict[str, torch.Tensor]:
+    """Parameters as fp32 device tensors; the weight of a grouped or dilated Conv2d op is replaced by its dense
+    equivalent (`network.dense_conv_weight`), so every step of the walkers sees groups = 1, dilation = 1."""
     raw = module.bindings.get("params", {})
     out = {}
     for k, v in (raw.items() if isinstance(raw, dict) else []):
         t = v if torch.is_tensor(v) else torch.as_tensor(v)
         out[k] = _f32(t, device)
+    dense_for: Dict[str, Tuple[int, Tuple[int, int]]] = {}
+    for op in module.get_entry_task().ops:
+        if op.op_type != "conv2d" or len(op.inputs) < 2 or op.inputs[1] not in out:
+            continue
+        key = (int(op.attrs.get("groups", 1)), _pair(op.attrs.get("dilation", 1)))
+        if dense_for.setdefault(op.inputs[1], key) != key:
+            raise NotImplementedError(f"weight '{op.inputs[1]}' is shared by Conv2d ops with different groups / dilation")
+    for name, (groups, dilation) in dense_for.items():
+        out[name] = dense_conv_weight(out[name], {"groups": groups, "dilation": dilation})
     return out
 
 
@@ -120,8 +132,6 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
                                                  _lib.ptr(yl), _lib.ptr(yu), None, B, n_in, n_out, s))
                 tr.shape[out] = (n_out,)
             else:
-                if int(op.attrs.get("groups", 1)) != 1 or _pair(op.attrs.get("dilation", 1)) != (1, 1):
-                    raise NotImplementedError("conv2d with dilation or groups is not supported by the CUDA backend")
                 Ci, Hi, Wi = tr.shape[x]
                 Co, _ci, kh, kw = (int(d) for d in W.shape)
                 st, pd = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))

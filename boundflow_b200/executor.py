@@ -20,7 +20,7 @@ import torch
 from . import _lib
 from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace, needs_graph_path
 from .ir import IntervalState, input_mid_rad, normalize_input_spec
-from .network import _pair
+from .network import _pair, dense_conv_weight
 
 
 def _is_interval_kind(kind: Any) -> bool:
@@ -64,8 +64,7 @@ class CudaIntervalDomain:
         B = int(xl.shape[0])
         if op == "conv2d" or (op is None and xl.dim() == 4 and w.dim() == 4):
             st, pd = _pair(attrs.get("stride", 1)), _pair(attrs.get("padding", 0))
-            if _pair(attrs.get("dilation", 1)) != (1, 1) or int(attrs.get("groups", 1)) != 1:
-                raise NotImplementedError("conv2d with dilation or groups is not supported by the CUDA backend")
+            w = dense_conv_weight(w, attrs)   # grouped / dilated: the equal dense convolution
             Ci, Hi, Wi = (int(d) for d in xl.shape[1:])
             Co, _, kh, kw = (int(d) for d in w.shape)
             Ho = (Hi + 2 * pd[0] - kh) // st[0] + 1

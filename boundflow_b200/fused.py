@@ -8,7 +8,8 @@ fused_crown.py:279-304): plain CROWN only, contiguous fp32 CUDA tensors without
 grad.  Returning False from `supports*` makes the reference runtime fall back to
 its eager step, exactly as for its own TVM executor.  Unlike the TVM v1 kernels
 (backends/tvm/fused_crown_conv2d.py:75-84) any kernel size / stride / padding is
-accepted for conv2d (groups = 1, dilation = 1).
+accepted for conv2d; groups and dilation run as the equal dense convolution
+(`network.dense_conv_weight`).
 """
 from __future__ import annotations
 
@@ -18,7 +19,7 @@ from typing import Any, Mapping, Optional, Tuple
 import torch
 
 from . import _lib
-from .network import _pair
+from .network import _pair, dense_conv_weight
 
 
 @dataclass(frozen=True)
@@ -69,10 +70,6 @@ class CudaFusedCrownExecutor:
             return False
         if getattr(descriptor, "dtype", torch.float32) != torch.float32:
             return False
-        if descriptor.kind == "conv2d":
-            attrs = descriptor.attrs
-            if _pair(attrs.get("dilation", 1)) != (1, 1) or int(attrs.get("groups", 1)) != 1:
-                return False
         return True
 
     def supports(self, request: Any, context: Any) -> bool:
@@ -82,8 +79,6 @@ class CudaFusedCrownExecutor:
         if request.bias is not None:
             tensors.append(request.bias)
         ok = all(t.device.type == "cuda" and t.dtype == torch.float32 and t.is_contiguous() and not t.requires_grad for t in tensors)
-        if ok and request.kind == "conv2d":
-            ok = _pair(request.attrs.get("dilation", 1)) == (1, 1) and int(request.attrs.get("groups", 1)) == 1
         return bool(ok)
 
     def run(self, request: Any, *, stream: Optional[torch.cuda.Stream] = None) -> FusedReluAffineResult:
@@ -112,14 +107,15 @@ class CudaFusedCrownExecutor:
                 else:
                     Co, Ho, Wo = (int(d) for d in request.output_shape)
                     Ci, Hi, Wi = (int(d) for d in request.input_shape)
-                    kh, kw = int(request.weight.shape[2]), int(request.weight.shape[3])
+                    weight = dense_conv_weight(request.weight, request.attrs)   # grouped / dilated: the equal dense convolution
+                    kh, kw = int(weight.shape[2]), int(weight.shape[3])
                     sh, sw = _pair(request.attrs.get("stride", 1))
                     ph, pw = _pair(request.attrs.get("padding", 0))
                     nbytes = int(self.lib.bf_crown_relu_conv2d_bwd_scratch_bytes(D, S, Co, Ho, Wo))
                     scratch = torch.empty(nbytes, dtype=torch.uint8, device=device)
                     _lib.check(self.lib.bf_crown_relu_conv2d_bwd(
                         _lib.ptr(A), side, _lib.ptr(request.alpha_u), _lib.ptr(request.alpha_l), _lib.ptr(request.beta_u),
-                        _lib.ptr(request.beta_l), _lib.ptr(request.weight), _lib.ptr(request.bias), _lib.ptr(A_prev),
+                        _lib.ptr(request.beta_l), _lib.ptr(weight), _lib.ptr(request.bias), _lib.ptr(A_prev),
                         _lib.ptr(delta), 0, _lib.ptr(scratch), nbytes, D, S, Ci, Hi, Wi, Co, Ho, Wo, kh, kw, sh, sw, ph, pw, sp))
                 outs.append((A_prev, delta))
         return FusedReluAffineResult(A_prev_u=outs[0][0], A_prev_l=outs[1][0], bias_delta_u=outs[0][1], bias_delta_l=outs[1][1])

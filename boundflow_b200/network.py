@@ -5,8 +5,9 @@ The reference interprets `task.ops` op by op on every call
 list is validated once, its parameters are made contiguous fp32 device tensors
 and handed to the C library as a `bf_chain`; every later call only passes
 pointers.  Supported ops are the ones the bound-propagation configurations use:
-linear, conv2d (groups=1, dilation=1), relu, flatten(start_dim=1); anything else
-raises NotImplementedError like the reference executors do for unknown ops.
+linear, conv2d, relu, flatten(start_dim=1); anything else raises NotImplementedError
+like the reference executors do for unknown ops.  A grouped or dilated Conv2d is handed
+to the kernels as the equal dense convolution (`dense_conv_weight`).
 """
 from __future__ import annotations
 
@@ -24,6 +25,51 @@ def _pair(v: Any) -> Tuple[int, int]:
         return (int(v), int(v))
     v = tuple(int(x) for x in v)
     return (v[0], v[0]) if len(v) == 1 else (v[0], v[1])
+
+
+class _DenseConvWeights:
+    """Dense equivalents of grouped / dilated Conv2d weights, one per (weight tensor, groups, dilation).  Keyed by
+    storage address, shape, device, in-place version counter and the two attributes; an entry keeps the original
+    tensor alive so its address cannot be reused while the entry exists; least recently used entries are dropped."""
+
+    def __init__(self, capacity: int = 32):
+        self.capacity = int(capacity)
+        self._entries: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def get(self, W: torch.Tensor, groups: int, dilation: Tuple[int, int]) -> torch.Tensor:
+        key = (W.data_ptr(), tuple(W.shape), str(W.device), int(W._version), int(groups), tuple(dilation))
+        hit = self._entries.pop(key, None)
+        if hit is None:
+            Co, Cig, kh, kw = (int(d) for d in W.shape)
+            if Co % groups != 0:
+                raise ValueError(f"conv2d: {Co} output channels are not divisible by groups={groups}")
+            cog, (dh, dw) = Co // groups, dilation
+            dense = torch.zeros(Co, Cig * groups, dh * (kh - 1) + 1, dw * (kw - 1) + 1, dtype=W.dtype, device=W.device)
+            for g in range(groups):
+                dense[g * cog:(g + 1) * cog, g * Cig:(g + 1) * Cig, ::dh, ::dw] = W[g * cog:(g + 1) * cog]
+            hit = (W, dense.contiguous())
+            while len(self._entries) >= self.capacity:
+                self._entries.pop(next(iter(self._entries)))
+        self._entries[key] = hit  # most recently used last
+        return hit[1]
+
+
+_DENSE_CONV = _DenseConvWeights()
+
+
+def dense_conv_weight(W: torch.Tensor, attrs: Any) -> torch.Tensor:
+    """The weight of the dense, undilated convolution that equals conv2d(x, W, groups=g, dilation=d): output channel
+    block k sees only input channel block k (zeros elsewhere) and the taps sit d apart in a kernel of d*(k-1)+1 (zeros
+    between them).  Products with the inserted zeros add exact zeros, so every kernel of the library applies unchanged
+    (`F.conv2d(..., dilation, groups)` in the reference: domains/interval.py:57-74, crown_ibp.py:1127-1170).  Returns W
+    itself for groups = 1, dilation = 1."""
+    attrs = attrs or {}
+    groups, dilation = int(attrs.get("groups", 1)), _pair(attrs.get("dilation", 1))
+    if groups == 1 and dilation == (1, 1):
+        return W
+    if groups < 1 or dilation[0] < 1 or dilation[1] < 1 or W.dim() != 4:
+        raise ValueError(f"conv2d: bad groups={groups} / dilation={dilation} for a weight of shape {tuple(W.shape)}")
+    return _DENSE_CONV.get(W, groups, dilation)
 
 
 @dataclass
@@ -85,11 +131,9 @@ class CudaChain:
                 out_shape = (int(W.shape[0]),)
                 layers.append(ChainLayer("linear", op.name, cur, op.outputs[0], shape, out_shape, W, b))
             elif t == "conv2d":
-                W = dev(params[op.inputs[1]])
+                W = dense_conv_weight(dev(params[op.inputs[1]]), op.attrs)
                 b = dev(params[op.inputs[2]]) if len(op.inputs) == 3 else None
                 st, pd = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
-                if _pair(op.attrs.get("dilation", 1)) != (1, 1) or int(op.attrs.get("groups", 1)) != 1:
-                    raise NotImplementedError("conv2d with dilation or groups is not supported")
                 if len(shape) != 3 or W.dim() != 4 or W.shape[1] != shape[0]:
                     raise ValueError(f"conv2d '{op.name}': weight {tuple(W.shape)} does not match input shape {shape}")
                 ho = (shape[1] + 2 * pd[0] - W.shape[2]) // st[0] + 1

@@ -351,6 +351,48 @@ def make_graph_certificate_cases(kind: str = "linear", seed: int = 1019):
     return module, x, lo, up, cases
 
 
+def make_grouped_dilated_cases(seed: int = 1021):
+    """Conv2d ops with groups and dilation: a chain (4x10x10 -> conv 8 ch k3 p1 groups 2 -> ReLU -> conv 8 ch k3 p2
+    dilation 2 groups 4 -> ReLU -> flatten -> Linear 5) and a residual graph whose main branch is a depthwise 3x3
+    convolution (groups = channels) beside a 1x1 skip.  Returns {name: (module, x, lo, up, C)}."""
+    g = torch.Generator("cpu").manual_seed(seed)
+
+    def rn(*shape, fan):
+        return torch.randn(*shape, generator=g) * math.sqrt(2.0 / fan)
+
+    def mod(tid, ops, params):
+        task = BoundTask(task_id=tid, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        return BFTaskModule(tasks=[task], entry_task_id=tid, bindings={"params": params})
+
+    cases = {}
+    ops = [
+        TaskOp("conv2d", "conv1", ["input", "w1", "b1"], ["h1"], {"stride": (1, 1), "padding": (1, 1), "dilation": (1, 1), "groups": 2}),
+        TaskOp("relu", "relu1", ["h1"], ["r1"]),
+        TaskOp("conv2d", "conv2", ["r1", "w2", "b2"], ["h2"], {"stride": (1, 1), "padding": (2, 2), "dilation": (2, 2), "groups": 4}),
+        TaskOp("relu", "relu2", ["h2"], ["r2"]),
+        TaskOp("flatten", "flatten", ["r2"], ["flat"], {"start_dim": 1, "end_dim": -1}),
+        TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"]),
+    ]
+    params = {"w1": rn(8, 2, 3, 3, fan=18), "b1": rn(8, fan=200), "w2": rn(8, 2, 3, 3, fan=18), "b2": rn(8, fan=200),
+              "wh": rn(5, 800, fan=800), "bh": rn(5, fan=200)}
+    x = torch.rand(3, 4, 10, 10, generator=g)
+    cases["grouped_dilated_chain"] = (mod("gd_chain", ops, params), x, (x - 0.03).clamp(0, 1), (x + 0.03).clamp(0, 1), None)
+    ops = [
+        TaskOp("conv2d", "depthwise", ["input", "wd", "bd"], ["hd"], {"stride": (2, 2), "padding": (1, 1), "dilation": (1, 1), "groups": 3}),
+        TaskOp("relu", "relu_d", ["hd"], ["rd"]),
+        TaskOp("conv2d", "skip", ["input", "ws", "bs"], ["hs"], {"stride": (2, 2), "padding": (0, 0), "dilation": (1, 1), "groups": 1}),
+        TaskOp("add", "merge", ["rd", "hs"], ["sum"]),
+        TaskOp("relu", "relu_out", ["sum"], ["rout"]),
+        TaskOp("flatten", "flatten", ["rout"], ["flat"], {"start_dim": 1, "end_dim": -1}),
+        TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"]),
+    ]
+    params = {"wd": rn(3, 1, 3, 3, fan=9), "bd": rn(3, fan=200), "ws": rn(3, 3, 1, 1, fan=3), "bs": rn(3, fan=200),
+              "wh": rn(4, 48, fan=48), "bh": rn(4, fan=200)}
+    x = torch.rand(2, 3, 8, 8, generator=g)
+    cases["depthwise_residual"] = (mod("dw_residual", ops, params), x, (x - 0.04).clamp(0, 1), (x + 0.04).clamp(0, 1), None)
+    return cases
+
+
 def make_graph_cases(seed: int = 1011):
     """Small graphs that are not chains, shaped like the reference's end-to-end fixtures
     (tests/test_phase7a_pr12_e2e_crown_runtime.py:98-239): a residual CNN block with a projection skip

@@ -114,12 +114,12 @@ def ibp_linear(l: torch.Tensor, u: torch.Tensor, W: torch.Tensor, b: Optional[to
     return y_l, y_u
 
 
-def ibp_conv2d(l, u, W, b, stride, padding):
+def ibp_conv2d(l, u, W, b, stride, padding, dilation=(1, 1), groups=1):
     """`IntervalDomain.affine_transformer` conv2d branch, domains/interval.py:57-74."""
     w_pos = torch.clamp(W, min=0.0)
     w_neg = torch.clamp(W, max=0.0)
-    y_l = F.conv2d(l, w_pos, None, stride, padding) + F.conv2d(u, w_neg, None, stride, padding)
-    y_u = F.conv2d(u, w_pos, None, stride, padding) + F.conv2d(l, w_neg, None, stride, padding)
+    y_l = F.conv2d(l, w_pos, None, stride, padding, dilation, groups) + F.conv2d(u, w_neg, None, stride, padding, dilation, groups)
+    y_u = F.conv2d(u, w_pos, None, stride, padding, dilation, groups) + F.conv2d(l, w_neg, None, stride, padding, dilation, groups)
     if b is not None:
         y_l = y_l + b.view(1, -1, 1, 1)
         y_u = y_u + b.view(1, -1, 1, 1)
@@ -209,7 +209,8 @@ def forward_ibp_trace(
                 cur_l, cur_u = ibp_linear(cur_l, cur_u, layer["W"], layer.get("b"))
             at_input = False
         elif op == "conv2d":
-            cur_l, cur_u = ibp_conv2d(cur_l, cur_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"])
+            cur_l, cur_u = ibp_conv2d(cur_l, cur_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"],
+                                      layer.get("dilation", (1, 1)), layer.get("groups", 1))
             at_input = False
         elif op == "relu":
             if constraints is not None:
@@ -302,14 +303,14 @@ def linear_backward(A, b, W, bias):
     return torch.einsum("bko,oi->bki", A, W), b_out
 
 
-def conv2d_output_padding(in_hw, out_hw, k, stride, padding):
-    """linear_operator.py:140-163: output_padding = H_in - ((H_out-1)*s - 2p + (k-1) + 1)."""
+def conv2d_output_padding(in_hw, out_hw, k, stride, padding, dilation=(1, 1)):
+    """linear_operator.py:140-163 / crown_ibp.py:1589-1596: output_padding = H_in - ((H_out-1)*s - 2p + d*(k-1) + 1)."""
     return tuple(
-        int(in_hw[i]) - ((int(out_hw[i]) - 1) * stride[i] - 2 * padding[i] + (k[i] - 1) + 1) for i in range(2)
+        int(in_hw[i]) - ((int(out_hw[i]) - 1) * stride[i] - 2 * padding[i] + dilation[i] * (k[i] - 1) + 1) for i in range(2)
     )
 
 
-def conv2d_backward(A, b, W, bias, stride, padding, in_shape, out_shape):
+def conv2d_backward(A, b, W, bias, stride, padding, in_shape, out_shape, dilation=(1, 1), groups=1):
     """`_backprop_conv2d_step`, crown_ibp.py:1106-1173, with
     `Conv2dLinearOperator.to_dense` (linear_operator.py:1067-1092): the
     coefficient rows [B,S,C_o*H_o*W_o] go through conv_transpose2d with batch =
@@ -320,8 +321,8 @@ def conv2d_backward(A, b, W, bias, stride, padding, in_shape, out_shape):
     b_out = b
     if bias is not None:
         b_out = b + (A4.sum(dim=(2, 3)) * bias.view(1, -1)).sum(dim=1).reshape(B, S)
-    opad = conv2d_output_padding(in_shape[1:], out_shape[1:], W.shape[2:], stride, padding)
-    prev = F.conv_transpose2d(A4, W, None, stride, padding, opad)
+    opad = conv2d_output_padding(in_shape[1:], out_shape[1:], W.shape[2:], stride, padding, dilation)
+    prev = F.conv_transpose2d(A4, W, None, stride, padding, opad, groups, dilation)
     return prev.reshape(B, S, -1), b_out
 
 
@@ -404,8 +405,9 @@ def crown_backward(
             A_l, b_l = linear_backward(A_l, b_l, layer["W"], layer.get("b"))
         elif op == "conv2d":
             in_shape, o_shape = trace.shapes[idx], trace.shapes[idx + 1]
-            A_u, b_u = conv2d_backward(A_u, b_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape)
-            A_l, b_l = conv2d_backward(A_l, b_l, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape)
+            dg = (layer.get("dilation", (1, 1)), layer.get("groups", 1))
+            A_u, b_u = conv2d_backward(A_u, b_u, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape, *dg)
+            A_l, b_l = conv2d_backward(A_l, b_l, layer["W"], layer.get("b"), layer["stride"], layer["padding"], in_shape, o_shape, *dg)
         elif op == "relu":
             r = relu_ids.index(idx)
             l, u = trace.pre[r]
@@ -767,7 +769,7 @@ def concrete_forward(layers: Layers, x: torch.Tensor) -> torch.Tensor:
             if layer.get("b") is not None:
                 x = x + layer["b"]
         elif op == "conv2d":
-            x = F.conv2d(x, layer["W"], layer.get("b"), layer["stride"], layer["padding"])
+            x = F.conv2d(x, layer["W"], layer.get("b"), layer["stride"], layer["padding"], layer.get("dilation", (1, 1)), layer.get("groups", 1))
         elif op == "relu":
             x = torch.relu(x)
         elif op == "flatten":

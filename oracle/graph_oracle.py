@@ -78,7 +78,8 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
             l, u = get(op.inputs[0])
             W = P[op.inputs[1]]
             b = P[op.inputs[2]] if len(op.inputs) == 3 else None
-            env[out] = O.ibp_conv2d(l, u, W, b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)))
+            env[out] = O.ibp_conv2d(l, u, W, b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)),
+                                    _pair(op.attrs.get("dilation", 1)), int(op.attrs.get("groups", 1)))
         elif t == "relu":
             x = op.inputs[0]
             l, u = get(x)
@@ -147,8 +148,9 @@ def crown_backward_graph(module: Any, env, relu_pre, C, lo, up, *, input_name: s
             W = P[op.inputs[1]]
             b = P[op.inputs[2]] if len(op.inputs) == 3 else None
             st_, pd_ = _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0))
-            Au2, bu2 = O.conv2d_backward(Au, bu, W, b, st_, pd_, shape[op.inputs[0]], shape[out])
-            Al2, bl2 = O.conv2d_backward(Al, bl, W, b, st_, pd_, shape[op.inputs[0]], shape[out])
+            dg = (_pair(op.attrs.get("dilation", 1)), int(op.attrs.get("groups", 1)))
+            Au2, bu2 = O.conv2d_backward(Au, bu, W, b, st_, pd_, shape[op.inputs[0]], shape[out], *dg)
+            Al2, bl2 = O.conv2d_backward(Al, bl, W, b, st_, pd_, shape[op.inputs[0]], shape[out], *dg)
             push(op.inputs[0], Au2, Al2, bu2, bl2)
         elif t == "relu":
             x = op.inputs[0]
@@ -301,7 +303,8 @@ def concrete_forward_graph(module: Any, x: torch.Tensor, *, input_name: str = "i
             env[out] = y + P[op.inputs[2]] if len(op.inputs) == 3 else y
         elif t == "conv2d":
             b = P[op.inputs[2]] if len(op.inputs) == 3 else None
-            env[out] = F.conv2d(get(op.inputs[0]), P[op.inputs[1]], b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)))
+            env[out] = F.conv2d(get(op.inputs[0]), P[op.inputs[1]], b, _pair(op.attrs.get("stride", 1)), _pair(op.attrs.get("padding", 0)),
+                                _pair(op.attrs.get("dilation", 1)), int(op.attrs.get("groups", 1)))
         elif t == "relu":
             pre[op.inputs[0]] = get(op.inputs[0])
             env[out] = torch.relu(get(op.inputs[0]))

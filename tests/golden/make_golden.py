@@ -578,6 +578,28 @@ def gen_add_coeff() -> None:
     save("add_coeff.npz", **out)
 
 
+def gen_grouped_dilated() -> None:
+    """Conv2d with groups and dilation (workloads.make_grouped_dilated_cases): IBP, CROWN-IBP and the per-domain alpha
+    loop (adaptive start, 3 steps) of the reference."""
+    out = {}
+    for name, (module, _x, lo, up, C) in W.make_grouped_dilated_cases().items():
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        spec = InputSpec.box(value_name="input", lower=lo, upper=up)
+        ibp = PythonTaskExecutor().run_ibp(m, spec)
+        crown = run_crown_ibp_mlp(m, spec, linear_spec_C=C)
+        _env, relu_pre = _forward_ibp_trace_mlp(m, spec)
+        a0 = adaptive_alpha(relu_pre)
+        b, _a, _b, _s = run_alpha_beta_crown_mlp(m, spec, linear_spec_C=C, steps=3, lr=0.1, per_batch_params=True,
+                                               warm_start_alpha=AlphaState(alpha_by_relu_input={n: v.clone() for n, v in a0.items()}))
+        out[f"{name}_ibp_lower"], out[f"{name}_ibp_upper"] = ibp.lower, ibp.upper
+        out[f"{name}_crown_lower"], out[f"{name}_crown_upper"] = crown.lower, crown.upper
+        out[f"{name}_alpha_lower_3"], out[f"{name}_alpha_upper_3"] = b.lower, b.upper
+    save("grouped_dilated.npz", **out)
+
+
 def gen_lp_alpha() -> None:
     """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
     wl = W.make_workload("c3", batch=8)
@@ -1021,7 +1043,8 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "shared_objectives": gen_shared_objectives, "graph_objectives": gen_graph_objectives,
               "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce,
               "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate,
-              "graph_trace": gen_graph_trace, "add_coeff": gen_add_coeff}
+              "graph_trace": gen_graph_trace, "add_coeff": gen_add_coeff,
+              "grouped_dilated": gen_grouped_dilated}
 
 
 def main() -> None:

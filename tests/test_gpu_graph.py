@@ -208,6 +208,33 @@ def test_trace_level_functions_on_graphs_match_reference_golden(dev, golden, nam
         forward_ibp_trace_mlp(module, spec, relu_pre_constraints={**cons, "not_a_relu_input": cons[first]})
 
 
+@pytest.mark.parametrize("name", ["grouped_dilated_chain", "depthwise_residual"])
+def test_grouped_and_dilated_convolutions_match_reference_golden(dev, golden, name):
+    """Conv2d with groups and dilation on a chain (fused sweeps) and on a residual graph (per-value walker), through the
+    dense-equivalent weights: IBP, CROWN-IBP and the per-domain alpha loop (tests/golden/grouped_dilated.npz)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, forward_ibp_trace_mlp, needs_graph_path, run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from boundflow_b200.executor import CudaTaskExecutor
+    from boundflow_b200.ir import InputSpec
+
+    g = golden("grouped_dilated.npz")
+    module, _x, lo, up, _C = W.make_grouped_dilated_cases()[name]
+    assert needs_graph_path(module) == (name == "depthwise_residual")
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    ibp = CudaTaskExecutor().run_ibp(module, spec)
+    assert_close(ibp.lower.reshape(B, -1), g[f"{name}_ibp_lower"].reshape(B, -1), "ibp lower")
+    assert_close(ibp.upper.reshape(B, -1), g[f"{name}_ibp_upper"].reshape(B, -1), "ibp upper")
+    crown = run_crown_ibp_mlp(module, spec)
+    assert_close(crown.lower.reshape(B, -1), g[f"{name}_crown_lower"].reshape(B, -1), "crown lower")
+    assert_close(crown.upper.reshape(B, -1), g[f"{name}_crown_upper"].reshape(B, -1), "crown upper")
+    _env, relu_pre = forward_ibp_trace_mlp(module, spec)
+    a0 = {x: ((st.lower >= 0) | ((st.lower < 0) & (st.upper > 0) & (st.upper > -st.lower))).float() for x, st in relu_pre.items()}
+    b, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, steps=3, lr=0.1, per_batch_params=True, warm_start_alpha=AlphaState(a0))
+    assert_close(b.lower.reshape(B, -1), g[f"{name}_alpha_lower_3"].reshape(B, -1), "alpha lower after 3")
+    assert_close(b.upper.reshape(B, -1), g[f"{name}_alpha_upper_3"].reshape(B, -1), "alpha upper after 3")
+
+
 def test_building_blocks_against_torch(dev):
     """bf_crown_relu_bwd (incl. rows wider than one chunk) and bf_accumulate."""
     from boundflow_b200 import _lib

@@ -189,6 +189,35 @@ def test_fused_relu_conv_region_golden(dev, golden):
     assert_close(res.bias_delta_l, g["conv_delta_l"], "conv delta_l")
 
 
+def test_fused_relu_conv_region_with_groups_and_dilation(dev):
+    """The fused ReLU + Conv2d backward region on a grouped, dilated convolution (run as the equal dense convolution)
+    against the oracle's ReLU step followed by conv_transpose2d with the same groups / dilation."""
+    from boundflow_b200.fused import CudaFusedCrownExecutor, FusedReluAffineRequest
+    from oracle import crown_oracle as O
+
+    gen = torch.Generator("cpu").manual_seed(91)
+    D, S, Ci, Co, k, groups, dil, st, pd, Hi = 3, 4, 4, 6, 3, 2, 2, 1, 2, 9
+    Ho = (Hi + 2 * pd - dil * (k - 1) - 1) // st + 1
+    A_u, A_l = torch.randn(D, S, Co, Ho, Ho, generator=gen), torch.randn(D, S, Co, Ho, Ho, generator=gen)
+    l = torch.randn(D, Co * Ho * Ho, generator=gen) - 0.2
+    u = l + torch.rand(D, Co * Ho * Ho, generator=gen) * 2.0
+    au, bu, al, bl = O.relu_relax(l, u)
+    Wc, bc = torch.randn(Co, Ci // groups, k, k, generator=gen), torch.randn(Co, generator=gen)
+    attrs = {"stride": (st, st), "padding": (pd, pd), "dilation": (dil, dil), "groups": groups}
+    t = lambda x: x.to(dev).contiguous()  # noqa: E731
+    ex = CudaFusedCrownExecutor()
+    req = FusedReluAffineRequest("conv2d", t(A_u), t(A_l), t(au), t(al), t(bu), t(bl), t(Wc), t(bc), (Ci, Hi, Hi), (Co, Ho, Ho), attrs)
+    res = ex.run(req)
+    z = torch.zeros(D, S)
+    Au2, Al2, bu2, bl2 = O.relu_backward(A_u.reshape(D, S, -1), A_l.reshape(D, S, -1), z, z, au, bu, al, bl)
+    ref_u, du = O.conv2d_backward(Au2, bu2, Wc, bc, (st, st), (pd, pd), (Ci, Hi, Hi), (Co, Ho, Ho), (dil, dil), groups)
+    ref_l, dl = O.conv2d_backward(Al2, bl2, Wc, bc, (st, st), (pd, pd), (Ci, Hi, Hi), (Co, Ho, Ho), (dil, dil), groups)
+    assert_close(res.A_prev_u.reshape(D, S, -1), ref_u, "grouped dilated A_prev_u")
+    assert_close(res.A_prev_l.reshape(D, S, -1), ref_l, "grouped dilated A_prev_l")
+    assert_close(res.bias_delta_u, du, "grouped dilated delta_u")
+    assert_close(res.bias_delta_l, dl, "grouped dilated delta_l")
+
+
 @pytest.mark.parametrize("B,S,n0", [(1, 1, 1), (4, 9, 784), (3, 7, 130), (2, 5, 3072)])
 def test_concretize_kernel(dev, B, S, n0):
     from boundflow_b200 import _lib

@@ -656,6 +656,38 @@ def test_add_coefficients_on_both_sides(golden):
     assert_close(up, g["fanout_upper"], "fan-out graph upper")
 
 
+@pytest.mark.parametrize("name", ["grouped_dilated_chain", "depthwise_residual"])
+def test_grouped_and_dilated_convolutions(golden, name):
+    """Conv2d with groups and dilation (domains/interval.py:57-74, crown_ibp.py:1127-1170): IBP, CROWN-IBP and the
+    per-domain alpha loop of the reference (grouped_dilated.npz) against the graph oracle, which walks chains too."""
+    from oracle import graph_oracle as GO
+
+    g = golden("grouped_dilated.npz")
+    module, _x, lo, up, _C = W.make_grouped_dilated_cases()[name]
+    B = lo.shape[0]
+    env, relu_pre = GO.forward_ibp_graph(module, lo, up)
+    assert_close(env["out"][0], g[f"{name}_ibp_lower"], "ibp lower")
+    assert_close(env["out"][1], g[f"{name}_ibp_upper"], "ibp upper")
+    n_out = env["out"][0].reshape(B, -1).shape[1]
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1)
+    lower, upper = GO.crown_backward_graph(module, env, relu_pre, Cb, lo, up)
+    assert_close(lower, g[f"{name}_crown_lower"].reshape(B, -1), "crown lower")
+    assert_close(upper, g[f"{name}_crown_upper"].reshape(B, -1), "crown upper")
+    lo_a, up_a, _a, _b = GO.alpha_crown_graph(module, lo, up, Cb, steps=3, lr=0.1, alpha0=GO.adaptive_alpha_init_graph(relu_pre))
+    assert_close(lo_a, g[f"{name}_alpha_lower_3"].reshape(B, -1), "alpha lower after 3")
+    assert_close(up_a, g[f"{name}_alpha_upper_3"].reshape(B, -1), "alpha upper after 3")
+    # the dense equivalent the CUDA path uses gives the same convolution
+    from boundflow_b200.network import dense_conv_weight
+
+    for op in module.get_entry_task().ops:
+        if op.op_type == "conv2d":
+            Wg = module.bindings["params"][op.inputs[1]]
+            x = torch.randn(2, Wg.shape[1] * int(op.attrs["groups"]), 9, 9)
+            ref = torch.nn.functional.conv2d(x, Wg, None, op.attrs["stride"], op.attrs["padding"], op.attrs["dilation"], op.attrs["groups"])
+            got = torch.nn.functional.conv2d(x, dense_conv_weight(Wg, op.attrs), None, op.attrs["stride"], op.attrs["padding"])
+            assert_close(got, ref, f"dense equivalent of {op.name}", atol=1e-5)
+
+
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
 GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
 
