@@ -74,6 +74,7 @@ SIGNATURES = {
     "bf_accumulate": (_i, [_p, _p, C.c_longlong, _p]),
     "bf_interval_relu": (_i, [_p, _p, _p, _p, C.c_longlong, _p]),
     "bf_interval_add": (_i, [_p, _p, _p, _p, _p, _p, C.c_longlong, _p]),
+    "bf_interval_mul": (_i, [_p, _p, _p, _p, _p, _p, C.c_longlong, _p]),
     "bf_first_layer_certificate_max_halfspaces": (_i, []),
     "bf_first_layer_certificate": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),
     "bf_first_layer_certificate_lp": (_i, [_p, _i, _p, _p, _p, _f, _i, _p, _p, _p, _i, _f, _f, _i, _i, _i, _p]),

@@ -589,6 +589,15 @@ __global__ void interval_add_kernel(const float* __restrict__ al, const float* _
     ou[i] = au[i] + bu[i];
   }
 }
+// Interval product: the smallest and largest of the four corner products (domains/interval.py:102-112).
+__global__ void interval_mul_kernel(const float* __restrict__ al, const float* __restrict__ au, const float* __restrict__ bl,
+                                    const float* __restrict__ bu, float* __restrict__ ol, float* __restrict__ ou, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float p0 = al[i] * bl[i], p1 = al[i] * bu[i], p2 = au[i] * bl[i], p3 = au[i] * bu[i];
+    ol[i] = fminf(fminf(p0, p1), fminf(p2, p3));
+    ou[i] = fmaxf(fmaxf(p0, p1), fmaxf(p2, p3));
+  }
+}
 __global__ void accumulate_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
 }
@@ -606,6 +615,14 @@ extern "C" int bf_interval_add(const float* a_l, const float* a_u, const float* 
   BF_REQUIRE(a_l && a_u && b_l && b_u && out_l && out_u && n > 0, BF_E_INVALID, "bf_interval_add: bad argument");
   bf::interval_add_kernel<<<bf::ew_grid(n, 256), 256, 0, bf::as_stream(stream)>>>(a_l, a_u, b_l, b_u, out_l, out_u, n);
   BF_CHECK_LAUNCH("interval_add_kernel");
+  return BF_OK;
+}
+
+extern "C" int bf_interval_mul(const float* a_l, const float* a_u, const float* b_l, const float* b_u, float* out_l, float* out_u,
+                               long long n, bf_stream_t stream) {
+  BF_REQUIRE(a_l && a_u && b_l && b_u && out_l && out_u && n > 0, BF_E_INVALID, "bf_interval_mul: bad argument");
+  bf::interval_mul_kernel<<<bf::ew_grid(n, 256), 256, 0, bf::as_stream(stream)>>>(a_l, a_u, b_l, b_u, out_l, out_u, n);
+  BF_CHECK_LAUNCH("interval_mul_kernel");
   return BF_OK;
 }
 

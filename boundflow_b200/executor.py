@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .crown import _cuda_device, _f32, _stream_ptr, ibp_trace, needs_graph_path
-from .ir import IntervalState, input_mid_rad, normalize_input_spec
+from .ir import IntervalState, input_mid_rad, lp_ball_of, normalize_input_spec
 from .network import _pair, dense_conv_weight
 
 
@@ -125,6 +125,15 @@ class CudaIntervalDomain:
             _lib.check(lib.bf_interval_add(_lib.ptr(al), _lib.ptr(au), _lib.ptr(bl), _lib.ptr(bu), _lib.ptr(ol), _lib.ptr(ou), al.numel(),
                                            _stream_ptr(device)))
             return _state_like(a, ol.to(a.lower.device), ou.to(a.lower.device))
+        if op == "mul":  # corner products; operands broadcast like torch's `*` (domains/interval.py:102-112)
+            lib = _lib.load()
+            device = _cuda_device(a.lower)
+            shape = torch.broadcast_shapes(tuple(a.lower.shape), tuple(b.lower.shape))
+            al, au, bl, bu = (_f32(t, device).expand(shape).contiguous() for t in (a.lower, a.upper, b.lower, b.upper))
+            ol, ou = torch.empty_like(al), torch.empty_like(au)
+            _lib.check(lib.bf_interval_mul(_lib.ptr(al), _lib.ptr(au), _lib.ptr(bl), _lib.ptr(bu), _lib.ptr(ol), _lib.ptr(ou), al.numel(),
+                                           _stream_ptr(device)))
+            return _state_like(a, ol.to(a.lower.device), ou.to(a.lower.device))
         raise NotImplementedError(f"unsupported elementwise op: {op}")
 
 
@@ -152,6 +161,9 @@ class CudaTaskExecutor:
         w_last = params.get(last.inputs[1]) if (last.op_type == "linear" and len(last.inputs) >= 2 and isinstance(params, dict)) else None
         if torch.is_tensor(w_last) and w_last.dim() == 3:
             return self._run_ibp_spec_fused(module, task, spec, output_value)
+        walkers = {"linear", "conv2d", "relu", "add", "concat", "flatten", "reshape"}
+        if any(op.op_type not in walkers for op in task.ops):
+            return self._run_ibp_generic(module, task, spec, output_value)
         if needs_graph_path(module):
             from .dag import run_ibp_dag
 
@@ -196,6 +208,122 @@ class CudaTaskExecutor:
             x = IntervalState(lower=x.lower.flatten(1), upper=x.upper.flatten(1))
         return self.domain.affine_transformer(x, w, b, op="linear", relu_in=relu_in)
 
+    # ---- op-by-op interpretation over the domain ---------------------------
+    def _interpret(self, ops, get_interval, put, get_tensor, linear_on_input=None) -> None:
+        """The op loop of the reference's executors (task_executor.py:184-350) over `self.domain`: linear / conv2d
+        (affine_transformer; a rank-3 weight is the batched form, 229-246), relu, add, mul, concat, flatten, reshape,
+        permute / transpose and spec_linear (185-213).  `linear_on_input(op)` may return the result of a Linear op that
+        reads the input set directly (an Lp ball needs its dual norms there), or None."""
+        for op in ops:
+            t = op.op_type
+            if t in ("linear", "conv2d"):
+                done = linear_on_input(op) if (t == "linear" and linear_on_input is not None) else None
+                if done is not None:
+                    put(op.outputs[0], done)
+                    continue
+                x = get_interval(op.inputs[0])
+                w = get_tensor(op.inputs[1])
+                b = get_tensor(op.inputs[2]) if len(op.inputs) == 3 else None
+                attrs = dict(op.attrs)
+                attrs["op"] = t
+                put(op.outputs[0], self.domain.affine_transformer(x, w, b, **attrs))
+            elif t == "spec_linear":
+                x = get_interval(op.inputs[0])
+                Cm = get_tensor(op.inputs[1])
+                Cm = Cm if torch.is_tensor(Cm) else torch.as_tensor(Cm)
+                if Cm.dim() != 3:
+                    raise ValueError(f"spec_linear expects C rank-3 [B,S,O], got {tuple(Cm.shape)}")
+                if x.lower.dim() != 2:
+                    raise ValueError(f"spec_linear expects logits rank-2 [B,O], got {tuple(x.lower.shape)}")
+                if Cm.shape[0] != x.lower.shape[0] or Cm.shape[2] != x.lower.shape[1]:
+                    raise ValueError(f"spec_linear shape mismatch: C={tuple(Cm.shape)} logits={tuple(x.lower.shape)}")
+                put(op.outputs[0], self.domain.affine_transformer(x, Cm, None, op="linear"))
+            elif t == "relu":
+                put(op.outputs[0], self.domain.relu_transformer(get_interval(op.inputs[0])))
+            elif t == "add":
+                a, b2 = get_interval(op.inputs[0]), get_interval(op.inputs[1])
+                if tuple(a.lower.shape) != tuple(b2.lower.shape):
+                    raise NotImplementedError("CudaTaskExecutor only supports add with exact same-shape inputs")
+                put(op.outputs[0], self.domain.elementwise_transformer([a, b2], op="add"))
+            elif t == "mul":
+                put(op.outputs[0], self.domain.elementwise_transformer([get_interval(op.inputs[0]), get_interval(op.inputs[1])], op="mul"))
+            elif t == "flatten":
+                x = get_interval(op.inputs[0])
+                sd, ed = int(op.attrs.get("start_dim", 0)), int(op.attrs.get("end_dim", -1))
+                put(op.outputs[0], IntervalState(lower=torch.flatten(x.lower, sd, ed), upper=torch.flatten(x.upper, sd, ed)))
+            elif t == "reshape":
+                x = get_interval(op.inputs[0])
+                shape = op.attrs.get("shape")
+                put(op.outputs[0], x if shape is None else IntervalState(lower=x.lower.reshape(shape), upper=x.upper.reshape(shape)))
+            elif t in ("permute", "transpose"):
+                x = get_interval(op.inputs[0])
+                dims = [int(d) for d in op.attrs.get("dims")]
+                put(op.outputs[0], IntervalState(lower=x.lower.permute(*dims), upper=x.upper.permute(*dims)))
+            elif t == "concat":
+                parts = [get_interval(n) for n in op.inputs]
+                axis = int(op.attrs.get("axis", 1))
+                put(op.outputs[0], IntervalState(lower=torch.cat([p.lower for p in parts], dim=axis), upper=torch.cat([p.upper for p in parts], dim=axis)))
+            else:
+                raise NotImplementedError(f"unsupported op_type in task executor: {t}")
+
+    def _run_ibp_generic(self, module: Any, task: Any, spec: Any, output_value: str) -> IntervalState:
+        """Whole-module IBP for op lists outside the chain / graph walkers (mul, permute / transpose, spec_linear):
+        every op through the domain's kernels, values kept in their own shapes."""
+        params = module.bindings.get("params", {})
+        ball = lp_ball_of(spec)
+        device = _cuda_device(spec.center)
+        if ball is not None:
+            center = _f32(spec.center, device)
+            lo, up = center - float(ball[1]), center + float(ball[1])   # the bounding box every non-Linear consumer sees
+        else:
+            _mid, _rad, lo, up = input_mid_rad(spec)
+        env: Dict[str, IntervalState] = {spec.value_name: IntervalState(lower=_f32(lo, device), upper=_f32(up, device))}
+        views = {spec.value_name}
+
+        def get_interval(name: str) -> IntervalState:
+            if name in env:
+                return env[name]
+            if name in params:
+                t = params[name]
+                t = _f32(t if torch.is_tensor(t) else torch.as_tensor(t), device)
+                return IntervalState(lower=t, upper=t)
+            raise KeyError(f"missing value in env/params: {name}")
+
+        def get_tensor(name: str) -> Any:
+            if name in params:
+                return params[name]
+            raise KeyError(f"missing param tensor: {name}")
+
+        def put(name: str, st: IntervalState) -> None:
+            env[name] = st
+
+        def linear_on_input(op):
+            if ball is None or op.inputs[0] not in views:
+                return None
+            lib = _lib.load()
+            W = _f32(get_tensor(op.inputs[1]), device)
+            if W.dim() != 2:
+                return None
+            b = _f32(get_tensor(op.inputs[2]), device) if len(op.inputs) == 3 else None
+            c = _f32(spec.center, device).reshape(int(spec.center.shape[0]), -1).contiguous()
+            n_out, n_in, Bc, s = int(W.shape[0]), int(W.shape[1]), int(c.shape[0]), _stream_ptr(device)
+            row_dev = torch.empty(n_out, dtype=torch.float32, device=device)
+            yl, yu = torch.empty(Bc, n_out, device=device), torch.empty(Bc, n_out, device=device)
+            _lib.check(lib.bf_row_dual_norms(_lib.ptr(W), n_out, n_in, int(ball[0]), float(ball[1]), _lib.ptr(row_dev), s))
+            _lib.check(lib.bf_ibp_linear_lp(_lib.ptr(c), _lib.ptr(row_dev), _lib.ptr(W), _lib.ptr(b), None, 0, None, None, _lib.ptr(yl), _lib.ptr(yu),
+                                            None, Bc, n_in, n_out, s))
+            return IntervalState(lower=yl, upper=yu)
+
+        for op in task.ops:   # one op at a time so that flatten / reshape views of the input stay known
+            self._interpret([op], get_interval, put, get_tensor, linear_on_input)
+            if op.op_type in ("flatten", "reshape") and op.inputs[0] in views:
+                views.add(op.outputs[0])
+        if output_value not in env:
+            raise KeyError(f"missing value in env/params: {output_value}")
+        out = env[output_value]
+        dev = spec.center.device
+        return IntervalState(lower=out.lower.to(dev), upper=out.upper.to(dev))
+
     # ---- one task of a scheduled task graph -------------------------------
     def run_ibp_task(self, task: Any, *, env: Dict[str, IntervalState], params: Dict[str, Any], storage_plan: Any) -> None:
         if not _is_interval_kind(task.kind):
@@ -224,37 +352,4 @@ class CudaTaskExecutor:
                 return params[value_name]
             raise KeyError(f"missing param tensor: {value_name}")
 
-        for op in task.ops:
-            t = op.op_type
-            if t in ("linear", "conv2d"):
-                x = get_interval(op.inputs[0])
-                w = get_tensor(op.inputs[1])
-                b = get_tensor(op.inputs[2]) if len(op.inputs) == 3 else None
-                attrs = dict(op.attrs)
-                attrs["op"] = t
-                env[buf(op.outputs[0])] = self.domain.affine_transformer(x, w, b, **attrs)
-            elif t == "relu":
-                env[buf(op.outputs[0])] = self.domain.relu_transformer(get_interval(op.inputs[0]))
-            elif t == "add":
-                a, b2 = get_interval(op.inputs[0]), get_interval(op.inputs[1])
-                if tuple(a.lower.shape) != tuple(b2.lower.shape):
-                    raise NotImplementedError("CudaTaskExecutor only supports add with exact same-shape inputs")
-                env[buf(op.outputs[0])] = self.domain.elementwise_transformer([a, b2], op="add")
-            elif t == "flatten":
-                x = get_interval(op.inputs[0])
-                sd, ed = int(op.attrs.get("start_dim", 0)), int(op.attrs.get("end_dim", -1))
-                env[buf(op.outputs[0])] = IntervalState(lower=torch.flatten(x.lower, sd, ed), upper=torch.flatten(x.upper, sd, ed))
-            elif t == "reshape":
-                x = get_interval(op.inputs[0])
-                shape = op.attrs.get("shape")
-                env[buf(op.outputs[0])] = x if shape is None else IntervalState(lower=x.lower.reshape(shape), upper=x.upper.reshape(shape))
-            elif t in ("permute", "transpose"):
-                x = get_interval(op.inputs[0])
-                dims = [int(d) for d in op.attrs.get("dims")]
-                env[buf(op.outputs[0])] = IntervalState(lower=x.lower.permute(*dims), upper=x.upper.permute(*dims))
-            elif t == "concat":
-                parts = [get_interval(n) for n in op.inputs]
-                axis = int(op.attrs.get("axis", 1))
-                env[buf(op.outputs[0])] = IntervalState(lower=torch.cat([p.lower for p in parts], dim=axis), upper=torch.cat([p.upper for p in parts], dim=axis))
-            else:
-                raise NotImplementedError(f"unsupported op_type in task executor: {t}")
+        self._interpret(task.ops, get_interval, lambda name, st: env.__setitem__(buf(name), st), get_tensor)

@@ -393,6 +393,43 @@ def make_grouped_dilated_cases(seed: int = 1021):
     return cases
 
 
+def make_executor_op_cases(seed: int = 1023):
+    """Small modules with the op types that only the interval executors handle (task_executor.py:184-350): an elementwise
+    product of two branches, a permute behind a convolution and a `spec_linear` output op.
+    Returns {name: (module, x, lo, up)}."""
+    g = torch.Generator("cpu").manual_seed(seed)
+
+    def rn(*shape, fan):
+        return torch.randn(*shape, generator=g) * math.sqrt(2.0 / fan)
+
+    def mod(tid, ops, params):
+        task = BoundTask(task_id=tid, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        return BFTaskModule(tasks=[task], entry_task_id=tid, bindings={"params": params})
+
+    def box(x, eps):
+        return (x - eps).clamp(0, 1), (x + eps).clamp(0, 1)
+
+    k3 = {"stride": (1, 1), "padding": (1, 1), "dilation": (1, 1), "groups": 1}
+    cases = {}
+    ops = [TaskOp("linear", "a", ["input", "wa", "ba"], ["ha"]), TaskOp("linear", "b", ["input", "wb", "bb"], ["hb"]),
+           TaskOp("relu", "gate", ["hb"], ["rb"]), TaskOp("mul", "product", ["ha", "rb"], ["m"]), TaskOp("linear", "head", ["m", "wh", "bh"], ["out"])]
+    params = {"wa": rn(5, 6, fan=6), "ba": rn(5, fan=50), "wb": rn(5, 6, fan=6), "bb": rn(5, fan=50), "wh": rn(3, 5, fan=5), "bh": rn(3, fan=50)}
+    x = torch.rand(4, 6, generator=g)
+    cases["mul_gate"] = (mod("mul_gate", ops, params), x) + box(x, 0.08)
+    ops = [TaskOp("conv2d", "conv", ["input", "wc", "bc"], ["hc"], k3), TaskOp("relu", "relu", ["hc"], ["rc"]),
+           TaskOp("permute", "to_nhwc", ["rc"], ["pc"], {"dims": [0, 2, 3, 1]}),
+           TaskOp("flatten", "flatten", ["pc"], ["flat"], {"start_dim": 1, "end_dim": -1}), TaskOp("linear", "head", ["flat", "wh", "bh"], ["out"])]
+    params = {"wc": rn(3, 2, 3, 3, fan=18), "bc": rn(3, fan=50), "wh": rn(4, 48, fan=48), "bh": rn(4, fan=50)}
+    x = torch.rand(3, 2, 4, 4, generator=g)
+    cases["permute_cnn"] = (mod("permute_cnn", ops, params), x) + box(x, 0.05)
+    ops = [TaskOp("linear", "body", ["input", "w1", "b1"], ["h1"]), TaskOp("relu", "relu", ["h1"], ["r1"]),
+           TaskOp("linear", "logits", ["r1", "w2", "b2"], ["logits"]), TaskOp("spec_linear", "spec", ["logits", "Cspec"], ["out"])]
+    params = {"w1": rn(7, 6, fan=6), "b1": rn(7, fan=50), "w2": rn(4, 7, fan=7), "b2": rn(4, fan=50), "Cspec": torch.randn(5, 3, 4, generator=g)}
+    x = torch.rand(5, 6, generator=g)
+    cases["spec_linear"] = (mod("spec_linear", ops, params), x) + box(x, 0.06)
+    return cases
+
+
 def make_graph_cases(seed: int = 1011):
     """Small graphs that are not chains, shaped like the reference's end-to-end fixtures
     (tests/test_phase7a_pr12_e2e_crown_runtime.py:98-239): a residual CNN block with a projection skip

@@ -202,8 +202,9 @@ int bf_crown_relu_conv2d_bwd(const float* A, int side,
  *            A_prev = A * slope_sel, delta (+)= sum_k A * intercept_sel.  A, A_prev [B,S,n] (may alias);
  *            slopes [B,n]; scratch (bf_crown_relu_bwd_scratch_bytes) only for n > 4096 with delta.
  *   bf_accumulate: dst += src, _accumulate_backward_state crown_ibp.py:879-913.
- *   bf_interval_relu / bf_interval_add: IntervalDomain.relu_transformer / elementwise_transformer("add"),
- *            boundflow/domains/interval.py:88-110. */
+ *   bf_interval_relu / bf_interval_add / bf_interval_mul: IntervalDomain.relu_transformer /
+ *            elementwise_transformer("add" | "mul"), boundflow/domains/interval.py:88-114 (mul: the smallest and
+ *            largest of the four corner products; same-shape operands, the caller expands a broadcast one). */
 size_t bf_crown_relu_bwd_scratch_bytes(int B, int S, int n);
 int bf_crown_relu_bwd(const float* A, int side, const float* alpha_u, const float* alpha_l,
                       const float* beta_u, const float* beta_l, float* A_prev, float* delta, int accumulate,
@@ -211,6 +212,8 @@ int bf_crown_relu_bwd(const float* A, int side, const float* alpha_u, const floa
 int bf_accumulate(float* dst, const float* src, long long n, bf_stream_t stream);
 int bf_interval_relu(const float* l, const float* u, float* out_l, float* out_u, long long n, bf_stream_t stream);
 int bf_interval_add(const float* a_l, const float* a_u, const float* b_l, const float* b_u,
+                    float* out_l, float* out_u, long long n, bf_stream_t stream);
+int bf_interval_mul(const float* a_l, const float* a_u, const float* b_l, const float* b_u,
                     float* out_l, float* out_u, long long n, bf_stream_t stream);
 
 /* Allocation-free variant of bf_crown_relu_conv2d_bwd.  It has no counterpart in the

@@ -104,6 +104,19 @@ def forward_ibp_graph(module: Any, lo: torch.Tensor, up: torch.Tensor, *, input_
         elif t == "concat":
             ls, us = zip(*[get(n) for n in op.inputs])
             env[out] = (torch.cat(ls, dim=1), torch.cat(us, dim=1))
+        elif t == "mul":  # IntervalDomain.elementwise_transformer("mul"), domains/interval.py:102-112
+            (al, au), (bl, bu) = get(op.inputs[0]), get(op.inputs[1])
+            cand = torch.stack([al * bl, al * bu, au * bl, au * bu], dim=0)
+            env[out] = (cand.min(dim=0).values, cand.max(dim=0).values)
+        elif t in ("permute", "transpose"):  # task_executor.py:334-346
+            l, u = get(op.inputs[0])
+            dims = [int(d) for d in op.attrs["dims"]]
+            env[out] = (l.permute(*dims), u.permute(*dims))
+        elif t == "spec_linear":  # y = C @ logits with C [B,S,O], task_executor.py:185-213
+            l, u = get(op.inputs[0])
+            Cm = P[op.inputs[1]]
+            c_pos, c_neg = Cm.clamp(min=0.0), Cm.clamp(max=0.0)
+            env[out] = ((c_pos * l.unsqueeze(1) + c_neg * u.unsqueeze(1)).sum(dim=-1), (c_pos * u.unsqueeze(1) + c_neg * l.unsqueeze(1)).sum(dim=-1))
         else:
             raise NotImplementedError(t)
     return env, relu_pre

@@ -600,6 +600,22 @@ def gen_grouped_dilated() -> None:
     save("grouped_dilated.npz", **out)
 
 
+def gen_executor_ops() -> None:
+    """`PythonTaskExecutor.run_ibp` on the modules of workloads.make_executor_op_cases (mul, permute, spec_linear), on the box and, for the two vector-input modules, on an L2 ball (first Linear: dual norms)."""
+    out = {}
+    for name, (module, x, lo, up) in W.make_executor_op_cases().items():
+        src = module.get_entry_task()
+        ops = [TaskOp(op_type=o.op_type, name=o.name, inputs=list(o.inputs), outputs=list(o.outputs), attrs=dict(o.attrs)) for o in src.ops]
+        task = BoundTask(task_id=src.task_id, kind=TaskKind.INTERVAL_IBP, ops=ops, input_values=["input"], output_values=["out"])
+        m = BFTaskModule(tasks=[task], entry_task_id=src.task_id, bindings={"params": dict(module.bindings["params"])})
+        ibp = PythonTaskExecutor().run_ibp(m, InputSpec.box(value_name="input", lower=lo, upper=up))
+        out[f"{name}_box_lower"], out[f"{name}_box_upper"] = ibp.lower, ibp.upper
+        if x.dim() == 2:
+            ibp = PythonTaskExecutor().run_ibp(m, InputSpec.l2(value_name="input", center=x, eps=0.2))
+            out[f"{name}_l2_lower"], out[f"{name}_l2_upper"] = ibp.lower, ibp.upper
+    save("executor_ops.npz", **out)
+
+
 def gen_lp_alpha() -> None:
     """alpha-CROWN (per-domain parameters, adaptive start) on L2 and L1 balls, c3 MLP, 8 inputs."""
     wl = W.make_workload("c3", batch=8)
@@ -1044,7 +1060,7 @@ GENERATORS = {"lp_ball": gen_lp_ball, "shared_alpha": gen_shared_alpha, "spec_fu
               "graph_certificate": gen_graph_certificate, "beta_reduce": gen_beta_reduce,
               "graph_lp": gen_graph_lp, "lp_certificate": gen_lp_certificate,
               "graph_trace": gen_graph_trace, "add_coeff": gen_add_coeff,
-              "grouped_dilated": gen_grouped_dilated}
+              "grouped_dilated": gen_grouped_dilated, "executor_ops": gen_executor_ops}
 
 
 def main() -> None:

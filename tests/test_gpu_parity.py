@@ -527,6 +527,46 @@ def test_sampled_soundness_c1_and_c3(dev):
     assert wlo <= 1e-2 and wup <= 1e-2   # bounds here are O(1e4); 1e-2 is 1e-6 relative
 
 
+@pytest.mark.parametrize("name", ["mul_gate", "permute_cnn", "spec_linear"])
+def test_executor_only_ops_match_reference_golden(dev, golden, name):
+    """mul, permute and spec_linear (task_executor.py:184-350) through `CudaTaskExecutor.run_ibp` (box and L2 ball) and, op by
+    op, through `run_ibp_task`, against `PythonTaskExecutor.run_ibp` (tests/golden/executor_ops.npz)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.executor import CudaIntervalDomain, CudaTaskExecutor
+    from boundflow_b200.ir import BoundTask, InputSpec, IntervalState, StoragePlan, TaskKind
+
+    g = golden("executor_ops.npz")
+    module, x, lo, up = W.make_executor_op_cases()[name]
+    ex = CudaTaskExecutor()
+    out = ex.run_ibp(module, InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev)))
+    assert_close(out.lower, g[f"{name}_box_lower"], "box lower")
+    assert_close(out.upper, g[f"{name}_box_upper"], "box upper")
+    if x.dim() == 2:
+        out = ex.run_ibp(module, InputSpec.l2(value_name="input", center=x.to(dev), eps=0.2))
+        assert_close(out.lower, g[f"{name}_l2_lower"], "L2 ball lower")
+        assert_close(out.upper, g[f"{name}_l2_upper"], "L2 ball upper")
+    ops = module.get_entry_task().ops
+    names = {"input"} | {o.outputs[0] for o in ops} | set(module.bindings["params"])
+    plan = StoragePlan(value_to_buffer={n: f"buf_{n}" for n in names})
+    env = {"buf_input": IntervalState(lower=lo.to(dev), upper=up.to(dev))}
+    params = {k: v.to(dev) for k, v in module.bindings["params"].items()}
+    for k, op in enumerate(ops):
+        task = BoundTask(task_id=f"t{k}", kind=TaskKind.INTERVAL_IBP, ops=[op], input_values=[op.inputs[0]], output_values=list(op.outputs))
+        ex.run_ibp_task(task, env=env, params=params, storage_plan=plan)
+    assert_close(env["buf_out"].lower, g[f"{name}_box_lower"], "task-by-task lower")
+    assert_close(env["buf_out"].upper, g[f"{name}_box_upper"], "task-by-task upper")
+    if name == "mul_gate":   # the domain op alone: mixed signs, and a broadcast operand
+        gen = torch.Generator("cpu").manual_seed(3)
+        al = torch.randn(5, 7, generator=gen)
+        au = al + torch.rand(5, 7, generator=gen)
+        bl = torch.randn(1, 7, generator=gen)
+        bu = bl + torch.rand(1, 7, generator=gen)
+        got = CudaIntervalDomain().elementwise_transformer([IntervalState(lower=al.to(dev), upper=au.to(dev)), IntervalState(lower=bl.to(dev), upper=bu.to(dev))],
+                                                           op="mul")
+        cand = torch.stack([al * bl, al * bu, au * bl, au * bu])
+        assert torch.equal(got.lower.cpu(), cand.min(dim=0).values) and torch.equal(got.upper.cpu(), cand.max(dim=0).values)
+
+
 def test_executor_run_ibp_task_matches_whole_module(dev):
     """Scheduler-style execution (one op per task over a buffer env) equals run_ibp."""
     from boundflow_b200 import workloads as W

@@ -688,6 +688,23 @@ def test_grouped_and_dilated_convolutions(golden, name):
             assert_close(got, ref, f"dense equivalent of {op.name}", atol=1e-5)
 
 
+@pytest.mark.parametrize("name", ["mul_gate", "permute_cnn", "spec_linear"])
+def test_executor_only_ops(golden, name):
+    """The op types that only the interval executors handle (mul, permute, spec_linear; task_executor.py:184-350), on a box
+    and on an L2 ball, against `PythonTaskExecutor.run_ibp` (executor_ops.npz)."""
+    from oracle import graph_oracle as GO
+
+    g = golden("executor_ops.npz")
+    module, x, lo, up = W.make_executor_op_cases()[name]
+    env, _pre = GO.forward_ibp_graph(module, lo, up)
+    assert_close(env["out"][0], g[f"{name}_box_lower"], "box lower")
+    assert_close(env["out"][1], g[f"{name}_box_upper"], "box upper")
+    if x.dim() == 2:
+        env, _pre = GO.forward_ibp_graph(module, x - 0.2, x + 0.2, ball=(2, 0.2))
+        assert_close(env["out"][0], g[f"{name}_l2_lower"], "L2 ball lower")
+        assert_close(env["out"][1], g[f"{name}_l2_upper"], "L2 ball upper")
+
+
 GRAPH_OBJECTIVE_CASES = (("upper", "mean"), ("gap", "min"), ("both", "softmin"), ("lower", "softmin"), ("lower", "min"))
 GRAPH_SHARED_CASES = (("lower", "mean"), ("gap", "mean"), ("both", "min"), ("upper", "softmin"))
 
