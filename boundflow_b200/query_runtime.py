@@ -114,10 +114,10 @@ class CudaQueryRuntime:
         steps = _option(opts, "alpha_steps", int)
         lr = _option(opts, "alpha_lr", float)
         alpha_init = _option(opts, "alpha_init", float)
-        objective = str(opts.get("objective", "lower"))
-        spec_reduce = str(opts.get("spec_reduce", "mean"))
-        if objective != "lower":
-            raise NotImplementedError("the CUDA backend optimises the lower bound only")
+        # objective / reduction options of the replay (bab_query.py:860-864, 882-886)
+        kw = {"objective": str(opts.get("objective", "lower")), "spec_reduce": str(opts.get("spec_reduce", "mean")),
+              "soft_tau": float(opts.get("soft_tau", 1.0)), "lb_weight": float(opts.get("lb_weight", 1.0)),
+              "ub_weight": float(opts.get("ub_weight", 1.0))}
         D = len(reqs)
         first = normalize_input_spec(reqs[0].payload.input_spec)
         dev_in = first.center.device
@@ -169,15 +169,15 @@ class CudaQueryRuntime:
             if splits:
                 beta_splits = [splits.get(n) for n in relu_names]
                 best_l, best_u, best_a, _last, _metric, best_b = alpha_crown_from_trace(
-                    trace, C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce, beta_splits=beta_splits, beta0=beta0)
+                    trace, C, alpha0, steps=steps, lr=lr, beta_splits=beta_splits, beta0=beta0, **kw)
             else:
-                best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
+                best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, C, alpha0, steps=steps, lr=lr, **kw)
                 best_b = beta0
             branches: List[Optional[Tuple[str, int]]] = branch_choices_from_trace(trace)
         elif method == "alpha-CROWN":
             # the reference replays these one node at a time with alpha shared across the node's single batch row
             # (bab_query.py:875-891); with one row per node that is the per-domain optimisation
-            best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, C, alpha0, steps=steps, lr=lr, spec_reduce=spec_reduce)
+            best_l, best_u, best_a, _last, _metric = alpha_crown_from_trace(trace, C, alpha0, steps=steps, lr=lr, **kw)
             branches = [None] * D
         else:
             raise ValueError(f"unsupported BaB query method: {method}")

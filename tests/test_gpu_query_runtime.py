@@ -99,3 +99,26 @@ def test_mixed_groups_and_alpha_only(dev):
         bad = _requests(dev, 1, method="CROWN")[2]
         CudaQueryRuntime().execute(wl.module, bad)
     assert CudaQueryRuntime().execute(wl.module, []) == []
+
+
+@pytest.mark.parametrize("objective,reduce", [("gap", "min"), ("lower", "softmin"), ("upper", "mean")])
+def test_objective_and_reduction_options_reach_the_loop(dev, objective, reduce):
+    """The replay options of a query (`objective`, `spec_reduce`, `soft_tau`, `lb_weight`, `ub_weight`; bab_query.py:860-864)
+    select the same loop as a direct call with those arguments."""
+    from boundflow_b200.crown import run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from boundflow_b200.query_runtime import CudaQueryRuntime
+
+    D = 6
+    opts = dict(OPTS, objective=objective, spec_reduce=reduce, soft_tau=20.0, lb_weight=1.0, ub_weight=0.5)
+    wl, splits, reqs = _requests(dev, D, opts=opts)
+    out = CudaQueryRuntime().execute(wl.module, reqs)
+    spec = InputSpec.box(value_name="input", lower=wl.lo.expand(D, -1).contiguous().to(dev), upper=wl.up.expand(D, -1).contiguous().to(dev))
+    state = {n: s.to(dev) for n, s in zip(wl.relu_names, splits)}
+    b, _a, _bt, _stats = run_alpha_beta_crown_mlp(wl.module, spec, linear_spec_C=wl.C.expand(D, -1, -1).contiguous().to(dev), relu_split_state=state,
+                                                 steps=5, lr=0.1, alpha_init=0.5, per_batch_params=True, objective=objective, spec_reduce=reduce,
+                                                 soft_tau=20.0, lb_weight=1.0, ub_weight=0.5)
+    for i, (_qid, r) in enumerate(out):
+        assert r.status == "ok"
+        assert_close(r.lower, b.lower[i : i + 1], f"node {i} lower")
+        assert_close(r.upper, b.upper[i : i + 1], f"node {i} upper")
