@@ -956,6 +956,8 @@ def _run_alpha_beta_crown_graph(module, input_spec, *, linear_spec_C, relu_split
     a_state = AlphaState({n: best_a[n].reshape(lead + tuple(tr.shape[n])).to(dev) for n in names})
     b_state = BetaState({n: best_b[n].reshape(lead + tuple(tr.shape[n])).to(dev) for n in names})
     stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(names))
+    stats.branch_choices = _branch_choices([tr.pre_l[n] for n in names], [tr.pre_u[n] for n in names], names,  # type: ignore[attr-defined]
+                                           [int(tr.pre_l[n].shape[1]) for n in names], tr.B, tr.mid.device)
     return bounds, a_state, b_state, stats
 
 
@@ -1077,14 +1079,23 @@ def run_alpha_beta_crown_mlp(
 def branch_choices_from_trace(trace: ForwardTrace) -> List[Optional[Tuple[str, int]]]:
     """Widest-unstable-gap branching hint per domain as (ReLU input name, flat neuron index) or None
     (`_branch_choices_from_relu_pre`, alpha_beta_crown.py:145-182).  Synchronises to return Python values."""
-    chain, B, device = trace.chain, trace.B, trace.mid.device
+    chain = trace.chain
+    return _branch_choices(trace.pre_l, trace.pre_u, chain.relu_input_names, chain.relu_widths, trace.B, trace.mid.device)
+
+
+def _branch_choices(pre_l: Sequence[torch.Tensor], pre_u: Sequence[torch.Tensor], names: Sequence[str], widths: Sequence[int], B: int,
+                    device: torch.device) -> List[Optional[Tuple[str, int]]]:
+    """The hint from the pre-activation bounds of the ReLUs in graph order ([B, n_r] each)."""
+    if not names:
+        return [None] * B
+    lib = _lib.load()
     gap = torch.empty(B, dtype=torch.float32, device=device)
     relu = torch.empty(B, dtype=torch.int32, device=device)
     idx = torch.empty(B, dtype=torch.int32, device=device)
-    _lib.check(chain.lib.bf_branch_scores(_lib.ptr_array(trace.pre_l), _lib.ptr_array(trace.pre_u), _lib.int_array(chain.relu_widths),
-                                          len(chain.relu_widths), _lib.ptr(gap), _lib.ptr(relu), _lib.ptr(idx), B, _stream_ptr(device)))
+    _lib.check(lib.bf_branch_scores(_lib.ptr_array(list(pre_l)), _lib.ptr_array(list(pre_u)), _lib.int_array(list(widths)), len(widths),
+                                    _lib.ptr(gap), _lib.ptr(relu), _lib.ptr(idx), B, _stream_ptr(device)))
     relu_h, idx_h = relu.cpu().tolist(), idx.cpu().tolist()
-    return [None if r < 0 else (chain.relu_input_names[r], int(j)) for r, j in zip(relu_h, idx_h)]
+    return [None if r < 0 else (names[r], int(j)) for r, j in zip(relu_h, idx_h)]
 
 
 def run_crown_intermediate_mlp(

@@ -9,7 +9,11 @@ reference's `execute_alpha_beta_query_batch` (boundflow/runtime/query_executor.p
 does -- stack the nodes' centres, split rows and warm starts, run the per-domain
 alpha-beta loop once, slice the results per node -- on the CUDA backend, with one
 difference: a node whose split assignment is empty gets `status="infeasible"` on its
-own instead of failing the whole batch.
+own instead of failing the whole batch.  Chains on a box run on the fused whole-chain
+loops; graphs that are not chains and L1 / L2 ball input sets go through
+`run_alpha_beta_crown_mlp(per_batch_params=True)` on the same stacked batch.  The query's
+`objective`, `spec_reduce`, `soft_tau`, `lb_weight` and `ub_weight` options reach the loop
+(bab_query.py:860-864).
 
 Requests are read by attribute only (`request.query.query_id`,
 `request.query.bound_method`, `request.query.execution_options`, `request.payload.*`),
@@ -23,8 +27,9 @@ from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from .crown import alpha_crown_from_trace, branch_choices_from_trace, ibp_trace
-from .ir import BoxPerturbation, InputSpec, input_mid_rad, normalize_input_spec
+from .crown import (AlphaState, BetaState, alpha_crown_from_trace, branch_choices_from_trace, ibp_trace, needs_graph_path,
+                    run_alpha_beta_crown_mlp)
+from .ir import BoxPerturbation, InputSpec, input_mid_rad, lp_ball_of, normalize_input_spec
 
 
 @dataclass(frozen=True)
@@ -48,6 +53,16 @@ def _result_type():
         return RefResult
     except Exception:
         return BoundQueryResult
+
+
+def _rows_of_spec(spec: Any, rows: Sequence[int], ball) -> Any:
+    """The input sets of the chosen nodes of a stacked spec."""
+    idx = torch.as_tensor(list(rows), device=spec.center.device)
+    if ball is not None:
+        mk = InputSpec.l2 if int(ball[0]) == 2 else InputSpec.l1
+        return mk(value_name=spec.value_name, center=spec.center[idx], eps=float(ball[1]))
+    pert = spec.perturbation
+    return InputSpec(spec.value_name, spec.center[idx], BoxPerturbation(lower=pert.lower[idx], upper=pert.upper[idx]))
 
 
 def _method_name(query: Any) -> str:
@@ -121,6 +136,8 @@ class CudaQueryRuntime:
         D = len(reqs)
         first = normalize_input_spec(reqs[0].payload.input_spec)
         dev_in = first.center.device
+        if needs_graph_path(module) or lp_ball_of(first) is not None:
+            return self._execute_batch_general(module, reqs, method, opts, kw, steps, lr, alpha_init)
         # stacked input set: per-node boxes (or L-inf balls as boxes)
         los, ups = [], []
         for r in reqs:
@@ -198,6 +215,105 @@ class CudaQueryRuntime:
             results.append(Result(
                 status="ok", lower=best_l[i : i + 1].to(dev_in).clone(), upper=best_u[i : i + 1].to(dev_in).clone(), branch=branches[i],
                 alpha_state_version=None, beta_state_version=None, alpha_by_relu_input=alpha_i, beta_by_relu_input=beta_i))
+        return results
+
+    # -- graphs that are not chains, and L1 / L2 ball inputs: the whole-query functions --------------
+    def _execute_batch_general(self, module: Any, reqs: Sequence[Any], method: str, opts: Mapping[str, object], kw: Mapping[str, object],
+                               steps: int, lr: float, alpha_init: float) -> List[Any]:
+        """The same stacking through `run_alpha_beta_crown_mlp(per_batch_params=True)`, which walks non-chain graphs and
+        takes Lp balls.  A batch with an empty node raises there; its nodes are then evaluated one by one so that only the
+        empty ones are reported."""
+        Result = _result_type()
+        D = len(reqs)
+        first = normalize_input_spec(reqs[0].payload.input_spec)
+        dev_in = first.center.device
+        ball = lp_ball_of(first)
+        specs = [normalize_input_spec(r.payload.input_spec) for r in reqs]
+        if any(int(sp.center.shape[0]) != 1 for sp in specs):
+            raise ValueError("a BaB query bounds one node: its input set must have batch size 1")
+        if ball is not None:
+            mk = InputSpec.l2 if int(ball[0]) == 2 else InputSpec.l1
+            spec = mk(value_name=first.value_name, center=torch.cat([sp.center for sp in specs], dim=0), eps=float(ball[1]))
+        else:
+            boxes = [input_mid_rad(sp) for sp in specs]
+            lo_b, up_b = torch.cat([b[2] for b in boxes], dim=0), torch.cat([b[3] for b in boxes], dim=0)
+            spec = InputSpec(first.value_name, (lo_b + up_b) / 2.0, BoxPerturbation(lower=lo_b, upper=up_b))
+        cs = [r.payload.linear_spec_c for r in reqs]
+        if all(c is None for c in cs):
+            C = None
+        elif any(c is None for c in cs):
+            raise ValueError("query batch mixes implicit and explicit output specs")
+        else:
+            C = torch.cat([c.unsqueeze(0) if c.dim() == 2 else c for c in cs], dim=0)
+        names = list(reqs[0].payload.split_by_relu_input)
+        splits = {n: torch.stack([r.payload.split_by_relu_input[n].reshape(-1) for r in reqs], dim=0) for n in names}
+
+        def warm(source: str, default: float):
+            """Stacked warm starts; a node without one takes the default value, a ReLU no node warms keeps the loop's own start."""
+            seen: Dict[str, torch.Tensor] = {}
+            for r in reqs:
+                for n, t in getattr(r.payload, source).items():
+                    if t is not None:
+                        seen.setdefault(n, t)
+            out = {}
+            for n, like in seen.items():
+                rows = []
+                for r in reqs:
+                    t = getattr(r.payload, source).get(n)
+                    rows.append(torch.full((like.numel(),), float(default), dtype=torch.float32, device=like.device) if t is None
+                                else t.detach().to(dtype=torch.float32).reshape(-1))
+                out[n] = torch.stack(rows, dim=0)
+            return out
+
+        with_beta = method == "alpha-beta-CROWN"
+        if method not in ("alpha-beta-CROWN", "alpha-CROWN"):
+            raise ValueError(f"unsupported BaB query method: {method}")
+        beta_init = _option(opts, "beta_init", float) if with_beta else 0.0
+        wa, wb = warm("warm_alpha_by_relu_input", alpha_init), (warm("warm_beta_by_relu_input", beta_init) if with_beta else {})
+
+        def run(rows: Sequence[int]):
+            sub = spec if len(rows) == D else _rows_of_spec(spec, rows, ball)
+            idx = torch.as_tensor(list(rows))
+            return run_alpha_beta_crown_mlp(
+                module, sub, linear_spec_C=None if C is None else C[idx.to(C.device)],
+                relu_split_state={n: v[idx.to(v.device)] for n, v in splits.items()} if splits else None, steps=steps, lr=lr, alpha_init=alpha_init,
+                beta_init=beta_init, warm_start_alpha=AlphaState({n: v[idx.to(v.device)] for n, v in wa.items()}) if wa else None,
+                warm_start_beta=BetaState({n: v[idx.to(v.device)] for n, v in wb.items()}) if wb else None, per_batch_params=True,
+                optimize_beta=bool(with_beta and splits), **kw)
+
+        self._batches += 1
+        self._queries += D
+        empty = Result(status="infeasible" if with_beta else "rejected", lower=None, upper=None, branch=None, alpha_state_version=None,
+                       beta_state_version=None)
+        try:
+            parts = [(list(range(D)), run(list(range(D))))]
+        except ValueError:
+            parts = []
+            for i in range(D):
+                try:
+                    parts.append(([i], run([i])))
+                except ValueError:
+                    parts.append(([i], None))
+        results: List[Any] = [None] * D
+        for rows, res in parts:
+            if res is None:
+                self._infeasible += len(rows)
+                for i in rows:
+                    results[i] = empty
+                continue
+            bounds, a_state, b_state, stats = res
+            if getattr(stats, "feasibility", "unknown") == "infeasible":   # the single-node certificate fired
+                self._infeasible += len(rows)
+                for i in rows:
+                    results[i] = empty
+                continue
+            choices = getattr(stats, "branch_choices", None)
+            for k, i in enumerate(rows):
+                alpha_i = {n: v[k].to(dev_in).clone() for n, v in a_state.alpha_by_relu_input.items()}
+                beta_i = {n: v[k].to(dev_in).clone() for n, v in b_state.beta_by_relu_input.items()} if with_beta else {}
+                results[i] = Result(status="ok", lower=bounds.lower[k : k + 1].to(dev_in).clone(), upper=bounds.upper[k : k + 1].to(dev_in).clone(),
+                                    branch=(choices[k] if (with_beta and choices) else None), alpha_state_version=None, beta_state_version=None,
+                                    alpha_by_relu_input=alpha_i, beta_by_relu_input=beta_i)
         return results
 
     def audit(self) -> Dict[str, object]:

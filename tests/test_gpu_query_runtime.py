@@ -122,3 +122,67 @@ def test_objective_and_reduction_options_reach_the_loop(dev, objective, reduce):
         assert r.status == "ok"
         assert_close(r.lower, b.lower[i : i + 1], f"node {i} lower")
         assert_close(r.upper, b.upper[i : i + 1], f"node {i} upper")
+
+
+def _node_requests(module_spec_rows, C_rows, split_rows, opts, method="alpha-beta-CROWN"):
+    reqs = []
+    for i, spec in enumerate(module_spec_rows):
+        payload = SimpleNamespace(input_spec=spec, linear_spec_c=None if C_rows is None else C_rows[i],
+                                  split_by_relu_input={n: s[i] for n, s in split_rows.items()}, warm_alpha_by_relu_input={}, warm_beta_by_relu_input={})
+        query = SimpleNamespace(query_id=f"n{i}", bound_method=SimpleNamespace(value=method), execution_options=dict(opts))
+        reqs.append(SimpleNamespace(query=query, payload=payload))
+    return reqs
+
+
+def test_graph_module_and_lp_ball_nodes(dev, golden):
+    """Nodes of a graph that is not a chain (splits of tests/golden/graph_alpha.npz) and nodes with an L2-ball input set go
+    through the whole-query functions: the same numbers as one direct call on the stacked batch, the branching hint of
+    every node, and an empty node reported alone."""
+    import numpy as np
+
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_alpha_beta_crown_mlp
+    from boundflow_b200.ir import InputSpec
+    from boundflow_b200.query_runtime import CudaQueryRuntime
+
+    ga = golden("graph_alpha.npz")
+    module, _x, lo, up, C = W.make_graph_cases()["fanout_mlp"]
+    B = int(lo.shape[0])
+    split = {"h": torch.from_numpy(np.asarray(ga["fanout_mlp_split_h"])).to(torch.int8).to(dev)}
+    specs = [InputSpec.box(value_name="input", lower=lo[i : i + 1].to(dev), upper=up[i : i + 1].to(dev)) for i in range(B)]
+    reqs = _node_requests(specs, C.to(dev), split, OPTS)
+    rt = CudaQueryRuntime()
+    out = rt.execute(module, reqs)
+    whole = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    b, _a, bt, stats = run_alpha_beta_crown_mlp(module, whole, linear_spec_C=C.to(dev), relu_split_state=split, steps=5, lr=0.1, alpha_init=0.5,
+                                               per_batch_params=True)
+    for i, (qid, r) in enumerate(out):
+        assert qid == f"n{i}" and r.status == "ok"
+        assert_close(r.lower, b.lower[i : i + 1], f"graph node {i} lower")
+        assert_close(r.upper, b.upper[i : i + 1], f"graph node {i} upper")
+        assert_close(r.beta_by_relu_input["h"], bt.beta_by_relu_input["h"][i], f"graph node {i} beta", atol=1e-6)
+        assert r.branch == stats.branch_choices[i]
+    # the hint: widest unstable gap of the (split) pre-activation bounds, first index on ties
+    from boundflow_b200.dag import forward_ibp_dag
+
+    tr = forward_ibp_dag(module, whole, split)
+    gap = torch.where((tr.pre_l["h"] < 0) & (tr.pre_u["h"] > 0), tr.pre_u["h"] - tr.pre_l["h"], torch.full_like(tr.pre_l["h"], -1.0))
+    assert [c[1] for c in stats.branch_choices] == gap.argmax(dim=1).cpu().tolist() and all(c[0] == "h" for c in stats.branch_choices)
+    # an empty node (a neuron forced inactive whose lower bound is positive) is reported alone
+    tr0 = forward_ibp_dag(module, whole)
+    on = int(torch.nonzero(tr0.pre_l["h"][1] > 0)[0])
+    bad = {"h": split["h"].clone()}
+    bad["h"][1, on] = -1
+    out = rt.execute(module, _node_requests(specs, C.to(dev), bad, OPTS))
+    assert [r.status for _q, r in out] == ["ok", "infeasible", "ok", "ok", "ok"]
+    assert_close(out[0][1].lower, b.lower[0:1], "node 0 beside the empty node")
+    # L2-ball nodes on the chain c1
+    wl = W.make_workload("c1", batch=6)
+    specs = [InputSpec.l2(value_name="input", center=wl.x[i : i + 1].to(dev), eps=0.1) for i in range(6)]
+    out = rt.execute(wl.module, _node_requests(specs, wl.C.to(dev), {}, OPTS, method="alpha-CROWN"))
+    b, _a, _bt, _s = run_alpha_beta_crown_mlp(wl.module, InputSpec.l2(value_name="input", center=wl.x.to(dev), eps=0.1), linear_spec_C=wl.C.to(dev),
+                                             steps=5, lr=0.1, alpha_init=0.5, per_batch_params=True)
+    for i, (_qid, r) in enumerate(out):
+        assert r.status == "ok" and r.branch is None
+        assert_close(r.lower, b.lower[i : i + 1], f"L2 node {i} lower")
+        assert_close(r.upper, b.upper[i : i + 1], f"L2 node {i} upper")
