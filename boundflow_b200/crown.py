@@ -464,9 +464,15 @@ def run_crown_ibp_mlp(
     relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None,
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
     relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+    materialization_plan: Any = None,
+    materialization_placement_plan: Any = None,
+    fused_crown_executor: Any = None,
+    fused_crown_steps: Sequence[Any] = (),
 ) -> IntervalState:
     """IBP trace + one CROWN backward sweep per side (crown_ibp.py:2054-2133).  Graphs with add / concat /
-    fan-out go through the general graph path (`dag.py`), chains through the fused sweeps."""
+    fan-out go through the general graph path (`dag.py`), chains through the fused sweeps.  The last four arguments
+    are the reference's execution-strategy arguments (when lazily kept operators are made dense, which steps a plug-in
+    executor takes): accepted so that existing calls keep working, without effect here - the bounds do not depend on them."""
     if needs_graph_path(module):
         from .dag import run_crown_ibp_dag
 
@@ -492,8 +498,14 @@ def run_crown_ibp_mlp_from_forward_trace(
     relu_alpha: Optional[Mapping[str, torch.Tensor]] = None,
     relu_pre_add_coeff_u: Optional[Mapping[str, torch.Tensor]] = None,
     relu_pre_add_coeff_l: Optional[Mapping[str, torch.Tensor]] = None,
+    materialization_plan: Any = None,
+    materialization_placement_plan: Any = None,
+    fused_crown_executor: Any = None,
+    fused_crown_steps: Sequence[Any] = (),
+    fused_crown_context: Any = None,
 ) -> IntervalState:
-    """Backward-only CROWN given a forward trace (crown_ibp.py:2136-2230)."""
+    """Backward-only CROWN given a forward trace (crown_ibp.py:2136-2230).  The last five arguments are the
+    reference's execution-strategy arguments, accepted without effect (the bounds do not depend on them)."""
     if needs_graph_path(module):
         from .dag import crown_dag
 
@@ -834,6 +846,8 @@ def run_alpha_crown_mlp(
     ub_weight: float = 1.0,
     warm_start: Optional[Any] = None,
     relu_split_state: Optional[Mapping[str, torch.Tensor]] = None,
+    materialization_plan: Any = None,
+    materialization_placement_plan: Any = None,
 ):
     """alpha-CROWN with alpha stored per ReLU neuron and shared across batch and spec rows
     (`run_alpha_crown_mlp`, runtime/alpha_crown.py:137-261): steps+1 evaluations, Adam on
@@ -980,8 +994,12 @@ def run_alpha_beta_crown_mlp(
     optimize_beta: Optional[bool] = None,
     lb_weight: float = 1.0,
     ub_weight: float = 1.0,
+    materialization_plan: Any = None,
+    materialization_placement_plan: Any = None,
 ):
-    """Per-domain alpha-beta optimisation (alpha_beta_crown.py:643-941).
+    """Per-domain alpha-beta optimisation (alpha_beta_crown.py:643-941).  `materialization_plan` /
+    `materialization_placement_plan` (also on `run_alpha_crown_mlp`) are the reference's execution-strategy
+    arguments, accepted without effect.
 
     Like the reference, beta (one multiplier >= 0 per split neuron and domain, start
     `beta_init` or `warm_start_beta`) is optimised together with alpha whenever a split

@@ -237,6 +237,10 @@ def test_whole_query_functions_accept_reference_objects(dev):
     got = run_crown_ibp_mlp(module, spec, linear_spec_C=C)
     assert_close(got.lower, want.lower, "CROWN lower")
     assert_close(got.upper, want.upper, "CROWN upper")
+    # the reference's execution-strategy keywords are accepted (no effect on the bounds)
+    got = run_crown_ibp_mlp(module, spec, linear_spec_C=C, materialization_plan=None, materialization_placement_plan=None,
+                            fused_crown_executor=None, fused_crown_steps=())
+    assert_close(got.lower, want.lower, "CROWN lower, strategy keywords given")
     env_w, pre_w = _forward_ibp_trace_mlp(module, spec)
     env_g, pre_g = forward_ibp_trace_mlp(module, spec)
     for name in pre_w:
