@@ -10,6 +10,7 @@ The sampler is test infrastructure: plain torch forward passes in float64 on the
   c4  alpha-CROWN (10 steps) on 8 ReLU-split subdomains; only samples that satisfy the split constraints count
       (the number of survivors is reported and must reach 10^3 per subdomain)
   c5  CROWN with full CROWN intermediate bounds, 8 inputs
+  conv chain and non-chain graphs with ReLU splits (alpha-beta), graphs on L2 / L1 balls, grouped / dilated convolutions
 """
 import pytest
 import torch
@@ -287,3 +288,79 @@ def test_graph_alpha_beta_with_splits_sound(dev, name):
     worst, fewest = _split_soundness(f"{name} alpha-beta with splits", fwd, lo, up, anchors, flat, Cb, b.lower.reshape(B, -1), b.upper.reshape(B, -1),
                                      dev, seed=31)
     assert fewest >= 1000 and worst <= 1.0
+
+
+def _graph_violation(module, points, Cb, lower, upper):
+    """Worst violation (in units of the parity tolerance) of C @ f(x) in [lower, upper] over points [B, n, *shape]."""
+    from oracle import graph_oracle as GO
+
+    B, n = points.shape[0], points.shape[1]
+    worst = 0.0
+    for b in range(B):
+        y = GO.concrete_forward_graph(module, points[b]).reshape(n, -1)
+        v = torch.einsum("so,no->ns", Cb[b].to(y), y)
+        lo_b, up_b = lower[b].to(y), upper[b].to(y)
+        tol_l, tol_u = 1e-4 + 1e-5 * lo_b.abs(), 1e-4 + 1e-5 * up_b.abs()
+        worst = max(worst, float(((lo_b - v) / tol_l).max()), float(((v - up_b) / tol_u).max()))
+    return worst
+
+
+@pytest.mark.parametrize("name", ["fanout_mlp", "residual_s1", "concat_mlp"])
+@pytest.mark.parametrize("p", [2, 1])
+def test_graph_bounds_on_lp_balls_sound(dev, name, p):
+    """CROWN-IBP and the per-domain alpha loop (6 steps) on L2 / L1 balls over graphs that are not chains: 10^4 points per
+    input, drawn inside the ball (random directions scaled to random radii, plus points on the sphere / at the vertices)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from boundflow_b200.ir import InputSpec
+
+    module, x, _lo, _up, C = W.make_graph_cases()[name]
+    B = int(x.shape[0])
+    eps = 0.25 if p == 2 else 0.6
+    mk = InputSpec.l2 if p == 2 else InputSpec.l1
+    spec = mk(value_name="input", center=x.to(dev), eps=eps)
+    Cd = None if C is None else C.to(dev)
+    crown = run_crown_ibp_mlp(module, spec, linear_spec_C=Cd)
+    alpha, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=6, lr=0.1, per_batch_params=True)
+    g = torch.Generator("cpu").manual_seed(40 + p)
+    n0 = x[0].numel()
+    d = torch.randn(B, N_SAMPLES, n0, generator=g, dtype=torch.float64)
+    if p == 2:
+        d = d / d.norm(dim=2, keepdim=True)
+    else:   # L1 ball: a point of the simplex with random signs
+        e = -torch.log(torch.rand(B, N_SAMPLES, n0, generator=g, dtype=torch.float64))
+        d = torch.sign(d) * e / e.sum(dim=2, keepdim=True)
+        k = torch.randint(0, n0, (B, N_SAMPLES // 10), generator=g)   # vertices: all of eps on one coordinate
+        d[:, : N_SAMPLES // 10] = torch.nn.functional.one_hot(k, n0).double() * torch.sign(d[:, : N_SAMPLES // 10])
+    r = torch.rand(B, N_SAMPLES, 1, generator=g, dtype=torch.float64) ** (1.0 / n0)
+    r[:, : N_SAMPLES // 4] = 1.0   # a quarter of the points on the boundary
+    pts = (x.double().reshape(B, 1, n0) + eps * r * d).reshape((B, N_SAMPLES) + tuple(x.shape[1:]))
+    n_out = int(crown.lower.reshape(B, -1).shape[1])
+    Cb = torch.eye(n_out).unsqueeze(0).expand(B, -1, -1) if C is None else (C if C.dim() == 3 else C.unsqueeze(0).expand(B, -1, -1))
+    for what, bnd in (("CROWN", crown), ("alpha-CROWN", alpha)):
+        worst = _graph_violation(module, pts, Cb.double(), bnd.lower.reshape(B, -1).cpu().double(), bnd.upper.reshape(B, -1).cpu().double())
+        assert worst <= 1.0, f"{name} L{p} {what}: worst violation {worst:.2f} x tolerance"
+
+
+@pytest.mark.parametrize("name", ["grouped_dilated_chain", "depthwise_residual"])
+def test_grouped_and_dilated_convolutions_sound(dev, name):
+    """CROWN-IBP and 6 alpha steps on the grouped / dilated convolution cases: 10^4 box samples per input through a
+    float64 forward pass with torch's own grouped, dilated conv2d."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import run_alpha_beta_crown_mlp, run_crown_ibp_mlp
+    from boundflow_b200.ir import InputSpec
+
+    module, _x, lo, up, _C = W.make_grouped_dilated_cases()[name]
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    crown = run_crown_ibp_mlp(module, spec)
+    alpha, _a, _bt, _s = run_alpha_beta_crown_mlp(module, spec, steps=6, lr=0.1, per_batch_params=True)
+    g = torch.Generator("cpu").manual_seed(50)
+    u01 = torch.rand((B, N_SAMPLES) + tuple(lo.shape[1:]), generator=g, dtype=torch.float64)
+    u01[:, : N_SAMPLES // 4] = torch.round(u01[:, : N_SAMPLES // 4])   # a quarter of the points at box corners
+    pts = lo.double().unsqueeze(1) + u01 * (up - lo).double().unsqueeze(1)
+    n_out = int(crown.lower.reshape(B, -1).shape[1])
+    Cb = torch.eye(n_out, dtype=torch.float64).unsqueeze(0).expand(B, -1, -1)
+    for what, bnd in (("CROWN", crown), ("alpha-CROWN", alpha)):
+        worst = _graph_violation(module, pts, Cb, bnd.lower.reshape(B, -1).cpu().double(), bnd.upper.reshape(B, -1).cpu().double())
+        assert worst <= 1.0, f"{name} {what}: worst violation {worst:.2f} x tolerance"
