@@ -6,7 +6,13 @@ stack so that callers (the BaB driver, benchmarks, tests) switch by import:
   forward_ibp_trace_mlp                 <- _forward_ibp_trace_mlp            runtime/crown_ibp.py:101-342
   run_crown_ibp_mlp                     <- run_crown_ibp_mlp                 runtime/crown_ibp.py:2054-2133
   run_crown_ibp_mlp_from_forward_trace  <- same name                         runtime/crown_ibp.py:2136-2230
-  run_alpha_beta_crown_mlp              <- same name (alpha part, beta = 0)  runtime/alpha_beta_crown.py:643-941
+  run_crown_ibp_mlp_with_relu_influence_from_forward_trace <- same name      runtime/crown_ibp.py:2201-2240
+  get_crown_ibp_mlp_stats               <- same name                         runtime/crown_ibp.py:2279-2349
+  run_alpha_crown_mlp                   <- same name                         runtime/alpha_crown.py:137-261
+  run_alpha_beta_crown_mlp              <- same name                         runtime/alpha_beta_crown.py:643-941
+  check_first_layer_infeasible_split    <- same name                         runtime/alpha_beta_crown.py:109-142
+  first_layer_certificate               <- _is_infeasible_split_first_layer_convex_combo, per domain
+                                                                             runtime/alpha_beta_crown.py:391-532
   run_crown_intermediate_mlp            <- the layer-by-layer refinement recipe of
                                            runtime/native_intermediate_refinement.py:923-988
 
@@ -46,6 +52,26 @@ class AlphaCrownStats:
     feasibility: str = "unknown"
     reason: str = "ok"
     infeasible_domains: Optional[torch.Tensor] = None
+
+
+@dataclass
+class AlphaBetaCrownStats:
+    """Result of `check_first_layer_infeasible_split` (AlphaBetaCrownStats, alpha_beta_crown.py:64-76)."""
+
+    feasibility: str
+    reason: str = ""
+    alpha_stats: Optional[Any] = None
+    infeasible_certificate: Optional[Dict[str, Any]] = None
+    branch_choices: Optional[List[Optional[Tuple[str, int]]]] = None
+
+
+@dataclass
+class CrownIbpStats:
+    """Result of `get_crown_ibp_mlp_stats` (crown_ibp.py:63-67)."""
+
+    supported: bool
+    reason: str = ""
+    ops_seen: Tuple[str, ...] = ()
 
 
 def _cuda_device(t: torch.Tensor) -> torch.device:
@@ -1092,6 +1118,61 @@ def run_alpha_beta_crown_mlp(
     stats = AlphaCrownStats(steps=int(steps), lr=float(lr), objective=objective, spec_reduce=spec_reduce, relu_inputs=tuple(chain.relu_input_names))
     stats.branch_choices = branch_choices_from_trace(trace)  # type: ignore[attr-defined]
     return bounds, a_state, b_state, stats
+
+
+def check_first_layer_infeasible_split(module: Any, input_spec: Any, *, relu_split_state: Mapping[str, torch.Tensor]) -> AlphaBetaCrownStats:
+    """`check_first_layer_infeasible_split` (alpha_beta_crown.py:109-142): the first-layer certificate for ONE node as a
+    stats object, `feasibility` "infeasible" when a certificate is found and "unknown" otherwise (no half-spaces, a batch
+    of more than one input set, or no certificate)."""
+    module.validate()
+    spec = normalize_input_spec(input_spec)
+    if int(spec.center.shape[0]) != 1:
+        return AlphaBetaCrownStats(feasibility="unknown", reason="skip (batch!=1)")
+    flags, values, counts = first_layer_certificate(module, spec, relu_split_state)
+    flag, count = int(flags[0]), int(counts[0])
+    if count == 0:
+        return AlphaBetaCrownStats(feasibility="unknown", reason="ok (no first-layer split halfspaces)")
+    if flag == 1:
+        value = float(values[0])
+        kind = "single_halfspace_max_negative" if count == 1 else "convex_combo_max_negative"
+        return AlphaBetaCrownStats(feasibility="infeasible", reason=f"infeasible: {kind} with max {value:.3e}",
+                                   infeasible_certificate={"type": kind, "max_value": value, "n_halfspaces": count})
+    return AlphaBetaCrownStats(feasibility="unknown", reason="ok (no certificate found)" if flag == 0 else "skip (too many halfspaces)")
+
+
+def get_crown_ibp_mlp_stats(module: Any) -> CrownIbpStats:
+    """`get_crown_ibp_mlp_stats` (crown_ibp.py:2279-2349): whether `run_crown_ibp_mlp` of this backend takes the module,
+    with the reason when it does not.  Same conditions as the reference: one INTERVAL_IBP task of linear / relu / conv2d /
+    flatten(start_dim=1) / reshape / add (two inputs) / concat (two or more inputs, feature axis) ops with one output each."""
+    try:
+        module.validate()
+        task = module.get_entry_task()
+        kind = getattr(task.kind, "value", task.kind)
+        if str(kind).lower().split(".")[-1] != "interval_ibp":
+            return CrownIbpStats(False, f"TaskKind={task.kind}")
+        if getattr(module, "task_graph", None) is not None or len(module.tasks) != 1:
+            return CrownIbpStats(False, "multi-task module not supported")
+        ops = tuple(op.op_type for op in task.ops)
+        if not ops:
+            return CrownIbpStats(False, "empty task", ops)
+        unknown = [t for t in ops if t not in ("linear", "relu", "conv2d", "flatten", "reshape", "add", "concat")]
+        if unknown:
+            return CrownIbpStats(False, f"unsupported ops: {unknown}", ops)
+        for i, op in enumerate(task.ops):
+            if len(op.outputs) != 1:
+                return CrownIbpStats(False, f"multi-output op not supported at op {i}: outputs={op.outputs}", ops)
+            if op.op_type == "flatten" and (int(op.attrs.get("start_dim", 1)) != 1 or int(op.attrs.get("end_dim", -1)) != -1):
+                return CrownIbpStats(False, f"unsupported flatten attrs at op {i}: {op.attrs}", ops)
+            if op.op_type == "add" and len(op.inputs) != 2:
+                return CrownIbpStats(False, f"add expects 2 inputs at op {i}, got {len(op.inputs)}", ops)
+            if op.op_type == "concat":
+                if len(op.inputs) < 2:
+                    return CrownIbpStats(False, f"concat expects at least 2 inputs at op {i}, got {len(op.inputs)}", ops)
+                if int(op.attrs.get("axis", 1)) not in (1, -1, -3):
+                    return CrownIbpStats(False, f"unsupported concat axis at op {i}: {op.attrs.get('axis', 1)}", ops)
+        return CrownIbpStats(True, "", ops)
+    except Exception as e:  # a module that does not even validate is unsupported, with the reason
+        return CrownIbpStats(False, str(e))
 
 
 def branch_choices_from_trace(trace: ForwardTrace) -> List[Optional[Tuple[str, int]]]:

@@ -203,3 +203,29 @@ def test_lp_ball_inputs_match_reference_golden_and_oracle(dev, golden, pname, p)
     rows = [(n, torch.cat([r["ha"], r["hb"]])) for n, r in cases]
     split = {k: torch.stack([r[k] for _n, r in cases]).to(dev) for k in ("ha", "hb")}
     check("graph", gmodule, x, split, torch.cat([P["Wa"], P["Wb"]]), torch.cat([P["ba"], P["bb"]]), rows)
+
+
+def test_single_node_wrapper_and_capability_query(dev):
+    """`check_first_layer_infeasible_split` (one node: "infeasible" with a certificate, else "unknown" with the reason) and
+    `get_crown_ibp_mlp_stats` (which modules `run_crown_ibp_mlp` takes)."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import check_first_layer_infeasible_split, get_crown_ibp_mlp_stats
+    from boundflow_b200.ir import InputSpec
+
+    module, _layers, _x, lo, up, cases = W.make_certificate_cases()
+    case = dict(cases)
+    spec1 = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    st = check_first_layer_infeasible_split(module, spec1, relu_split_state={"h1": case["pair_contradiction_needs_steps"].unsqueeze(0).to(dev)})
+    assert st.feasibility == "infeasible" and st.infeasible_certificate["type"] == "convex_combo_max_negative"
+    assert st.infeasible_certificate["max_value"] < -1e-6 and st.infeasible_certificate["n_halfspaces"] == 2
+    st = check_first_layer_infeasible_split(module, spec1, relu_split_state={"h1": case["feasible_pair"].unsqueeze(0).to(dev)})
+    assert st.feasibility == "unknown" and st.infeasible_certificate is None
+    st = check_first_layer_infeasible_split(module, spec1, relu_split_state={"h1": case["no_split"].unsqueeze(0).to(dev)})
+    assert st.feasibility == "unknown" and "no first-layer split halfspaces" in st.reason
+    spec3 = InputSpec.box(value_name="input", lower=lo.expand(3, -1).contiguous().to(dev), upper=up.expand(3, -1).contiguous().to(dev))
+    st = check_first_layer_infeasible_split(module, spec3, relu_split_state={"h1": case["pair_contradiction_needs_steps"].to(dev)})
+    assert st.feasibility == "unknown" and st.reason == "skip (batch!=1)"
+    assert get_crown_ibp_mlp_stats(module).supported
+    assert get_crown_ibp_mlp_stats(W.make_graph_cases()["mini_resnet"][0]).supported
+    bad = get_crown_ibp_mlp_stats(W.make_executor_op_cases()["permute_cnn"][0])
+    assert not bad.supported and "permute" in bad.reason and bad.ops_seen[2] == "permute"
