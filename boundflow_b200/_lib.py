@@ -94,6 +94,7 @@ SIGNATURES = {
     "bf_chain_alpha_crown_objective": (_i, [_p] * 8 + [_i, _f, _p, _p, _i, _f, _i, _i, _f, _f, _f, _p, _sz, _i, _i, _p]),
     "bf_conv2d_dense_rows": (_i, [_p, _p, _p, _i, _p, _p] + [_i] * 12 + [_p]),
     "bf_relu_split_apply": (_i, [_p, _p, _p, _i, _p, _i, _i, _p]),
+    "bf_interval_intersect": (_i, [_p, _p, _p, _p, _p, _i, _i, _p]),
     "bf_rows_add_broadcast": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "bf_adjoint_start_box": (_i, [_p, _p, _p, _i, _i, _i, _p]),
     "bf_adjoint_start_lp": (_i, [_p, _p, _f, _i, _i, _i, _i, _p]),

@@ -606,6 +606,13 @@ extern "C" int bf_relu_split_apply(float* l, float* u, const int8_t* split, int 
   return bf::launch_relu_split_apply(l, u, split, split_stride, infeasible, B, n, bf::as_stream(stream));
 }
 
+extern "C" int bf_interval_intersect(float* l, float* u, const float* cons_l, const float* cons_u, int* infeasible, int B, int n,
+                                     bf_stream_t stream) {
+  BF_REQUIRE(l && u && cons_l && cons_u, BF_E_INVALID, "bf_interval_intersect: null tensor");
+  BF_REQUIRE(B > 0 && n > 0, BF_E_INVALID, "bf_interval_intersect: bad sizes");
+  return bf::launch_interval_intersect(l, u, cons_l, cons_u, infeasible, B, n, bf::as_stream(stream));
+}
+
 extern "C" int bf_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, bf_stream_t stream) {
   BF_REQUIRE(A && v, BF_E_INVALID, "bf_rows_add_broadcast: null tensor");
   BF_REQUIRE(B > 0 && S > 0 && n > 0 && (v_stride == 0 || v_stride == n), BF_E_INVALID, "bf_rows_add_broadcast: bad sizes");

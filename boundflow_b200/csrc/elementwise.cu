@@ -802,6 +802,29 @@ int launch_relu_split_apply(float* l, float* u, const int8_t* split, int split_s
   return BF_OK;
 }
 
+// Intersection of the bounds of a value with a constraint interval, in place: l = max(l, cl), u = min(u, cu); a domain
+// with l > u afterwards on any neuron is flagged.  One block row per domain.
+__global__ void __launch_bounds__(256) interval_intersect_kernel(float* __restrict__ l, float* __restrict__ u, const float* __restrict__ cl,
+                                                                 const float* __restrict__ cu, int* __restrict__ infeasible, int n) {
+  const int b = blockIdx.x;
+  bool bad = false;
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < n; j += gridDim.y * blockDim.x) {
+    const size_t o = (size_t)b * n + j;
+    const float lo = fmaxf(l[o], cl[o]), up = fminf(u[o], cu[o]);
+    l[o] = lo;
+    u[o] = up;
+    bad |= lo > up;
+  }
+  if (infeasible && __syncthreads_or(bad ? 1 : 0) && threadIdx.x == 0) atomicOr(&infeasible[b], 1);
+}
+
+int launch_interval_intersect(float* l, float* u, const float* cl, const float* cu, int* infeasible, int B, int n, cudaStream_t stream) {
+  dim3 grid(B, std::min(ceil_div(n, 256), 64));
+  interval_intersect_kernel<<<grid, 256, 0, stream>>>(l, u, cl, cu, infeasible, n);
+  BF_CHECK_LAUNCH("interval_intersect_kernel");
+  return BF_OK;
+}
+
 // A[b, s, :] += v[b, :] (v_stride = n) or += v[:] (v_stride = 0)
 __global__ void rows_add_broadcast_kernel(float* __restrict__ A, const float* __restrict__ v, int v_stride, long long total, int S,
                                           int n) {

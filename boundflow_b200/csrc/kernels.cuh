@@ -91,6 +91,7 @@ int launch_colmax_abs(const float* A, float* out, int B, int S, int n, cudaStrea
 int launch_relu_adjoint_rows(float* G, const float* Ahat, const float* dpos, const float* dneg, const float* eneg,
                              const float* pre_l, const float* pre_u, float* grad, float* gsum, int B, int S, int n,
                              cudaStream_t stream, const float* gw = nullptr);
+int launch_interval_intersect(float* l, float* u, const float* cl, const float* cu, int* infeasible, int B, int n, cudaStream_t stream);
 int launch_h0_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, cudaStream_t stream);
 // windowed coefficient rows of identity-row sweeps on conv layers (conv.cu)
 struct WindowGeom {

@@ -152,9 +152,12 @@ def forward_ibp_dag(module: Any, input_spec: Any, relu_split_state: Optional[Map
                 if (c is None or not hasattr(c, "lower") or tuple(c.lower.shape) != shape_x or tuple(c.upper.shape) != shape_x
                         or not bool(torch.isfinite(c.lower).all()) or not bool(torch.isfinite(c.upper).all()) or not bool((c.lower <= c.upper).all())):
                     raise ValueError(f"ReLU pre-activation constraint schema differs for {x}")
-                pl = torch.maximum(pl, _f32(c.lower, device).reshape(B, -1))
-                pu = torch.minimum(pu, _f32(c.upper, device).reshape(B, -1))
-                if bool((pl > pu).any()):
+                n = _numel(tr.shape[x])
+                pl, pu = pl.clone(), pu.clone()
+                cl, cu = _f32(c.lower, device).reshape(B, n).contiguous(), _f32(c.upper, device).reshape(B, n).contiguous()
+                empty = torch.zeros(B, dtype=torch.int32, device=device)
+                _lib.check(lib.bf_interval_intersect(_lib.ptr(pl), _lib.ptr(pu), _lib.ptr(cl), _lib.ptr(cu), _lib.ptr(empty), B, n, s))
+                if int(empty.sum()) != 0:
                     raise ValueError(f"infeasible ReLU pre-activation intersection for {x}")
             sp = relu_split_state.get(x) if relu_split_state else None
             if sp is not None:

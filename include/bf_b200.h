@@ -511,6 +511,9 @@ int bf_chain_alpha_crown_objective(const bf_chain* chain,
  *   bf_relu_split_apply   _apply_relu_split, crown_ibp.py:70-98, on the bounds of one ReLU input, in place: split +1
  *                         clamps l to >= 0, -1 clamps u to <= 0; infeasible[b] (int32, may be NULL) is OR-ed with
  *                         "some neuron has l > u".  split int8 [B,n] (stride n) or [1,n] (stride 0).
+ *   bf_interval_intersect the constraint intersection crown_ibp.py:186-209 on the bounds of one ReLU input, in place:
+ *                         l = max(l, cons_l), u = min(u, cons_u) ([B,n] each); infeasible[b] (int32, may be NULL) is OR-ed
+ *                         with "some neuron has l > u".
  *   bf_rows_add_broadcast A[b,s,:] += v[b,:] (v_stride = n) or v[:] (v_stride = 0): the split term -beta*s added to the
  *                         lower coefficients after a ReLU backward step (alpha_beta_crown.py:615-640), and the bias of a
  *                         forward Linear step on rows.
@@ -540,6 +543,8 @@ int bf_chain_alpha_crown_objective(const bf_chain* chain,
  *                         for the next sweep; improve / best_beta may be NULL. */
 int bf_relu_split_apply(float* l, float* u, const int8_t* split, int split_stride, int* infeasible, int B, int n,
                         bf_stream_t stream);
+int bf_interval_intersect(float* l, float* u, const float* cons_l, const float* cons_u, int* infeasible, int B, int n,
+                          bf_stream_t stream);
 int bf_rows_add_broadcast(float* A, const float* v, int v_stride, int B, int S, int n, bf_stream_t stream);
 int bf_adjoint_start_box(float* A0, const float* mid, const float* rad, int B, int S, int n0, bf_stream_t stream);
 int bf_adjoint_start_lp(float* A0, const float* center, float eps, int p, int B, int S, int n0, bf_stream_t stream);
