@@ -252,3 +252,45 @@ def test_query_runtime_groups_chunks_and_keeps_request_order(monkeypatch):
     assert rt.execute(None, []) == []
     with pytest.raises(ValueError):
         CudaQueryRuntime(max_batch_size=0)
+
+
+def test_capability_query_graph_detection_and_dense_conv_weights():
+    """Host logic that needs no GPU: `get_crown_ibp_mlp_stats` (same conditions as the reference, crown_ibp.py:2279-2349),
+    `needs_graph_path`, and the dense equivalent of a grouped, dilated Conv2d weight."""
+    import torch
+
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import get_crown_ibp_mlp_stats, needs_graph_path
+    from boundflow_b200.ir import BFTaskModule, BoundTask, TaskKind, TaskOp
+    from boundflow_b200.network import dense_conv_weight
+
+    chain = W.make_workload("c2", batch=1).module
+    st = get_crown_ibp_mlp_stats(chain)
+    assert st.supported and st.ops_seen[0] == "conv2d" and not needs_graph_path(chain)
+    for name, module in ((k, v[0]) for k, v in W.make_graph_cases().items()):
+        assert needs_graph_path(module), name
+        assert get_crown_ibp_mlp_stats(module).supported, name
+    for name, (module, *_rest) in W.make_executor_op_cases().items():
+        assert not get_crown_ibp_mlp_stats(module).supported, name
+
+    def one_op(op):
+        task = BoundTask(task_id="t", kind=TaskKind.INTERVAL_IBP, ops=[op], input_values=["input"], output_values=[op.outputs[0]])
+        return BFTaskModule(tasks=[task], entry_task_id="t", bindings={"params": {}})
+
+    assert "flatten" in get_crown_ibp_mlp_stats(one_op(TaskOp("flatten", "f", ["input"], ["y"], {"start_dim": 0, "end_dim": -1}))).reason
+    assert "add expects 2 inputs" in get_crown_ibp_mlp_stats(one_op(TaskOp("add", "a", ["input"], ["y"]))).reason
+    assert "concat axis" in get_crown_ibp_mlp_stats(one_op(TaskOp("concat", "c", ["input", "input"], ["y"], {"axis": 2}))).reason
+    # dense equivalents: groups only, dilation only, both, and the identity case
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 6, 9, 9, generator=g)
+    for groups, dil, k in ((3, 1, 3), (1, 2, 3), (2, 3, 2), (6, 1, 1)):
+        Wg = torch.randn(6, 6 // groups, k, k, generator=g)
+        attrs = {"groups": groups, "dilation": (dil, dil)}
+        ref = torch.nn.functional.conv2d(x, Wg, None, 1, 2, dil, groups)
+        got = torch.nn.functional.conv2d(x, dense_conv_weight(Wg, attrs), None, 1, 2)
+        assert torch.allclose(got, ref, atol=1e-5), (groups, dil)
+        assert dense_conv_weight(Wg, attrs) is dense_conv_weight(Wg, attrs)   # cached per weight tensor
+    W1 = torch.randn(4, 6, 3, 3, generator=g)
+    assert dense_conv_weight(W1, {"groups": 1, "dilation": 1}) is W1
+    with pytest.raises(ValueError):
+        dense_conv_weight(torch.randn(5, 3, 3, 3), {"groups": 2})
