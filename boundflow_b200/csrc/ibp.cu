@@ -22,7 +22,9 @@ struct IbpArgs {
 };
 
 // Two CTAs per SM (95 registers).  Forcing three (80 registers) was measured at +2 % on 8192 x 512 x 512, +10 % on the
-// 784-wide first layer and -7 % on 1024 rows and fewer; four CTAs spill and lose everywhere: occupancy is not the limit.
+// 784-wide first layer and -7 % on 1024 rows and fewer; four CTAs spill and lose everywhere: occupancy is not the limit.  A 64 x 128 tile (4 x 8 outputs per thread, 1.0 instead of
+// 1.5 shared-memory bytes per FFMA, 128 registers) was measured at 233 against 226 us on 8192 x 512 x 512 (512 CTAs are 1.7
+// waves of 296), 364 against 391 us on the 784-wide layer and 137 against 105 us on a ragged 260-wide one: not kept.
 __global__ void __launch_bounds__(256) ibp_linear_kernel(IbpArgs g) {
   __shared__ __align__(16) float smem[2 * 3 * ISLAB];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
