@@ -26,8 +26,7 @@ CROWN bounds/s configuration, `--kernels` times single kernels on resident data 
 reports their HBM / FP32 rooflines, `--conv-layers a,b --rows R` times the fused ReLU +
 transposed-convolution layer call on the CNN configurations' layer shapes,
 `--linear-layer D,S,n_cur,n_prev` times the ReLU + Linear backward layer call on one
-synthetic layer (the kernel is chosen by the library's environment switches),
-`--mma-rate` measures the issue rate of tcgen05.mma kind::tf32 on every SM.
+synthetic layer (the kernel is chosen by the library's environment switches).
 """
 from __future__ import annotations
 
@@ -360,38 +359,6 @@ CONV_LAYERS = {  # name: (Co, Ho, Wo, Ci, Hi, Wi, kernel, stride, padding) of th
 }
 
 
-def mma_rate_bench(dev, iters=400000, launches=20):
-    """Issue rate of tcgen05.mma kind::tf32 (M = 128, K = 8) with one issuing thread per SM (`bf_tf32_mma_rate`): clock
-    cycles per MMA and multiply-accumulates per clock and SM for N = 256 and 128, the SM clock sampled while the probe runs,
-    and the fp32-equivalent rate of the three-product split that follows from it."""
-    from boundflow_b200 import _lib
-
-    lib = _lib.load()
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    out = {"sms": sms, "iters": iters, "cases": []}
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    for n_cols in (256, 128):
-        cycles = torch.zeros(sms, dtype=torch.int64, device=dev)
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        for _ in range(launches):   # about half a second per case, so that the clock sampler sees the load; the last launch is read
-            _lib.check(lib.bf_tf32_mma_rate(n_cols, iters, sms, cycles.data_ptr(), status.data_ptr(), stream))
-        torch.cuda.synchronize(dev)
-        if int(status.item()) != 0 or int(cycles.min().item()) < 0:
-            raise RuntimeError("bf_tf32_mma_rate: a bounded wait expired")
-        clk = float(cycles.double().mean().item()) / iters
-        out["cases"].append({"n_cols": n_cols, "clk_per_mma": round(clk, 2), "mac_per_clk_per_sm": round(128 * n_cols * 8 / clk, 1),
-                             "min_clk_per_mma": round(float(cycles.min().item()) / iters, 2), "max_clk_per_mma": round(float(cycles.max().item()) / iters, 2)})
-    out["clocks"] = sampler.stop()
-    mhz = out["clocks"].get("sm_mhz") or out["clocks"].get("sm_max_mhz")
-    if mhz:
-        tf32 = sms * out["cases"][0]["mac_per_clk_per_sm"] * 2 * mhz * 1e6 / 1e12
-        out["tf32_tflops_at_sampled_clock"] = round(tf32, 1)
-        out["fp32_equivalent_3xtf32_tflops"] = round(tf32 / 3, 1)
-    return out
-
-
 def linear_layer_bench(dev, shape, reps):
     """Times the layer-level ReLU backward + Linear backward entry point (`bf_crown_relu_linear_bwd_packed`) on one
     synthetic layer `domains,specs,n_cur,n_prev`; the environment switches (BF_B200_BWD_PERSISTENT, BF_B200_BWD_PAIRS,
@@ -557,7 +524,6 @@ def main():
                     help="time only this CROWN bounds/s configuration and print its figures with per-kernel times (profiling aid)")
     ap.add_argument("--kernels", action="store_true", help="time single kernels on resident data and print their rooflines (profiling aid)")
     ap.add_argument("--conv-layers", default=None, help="comma-separated layer names: time the fused ReLU + transposed-convolution call (profiling aid)")
-    ap.add_argument("--mma-rate", action="store_true", help="measure the tcgen05.mma kind::tf32 issue rate on every SM (profiling aid)")
     ap.add_argument("--linear-layer", default=None, help="domains,specs,n_cur,n_prev: time the ReLU + Linear backward entry point on one layer (profiling aid)")
     ap.add_argument("--rows", type=int, default=2048, help="coefficient rows for --conv-layers")
     ap.add_argument("--reps", type=int, default=10, help="repetitions for --conv-layers")
@@ -604,9 +570,6 @@ def main():
         return
     if args.linear_layer:
         print(json.dumps({"linear_layer": linear_layer_bench(dev, args.linear_layer, args.reps)}))
-        return
-    if args.mma_rate:
-        print(json.dumps({"tf32_mma_rate": mma_rate_bench(dev)}))
         return
     warmup = max(int(args.warmup), 3)
     strong = args.scaling == "strong"

@@ -37,7 +37,6 @@ class LayerDesc(C.Structure):
 # name -> (restype, argtypes); mirrors include/bf_b200.h one to one
 SIGNATURES = {
     "bf_version": (_i, []),
-    "bf_tf32_mma_rate": (_i, [_i, _i, _i, _p, _p, _p]),
     "bf_last_error_string": (C.c_char_p, []),
     "bf_launch_count": (C.c_ulonglong, []),
     "bf_tc_launch_count": (C.c_ulonglong, []),

@@ -12,7 +12,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["chain.cu", "chain_alpha.cu", "crown_linear.cu", "crown_tc.cu", "crown_tc_persist.cu", "crown_tc_adj.cu", "ibp.cu", "elementwise.cu", "conv.cu", "certificate.cu", "mma_rate.cu"]
+SOURCES = ["chain.cu", "chain_alpha.cu", "crown_linear.cu", "crown_tc.cu", "crown_tc_persist.cu", "crown_tc_adj.cu", "ibp.cu", "elementwise.cu", "conv.cu", "certificate.cu"]
 HEADERS = ["common.cuh", "kernels.cuh", "gemm_ffma.cuh", "chain_internal.cuh", "tc_primitives.cuh", os.path.join("..", "..", "include", "bf_b200.h")]
 LIB = os.path.join(os.path.dirname(HERE), "libbf_b200.so")
 

@@ -81,13 +81,6 @@ const char* bf_kernel_timing_slot_name(int slot);
 int bf_kernel_timing_read(int slot, int* launches, float* total_ms);
 int bf_kernel_timing_read_work(int slot, int* launches, float* total_ms, double* bytes, double* flops);
 
-/* Measurement aid: issue rate of tcgen05.mma kind::tf32 (M = 128, N = n_cols, K = 8, operands in shared memory,
- * accumulator in tensor memory).  n_ctas CTAs (one per SM when n_ctas = the SM count); thread 0 of each issues `iters`
- * MMAs back to back, commits and waits (bounded).  cycles: device int64 [n_ctas], the SM clock cycles from the first
- * issue to the commit's arrival, or -1 where the wait gave up (status, a device int, is then set to 1).  No counterpart
- * in the reference: it gives the pipe rate next to which the contraction kernels' MMA rate is read. */
-int bf_tf32_mma_rate(int n_cols, int iters, int n_ctas, long long* cycles, int* status, bf_stream_t stream);
-
 /* ------------------------------------------------------------------------
  * Layer-level kernels
  * ---------------------------------------------------------------------- */

@@ -228,23 +228,3 @@ def test_opt_in_backward_kernels_match_oracle(dev, switch):
         assert_close(best_u[sel.to(dev)], up_ref, "c4 upper at the returned alpha")
     finally:
         os.environ.pop(switch, None)
-
-
-def test_mma_rate_probe_runs_and_reports_plausible_cycles():
-    """`bf_tf32_mma_rate` (the measurement behind `bench.py --mma-rate`): a short run on eight CTAs ends with status 0 and a
-    cycle count per MMA of the order of the pipe's 128 (N = 256) and 64 (N = 128) clocks; bad arguments are refused."""
-    from boundflow_b200 import _lib
-
-    lib = _lib.load()
-    dev = torch.device("cuda", 0)
-    stream = torch.cuda.current_stream(dev).cuda_stream
-    for n_cols, nominal in ((256, 128.0), (128, 64.0)):
-        cycles = torch.zeros(8, dtype=torch.int64, device=dev)
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        for _ in range(2):
-            _lib.check(lib.bf_tf32_mma_rate(n_cols, 4000, 8, cycles.data_ptr(), status.data_ptr(), stream))
-        torch.cuda.synchronize(dev)
-        assert int(status.item()) == 0 and int(cycles.min().item()) > 0
-        per = cycles.double() / 4000
-        assert float(per.min()) >= 0.95 * nominal and float(per.max()) <= 2.0 * nominal, per.tolist()
-    assert lib.bf_tf32_mma_rate(100, 10, 8, cycles.data_ptr(), status.data_ptr(), stream) == _lib.BF_E_INVALID
