@@ -235,6 +235,34 @@ def test_grouped_and_dilated_convolutions_match_reference_golden(dev, golden, na
     assert_close(b.upper.reshape(B, -1), g[f"{name}_alpha_upper_3"].reshape(B, -1), "alpha upper after 3")
 
 
+@pytest.mark.parametrize("name", ["mini_resnet", "fanout_mlp"])
+def test_warm_starts_on_graphs(dev, name):
+    """Warm starts in the value's own shape: a shared alpha of 0.5 equals the default start of `run_alpha_crown_mlp`, a
+    per-domain one the default of `run_alpha_beta_crown_mlp(per_batch_params=True)`; the shared mode refuses a
+    batch-specific warm start like the reference."""
+    from boundflow_b200 import workloads as W
+    from boundflow_b200.crown import AlphaState, run_alpha_beta_crown_mlp, run_alpha_crown_mlp
+    from boundflow_b200.dag import forward_ibp_dag
+    from boundflow_b200.ir import InputSpec
+
+    module, _x, lo, up, C = W.make_graph_cases()[name]
+    B = int(lo.shape[0])
+    spec = InputSpec.box(value_name="input", lower=lo.to(dev), upper=up.to(dev))
+    Cd = None if C is None else C.to(dev)
+    tr = forward_ibp_dag(module, spec)
+    shared = AlphaState({x: torch.full(tuple(tr.shape[x]), 0.5, device=dev) for x in tr.pre_l})
+    a, _sa, _ = run_alpha_crown_mlp(module, spec, linear_spec_C=Cd, steps=3, lr=0.1)
+    b, sb, _ = run_alpha_crown_mlp(module, spec, linear_spec_C=Cd, steps=3, lr=0.1, warm_start=shared)
+    assert torch.equal(a.lower, b.lower) and torch.equal(a.upper, b.upper)
+    assert {k: tuple(v.shape) for k, v in sb.alpha_by_relu_input.items()} == {x: tuple(tr.shape[x]) for x in tr.pre_l}
+    per_domain = AlphaState({x: torch.full((B,) + tuple(tr.shape[x]), 0.5, device=dev) for x in tr.pre_l})
+    c, _a, _b, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=3, lr=0.1, per_batch_params=True, warm_start_alpha=per_domain)
+    d, _a, _b, _s = run_alpha_beta_crown_mlp(module, spec, linear_spec_C=Cd, steps=3, lr=0.1, per_batch_params=True)
+    assert torch.equal(c.lower, d.lower) and torch.equal(c.upper, d.upper)
+    with pytest.raises(ValueError):
+        run_alpha_crown_mlp(module, spec, linear_spec_C=Cd, steps=1, lr=0.1, warm_start=per_domain)
+
+
 def test_building_blocks_against_torch(dev):
     """bf_crown_relu_bwd (incl. rows wider than one chunk) and bf_accumulate."""
     from boundflow_b200 import _lib
