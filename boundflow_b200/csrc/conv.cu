@@ -760,7 +760,11 @@ __global__ void __launch_bounds__(256) onehot_conv_window_kernel(const float* __
 
 // ReLU backward on windows: Lam = A * slope_sel inside the feature map, 0 outside;
 // delta += sum A * icpt_sel + Lam * bias[channel].  T threads per row (T = 32 ... 256, by window size), 256 / T
-// rows per block; a thread walks the window with counters instead of divisions.
+// rows per block.  A thread owns positions of the WH x WW window plane and walks the channels: the image pixel of a
+// position, whether it lies inside the feature map and both offsets are computed once per position.  The kernel is bound
+// by the latency of its reads (the window value, then the slope and intercept that value selects, gathered from the
+// feature map), so the channel loop handles eight channels at a time: eight window values in flight, then eight slopes.
+// When the plane is smaller than T the threads split into T / plane channel groups (thread = group * plane + position).
 template <int T>
 __global__ void __launch_bounds__(256) relu_bwd_window_kernel(const float* __restrict__ A, const float* __restrict__ dpos,
                                                               const float* __restrict__ dneg, const float* __restrict__ epos,
@@ -776,29 +780,57 @@ __global__ void __launch_bounds__(256) relu_bwd_window_kernel(const float* __res
     const int rem = j % (w.HoB * w.WoB);
     const int top = (rem / w.WoB) * w.sy + w.ty, left = (rem % w.WoB) * w.sx + w.tx;
     const int plane = w.WH * w.WW;
-    const int n_win = w.C * plane;
-    const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
-    const float* a = A + (size_t)m * n_win;
-    float* lo = Lam + (size_t)m * n_win;
-    // element e = t + T*i: (c, y, x) advanced incrementally
-    int c = t / plane, r2 = t - c * plane;
-    int y = r2 / w.WW, x = r2 - y * w.WW;
-    const int dy = T / w.WW, dx = T - dy * w.WW;  // step of T elements inside a plane
-    for (int e = t; e < n_win; e += T) {
-      const int Y = top + y, X = left + x;
-      float lam = 0.f;
-      if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
-        const float v = a[e];
-        const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
-        const bool sel = v >= 0.f;
-        lam = v * (sel ? dpos[k] : dneg[k]);
-        acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
-        if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
+    const int HW = w.H * w.W;
+    const size_t dom = (size_t)(m / w.S) * w.C * HW;
+    const float* a_row = A + (size_t)m * w.C * plane;
+    float* lo_row = Lam + (size_t)m * w.C * plane;
+    const int groups = (plane < T) ? T / plane : 1;          // channel groups when the plane is smaller than T
+    const int c0 = (plane < T) ? t / plane : 0;              // this thread's first channel
+    const int p0 = (plane < T) ? t - c0 * plane : t;         // and its first position
+    const int pstep = (plane < T) ? plane : T;               // plane < T: a single position per thread
+    if (c0 < groups) {
+      const size_t astep = (size_t)groups * plane, kstep = (size_t)groups * HW;
+      for (int pos = p0; pos < plane; pos += pstep) {
+        const int y = pos / w.WW, x = pos - y * w.WW;
+        const int Y = top + y, X = left + x;
+        const bool inside = Y >= 0 && Y < w.H && X >= 0 && X < w.W;
+        const float* a = a_row + (size_t)c0 * plane + pos;
+        float* lo = lo_row + (size_t)c0 * plane + pos;
+        if (!inside) {
+          for (int c = c0; c < w.C; c += groups, lo += astep) *lo = 0.f;
+          continue;
+        }
+        size_t k = dom + (size_t)c0 * HW + (size_t)Y * w.W + X;
+        int c = c0;
+        constexpr int U = 8;   // channels in flight
+        for (; c + (U - 1) * groups < w.C; c += U * groups, a += U * astep, lo += U * astep, k += U * kstep) {
+          float v[U], sl[U], ic[U];
+#pragma unroll
+          for (int q = 0; q < U; ++q) v[q] = a[q * astep];
+#pragma unroll
+          for (int q = 0; q < U; ++q) {
+            const size_t kq = k + q * kstep;
+            const bool sel = v[q] >= 0.f;
+            sl[q] = sel ? dpos[kq] : dneg[kq];
+            ic[q] = sel ? (epos ? epos[kq] : 0.f) : (eneg ? eneg[kq] : 0.f);
+          }
+#pragma unroll
+          for (int q = 0; q < U; ++q) {
+            const float lam = v[q] * sl[q];
+            acc = fmaf(v[q], ic[q], acc);
+            if (bias) acc = fmaf(lam, __ldg(bias + c + q * groups), acc);
+            lo[q * astep] = lam;
+          }
+        }
+        for (; c < w.C; c += groups, a += astep, lo += astep, k += kstep) {
+          const float v = *a;
+          const bool sel = v >= 0.f;
+          const float lam = v * (sel ? dpos[k] : dneg[k]);
+          acc = fmaf(v, sel ? (epos ? epos[k] : 0.f) : (eneg ? eneg[k] : 0.f), acc);
+          if (bias) acc = fmaf(lam, __ldg(bias + c), acc);
+          *lo = lam;
+        }
       }
-      lo[e] = lam;
-      x += dx; y += dy;
-      if (x >= w.WW) { x -= w.WW; ++y; }
-      while (y >= w.WH) { y -= w.WH; ++c; }
     }
   }
 #pragma unroll
