@@ -876,14 +876,29 @@ __global__ void __launch_bounds__(256) concretize_window_kernel(const float* __r
   const int n_win = w.C * w.WH * w.WW;
   const size_t dom = (size_t)(m / w.S) * w.C * w.H * w.W;
   float acc = 0.f;
-  for (int e = lane; e < n_win; e += 32) {
-    const int c = e / (w.WH * w.WW), r2 = e - c * (w.WH * w.WW);
-    const int Y = top + r2 / w.WW, X = left + r2 % w.WW;
-    if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
-      const float v = Awin[(size_t)m * n_win + e];
-      const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
-      acc = fmaf(v, mid[k], acc);
-      acc = fmaf(sgn * fabsf(v), rad[k], acc);
+  // four elements of a lane per iteration: their index arithmetic first, then all loads, then the sums in element order
+  // (the loop is bound by the latency of its gathered reads, like the ReLU pass on windows)
+  for (int e0 = lane; e0 < n_win; e0 += 128) {
+    float v[4], cm[4], cr[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = e0 + 32 * q;
+      v[q] = cm[q] = cr[q] = 0.f;
+      if (e < n_win) {
+        const int c = e / (w.WH * w.WW), r2 = e - c * (w.WH * w.WW);
+        const int Y = top + r2 / w.WW, X = left + r2 % w.WW;
+        if (Y >= 0 && Y < w.H && X >= 0 && X < w.W) {
+          const size_t k = dom + ((size_t)c * w.H + Y) * w.W + X;
+          v[q] = Awin[(size_t)m * n_win + e];
+          cm[q] = mid[k];
+          cr[q] = rad[k];
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {   // an element outside the window or the image contributes exact zeros
+      acc = fmaf(v[q], cm[q], acc);
+      acc = fmaf(sgn * fabsf(v[q]), cr[q], acc);
     }
   }
 #pragma unroll
