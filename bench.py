@@ -348,7 +348,7 @@ def kernel_rooflines(dev, peaks):
         Wc, bc = torch.randn(Co, Ci, k, k, generator=g).to(dev), torch.randn(Co, generator=g).to(dev)
         ol, ou = torch.empty(Bq, Co * Ho * Ho, device=dev), torch.empty(Bq, Co * Ho * Ho, device=dev)
         s = timed(lambda: _lib.check(lib.bf_ibp_conv2d(lo.data_ptr(), up.data_ptr(), _lib.IN_LOWER_UPPER, 0, Wc.data_ptr(), bc.data_ptr(), None, 0, None, None,
-                                                       ol.data_ptr(), ou.data_ptr(), None, Bq, Ci, Hi, Hi, Co, Ho, Ho, k, k, stv, stv, pd, pd, st)), 10, True)
+                                                       ol.data_ptr(), ou.data_ptr(), None, Bq, Ci, Hi, Hi, Co, k, k, stv, stv, pd, pd, st)), 10, True)
         out[f"ibp_conv2d_kernel_{tag}"] = hbm_roofline("ibp_conv2d_kernel", s["ibp_conv2d_kernel"], peaks, "L2 flushed between launches")
     return out
 
@@ -471,9 +471,12 @@ def crown_bounds_secondary(world: int, rank: int, dev, only=None, with_slots=Fal
             if name == "c1":
                 res = run_crown_ibp_mlp(wl.module, spec, linear_spec_C=C).lower
             elif name == "c2":
-                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=512)[0].lower
-            elif name == "c5":  # about 4096 coefficient rows per sweep
-                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=max(64, 4096 // max(1, b - a)))[0].lower
+                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=2048)[0].lower
+            elif name == "c5":
+                # about 32768 coefficient rows per sweep (20 GB of coefficient buffers): the sweeps of one layer's identity rows are
+                # independent, so larger chunks only make fewer, larger launches - same bounds bit for bit, 339 -> 284 ms at 64 inputs
+                # against 4096 rows per sweep
+                res = run_crown_intermediate_mlp(wl.module, spec, linear_spec_C=C, chunk_rows=max(64, 32768 // max(1, b - a)))[0].lower
             else:
                 tr = ibp_trace(wl.module, spec)
                 a0 = adaptive_alpha_from_trace(tr)
@@ -542,6 +545,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # the one collective of a step gathers a few hundred KB: it gains nothing from in-switch multicast buffers, and
+        # without them a rank that ends does not touch its peers' mappings
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     from boundflow_b200.csrc import build as _build
@@ -643,11 +649,16 @@ def main():
     tc_status = compile_chain(wl.module, (784,), dev).tc_status()
 
     secondary = None if args.no_secondary else crown_bounds_secondary(world, rank, dev)
+    if world > 1:
+        # every rank leaves the process group TOGETHER, before rank 0 goes on alone with the single-kernel timings: a peer
+        # that tears its communicator down while another rank still runs kernels with its own communicator alive has
+        # ended that rank with "illegal memory access" (seen once, at 4 ranks)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        dist.destroy_process_group()
     kernels = None if (args.no_secondary or rank != 0) else kernel_rooflines(dev, peaks)
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return
 
     lower, verdict, res = out
@@ -708,8 +719,6 @@ def main():
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": arm.cores, "kind": arm.kind,
                                 "sample": arm.describe() + f"; 1 warm-up pass, median of 3 ({t:.2f} s per pass)"}
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

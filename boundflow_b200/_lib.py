@@ -142,8 +142,24 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
+        setattr(lib, name, _exact_arity(fn, len(args), name))
     _lib = lib
     return lib
+
+
+def _exact_arity(fn, n_args: int, name: str):
+    """ctypes refuses a call with too FEW arguments but passes surplus ones on, which silently shifts every later argument of
+    a call written against an older signature (sizes, strides, the stream).  Every entry point is therefore called through
+    this check: exactly the declared number of arguments, or TypeError."""
+
+    def call(*args):
+        if len(args) != n_args:
+            raise TypeError(f"{name} takes exactly {n_args} arguments ({len(args)} given)")
+        return fn(*args)
+
+    call.__name__ = name
+    call.restype, call.argtypes = fn.restype, fn.argtypes
+    return call
 
 
 def check(code: int) -> None:

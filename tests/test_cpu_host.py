@@ -51,6 +51,11 @@ def test_argument_validation_needs_no_gpu(lib):
         _lib.check(_lib.BF_E_INVALID)
     with pytest.raises(NotImplementedError):
         _lib.check(_lib.BF_E_UNSUPPORTED)
+    # a surplus argument (a call written against an older signature) is refused instead of shifting the later ones
+    with pytest.raises(TypeError):
+        lib.bf_concretize(None, None, None, None, None, 0, 1, 1, 1, 1, None)
+    with pytest.raises(TypeError):
+        lib.bf_concretize(None, None, None, None, None, 0, 1, 1, 1)
 
 
 def test_chain_workspace_queries(lib):
