@@ -650,9 +650,8 @@ def main():
 
     secondary = None if args.no_secondary else crown_bounds_secondary(world, rank, dev)
     if world > 1:
-        # every rank leaves the process group TOGETHER, before rank 0 goes on alone with the single-kernel timings: a peer
-        # that tears its communicator down while another rank still runs kernels with its own communicator alive has
-        # ended that rank with "illegal memory access" (seen once, at 4 ranks)
+        # every rank leaves the process group TOGETHER, before rank 0 goes on alone with the single-kernel timings, so
+        # that no rank runs kernels while a peer tears its communicator down
         torch.cuda.synchronize(dev)
         dist.barrier()
         dist.destroy_process_group()
